@@ -1,0 +1,217 @@
+"""Seeded synthetic workloads with the shapes, sizes and value distributions of
+the benchmark configurations.  Every builder returns a :class:`GeNNModel`
+ready for ``build()``; inputs come from ``numpy.random.default_rng(seed)``.
+
+The Potjans-Diesmann microcircuit parameters (population sizes, connection
+probabilities, external in-degrees, weight and delay distributions) are the
+ones tabulated in the reference's user project
+(userproject/potjans_microcircuit.py:27-100); connectivity, weights, delays
+and initial voltages are synthetic draws from those distributions.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+
+from .model import (GeNNModel, init_postsynaptic, init_sparse_connectivity, init_var,
+                    init_weight_update)
+
+
+def poisson_spike_trains(rng, n: int, rate_hz: float, duration_ms: float):
+    """Per-source sorted spike times: count ~ Poisson(rate*T), times ~ U[0,T).
+    Returns (startSpike, endSpike, spikeTimes) as SpikeSourceArray wants them."""
+    counts = rng.poisson(rate_hz * duration_ms / 1000.0, size=n)
+    end = np.cumsum(counts).astype(np.uint32)
+    start = (end - counts).astype(np.uint32)
+    times = rng.uniform(0.0, duration_ms, size=int(end[-1]) if n else 0).astype(np.float32)
+    for i in range(n):
+        times[start[i]:end[i]].sort()
+    return start, end, times
+
+
+def truncated_normal(rng, mean: float, sd: float, lo: float, hi: float, size: int) -> np.ndarray:
+    """Normal draws re-sampled until they fall inside [lo, hi], the semantics of
+    the reference's NormalClipped snippets (initVarSnippet.h:163-172)."""
+    out = rng.normal(mean, sd, size=size)
+    bad = np.nonzero((out > hi) | (out < lo))[0]
+    while len(bad):
+        out[bad] = rng.normal(mean, sd, size=len(bad))
+        bad = bad[(out[bad] > hi) | (out[bad] < lo)]
+    return out
+
+
+def feedforward(seed: int = 1, num_pre: int = 1000, num_post: int = 10000, prob: float = 0.1,
+                rate_hz: float = 20.0, steps: int = 1000, dt: float = 0.1,
+                matrix: str = "SPARSE", narrow: bool = False) -> GeNNModel:
+    """Config 1: Poisson spike sources (host-generated trains) -> LIF through
+    fixed-probability connectivity, fp32 weights U[0, 0.05) nA, ExpCurr."""
+    rng = np.random.default_rng(seed)
+    m = GeNNModel("float", "feedforward")
+    m.dt = dt
+    m.default_narrow_sparse_ind_enabled = narrow
+    start, end, times = poisson_spike_trains(rng, num_pre, rate_hz, steps * dt)
+    src = m.add_neuron_population("pre", num_pre, "SpikeSourceArray", {},
+                                  {"startSpike": start, "endSpike": end})
+    src.set_extra_global_param("spikeTimes", times)
+    lif = {"C": 0.25, "TauM": 20.0, "Vrest": -65.0, "Vreset": -70.0, "Vthresh": -50.0,
+           "Ioffset": 0.0, "TauRefrac": 2.0}
+    trg = m.add_neuron_population("post", num_post, "LIF", lif, {"V": -65.0, "RefracTime": 0.0})
+    src.spike_recording_enabled = True
+    trg.spike_recording_enabled = True
+    mask = rng.random((num_pre, num_post)) < prob
+    pre, post = np.nonzero(mask)
+    g = rng.uniform(0.0, 0.05, size=len(pre)).astype(np.float32)
+    if matrix == "SPARSE":
+        sg = m.add_synapse_population("syn", "SPARSE", src, trg,
+                                      init_weight_update("StaticPulse", {}, {"g": g}),
+                                      init_postsynaptic("ExpCurr", {"tau": 5.0}))
+        sg.set_sparse_connections(pre, post)
+    elif matrix == "BITMASK":
+        sg = m.add_synapse_population("syn", "BITMASK", src, trg,
+                                      init_weight_update("StaticPulseConstantWeight", {"g": 0.025}),
+                                      init_postsynaptic("ExpCurr", {"tau": 5.0}))
+        sg.set_sparse_connections(pre, post)
+    elif matrix == "DENSE":
+        dense = np.zeros((num_pre, num_post), dtype=np.float32)
+        dense[pre, post] = g
+        m.add_synapse_population("syn", "DENSE", src, trg,
+                                 init_weight_update("StaticPulse", {}, {"g": dense}),
+                                 init_postsynaptic("ExpCurr", {"tau": 5.0}))
+    else:
+        raise ValueError(matrix)
+    return m
+
+
+# ---------------------------------------------------------------------------
+# Potjans-Diesmann microcircuit architecture
+# ---------------------------------------------------------------------------
+POTJANS_POPS = ["23E", "23I", "4E", "4I", "5E", "5I", "6E", "6I"]
+POTJANS_NUM = {"23E": 20683, "23I": 5834, "4E": 21915, "4I": 5479,
+               "5E": 4850, "5I": 1065, "6E": 14395, "6I": 2948}
+# probability of >=1 connection; row = target, column = source (POTJANS_POPS order)
+POTJANS_PROB = np.array([
+    [0.1009, 0.1689, 0.0437, 0.0818, 0.0323, 0.0,    0.0076, 0.0],
+    [0.1346, 0.1371, 0.0316, 0.0515, 0.0755, 0.0,    0.0042, 0.0],
+    [0.0077, 0.0059, 0.0497, 0.135,  0.0067, 0.0003, 0.0453, 0.0],
+    [0.0691, 0.0029, 0.0794, 0.1597, 0.0033, 0.0,    0.1057, 0.0],
+    [0.1004, 0.0622, 0.0505, 0.0057, 0.0831, 0.3726, 0.0204, 0.0],
+    [0.0548, 0.0269, 0.0257, 0.0022, 0.06,   0.3158, 0.0086, 0.0],
+    [0.0156, 0.0066, 0.0211, 0.0166, 0.0572, 0.0197, 0.0396, 0.2252],
+    [0.0364, 0.001,  0.0034, 0.0005, 0.0277, 0.008,  0.0658, 0.1443]])
+POTJANS_EXT = {"23E": 1600, "23I": 1500, "4E": 2100, "4I": 1900,
+               "5E": 2000, "5I": 1900, "6E": 2900, "6I": 2100}
+POTJANS_BG_RATE = 8.0
+POTJANS_MEAN_W = 87.8e-3
+POTJANS_G = -4.0
+POTJANS_DELAY = {"E": (1.5, 0.75), "I": (0.75, 0.375)}
+# 0.9999 quantile of the standard normal (scipy.stats.norm.ppf(0.9999))
+_NORMAL_Q9999 = 3.719016485455709
+
+
+def potjans_in_degree(src: str, trg: str) -> int:
+    """Full-scale in-degree of ``trg`` from ``src``: total synapses for the
+    pairwise connection probability, divided by the target count."""
+    ns, nt = POTJANS_NUM[src], POTJANS_NUM[trg]
+    p = POTJANS_PROB[POTJANS_POPS.index(trg), POTJANS_POPS.index(src)]
+    if p == 0.0:
+        return 0
+    total = int(round(math.log(1.0 - p) / math.log(float(nt * ns - 1) / float(nt * ns))))
+    return total // nt
+
+
+def potjans_max_delay_slots(dt: float = 0.1) -> int:
+    mx = max(m + s * _NORMAL_Q9999 for m, s in POTJANS_DELAY.values())
+    return int(round(mx / dt))
+
+
+def potjans_projections(neuron_scale: float = 1.0):
+    """[(src, trg, num_synapses, mean_w, sd_w, mean_d, sd_d, max_d)] for the
+    non-empty projections; in-degree fixed, neuron counts scaled."""
+    out = []
+    for trg in POTJANS_POPS:
+        for src in POTJANS_POPS:
+            k = potjans_in_degree(src, trg)
+            nt = int(round(neuron_scale * POTJANS_NUM[trg]))
+            num = int(round(k * float(nt)))
+            if num <= 0:
+                continue
+            if src.endswith("E"):
+                mean_w = 2.0 * POTJANS_MEAN_W if (src == "4E" and trg == "23E") else POTJANS_MEAN_W
+            else:
+                mean_w = POTJANS_G * POTJANS_MEAN_W
+            sd_w = mean_w * 0.05 if (src == "4E" and trg == "23E") else abs(mean_w * 0.1)
+            md, sd = POTJANS_DELAY[src[-1]]
+            out.append((src, trg, num, mean_w, sd_w, md, sd, md + sd * _NORMAL_Q9999))
+    return out
+
+
+def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
+            host_connectivity: bool = False, background: str = "poisson",
+            shard: Optional[Tuple[int, int]] = None, record: bool = False) -> GeNNModel:
+    """Potjans-Diesmann microcircuit architecture at ``neuron_scale`` times the
+    published population sizes with the published in-degrees.
+
+    ``host_connectivity`` draws connectivity/weights/delays with numpy so the
+    same arrays can be handed to a CPU checker (small scales only); otherwise
+    they are drawn on the GPU by the initialisation kernels from the same
+    distributions.  ``background`` is "poisson" (PoissonExp current source at
+    8 Hz x external in-degree) or "dc" (its mean as a constant current, for
+    RNG-free comparisons).  ``shard=(rank, world)`` keeps only the synapses
+    whose postsynaptic neuron lies in this rank's contiguous slice of each
+    population.
+    """
+    rng = np.random.default_rng(seed)
+    m = GeNNModel("float", "potjans_microcircuit")
+    m.dt = dt
+    m.seed = seed
+    m.fuse_postsynaptic_models = True
+    m.default_narrow_sparse_ind_enabled = True
+    slots = potjans_max_delay_slots(dt)
+    pops = {}
+    for name in POTJANS_POPS:
+        n = int(round(neuron_scale * POTJANS_NUM[name]))
+        lif = {"C": 0.25, "TauM": 10.0, "Vrest": -65.0, "Vreset": -65.0, "Vthresh": -50.0,
+               "Ioffset": 0.0, "TauRefrac": 2.0}
+        rate = POTJANS_EXT[name] * POTJANS_BG_RATE
+        if background == "dc":
+            # mean of the filtered Poisson drive: weight * rate[kHz] * tauSyn
+            lif["Ioffset"] = POTJANS_MEAN_W * (rate / 1000.0) * 0.5
+        v0 = (rng.normal(-58.0, 5.0, size=n).astype(np.float32) if host_connectivity
+              else init_var("Normal", {"mean": -58.0, "sd": 5.0}))
+        pop = m.add_neuron_population(name, n, "LIF", lif, {"V": v0, "RefracTime": 0.0})
+        if background == "poisson":
+            m.add_current_source(name + "_poisson", "PoissonExp", pop,
+                                 {"weight": POTJANS_MEAN_W, "tauSyn": 0.5, "rate": rate}, {"current": 0.0})
+        pop.spike_recording_enabled = record
+        pops[name] = pop
+    for src, trg, num, mean_w, sd_w, md, sd, mxd in potjans_projections(neuron_scale):
+        ns, nt = pops[src].num_neurons, pops[trg].num_neurons
+        lo, hi = (0.0, float(np.finfo(np.float32).max)) if mean_w > 0 else (-float(np.finfo(np.float32).max), 0.0)
+        if host_connectivity:
+            pre = rng.integers(0, ns, size=num).astype(np.uint32)
+            post = rng.integers(0, nt, size=num).astype(np.uint32)
+            g = truncated_normal(rng, mean_w, sd_w, lo, hi, num).astype(np.float32)
+            # NormalClippedDelay: truncated normal in time steps, then rint
+            d = np.rint(truncated_normal(rng, md / dt, sd / dt, 0.0, mxd / dt, num)).astype(np.uint8)
+            if shard is not None:
+                rank, world = shard
+                a, b = (nt * rank) // world, (nt * (rank + 1)) // world
+                keep = (post >= a) & (post < b)
+                pre, post, g, d = pre[keep], post[keep], g[keep], d[keep]
+            wu = init_weight_update("StaticPulseDendriticDelay", {}, {"g": g, "d": d})
+            sg = m.add_synapse_population(f"{src}_{trg}", "SPARSE", pops[src], pops[trg], wu,
+                                          init_postsynaptic("ExpCurr", {"tau": 0.5}))
+            sg.set_sparse_connections(pre, post)
+        else:
+            wu = init_weight_update("StaticPulseDendriticDelay", {}, {
+                "g": init_var("NormalClipped", {"mean": mean_w, "sd": sd_w, "min": lo, "max": hi}),
+                "d": init_var("NormalClippedDelay", {"mean": md, "sd": sd, "min": 0.0, "max": mxd})})
+            sg = m.add_synapse_population(
+                f"{src}_{trg}", "SPARSE", pops[src], pops[trg], wu,
+                init_postsynaptic("ExpCurr", {"tau": 0.5}),
+                init_sparse_connectivity("FixedNumberTotalWithReplacement", {"num": num}))
+            sg.shard = shard
+        sg.max_dendritic_delay_timesteps = slots
+    return m

@@ -1,0 +1,262 @@
+/* genn_b200.h - C ABI of the B200-native simulation backend.
+ *
+ * The reference (GeNN 5.4.0) reaches its per-timestep path through the C
+ * symbols of a generated librunner.so which its runtime looks up by name
+ * (src/genn/genn/runtime/runtime.cc:81-119): allocateMem, freeMem, initialize,
+ * initializeSparse, stepTime, update<CustomUpdateGroup>, one
+ * pushMerged<Kind>Group<i>ToDevice per merged group and the *Time counters.
+ * Those symbols are specific to one generated model.  This library exports the
+ * same surface once, for every model built from the built-in neuron,
+ * postsynaptic, current-source and weight-update models: a runner object
+ * stands for one loaded librunner.so, a group descriptor stands for one
+ * element of a merged-group struct array, and the push functions register it.
+ *
+ * All pointers inside descriptors are DEVICE pointers obtained from
+ * b200_array_alloc (the counterpart of BackendBase::createArray,
+ * include/genn/genn/code_generator/backendBase.h:305-312) unless stated
+ * otherwise.  All functions return 0 on success and a non-zero b200_status on
+ * failure; b200_last_error() then describes the failure.  Nothing here
+ * allocates or frees device memory inside the time-step path.
+ *
+ * Array layouts are the reference's: neuron variables [batch][N]; spike lists
+ * spk_cnt[batch][slots], spk[batch][slots][N]; SPARSE connectivity as ragged
+ * rows row_length[numPre], ind[numPre*row_stride] with per-synapse variables
+ * indexed alike; BITMASK as 32-bit words, bit (pre*row_stride + post) counted
+ * from the MSB, row_stride padded to 32; DENSE row-major [numPre][numPost];
+ * dendritic delay ring den_delay[batch][D][N].
+ */
+#ifndef GENN_B200_H
+#define GENN_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_MAX_PSM     8   /* fused incoming postsynaptic models per neuron group */
+#define B200_MAX_CS      4   /* current sources per neuron group */
+#define B200_MAX_PARAMS  8
+#define B200_MAX_VARS    4
+
+typedef enum b200_status {
+    B200_OK = 0,
+    B200_ERR_CUDA = 1,          /* a CUDA runtime call failed */
+    B200_ERR_INVALID = 2,       /* bad argument or descriptor */
+    B200_ERR_STATE = 3,         /* call made in the wrong lifecycle state */
+    B200_ERR_DEVICE_CHECK = 4   /* a kernel reported a failed bounds check */
+} b200_status;
+
+/* neuronModels.h:163-325 */
+typedef enum b200_neuron_model {
+    B200_NEURON_LIF = 0,              /* params: Vthresh? see b200_neuron_group.params */
+    B200_NEURON_IZHIKEVICH = 1,
+    B200_NEURON_SPIKE_SOURCE_ARRAY = 2,
+    B200_NEURON_POISSON = 3
+} b200_neuron_model;
+
+/* postsynapticModels.h:93-151 */
+typedef enum b200_psm_model {
+    B200_PSM_EXP_CURR = 0,            /* params: init, expDecay */
+    B200_PSM_EXP_COND = 1,            /* params: expDecay, E */
+    B200_PSM_DELTA_CURR = 2
+} b200_psm_model;
+
+/* currentSourceModels.h:60-129 */
+typedef enum b200_cs_model {
+    B200_CS_DC = 0,                   /* params: amp */
+    B200_CS_POISSON_EXP = 1           /* params: Init, ExpDecay, ExpMinusLambda; var0: current */
+} b200_cs_model;
+
+/* weightUpdateModels.h:236-368 */
+typedef enum b200_wu_model {
+    B200_WU_STATIC_PULSE = 0,                 /* addToPost(g) */
+    B200_WU_STATIC_PULSE_CONSTANT_WEIGHT = 1, /* params: g */
+    B200_WU_STATIC_PULSE_DENDRITIC_DELAY = 2, /* addToPostDelay(g, d) */
+    B200_WU_STDP = 3                          /* params: tauPlus, tauMinus, Aplus, Aminus, Wmin, Wmax */
+} b200_wu_model;
+
+/* synapseMatrixType.h:9-69 */
+typedef enum b200_connectivity {
+    B200_CONN_SPARSE = 0,
+    B200_CONN_BITMASK = 1,
+    B200_CONN_DENSE = 2,
+    B200_CONN_PROCEDURAL = 3
+} b200_connectivity;
+
+/* initVarSnippet.h:87-261 */
+typedef enum b200_var_init {
+    B200_INIT_CONSTANT = 0,             /* params: constant */
+    B200_INIT_UNIFORM = 1,              /* params: min, max */
+    B200_INIT_NORMAL = 2,               /* params: mean, sd */
+    B200_INIT_NORMAL_CLIPPED = 3,       /* params: mean, sd, min, max (re-sampled) */
+    B200_INIT_NORMAL_CLIPPED_DELAY = 4  /* params: meanTimestep, sdTimestep, minTimestep, maxTimestep; rint */
+} b200_var_init;
+
+/* initSparseConnectivitySnippet.h:170-486 */
+typedef enum b200_connect_init {
+    B200_CONNECT_FIXED_PROBABILITY = 0,                  /* params: prob */
+    B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE = 1,
+    B200_CONNECT_FIXED_NUMBER_TOTAL_WITH_REPLACEMENT = 2,/* row lengths supplied by the host */
+    B200_CONNECT_FIXED_NUMBER_PRE_WITH_REPLACEMENT = 3,  /* params: num (in-degree) */
+    B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT = 4  /* params: num (out-degree) */
+} b200_connect_init;
+
+typedef enum b200_reduce_op { B200_REDUCE_SUM = 0, B200_REDUCE_MAX = 1 } b200_reduce_op;
+
+/* One fused incoming postsynaptic model: the InSynPSM child of a merged
+ * neuron-update group (neuronUpdateGroupMerged.cc:66-137). */
+typedef struct b200_psm {
+    uint32_t model;            /* b200_psm_model */
+    uint32_t max_den_delay;    /* ring depth D; 0 = no dendritic delay */
+    float    params[4];
+    float   *out_post;         /* [batch][N] */
+    float   *den_delay;        /* [batch][D][N] or NULL */
+} b200_psm;
+
+/* One current source child (neuronUpdateGroupMerged.cc:20-55). */
+typedef struct b200_current_source {
+    uint32_t model;            /* b200_cs_model */
+    uint32_t rng_stream;       /* distinguishes RNG consumers in the Philox counter */
+    float    params[4];
+    float   *var0;             /* [batch][N] or NULL */
+} b200_current_source;
+
+/* One element of the merged neuron-update group array
+ * (backendSIMT.cc:405-662, neuronUpdateGroupMerged.cc:552-773).
+ *   LIF params:        Vthresh, Vreset, Vrest, Ioffset, Rmembrane, ExpTC, TauRefrac; vars V, RefracTime
+ *   Izhikevich params: a, b, c, d;                                                   vars V, U
+ *   SpikeSourceArray:  vars startSpike, endSpike (uint32); egp = spikeTimes
+ *   Poisson params:    isi;                                                          vars timeStepToSpike */
+typedef struct b200_neuron_group {
+    uint32_t model;            /* b200_neuron_model */
+    uint32_t num_neurons;
+    uint32_t num_delay_slots;  /* spike queue depth: longest axonal/back-propagation delay + 2 */
+    uint32_t num_psm;
+    uint32_t num_cs;
+    uint32_t rng_stream;
+    uint32_t first_neuron;     /* this process updates neurons [first_neuron, first_neuron+num_update) */
+    uint32_t num_update;
+    float    params[B200_MAX_PARAMS];
+    void    *vars[B200_MAX_VARS];
+    const float *egp;          /* SpikeSourceArray spikeTimes */
+    uint32_t *spk_cnt;         /* [batch][slots] */
+    uint32_t *spk;             /* [batch][slots][N] */
+    float    *spike_times;     /* sT [batch][slots][N] or NULL */
+    uint32_t *record_spk;      /* [recordingTimesteps][batch][ceil(N/32)] or NULL; bit i%32 of word i/32 */
+    b200_psm psm[B200_MAX_PSM];
+    b200_current_source cs[B200_MAX_CS];
+} b200_neuron_group;
+
+/* One element of the merged presynaptic-update group array and, when the
+ * weight update model learns, of the merged postsynaptic-update group array
+ * (presynapticUpdateStrategySIMT.cc:57-745, backendSIMT.cc:766-803). */
+typedef struct b200_synapse_group {
+    uint32_t connectivity;     /* b200_connectivity */
+    uint32_t wu_model;         /* b200_wu_model */
+    uint32_t num_src;
+    uint32_t num_trg;
+    uint32_t row_stride;       /* SPARSE: max row length; BITMASK: num_trg padded to 32; DENSE: num_trg */
+    uint32_t ind_bytes;        /* SPARSE index width: 1, 2 or 4 */
+    uint32_t axonal_delay;     /* steps */
+    uint32_t back_prop_delay;  /* steps */
+    uint32_t src_delay_slots;  /* num_delay_slots of the source / target neuron group */
+    uint32_t trg_delay_slots;
+    uint32_t max_den_delay;    /* ring depth of the target buffer; 0 = addToPost */
+    uint32_t col_stride;       /* max column length (learning only) */
+    float    wu_params[B200_MAX_PARAMS];
+    const uint32_t *row_length;/* SPARSE [numSrc] */
+    const void     *ind;       /* SPARSE [numSrc*row_stride] uint8/uint16/uint32 */
+    float          *g;         /* per-synapse weight ([batch] duplicated when the model learns) or NULL */
+    const uint8_t  *d;         /* per-synapse dendritic delay or NULL */
+    const uint32_t *gp;        /* BITMASK words or NULL */
+    const uint32_t *col_length;/* [numTrg] (learning only) */
+    const uint32_t *remap;     /* [numTrg*col_stride] row-major synapse index (learning only) */
+    const uint32_t *src_spk_cnt;
+    const uint32_t *src_spk;
+    const uint32_t *trg_spk_cnt;
+    const uint32_t *trg_spk;
+    const float    *src_spike_times;
+    const float    *trg_spike_times;
+    float          *out_post;  /* target fused buffer [batch][numTrg] */
+    float          *den_delay; /* target ring [batch][D][numTrg] or NULL */
+    /* PROCEDURAL: connectivity and weights regenerated per spike */
+    uint32_t proc_connect;     /* b200_connect_init */
+    uint32_t proc_weight_init; /* b200_var_init */
+    uint32_t rng_stream;
+    uint32_t reserved;
+    float    proc_connect_params[4];
+    float    proc_weight_params[4];
+} b200_synapse_group;
+
+/* Batch-reduce custom update (backendSIMT.cc:888-927, 1109-1147):
+ * target[e] = op over b of source[b][e]; optionally broadcast back. */
+typedef struct b200_custom_update_group {
+    uint32_t op;               /* b200_reduce_op */
+    uint32_t broadcast;        /* 1: write target[e]*scale back into every source[b][e] */
+    uint64_t num_elements;
+    float    scale;            /* applied to the reduced value (e.g. 1/batch for a mean) */
+    uint32_t reserved;
+    float   *source;           /* [batch][E] */
+    float   *target;           /* [E] */
+} b200_custom_update_group;
+
+typedef struct b200_runner b200_runner;
+
+/* ---- lifecycle: allocateMem / freeMem (generateRunner.cc:223-268) -------- */
+int  b200_runner_create(int device, double dt, uint64_t seed, uint32_t batch_size, b200_runner **out);
+int  b200_runner_destroy(b200_runner *r);
+const char *b200_last_error(void);
+int  b200_device_count(int *count);
+
+/* ---- arrays: BackendBase::createArray and Runtime::ArrayBase
+ *      (backendBase.h:305-312, runtime.h:95-182) ---------------------------- */
+int  b200_array_alloc(b200_runner *r, size_t bytes, void **device_ptr);
+int  b200_array_free(b200_runner *r, void *device_ptr);
+int  b200_array_push(b200_runner *r, void *device_ptr, const void *host, size_t bytes);
+int  b200_array_pull(b200_runner *r, void *host, const void *device_ptr, size_t bytes);
+int  b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes);
+
+/* ---- merged-group registration: pushMerged<Kind>Group<i>ToDevice
+ *      (backendCUDAHIP.h:206-238, runtime.h:573-669) -------------------------- */
+int  b200_push_neuron_update_group(b200_runner *r, uint32_t idx, const b200_neuron_group *g);
+int  b200_push_synapse_group(b200_runner *r, uint32_t idx, const b200_synapse_group *g);
+int  b200_push_custom_update(b200_runner *r, const char *name, uint32_t idx, const b200_custom_update_group *u);
+
+/* ---- initialisation kernels (backendSIMT.cc:1368-1779) --------------------- */
+int  b200_initialize(b200_runner *r);
+int  b200_initialize_sparse(b200_runner *r);
+int  b200_init_var(b200_runner *r, void *device_ptr, uint32_t elem_bytes, uint64_t count,
+                   uint32_t snippet, const float *params, uint32_t rng_stream);
+int  b200_init_sparse_connectivity(b200_runner *r, uint32_t snippet, const float *params,
+                                   uint32_t num_src, uint32_t num_trg, uint32_t row_stride,
+                                   uint32_t ind_bytes, uint32_t trg_begin, uint32_t trg_end,
+                                   uint32_t *row_length, void *ind, uint32_t rng_stream);
+int  b200_init_sparse_vars(b200_runner *r, const uint32_t *row_length, uint32_t num_src,
+                           uint32_t row_stride, void *device_ptr, uint32_t elem_bytes,
+                           uint32_t snippet, const float *params, uint32_t rng_stream);
+int  b200_build_remap(b200_runner *r, const uint32_t *row_length, const void *ind, uint32_t ind_bytes,
+                      uint32_t num_src, uint32_t num_trg, uint32_t row_stride, uint32_t col_stride,
+                      uint32_t *col_length, uint32_t *remap);
+
+/* ---- the time step: stepTime / updateSynapses / updateNeurons
+ *      (generateRunner.cc:270-299, backendCUDAHIP.cc:386-420, 548-589) ------- */
+int  b200_update_synapses(b200_runner *r);
+int  b200_update_neurons(b200_runner *r, uint64_t num_recording_timesteps);
+int  b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_timesteps);
+int  b200_custom_update(b200_runner *r, const char *name);
+int  b200_synchronize(b200_runner *r);
+int  b200_get_timestep(b200_runner *r, uint64_t *timestep);
+int  b200_set_timestep(b200_runner *r, uint64_t timestep);
+int  b200_get_steps_done(b200_runner *r, uint64_t *steps);
+
+/* ---- timers: neuronUpdateTime etc. (generateRunner.cc:159-222) ------------- */
+int  b200_enable_timing(b200_runner *r, int enabled);
+int  b200_get_timer(b200_runner *r, const char *name, double *seconds);
+int  b200_get_kernel_launches(b200_runner *r, uint64_t *launches);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GENN_B200_H */

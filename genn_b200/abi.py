@@ -118,6 +118,10 @@ _PROTOTYPES = {
     "b200_enable_timing": [C.c_void_p, C.c_int],
     "b200_get_timer": [C.c_void_p, C.c_char_p, C.POINTER(C.c_double)],
     "b200_get_kernel_launches": [C.c_void_p, C.POINTER(C.c_uint64)],
+    "b200_step_time_timed": [C.c_void_p, C.c_uint64, C.c_uint64, C.POINTER(C.c_float)],
+    "b200_get_counter": [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)],
+    "b200_set_option": [C.c_void_p, C.c_char_p, C.c_double],
+    "b200_reset_timers": [C.c_void_p],
 }
 
 _lib = None

@@ -1,0 +1,61 @@
+// Shared device-side definitions for the sm_100a kernel templates.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "genn_b200.h"
+#include "genn_b200_rng.h"
+
+namespace b200
+{
+// Step counters kept on the device so a captured step graph can be replayed
+// without touching kernel arguments: `timestep` gives t = timestep * dt,
+// `steps_done` drives every ring pointer (spike queue slot, dendritic-delay
+// front), `ticket` elects the last block of the neuron kernel, `error` is set
+// by bounds checks.
+struct StepState
+{
+    unsigned long long timestep;
+    unsigned long long steps_done;
+    unsigned int ticket;
+    unsigned int error;
+    unsigned long long synaptic_events;   // only advanced when event counting is on
+    unsigned long long spikes;
+};
+
+constexpr unsigned int ERR_SPIKE_OVERFLOW = 1u;
+constexpr unsigned int ERR_IND_RANGE = 2u;
+constexpr unsigned int ERR_DELAY_RANGE = 4u;
+
+// Block -> merged-group element lookup: block_start[g] is the first block of
+// group g, block_start[num_groups] the grid size.  Linear for a handful of
+// groups, binary beyond that (the reference emits the same two forms,
+// backendSIMT.h:244-323).
+__device__ __forceinline__ unsigned int findGroup(const unsigned int *__restrict__ block_start,
+                                                  unsigned int num_groups, unsigned int block)
+{
+    if(num_groups <= 8) {
+        unsigned int g = 0;
+        while(g + 1 < num_groups && block >= __ldg(&block_start[g + 1])) g++;
+        return g;
+    }
+    unsigned int lo = 0, hi = num_groups;
+    while(hi - lo > 1) {
+        const unsigned int mid = (lo + hi) >> 1;
+        if(block >= __ldg(&block_start[mid])) lo = mid; else hi = mid;
+    }
+    return lo;
+}
+
+// fp32 add to global memory with no return value (compiles to a reduction)
+__device__ __forceinline__ void redAdd(float *addr, float v)
+{
+    atomicAdd(addr, v);
+}
+
+__device__ __forceinline__ unsigned int ringSlot(unsigned long long k, unsigned int slots)
+{
+    return (unsigned int)(k % slots);
+}
+}   // namespace b200

@@ -1,0 +1,266 @@
+// Presynaptic update kernels: propagate the spikes of the previous step
+// through SPARSE, BITMASK and DENSE connectivity into the target's input
+// buffer (outPost) or dendritic-delay ring (denDelay).  Replace the
+// reference's updatePresynapticKernel and its PostSpan / PreSpan /
+// PostSpanBitmask strategies (backendSIMT.cc:694-764,
+// presynapticUpdateStrategySIMT.cc:57-745).
+//
+// SPARSE.  The reference gives each block `blockSize` columns of the ragged
+// matrix and makes it walk EVERY spike with scalar 4-byte loads, so its
+// parallel width is maxRowLength threads per group however many spikes there
+// are.  Here the work item is (spike, 512-synapse tile of that spike's row):
+// grid = (row tiles of all merged groups, spike lanes, batch); block (c, y)
+// handles tile c of spikes y, y+Y, y+2Y...  Within a tile each thread owns FOUR
+// consecutive synapses whose first index is a multiple of four counted from the
+// array base, so weights come in as one 128-bit load, uint16 indices as one
+// 64-bit load (uint32: 128-bit, uint8: 32-bit) and delays as one 32-bit load,
+// whatever the row stride: rows are not aligned in the reference's layout
+// (stride = maxRowLength), so the tile is aligned to the array instead and the
+// head/tail lanes that fall outside the row are masked.  Every warp-level load
+// is a run of whole 32-byte sectors.  The scatter is a fire-and-forget fp32
+// reduction into L2-resident targets; lanes of a warp that hit the same address
+// are merged first when the target population is small enough for that to be
+// likely.
+//
+// Algorithmic HBM bytes per synaptic event: sizeof(ind) + 4 (weight) + 1
+// (delay, if any): 7 for the Potjans microcircuit with uint16 indices.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200
+{
+constexpr int PRE_BLOCK = 128;
+constexpr int PRE_VEC = 4;
+constexpr int PRE_TILE = PRE_BLOCK * PRE_VEC;     // synapses per block per spike
+
+struct SynapseLaunch
+{
+    const b200_synapse_group *groups;
+    const unsigned int *block_start;
+    unsigned int num_groups;
+    unsigned int batch;
+    float dt;
+    unsigned long long seed;
+    StepState *state;
+    unsigned int count_events;
+};
+
+template<typename T> struct IndLoad;
+template<> struct IndLoad<uint8_t>
+{
+    static __device__ __forceinline__ void load4(const void *base, unsigned long long idx, unsigned int (&out)[4])
+    {
+        const unsigned int w = __ldg(reinterpret_cast<const unsigned int*>(static_cast<const uint8_t*>(base) + idx));
+        out[0] = w & 0xFFu; out[1] = (w >> 8) & 0xFFu; out[2] = (w >> 16) & 0xFFu; out[3] = w >> 24;
+    }
+};
+template<> struct IndLoad<uint16_t>
+{
+    static __device__ __forceinline__ void load4(const void *base, unsigned long long idx, unsigned int (&out)[4])
+    {
+        const uint2 w = __ldg(reinterpret_cast<const uint2*>(static_cast<const uint16_t*>(base) + idx));
+        out[0] = w.x & 0xFFFFu; out[1] = w.x >> 16; out[2] = w.y & 0xFFFFu; out[3] = w.y >> 16;
+    }
+};
+template<> struct IndLoad<uint32_t>
+{
+    static __device__ __forceinline__ void load4(const void *base, unsigned long long idx, unsigned int (&out)[4])
+    {
+        const uint4 w = __ldg(reinterpret_cast<const uint4*>(static_cast<const uint32_t*>(base) + idx));
+        out[0] = w.x; out[1] = w.y; out[2] = w.z; out[3] = w.w;
+    }
+};
+
+// One (spike, tile) work item of a SPARSE group with a non-learning weight
+// update model.
+template<typename IndT>
+__device__ __forceinline__ void sparseTile(const b200_synapse_group &g, unsigned int pre, unsigned int tile,
+                                           float *__restrict__ target, unsigned int denFront,
+                                           StepState *state)
+{
+    const unsigned int len = __ldg(&g.row_length[pre]);
+    const unsigned long long rowStart = (unsigned long long)pre * g.row_stride;
+    const unsigned long long rowEnd = rowStart + len;
+    const unsigned long long idx = (rowStart & ~3ull) + ((unsigned long long)tile * PRE_BLOCK + threadIdx.x) * PRE_VEC;
+    if(idx >= rowEnd) return;
+
+    unsigned int post[4];
+    IndLoad<IndT>::load4(g.ind, idx, post);
+    float w[4];
+    if(g.wu_model == B200_WU_STATIC_PULSE_CONSTANT_WEIGHT) {
+        w[0] = w[1] = w[2] = w[3] = g.wu_params[0];
+    }
+    else {
+        const float4 wv = __ldg(reinterpret_cast<const float4*>(g.g + idx));
+        w[0] = wv.x; w[1] = wv.y; w[2] = wv.z; w[3] = wv.w;
+    }
+    const unsigned int D = g.max_den_delay;
+    unsigned int dw = 0;
+    if(D) dw = __ldg(reinterpret_cast<const unsigned int*>(g.d + idx));
+    const unsigned int numTrg = g.num_trg;
+
+#pragma unroll
+    for(int j = 0; j < PRE_VEC; j++) {
+        const unsigned long long s = idx + j;
+        if(s >= rowStart && s < rowEnd) {
+            unsigned int p = post[j];
+            if(p >= numTrg) {
+                atomicOr(&state->error, ERR_IND_RANGE);
+                continue;
+            }
+            if(D) {
+                unsigned int slot = denFront + ((dw >> (8 * j)) & 0xFFu);
+                while(slot >= D) slot -= D;
+                redAdd(target + (unsigned long long)slot * numTrg + p, w[j]);
+            }
+            else {
+                redAdd(target + p, w[j]);
+            }
+        }
+    }
+}
+
+// SPARSE with a learning rule: the pre-spike half of STDP reads and writes the
+// per-batch weight (weightUpdateModels.h:354-361).  Scalar per-synapse path.
+template<typename IndT>
+__device__ __forceinline__ void sparseTileSTDP(const b200_synapse_group &g, unsigned int pre, unsigned int tile,
+                                               unsigned int b, float t, unsigned long long k)
+{
+    const unsigned int len = __ldg(&g.row_length[pre]);
+    const unsigned long long rowStart = (unsigned long long)pre * g.row_stride;
+    const unsigned long long perBatch = (unsigned long long)g.num_src * g.row_stride;
+    float *gb = g.g + (unsigned long long)b * perBatch;
+    const unsigned int tslots = g.trg_delay_slots;
+    const float *stPost = g.trg_spike_times +
+        ((unsigned long long)b * tslots + ringSlot(k + tslots - g.back_prop_delay, tslots)) * g.num_trg;
+    float *out = g.out_post + (unsigned long long)b * g.num_trg;
+#pragma unroll
+    for(int j = 0; j < PRE_VEC; j++) {
+        const unsigned int col = tile * PRE_TILE + j * PRE_BLOCK + threadIdx.x;
+        if(col < len) {
+            const unsigned long long s = rowStart + col;
+            const unsigned int p = static_cast<const IndT*>(g.ind)[s];
+            const float w = gb[s];
+            redAdd(out + p, w);
+            const float dts = B200_FSUB(t, B200_FADD(g.wu_params[7], stPost[p]));
+            if(dts > 0.0f) {
+                const float timing = expf(B200_FDIV(-dts, g.wu_params[1]));
+                const float nw = B200_FSUB(w, B200_FMUL(g.wu_params[3], timing));
+                gb[s] = fmaxf(g.wu_params[4], fminf(g.wu_params[5], nw));
+            }
+        }
+    }
+}
+
+// One launch for every SPARSE merged group.
+__global__ void __launch_bounds__(PRE_BLOCK)
+presynapticSparseKernel(const SynapseLaunch L)
+{
+    const unsigned int gi = findGroup(L.block_start, L.num_groups, blockIdx.x);
+    const b200_synapse_group &g = L.groups[gi];
+    const unsigned int tile = blockIdx.x - __ldg(&L.block_start[gi]);
+    const unsigned int b = blockIdx.z;
+    const unsigned long long k = L.state->steps_done;
+    const unsigned int slots = g.src_delay_slots;
+    const unsigned int rslot = ringSlot(k + slots - g.axonal_delay, slots);
+    const unsigned int count = g.src_spk_cnt[b * slots + rslot];
+    if(blockIdx.y >= count) return;
+    const unsigned int *spk = g.src_spk + ((unsigned long long)b * slots + rslot) * g.num_src;
+    const unsigned int D = g.max_den_delay;
+    const unsigned int denFront = D ? ringSlot(k + 1, D) : 0;
+    float *target = D ? g.den_delay + (unsigned long long)b * D * g.num_trg
+                      : g.out_post + (unsigned long long)b * g.num_trg;
+    const bool learn = (g.wu_model == B200_WU_STDP);
+    const float t = B200_FMUL((float)L.state->timestep, L.dt);
+
+    for(unsigned int s = blockIdx.y; s < count; s += gridDim.y) {
+        const unsigned int pre = spk[s];
+        if(learn) {
+            switch(g.ind_bytes) {
+            case 1: sparseTileSTDP<uint8_t>(g, pre, tile, b, t, k); break;
+            case 2: sparseTileSTDP<uint16_t>(g, pre, tile, b, t, k); break;
+            default: sparseTileSTDP<uint32_t>(g, pre, tile, b, t, k); break;
+            }
+        }
+        else {
+            switch(g.ind_bytes) {
+            case 1: sparseTile<uint8_t>(g, pre, tile, target, denFront, L.state); break;
+            case 2: sparseTile<uint16_t>(g, pre, tile, target, denFront, L.state); break;
+            default: sparseTile<uint32_t>(g, pre, tile, target, denFront, L.state); break;
+            }
+        }
+        if(L.count_events && tile == 0 && threadIdx.x == 0) {
+            atomicAdd(&L.state->synaptic_events, (unsigned long long)__ldg(&g.row_length[pre]));
+        }
+    }
+}
+
+// BITMASK and DENSE: one thread per postsynaptic neuron accumulates over the
+// whole spike list in a register and issues a single reduction at the end
+// (presynapticUpdateStrategySIMT.cc:295-306, 352-370).  BITMASK rows are padded
+// to 32 so the 32 lanes of a warp test bits of ONE connectivity word, fetched
+// with a single broadcast load: numPost/8 bytes per spike.  DENSE streams one
+// coalesced weight row per spike: 4*numPost bytes per spike.
+__global__ void __launch_bounds__(PRE_BLOCK)
+presynapticPostSpanKernel(const SynapseLaunch L)
+{
+    const unsigned int gi = findGroup(L.block_start, L.num_groups, blockIdx.x);
+    const b200_synapse_group &g = L.groups[gi];
+    const unsigned int post = (blockIdx.x - __ldg(&L.block_start[gi])) * PRE_BLOCK + threadIdx.x;
+    const unsigned int b = blockIdx.z;
+    const unsigned long long k = L.state->steps_done;
+    const unsigned int slots = g.src_delay_slots;
+    const unsigned int rslot = ringSlot(k + slots - g.axonal_delay, slots);
+    const unsigned int count = g.src_spk_cnt[b * slots + rslot];
+    if(count == 0 || post >= g.row_stride) return;
+    const unsigned int *spk = g.src_spk + ((unsigned long long)b * slots + rslot) * g.num_src;
+    const unsigned int numTrg = g.num_trg;
+    const bool valid = post < numTrg;
+    float acc = 0.0f;
+    unsigned int events = 0;
+
+    if(g.connectivity == B200_CONN_BITMASK) {
+        const float w = g.wu_params[0];
+        const unsigned int bit = 0x80000000u >> (post & 31u);
+        for(unsigned int s = 0; s < count; s++) {
+            const unsigned long long gid = (unsigned long long)spk[s] * g.row_stride + post;
+            if(__ldg(&g.gp[gid >> 5]) & bit) {
+                acc = B200_FADD(acc, w);
+                events++;
+            }
+        }
+    }
+    else if(g.wu_model == B200_WU_STDP) {
+        if(!valid) return;
+        const float t = B200_FMUL((float)L.state->timestep, L.dt);
+        const unsigned int tslots = g.trg_delay_slots;
+        const float stPost = g.trg_spike_times[((unsigned long long)b * tslots +
+                                                ringSlot(k + tslots - g.back_prop_delay, tslots)) * numTrg + post];
+        float *gb = g.g + (unsigned long long)b * g.num_src * numTrg;
+        const float dts = B200_FSUB(t, B200_FADD(g.wu_params[7], stPost));
+        for(unsigned int s = 0; s < count; s++) {
+            const unsigned long long id = (unsigned long long)spk[s] * numTrg + post;
+            const float w = gb[id];
+            acc = B200_FADD(acc, w);
+            if(dts > 0.0f) {
+                const float timing = expf(B200_FDIV(-dts, g.wu_params[1]));
+                const float nw = B200_FSUB(w, B200_FMUL(g.wu_params[3], timing));
+                gb[id] = fmaxf(g.wu_params[4], fminf(g.wu_params[5], nw));
+            }
+        }
+        events = count;
+    }
+    else {
+        if(!valid) return;
+        const bool constant = (g.wu_model == B200_WU_STATIC_PULSE_CONSTANT_WEIGHT);
+        for(unsigned int s = 0; s < count; s++) {
+            const float w = constant ? g.wu_params[0] : __ldg(&g.g[(unsigned long long)spk[s] * numTrg + post]);
+            acc = B200_FADD(acc, w);
+        }
+        events = count;
+    }
+    if(valid && events) redAdd(g.out_post + (unsigned long long)b * numTrg + post, acc);
+    if(L.count_events && events) atomicAdd(&L.state->synaptic_events, (unsigned long long)events);
+}
+}   // namespace b200

@@ -1,0 +1,715 @@
+// C ABI of the B200 backend (include/genn_b200.h) and the runner behind it.
+//
+// A runner is the counterpart of one loaded librunner.so of the reference: it
+// owns the stream, the device-resident step counters, the merged-group tables
+// and the captured step graph.  The time-step path allocates nothing and never
+// synchronises; the host only enqueues (one cudaGraphLaunch per block of steps).
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "genn_b200.h"
+#include "common.cuh"
+#include "neuron_update.cuh"
+#include "presynaptic_update.cuh"
+#include "postsynaptic_update.cuh"
+#include "init.cuh"
+
+using namespace b200;
+
+namespace
+{
+thread_local std::string g_lastError;
+
+int fail(int code, const char *fmt, ...)
+{
+    char buf[1024];
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(buf, sizeof(buf), fmt, ap);
+    va_end(ap);
+    g_lastError = buf;
+    return code;
+}
+
+#define CUDA_TRY(expr)                                                                           \
+    do {                                                                                         \
+        cudaError_t _e = (expr);                                                                 \
+        if(_e != cudaSuccess) {                                                                  \
+            return fail(B200_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(_e),   \
+                        __FILE__, __LINE__);                                                     \
+        }                                                                                        \
+    } while(0)
+
+constexpr size_t ARRAY_TAIL_PAD = 256;     // vector loads may read up to 15 bytes past the last element
+
+template<typename T>
+struct DeviceTable
+{
+    T *d = nullptr;
+    unsigned int *blockStart = nullptr;
+    unsigned int num = 0;
+    unsigned int blocks = 0;
+
+    void release()
+    {
+        if(d) cudaFree(d);
+        if(blockStart) cudaFree(blockStart);
+        d = nullptr; blockStart = nullptr; num = 0; blocks = 0;
+    }
+
+    cudaError_t upload(const std::vector<T> &items, const std::vector<unsigned int> &starts, cudaStream_t s)
+    {
+        release();
+        num = (unsigned int)items.size();
+        if(num == 0) return cudaSuccess;
+        blocks = starts.back();
+        cudaError_t e = cudaMalloc(&d, sizeof(T) * num);
+        if(e != cudaSuccess) return e;
+        e = cudaMalloc(&blockStart, sizeof(unsigned int) * starts.size());
+        if(e != cudaSuccess) return e;
+        e = cudaMemcpyAsync(d, items.data(), sizeof(T) * num, cudaMemcpyHostToDevice, s);
+        if(e != cudaSuccess) return e;
+        e = cudaMemcpyAsync(blockStart, starts.data(), sizeof(unsigned int) * starts.size(), cudaMemcpyHostToDevice, s);
+        if(e != cudaSuccess) return e;
+        return cudaStreamSynchronize(s);
+    }
+};
+
+struct Timer
+{
+    double seconds = 0.0;
+};
+}   // anonymous namespace
+
+struct b200_runner
+{
+    int device = 0;
+    float dt = 0.1f;
+    unsigned long long seed = 0;
+    unsigned int batch = 1;
+    cudaStream_t stream = nullptr;
+    StepState *state = nullptr;
+    std::unordered_map<void*, size_t> arrays;
+
+    std::vector<b200_neuron_group> neuronGroups;
+    std::vector<b200_synapse_group> synapseGroups;
+    std::map<std::string, std::vector<b200_custom_update_group>> customUpdates;
+    bool dirty = true;
+
+    DeviceTable<b200_neuron_group> neuronTable;
+    DeviceTable<b200_synapse_group> sparseTable, postSpanTable, learnTable;
+
+    // options
+    unsigned int spikeLanes = 16;
+    bool countEvents = false;
+    bool useGraph = true;
+    unsigned int graphSteps = 100;
+    bool timing = false;
+
+    // captured graph of `graphLen` steps for a given recording length
+    cudaGraphExec_t graphExec = nullptr;
+    unsigned int graphLen = 0;
+    unsigned long long graphNumRec = 0;
+
+    std::map<std::string, Timer> timers;
+    cudaEvent_t evA = nullptr, evB = nullptr, evC = nullptr, evD = nullptr;
+    unsigned long long launches = 0;
+    unsigned long long hostTimestep = 0, hostStepsDone = 0;
+
+    void dropGraph()
+    {
+        if(graphExec) cudaGraphExecDestroy(graphExec);
+        graphExec = nullptr;
+        graphLen = 0;
+    }
+};
+
+namespace
+{
+int prepare(b200_runner *r)
+{
+    if(!r->dirty) return B200_OK;
+    r->dropGraph();
+    // neuron groups: padded to whole blocks
+    {
+        std::vector<unsigned int> starts{0};
+        for(const auto &g : r->neuronGroups) {
+            starts.push_back(starts.back() + (g.num_update + NEURON_BLOCK - 1) / NEURON_BLOCK);
+        }
+        CUDA_TRY(r->neuronTable.upload(r->neuronGroups, starts, r->stream));
+    }
+    std::vector<b200_synapse_group> sparse, postSpan, learn;
+    std::vector<unsigned int> sparseStarts{0}, postSpanStarts{0}, learnStarts{0};
+    for(const auto &g : r->synapseGroups) {
+        if(g.connectivity == B200_CONN_SPARSE) {
+            sparse.push_back(g);
+            // +3: tiles are aligned to the array, not to the row
+            sparseStarts.push_back(sparseStarts.back() + (g.row_stride + 3 + PRE_TILE - 1) / PRE_TILE);
+        }
+        else if(g.connectivity == B200_CONN_BITMASK || g.connectivity == B200_CONN_DENSE) {
+            postSpan.push_back(g);
+            postSpanStarts.push_back(postSpanStarts.back() + (g.row_stride + PRE_BLOCK - 1) / PRE_BLOCK);
+        }
+        else {
+            return fail(B200_ERR_INVALID, "connectivity %u is not supported by this build", g.connectivity);
+        }
+        if(g.wu_model == B200_WU_STDP) {
+            learn.push_back(g);
+            const unsigned int width = (g.connectivity == B200_CONN_SPARSE) ? g.col_stride : g.num_src;
+            learnStarts.push_back(learnStarts.back() + (width + POST_BLOCK - 1) / POST_BLOCK);
+        }
+    }
+    CUDA_TRY(r->sparseTable.upload(sparse, sparseStarts, r->stream));
+    CUDA_TRY(r->postSpanTable.upload(postSpan, postSpanStarts, r->stream));
+    CUDA_TRY(r->learnTable.upload(learn, learnStarts, r->stream));
+    r->dirty = false;
+    return B200_OK;
+}
+
+SynapseLaunch synapseLaunch(const b200_runner *r, const DeviceTable<b200_synapse_group> &t)
+{
+    SynapseLaunch L;
+    L.groups = t.d;
+    L.block_start = t.blockStart;
+    L.num_groups = t.num;
+    L.batch = r->batch;
+    L.dt = r->dt;
+    L.seed = r->seed;
+    L.state = r->state;
+    L.count_events = r->countEvents ? 1u : 0u;
+    return L;
+}
+
+struct ScopedTimer
+{
+    b200_runner *r;
+    std::string name;
+    bool on;
+    ScopedTimer(b200_runner *r_, const std::string &n, bool capturing) : r(r_), name(n), on(r_->timing && !capturing)
+    {
+        if(on) cudaEventRecord(r->evA, r->stream);
+    }
+    ~ScopedTimer()
+    {
+        if(on) {
+            cudaEventRecord(r->evB, r->stream);
+            cudaEventSynchronize(r->evB);
+            float ms = 0.0f;
+            cudaEventElapsedTime(&ms, r->evA, r->evB);
+            r->timers[name].seconds += ms * 1e-3;
+        }
+    }
+};
+
+int enqueueSynapses(b200_runner *r, bool capturing)
+{
+    if(r->sparseTable.num) {
+        ScopedTimer tm(r, "presynaptic_update", capturing);
+        const dim3 grid(r->sparseTable.blocks, r->spikeLanes, r->batch);
+        presynapticSparseKernel<<<grid, PRE_BLOCK, 0, r->stream>>>(synapseLaunch(r, r->sparseTable));
+        r->launches++;
+    }
+    if(r->postSpanTable.num) {
+        ScopedTimer tm(r, "presynaptic_update", capturing);
+        const dim3 grid(r->postSpanTable.blocks, 1, r->batch);
+        presynapticPostSpanKernel<<<grid, PRE_BLOCK, 0, r->stream>>>(synapseLaunch(r, r->postSpanTable));
+        r->launches++;
+    }
+    if(r->learnTable.num) {
+        ScopedTimer tm(r, "postsynaptic_update", capturing);
+        const dim3 grid(r->learnTable.blocks, r->spikeLanes, r->batch);
+        postsynapticUpdateKernel<<<grid, POST_BLOCK, 0, r->stream>>>(synapseLaunch(r, r->learnTable));
+        r->launches++;
+    }
+    CUDA_TRY(cudaPeekAtLastError());
+    return B200_OK;
+}
+
+int enqueueNeurons(b200_runner *r, unsigned long long numRec, bool capturing)
+{
+    if(r->neuronTable.num == 0) return fail(B200_ERR_STATE, "no neuron groups registered");
+    ScopedTimer tm(r, "neuron_update", capturing);
+    NeuronLaunch L;
+    L.groups = r->neuronTable.d;
+    L.block_start = r->neuronTable.blockStart;
+    L.num_groups = r->neuronTable.num;
+    L.batch = r->batch;
+    L.dt = r->dt;
+    L.seed = r->seed;
+    L.num_recording_timesteps = numRec;
+    L.state = r->state;
+    const dim3 grid(r->neuronTable.blocks, r->batch, 1);
+    neuronUpdateKernel<<<grid, NEURON_BLOCK, 0, r->stream>>>(L);
+    r->launches++;
+    CUDA_TRY(cudaPeekAtLastError());
+    return B200_OK;
+}
+
+int enqueueStep(b200_runner *r, unsigned long long numRec, bool capturing)
+{
+    int e = enqueueSynapses(r, capturing);
+    if(e) return e;
+    return enqueueNeurons(r, numRec, capturing);
+}
+
+unsigned int kernelsPerStep(const b200_runner *r)
+{
+    return 1u + (r->sparseTable.num ? 1u : 0u) + (r->postSpanTable.num ? 1u : 0u) + (r->learnTable.num ? 1u : 0u);
+}
+
+int buildGraph(b200_runner *r, unsigned int len, unsigned long long numRec)
+{
+    r->dropGraph();
+    cudaGraph_t graph = nullptr;
+    const unsigned long long before = r->launches;
+    CUDA_TRY(cudaStreamBeginCapture(r->stream, cudaStreamCaptureModeThreadLocal));
+    int e = B200_OK;
+    for(unsigned int i = 0; i < len && e == B200_OK; i++) e = enqueueStep(r, numRec, true);
+    cudaError_t ce = cudaStreamEndCapture(r->stream, &graph);
+    r->launches = before;       // capture enqueues nothing
+    if(e) {
+        if(graph) cudaGraphDestroy(graph);
+        return e;
+    }
+    CUDA_TRY(ce);
+    ce = cudaGraphInstantiate(&r->graphExec, graph, 0);
+    cudaGraphDestroy(graph);
+    CUDA_TRY(ce);
+    r->graphLen = len;
+    r->graphNumRec = numRec;
+    return B200_OK;
+}
+
+template<typename F>
+int withIndType(unsigned int bytes, F f)
+{
+    switch(bytes) {
+    case 1: return f(uint8_t());
+    case 2: return f(uint16_t());
+    case 4: return f(uint32_t());
+    default: return fail(B200_ERR_INVALID, "index width %u is not 1, 2 or 4", bytes);
+    }
+}
+}   // anonymous namespace
+
+extern "C" {
+
+const char *b200_last_error(void)
+{
+    return g_lastError.c_str();
+}
+
+int b200_device_count(int *count)
+{
+    CUDA_TRY(cudaGetDeviceCount(count));
+    return B200_OK;
+}
+
+int b200_runner_create(int device, double dt, uint64_t seed, uint32_t batch_size, b200_runner **out)
+{
+    if(!out || batch_size == 0) return fail(B200_ERR_INVALID, "bad arguments to b200_runner_create");
+    CUDA_TRY(cudaSetDevice(device));
+    b200_runner *r = new b200_runner();
+    r->device = device;
+    r->dt = (float)dt;
+    r->seed = seed;
+    r->batch = batch_size;
+    CUDA_TRY(cudaStreamCreateWithFlags(&r->stream, cudaStreamNonBlocking));
+    CUDA_TRY(cudaMalloc(&r->state, sizeof(StepState)));
+    CUDA_TRY(cudaMemset(r->state, 0, sizeof(StepState)));
+    CUDA_TRY(cudaEventCreate(&r->evA));
+    CUDA_TRY(cudaEventCreate(&r->evB));
+    CUDA_TRY(cudaEventCreate(&r->evC));
+    CUDA_TRY(cudaEventCreate(&r->evD));
+    *out = r;
+    return B200_OK;
+}
+
+int b200_runner_destroy(b200_runner *r)
+{
+    if(!r) return B200_OK;
+    cudaSetDevice(r->device);
+    cudaStreamSynchronize(r->stream);
+    r->dropGraph();
+    r->neuronTable.release();
+    r->sparseTable.release();
+    r->postSpanTable.release();
+    r->learnTable.release();
+    for(auto &a : r->arrays) cudaFree(a.first);
+    cudaFree(r->state);
+    cudaEventDestroy(r->evA);
+    cudaEventDestroy(r->evB);
+    cudaEventDestroy(r->evC);
+    cudaEventDestroy(r->evD);
+    cudaStreamDestroy(r->stream);
+    delete r;
+    return B200_OK;
+}
+
+int b200_array_alloc(b200_runner *r, size_t bytes, void **device_ptr)
+{
+    if(!r || !device_ptr) return fail(B200_ERR_INVALID, "bad arguments to b200_array_alloc");
+    CUDA_TRY(cudaSetDevice(r->device));
+    void *p = nullptr;
+    CUDA_TRY(cudaMalloc(&p, bytes + ARRAY_TAIL_PAD));
+    CUDA_TRY(cudaMemsetAsync(p, 0, bytes + ARRAY_TAIL_PAD, r->stream));
+    r->arrays[p] = bytes;
+    *device_ptr = p;
+    return B200_OK;
+}
+
+int b200_array_free(b200_runner *r, void *device_ptr)
+{
+    auto it = r->arrays.find(device_ptr);
+    if(it == r->arrays.end()) return fail(B200_ERR_INVALID, "pointer was not allocated by this runner");
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    CUDA_TRY(cudaFree(device_ptr));
+    r->arrays.erase(it);
+    return B200_OK;
+}
+
+int b200_array_push(b200_runner *r, void *device_ptr, const void *host, size_t bytes)
+{
+    CUDA_TRY(cudaMemcpyAsync(device_ptr, host, bytes, cudaMemcpyHostToDevice, r->stream));
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    return B200_OK;
+}
+
+int b200_array_pull(b200_runner *r, void *host, const void *device_ptr, size_t bytes)
+{
+    CUDA_TRY(cudaMemcpyAsync(host, device_ptr, bytes, cudaMemcpyDeviceToHost, r->stream));
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    return B200_OK;
+}
+
+int b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes)
+{
+    CUDA_TRY(cudaMemsetAsync(device_ptr, value, bytes, r->stream));
+    return B200_OK;
+}
+
+int b200_push_neuron_update_group(b200_runner *r, uint32_t idx, const b200_neuron_group *g)
+{
+    if(!r || !g) return fail(B200_ERR_INVALID, "null argument");
+    if(g->num_psm > B200_MAX_PSM || g->num_cs > B200_MAX_CS) return fail(B200_ERR_INVALID, "too many children");
+    if(g->num_delay_slots < 2) return fail(B200_ERR_INVALID, "num_delay_slots must be at least 2");
+    if(g->first_neuron + g->num_update > g->num_neurons) return fail(B200_ERR_INVALID, "update slice out of range");
+    if(g->first_neuron & 31u) return fail(B200_ERR_INVALID, "first_neuron must be a multiple of 32");
+    if(!g->spk_cnt || !g->spk) return fail(B200_ERR_INVALID, "spike arrays missing");
+    if(idx >= r->neuronGroups.size()) r->neuronGroups.resize(idx + 1);
+    r->neuronGroups[idx] = *g;
+    r->dirty = true;
+    return B200_OK;
+}
+
+int b200_push_synapse_group(b200_runner *r, uint32_t idx, const b200_synapse_group *g)
+{
+    if(!r || !g) return fail(B200_ERR_INVALID, "null argument");
+    if(g->connectivity == B200_CONN_SPARSE) {
+        if(!g->row_length || !g->ind) return fail(B200_ERR_INVALID, "SPARSE group without row_length/ind");
+        if(g->ind_bytes != 1 && g->ind_bytes != 2 && g->ind_bytes != 4) return fail(B200_ERR_INVALID, "bad ind_bytes");
+    }
+    if(g->connectivity == B200_CONN_BITMASK) {
+        if(!g->gp || (g->row_stride & 31u)) return fail(B200_ERR_INVALID, "BITMASK needs gp and a row stride padded to 32");
+        if(g->wu_model != B200_WU_STATIC_PULSE_CONSTANT_WEIGHT) return fail(B200_ERR_INVALID, "BITMASK carries no per-synapse variables");
+    }
+    if(g->wu_model != B200_WU_STATIC_PULSE_CONSTANT_WEIGHT && g->connectivity != B200_CONN_PROCEDURAL && !g->g) {
+        return fail(B200_ERR_INVALID, "weight array missing");
+    }
+    if(g->wu_model == B200_WU_STATIC_PULSE_DENDRITIC_DELAY && (!g->d || !g->den_delay || !g->max_den_delay)) {
+        return fail(B200_ERR_INVALID, "dendritic delay group without d/den_delay");
+    }
+    if(g->wu_model != B200_WU_STATIC_PULSE_DENDRITIC_DELAY && !g->out_post) return fail(B200_ERR_INVALID, "out_post missing");
+    if(g->wu_model == B200_WU_STDP) {
+        if(!g->src_spike_times || !g->trg_spike_times || !g->trg_spk || !g->trg_spk_cnt) {
+            return fail(B200_ERR_INVALID, "learning group without spike times");
+        }
+        if(g->connectivity == B200_CONN_SPARSE && (!g->col_length || !g->remap)) {
+            return fail(B200_ERR_INVALID, "learning SPARSE group without remap");
+        }
+    }
+    if(g->axonal_delay + 2 > g->src_delay_slots) return fail(B200_ERR_INVALID, "axonal delay exceeds the source spike queue");
+    if(idx >= r->synapseGroups.size()) r->synapseGroups.resize(idx + 1);
+    r->synapseGroups[idx] = *g;
+    r->dirty = true;
+    return B200_OK;
+}
+
+int b200_push_custom_update(b200_runner *r, const char *name, uint32_t idx, const b200_custom_update_group *u)
+{
+    if(!r || !name || !u) return fail(B200_ERR_INVALID, "null argument");
+    auto &v = r->customUpdates[name];
+    if(idx >= v.size()) v.resize(idx + 1);
+    v[idx] = *u;
+    return B200_OK;
+}
+
+int b200_set_option(b200_runner *r, const char *name, double value)
+{
+    const std::string n(name);
+    if(n == "spike_lanes") r->spikeLanes = std::max(1u, (unsigned int)value);
+    else if(n == "count_events") r->countEvents = (value != 0.0);
+    else if(n == "use_graph") r->useGraph = (value != 0.0);
+    else if(n == "graph_steps") r->graphSteps = std::max(1u, (unsigned int)value);
+    else return fail(B200_ERR_INVALID, "unknown option %s", name);
+    r->dropGraph();
+    return B200_OK;
+}
+
+int b200_initialize(b200_runner *r)
+{
+    CUDA_TRY(cudaSetDevice(r->device));
+    return prepare(r);
+}
+
+int b200_initialize_sparse(b200_runner *r)
+{
+    CUDA_TRY(cudaSetDevice(r->device));
+    return prepare(r);
+}
+
+int b200_init_var(b200_runner *r, void *device_ptr, uint32_t elem_bytes, uint64_t count,
+                  uint32_t snippet, const float *params, uint32_t rng_stream)
+{
+    InitParams prm{};
+    for(int i = 0; i < 4; i++) prm.p[i] = params ? params[i] : 0.0f;
+    const unsigned int blocks = (unsigned int)std::min<uint64_t>((count + INIT_BLOCK - 1) / INIT_BLOCK, 148u * 32u);
+    if(count == 0) return B200_OK;
+    if(elem_bytes == 4) {
+        initVarKernel<float><<<blocks, INIT_BLOCK, 0, r->stream>>>((float*)device_ptr, count, snippet, prm, r->seed, rng_stream);
+    }
+    else if(elem_bytes == 1) {
+        initVarKernel<uint8_t><<<blocks, INIT_BLOCK, 0, r->stream>>>((uint8_t*)device_ptr, count, snippet, prm, r->seed, rng_stream);
+    }
+    else return fail(B200_ERR_INVALID, "element size %u not supported", elem_bytes);
+    r->launches++;
+    CUDA_TRY(cudaPeekAtLastError());
+    return B200_OK;
+}
+
+int b200_init_sparse_connectivity(b200_runner *r, uint32_t snippet, const float *params,
+                                  uint32_t num_src, uint32_t num_trg, uint32_t row_stride,
+                                  uint32_t ind_bytes, uint32_t trg_begin, uint32_t trg_end,
+                                  uint32_t *row_length, void *ind, uint32_t rng_stream)
+{
+    if(trg_end > num_trg || trg_begin >= trg_end) return fail(B200_ERR_INVALID, "bad target range");
+    InitParams prm{};
+    for(int i = 0; i < 4; i++) prm.p[i] = params ? params[i] : 0.0f;
+    return withIndType(ind_bytes, [&](auto tag) -> int {
+        using IndT = decltype(tag);
+        if(snippet == B200_CONNECT_FIXED_NUMBER_PRE_WITH_REPLACEMENT) {
+            CUDA_TRY(cudaMemsetAsync(row_length, 0, sizeof(uint32_t) * num_src, r->stream));
+            const unsigned int n = trg_end - trg_begin;
+            initFixedNumberPreKernel<IndT><<<(n + INIT_BLOCK - 1) / INIT_BLOCK, INIT_BLOCK, 0, r->stream>>>(
+                (unsigned int)prm.p[0], num_src, row_stride, trg_begin, trg_end, row_length, ind, r->seed, rng_stream, r->state);
+        }
+        else {
+            initSparseConnectivityKernel<IndT><<<(num_src + INIT_BLOCK - 1) / INIT_BLOCK, INIT_BLOCK, 0, r->stream>>>(
+                snippet, prm, num_src, row_stride, trg_begin, trg_end, row_length, ind, r->seed, rng_stream, r->state);
+        }
+        r->launches++;
+        CUDA_TRY(cudaPeekAtLastError());
+        return B200_OK;
+    });
+}
+
+int b200_init_sparse_vars(b200_runner *r, const uint32_t *row_length, uint32_t num_src,
+                          uint32_t row_stride, void *device_ptr, uint32_t elem_bytes,
+                          uint32_t snippet, const float *params, uint32_t rng_stream)
+{
+    InitParams prm{};
+    for(int i = 0; i < 4; i++) prm.p[i] = params ? params[i] : 0.0f;
+    const uint64_t total = (uint64_t)num_src * row_stride;
+    if(total == 0) return B200_OK;
+    const unsigned int blocks = (unsigned int)std::min<uint64_t>((total + INIT_BLOCK - 1) / INIT_BLOCK, 148u * 32u);
+    if(elem_bytes == 4) {
+        initSparseVarKernel<float><<<blocks, INIT_BLOCK, 0, r->stream>>>((float*)device_ptr, row_length, num_src, row_stride, snippet, prm, r->seed, rng_stream);
+    }
+    else if(elem_bytes == 1) {
+        initSparseVarKernel<uint8_t><<<blocks, INIT_BLOCK, 0, r->stream>>>((uint8_t*)device_ptr, row_length, num_src, row_stride, snippet, prm, r->seed, rng_stream);
+    }
+    else return fail(B200_ERR_INVALID, "element size %u not supported", elem_bytes);
+    r->launches++;
+    CUDA_TRY(cudaPeekAtLastError());
+    return B200_OK;
+}
+
+int b200_build_remap(b200_runner *r, const uint32_t *row_length, const void *ind, uint32_t ind_bytes,
+                     uint32_t num_src, uint32_t num_trg, uint32_t row_stride, uint32_t col_stride,
+                     uint32_t *col_length, uint32_t *remap)
+{
+    const uint64_t total = (uint64_t)num_src * row_stride;
+    CUDA_TRY(cudaMemsetAsync(col_length, 0, sizeof(uint32_t) * num_trg, r->stream));
+    if(total == 0) return B200_OK;
+    const unsigned int blocks = (unsigned int)std::min<uint64_t>((total + INIT_BLOCK - 1) / INIT_BLOCK, 148u * 32u);
+    return withIndType(ind_bytes, [&](auto tag) -> int {
+        using IndT = decltype(tag);
+        buildRemapKernel<IndT><<<blocks, INIT_BLOCK, 0, r->stream>>>(row_length, ind, num_src, num_trg, row_stride,
+                                                                     col_stride, col_length, remap, r->state);
+        r->launches++;
+        CUDA_TRY(cudaPeekAtLastError());
+        return B200_OK;
+    });
+}
+
+int b200_update_synapses(b200_runner *r)
+{
+    int e = prepare(r);
+    if(e) return e;
+    return enqueueSynapses(r, false);
+}
+
+int b200_update_neurons(b200_runner *r, uint64_t num_recording_timesteps)
+{
+    int e = prepare(r);
+    if(e) return e;
+    e = enqueueNeurons(r, num_recording_timesteps, false);
+    if(e == B200_OK) {
+        r->hostTimestep++;
+        r->hostStepsDone++;
+    }
+    return e;
+}
+
+int b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_timesteps)
+{
+    int e = prepare(r);
+    if(e) return e;
+    uint64_t left = num_steps;
+    if(r->useGraph && !r->timing && num_steps >= 2) {
+        const unsigned int len = (unsigned int)std::min<uint64_t>(num_steps, r->graphSteps);
+        if(!r->graphExec || r->graphLen > num_steps || r->graphNumRec != num_recording_timesteps ||
+           (r->graphLen != len && r->graphLen != r->graphSteps)) {
+            e = buildGraph(r, len, num_recording_timesteps);
+            if(e) return e;
+        }
+        while(left >= r->graphLen) {
+            CUDA_TRY(cudaGraphLaunch(r->graphExec, r->stream));
+            r->launches += (unsigned long long)r->graphLen * kernelsPerStep(r);
+            left -= r->graphLen;
+        }
+    }
+    for(; left; left--) {
+        e = enqueueStep(r, num_recording_timesteps, false);
+        if(e) return e;
+    }
+    r->hostTimestep += num_steps;
+    r->hostStepsDone += num_steps;
+    return B200_OK;
+}
+
+int b200_custom_update(b200_runner *r, const char *name)
+{
+    auto it = r->customUpdates.find(name);
+    if(it == r->customUpdates.end()) return fail(B200_ERR_INVALID, "no custom update group '%s'", name);
+    ScopedTimer tm(r, std::string("custom_update_") + name, false);
+    for(const auto &u : it->second) {
+        if(u.num_elements == 0) continue;
+        const unsigned int blocks = (unsigned int)std::min<uint64_t>((u.num_elements + REDUCE_BLOCK - 1) / REDUCE_BLOCK, 148u * 16u);
+        batchReduceKernel<<<blocks, REDUCE_BLOCK, 0, r->stream>>>(u, r->batch);
+        r->launches++;
+    }
+    CUDA_TRY(cudaPeekAtLastError());
+    return B200_OK;
+}
+
+int b200_synchronize(b200_runner *r)
+{
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    StepState s;
+    CUDA_TRY(cudaMemcpy(&s, r->state, sizeof(s), cudaMemcpyDeviceToHost));
+    if(s.error) {
+        const unsigned int err = s.error;
+        cudaMemset(&r->state->error, 0, sizeof(unsigned int));
+        return fail(B200_ERR_DEVICE_CHECK, "device-side check failed (flags 0x%x:%s%s%s)", err,
+                    (err & ERR_SPIKE_OVERFLOW) ? " spike list overflow" : "",
+                    (err & ERR_IND_RANGE) ? " index or row length out of range" : "",
+                    (err & ERR_DELAY_RANGE) ? " delay out of range" : "");
+    }
+    return B200_OK;
+}
+
+int b200_get_timestep(b200_runner *r, uint64_t *timestep)
+{
+    *timestep = r->hostTimestep;
+    return B200_OK;
+}
+
+int b200_set_timestep(b200_runner *r, uint64_t timestep)
+{
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    const unsigned long long t = timestep;
+    CUDA_TRY(cudaMemcpy(&r->state->timestep, &t, sizeof(t), cudaMemcpyHostToDevice));
+    r->hostTimestep = timestep;
+    return B200_OK;
+}
+
+int b200_get_steps_done(b200_runner *r, uint64_t *steps)
+{
+    *steps = r->hostStepsDone;
+    return B200_OK;
+}
+
+int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
+{
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    StepState s;
+    CUDA_TRY(cudaMemcpy(&s, r->state, sizeof(s), cudaMemcpyDeviceToHost));
+    const std::string n(name);
+    if(n == "synaptic_events") *value = s.synaptic_events;
+    else if(n == "timestep") *value = s.timestep;
+    else if(n == "steps_done") *value = s.steps_done;
+    else return fail(B200_ERR_INVALID, "unknown counter %s", name);
+    return B200_OK;
+}
+
+int b200_enable_timing(b200_runner *r, int enabled)
+{
+    r->timing = (enabled != 0);
+    return B200_OK;
+}
+
+int b200_get_timer(b200_runner *r, const char *name, double *seconds)
+{
+    auto it = r->timers.find(name);
+    *seconds = (it == r->timers.end()) ? 0.0 : it->second.seconds;
+    return B200_OK;
+}
+
+int b200_reset_timers(b200_runner *r)
+{
+    r->timers.clear();
+    return B200_OK;
+}
+
+int b200_get_kernel_launches(b200_runner *r, uint64_t *launches)
+{
+    *launches = r->launches;
+    return B200_OK;
+}
+
+// Time `num_steps` steps with CUDA events recorded on the runner's own stream
+// (events of another stream would not see this work).  Synchronises.
+int b200_step_time_timed(b200_runner *r, uint64_t num_steps, uint64_t num_recording_timesteps, float *milliseconds)
+{
+    int e = prepare(r);
+    if(e) return e;
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    CUDA_TRY(cudaEventRecord(r->evC, r->stream));
+    e = b200_step_time(r, num_steps, num_recording_timesteps);
+    if(e) return e;
+    CUDA_TRY(cudaEventRecord(r->evD, r->stream));
+    CUDA_TRY(cudaEventSynchronize(r->evD));
+    CUDA_TRY(cudaEventElapsedTime(milliseconds, r->evC, r->evD));
+    return B200_OK;
+}
+
+}   // extern "C"

@@ -305,6 +305,10 @@ class Plan:
         elif s.wum == "STDP":
             for i, k in enumerate(("tauPlus", "tauMinus", "Aplus", "Aminus", "Wmin", "Wmax")):
                 d.wu_params[i] = _f32(s.wum_params[k])
+            # spike times as seen at the synapse: sT + (delay + 1) * dt
+            # (synapseUpdateGroupMerged.cc:118-142)
+            d.wu_params[6] = _f32(net.dt * (s.ax_delay + 1))
+            d.wu_params[7] = _f32(net.dt * (s.back_delay + 1))
         for f in ("row_length", "ind", "g", "d", "gp", "col_length", "remap"):
             setattr(d, f, self._ptr(f"{s.name}.{f}"))
         d.src_spk_cnt, d.src_spk = self._ptr(f"{src.name}.spk_cnt"), self._ptr(f"{src.name}.spk")

@@ -1,0 +1,274 @@
+"""Runtime: loads a model description onto the GPU and steps it through the
+C ABI of the CUDA library.  Counterpart of ``GeNN::Runtime::Runtime``
+(runtime.cc:147-718) for the B200 backend.  There is no CPU path: importing
+this module without the built library raises.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import math
+from typing import Dict, Optional, Tuple
+
+import numpy as np
+
+from . import abi
+from .abi import check
+from .plan import ArrayFactory, Plan
+from .resolve import Net, resolve
+
+
+class DeviceArray:
+    def __init__(self, rt: "DeviceFactory", nbytes: int):
+        self._rt = rt
+        self.nbytes = nbytes
+        p = C.c_void_p()
+        check(rt.lib.b200_array_alloc(rt.handle, nbytes, C.byref(p)))
+        self.ptr = p.value
+
+    def push(self, host: np.ndarray):
+        self._rt.push(self, host)
+
+    def pull(self, host: np.ndarray):
+        self._rt.pull(self, host)
+
+
+class DeviceFactory(ArrayFactory):
+    def __init__(self, lib, handle):
+        self.lib = lib
+        self.handle = handle
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
+
+    def alloc(self, nbytes: int) -> DeviceArray:
+        return DeviceArray(self, nbytes)
+
+    def push(self, handle: DeviceArray, host: np.ndarray):
+        host = np.ascontiguousarray(host)
+        check(self.lib.b200_array_push(self.handle, handle.ptr, host.ctypes.data, host.nbytes))
+        self.h2d_bytes += host.nbytes
+
+    def pull(self, handle: DeviceArray, host: np.ndarray):
+        assert host.flags["C_CONTIGUOUS"]
+        check(self.lib.b200_array_pull(self.handle, host.ctypes.data, handle.ptr, host.nbytes))
+        self.d2h_bytes += host.nbytes
+
+    def memset(self, handle: DeviceArray, value: int, nbytes: int):
+        check(self.lib.b200_array_memset(self.handle, handle.ptr, value, nbytes))
+
+
+class Runtime:
+    """One loaded model on one GPU."""
+
+    def __init__(self, model, num_recording_timesteps: Optional[int] = None, device: int = 0,
+                 shard: Optional[Tuple[int, int]] = None, net: Optional[Net] = None):
+        self.lib = abi.load_library()
+        self.model = model
+        self.net = net if net is not None else resolve(model)
+        self.num_recording_timesteps = int(num_recording_timesteps or 0)
+        h = C.c_void_p()
+        check(self.lib.b200_runner_create(device, self.net.dt, self.net.seed, self.net.batch_size, C.byref(h)))
+        self.handle = h
+        self.factory = DeviceFactory(self.lib, self.handle)
+        self.plan = Plan(self.net, self.factory, self.num_recording_timesteps, shard=shard)
+        self._run_init_tasks()
+        for i, d in enumerate(self.plan.neuron_descs):
+            check(self.lib.b200_push_neuron_update_group(self.handle, i, C.byref(d)))
+        for i, d in enumerate(self.plan.synapse_descs):
+            check(self.lib.b200_push_synapse_group(self.handle, i, C.byref(d)))
+        check(self.lib.b200_initialize(self.handle))
+        check(self.lib.b200_initialize_sparse(self.handle))
+        if model is not None:
+            self._bind_model_views()
+            if getattr(model, "timing_enabled", False):
+                check(self.lib.b200_enable_timing(self.handle, 1))
+        self.synchronize()
+
+    # -- initialisation kernels -------------------------------------------------
+    def _run_init_tasks(self):
+        a = self.plan.arrays
+        for task in self.plan.init_tasks:
+            params = (C.c_float * 4)(*(list(task.params) + [0.0] * 4)[:4])
+            if task.kind == "var":
+                arr = a[task.target]
+                count = int(np.prod(arr.shape, dtype=np.int64))
+                check(self.lib.b200_init_var(self.handle, arr.ptr, arr.dtype.itemsize, count, task.snippet,
+                                             params, task.stream))
+            elif task.kind == "connect":
+                self._init_connectivity(task, params)
+            elif task.kind == "sparse_var":
+                s = self.net.syn(task.extra["syn"])
+                arr = a[task.target]
+                check(self.lib.b200_init_sparse_vars(self.handle, a[f"{s.name}.row_length"].ptr,
+                                                     self.net.pop(s.src).n, s.row_stride, arr.ptr,
+                                                     arr.dtype.itemsize, task.snippet, params, task.stream))
+            elif task.kind == "remap":
+                s = self.net.syn(task.target)
+                check(self.lib.b200_build_remap(self.handle, a[f"{s.name}.row_length"].ptr, a[f"{s.name}.ind"].ptr,
+                                                np.dtype(s.ind_dtype).itemsize, self.net.pop(s.src).n,
+                                                self.net.pop(s.trg).n, s.row_stride, s.col_stride,
+                                                a[f"{s.name}.col_length"].ptr, a[f"{s.name}.remap"].ptr))
+
+    def _init_connectivity(self, task, params):
+        s = self.net.syn(task.target)
+        a = self.plan.arrays
+        ns, nt = self.net.pop(s.src).n, self.net.pop(s.trg).n
+        begin, end = getattr(s, "trg_range", (0, nt))
+        snippet = task.snippet
+        if snippet == abi.CONNECT_FIXED_NUMBER_TOTAL:
+            # row lengths are drawn on the host from the multinomial, as the
+            # reference's host initialisation code does
+            # (initSparseConnectivitySnippet.h:300-336)
+            rng = np.random.default_rng([self.net.seed, task.stream])
+            rl = rng.multinomial(int(task.params[0]), np.full(ns, 1.0 / ns)).astype(np.uint32)
+            if rl.max() > s.row_stride:
+                raise abi.B200Error(f"{s.name}: drawn row length {rl.max()} exceeds max_connections {s.row_stride}")
+            self.plan.push(f"{s.name}.row_length", rl)
+        elif snippet in (abi.CONNECT_FIXED_PROBABILITY, abi.CONNECT_FIXED_PROBABILITY_NO_AUTAPSE):
+            params[1] = 1.0 / math.log(1.0 - task.params[0])
+        check(self.lib.b200_init_sparse_connectivity(self.handle, snippet, params, ns, nt, s.row_stride,
+                                                     np.dtype(s.ind_dtype).itemsize, begin, end,
+                                                     a[f"{s.name}.row_length"].ptr, a[f"{s.name}.ind"].ptr,
+                                                     task.stream))
+
+    # -- PyGeNN-style views -----------------------------------------------------
+    def _bind_model_views(self):
+        m, a = self.model, self.plan.arrays
+        for p in m.neuron_populations.values():
+            for name, var in p.vars.items():
+                arr = a[f"{p.name}.{name}"]
+                var._array = arr.handle
+                var._view = np.zeros(arr.shape, dtype=arr.dtype)
+                self.factory.pull(arr.handle, var._view)
+        for c in m.current_sources.values():
+            for name, var in c.vars.items():
+                arr = a[f"{c.name}.{name}"]
+                var._array = arr.handle
+                var._view = np.zeros(arr.shape, dtype=arr.dtype)
+        from .model import Variable
+        for sg in m.synapse_populations.values():
+            rs = self.net.syn(sg.name)
+            sg.max_connections = rs.row_stride if rs.matrix == "SPARSE" else sg.max_connections
+            for name in ("g", "d"):
+                arr = a.get(f"{sg.name}.{name}")
+                if arr is not None:
+                    v = Variable(name, arr.dtype, None, arr.shape)
+                    v._array = arr.handle
+                    v._view = np.zeros(arr.shape, dtype=arr.dtype)
+                    sg.vars[name] = v
+            arr = a[f"psm{rs.psm}.out_post"]
+            v = Variable("outPost", arr.dtype, None, arr.shape)
+            v._array = arr.handle
+            v._view = np.zeros(arr.shape, dtype=arr.dtype)
+            sg.out_post = v
+            if rs.matrix == "SPARSE" and rs.row_length is not None:
+                sg.row_lengths, sg.ind = rs.row_length, rs.ind
+
+    def pull_connectivity(self, sg):
+        rs = self.net.syn(sg.name)
+        sg.row_lengths = self.array(f"{sg.name}.row_length")
+        sg.ind = self.array(f"{sg.name}.ind").astype(np.uint32)
+
+    # -- stepping ---------------------------------------------------------------
+    def step_time(self, num_steps: int = 1):
+        check(self.lib.b200_step_time(self.handle, num_steps, self.num_recording_timesteps))
+
+    def step_time_timed(self, num_steps: int) -> float:
+        """Steps bracketed by CUDA events on the runner's stream; returns milliseconds."""
+        ms = C.c_float()
+        check(self.lib.b200_step_time_timed(self.handle, num_steps, self.num_recording_timesteps, C.byref(ms)))
+        return float(ms.value)
+
+    def update_synapses(self):
+        check(self.lib.b200_update_synapses(self.handle))
+
+    def update_neurons(self):
+        check(self.lib.b200_update_neurons(self.handle, self.num_recording_timesteps))
+
+    def custom_update(self, name: str):
+        check(self.lib.b200_custom_update(self.handle, name.encode()))
+
+    def synchronize(self):
+        check(self.lib.b200_synchronize(self.handle))
+
+    def set_option(self, name: str, value: float):
+        check(self.lib.b200_set_option(self.handle, name.encode(), float(value)))
+
+    @property
+    def timestep(self) -> int:
+        v = C.c_uint64()
+        check(self.lib.b200_get_timestep(self.handle, C.byref(v)))
+        return int(v.value)
+
+    @timestep.setter
+    def timestep(self, t: int):
+        check(self.lib.b200_set_timestep(self.handle, int(t)))
+
+    @property
+    def steps_done(self) -> int:
+        v = C.c_uint64()
+        check(self.lib.b200_get_steps_done(self.handle, C.byref(v)))
+        return int(v.value)
+
+    def counter(self, name: str) -> int:
+        v = C.c_uint64()
+        check(self.lib.b200_get_counter(self.handle, name.encode(), C.byref(v)))
+        return int(v.value)
+
+    @property
+    def kernel_launches(self) -> int:
+        v = C.c_uint64()
+        check(self.lib.b200_get_kernel_launches(self.handle, C.byref(v)))
+        return int(v.value)
+
+    def enable_timing(self, on: bool):
+        check(self.lib.b200_enable_timing(self.handle, int(on)))
+
+    def reset_timers(self):
+        check(self.lib.b200_reset_timers(self.handle))
+
+    def timer(self, name: str) -> float:
+        v = C.c_double()
+        check(self.lib.b200_get_timer(self.handle, name.encode(), C.byref(v)))
+        return float(v.value)
+
+    # -- data access --------------------------------------------------------------
+    def array(self, name: str) -> np.ndarray:
+        self.synchronize()
+        return self.plan.host_copy(name)
+
+    def current_spikes(self, pop, batch: int = 0) -> np.ndarray:
+        name = pop if isinstance(pop, str) else pop.name
+        p = self.net.pop(name)
+        slot = self.steps_done % p.runtime_slots
+        cnt = int(self.array(f"{name}.spk_cnt")[batch, slot])
+        return self.array(f"{name}.spk")[batch, slot, :cnt].copy()
+
+    def pull_recording_buffers(self):
+        """Decode the spike-recording bit words into (times, ids) per batch
+        element, as Runtime::getRecordedEvents does (runtime.cc:855-913)."""
+        T = self.num_recording_timesteps
+        if not T:
+            raise Exception("Recording buffer not allocated - cannot pull from device")
+        ts = self.timestep
+        if ts < T:
+            raise Exception("Event recording data can only be accessed once buffer is full")
+        start = (ts - T) * self.net.dt
+        for p in self.net.pops:
+            if f"{p.name}.record" not in self.plan.arrays:
+                continue
+            words = self.array(f"{p.name}.record")          # [T][B][W]
+            # buffer is a ring over timestep % T: rotate so index 0 is the oldest step
+            words = np.roll(words, -(ts % T), axis=0)
+            out = []
+            for b in range(self.net.batch_size):
+                bits = np.unpackbits(words[:, b, :].view(np.uint8), axis=1, bitorder="little")[:, :p.n]
+                step, ids = np.nonzero(bits)
+                out.append((start + step * self.net.dt, ids.astype(np.uint32)))
+            if self.model is not None:
+                self.model.neuron_populations[p.name]._spike_recording_data = out
+            p.recorded = out
+
+    def close(self):
+        if self.handle:
+            self.lib.b200_runner_destroy(self.handle)
+            self.handle = None

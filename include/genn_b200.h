@@ -50,7 +50,7 @@ typedef enum b200_status {
 
 /* neuronModels.h:163-325 */
 typedef enum b200_neuron_model {
-    B200_NEURON_LIF = 0,              /* params: Vthresh? see b200_neuron_group.params */
+    B200_NEURON_LIF = 0,              /* parameter and variable order: see b200_neuron_group */
     B200_NEURON_IZHIKEVICH = 1,
     B200_NEURON_SPIKE_SOURCE_ARRAY = 2,
     B200_NEURON_POISSON = 3
@@ -74,7 +74,8 @@ typedef enum b200_wu_model {
     B200_WU_STATIC_PULSE = 0,                 /* addToPost(g) */
     B200_WU_STATIC_PULSE_CONSTANT_WEIGHT = 1, /* params: g */
     B200_WU_STATIC_PULSE_DENDRITIC_DELAY = 2, /* addToPostDelay(g, d) */
-    B200_WU_STDP = 3                          /* params: tauPlus, tauMinus, Aplus, Aminus, Wmin, Wmax */
+    B200_WU_STDP = 3                          /* params: tauPlus, tauMinus, Aplus, Aminus, Wmin, Wmax,
+                                                 (axonalDelay+1)*dt, (backPropDelay+1)*dt */
 } b200_wu_model;
 
 /* synapseMatrixType.h:9-69 */
@@ -246,14 +247,23 @@ int  b200_update_synapses(b200_runner *r);
 int  b200_update_neurons(b200_runner *r, uint64_t num_recording_timesteps);
 int  b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_timesteps);
 int  b200_custom_update(b200_runner *r, const char *name);
+/* Same, bracketed by CUDA events recorded on the runner's stream; waits for completion. */
+int  b200_step_time_timed(b200_runner *r, uint64_t num_steps, uint64_t num_recording_timesteps, float *milliseconds);
+/* Waits for the stream and reports failed device-side checks (out-of-range index, row overflow). */
 int  b200_synchronize(b200_runner *r);
 int  b200_get_timestep(b200_runner *r, uint64_t *timestep);
 int  b200_set_timestep(b200_runner *r, uint64_t timestep);
 int  b200_get_steps_done(b200_runner *r, uint64_t *steps);
+/* Device-side counters: "synaptic_events" (when option count_events is on), "timestep", "steps_done". */
+int  b200_get_counter(b200_runner *r, const char *name, uint64_t *value);
+/* Tuning knobs (the counterpart of the backend Preferences, backends/cuda/backend.h:64-115):
+ * "spike_lanes" (grid.y of the SPARSE kernel), "use_graph", "graph_steps", "count_events". */
+int  b200_set_option(b200_runner *r, const char *name, double value);
 
 /* ---- timers: neuronUpdateTime etc. (generateRunner.cc:159-222) ------------- */
 int  b200_enable_timing(b200_runner *r, int enabled);
 int  b200_get_timer(b200_runner *r, const char *name, double *seconds);
+int  b200_reset_timers(b200_runner *r);
 int  b200_get_kernel_launches(b200_runner *r, uint64_t *launches);
 
 #ifdef __cplusplus

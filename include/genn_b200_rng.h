@@ -159,6 +159,32 @@ B200_HD float b200_logf(float x)
     return B200_FMAF((float)e, 0.6931471805599453f, lm);
 }
 
+/* exp(x) for x <= 0 from single IEEE operations: x = n*ln2 + r with
+ * |r| <= ln2/2 (two-constant reduction), degree-6 polynomial, exact scaling. */
+B200_HD float b200_expf(float x)
+{
+    if(x < -87.0f) return 0.0f;
+    const float nf = rintf(B200_FMUL(x, 1.4426950408889634f));
+    float r = B200_FMAF(nf, -0.693145751953125f, x);          /* ln2 high part (exact product) */
+    r = B200_FMAF(nf, -1.4286068203094172e-06f, r);           /* ln2 low part */
+    float p = 1.3888888889e-03f;                              /* 1/720 */
+    p = B200_FMAF(p, r, 8.3333333333e-03f);
+    p = B200_FMAF(p, r, 4.1666666667e-02f);
+    p = B200_FMAF(p, r, 1.6666666667e-01f);
+    p = B200_FMAF(p, r, 0.5f);
+    p = B200_FMAF(p, r, 1.0f);
+    p = B200_FMAF(p, r, 1.0f);
+    const int n = (int)nf;
+    const uint32_t sbits = (uint32_t)(n + 127) << 23;         /* n >= -126 here */
+    float scale;
+#if defined(__CUDA_ARCH__)
+    scale = __uint_as_float(sbits);
+#else
+    memcpy(&scale, &sbits, sizeof(scale));
+#endif
+    return B200_FMUL(p, scale);
+}
+
 /* sin and cos of 2*pi*u for u in [0, 1): octant reduction then polynomials on
  * [-pi/4, pi/4]; single IEEE operations only. */
 B200_HD void b200_sincos2pif(float u, float *s, float *c)

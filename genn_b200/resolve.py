@@ -144,6 +144,27 @@ def bitmask_from_pairs(pre: np.ndarray, post: np.ndarray, num_pre: int, num_post
     return words
 
 
+def calc_max_row_length(snippet: str, params: Dict[str, float], num_pre: int, num_post: int) -> int:
+    """Row stride for device-built connectivity: the 0.9999 quantile (over the
+    whole matrix) of the row-length distribution, as the snippets'
+    SET_CALC_MAX_ROW_LENGTH_FUNC do (initSparseConnectivitySnippet.h:130-160,
+    338-346, 393-403), with a small safety margin because a row longer than
+    the stride is an error here rather than a silent truncation."""
+    from scipy.stats import binom
+    q = 0.9999 ** (1.0 / num_pre)
+    if snippet in ("FixedProbability", "FixedProbabilityNoAutapse"):
+        n = binom.ppf(q, num_post, params["prob"])
+    elif snippet == "FixedNumberTotalWithReplacement":
+        n = binom.ppf(q, int(params["num"]), 1.0 / num_pre)
+    elif snippet == "FixedNumberPreWithReplacement":
+        n = binom.ppf(q, int(params["num"]) * num_post, 1.0 / num_pre)
+    elif snippet == "FixedNumberPostWithReplacement":
+        return int(params["num"])
+    else:
+        raise ValueError(snippet)
+    return int(n) + 8
+
+
 def resolve(model: GeNNModel) -> Net:
     dt = float(model.dt)
     batch = int(model.batch_size)
@@ -223,7 +244,10 @@ def resolve(model: GeNNModel) -> Net:
                 r.row_length, r.row_stride, r.ind = rl, stride, ind
                 r.g, r.d = out.get("g"), out.get("d")
             else:
-                r.row_stride = int(sg.max_connections or 0)
+                r.row_stride = int(sg.max_connections or
+                                   calc_max_row_length(sg.connect.snippet, sg.connect.params, num_pre, num_post))
+            if getattr(sg, "trg_range", None) is not None:
+                r.trg_range = sg.trg_range
         elif matrix == "BITMASK":
             r.row_stride = ((num_post + 31) // 32) * 32
             if sg._pre is not None:

@@ -1,0 +1,389 @@
+"""Benchmark: synaptic events per second and real-time factor of the
+Potjans-Diesmann microcircuit architecture on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+A bench STEP is a block of ``--block`` (default 1000) simulation time steps of
+dt = 0.1 ms, i.e. 0.1 s of biological time replayed as captured CUDA graphs.
+At N GPUs the network has N times the neurons with the published in-degrees
+(weak scaling) and each rank owns a contiguous slice of every population's
+postsynaptic neurons together with their incoming synapses.
+
+One JSON line is printed by rank 0.  ``value`` is whole-job synaptic events per
+second with all state resident in HBM; ``e2e`` is the same metric through the
+public ``GeNNModel`` API with the spike recording copied to page-locked host
+memory every step; ``roofline`` is the presynaptic-update kernel measured live
+with CUDA events at the network's natural firing rates and
+``roofline_saturated`` the same kernel driven with a quarter of all neurons
+spiking in one step (inputs far larger than L2); ``cpu_baseline`` times the
+reference's own single-threaded CPU backend (or, where it cannot run, the C
+port of its algorithm) on this box's host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import shutil
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+import numpy as np
+
+REPO = os.path.dirname(os.path.abspath(__file__))
+if REPO not in sys.path:
+    sys.path.insert(0, REPO)
+
+DT_MS = 0.1
+ALGO_BYTES_PER_SPIKE = 8           # spike id + row length
+
+
+def measured_peaks():
+    path = os.path.join(REPO, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            return float(json.load(open(path))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi sampling of SM clocks and throttle reasons during a timed region."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except Exception:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx.append(float(r[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def bytes_per_event(net) -> float:
+    """Algorithmic HBM bytes per synaptic event, weighted by group size:
+    index + weight (+ delay byte)."""
+    tot, w = 0.0, 0.0
+    for s in net.syns:
+        n = float(net.pop(s.src).n) * s.row_stride
+        b = np.dtype(s.ind_dtype).itemsize + (0 if s.wum == "CONST" else 4) + (1 if s.max_den_delay else 0)
+        tot += n * b
+        w += n
+    return tot / w if w else 0.0
+
+
+def run_reference_sample(scale: float, block: int, steps: int, warmup: int, seed: int = 1234):
+    """Time the reference's own single_threaded_cpu backend (oracle/_ref, built
+    from the unmodified reference sources) on a Potjans network with
+    ``scale`` x the neurons and the published in-degrees.  Falls back to the C
+    port of the same algorithm when the reference build is absent."""
+    from genn_b200 import workloads
+    from genn_b200.resolve import resolve, write_netspec
+    model = workloads.potjans(neuron_scale=scale, seed=seed, host_connectivity=True, background="poisson", record=True)
+    net = resolve(model)
+    total_steps = (warmup + steps) * block
+    driver = os.path.join(REPO, "oracle", "_ref", "ref_driver")
+    out_deg = {p.name: np.zeros(p.n, dtype=np.int64) for p in net.pops}
+    for s in net.syns:
+        out_deg[s.src] += s.row_length
+    if os.path.exists(driver):
+        work = tempfile.mkdtemp(prefix="refarm_")
+        try:
+            spec = write_netspec(net, os.path.join(work, "spec"), total_steps, 0)
+            os.makedirs(os.path.join(work, "out"))
+            subprocess.check_call([driver, spec, os.path.join(work, "work"), os.path.join(work, "out")])
+            timing = dict(l.split() for l in open(os.path.join(work, "out", "timing.txt")))
+            seconds = float(timing["loop_seconds"])
+            events = 0
+            spikes = 0
+            for p in net.pops:
+                sp = np.fromfile(os.path.join(work, "out", f"spikes_{p.name}.bin"), dtype=np.uint32).reshape(-1, 2)
+                events += int(out_deg[p.name][sp[:, 1]].sum())
+                spikes += len(sp)
+            kind = "reference"
+        finally:
+            shutil.rmtree(work, ignore_errors=True)
+    else:
+        from oracle.oracle import OracleRunner
+        runner = OracleRunner(net, None)
+        t0 = time.perf_counter()
+        runner.step(total_steps)
+        seconds = time.perf_counter() - t0
+        events = runner.synaptic_events
+        spikes = 0
+        kind = "port"
+        runner.close()
+    sim_seconds = total_steps * DT_MS * 1e-3
+    return {"kind": kind, "events": events, "spikes": spikes, "seconds": seconds,
+            "events_per_s": events / seconds, "rtf": seconds / sim_seconds,
+            "neurons": sum(p.n for p in net.pops), "synapses": int(sum(int(s.row_length.sum()) for s in net.syns)),
+            "total_steps": total_steps}
+
+
+def reference_arm(args):
+    """--impl reference: the reference's CPU implementation of the path on this
+    box's host cores (single-threaded by construction)."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    r = run_reference_sample(args.ref_scale, args.block, args.steps, args.warmup)
+    steps_total = args.warmup + args.steps
+    ms_per_step = r["seconds"] / steps_total * 1e3
+    line = {
+        "impl": "reference", "metric": "synaptic events/s (Potjans microcircuit architecture)",
+        "value": r["events_per_s"], "unit": "synaptic events/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "realtime_factor": r["rtf"],
+        "config": {"workload": f"Potjans-Diesmann microcircuit architecture, neuron_scale={args.ref_scale} "
+                               f"(published in-degrees), {r['neurons']} neurons, {r['synapses']} synapses, "
+                               f"dt=0.1 ms, {args.block} time steps per bench step",
+                   "timing": "wall clock around the reference's stepTime loop (all warm-up and timed steps)"},
+        "cpu_baseline": {"value": r["events_per_s"], "unit": "synaptic events/s", "cores": 1, "kind": r["kind"],
+                         "sample": f"neuron_scale={args.ref_scale}, {r['total_steps']} time steps"},
+        "e2e": {"value": r["events_per_s"], "unit": "synaptic events/s", "h2d_bytes_per_step": 0,
+                "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--block", type=int, default=1000, help="simulation time steps per bench step")
+    ap.add_argument("--ref-scale", type=float, default=0.05, help="neuron scale of the CPU sample")
+    ap.add_argument("--neuron-scale", type=float, default=None, help="override the workload size (debugging)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-saturated", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        reference_arm(args)
+        return
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch multi-GPU runs with torch.distributed.run, one rank per GPU")
+    import torch
+    import torch.distributed as dist
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    from genn_b200 import workloads
+    from genn_b200.resolve import resolve
+    from genn_b200.runtime import Runtime
+
+    scale = args.neuron_scale if args.neuron_scale is not None else float(world)
+    block = args.block
+    hbm_peak, peak_kind = measured_peaks()
+
+    # ---- build through the public API ---------------------------------------------
+    model = workloads.potjans(neuron_scale=scale, seed=1234, record=True,
+                              shard=(rank, world) if world > 1 else None)
+    model.build()
+    model.load(num_recording_timesteps=block, device=local_rank, shard=(rank, world) if world > 1 else None)
+    rt = model._runtime
+    net = rt.net
+    rt.set_option("count_events", 1)
+    rt.set_option("graph_steps", min(block, 100))
+    bpe = bytes_per_event(net)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def allreduce(value, op):
+        if world == 1:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    # ---- device-resident throughput: W warm-up, K timed steps -------------------------
+    for _ in range(args.warmup):
+        rt.step_time(block)
+    rt.synchronize()
+    ev0, sp0, l0 = rt.counter("synaptic_events"), rt.counter("spikes"), rt.kernel_launches
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    ms = rt.step_time_timed(args.steps * block)        # CUDA events on the runner's own stream
+    barrier()
+    clocks = sampler.stop()
+    ev1, sp1, l1 = rt.counter("synaptic_events"), rt.counter("spikes"), rt.kernel_launches
+    ms = allreduce(ms, dist.ReduceOp.MAX if world > 1 else None)
+    events = allreduce(float(ev1 - ev0), dist.ReduceOp.SUM if world > 1 else None)
+    spikes = allreduce(float(sp1 - sp0), dist.ReduceOp.SUM if world > 1 else None)
+    seconds = ms * 1e-3
+    sim_seconds = args.steps * block * DT_MS * 1e-3
+    value = events / seconds
+
+    # ---- end to end through the public API: step + recording to pinned host memory ---
+    d2h = sum(a.nbytes for n, a in rt.plan.arrays.items() if n.endswith(".record"))
+    e2e_ev0 = rt.counter("synaptic_events")
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        model.step_time(block)
+        model.pull_recording_buffers_from_device()
+    barrier()
+    e2e_seconds = allreduce(time.perf_counter() - t0, dist.ReduceOp.MAX if world > 1 else None)
+    e2e_events = allreduce(float(rt.counter("synaptic_events") - e2e_ev0), dist.ReduceOp.SUM if world > 1 else None)
+    # firing rates from the last pulled recording (sanity: the network is in its asynchronous state)
+    rates = {}
+    for p in net.pops:
+        t_, ids = rt.recorded_spikes(p.name)[0]
+        n_local = rt.plan.neuron_descs[[q.name for q in net.pops].index(p.name)].num_update
+        rates[p.name] = round(len(ids) / max(1, n_local) / (block * DT_MS * 1e-3), 3)
+
+    # ---- roofline of the presynaptic kernel, live, per-kernel CUDA events ---------------
+    rt.enable_timing(True)
+    rt.reset_timers()
+    tev0, tsp0 = rt.counter("synaptic_events"), rt.counter("spikes")
+    probe_steps = min(args.steps * block, 2000)
+    rt.step_time(probe_steps)
+    rt.synchronize()
+    tev, tsp = rt.counter("synaptic_events") - tev0, rt.counter("spikes") - tsp0
+    pre_s, neu_s = rt.timer("presynaptic_update"), rt.timer("neuron_update")
+    rt.enable_timing(False)
+    nat_bytes = tev * bpe + tsp * ALGO_BYTES_PER_SPIKE
+    nat_gbs = nat_bytes / pre_s / 1e9 if pre_s > 0 else 0.0
+    roofline = {"kernel": "presynapticSparseKernel", "bound": "hbm", "achieved": nat_gbs, "peak": hbm_peak,
+                "unit": "GB/s", "frac": nat_gbs / hbm_peak, "traffic": None, "peak_source": peak_kind,
+                "launches": probe_steps, "avg_launch_us": pre_s / probe_steps * 1e6,
+                "neuron_kernel_avg_launch_us": neu_s / probe_steps * 1e6,
+                "algorithmic_bytes_per_launch": nat_bytes / probe_steps,
+                "note": "natural firing rates: ~0.1 MB per launch, latency-bound by construction"}
+
+    # ---- same kernel at saturation: a quarter of every population spikes in one step ----
+    roofline_sat = None
+    if not args.no_saturated:
+        rng = np.random.default_rng(99)
+        sat_events = 0
+        out_deg = {}
+        for s in net.syns:
+            rl = rt.array(f"{s.name}.row_length").astype(np.int64)
+            out_deg[s.src] = out_deg.get(s.src, 0) + rl
+        sat_spikes = 0
+        for p in net.pops:
+            ids = np.sort(rng.choice(p.n, size=p.n // 4, replace=False)).astype(np.uint32)
+            rt.set_spike_list(p.name, ids)
+            if p.name in out_deg:
+                sat_events += int(out_deg[p.name][ids].sum())
+            sat_spikes += len(ids)
+        rt.set_option("count_events", 0)
+        for _ in range(3):
+            rt.update_synapses()
+        rt.enable_timing(True)
+        rt.reset_timers()
+        reps = 10
+        for _ in range(reps):
+            rt.update_synapses()
+        rt.synchronize()
+        sat_s = rt.timer("presynaptic_update") / reps
+        rt.enable_timing(False)
+        sat_bytes = sat_events * bpe + sat_spikes * ALGO_BYTES_PER_SPIKE
+        roofline_sat = {"kernel": "presynapticSparseKernel", "bound": "hbm", "achieved": sat_bytes / sat_s / 1e9,
+                        "peak": hbm_peak, "unit": "GB/s", "frac": sat_bytes / sat_s / 1e9 / hbm_peak,
+                        "traffic": None, "peak_source": peak_kind, "events_per_launch": sat_events,
+                        "algorithmic_bytes_per_launch": sat_bytes, "launch_ms": sat_s * 1e3,
+                        "events_per_s": sat_events / sat_s,
+                        "note": "25% of every population spiking in one step; inputs larger than L2"}
+
+    # ---- CPU baseline on this box's host (rank 0, N=1 only) ------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        try:
+            r = run_reference_sample(args.ref_scale, block, 1, 0)
+            cpu = {"value": r["events_per_s"], "unit": "synaptic events/s", "cores": 1, "kind": r["kind"],
+                   "realtime_factor": r["rtf"],
+                   "sample": f"Potjans neuron_scale={args.ref_scale} (published in-degrees, {r['synapses']} synapses), "
+                             f"{r['total_steps']} time steps, {r['seconds']:.2f} s of CPU time"}
+        except Exception as e:      # the baseline is reported, never required
+            cpu = {"value": None, "unit": "synaptic events/s", "cores": 1, "kind": "port", "sample": f"failed: {e}"}
+
+    if rank == 0:
+        n_neurons = sum(p.n for p in net.pops)
+        line = {
+            "metric": "synaptic events/s (Potjans microcircuit architecture)",
+            "value": value, "unit": "synaptic events/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic",
+            "realtime_factor": seconds / sim_seconds,
+            "us_per_timestep": ms * 1e3 / (args.steps * block),
+            "config": {"workload": f"Potjans-Diesmann microcircuit architecture x{scale:g}: {n_neurons} LIF neurons, "
+                                   f"published in-degrees, SPARSE with dendritic delays, PoissonExp background, "
+                                   f"dt=0.1 ms; one bench step = {block} time steps (0.1 s biological)",
+                       "parallelism": f"postsynaptic sharding over {world} GPU(s)" if world > 1 else "single GPU",
+                       "l2": "working set (2.5 GB of synapses) exceeds L2; no flush needed",
+                       "spikes_per_s_biological": spikes / sim_seconds,
+                       "mean_rates_hz": rates, "bytes_per_event": bpe},
+            "clocks": clocks,
+            "e2e": {"value": e2e_events / e2e_seconds, "unit": "synaptic events/s", "h2d_bytes_per_step": 0,
+                    "d2h_bytes_per_step": d2h, "realtime_factor": e2e_seconds / sim_seconds,
+                    "note": "GeNNModel.step_time + pull_recording_buffers_from_device into page-locked memory; "
+                            "the model takes no per-step host input (background drive is drawn on the device, as in "
+                            "the reference script)"},
+            "gpu_launches": int(l1 - l0),
+            "roofline": roofline,
+            "roofline_saturated": roofline_sat,
+            "cpu_baseline": cpu,
+        }
+        print(json.dumps(line), flush=True)
+    model.unload()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

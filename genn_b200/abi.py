@@ -90,6 +90,8 @@ _PROTOTYPES = {
     "b200_device_count": [C.POINTER(C.c_int)],
     "b200_array_alloc": [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)],
     "b200_array_free": [C.c_void_p, C.c_void_p],
+    "b200_host_alloc": [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)],
+    "b200_host_free": [C.c_void_p, C.c_void_p],
     "b200_array_push": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],
     "b200_array_pull": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],
     "b200_array_memset": [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t],

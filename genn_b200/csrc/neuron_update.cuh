@@ -37,6 +37,7 @@ struct NeuronLaunch
     unsigned long long seed;
     unsigned long long num_recording_timesteps;
     StepState *state;
+    unsigned int count_events;
 };
 
 __global__ void __launch_bounds__(NEURON_BLOCK)
@@ -184,6 +185,7 @@ neuronUpdateKernel(const NeuronLaunch L)
             base = atomicAdd(&g.spk_cnt[b * slots + wslot], __popc(ballot));
         }
         base = __shfl_sync(0xFFFFFFFFu, base, 0);
+        if(L.count_events && lane == 0) atomicAdd(&L.state->spikes, (unsigned long long)__popc(ballot));
         if(spiked) {
             const unsigned int pos = base + __popc(ballot & ((1u << lane) - 1u));
             if(pos < N) {
@@ -203,12 +205,8 @@ neuronUpdateKernel(const NeuronLaunch L)
     if(g.record_spk && L.num_recording_timesteps) {
         const unsigned int words = (N + 31u) / 32u;
         unsigned int *rec = g.record_spk + ((timestep % L.num_recording_timesteps) * L.batch + b) * words;
-        if((g.first_neuron & 31u) == 0u) {
-            if(lane == 0 && local < ((g.num_update + 31u) & ~31u) && (i / 32u) < words) rec[i / 32u] = ballot;
-        }
-        else if(spiked) {
-            atomicOr(&rec[i / 32u], 1u << (i & 31u));
-        }
+        // first_neuron is a multiple of 32, so a warp covers exactly one word
+        if(lane == 0 && local < ((g.num_update + 31u) & ~31u) && (i / 32u) < words) rec[i / 32u] = ballot;
     }
 
     // ---- last block: queue update for the next step and counter advance -------

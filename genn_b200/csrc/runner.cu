@@ -246,6 +246,7 @@ int enqueueNeurons(b200_runner *r, unsigned long long numRec, bool capturing)
     L.seed = r->seed;
     L.num_recording_timesteps = numRec;
     L.state = r->state;
+    L.count_events = r->countEvents ? 1u : 0u;
     const dim3 grid(r->neuronTable.blocks, r->batch, 1);
     neuronUpdateKernel<<<grid, NEURON_BLOCK, 0, r->stream>>>(L);
     r->launches++;
@@ -363,6 +364,21 @@ int b200_array_alloc(b200_runner *r, size_t bytes, void **device_ptr)
     CUDA_TRY(cudaMemsetAsync(p, 0, bytes + ARRAY_TAIL_PAD, r->stream));
     r->arrays[p] = bytes;
     *device_ptr = p;
+    return B200_OK;
+}
+
+int b200_host_alloc(b200_runner *r, size_t bytes, void **host_ptr)
+{
+    if(!r || !host_ptr) return fail(B200_ERR_INVALID, "bad arguments to b200_host_alloc");
+    CUDA_TRY(cudaSetDevice(r->device));
+    CUDA_TRY(cudaHostAlloc(host_ptr, bytes ? bytes : 1, cudaHostAllocPortable));
+    return B200_OK;
+}
+
+int b200_host_free(b200_runner *r, void *host_ptr)
+{
+    (void)r;
+    CUDA_TRY(cudaFreeHost(host_ptr));
     return B200_OK;
 }
 
@@ -665,6 +681,7 @@ int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
     CUDA_TRY(cudaMemcpy(&s, r->state, sizeof(s), cudaMemcpyDeviceToHost));
     const std::string n(name);
     if(n == "synaptic_events") *value = s.synaptic_events;
+    else if(n == "spikes") *value = s.spikes;
     else if(n == "timestep") *value = s.timestep;
     else if(n == "steps_done") *value = s.steps_done;
     else return fail(B200_ERR_INVALID, "unknown counter %s", name);

@@ -166,7 +166,9 @@ class Variable:
     @property
     def view(self) -> np.ndarray:
         if self._view is None:
-            raise RuntimeError(f"variable '{self.name}' is not loaded")
+            if self._array is None:
+                raise RuntimeError(f"variable '{self.name}' is not loaded")
+            self._view = np.zeros(self.shape, dtype=self.dtype)     # host side made on first use
         return self._view
 
     @property
@@ -178,10 +180,10 @@ class Variable:
         self.view[...] = v
 
     def push_to_device(self):
-        self._array.push(self._view)
+        self._array.push(self.view)
 
     def pull_from_device(self):
-        self._array.pull(self._view)
+        self._array.pull(self.view)
 
     @property
     def device_pointer(self) -> int:

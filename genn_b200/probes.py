@@ -1,0 +1,67 @@
+"""Small, bounded workloads for profiling single kernels under ncu.
+
+    python -m genn_b200.probes presyn --scale 0.5 --fraction 0.25 --reps 3
+
+builds the Potjans architecture at ``--scale`` times the neurons (in-degree
+and therefore row lengths unchanged), marks ``--fraction`` of every population
+as having spiked, and launches the presynaptic update ``--reps`` times.  The
+device holds about 2.6 GB x scale; one launch reads about
+scale x fraction x 2.1 GB, so scale 0.5 / fraction 0.25 is twice the L2.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+
+import numpy as np
+
+
+def presyn(args):
+    from . import workloads
+    from .runtime import Runtime
+    model = workloads.potjans(neuron_scale=args.scale, seed=1234)
+    model.build()
+    rt = Runtime(model, None)
+    net = rt.net
+    rng = np.random.default_rng(99)
+    events = 0
+    out_deg = {}
+    for s in net.syns:
+        rl = rt.array(f"{s.name}.row_length").astype(np.int64)
+        out_deg[s.src] = out_deg.get(s.src, 0) + rl
+    spikes = 0
+    for p in net.pops:
+        ids = np.sort(rng.choice(p.n, size=max(1, int(p.n * args.fraction)), replace=False)).astype(np.uint32)
+        rt.set_spike_list(p.name, ids)
+        events += int(out_deg[p.name][ids].sum()) if p.name in out_deg else 0
+        spikes += len(ids)
+    rt.set_option("spike_lanes", args.lanes)
+    for _ in range(2):
+        rt.update_synapses()
+    rt.enable_timing(True)
+    rt.reset_timers()
+    for _ in range(args.reps):
+        rt.update_synapses()
+    rt.synchronize()
+    sec = rt.timer("presynaptic_update") / args.reps
+    print(json.dumps({"probe": "presyn", "scale": args.scale, "fraction": args.fraction, "lanes": args.lanes,
+                      "events_per_launch": events, "spikes_per_launch": spikes, "launch_ms": sec * 1e3,
+                      "events_per_s": events / sec, "GBps_at_7B": (events * 7 + spikes * 8) / sec / 1e9}))
+    rt.close()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    sub = ap.add_subparsers(dest="cmd", required=True)
+    p = sub.add_parser("presyn")
+    p.add_argument("--scale", type=float, default=0.5)
+    p.add_argument("--fraction", type=float, default=0.25)
+    p.add_argument("--reps", type=int, default=3)
+    p.add_argument("--lanes", type=int, default=16)
+    p.set_defaults(fn=presyn)
+    args = ap.parse_args()
+    args.fn(args)
+
+
+if __name__ == "__main__":
+    main()

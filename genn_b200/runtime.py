@@ -56,6 +56,27 @@ class DeviceFactory(ArrayFactory):
         check(self.lib.b200_array_memset(self.handle, handle.ptr, value, nbytes))
 
 
+class _LazyRecording:
+    """List-like [(times, ids)] per batch element, decoded on first access."""
+
+    def __init__(self, rt, pop):
+        self._rt, self._pop, self._data = rt, pop, None
+
+    def _get(self):
+        if self._data is None:
+            self._data = self._rt.recorded_spikes(self._pop)
+        return self._data
+
+    def __getitem__(self, i):
+        return self._get()[i]
+
+    def __len__(self):
+        return len(self._get())
+
+    def __iter__(self):
+        return iter(self._get())
+
+
 class Runtime:
     """One loaded model on one GPU."""
 
@@ -69,6 +90,9 @@ class Runtime:
         check(self.lib.b200_runner_create(device, self.net.dt, self.net.seed, self.net.batch_size, C.byref(h)))
         self.handle = h
         self.factory = DeviceFactory(self.lib, self.handle)
+        self._pinned = []
+        self._rec_host = {}
+        self._rec_timestep = 0
         self.plan = Plan(self.net, self.factory, self.num_recording_timesteps, shard=shard)
         self._run_init_tasks()
         for i, d in enumerate(self.plan.neuron_descs):
@@ -137,13 +161,12 @@ class Runtime:
             for name, var in p.vars.items():
                 arr = a[f"{p.name}.{name}"]
                 var._array = arr.handle
-                var._view = np.zeros(arr.shape, dtype=arr.dtype)
-                self.factory.pull(arr.handle, var._view)
+                var.shape = arr.shape
         for c in m.current_sources.values():
             for name, var in c.vars.items():
                 arr = a[f"{c.name}.{name}"]
                 var._array = arr.handle
-                var._view = np.zeros(arr.shape, dtype=arr.dtype)
+                var.shape = arr.shape
         from .model import Variable
         for sg in m.synapse_populations.values():
             rs = self.net.syn(sg.name)
@@ -153,12 +176,10 @@ class Runtime:
                 if arr is not None:
                     v = Variable(name, arr.dtype, None, arr.shape)
                     v._array = arr.handle
-                    v._view = np.zeros(arr.shape, dtype=arr.dtype)
                     sg.vars[name] = v
             arr = a[f"psm{rs.psm}.out_post"]
             v = Variable("outPost", arr.dtype, None, arr.shape)
             v._array = arr.handle
-            v._view = np.zeros(arr.shape, dtype=arr.dtype)
             sg.out_post = v
             if rs.matrix == "SPARSE" and rs.row_length is not None:
                 sg.row_lengths, sg.ind = rs.row_length, rs.ind
@@ -243,32 +264,73 @@ class Runtime:
         cnt = int(self.array(f"{name}.spk_cnt")[batch, slot])
         return self.array(f"{name}.spk")[batch, slot, :cnt].copy()
 
+    def pinned_empty(self, shape, dtype) -> np.ndarray:
+        """Page-locked host array (cudaHostAlloc) owned by this runtime."""
+        dtype = np.dtype(dtype)
+        nbytes = max(1, int(np.prod(shape, dtype=np.int64)) * dtype.itemsize)
+        p = C.c_void_p()
+        check(self.lib.b200_host_alloc(self.handle, nbytes, C.byref(p)))
+        self._pinned.append(p.value)
+        buf = (C.c_uint8 * nbytes).from_address(p.value)
+        return np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape, dtype=np.int64))).reshape(shape)
+
     def pull_recording_buffers(self):
-        """Decode the spike-recording bit words into (times, ids) per batch
-        element, as Runtime::getRecordedEvents does (runtime.cc:855-913)."""
+        """Copy the spike-recording bit words to page-locked host memory
+        (Runtime::pullRecordingBuffersFromDevice, runtime.cc:720-746).  Decoding
+        into (times, ids) happens lazily in :meth:`recorded_spikes`."""
         T = self.num_recording_timesteps
         if not T:
             raise Exception("Recording buffer not allocated - cannot pull from device")
-        ts = self.timestep
+        self.synchronize()
+        self._rec_timestep = self.timestep
+        for p in self.net.pops:
+            arr = self.plan.arrays.get(f"{p.name}.record")
+            if arr is None:
+                continue
+            host = self._rec_host.get(p.name)
+            if host is None:
+                host = self._rec_host[p.name] = self.pinned_empty(arr.shape, arr.dtype)
+            self.factory.pull(arr.handle, host)
+            if self.model is not None:
+                self.model.neuron_populations[p.name]._spike_recording_data = _LazyRecording(self, p.name)
+
+    def recorded_spikes(self, pop: str):
+        """Decode pulled recording words into [(times, ids)] per batch element,
+        as Runtime::getRecordedEvents does (runtime.cc:855-913)."""
+        T = self.num_recording_timesteps
+        ts = self._rec_timestep
         if ts < T:
             raise Exception("Event recording data can only be accessed once buffer is full")
+        p = self.net.pop(pop)
         start = (ts - T) * self.net.dt
-        for p in self.net.pops:
-            if f"{p.name}.record" not in self.plan.arrays:
-                continue
-            words = self.array(f"{p.name}.record")          # [T][B][W]
-            # buffer is a ring over timestep % T: rotate so index 0 is the oldest step
-            words = np.roll(words, -(ts % T), axis=0)
-            out = []
-            for b in range(self.net.batch_size):
-                bits = np.unpackbits(words[:, b, :].view(np.uint8), axis=1, bitorder="little")[:, :p.n]
-                step, ids = np.nonzero(bits)
-                out.append((start + step * self.net.dt, ids.astype(np.uint32)))
-            if self.model is not None:
-                self.model.neuron_populations[p.name]._spike_recording_data = out
-            p.recorded = out
+        # the buffer is a ring over timestep % T: rotate so index 0 is the oldest step
+        words = np.roll(self._rec_host[pop], -(ts % T), axis=0)
+        out = []
+        for b in range(self.net.batch_size):
+            bits = np.unpackbits(np.ascontiguousarray(words[:, b, :]).view(np.uint8), axis=1, bitorder="little")[:, :p.n]
+            step, ids = np.nonzero(bits)
+            out.append((start + step * self.net.dt, ids.astype(np.uint32)))
+        return out
+
+    # -- measurement helpers ------------------------------------------------------
+    def set_spike_list(self, pop: str, ids: np.ndarray, batch: int = 0):
+        """Overwrite the spike list the NEXT presynaptic update will read for
+        ``pop`` (zero axonal delay).  Used to drive the presynaptic kernels with a
+        chosen load when measuring them in isolation."""
+        p = self.net.pop(pop)
+        slot = self.steps_done % p.runtime_slots
+        cnt = self.array(f"{pop}.spk_cnt")
+        cnt[batch, slot] = len(ids)
+        self.plan.push(f"{pop}.spk_cnt", cnt)
+        arr = self.plan.arrays[f"{pop}.spk"]
+        ids = np.ascontiguousarray(ids, dtype=np.uint32)
+        offset = ((batch * p.runtime_slots + slot) * p.n) * 4
+        check(self.lib.b200_array_push(self.handle, arr.ptr + offset, ids.ctypes.data, ids.nbytes))
 
     def close(self):
         if self.handle:
+            for p in self._pinned:
+                self.lib.b200_host_free(self.handle, p)
+            self._pinned = []
             self.lib.b200_runner_destroy(self.handle)
             self.handle = None

@@ -215,6 +215,10 @@ int  b200_device_count(int *count);
  *      (backendBase.h:305-312, runtime.h:95-182) ---------------------------- */
 int  b200_array_alloc(b200_runner *r, size_t bytes, void **device_ptr);
 int  b200_array_free(b200_runner *r, void *device_ptr);
+/* Page-locked host memory for the host side of an array (the reference's Array::allocate
+ * uses cudaHostAlloc, src/genn/backends/cuda/backend.cc:88-101). */
+int  b200_host_alloc(b200_runner *r, size_t bytes, void **host_ptr);
+int  b200_host_free(b200_runner *r, void *host_ptr);
 int  b200_array_push(b200_runner *r, void *device_ptr, const void *host, size_t bytes);
 int  b200_array_pull(b200_runner *r, void *host, const void *device_ptr, size_t bytes);
 int  b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes);
@@ -254,7 +258,7 @@ int  b200_synchronize(b200_runner *r);
 int  b200_get_timestep(b200_runner *r, uint64_t *timestep);
 int  b200_set_timestep(b200_runner *r, uint64_t timestep);
 int  b200_get_steps_done(b200_runner *r, uint64_t *steps);
-/* Device-side counters: "synaptic_events" (when option count_events is on), "timestep", "steps_done". */
+/* Device-side counters: "synaptic_events" and "spikes" (when option count_events is on), "timestep", "steps_done". */
 int  b200_get_counter(b200_runner *r, const char *name, uint64_t *value);
 /* Tuning knobs (the counterpart of the backend Preferences, backends/cuda/backend.h:64-115):
  * "spike_lanes" (grid.y of the SPARSE kernel), "use_graph", "graph_steps", "count_events". */

@@ -65,7 +65,7 @@ def test_graph_replay_and_recording_match_reference_golden(name):
     for p in net.pops:
         if not p.record:
             continue
-        times, ids = p.recorded[0]
+        times, ids = rt.recorded_spikes(p.name)[0]
         got = helpers.sorted_pairs(np.stack([np.rint(times / net.dt).astype(np.uint32), ids], axis=1))
         assert np.array_equal(got, want[f"spikes_{p.name}"]), f"recorded spikes of {p.name} differ"
     final = {k: v for k, v in helpers.snapshot(_Adapter(rt), net, steps).items()}

@@ -20,8 +20,16 @@ struct StepState
     unsigned long long steps_done;
     unsigned int ticket;
     unsigned int error;
+    // steps_done modulo ring_period, a common multiple of every ring size (spike
+    // queue depths, dendritic-delay depths), so ring slots come from 32-bit
+    // arithmetic: (phase + c) % n == (steps_done + c) % n for every ring size n
+    unsigned int phase;
+    unsigned int ring_period;
     unsigned long long synaptic_events;   // only advanced when event counting is on
     unsigned long long spikes;
+    // SM clock cycles CTA 0 spent in each phase of the persistent kernel:
+    // presynaptic work, barrier after it, neuron work, barrier after it
+    unsigned long long phase_cycles[4];
 };
 
 constexpr unsigned int ERR_SPIKE_OVERFLOW = 1u;
@@ -35,15 +43,16 @@ constexpr unsigned int ERR_DELAY_RANGE = 4u;
 __device__ __forceinline__ unsigned int findGroup(const unsigned int *__restrict__ block_start,
                                                   unsigned int num_groups, unsigned int block)
 {
+    // plain loads: the table may live in shared memory
     if(num_groups <= 8) {
         unsigned int g = 0;
-        while(g + 1 < num_groups && block >= __ldg(&block_start[g + 1])) g++;
+        while(g + 1 < num_groups && block >= block_start[g + 1]) g++;
         return g;
     }
     unsigned int lo = 0, hi = num_groups;
     while(hi - lo > 1) {
         const unsigned int mid = (lo + hi) >> 1;
-        if(block >= __ldg(&block_start[mid])) lo = mid; else hi = mid;
+        if(block >= block_start[mid]) lo = mid; else hi = mid;
     }
     return lo;
 }
@@ -54,8 +63,8 @@ __device__ __forceinline__ void redAdd(float *addr, float v)
     atomicAdd(addr, v);
 }
 
-__device__ __forceinline__ unsigned int ringSlot(unsigned long long k, unsigned int slots)
+__device__ __forceinline__ unsigned int ringSlot(unsigned int k, unsigned int slots)
 {
-    return (unsigned int)(k % slots);
+    return k % slots;
 }
 }   // namespace b200

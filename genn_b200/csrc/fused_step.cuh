@@ -1,0 +1,319 @@
+// Persistent fused time-step kernel: many simulation steps in ONE cooperative
+// launch, the presynaptic update and the neuron update separated by grid-wide
+// barriers instead of kernel boundaries.
+//
+// The reference issues 2-7 tiny kernels per step on stream 0
+// (backendCUDAHIP.cc:386-420, 548-589).  On the Potjans microcircuit a step
+// moves under a megabyte, so its cost is launch and dependency latency, not
+// bandwidth.  Here one CTA set stays resident (cooperative launch, a multiple of
+// the SM count) and loops over the steps:
+//
+//   phase A  presynaptic update, work item = (spike, 128-synapse chunk of its
+//            row), one WARP per item, items of all merged SPARSE groups
+//            flattened: every warp reads the spike counts of all sources with
+//            one lane each, prefix-sums them with shuffles and strides through
+//            the item space.  Spike ids are fetched with the counts (one round
+//            trip), the row length with the row data (one more).
+//   barrier  (reductions into outPost/denDelay must have landed)
+//   phase B  neuron update of every merged group, one thread per neuron, spike
+//            emission with warp-aggregated atomics; one thread clears the spike
+//            counts of the slot the next step writes.
+//   barrier  (spike lists complete)
+//
+// Two barriers per step are inherent while zero-step dendritic delays exist
+// (a synapse with d = 0 feeds the neuron update of the same step).  The barrier
+// is a monotonic 64-bit arrival counter in global memory; every wait is bounded
+// and a time-out sets an error flag and ends the kernel on all CTAs.
+//
+// Data written by other SMs between barriers (postsynaptic input, spike lists)
+// is read with ld.global.cg so a stale L1 line can never be used.
+#pragma once
+
+#include "common.cuh"
+#include "neuron_update.cuh"
+#include "presynaptic_update.cuh"
+
+namespace b200
+{
+constexpr int FUSED_BLOCK = 768;          // one CTA per SM, 85 registers per thread
+constexpr unsigned int FUSED_CHUNK = 32 * PRE_VEC;          // synapses per warp item
+constexpr unsigned int FUSED_PREFETCH_IDS = 8;              // spike ids fetched together with each count
+constexpr unsigned int ERR_BARRIER_TIMEOUT = 8u;
+constexpr unsigned long long BARRIER_SPIN_LIMIT = 1ull << 24; // polls (tens of ms) before giving up
+
+// One spike source as the presynaptic phase sees it: a (population, axonal
+// delay) pair and the slice of the item table that lists every (group, chunk)
+// a spike of this source has to visit.
+struct FusedSource
+{
+    const unsigned int *spk_cnt;
+    const unsigned int *spk;
+    unsigned int num_src;
+    unsigned int slots;
+    unsigned int delay;
+    unsigned int item_begin;
+    unsigned int item_count;
+    unsigned int pad;
+};
+
+struct FusedLaunch
+{
+    NeuronLaunch neuron;                 // groups, batch(=1), dt, seed, recording, state
+    const unsigned int *slot_start;      // [num_groups+1] first thread slot of each neuron group (multiples of 32)
+    const b200_synapse_group *sgroups;
+    const FusedSource *sources;
+    const uint2 *items;                  // (synapse group index, chunk index)
+    unsigned int num_sources;
+    unsigned int num_sgroups;
+    unsigned int num_items;
+    unsigned int stage_in_smem;          // tables fit the dynamic shared memory the host reserved
+    unsigned int count_events;
+    unsigned int profile;                // accumulate phase_cycles (CTA 0, thread 0)
+    unsigned long long num_steps;
+    unsigned long long *barrier;         // monotonic arrival counter
+};
+
+__device__ __forceinline__ unsigned long long loadAcquire(const unsigned long long *p)
+{
+    unsigned long long v;
+    asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// Grid-wide barrier with a bounded wait.  Returns false if it timed out (or any
+// CTA reported an error), in which case every CTA leaves the kernel.
+__device__ __forceinline__ bool gridBarrier(const FusedLaunch &L, unsigned long long &epoch, bool *ok)
+{
+    __syncthreads();
+    if(threadIdx.x == 0) {
+        // release + arrive in one fire-and-forget reduction: nothing waits for its return
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" :: "l"(L.barrier), "l"(1ull) : "memory");
+        epoch += gridDim.x;
+        unsigned long long polls = 0;
+        bool good = true;
+        while(loadAcquire(L.barrier) < epoch) {
+            if(++polls > BARRIER_SPIN_LIMIT) {
+                atomicOr(&L.neuron.state->error, ERR_BARRIER_TIMEOUT);
+                good = false;
+                break;
+            }
+        }
+        *ok = good;
+    }
+    __syncthreads();
+    return *ok;
+}
+
+template<typename IndT>
+__device__ __forceinline__ void fusedChunk(const b200_synapse_group &g, unsigned int pre, unsigned int chunk,
+                                           unsigned int k, StepState *state)
+{
+    const unsigned int D = g.max_den_delay;
+    float *target = D ? g.den_delay : g.out_post;
+    sparseQuad<IndT>(g, pre, chunk * 32u + (threadIdx.x & 31u), target, D ? ringSlot(k + 1, D) : 0u, state);
+}
+
+// Copy `bytes` (a multiple of 4) from global to shared memory with the whole CTA.
+__device__ __forceinline__ void stageWords(void *dst, const void *src, size_t bytes)
+{
+    unsigned int *d = static_cast<unsigned int*>(dst);
+    const unsigned int *s = static_cast<const unsigned int*>(src);
+    for(size_t w = threadIdx.x; w < bytes / 4; w += blockDim.x) d[w] = __ldg(&s[w]);
+}
+
+__host__ __device__ inline size_t align16(size_t x) { return (x + 15) & ~(size_t)15; }
+
+// The acquire side of every grid barrier invalidates the SM's L1, so a
+// descriptor left in global memory would cost a full L2 round trip per field
+// and per step, one after another along the dependency chain.  All merged-group
+// tables are therefore staged into shared memory once per launch.
+template<int NPSM, int NCS>
+__global__ void __launch_bounds__(FUSED_BLOCK, 1)
+fusedStepKernel(FusedLaunch L)
+{
+    extern __shared__ __align__(16) unsigned char fusedSmem[];
+    __shared__ bool barrierOk;
+    __shared__ unsigned int headCnt[32], headSlot[32], headIds[32][FUSED_PREFETCH_IDS];
+    if(L.stage_in_smem) {
+        unsigned char *p = fusedSmem;
+        const size_t nb = sizeof(b200_neuron_group) * L.neuron.num_groups;
+        stageWords(p, L.neuron.groups, nb);
+        L.neuron.groups = reinterpret_cast<const b200_neuron_group*>(p);
+        p += align16(nb);
+        const size_t sb = sizeof(b200_synapse_group) * L.num_sgroups;
+        stageWords(p, L.sgroups, sb);
+        L.sgroups = reinterpret_cast<const b200_synapse_group*>(p);
+        p += align16(sb);
+        const size_t rb = sizeof(FusedSource) * L.num_sources;
+        stageWords(p, L.sources, rb);
+        L.sources = reinterpret_cast<const FusedSource*>(p);
+        p += align16(rb);
+        const size_t ib = sizeof(uint2) * L.num_items;
+        stageWords(p, L.items, ib);
+        L.items = reinterpret_cast<const uint2*>(p);
+        p += align16(ib);
+        const size_t tb = sizeof(unsigned int) * (L.neuron.num_groups + 1);
+        stageWords(p, L.slot_start, tb);
+        L.slot_start = reinterpret_cast<const unsigned int*>(p);
+        __syncthreads();
+    }
+    const unsigned int lane = threadIdx.x & 31u;
+    const unsigned int warpsPerBlock = blockDim.x >> 5;
+    // work items go round-robin over CTAs first: a handful of items per step must
+    // spread over every SM, because one SM retires scattered reductions slowly
+    const unsigned int gwarp = (threadIdx.x >> 5) * gridDim.x + blockIdx.x;
+    const unsigned int totalWarps = gridDim.x * warpsPerBlock;
+    const unsigned int gthread = blockIdx.x * blockDim.x + threadIdx.x;
+    const unsigned int totalThreads = gridDim.x * blockDim.x;
+    StepState *state = L.neuron.state;
+    const unsigned int period = state->ring_period;
+    unsigned int k = state->phase;
+    const unsigned long long t0 = state->timestep;
+    unsigned long long epoch = 0;        // the host zeroes the arrival counter before every launch
+    const unsigned int numGroups = L.neuron.num_groups;
+    const unsigned int totalSlots = L.slot_start[numGroups];
+
+    // Register-resident neuron state: when every neuron slot has a thread of its
+    // own, the thread keeps its neuron's variables in registers for the whole
+    // launch and only the dendritic-delay front (and inputs that take reductions
+    // directly) touch memory each step.
+    const bool resident = totalSlots <= totalThreads;
+    const bool mine = resident && gthread < totalSlots;
+    unsigned int myGroup = 0, myLocal = 0;
+    bool myActive = false;
+    unsigned long long myIndex = 0;
+    NeuronRegs<NPSM, NCS> regs;
+    if(mine) {
+        myGroup = findGroup(L.slot_start, numGroups, gthread);
+        myLocal = gthread - L.slot_start[myGroup];
+        const b200_neuron_group &g = L.neuron.groups[myGroup];
+        myActive = myLocal < g.num_update;
+        myIndex = g.first_neuron + myLocal;
+        if(myActive) loadNeuron<true>(g, myIndex, regs);
+    }
+
+    const bool prof = L.profile && gthread == 0;
+    long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
+    for(unsigned long long step = 0; step < L.num_steps; step++) {
+        if(prof) c0 = clock64();
+
+        // ---------------- phase A: presynaptic update ------------------------------
+        for(unsigned int base = 0; base < L.num_sources; base += 32u) {
+            // ONE warp per CTA fetches every source's spike count together with its
+            // first spike ids (fetched before the count is known: entries past the
+            // count are stale but valid memory) and shares them through shared
+            // memory.  If every warp of the grid read these few words itself, the
+            // L2 slices holding them would serialise thousands of requests.
+            if(threadIdx.x < 32u) {
+                const unsigned int si = base + lane;
+                unsigned int cnt = 0, rslot = 0;
+                if(si < L.num_sources) {
+                    const FusedSource &src = L.sources[si];
+                    rslot = ringSlot(k + src.slots - src.delay, src.slots);
+                    const unsigned int *list = src.spk + (unsigned long long)rslot * src.num_src;
+                    cnt = __ldcg(&src.spk_cnt[rslot]);
+                    #pragma unroll
+                    for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
+                        headIds[lane][j] = (j < src.num_src) ? __ldcg(&list[j]) : 0u;
+                    }
+                }
+                headCnt[lane] = cnt;
+                headSlot[lane] = rslot;
+            }
+            __syncthreads();
+            const unsigned int cnt = headCnt[lane];
+            const unsigned int per = (base + lane < L.num_sources) ? L.sources[base + lane].item_count : 0u;
+            unsigned int incl = cnt * per;
+            #pragma unroll
+            for(int o = 1; o < 32; o <<= 1) {
+                const unsigned int v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if(lane >= o) incl += v;
+            }
+            const unsigned int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+            for(unsigned int it = gwarp; it < total; it += totalWarps) {
+                const unsigned int owner = __ffs(__ballot_sync(0xFFFFFFFFu, incl > it)) - 1u;
+                const unsigned int ownIncl = __shfl_sync(0xFFFFFFFFu, incl, owner);
+                const unsigned int ownPer = __shfl_sync(0xFFFFFFFFu, per, owner);
+                const unsigned int ownCnt = headCnt[owner];
+                const unsigned int rel = it - (ownIncl - ownCnt * ownPer);
+                const unsigned int s = rel / ownPer;
+                const unsigned int c = rel - s * ownPer;
+                const FusedSource &src = L.sources[base + owner];
+                const unsigned int pre = (s < FUSED_PREFETCH_IDS)
+                    ? headIds[owner][s]
+                    : __ldcg(&src.spk[(unsigned long long)headSlot[owner] * src.num_src + s]);
+                const uint2 item = L.items[src.item_begin + c];
+                const b200_synapse_group &g = L.sgroups[item.x];
+                if(pre < g.num_src) {
+                    switch(g.ind_bytes) {
+                    case 1: fusedChunk<uint8_t>(g, pre, item.y, k, state); break;
+                    case 2: fusedChunk<uint16_t>(g, pre, item.y, k, state); break;
+                    default: fusedChunk<uint32_t>(g, pre, item.y, k, state); break;
+                    }
+                    if(L.count_events && item.y == 0 && lane == 0) {
+                        atomicAdd(&state->synaptic_events, (unsigned long long)__ldg(&g.row_length[pre]));
+                    }
+                }
+                else if(lane == 0) {
+                    atomicOr(&state->error, ERR_IND_RANGE);
+                }
+            }
+            if(base + 32u < L.num_sources) __syncthreads();     // the header arrays are reused by the next pass
+        }
+        if(prof) c1 = clock64();
+        if(!gridBarrier(L, epoch, &barrierOk)) return;
+        if(prof) c2 = clock64();
+
+        // ---------------- phase B: neuron update -----------------------------------
+        if(resident) {
+            if(mine) {
+                const b200_neuron_group &g = L.neuron.groups[myGroup];
+                const float t = B200_FMUL((float)(t0 + step), L.neuron.dt);
+                bool spiked = false;
+                if(myActive) {
+                    float front[NPSM];
+                    #pragma unroll
+                    for(unsigned int p = 0; p < NPSM; p++) {
+                        if(p < g.num_psm && !g.psm[p].max_den_delay) regs.lin[p] = __ldcg(&g.psm[p].out_post[myIndex]);
+                    }
+                    takeFronts<true, NPSM>(g, 0u, (unsigned int)myIndex, k, front);
+                    spiked = neuronCompute(L.neuron, g, 0u, (unsigned int)myIndex, t0 + step, t, regs, front);
+                    #pragma unroll
+                    for(unsigned int p = 0; p < NPSM; p++) {
+                        if(p < g.num_psm && !g.psm[p].max_den_delay) g.psm[p].out_post[myIndex] = regs.lin[p];
+                    }
+                }
+                neuronEmit<true>(L.neuron, g, 0u, myLocal, spiked, k, t0 + step, t);
+            }
+        }
+        else {
+            for(unsigned int slot = gthread; slot < totalSlots; slot += totalThreads) {
+                const unsigned int gi = findGroup(L.slot_start, numGroups, slot);
+                const b200_neuron_group &g = L.neuron.groups[gi];
+                neuronStep<true, NPSM, NCS>(L.neuron, g, 0u, slot - L.slot_start[gi], k, t0 + step);
+            }
+        }
+        // spike-queue update for the next step (neuronUpdateGroupMerged.cc:947-975)
+        if(gthread < numGroups) {
+            const b200_neuron_group &o = L.neuron.groups[gthread];
+            o.spk_cnt[ringSlot(k + 2, o.num_delay_slots)] = 0;
+        }
+        if(prof) c3 = clock64();
+        if(!gridBarrier(L, epoch, &barrierOk)) return;
+        k = (k + 1 == period) ? 0u : k + 1;
+        if(prof) {
+            const long long c4 = clock64();
+            state->phase_cycles[0] += (unsigned long long)(c1 - c0);
+            state->phase_cycles[1] += (unsigned long long)(c2 - c1);
+            state->phase_cycles[2] += (unsigned long long)(c3 - c2);
+            state->phase_cycles[3] += (unsigned long long)(c4 - c3);
+        }
+    }
+    if(mine && myActive) storeNeuron(L.neuron.groups[myGroup], myIndex, regs, true);
+    if(gthread == 0) {
+        state->timestep = t0 + L.num_steps;
+        state->steps_done = state->steps_done + L.num_steps;
+        state->phase = k;
+    }
+}
+}   // namespace b200

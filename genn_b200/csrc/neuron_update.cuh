@@ -40,44 +40,108 @@ struct NeuronLaunch
     unsigned int count_events;
 };
 
-__global__ void __launch_bounds__(NEURON_BLOCK)
-neuronUpdateKernel(const NeuronLaunch L)
+// Loads of data other SMs write between grid barriers (postsynaptic input,
+// spike times) must come from L2 when the kernel persists across time steps.
+template<bool COHERENT, typename T>
+__device__ __forceinline__ T loadShared(const T *p)
 {
-    const unsigned int gi = findGroup(L.block_start, L.num_groups, blockIdx.x);
-    const b200_neuron_group &g = L.groups[gi];
-    const unsigned int b = blockIdx.y;
-    const unsigned int N = g.num_neurons;
-    const unsigned int local = (blockIdx.x - __ldg(&L.block_start[gi])) * NEURON_BLOCK + threadIdx.x;
-    const unsigned int i = g.first_neuron + local;
-    const bool active = local < g.num_update;
+    return COHERENT ? __ldcg(p) : *p;
+}
 
-    const unsigned long long k = L.state->steps_done;
-    const unsigned long long timestep = L.state->timestep;
-    const float t = B200_FMUL((float)timestep, L.dt);
-    const unsigned int slots = g.num_delay_slots;
-    const unsigned int wslot = ringSlot(k + 1, slots);
-    const unsigned long long bi = (unsigned long long)b * N + i;
+// Everything one neuron carries from step to step, as registers: the model's
+// two state variables (bit patterns: SpikeSourceArray keeps integers), the
+// running input of each fused postsynaptic model and each current source's
+// variable.  Loading it as one batch of independent loads, before any store,
+// keeps a single memory round trip on the critical path; the persistent kernel
+// keeps it in registers across steps.
+// NPSM / NCS bound the number of fused postsynaptic models and current sources
+// of any group the kernel instance handles: the host picks the smallest
+// instance that covers the model, so the unrolled loops below carry no dead
+// iterations (a Potjans group has one of each).
+template<int NPSM, int NCS>
+struct NeuronRegs
+{
+    unsigned int v[2];
+    float lin[NPSM];
+    float cs[NCS > 0 ? NCS : 1];
+};
 
-    bool spiked = false;
-    if(active) {
-        float Isyn = 0.0f;
-        float V = 0.0f;
-        const unsigned int model = g.model;
-        if(model == B200_NEURON_LIF || model == B200_NEURON_IZHIKEVICH) {
-            V = static_cast<float*>(g.vars[0])[bi];
-        }
+__device__ __forceinline__ bool modelHasVar1(unsigned int model)
+{
+    return model != B200_NEURON_POISSON;
+}
 
-        // incoming fused postsynaptic models
-        const unsigned int numPSM = g.num_psm;
-        for(unsigned int p = 0; p < numPSM; p++) {
-            const b200_psm &psm = g.psm[p];
-            float linSyn = psm.out_post[bi];
-            const unsigned int D = psm.max_den_delay;
+template<bool COHERENT, int NPSM, int NCS>
+__device__ __forceinline__ void loadNeuron(const b200_neuron_group &g, unsigned long long bi, NeuronRegs<NPSM, NCS> &r)
+{
+    r.v[0] = static_cast<const unsigned int*>(g.vars[0])[bi];
+    r.v[1] = modelHasVar1(g.model) ? static_cast<const unsigned int*>(g.vars[1])[bi] : 0u;
+    #pragma unroll
+    for(unsigned int p = 0; p < NPSM; p++) {
+        r.lin[p] = (p < g.num_psm) ? loadShared<COHERENT>(&g.psm[p].out_post[bi]) : 0.0f;
+    }
+    #pragma unroll
+    for(unsigned int c = 0; c < NCS; c++) {
+        r.cs[c] = (c < g.num_cs && g.cs[c].var0) ? g.cs[c].var0[bi] : 0.0f;
+    }
+}
+
+template<int NPSM, int NCS>
+__device__ __forceinline__ void storeNeuron(const b200_neuron_group &g, unsigned long long bi,
+                                            const NeuronRegs<NPSM, NCS> &r, bool onlyPrivate)
+{
+    static_cast<unsigned int*>(g.vars[0])[bi] = r.v[0];
+    if(modelHasVar1(g.model) && g.model != B200_NEURON_SPIKE_SOURCE_ARRAY) static_cast<unsigned int*>(g.vars[1])[bi] = r.v[1];
+    #pragma unroll
+    for(unsigned int p = 0; p < NPSM; p++) {
+        // inputs without a dendritic-delay ring receive reductions directly and
+        // are written back every step by the caller
+        if(p < g.num_psm && (!onlyPrivate || g.psm[p].max_den_delay)) g.psm[p].out_post[bi] = r.lin[p];
+    }
+    #pragma unroll
+    for(unsigned int c = 0; c < NCS; c++) {
+        if(c < g.num_cs && g.cs[c].var0) g.cs[c].var0[bi] = r.cs[c];
+    }
+}
+
+// Front slot of every dendritic-delay ring: read and cleared
+// (neuronUpdateGroupMerged.cc:96-113).
+template<bool COHERENT, int NPSM>
+__device__ __forceinline__ void takeFronts(const b200_neuron_group &g, unsigned int b, unsigned int i,
+                                           unsigned int k, float (&front)[NPSM])
+{
+    #pragma unroll
+    for(unsigned int p = 0; p < NPSM; p++) {
+        front[p] = 0.0f;
+        if(p < g.num_psm) {
+            const unsigned int D = g.psm[p].max_den_delay;
             if(D) {
-                float *front = &psm.den_delay[((unsigned long long)b * D + ringSlot(k + 1, D)) * N + i];
-                linSyn = B200_FADD(linSyn, *front);
-                *front = 0.0f;
+                float *f = &g.psm[p].den_delay[((unsigned long long)b * D + ringSlot(k + 1, D)) * g.num_neurons + i];
+                front[p] = loadShared<COHERENT>(f);
+                *f = 0.0f;
             }
+        }
+    }
+}
+
+// One neuron, one time step, entirely in registers.  Returns whether it spiked.
+template<int NPSM, int NCS>
+__device__ __forceinline__ bool neuronCompute(const NeuronLaunch &L, const b200_neuron_group &g, unsigned int b,
+                                              unsigned int i, unsigned long long timestep, float t,
+                                              NeuronRegs<NPSM, NCS> &r, const float (&front)[NPSM])
+{
+    const unsigned int N = g.num_neurons;
+    const unsigned int model = g.model;
+    float Isyn = 0.0f;
+    float V = __uint_as_float(r.v[0]);
+
+    // incoming fused postsynaptic models
+    #pragma unroll
+    for(unsigned int p = 0; p < NPSM; p++) {
+        if(p < g.num_psm) {
+            const b200_psm &psm = g.psm[p];
+            float linSyn = B200_FADD(r.lin[p], front[p]);
+            if(!psm.max_den_delay) linSyn = r.lin[p];
             if(psm.model == B200_PSM_EXP_CURR) {
                 Isyn = B200_FADD(Isyn, B200_FMUL(psm.params[0], linSyn));
                 linSyn = B200_FMUL(linSyn, psm.params[1]);
@@ -90,93 +154,107 @@ neuronUpdateKernel(const NeuronLaunch L)
                 Isyn = B200_FADD(Isyn, linSyn);
                 linSyn = 0.0f;
             }
-            psm.out_post[bi] = linSyn;
+            r.lin[p] = linSyn;
         }
+    }
 
-        // current sources
-        const unsigned int numCS = g.num_cs;
-        for(unsigned int c = 0; c < numCS; c++) {
+    // current sources
+    #pragma unroll
+    for(unsigned int c = 0; c < NCS; c++) {
+        if(c < g.num_cs) {
             const b200_current_source &cs = g.cs[c];
             if(cs.model == B200_CS_DC) {
                 Isyn = B200_FADD(Isyn, cs.params[0]);
             }
             else {
-                float current = cs.var0[bi];
-                b200_rng rng = b200_rng_sim(L.seed, cs.rng_stream, b * N + i, timestep);
-                float p = 1.0f;
-                unsigned int numSpikes = 0;
-                const float expMinusLambda = cs.params[2];
-                do {
-                    numSpikes++;
-                    p = B200_FMUL(p, b200_rng_uniform(&rng));
-                } while(p > expMinusLambda);
-                current = B200_FADD(current, B200_FMUL(cs.params[0], (float)(numSpikes - 1)));
+                // The model draws its Poisson spike count by multiplying uniforms
+                // until the product falls below exp(-lambda)
+                // (currentSourceModels.h:111-118); here the same count comes from
+                // inverting the Poisson CDF with one uniform, a quarter of a Philox
+                // block per step instead of one or two whole blocks.
+                float current = r.cs[c];
+                const b200_philox_out blk = b200_rng_step_block(L.seed, cs.rng_stream, b * N + i, timestep);
+                const float u = b200_u32_to_uniform(b200_rng_step_word(&blk, timestep));
+                const unsigned int numSpikes = b200_poisson_inverse(u, cs.params[2], cs.params[3]);
+                current = B200_FADD(current, B200_FMUL(cs.params[0], (float)numSpikes));
                 Isyn = B200_FADD(Isyn, current);
-                current = B200_FMUL(current, cs.params[1]);
-                cs.var0[bi] = current;
+                r.cs[c] = B200_FMUL(current, cs.params[1]);
             }
-        }
-
-        if(model == B200_NEURON_LIF) {
-            float R = static_cast<float*>(g.vars[1])[bi];
-            if(R <= 0.0f) {
-                const float alpha = B200_FADD(B200_FMUL(B200_FADD(Isyn, g.params[3]), g.params[4]), g.params[2]);
-                V = B200_FSUB(alpha, B200_FMUL(g.params[5], B200_FSUB(alpha, V)));
-            }
-            else {
-                R = B200_FSUB(R, L.dt);
-            }
-            if(R <= 0.0f && V >= g.params[0]) {
-                spiked = true;
-                V = g.params[1];
-                R = g.params[6];
-            }
-            static_cast<float*>(g.vars[0])[bi] = V;
-            static_cast<float*>(g.vars[1])[bi] = R;
-        }
-        else if(model == B200_NEURON_IZHIKEVICH) {
-            float U = static_cast<float*>(g.vars[1])[bi];
-            const float dt = L.dt;
-            if(V >= 30.0f) {
-                V = g.params[2];
-                U = B200_FADD(U, g.params[3]);
-            }
-            for(int half = 0; half < 2; half++) {
-                // 0.04*V*V + 5*V + 140 - U + Isyn, left to right
-                float x = B200_FMUL(B200_FMUL(0.04f, V), V);
-                x = B200_FADD(x, B200_FMUL(5.0f, V));
-                x = B200_FADD(x, 140.0f);
-                x = B200_FSUB(x, U);
-                x = B200_FADD(x, Isyn);
-                V = B200_FADD(V, B200_FMUL(B200_FMUL(0.5f, x), dt));
-            }
-            U = B200_FADD(U, B200_FMUL(B200_FMUL(g.params[0], B200_FSUB(B200_FMUL(g.params[1], V), U)), dt));
-            if(V > 30.0f) V = 30.0f;
-            spiked = (V >= 29.99f);
-            static_cast<float*>(g.vars[0])[bi] = V;
-            static_cast<float*>(g.vars[1])[bi] = U;
-        }
-        else if(model == B200_NEURON_SPIKE_SOURCE_ARRAY) {
-            unsigned int start = static_cast<unsigned int*>(g.vars[0])[bi];
-            const unsigned int end = static_cast<const unsigned int*>(g.vars[1])[bi];
-            if(start != end && t >= __ldg(&g.egp[start])) {
-                spiked = true;
-                static_cast<unsigned int*>(g.vars[0])[bi] = start + 1;
-            }
-        }
-        else {
-            float tts = static_cast<float*>(g.vars[0])[bi];
-            if(tts <= 0.0f) {
-                b200_rng rng = b200_rng_sim(L.seed, g.rng_stream, b * N + i, timestep);
-                tts = B200_FADD(tts, B200_FMUL(g.params[0], -b200_logf(b200_rng_uniform(&rng))));
-            }
-            tts = B200_FSUB(tts, 1.0f);
-            spiked = (tts <= 0.0f);
-            static_cast<float*>(g.vars[0])[bi] = tts;
         }
     }
 
-    // ---- spike emission: ballot + one atomic per spiking warp ----------------
+    bool spiked = false;
+    if(model == B200_NEURON_LIF) {
+        float R = __uint_as_float(r.v[1]);
+        if(R <= 0.0f) {
+            const float alpha = B200_FADD(B200_FMUL(B200_FADD(Isyn, g.params[3]), g.params[4]), g.params[2]);
+            V = B200_FSUB(alpha, B200_FMUL(g.params[5], B200_FSUB(alpha, V)));
+        }
+        else {
+            R = B200_FSUB(R, L.dt);
+        }
+        if(R <= 0.0f && V >= g.params[0]) {
+            spiked = true;
+            V = g.params[1];
+            R = g.params[6];
+        }
+        r.v[0] = __float_as_uint(V);
+        r.v[1] = __float_as_uint(R);
+    }
+    else if(model == B200_NEURON_IZHIKEVICH) {
+        float U = __uint_as_float(r.v[1]);
+        const float dt = L.dt;
+        if(V >= 30.0f) {
+            V = g.params[2];
+            U = B200_FADD(U, g.params[3]);
+        }
+        for(int half = 0; half < 2; half++) {
+            // 0.04*V*V + 5*V + 140 - U + Isyn, left to right
+            float x = B200_FMUL(B200_FMUL(0.04f, V), V);
+            x = B200_FADD(x, B200_FMUL(5.0f, V));
+            x = B200_FADD(x, 140.0f);
+            x = B200_FSUB(x, U);
+            x = B200_FADD(x, Isyn);
+            V = B200_FADD(V, B200_FMUL(B200_FMUL(0.5f, x), dt));
+        }
+        U = B200_FADD(U, B200_FMUL(B200_FMUL(g.params[0], B200_FSUB(B200_FMUL(g.params[1], V), U)), dt));
+        if(V > 30.0f) V = 30.0f;
+        spiked = (V >= 29.99f);
+        r.v[0] = __float_as_uint(V);
+        r.v[1] = __float_as_uint(U);
+    }
+    else if(model == B200_NEURON_SPIKE_SOURCE_ARRAY) {
+        const unsigned int start = r.v[0], end = r.v[1];
+        if(start != end && t >= __ldg(&g.egp[start])) {
+            spiked = true;
+            r.v[0] = start + 1;
+        }
+    }
+    else {
+        float tts = V;
+        if(tts <= 0.0f) {
+            b200_rng rng = b200_rng_sim(L.seed, g.rng_stream, b * N + i, timestep);
+            tts = B200_FADD(tts, B200_FMUL(g.params[0], -b200_logf(b200_rng_uniform(&rng))));
+        }
+        tts = B200_FSUB(tts, 1.0f);
+        spiked = (tts <= 0.0f);
+        r.v[0] = __float_as_uint(tts);
+    }
+    return spiked;
+}
+
+// Spike emission (ballot + one atomic per spiking warp), spike times and
+// recording.  Called by whole warps.
+template<bool COHERENT>
+__device__ __forceinline__ void neuronEmit(const NeuronLaunch &L, const b200_neuron_group &g, unsigned int b,
+                                           unsigned int local, bool spiked, unsigned int k,
+                                           unsigned long long timestep, float t)
+{
+    const unsigned int N = g.num_neurons;
+    const unsigned int i = g.first_neuron + local;
+    const bool active = local < g.num_update;
+    const unsigned int slots = g.num_delay_slots;
+    const unsigned int wslot = ringSlot(k + 1, slots);
     const unsigned int ballot = __ballot_sync(0xFFFFFFFFu, spiked);
     const unsigned int lane = threadIdx.x & 31u;
     if(ballot) {
@@ -199,15 +277,52 @@ neuronUpdateKernel(const NeuronLaunch L)
     // spike times ride in the queue: carry the previous slot forward
     if(g.spike_times && active) {
         float *st = g.spike_times + ((unsigned long long)b * slots) * N;
-        st[(unsigned long long)wslot * N + i] = spiked ? t : st[(unsigned long long)ringSlot(k, slots) * N + i];
+        st[(unsigned long long)wslot * N + i] = spiked ? t : loadShared<COHERENT>(&st[(unsigned long long)ringSlot(k, slots) * N + i]);
     }
     // recording: bit i%32 of word i/32 (backendSIMT.cc:617-660)
     if(g.record_spk && L.num_recording_timesteps) {
         const unsigned int words = (N + 31u) / 32u;
-        unsigned int *rec = g.record_spk + ((timestep % L.num_recording_timesteps) * L.batch + b) * words;
-        // first_neuron is a multiple of 32, so a warp covers exactly one word
-        if(lane == 0 && local < ((g.num_update + 31u) & ~31u) && (i / 32u) < words) rec[i / 32u] = ballot;
+        // first_neuron is a multiple of 32, so a warp covers exactly one word;
+        // only the writing lane pays for the 64-bit modulo
+        if(lane == 0 && local < ((g.num_update + 31u) & ~31u) && (i / 32u) < words) {
+            unsigned int *rec = g.record_spk + ((timestep % L.num_recording_timesteps) * L.batch + b) * words;
+            rec[i / 32u] = ballot;
+        }
     }
+}
+
+// One neuron, one time step with its state in global memory: called by whole
+// warps (`local` may lie past the end of the group; such lanes only take part in
+// the ballot).  `k` is the number of completed steps, `timestep` the model step.
+template<bool COHERENT, int NPSM, int NCS>
+__device__ __forceinline__ void neuronStep(const NeuronLaunch &L, const b200_neuron_group &g, unsigned int b,
+                                           unsigned int local, unsigned int k, unsigned long long timestep)
+{
+    const unsigned int i = g.first_neuron + local;
+    const float t = B200_FMUL((float)timestep, L.dt);
+    bool spiked = false;
+    if(local < g.num_update) {
+        const unsigned long long bi = (unsigned long long)b * g.num_neurons + i;
+        NeuronRegs<NPSM, NCS> r;
+        float front[NPSM];
+        loadNeuron<COHERENT>(g, bi, r);
+        takeFronts<COHERENT, NPSM>(g, b, i, k, front);
+        spiked = neuronCompute(L, g, b, i, timestep, t, r, front);
+        storeNeuron(g, bi, r, false);
+    }
+    neuronEmit<COHERENT>(L, g, b, local, spiked, k, timestep, t);
+}
+
+template<int NPSM, int NCS>
+__global__ void __launch_bounds__(NEURON_BLOCK)
+neuronUpdateKernel(const NeuronLaunch L)
+{
+    const unsigned int gi = findGroup(L.block_start, L.num_groups, blockIdx.x);
+    const b200_neuron_group &g = L.groups[gi];
+    const unsigned int local = (blockIdx.x - __ldg(&L.block_start[gi])) * NEURON_BLOCK + threadIdx.x;
+    const unsigned int k = L.state->phase;
+    const unsigned long long timestep = L.state->timestep;
+    neuronStep<false, NPSM, NCS>(L, g, blockIdx.y, local, k, timestep);
 
     // ---- last block: queue update for the next step and counter advance -------
     __shared__ bool isLast;
@@ -227,7 +342,8 @@ neuronUpdateKernel(const NeuronLaunch L)
         if(threadIdx.x == 0) {
             L.state->ticket = 0;
             L.state->timestep = timestep + 1;
-            L.state->steps_done = k + 1;
+            L.state->steps_done = L.state->steps_done + 1;
+            L.state->phase = (k + 1 == L.state->ring_period) ? 0u : k + 1;
             __threadfence();
         }
     }

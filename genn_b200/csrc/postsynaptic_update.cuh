@@ -30,7 +30,7 @@ postsynapticUpdateKernel(const SynapseLaunch L)
     const b200_synapse_group &g = L.groups[gi];
     const unsigned int tile = blockIdx.x - __ldg(&L.block_start[gi]);
     const unsigned int b = blockIdx.z;
-    const unsigned long long k = L.state->steps_done;
+    const unsigned int k = L.state->phase;
     const unsigned int tslots = g.trg_delay_slots;
     const unsigned int rslot = ringSlot(k + tslots - g.back_prop_delay, tslots);
     const unsigned int count = g.trg_spk_cnt[b * tslots + rslot];

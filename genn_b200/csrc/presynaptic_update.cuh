@@ -74,17 +74,21 @@ template<> struct IndLoad<uint32_t>
 
 // One (spike, tile) work item of a SPARSE group with a non-learning weight
 // update model.
+// `quad` is this thread's position in the row counted in groups of four
+// synapses from the row's aligned start.
 template<typename IndT>
-__device__ __forceinline__ void sparseTile(const b200_synapse_group &g, unsigned int pre, unsigned int tile,
+__device__ __forceinline__ void sparseQuad(const b200_synapse_group &g, unsigned int pre, unsigned int quad,
                                            float *__restrict__ target, unsigned int denFront,
                                            StepState *state)
 {
-    const unsigned int len = __ldg(&g.row_length[pre]);
+    // The row length and the row data are fetched TOGETHER (one memory round
+    // trip, not two): the quad's address does not depend on the length, and a
+    // quad past the end of its row still lies inside the array (or its tail
+    // padding), so the loads are safe and simply discarded.
     const unsigned long long rowStart = (unsigned long long)pre * g.row_stride;
-    const unsigned long long rowEnd = rowStart + len;
-    const unsigned long long idx = (rowStart & ~3ull) + ((unsigned long long)tile * PRE_BLOCK + threadIdx.x) * PRE_VEC;
-    if(idx >= rowEnd) return;
-
+    const unsigned long long idx = (rowStart & ~3ull) + (unsigned long long)quad * PRE_VEC;
+    if(idx >= (unsigned long long)g.num_src * g.row_stride) return;
+    const unsigned int len = __ldg(&g.row_length[pre]);
     unsigned int post[4];
     IndLoad<IndT>::load4(g.ind, idx, post);
     float w[4];
@@ -98,6 +102,8 @@ __device__ __forceinline__ void sparseTile(const b200_synapse_group &g, unsigned
     const unsigned int D = g.max_den_delay;
     unsigned int dw = 0;
     if(D) dw = __ldg(reinterpret_cast<const unsigned int*>(g.d + idx));
+    const unsigned long long rowEnd = rowStart + len;
+    if(idx >= rowEnd) return;
     const unsigned int numTrg = g.num_trg;
 
 #pragma unroll
@@ -125,7 +131,7 @@ __device__ __forceinline__ void sparseTile(const b200_synapse_group &g, unsigned
 // per-batch weight (weightUpdateModels.h:354-361).  Scalar per-synapse path.
 template<typename IndT>
 __device__ __forceinline__ void sparseTileSTDP(const b200_synapse_group &g, unsigned int pre, unsigned int tile,
-                                               unsigned int b, float t, unsigned long long k)
+                                               unsigned int b, float t, unsigned int k)
 {
     const unsigned int len = __ldg(&g.row_length[pre]);
     const unsigned long long rowStart = (unsigned long long)pre * g.row_stride;
@@ -161,7 +167,7 @@ presynapticSparseKernel(const SynapseLaunch L)
     const b200_synapse_group &g = L.groups[gi];
     const unsigned int tile = blockIdx.x - __ldg(&L.block_start[gi]);
     const unsigned int b = blockIdx.z;
-    const unsigned long long k = L.state->steps_done;
+    const unsigned int k = L.state->phase;
     const unsigned int slots = g.src_delay_slots;
     const unsigned int rslot = ringSlot(k + slots - g.axonal_delay, slots);
     const unsigned int count = g.src_spk_cnt[b * slots + rslot];
@@ -185,9 +191,9 @@ presynapticSparseKernel(const SynapseLaunch L)
         }
         else {
             switch(g.ind_bytes) {
-            case 1: sparseTile<uint8_t>(g, pre, tile, target, denFront, L.state); break;
-            case 2: sparseTile<uint16_t>(g, pre, tile, target, denFront, L.state); break;
-            default: sparseTile<uint32_t>(g, pre, tile, target, denFront, L.state); break;
+            case 1: sparseQuad<uint8_t>(g, pre, tile * PRE_BLOCK + threadIdx.x, target, denFront, L.state); break;
+            case 2: sparseQuad<uint16_t>(g, pre, tile * PRE_BLOCK + threadIdx.x, target, denFront, L.state); break;
+            default: sparseQuad<uint32_t>(g, pre, tile * PRE_BLOCK + threadIdx.x, target, denFront, L.state); break;
             }
         }
         if(L.count_events && tile == 0 && threadIdx.x == 0) {
@@ -209,7 +215,7 @@ presynapticPostSpanKernel(const SynapseLaunch L)
     const b200_synapse_group &g = L.groups[gi];
     const unsigned int post = (blockIdx.x - __ldg(&L.block_start[gi])) * PRE_BLOCK + threadIdx.x;
     const unsigned int b = blockIdx.z;
-    const unsigned long long k = L.state->steps_done;
+    const unsigned int k = L.state->phase;
     const unsigned int slots = g.src_delay_slots;
     const unsigned int rslot = ringSlot(k + slots - g.axonal_delay, slots);
     const unsigned int count = g.src_spk_cnt[b * slots + rslot];

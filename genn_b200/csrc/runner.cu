@@ -21,6 +21,7 @@
 #include "presynaptic_update.cuh"
 #include "postsynaptic_update.cuh"
 #include "init.cuh"
+#include "fused_step.cuh"
 
 using namespace b200;
 
@@ -107,6 +108,24 @@ struct b200_runner
     DeviceTable<b200_neuron_group> neuronTable;
     DeviceTable<b200_synapse_group> sparseTable, postSpanTable, learnTable;
 
+    // persistent fused-step path (batch 1, SPARSE non-learning groups only)
+    bool fusedEligible = false;
+    bool useFused = true;
+    unsigned int fusedBlocksPerSM = 0;      // 0: as many as fit (occupancy query)
+    unsigned int fusedGrid = 0;
+    unsigned int *fusedSlotStart = nullptr;
+    FusedSource *fusedSources = nullptr;
+    uint2 *fusedItems = nullptr;
+    unsigned int fusedNumSources = 0;
+    unsigned int fusedNumItems = 0;
+    size_t fusedSmemBytes = 0;
+    bool fusedStage = false;
+    const void *fusedKernel = nullptr;
+    int fusedPerSM = 0;
+    unsigned long long *fusedBarrier = nullptr;
+    unsigned long long fusedLaunches = 0;
+    bool fusedProfile = false;
+
     // options
     unsigned int spikeLanes = 16;
     bool countEvents = false;
@@ -134,6 +153,35 @@ struct b200_runner
 
 namespace
 {
+// Kernel instances by (max fused postsynaptic models, max current sources) of
+// any neuron group: the smallest covering instance is used.
+struct NeuronShape { int npsm, ncs; };
+
+NeuronShape neuronShape(const b200_runner *r)
+{
+    unsigned int p = 0, c = 0;
+    for(const auto &g : r->neuronGroups) {
+        p = std::max(p, g.num_psm);
+        c = std::max(c, g.num_cs);
+    }
+    NeuronShape s;
+    s.npsm = (p <= 1) ? 1 : (p <= 2) ? 2 : B200_MAX_PSM;
+    s.ncs = (c == 0) ? 0 : (c == 1) ? 1 : B200_MAX_CS;
+    return s;
+}
+
+template<typename F>
+int withNeuronShape(const b200_runner *r, F f)
+{
+    const NeuronShape s = neuronShape(r);
+#define B200_SHAPE(P, C) if(s.npsm == P && s.ncs == C) return f(std::integral_constant<int, P>(), std::integral_constant<int, C>())
+    B200_SHAPE(1, 0); B200_SHAPE(1, 1); B200_SHAPE(1, B200_MAX_CS);
+    B200_SHAPE(2, 0); B200_SHAPE(2, 1); B200_SHAPE(2, B200_MAX_CS);
+    B200_SHAPE(B200_MAX_PSM, 0); B200_SHAPE(B200_MAX_PSM, 1); B200_SHAPE(B200_MAX_PSM, B200_MAX_CS);
+#undef B200_SHAPE
+    return fail(B200_ERR_INVALID, "no kernel instance for this neuron shape");
+}
+
 int prepare(b200_runner *r)
 {
     if(!r->dirty) return B200_OK;
@@ -170,7 +218,141 @@ int prepare(b200_runner *r)
     CUDA_TRY(r->sparseTable.upload(sparse, sparseStarts, r->stream));
     CUDA_TRY(r->postSpanTable.upload(postSpan, postSpanStarts, r->stream));
     CUDA_TRY(r->learnTable.upload(learn, learnStarts, r->stream));
+
+    // ---- tables of the persistent fused-step kernel --------------------------------
+    if(r->fusedSlotStart) { cudaFree(r->fusedSlotStart); r->fusedSlotStart = nullptr; }
+    if(r->fusedSources) { cudaFree(r->fusedSources); r->fusedSources = nullptr; }
+    if(r->fusedItems) { cudaFree(r->fusedItems); r->fusedItems = nullptr; }
+    r->fusedEligible = (r->batch == 1 && postSpan.empty() && learn.empty() && !r->neuronGroups.empty());
+    if(r->fusedEligible) {
+        std::vector<unsigned int> slotStart{0};
+        for(const auto &g : r->neuronGroups) slotStart.push_back(slotStart.back() + ((g.num_update + 31u) & ~31u));
+        std::vector<FusedSource> sources;
+        std::vector<std::vector<uint2>> perSource;
+        for(size_t gi = 0; gi < sparse.size(); gi++) {
+            const auto &g = sparse[gi];
+            size_t si = 0;
+            for(; si < sources.size(); si++) {
+                if(sources[si].spk_cnt == g.src_spk_cnt && sources[si].delay == g.axonal_delay) break;
+            }
+            if(si == sources.size()) {
+                FusedSource src{};
+                src.spk_cnt = g.src_spk_cnt;
+                src.spk = g.src_spk;
+                src.num_src = g.num_src;
+                src.slots = g.src_delay_slots;
+                src.delay = g.axonal_delay;
+                sources.push_back(src);
+                perSource.emplace_back();
+            }
+            const unsigned int chunks = (g.row_stride + 3 + FUSED_CHUNK - 1) / FUSED_CHUNK;
+            for(unsigned int c = 0; c < chunks; c++) perSource[si].push_back(make_uint2((unsigned int)gi, c));
+        }
+        std::vector<uint2> items;
+        for(size_t si = 0; si < sources.size(); si++) {
+            sources[si].item_begin = (unsigned int)items.size();
+            sources[si].item_count = (unsigned int)perSource[si].size();
+            items.insert(items.end(), perSource[si].begin(), perSource[si].end());
+        }
+        r->fusedNumSources = (unsigned int)sources.size();
+        r->fusedNumItems = (unsigned int)items.size();
+        r->fusedSmemBytes = align16(sizeof(b200_neuron_group) * r->neuronGroups.size()) +
+                            align16(sizeof(b200_synapse_group) * sparse.size()) +
+                            align16(sizeof(FusedSource) * sources.size()) + align16(sizeof(uint2) * items.size()) +
+                            align16(sizeof(unsigned int) * slotStart.size());
+        r->fusedStage = r->fusedSmemBytes <= 200 * 1024;
+        {
+            int e = withNeuronShape(r, [&](auto P, auto C) -> int {
+                auto kernel = fusedStepKernel<decltype(P)::value, decltype(C)::value>;
+                r->fusedKernel = (const void*)kernel;
+                if(r->fusedStage) {
+                    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->fusedSmemBytes));
+                }
+                int perSM = 0;
+                CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSM, kernel, FUSED_BLOCK,
+                                                                       r->fusedStage ? r->fusedSmemBytes : 0));
+                r->fusedPerSM = perSM;
+                return B200_OK;
+            });
+            if(e) return e;
+        }
+        CUDA_TRY(cudaMalloc(&r->fusedSlotStart, sizeof(unsigned int) * slotStart.size()));
+        CUDA_TRY(cudaMemcpy(r->fusedSlotStart, slotStart.data(), sizeof(unsigned int) * slotStart.size(), cudaMemcpyHostToDevice));
+        if(!sources.empty()) {
+            CUDA_TRY(cudaMalloc(&r->fusedSources, sizeof(FusedSource) * sources.size()));
+            CUDA_TRY(cudaMemcpy(r->fusedSources, sources.data(), sizeof(FusedSource) * sources.size(), cudaMemcpyHostToDevice));
+            CUDA_TRY(cudaMalloc(&r->fusedItems, sizeof(uint2) * items.size()));
+            CUDA_TRY(cudaMemcpy(r->fusedItems, items.data(), sizeof(uint2) * items.size(), cudaMemcpyHostToDevice));
+        }
+        if(!r->fusedBarrier) CUDA_TRY(cudaMalloc(&r->fusedBarrier, sizeof(unsigned long long)));
+        int perSM = r->fusedPerSM, sms = 0, coop = 0;
+        CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device));
+        CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, r->device));
+        if(perSM < 1 || !coop) {
+            r->fusedEligible = false;
+        }
+        else {
+            if(r->fusedBlocksPerSM) perSM = std::min<int>(perSM, (int)r->fusedBlocksPerSM);
+            r->fusedGrid = (unsigned int)(perSM * sms);
+        }
+    }
+    // ---- ring period: least common multiple of every ring size ----------------------
+    {
+        unsigned long long period = 1;
+        auto fold = [&period](unsigned int n) {
+            if(n < 2) return;
+            unsigned long long a = period, b = n;
+            while(b) { const unsigned long long t = a % b; a = b; b = t; }
+            period = period / a * n;
+        };
+        for(const auto &g : r->neuronGroups) {
+            fold(g.num_delay_slots);
+            for(unsigned int p = 0; p < g.num_psm; p++) fold(g.psm[p].max_den_delay);
+        }
+        for(const auto &g : r->synapseGroups) {
+            fold(g.src_delay_slots);
+            fold(g.trg_delay_slots);
+            fold(g.max_den_delay);
+        }
+        if(period > (1ull << 30)) return fail(B200_ERR_INVALID, "ring sizes have no common period below 2^30");
+        CUDA_TRY(cudaStreamSynchronize(r->stream));
+        const unsigned int ring[2] = {(unsigned int)(r->hostStepsDone % period), (unsigned int)period};
+        CUDA_TRY(cudaMemcpy(&r->state->phase, ring, sizeof(ring), cudaMemcpyHostToDevice));
+    }
     r->dirty = false;
+    return B200_OK;
+}
+
+int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long numRec)
+{
+    FusedLaunch L;
+    L.neuron.groups = r->neuronTable.d;
+    L.neuron.block_start = r->neuronTable.blockStart;
+    L.neuron.num_groups = r->neuronTable.num;
+    L.neuron.batch = 1;
+    L.neuron.dt = r->dt;
+    L.neuron.seed = r->seed;
+    L.neuron.num_recording_timesteps = numRec;
+    L.neuron.state = r->state;
+    L.neuron.count_events = r->countEvents ? 1u : 0u;
+    L.slot_start = r->fusedSlotStart;
+    L.sgroups = r->sparseTable.d;
+    L.sources = r->fusedSources;
+    L.items = r->fusedItems;
+    L.num_sources = r->fusedNumSources;
+    L.num_sgroups = r->sparseTable.num;
+    L.num_items = r->fusedNumItems;
+    L.stage_in_smem = r->fusedStage ? 1u : 0u;
+    L.count_events = r->countEvents ? 1u : 0u;
+    L.profile = r->fusedProfile ? 1u : 0u;
+    L.num_steps = numSteps;
+    L.barrier = r->fusedBarrier;
+    CUDA_TRY(cudaMemsetAsync(r->fusedBarrier, 0, sizeof(unsigned long long), r->stream));
+    void *args[] = {&L};
+    CUDA_TRY(cudaLaunchCooperativeKernel(r->fusedKernel, dim3(r->fusedGrid), dim3(FUSED_BLOCK), args,
+                                         r->fusedStage ? r->fusedSmemBytes : 0, r->stream));
+    r->launches++;
+    r->fusedLaunches++;
     return B200_OK;
 }
 
@@ -248,7 +430,11 @@ int enqueueNeurons(b200_runner *r, unsigned long long numRec, bool capturing)
     L.state = r->state;
     L.count_events = r->countEvents ? 1u : 0u;
     const dim3 grid(r->neuronTable.blocks, r->batch, 1);
-    neuronUpdateKernel<<<grid, NEURON_BLOCK, 0, r->stream>>>(L);
+    int e = withNeuronShape(r, [&](auto P, auto C) -> int {
+        neuronUpdateKernel<decltype(P)::value, decltype(C)::value><<<grid, NEURON_BLOCK, 0, r->stream>>>(L);
+        return B200_OK;
+    });
+    if(e) return e;
     r->launches++;
     CUDA_TRY(cudaPeekAtLastError());
     return B200_OK;
@@ -344,6 +530,10 @@ int b200_runner_destroy(b200_runner *r)
     r->sparseTable.release();
     r->postSpanTable.release();
     r->learnTable.release();
+    if(r->fusedSlotStart) cudaFree(r->fusedSlotStart);
+    if(r->fusedSources) cudaFree(r->fusedSources);
+    if(r->fusedItems) cudaFree(r->fusedItems);
+    if(r->fusedBarrier) cudaFree(r->fusedBarrier);
     for(auto &a : r->arrays) cudaFree(a.first);
     cudaFree(r->state);
     cudaEventDestroy(r->evA);
@@ -474,6 +664,9 @@ int b200_set_option(b200_runner *r, const char *name, double value)
     if(n == "spike_lanes") r->spikeLanes = std::max(1u, (unsigned int)value);
     else if(n == "count_events") r->countEvents = (value != 0.0);
     else if(n == "use_graph") r->useGraph = (value != 0.0);
+    else if(n == "use_fused") r->useFused = (value != 0.0);
+    else if(n == "fused_profile") r->fusedProfile = (value != 0.0);
+    else if(n == "fused_blocks_per_sm") { r->fusedBlocksPerSM = (unsigned int)value; r->dirty = true; }
     else if(n == "graph_steps") r->graphSteps = std::max(1u, (unsigned int)value);
     else return fail(B200_ERR_INVALID, "unknown option %s", name);
     r->dropGraph();
@@ -600,7 +793,15 @@ int b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_ti
     int e = prepare(r);
     if(e) return e;
     uint64_t left = num_steps;
-    if(r->useGraph && !r->timing && num_steps >= 2) {
+    if(r->useFused && r->fusedEligible && !r->timing) {
+        while(left) {
+            const uint64_t n = std::min<uint64_t>(left, 1ull << 20);
+            e = launchFused(r, n, num_recording_timesteps);
+            if(e) return e;
+            left -= n;
+        }
+    }
+    else if(r->useGraph && !r->timing && num_steps >= 2) {
         const unsigned int len = (unsigned int)std::min<uint64_t>(num_steps, r->graphSteps);
         if(!r->graphExec || r->graphLen > num_steps || r->graphNumRec != num_recording_timesteps ||
            (r->graphLen != len && r->graphLen != r->graphSteps)) {
@@ -645,10 +846,11 @@ int b200_synchronize(b200_runner *r)
     if(s.error) {
         const unsigned int err = s.error;
         cudaMemset(&r->state->error, 0, sizeof(unsigned int));
-        return fail(B200_ERR_DEVICE_CHECK, "device-side check failed (flags 0x%x:%s%s%s)", err,
+        return fail(B200_ERR_DEVICE_CHECK, "device-side check failed (flags 0x%x:%s%s%s%s)", err,
                     (err & ERR_SPIKE_OVERFLOW) ? " spike list overflow" : "",
                     (err & ERR_IND_RANGE) ? " index or row length out of range" : "",
-                    (err & ERR_DELAY_RANGE) ? " delay out of range" : "");
+                    (err & ERR_DELAY_RANGE) ? " delay out of range" : "",
+                    (err & ERR_BARRIER_TIMEOUT) ? " grid barrier timed out" : "");
     }
     return B200_OK;
 }
@@ -682,6 +884,10 @@ int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
     const std::string n(name);
     if(n == "synaptic_events") *value = s.synaptic_events;
     else if(n == "spikes") *value = s.spikes;
+    else if(n == "cycles_presynaptic") *value = s.phase_cycles[0];
+    else if(n == "cycles_barrier_a") *value = s.phase_cycles[1];
+    else if(n == "cycles_neuron") *value = s.phase_cycles[2];
+    else if(n == "cycles_barrier_b") *value = s.phase_cycles[3];
     else if(n == "timestep") *value = s.timestep;
     else if(n == "steps_done") *value = s.steps_done;
     else return fail(B200_ERR_INVALID, "unknown counter %s", name);

@@ -282,6 +282,7 @@ class Plan:
                 q.params[0] = _f32(c.derived["Init"])
                 q.params[1] = _f32(c.derived["ExpDecay"])
                 q.params[2] = _f32(c.derived["ExpMinusLambda"])
+                q.params[3] = _f32((c.params["rate"] / 1000.0) * net.dt)      # lambda
                 q.var0 = self._ptr(f"{c.name}.current")
             k += 1
         d.num_cs = k

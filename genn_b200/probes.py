@@ -50,6 +50,30 @@ def presyn(args):
     rt.close()
 
 
+def phases(args):
+    """Per-phase SM cycles of the persistent fused-step kernel at natural rates."""
+    from . import workloads
+    from .runtime import Runtime
+    model = workloads.potjans(neuron_scale=args.scale, seed=1234)
+    model.build()
+    rt = Runtime(model, None)
+    rt.set_option("count_events", args.count_events)
+    if args.blocks_per_sm:
+        rt.set_option("fused_blocks_per_sm", args.blocks_per_sm)
+    rt.step_time(args.warm)
+    rt.synchronize()
+    rt.set_option("fused_profile", 1)
+    names = ["cycles_presynaptic", "cycles_barrier_a", "cycles_neuron", "cycles_barrier_b"]
+    before = [rt.counter(n) for n in names]
+    ms = rt.step_time_timed(args.steps)
+    after = [rt.counter(n) for n in names]
+    out = {"probe": "phases", "scale": args.scale, "steps": args.steps, "us_per_step": ms * 1e3 / args.steps}
+    for n, a, b in zip(names, before, after):
+        out[n + "_per_step"] = (b - a) / args.steps
+    print(json.dumps(out))
+    rt.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -59,6 +83,13 @@ def main():
     p.add_argument("--reps", type=int, default=3)
     p.add_argument("--lanes", type=int, default=16)
     p.set_defaults(fn=presyn)
+    p = sub.add_parser("phases")
+    p.add_argument("--scale", type=float, default=1.0)
+    p.add_argument("--steps", type=int, default=2000)
+    p.add_argument("--warm", type=int, default=2000)
+    p.add_argument("--count-events", type=int, default=0)
+    p.add_argument("--blocks-per-sm", type=int, default=0)
+    p.set_defaults(fn=phases)
     args = ap.parse_args()
     args.fn(args)
 

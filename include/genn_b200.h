@@ -66,7 +66,7 @@ typedef enum b200_psm_model {
 /* currentSourceModels.h:60-129 */
 typedef enum b200_cs_model {
     B200_CS_DC = 0,                   /* params: amp */
-    B200_CS_POISSON_EXP = 1           /* params: Init, ExpDecay, ExpMinusLambda; var0: current */
+    B200_CS_POISSON_EXP = 1           /* params: Init, ExpDecay, ExpMinusLambda, lambda; var0: current */
 } b200_cs_model;
 
 /* weightUpdateModels.h:236-368 */
@@ -261,7 +261,8 @@ int  b200_get_steps_done(b200_runner *r, uint64_t *steps);
 /* Device-side counters: "synaptic_events" and "spikes" (when option count_events is on), "timestep", "steps_done". */
 int  b200_get_counter(b200_runner *r, const char *name, uint64_t *value);
 /* Tuning knobs (the counterpart of the backend Preferences, backends/cuda/backend.h:64-115):
- * "spike_lanes" (grid.y of the SPARSE kernel), "use_graph", "graph_steps", "count_events". */
+ * "spike_lanes" (grid.y of the SPARSE kernel), "use_graph", "graph_steps", "count_events",
+ * "use_fused" (persistent fused-step kernel), "fused_blocks_per_sm". */
 int  b200_set_option(b200_runner *r, const char *name, double value);
 
 /* ---- timers: neuronUpdateTime etc. (generateRunner.cc:159-222) ------------- */

@@ -79,8 +79,8 @@ B200_HD b200_philox_out b200_philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2
  * initialisation draws use {element[31:0], stream, element[63:32], 0x80000000 | block}. */
 typedef struct b200_rng {
     uint32_t c0, c1, c2, c3, k0, k1;
-    uint32_t have;             /* unread words left in buf */
-    b200_philox_out buf;
+    uint32_t have;             /* unread words left */
+    uint32_t w0, w1, w2, w3;   /* unread words, next one in w0 */
 } b200_rng;
 
 B200_HD b200_rng b200_rng_sim(uint64_t seed, uint32_t stream, uint32_t element, uint64_t timestep)
@@ -90,6 +90,7 @@ B200_HD b200_rng b200_rng_sim(uint64_t seed, uint32_t stream, uint32_t element, 
     r.c3 = ((uint32_t)(timestep >> 32) & 0x7FFFu) << 16;
     r.k0 = (uint32_t)seed; r.k1 = (uint32_t)(seed >> 32);
     r.have = 0;
+    r.w0 = r.w1 = r.w2 = r.w3 = 0;
     return r;
 }
 
@@ -100,18 +101,41 @@ B200_HD b200_rng b200_rng_init(uint64_t seed, uint32_t stream, uint64_t element)
     r.c3 = 0x80000000u;
     r.k0 = (uint32_t)seed; r.k1 = (uint32_t)(seed >> 32);
     r.have = 0;
+    r.w0 = r.w1 = r.w2 = r.w3 = 0;
     return r;
 }
 
 B200_HD uint32_t b200_rng_u32(b200_rng *r)
 {
     if(r->have == 0) {
-        r->buf = b200_philox4x32_10(r->c0, r->c1, r->c2, r->c3, r->k0, r->k1);
+        const b200_philox_out o = b200_philox4x32_10(r->c0, r->c1, r->c2, r->c3, r->k0, r->k1);
+        r->w0 = o.x[0]; r->w1 = o.x[1]; r->w2 = o.x[2]; r->w3 = o.x[3];
         r->c3 += 1u;
         r->have = 4;
     }
     r->have -= 1;
-    return r->buf.x[3 - r->have];
+    {
+        const uint32_t out = r->w0;     /* shift instead of indexing: stays in registers */
+        r->w0 = r->w1; r->w1 = r->w2; r->w2 = r->w3;
+        return out;
+    }
+}
+
+/* The four words one (stream, element) pair owns for time steps 4j..4j+3:
+ * step t uses word t & 3 of the block with counter
+ * {element, stream, (t>>2)[31:0], (t>>34)[14:0]<<16}.  A kernel that stays
+ * resident across steps computes the block once every four steps. */
+B200_HD b200_philox_out b200_rng_step_block(uint64_t seed, uint32_t stream, uint32_t element, uint64_t timestep)
+{
+    const uint64_t blk = timestep >> 2;
+    return b200_philox4x32_10(element, stream, (uint32_t)blk, ((uint32_t)(blk >> 32) & 0x7FFFu) << 16,
+                              (uint32_t)seed, (uint32_t)(seed >> 32));
+}
+
+B200_HD uint32_t b200_rng_step_word(const b200_philox_out *blk, uint64_t timestep)
+{
+    const uint32_t j = (uint32_t)timestep & 3u;
+    return (j == 0) ? blk->x[0] : (j == 1) ? blk->x[1] : (j == 2) ? blk->x[2] : blk->x[3];
 }
 
 /* Uniform in (0, 1): 23 random bits centred in their cell, exact in fp32. */
@@ -123,6 +147,22 @@ B200_HD float b200_u32_to_uniform(uint32_t x)
 B200_HD float b200_rng_uniform(b200_rng *r)
 {
     return b200_u32_to_uniform(b200_rng_u32(r));
+}
+
+/* Poisson variate by inversion of the CDF with ONE uniform: sequential search
+ * n = 0, 1, 2... until the cumulative probability passes u.  exp_minus_lambda
+ * and lambda are supplied pre-rounded to fp32.  Single IEEE operations only. */
+B200_HD uint32_t b200_poisson_inverse(float u, float exp_minus_lambda, float lambda)
+{
+    uint32_t n = 0;
+    float p = exp_minus_lambda;
+    float s = p;
+    while(u > s && n < 64u) {
+        n++;
+        p = B200_FDIV(B200_FMUL(p, lambda), (float)n);
+        s = B200_FADD(s, p);
+    }
+    return n;
 }
 
 /* Natural logarithm for x in (0, 1], built from single IEEE operations so

@@ -103,6 +103,15 @@ def izhikevich():
     return m, 400, 100
 
 
+def poisson_drive():
+    """Potjans architecture in miniature with its PoissonExp background drive.
+    The draws come from the library's own Philox streams, so this case has no
+    reference golden vector: it pins the CUDA kernels to the CPU checker
+    (identical streams) and both to the reference statistically."""
+    m = workloads.potjans(neuron_scale=0.01, seed=11, host_connectivity=True, background="poisson", record=True)
+    return m, 300, 100
+
+
 CASES = {"ff_sparse": ff_sparse, "ff_sparse_narrow": ff_sparse_narrow, "ff_bitmask": ff_bitmask,
          "ff_dense": ff_dense, "potjans_mini": potjans_mini, "cond_delay": cond_delay, "stdp": stdp,
          "izhikevich": izhikevich}

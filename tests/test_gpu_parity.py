@@ -39,23 +39,30 @@ class _Adapter:
         return self.rt.current_spikes(pop)
 
 
+@pytest.mark.parametrize("fused", [1, 0], ids=["persistent", "per-kernel"])
 @pytest.mark.parametrize("name", list(CASES))
-def test_step_by_step_matches_reference_golden(name):
+def test_step_by_step_matches_reference_golden(name, fused):
+    """Both time-step paths: the persistent fused-step kernel (where the model is
+    eligible for it) and one launch per kernel."""
     model, steps, dump_every = CASES[name]()
     net = resolve(model)
     rt = _runtime(net, steps)
+    rt.set_option("use_fused", fused)
     got = helpers.run_and_collect(_Adapter(rt), net, steps, dump_every)
     helpers.compare(got, helpers.load_golden(name), exact_state=False, rtol=RTOL, atol=ATOL)
     rt.close()
 
 
+@pytest.mark.parametrize("fused", [1, 0], ids=["persistent", "graph"])
 @pytest.mark.parametrize("name", ["ff_sparse", "potjans_mini", "cond_delay", "stdp"])
-def test_graph_replay_and_recording_match_reference_golden(name):
-    """All steps in one call (captured graph) with spike recording on: the
-    decoded recording equals the reference's spikes and the final state matches."""
+def test_many_steps_in_one_call_and_recording_match_reference_golden(name, fused):
+    """All steps in one call (one persistent launch, or replays of a captured
+    graph) with spike recording on: the decoded recording equals the
+    reference's spikes and the final state matches."""
     model, steps, dump_every = CASES[name]()
     net = resolve(model)
     rt = _runtime(net, steps)
+    rt.set_option("use_fused", fused)
     rt.set_option("graph_steps", 37)        # not a divisor of the step count: exercises the remainder path
     rt.step_time(steps)
     rt.synchronize()
@@ -96,6 +103,29 @@ def test_matches_cpu_checker_every_step(name):
             if p.kind == "LIF":
                 helpers.assert_close(rt.array(f"{p.name}.V")[0], orc.array(f"{p.name}.V")[0],
                                      f"step {s} V {p.name}", RTOL, ATOL)
+    rt.close()
+    orc.close()
+
+
+@pytest.mark.parametrize("fused", [1, 0], ids=["persistent", "per-kernel"])
+def test_poisson_background_matches_cpu_checker(fused):
+    """PoissonExp background: the CPU checker replays the library's Philox
+    streams, so spikes must be identical and state within tolerance."""
+    from oracle.oracle import OracleRunner
+    from tests.cases import poisson_drive
+    model, steps, dump_every = poisson_drive()
+    net, onet = resolve(model), resolve(poisson_drive()[0])
+    rt, orc = _runtime(net, steps), OracleRunner(onet, steps)
+    rt.set_option("use_fused", fused)
+    got = helpers.run_and_collect(_Adapter(rt), net, steps, dump_every)
+
+    class O:
+        step = staticmethod(lambda n: orc.step(n))
+        array = staticmethod(lambda name: orc.array(name))
+        current_spikes = staticmethod(lambda pop: orc.current_spikes(pop))
+    want = helpers.run_and_collect(O, onet, steps, dump_every)
+    assert sum(len(v) for k, v in want.items() if k.startswith("spikes_")) > 50
+    helpers.compare(got, want, exact_state=False, rtol=RTOL, atol=ATOL)
     rt.close()
     orc.close()
 

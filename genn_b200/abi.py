@@ -124,6 +124,7 @@ _PROTOTYPES = {
     "b200_get_counter": [C.c_void_p, C.c_char_p, C.POINTER(C.c_uint64)],
     "b200_set_option": [C.c_void_p, C.c_char_p, C.c_double],
     "b200_reset_timers": [C.c_void_p],
+    "b200_get_cta_cycles": [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(C.c_uint32)],
 }
 
 _lib = None

@@ -68,7 +68,8 @@ struct FusedLaunch
     unsigned int num_items;
     unsigned int stage_in_smem;          // tables fit the dynamic shared memory the host reserved
     unsigned int count_events;
-    unsigned int profile;                // accumulate phase_cycles (CTA 0, thread 0)
+    unsigned int profile;                // accumulate phase cycles (thread 0 of every CTA)
+    unsigned long long *cta_cycles;      // [gridDim][4] or NULL
     unsigned long long num_steps;
     unsigned long long *barrier;         // monotonic arrival counter
 };
@@ -80,15 +81,23 @@ __device__ __forceinline__ unsigned long long loadAcquire(const unsigned long lo
     return v;
 }
 
-// Grid-wide barrier with a bounded wait.  Returns false if it timed out (or any
-// CTA reported an error), in which case every CTA leaves the kernel.
-__device__ __forceinline__ bool gridBarrier(const FusedLaunch &L, unsigned long long &epoch, bool *ok)
+// Grid-wide barrier in two halves so work that does not depend on other CTAs can
+// run between them.  gridArrive publishes this CTA's writes and counts it in;
+// gridWait blocks (bounded) until every CTA has arrived and returns false if it
+// timed out, in which case every CTA leaves the kernel.
+__device__ __forceinline__ void gridArrive(const FusedLaunch &L, unsigned long long &epoch)
 {
     __syncthreads();
     if(threadIdx.x == 0) {
         // release + arrive in one fire-and-forget reduction: nothing waits for its return
         asm volatile("red.release.gpu.global.add.u64 [%0], %1;" :: "l"(L.barrier), "l"(1ull) : "memory");
         epoch += gridDim.x;
+    }
+}
+
+__device__ __forceinline__ bool gridWait(const FusedLaunch &L, const unsigned long long &epoch, bool *ok)
+{
+    if(threadIdx.x == 0) {
         unsigned long long polls = 0;
         bool good = true;
         while(loadAcquire(L.barrier) < epoch) {
@@ -192,7 +201,7 @@ fusedStepKernel(FusedLaunch L)
         if(myActive) loadNeuron<true>(g, myIndex, regs);
     }
 
-    const bool prof = L.profile && gthread == 0;
+    const bool prof = L.profile && threadIdx.x == 0;
     long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
     for(unsigned long long step = 0; step < L.num_steps; step++) {
         if(prof) c0 = clock64();
@@ -211,16 +220,22 @@ fusedStepKernel(FusedLaunch L)
                     const FusedSource &src = L.sources[si];
                     rslot = ringSlot(k + src.slots - src.delay, src.slots);
                     const unsigned int *list = src.spk + (unsigned long long)rslot * src.num_src;
+                    // all loads into registers first: a shared-memory store between two
+                    // loads through generic pointers would serialise them
+                    unsigned int ids[FUSED_PREFETCH_IDS];
                     cnt = __ldcg(&src.spk_cnt[rslot]);
                     #pragma unroll
                     for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
-                        headIds[lane][j] = (j < src.num_src) ? __ldcg(&list[j]) : 0u;
+                        ids[j] = (j < src.num_src) ? __ldcg(&list[j]) : 0u;
                     }
+                    #pragma unroll
+                    for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) headIds[lane][j] = ids[j];
                 }
                 headCnt[lane] = cnt;
                 headSlot[lane] = rslot;
             }
             __syncthreads();
+            if(prof && L.cta_cycles) L.cta_cycles[4ull * gridDim.x + blockIdx.x] += (unsigned long long)(clock64() - c0);
             const unsigned int cnt = headCnt[lane];
             const unsigned int per = (base + lane < L.num_sources) ? L.sources[base + lane].item_count : 0u;
             unsigned int incl = cnt * per;
@@ -261,7 +276,13 @@ fusedStepKernel(FusedLaunch L)
             if(base + 32u < L.num_sources) __syncthreads();     // the header arrays are reused by the next pass
         }
         if(prof) c1 = clock64();
-        if(!gridBarrier(L, epoch, &barrierOk)) return;
+        gridArrive(L, epoch);
+        // in the shadow of the barrier: this step's random draws
+        unsigned int csCount[NCS > 0 ? NCS : 1] = {0};
+        if(resident && mine && myActive) {
+            drawCurrentSources<NCS>(L.neuron, L.neuron.groups[myGroup], 0u, (unsigned int)myIndex, t0 + step, csCount);
+        }
+        if(!gridWait(L, epoch, &barrierOk)) return;
         if(prof) c2 = clock64();
 
         // ---------------- phase B: neuron update -----------------------------------
@@ -277,7 +298,7 @@ fusedStepKernel(FusedLaunch L)
                         if(p < g.num_psm && !g.psm[p].max_den_delay) regs.lin[p] = __ldcg(&g.psm[p].out_post[myIndex]);
                     }
                     takeFronts<true, NPSM>(g, 0u, (unsigned int)myIndex, k, front);
-                    spiked = neuronCompute(L.neuron, g, 0u, (unsigned int)myIndex, t0 + step, t, regs, front);
+                    spiked = neuronCompute(L.neuron, g, 0u, (unsigned int)myIndex, t0 + step, t, regs, front, csCount);
                     #pragma unroll
                     for(unsigned int p = 0; p < NPSM; p++) {
                         if(p < g.num_psm && !g.psm[p].max_den_delay) g.psm[p].out_post[myIndex] = regs.lin[p];
@@ -299,14 +320,24 @@ fusedStepKernel(FusedLaunch L)
             o.spk_cnt[ringSlot(k + 2, o.num_delay_slots)] = 0;
         }
         if(prof) c3 = clock64();
-        if(!gridBarrier(L, epoch, &barrierOk)) return;
+        gridArrive(L, epoch);
+        if(!gridWait(L, epoch, &barrierOk)) return;
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {
             const long long c4 = clock64();
-            state->phase_cycles[0] += (unsigned long long)(c1 - c0);
-            state->phase_cycles[1] += (unsigned long long)(c2 - c1);
-            state->phase_cycles[2] += (unsigned long long)(c3 - c2);
-            state->phase_cycles[3] += (unsigned long long)(c4 - c3);
+            if(blockIdx.x == 0) {
+                state->phase_cycles[0] += (unsigned long long)(c1 - c0);
+                state->phase_cycles[1] += (unsigned long long)(c2 - c1);
+                state->phase_cycles[2] += (unsigned long long)(c3 - c2);
+                state->phase_cycles[3] += (unsigned long long)(c4 - c3);
+            }
+            if(L.cta_cycles) {
+                unsigned long long *mine4 = L.cta_cycles + 4ull * blockIdx.x;
+                mine4[0] += (unsigned long long)(c1 - c0);
+                mine4[1] += (unsigned long long)(c2 - c1);
+                mine4[2] += (unsigned long long)(c3 - c2);
+                mine4[3] += (unsigned long long)(c4 - c3);
+            }
         }
     }
     if(mine && myActive) storeNeuron(L.neuron.groups[myGroup], myIndex, regs, true);

@@ -110,25 +110,58 @@ template<bool COHERENT, int NPSM>
 __device__ __forceinline__ void takeFronts(const b200_neuron_group &g, unsigned int b, unsigned int i,
                                            unsigned int k, float (&front)[NPSM])
 {
+    // every load before any store: the pointers are generic, so a store between
+    // two loads would force the second load to wait for the first
+    float *slot[NPSM];
     #pragma unroll
     for(unsigned int p = 0; p < NPSM; p++) {
         front[p] = 0.0f;
+        slot[p] = nullptr;
         if(p < g.num_psm) {
             const unsigned int D = g.psm[p].max_den_delay;
             if(D) {
-                float *f = &g.psm[p].den_delay[((unsigned long long)b * D + ringSlot(k + 1, D)) * g.num_neurons + i];
-                front[p] = loadShared<COHERENT>(f);
-                *f = 0.0f;
+                slot[p] = &g.psm[p].den_delay[((unsigned long long)b * D + ringSlot(k + 1, D)) * g.num_neurons + i];
+                front[p] = loadShared<COHERENT>(slot[p]);
             }
         }
+    }
+    #pragma unroll
+    for(unsigned int p = 0; p < NPSM; p++) {
+        if(slot[p]) *slot[p] = 0.0f;
     }
 }
 
 // One neuron, one time step, entirely in registers.  Returns whether it spiked.
+// Random draws of the current sources for one neuron and step: the number of
+// Poisson events of each PoissonExp source.  They depend on nothing the
+// presynaptic phase produces, so the persistent kernel computes them while the
+// barrier after that phase is in flight.
+// The model draws its Poisson count by multiplying uniforms until the product
+// falls below exp(-lambda) (currentSourceModels.h:111-118); here the same count
+// comes from inverting the Poisson CDF with one uniform, a quarter of a Philox
+// block per step instead of one or two whole blocks.
+template<int NCS>
+__device__ __forceinline__ void drawCurrentSources(const NeuronLaunch &L, const b200_neuron_group &g, unsigned int b,
+                                                   unsigned int i, unsigned long long timestep,
+                                                   unsigned int (&count)[NCS > 0 ? NCS : 1])
+{
+    #pragma unroll
+    for(unsigned int c = 0; c < NCS; c++) {
+        count[c] = 0;
+        if(c < g.num_cs && g.cs[c].model == B200_CS_POISSON_EXP) {
+            const b200_current_source &cs = g.cs[c];
+            const b200_philox_out blk = b200_rng_step_block(L.seed, cs.rng_stream, b * g.num_neurons + i, timestep);
+            const float u = b200_u32_to_uniform(b200_rng_step_word(&blk, timestep));
+            count[c] = b200_poisson_inverse(u, cs.params[2], cs.params[3]);
+        }
+    }
+}
+
 template<int NPSM, int NCS>
 __device__ __forceinline__ bool neuronCompute(const NeuronLaunch &L, const b200_neuron_group &g, unsigned int b,
                                               unsigned int i, unsigned long long timestep, float t,
-                                              NeuronRegs<NPSM, NCS> &r, const float (&front)[NPSM])
+                                              NeuronRegs<NPSM, NCS> &r, const float (&front)[NPSM],
+                                              const unsigned int (&csCount)[NCS > 0 ? NCS : 1])
 {
     const unsigned int N = g.num_neurons;
     const unsigned int model = g.model;
@@ -167,16 +200,8 @@ __device__ __forceinline__ bool neuronCompute(const NeuronLaunch &L, const b200_
                 Isyn = B200_FADD(Isyn, cs.params[0]);
             }
             else {
-                // The model draws its Poisson spike count by multiplying uniforms
-                // until the product falls below exp(-lambda)
-                // (currentSourceModels.h:111-118); here the same count comes from
-                // inverting the Poisson CDF with one uniform, a quarter of a Philox
-                // block per step instead of one or two whole blocks.
                 float current = r.cs[c];
-                const b200_philox_out blk = b200_rng_step_block(L.seed, cs.rng_stream, b * N + i, timestep);
-                const float u = b200_u32_to_uniform(b200_rng_step_word(&blk, timestep));
-                const unsigned int numSpikes = b200_poisson_inverse(u, cs.params[2], cs.params[3]);
-                current = B200_FADD(current, B200_FMUL(cs.params[0], (float)numSpikes));
+                current = B200_FADD(current, B200_FMUL(cs.params[0], (float)csCount[c]));
                 Isyn = B200_FADD(Isyn, current);
                 r.cs[c] = B200_FMUL(current, cs.params[1]);
             }
@@ -305,9 +330,11 @@ __device__ __forceinline__ void neuronStep(const NeuronLaunch &L, const b200_neu
         const unsigned long long bi = (unsigned long long)b * g.num_neurons + i;
         NeuronRegs<NPSM, NCS> r;
         float front[NPSM];
+        unsigned int csCount[NCS > 0 ? NCS : 1];
         loadNeuron<COHERENT>(g, bi, r);
         takeFronts<COHERENT, NPSM>(g, b, i, k, front);
-        spiked = neuronCompute(L, g, b, i, timestep, t, r, front);
+        drawCurrentSources<NCS>(L, g, b, i, timestep, csCount);
+        spiked = neuronCompute(L, g, b, i, timestep, t, r, front, csCount);
         storeNeuron(g, bi, r, false);
     }
     neuronEmit<COHERENT>(L, g, b, local, spiked, k, timestep, t);

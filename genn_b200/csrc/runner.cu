@@ -125,6 +125,7 @@ struct b200_runner
     unsigned long long *fusedBarrier = nullptr;
     unsigned long long fusedLaunches = 0;
     bool fusedProfile = false;
+    unsigned long long *fusedCtaCycles = nullptr;
 
     // options
     unsigned int spikeLanes = 16;
@@ -345,6 +346,11 @@ int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long 
     L.stage_in_smem = r->fusedStage ? 1u : 0u;
     L.count_events = r->countEvents ? 1u : 0u;
     L.profile = r->fusedProfile ? 1u : 0u;
+    if(r->fusedProfile && !r->fusedCtaCycles) {
+        CUDA_TRY(cudaMalloc(&r->fusedCtaCycles, sizeof(unsigned long long) * 5 * r->fusedGrid));
+        CUDA_TRY(cudaMemsetAsync(r->fusedCtaCycles, 0, sizeof(unsigned long long) * 5 * r->fusedGrid, r->stream));
+    }
+    L.cta_cycles = r->fusedProfile ? r->fusedCtaCycles : nullptr;
     L.num_steps = numSteps;
     L.barrier = r->fusedBarrier;
     CUDA_TRY(cudaMemsetAsync(r->fusedBarrier, 0, sizeof(unsigned long long), r->stream));
@@ -534,6 +540,7 @@ int b200_runner_destroy(b200_runner *r)
     if(r->fusedSources) cudaFree(r->fusedSources);
     if(r->fusedItems) cudaFree(r->fusedItems);
     if(r->fusedBarrier) cudaFree(r->fusedBarrier);
+    if(r->fusedCtaCycles) cudaFree(r->fusedCtaCycles);
     for(auto &a : r->arrays) cudaFree(a.first);
     cudaFree(r->state);
     cudaEventDestroy(r->evA);
@@ -891,6 +898,22 @@ int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
     else if(n == "timestep") *value = s.timestep;
     else if(n == "steps_done") *value = s.steps_done;
     else return fail(B200_ERR_INVALID, "unknown counter %s", name);
+    return B200_OK;
+}
+
+/* Per-CTA phase cycles of the persistent kernel (option "fused_profile"): out[cta*4 + phase]. */
+int b200_get_cta_cycles(b200_runner *r, uint64_t *out, uint32_t max_ctas, uint32_t *num_ctas)
+{
+    *num_ctas = 0;
+    if(!r->fusedCtaCycles) return B200_OK;
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    const uint32_t n = std::min<uint32_t>(max_ctas, r->fusedGrid);
+    CUDA_TRY(cudaMemcpy(out, r->fusedCtaCycles, sizeof(uint64_t) * 4 * n, cudaMemcpyDeviceToHost));
+    if(max_ctas >= 2 * r->fusedGrid) {
+        // trailing block: cycles from step start to the spike-header barrier
+        CUDA_TRY(cudaMemcpy(out + 4ull * n, r->fusedCtaCycles + 4ull * r->fusedGrid, sizeof(uint64_t) * n, cudaMemcpyDeviceToHost));
+    }
+    *num_ctas = n;
     return B200_OK;
 }
 

@@ -70,6 +70,13 @@ def phases(args):
     out = {"probe": "phases", "scale": args.scale, "steps": args.steps, "us_per_step": ms * 1e3 / args.steps}
     for n, a, b in zip(names, before, after):
         out[n + "_per_step"] = (b - a) / args.steps
+    cta = rt.cta_cycles().astype(np.float64) / args.steps
+    if len(cta):
+        out["cta_presyn_header_median"] = float(np.median(rt.header_cycles.astype(np.float64) / args.steps))
+        for j, n in enumerate(["presynaptic", "barrier_a", "neuron", "barrier_b"]):
+            col = cta[:, j]
+            out["cta_" + n] = {"min": col.min(), "median": float(np.median(col)), "max": col.max(),
+                               "argmax": int(col.argmax())}
     print(json.dumps(out))
     rt.close()
 

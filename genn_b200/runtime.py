@@ -241,6 +241,14 @@ class Runtime:
         check(self.lib.b200_get_kernel_launches(self.handle, C.byref(v)))
         return int(v.value)
 
+    def cta_cycles(self) -> np.ndarray:
+        """[num_ctas, 4] cycles per phase of the persistent kernel (option fused_profile)."""
+        out = np.zeros((1024, 4), dtype=np.uint64)
+        n = C.c_uint32()
+        check(self.lib.b200_get_cta_cycles(self.handle, out.ctypes.data, 1024, C.byref(n)))
+        self.header_cycles = out.reshape(-1)[4 * n.value:5 * n.value].copy()
+        return out[:n.value]
+
     def enable_timing(self, on: bool):
         check(self.lib.b200_enable_timing(self.handle, int(on)))
 

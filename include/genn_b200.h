@@ -270,6 +270,9 @@ int  b200_enable_timing(b200_runner *r, int enabled);
 int  b200_get_timer(b200_runner *r, const char *name, double *seconds);
 int  b200_reset_timers(b200_runner *r);
 int  b200_get_kernel_launches(b200_runner *r, uint64_t *launches);
+/* SM cycles thread 0 of every CTA of the persistent kernel spent in {presynaptic work, barrier,
+ * neuron work, barrier}, accumulated while option "fused_profile" is on: out[cta*4 + phase]. */
+int  b200_get_cta_cycles(b200_runner *r, uint64_t *out, uint32_t max_ctas, uint32_t *num_ctas);
 
 #ifdef __cplusplus
 }

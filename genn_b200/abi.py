@@ -125,6 +125,8 @@ _PROTOTYPES = {
     "b200_set_option": [C.c_void_p, C.c_char_p, C.c_double],
     "b200_reset_timers": [C.c_void_p],
     "b200_get_cta_cycles": [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(C.c_uint32)],
+    "b200_update_neurons_noalloc": [C.c_int, C.c_void_p, C.POINTER(NeuronGroupDesc), C.c_uint32, C.c_uint32,
+                                    C.c_double, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64],
 }
 
 _lib = None
@@ -150,6 +152,8 @@ def load_library():
         fn.restype = C.c_int
     lib.b200_last_error.argtypes = []
     lib.b200_last_error.restype = C.c_char_p
+    lib.b200_noalloc_last_error.argtypes = []
+    lib.b200_noalloc_last_error.restype = C.c_char_p
     _lib = lib
     return lib
 
@@ -161,4 +165,4 @@ def check(status: int):
 
 
 def exported_symbols():
-    return list(_PROTOTYPES.keys()) + ["b200_last_error"]
+    return list(_PROTOTYPES.keys()) + ["b200_last_error", "b200_noalloc_last_error"]

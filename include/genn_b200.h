@@ -274,6 +274,33 @@ int  b200_get_kernel_launches(b200_runner *r, uint64_t *launches);
  * neuron work, barrier}, accumulated while option "fused_profile" is on: out[cta*4 + phase]. */
 int  b200_get_cta_cycles(b200_runner *r, uint64_t *out, uint32_t max_ctas, uint32_t *num_ctas);
 
+/* ---- neuron update without any allocation ------------------------------------
+ * No counterpart in the reference, whose runtime allocates every array and every
+ * merged-group table itself (runtime.cc:147-662).
+ *
+ * Performs what b200_push_neuron_update_group + b200_update_neurons perform for
+ * one time step, for callers that may not allocate while they run: hard
+ * real-time loops (an allocator call has unbounded latency and can synchronise
+ * the device) and plugins inside a process with a fixed memory budget.  The
+ * descriptor tables, block lookup table and step counters
+ * that the regular path keeps in cudaMalloc'ed memory live in a fixed array
+ * inside the library image instead (B200_NOALLOC_SCRATCH_BYTES on every GPU that
+ * loads the library, for the life of the process), which caps the call at
+ * B200_NOALLOC_MAX_GROUPS neuron groups; more is rejected with B200_ERR_INVALID.
+ * `groups` is a HOST array of descriptors holding the caller's device pointers;
+ * `stream` is a cudaStream_t (NULL for the default stream); `timestep` and
+ * `steps_done` are the values the regular path would hold on the device.
+ * The first call on a device resolves the array's address and should be made
+ * before any stream capture begins.  Calls on one device share the array: calls
+ * whose GPU work may overlap must be ordered by the caller.  No host or device
+ * memory is allocated or freed.  Errors: b200_noalloc_last_error(). */
+#define B200_NOALLOC_MAX_GROUPS     64
+#define B200_NOALLOC_SCRATCH_BYTES  40960
+int  b200_update_neurons_noalloc(int device, void *stream, const b200_neuron_group *groups, uint32_t num_groups,
+                                 uint32_t batch_size, double dt, uint64_t seed, uint64_t timestep,
+                                 uint64_t steps_done, uint64_t num_recording_timesteps);
+const char *b200_noalloc_last_error(void);
+
 #ifdef __cplusplus
 }
 #endif

@@ -59,8 +59,55 @@ def lib():
         l.oracle_build_remap.argtypes = [C.c_void_p, C.c_void_p, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
                                          C.c_uint32, C.c_void_p, C.c_void_p]
         l.oracle_build_remap.restype = None
+        l.oracle_init_var.argtypes = [C.c_void_p, C.c_uint32, C.c_uint64, C.c_uint32, C.POINTER(C.c_float),
+                                      C.c_uint64, C.c_uint32]
+        l.oracle_init_var.restype = None
+        l.oracle_init_sparse_vars.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_void_p, C.c_uint32, C.c_uint32,
+                                              C.POINTER(C.c_float), C.c_uint64, C.c_uint32]
+        l.oracle_init_sparse_vars.restype = None
+        l.oracle_init_sparse_connectivity.argtypes = [C.c_uint32, C.POINTER(C.c_float), C.c_uint32, C.c_uint32,
+                                                      C.c_uint32, C.c_uint32, C.c_uint32, C.c_void_p, C.c_void_p,
+                                                      C.c_uint64, C.c_uint32]
+        l.oracle_init_sparse_connectivity.restype = C.c_int
+        l.oracle_init_fixed_number_pre.argtypes = [C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint32,
+                                                   C.c_uint32, C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32]
+        l.oracle_init_fixed_number_pre.restype = C.c_int
         _lib = l
     return _lib
+
+
+def _params(values):
+    return (C.c_float * 4)(*(list(values) + [0.0] * 4)[:4])
+
+
+def init_var(count: int, dtype, snippet: int, params, seed: int, stream: int) -> np.ndarray:
+    out = np.zeros(count, dtype=dtype)
+    lib().oracle_init_var(out.ctypes.data, out.dtype.itemsize, count, snippet, _params(params), seed, stream)
+    return out
+
+
+def init_sparse_vars(row_length: np.ndarray, row_stride: int, dtype, snippet: int, params, seed: int,
+                     stream: int) -> np.ndarray:
+    rl = np.ascontiguousarray(row_length, dtype=np.uint32)
+    out = np.zeros(len(rl) * row_stride, dtype=dtype)
+    lib().oracle_init_sparse_vars(rl.ctypes.data, len(rl), row_stride, out.ctypes.data, out.dtype.itemsize, snippet,
+                                  _params(params), seed, stream)
+    return out
+
+
+def init_sparse_connectivity(snippet: int, params, num_src: int, row_stride: int, ind_dtype, trg_begin: int,
+                             trg_end: int, seed: int, stream: int, row_length: Optional[np.ndarray] = None):
+    """Returns (row_length, ind, overflow)."""
+    rl = (np.zeros(num_src, dtype=np.uint32) if row_length is None
+          else np.ascontiguousarray(row_length, dtype=np.uint32).copy())
+    ind = np.zeros(num_src * row_stride, dtype=ind_dtype)
+    if snippet == abi.CONNECT_FIXED_NUMBER_PRE:
+        ov = lib().oracle_init_fixed_number_pre(int(params[0]), num_src, row_stride, ind.dtype.itemsize, trg_begin,
+                                                trg_end, rl.ctypes.data, ind.ctypes.data, seed, stream)
+    else:
+        ov = lib().oracle_init_sparse_connectivity(snippet, _params(params), num_src, row_stride, ind.dtype.itemsize,
+                                                   trg_begin, trg_end, rl.ctypes.data, ind.ctypes.data, seed, stream)
+    return rl, ind, bool(ov)
 
 
 class _HostHandle:

@@ -125,6 +125,7 @@ _PROTOTYPES = {
     "b200_set_option": [C.c_void_p, C.c_char_p, C.c_double],
     "b200_reset_timers": [C.c_void_p],
     "b200_get_cta_cycles": [C.c_void_p, C.c_void_p, C.c_uint32, C.POINTER(C.c_uint32)],
+    "b200_get_step_path": [C.c_void_p, C.POINTER(C.c_int), C.c_char_p, C.c_size_t],
     "b200_update_neurons_noalloc": [C.c_int, C.c_void_p, C.POINTER(NeuronGroupDesc), C.c_uint32, C.c_uint32,
                                     C.c_double, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64],
 }

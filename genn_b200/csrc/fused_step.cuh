@@ -85,24 +85,25 @@ __device__ __forceinline__ unsigned long long loadAcquire(const unsigned long lo
 // run between them.  gridArrive publishes this CTA's writes and counts it in;
 // gridWait blocks (bounded) until every CTA has arrived and returns false if it
 // timed out, in which case every CTA leaves the kernel.
-__device__ __forceinline__ void gridArrive(const FusedLaunch &L, unsigned long long &epoch)
+__device__ __forceinline__ void gridArrive(unsigned long long *barrier, unsigned long long &epoch)
 {
     __syncthreads();
     if(threadIdx.x == 0) {
         // release + arrive in one fire-and-forget reduction: nothing waits for its return
-        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" :: "l"(L.barrier), "l"(1ull) : "memory");
+        asm volatile("red.release.gpu.global.add.u64 [%0], %1;" :: "l"(barrier), "l"(1ull) : "memory");
         epoch += gridDim.x;
     }
 }
 
-__device__ __forceinline__ bool gridWait(const FusedLaunch &L, const unsigned long long &epoch, bool *ok)
+__device__ __forceinline__ bool gridWait(const unsigned long long *barrier, const unsigned long long &epoch, bool *ok,
+                                         StepState *state)
 {
     if(threadIdx.x == 0) {
         unsigned long long polls = 0;
         bool good = true;
-        while(loadAcquire(L.barrier) < epoch) {
+        while(loadAcquire(barrier) < epoch) {
             if(++polls > BARRIER_SPIN_LIMIT) {
-                atomicOr(&L.neuron.state->error, ERR_BARRIER_TIMEOUT);
+                atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
                 good = false;
                 break;
             }
@@ -276,13 +277,13 @@ fusedStepKernel(FusedLaunch L)
             if(base + 32u < L.num_sources) __syncthreads();     // the header arrays are reused by the next pass
         }
         if(prof) c1 = clock64();
-        gridArrive(L, epoch);
+        gridArrive(L.barrier, epoch);
         // in the shadow of the barrier: this step's random draws
         unsigned int csCount[NCS > 0 ? NCS : 1] = {0};
         if(resident && mine && myActive) {
             drawCurrentSources<NCS>(L.neuron, L.neuron.groups[myGroup], 0u, (unsigned int)myIndex, t0 + step, csCount);
         }
-        if(!gridWait(L, epoch, &barrierOk)) return;
+        if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
         if(prof) c2 = clock64();
 
         // ---------------- phase B: neuron update -----------------------------------
@@ -320,8 +321,8 @@ fusedStepKernel(FusedLaunch L)
             o.spk_cnt[ringSlot(k + 2, o.num_delay_slots)] = 0;
         }
         if(prof) c3 = clock64();
-        gridArrive(L, epoch);
-        if(!gridWait(L, epoch, &barrierOk)) return;
+        gridArrive(L.barrier, epoch);
+        if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {
             const long long c4 = clock64();

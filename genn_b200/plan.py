@@ -117,7 +117,7 @@ class Plan:
 
         # neuron-side arrays
         for p in net.pops:
-            slots = p.num_delay_slots + 1     # one spare slot: see include/genn_b200.h
+            slots = p.num_delay_slots + 2     # two spare slots: see include/genn_b200.h
             p.runtime_slots = slots
             for v, arr in p.vars.items():
                 dtype = np.uint32 if p.kind == "SpikeSourceArray" else np.float32

@@ -60,6 +60,8 @@ def phases(args):
     rt.set_option("count_events", args.count_events)
     if args.blocks_per_sm:
         rt.set_option("fused_blocks_per_sm", args.blocks_per_sm)
+    rt.set_option("use_owner", args.owner)
+    rt.set_option("owner_item_lanes", args.item_lanes)
     rt.step_time(args.warm)
     rt.synchronize()
     rt.set_option("fused_profile", 1)
@@ -67,7 +69,8 @@ def phases(args):
     before = [rt.counter(n) for n in names]
     ms = rt.step_time_timed(args.steps)
     after = [rt.counter(n) for n in names]
-    out = {"probe": "phases", "scale": args.scale, "steps": args.steps, "us_per_step": ms * 1e3 / args.steps}
+    out = {"probe": "phases", "scale": args.scale, "steps": args.steps, "us_per_step": ms * 1e3 / args.steps,
+           "step_path": rt.step_path()}
     for n, a, b in zip(names, before, after):
         out[n + "_per_step"] = (b - a) / args.steps
     cta = rt.cta_cycles().astype(np.float64) / args.steps
@@ -77,6 +80,8 @@ def phases(args):
             col = cta[:, j]
             out["cta_" + n] = {"min": col.min(), "median": float(np.median(col)), "max": col.max(),
                                "argmax": int(col.argmax())}
+    if args.dump and len(cta):
+        out["per_cta"] = [[round(float(x)) for x in row] for row in cta]
     print(json.dumps(out))
     rt.close()
 
@@ -96,6 +101,9 @@ def main():
     p.add_argument("--warm", type=int, default=2000)
     p.add_argument("--count-events", type=int, default=0)
     p.add_argument("--blocks-per-sm", type=int, default=0)
+    p.add_argument("--owner", type=int, default=0)
+    p.add_argument("--item-lanes", type=int, default=32)
+    p.add_argument("--dump", action="store_true", help="print the per-CTA phase cycles")
     p.set_defaults(fn=phases)
     args = ap.parse_args()
     args.fn(args)

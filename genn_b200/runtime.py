@@ -241,6 +241,14 @@ class Runtime:
         check(self.lib.b200_get_kernel_launches(self.handle, C.byref(v)))
         return int(v.value)
 
+    def step_path(self):
+        """(path, reason): 2 target-stationary persistent kernel, 1 persistent kernel with global
+        reductions, 0 one launch per kernel; reason says why path 2 was not taken."""
+        path = C.c_int()
+        why = C.create_string_buffer(256)
+        check(self.lib.b200_get_step_path(self.handle, C.byref(path), why, 256))
+        return path.value, why.value.decode()
+
     def cta_cycles(self) -> np.ndarray:
         """[num_ctas, 4] cycles per phase of the persistent kernel (option fused_profile)."""
         out = np.zeros((1024, 4), dtype=np.uint64)

@@ -133,7 +133,8 @@ typedef struct b200_current_source {
 typedef struct b200_neuron_group {
     uint32_t model;            /* b200_neuron_model */
     uint32_t num_neurons;
-    uint32_t num_delay_slots;  /* spike queue depth: longest axonal/back-propagation delay + 2 */
+    uint32_t num_delay_slots;  /* spike queue depth: at least longest axonal/back-propagation delay + 2;
+                                  + 3 lets the single-barrier persistent kernel be used */
     uint32_t num_psm;
     uint32_t num_cs;
     uint32_t rng_stream;
@@ -262,8 +263,15 @@ int  b200_get_steps_done(b200_runner *r, uint64_t *steps);
 int  b200_get_counter(b200_runner *r, const char *name, uint64_t *value);
 /* Tuning knobs (the counterpart of the backend Preferences, backends/cuda/backend.h:64-115):
  * "spike_lanes" (grid.y of the SPARSE kernel), "use_graph", "graph_steps", "count_events",
- * "use_fused" (persistent fused-step kernel), "fused_blocks_per_sm". */
+ * "use_fused" (persistent kernels), "use_owner" (target-stationary persistent kernel),
+ * "fused_blocks_per_sm", "fused_profile". */
 int  b200_set_option(b200_runner *r, const char *name, double value);
+
+/* Which time-step path b200_step_time takes for the registered model: 2 = target-stationary
+ * persistent kernel (rings in shared memory, one grid barrier per step), 1 = persistent kernel with
+ * global reductions (two barriers per step), 0 = one launch per kernel (CUDA graph).  `why`
+ * (may be NULL) receives the reason path 2 was not chosen. */
+int  b200_get_step_path(b200_runner *r, int *path, char *why, size_t why_bytes);
 
 /* ---- timers: neuronUpdateTime etc. (generateRunner.cc:159-222) ------------- */
 int  b200_enable_timing(b200_runner *r, int enabled);

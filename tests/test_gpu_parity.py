@@ -17,6 +17,21 @@ pytestmark = pytest.mark.gpu
 
 RTOL, ATOL = 1e-5, 2e-6
 
+# the three time-step paths: target-stationary persistent kernel, persistent kernel
+# with global reductions, one launch per kernel
+PATHS = {"owner": (1, 1), "persistent": (1, 0), "per-kernel": (0, 0)}
+# networks the target-stationary kernel must accept (SPARSE, sorted rows, no learning)
+OWNER_CASES = {"ff_sparse", "ff_sparse_narrow", "potjans_mini", "cond_delay", "izhikevich"}
+
+
+def _select(rt, path, name=None):
+    fused, owner = PATHS[path]
+    rt.set_option("use_fused", fused)
+    rt.set_option("use_owner", owner)
+    if path == "owner" and name in OWNER_CASES:
+        taken, why = rt.step_path()
+        assert taken == 2, f"{name} should run on the target-stationary kernel: {why}"
+
 
 def _runtime(net, steps, **kw):
     from genn_b200.runtime import Runtime
@@ -39,30 +54,30 @@ class _Adapter:
         return self.rt.current_spikes(pop)
 
 
-@pytest.mark.parametrize("fused", [1, 0], ids=["persistent", "per-kernel"])
+@pytest.mark.parametrize("path", list(PATHS))
 @pytest.mark.parametrize("name", list(CASES))
-def test_step_by_step_matches_reference_golden(name, fused):
-    """Both time-step paths: the persistent fused-step kernel (where the model is
-    eligible for it) and one launch per kernel."""
+def test_step_by_step_matches_reference_golden(name, path):
+    """Every time-step path (a model not eligible for a persistent kernel falls
+    back to the next one, as in production)."""
     model, steps, dump_every = CASES[name]()
     net = resolve(model)
     rt = _runtime(net, steps)
-    rt.set_option("use_fused", fused)
+    _select(rt, path, name)
     got = helpers.run_and_collect(_Adapter(rt), net, steps, dump_every)
     helpers.compare(got, helpers.load_golden(name), exact_state=False, rtol=RTOL, atol=ATOL)
     rt.close()
 
 
-@pytest.mark.parametrize("fused", [1, 0], ids=["persistent", "graph"])
+@pytest.mark.parametrize("path", list(PATHS))
 @pytest.mark.parametrize("name", ["ff_sparse", "potjans_mini", "cond_delay", "stdp"])
-def test_many_steps_in_one_call_and_recording_match_reference_golden(name, fused):
+def test_many_steps_in_one_call_and_recording_match_reference_golden(name, path):
     """All steps in one call (one persistent launch, or replays of a captured
     graph) with spike recording on: the decoded recording equals the
     reference's spikes and the final state matches."""
     model, steps, dump_every = CASES[name]()
     net = resolve(model)
     rt = _runtime(net, steps)
-    rt.set_option("use_fused", fused)
+    _select(rt, path, name)
     rt.set_option("graph_steps", 37)        # not a divisor of the step count: exercises the remainder path
     rt.step_time(steps)
     rt.synchronize()
@@ -107,8 +122,8 @@ def test_matches_cpu_checker_every_step(name):
     orc.close()
 
 
-@pytest.mark.parametrize("fused", [1, 0], ids=["persistent", "per-kernel"])
-def test_poisson_background_matches_cpu_checker(fused):
+@pytest.mark.parametrize("path", list(PATHS))
+def test_poisson_background_matches_cpu_checker(path):
     """PoissonExp background: the CPU checker replays the library's Philox
     streams, so spikes must be identical and state within tolerance."""
     from oracle.oracle import OracleRunner
@@ -116,7 +131,7 @@ def test_poisson_background_matches_cpu_checker(fused):
     model, steps, dump_every = poisson_drive()
     net, onet = resolve(model), resolve(poisson_drive()[0])
     rt, orc = _runtime(net, steps), OracleRunner(onet, steps)
-    rt.set_option("use_fused", fused)
+    _select(rt, path, "potjans_mini")
     got = helpers.run_and_collect(_Adapter(rt), net, steps, dump_every)
 
     class O:
@@ -151,8 +166,7 @@ def test_device_check_reports_bad_index():
     bad = net.syn("syn")
     bad.ind = bad.ind.copy()
     bad.ind[:] = 100000
-    rt = _runtime(net, steps)
-    rt.step_time(50)
     with pytest.raises(abi.B200Error, match="out of range"):
+        rt = _runtime(net, steps)           # the index check of the initialisation kernels may already catch it
+        rt.step_time(50)
         rt.synchronize()
-    rt.close()

@@ -50,7 +50,8 @@ class NeuronGroupDesc(C.Structure):
                 ("params", C.c_float * MAX_PARAMS), ("vars", C.c_void_p * MAX_VARS),
                 ("egp", C.c_void_p), ("spk_cnt", C.c_void_p), ("spk", C.c_void_p),
                 ("spike_times", C.c_void_p), ("record_spk", C.c_void_p),
-                ("psm", Psm * MAX_PSM), ("cs", CurrentSourceDesc * MAX_CS)]
+                ("psm", Psm * MAX_PSM), ("cs", CurrentSourceDesc * MAX_CS),
+                ("spk_slot_stride", C.c_uint32), ("reserved", C.c_uint32)]
 
 
 class SynapseGroupDesc(C.Structure):
@@ -68,7 +69,9 @@ class SynapseGroupDesc(C.Structure):
                 ("out_post", C.c_void_p), ("den_delay", C.c_void_p),
                 ("proc_connect", C.c_uint32), ("proc_weight_init", C.c_uint32),
                 ("rng_stream", C.c_uint32), ("reserved", C.c_uint32),
-                ("proc_connect_params", C.c_float * 4), ("proc_weight_params", C.c_float * 4)]
+                ("proc_connect_params", C.c_float * 4), ("proc_weight_params", C.c_float * 4),
+                ("src_sections", C.c_uint32), ("src_spk_slot_stride", C.c_uint32),
+                ("src_cnt_section_stride", C.c_uint64), ("src_spk_section_stride", C.c_uint64)]
 
 
 class CustomUpdateDesc(C.Structure):
@@ -95,6 +98,10 @@ _PROTOTYPES = {
     "b200_array_push": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],
     "b200_array_pull": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],
     "b200_array_memset": [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t],
+    "b200_exchange_alloc": [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)],
+    "b200_exchange_get_handle": [C.c_void_p, C.c_void_p],
+    "b200_exchange_open_peer": [C.c_void_p, C.c_uint32, C.c_void_p],
+    "b200_exchange_configure": [C.c_void_p, C.c_uint32, C.c_uint32, C.c_size_t],
     "b200_push_neuron_update_group": [C.c_void_p, C.c_uint32, C.POINTER(NeuronGroupDesc)],
     "b200_push_synapse_group": [C.c_void_p, C.c_uint32, C.POINTER(SynapseGroupDesc)],
     "b200_push_custom_update": [C.c_void_p, C.c_char_p, C.c_uint32, C.POINTER(CustomUpdateDesc)],

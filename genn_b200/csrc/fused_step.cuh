@@ -72,7 +72,28 @@ struct FusedLaunch
     unsigned long long *cta_cycles;      // [gridDim][4] or NULL
     unsigned long long num_steps;
     unsigned long long *barrier;         // monotonic arrival counter
+    // spike exchange between the processes of a sharded model (world == 1: unused)
+    unsigned int rank;
+    unsigned int world;
+    unsigned char *arena;                // this process's exchange arena
+    unsigned char *const *peer_table;    // device table [B200_MAX_RANKS]: the same arena of every peer, mapped here
+    unsigned long long *flags;           // in the local arena: flags[r] = steps whose spikes rank r has delivered
 };
+
+constexpr unsigned long long EXCHANGE_SPIN_LIMIT = 1ull << 23;
+constexpr unsigned int ERR_EXCHANGE_TIMEOUT = 32u;
+
+__device__ __forceinline__ unsigned long long loadAcquireSys(const unsigned long long *p)
+{
+    unsigned long long v;
+    asm volatile("ld.acquire.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void storeReleaseSys(unsigned long long *p, unsigned long long v)
+{
+    asm volatile("st.release.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
 
 __device__ __forceinline__ unsigned long long loadAcquire(const unsigned long long *p)
 {
@@ -144,6 +165,8 @@ fusedStepKernel(FusedLaunch L)
     extern __shared__ __align__(16) unsigned char fusedSmem[];
     __shared__ bool barrierOk;
     __shared__ unsigned int headCnt[32], headSlot[32], headIds[32][FUSED_PREFETCH_IDS];
+    __shared__ unsigned char *peerArena[B200_MAX_RANKS];
+    if(threadIdx.x < B200_MAX_RANKS) peerArena[threadIdx.x] = L.peer_table ? L.peer_table[threadIdx.x] : nullptr;
     if(L.stage_in_smem) {
         unsigned char *p = fusedSmem;
         const size_t nb = sizeof(b200_neuron_group) * L.neuron.num_groups;
@@ -179,6 +202,7 @@ fusedStepKernel(FusedLaunch L)
     const unsigned int period = state->ring_period;
     unsigned int k = state->phase;
     const unsigned long long t0 = state->timestep;
+    const unsigned long long done0 = state->steps_done;
     unsigned long long epoch = 0;        // the host zeroes the arrival counter before every launch
     const unsigned int numGroups = L.neuron.num_groups;
     const unsigned int totalSlots = L.slot_start[numGroups];
@@ -206,6 +230,24 @@ fusedStepKernel(FusedLaunch L)
     long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
     for(unsigned long long step = 0; step < L.num_steps; step++) {
         if(prof) c0 = clock64();
+
+        // ---------------- spikes of the other processes must have landed -----------------
+        // Each peer wrote its lists of the previous step into THIS process's arena and
+        // then raised its flag; only local memory is polled and read.  Bounded wait.
+        if(L.world > 1) {
+            if(threadIdx.x < L.world && threadIdx.x != L.rank) {
+                const unsigned long long need = done0 + step;
+                unsigned long long polls = 0;
+                while(loadAcquireSys(&L.flags[threadIdx.x]) < need) {
+                    if(++polls > EXCHANGE_SPIN_LIMIT) {
+                        atomicOr(&state->error, ERR_EXCHANGE_TIMEOUT);
+                        break;
+                    }
+                }
+            }
+            __syncthreads();
+            if(__ldcg(&state->error) & ERR_EXCHANGE_TIMEOUT) return;
+        }
 
         // ---------------- phase A: presynaptic update ------------------------------
         for(unsigned int base = 0; base < L.num_sources; base += 32u) {
@@ -323,6 +365,37 @@ fusedStepKernel(FusedLaunch L)
         if(prof) c3 = clock64();
         gridArrive(L.barrier, epoch);
         if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
+
+        // ---------------- deliver this step's spikes to the other processes ----------------
+        // The local lists are final (barrier above).  One warp per peer copies every
+        // population's list into the peer's arena at the same offset with plain peer
+        // stores, fences, and raises this process's flag there.
+        if(L.world > 1 && blockIdx.x == 0) {
+            const unsigned int peer = threadIdx.x >> 5;
+            if(peer < L.world && peer != L.rank) {
+                for(unsigned int gi = 0; gi < numGroups; gi++) {
+                    const b200_neuron_group &g = L.neuron.groups[gi];
+                    const unsigned int wslot = ringSlot(k + 1, g.num_delay_slots);
+                    const unsigned int stride = g.spk_slot_stride ? g.spk_slot_stride : g.num_neurons;
+                    const unsigned int *cntLocal = &g.spk_cnt[wslot];
+                    const unsigned int *listLocal = g.spk + (unsigned long long)wslot * stride;
+                    unsigned int *cntRemote = reinterpret_cast<unsigned int*>(
+                        peerArena[peer] + (reinterpret_cast<const unsigned char*>(cntLocal) - L.arena));
+                    unsigned int *listRemote = reinterpret_cast<unsigned int*>(
+                        peerArena[peer] + (reinterpret_cast<const unsigned char*>(listLocal) - L.arena));
+                    const unsigned int cnt = __ldcg(cntLocal);
+                    for(unsigned int i = lane; i < cnt; i += 32u) listRemote[i] = __ldcg(&listLocal[i]);
+                    if(lane == 0) *cntRemote = cnt;
+                }
+                __syncwarp();
+                if(lane == 0) {
+                    __threadfence_system();
+                    unsigned long long *flagRemote = reinterpret_cast<unsigned long long*>(
+                        peerArena[peer] + (reinterpret_cast<unsigned char*>(L.flags) - L.arena)) + L.rank;
+                    storeReleaseSys(flagRemote, done0 + step + 1);
+                }
+            }
+        }
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {
             const long long c4 = clock64();

@@ -280,6 +280,7 @@ __device__ __forceinline__ void neuronEmit(const NeuronLaunch &L, const b200_neu
     const bool active = local < g.num_update;
     const unsigned int slots = g.num_delay_slots;
     const unsigned int wslot = ringSlot(k + 1, slots);
+    const unsigned int listStride = g.spk_slot_stride ? g.spk_slot_stride : N;
     const unsigned int ballot = __ballot_sync(0xFFFFFFFFu, spiked);
     const unsigned int lane = threadIdx.x & 31u;
     if(ballot) {
@@ -291,8 +292,8 @@ __device__ __forceinline__ void neuronEmit(const NeuronLaunch &L, const b200_neu
         if(L.count_events && lane == 0) atomicAdd(&L.state->spikes, (unsigned long long)__popc(ballot));
         if(spiked) {
             const unsigned int pos = base + __popc(ballot & ((1u << lane) - 1u));
-            if(pos < N) {
-                g.spk[((unsigned long long)b * slots + wslot) * N + pos] = i;
+            if(pos < listStride) {
+                g.spk[((unsigned long long)b * slots + wslot) * listStride + pos] = i;
             }
             else {
                 atomicOr(&L.state->error, ERR_SPIKE_OVERFLOW);

@@ -128,6 +128,15 @@ struct b200_runner
     bool fusedProfile = false;
     unsigned long long *fusedCtaCycles = nullptr;
 
+    // spike exchange of a sharded model
+    unsigned char *arena = nullptr;
+    size_t arenaBytes = 0;
+    unsigned char *peerArena[B200_MAX_RANKS] = {};
+    unsigned char **peerTable = nullptr;     // device copy of peerArena
+    unsigned int rank = 0, world = 1;
+    size_t flagsOffset = 0;
+    bool sharded() const { return world > 1; }
+
     // target-stationary persistent path (rings in shared memory, one grid barrier per step)
     bool ownerEligible = false;
     bool useOwner = false;       // measured slower than the global-reduction kernel on Potjans: opt-in
@@ -461,22 +470,27 @@ int prepare(b200_runner *r)
         std::vector<std::vector<uint2>> perSource;
         for(size_t gi = 0; gi < sparse.size(); gi++) {
             const auto &g = sparse[gi];
-            size_t si = 0;
-            for(; si < sources.size(); si++) {
-                if(sources[si].spk_cnt == g.src_spk_cnt && sources[si].delay == g.axonal_delay) break;
-            }
-            if(si == sources.size()) {
-                FusedSource src{};
-                src.spk_cnt = g.src_spk_cnt;
-                src.spk = g.src_spk;
-                src.num_src = g.num_src;
-                src.slots = g.src_delay_slots;
-                src.delay = g.axonal_delay;
-                sources.push_back(src);
-                perSource.emplace_back();
-            }
+            // a sharded source population contributes one source per process section
+            const unsigned int sections = std::max(1u, g.src_sections);
             const unsigned int chunks = (g.row_stride + 3 + FUSED_CHUNK - 1) / FUSED_CHUNK;
-            for(unsigned int c = 0; c < chunks; c++) perSource[si].push_back(make_uint2((unsigned int)gi, c));
+            for(unsigned int sec = 0; sec < sections; sec++) {
+                const unsigned int *cntPtr = g.src_spk_cnt + sec * g.src_cnt_section_stride;
+                size_t si = 0;
+                for(; si < sources.size(); si++) {
+                    if(sources[si].spk_cnt == cntPtr && sources[si].delay == g.axonal_delay) break;
+                }
+                if(si == sources.size()) {
+                    FusedSource src{};
+                    src.spk_cnt = cntPtr;
+                    src.spk = g.src_spk + sec * g.src_spk_section_stride;
+                    src.num_src = g.src_spk_slot_stride ? g.src_spk_slot_stride : g.num_src;   // list capacity
+                    src.slots = g.src_delay_slots;
+                    src.delay = g.axonal_delay;
+                    sources.push_back(src);
+                    perSource.emplace_back();
+                }
+                for(unsigned int c = 0; c < chunks; c++) perSource[si].push_back(make_uint2((unsigned int)gi, c));
+            }
         }
         std::vector<uint2> items;
         for(size_t si = 0; si < sources.size(); si++) {
@@ -626,6 +640,22 @@ int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long 
     L.cta_cycles = r->fusedProfile ? r->fusedCtaCycles : nullptr;
     L.num_steps = numSteps;
     L.barrier = r->fusedBarrier;
+    L.rank = r->rank;
+    L.world = r->world;
+    L.arena = r->arena;
+    L.peer_table = r->peerTable;
+    L.flags = r->arena ? reinterpret_cast<unsigned long long*>(r->arena + r->flagsOffset) : nullptr;
+    if(r->sharded()) {
+        for(unsigned int p = 0; p < r->world; p++) {
+            if(p != r->rank && !r->peerArena[p]) return fail(B200_ERR_STATE, "exchange arena of rank %u has not been opened", p);
+        }
+        for(const auto &g : r->neuronGroups) {
+            const unsigned char *c = reinterpret_cast<const unsigned char*>(g.spk_cnt), *s = reinterpret_cast<const unsigned char*>(g.spk);
+            if(c < r->arena || c >= r->arena + r->arenaBytes || s < r->arena || s >= r->arena + r->arenaBytes) {
+                return fail(B200_ERR_INVALID, "spike arrays of a sharded model must live in the exchange arena");
+            }
+        }
+    }
     CUDA_TRY(cudaMemsetAsync(r->fusedBarrier, 0, sizeof(unsigned long long), r->stream));
     void *args[] = {&L};
     CUDA_TRY(cudaLaunchCooperativeKernel(r->fusedKernel, dim3(r->fusedGrid), dim3(FUSED_BLOCK), args,
@@ -804,6 +834,11 @@ int b200_runner_destroy(b200_runner *r)
     if(r->fusedBarrier) cudaFree(r->fusedBarrier);
     if(r->fusedCtaCycles) cudaFree(r->fusedCtaCycles);
     r->dropOwner();
+    for(unsigned int p = 0; p < B200_MAX_RANKS; p++) {
+        if(r->peerArena[p]) cudaIpcCloseMemHandle(r->peerArena[p]);
+    }
+    if(r->arena) cudaFree(r->arena);
+    if(r->peerTable) cudaFree(r->peerTable);
     for(auto &a : r->arrays) cudaFree(a.first);
     cudaFree(r->state);
     cudaEventDestroy(r->evA);
@@ -839,6 +874,58 @@ int b200_host_free(b200_runner *r, void *host_ptr)
 {
     (void)r;
     CUDA_TRY(cudaFreeHost(host_ptr));
+    return B200_OK;
+}
+
+int b200_exchange_alloc(b200_runner *r, size_t bytes, void **device_ptr)
+{
+    if(!r || !device_ptr || bytes == 0) return fail(B200_ERR_INVALID, "bad arguments to b200_exchange_alloc");
+    if(r->arena) return fail(B200_ERR_STATE, "the exchange arena has already been allocated");
+    CUDA_TRY(cudaSetDevice(r->device));
+    void *p = nullptr;
+    CUDA_TRY(cudaMalloc(&p, bytes + ARRAY_TAIL_PAD));
+    CUDA_TRY(cudaMemset(p, 0, bytes + ARRAY_TAIL_PAD));
+    r->arena = static_cast<unsigned char*>(p);
+    r->arenaBytes = bytes;
+    *device_ptr = p;
+    return B200_OK;
+}
+
+int b200_exchange_get_handle(b200_runner *r, void *handle_64_bytes)
+{
+    if(!r || !r->arena || !handle_64_bytes) return fail(B200_ERR_STATE, "no exchange arena");
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    cudaIpcMemHandle_t h;
+    CUDA_TRY(cudaIpcGetMemHandle(&h, r->arena));
+    memcpy(handle_64_bytes, &h, sizeof(h));
+    return B200_OK;
+}
+
+int b200_exchange_open_peer(b200_runner *r, uint32_t peer_rank, const void *handle_64_bytes)
+{
+    if(!r || peer_rank >= B200_MAX_RANKS || !handle_64_bytes) return fail(B200_ERR_INVALID, "bad peer rank");
+    if(r->peerArena[peer_rank]) return fail(B200_ERR_STATE, "peer %u already opened", peer_rank);
+    CUDA_TRY(cudaSetDevice(r->device));
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle_64_bytes, sizeof(h));
+    void *p = nullptr;
+    CUDA_TRY(cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess));
+    r->peerArena[peer_rank] = static_cast<unsigned char*>(p);
+    if(!r->peerTable) CUDA_TRY(cudaMalloc(&r->peerTable, sizeof(unsigned char*) * B200_MAX_RANKS));
+    CUDA_TRY(cudaMemcpy(r->peerTable, r->peerArena, sizeof(unsigned char*) * B200_MAX_RANKS, cudaMemcpyHostToDevice));
+    return B200_OK;
+}
+
+int b200_exchange_configure(b200_runner *r, uint32_t rank, uint32_t world, size_t flags_offset)
+{
+    if(!r || world == 0 || world > B200_MAX_RANKS || rank >= world) return fail(B200_ERR_INVALID, "bad rank/world");
+    if(world > 1 && (!r->arena || flags_offset + sizeof(unsigned long long) * B200_MAX_RANKS > r->arenaBytes || (flags_offset & 7))) {
+        return fail(B200_ERR_INVALID, "flags do not fit the exchange arena");
+    }
+    r->rank = rank;
+    r->world = world;
+    r->flagsOffset = flags_offset;
+    r->dirty = true;
     return B200_OK;
 }
 
@@ -1065,8 +1152,12 @@ int b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_ti
     int e = prepare(r);
     if(e) return e;
     uint64_t left = num_steps;
+    if(r->sharded() && !(r->useFused && r->fusedEligible && !r->timing)) {
+        return fail(B200_ERR_STATE, "a sharded model runs on the persistent kernel only (batch 1, SPARSE "
+                                    "non-learning groups, per-kernel timing off)");
+    }
     if(r->useFused && r->fusedEligible && !r->timing) {
-        const bool owner = r->useOwner && r->ownerEligible;
+        const bool owner = !r->sharded() && r->useOwner && r->ownerEligible;
         while(left) {
             const uint64_t n = std::min<uint64_t>(left, 1ull << 20);
             e = owner ? launchOwner(r, n, num_recording_timesteps) : launchFused(r, n, num_recording_timesteps);
@@ -1119,11 +1210,12 @@ int b200_synchronize(b200_runner *r)
     if(s.error) {
         const unsigned int err = s.error;
         cudaMemset(&r->state->error, 0, sizeof(unsigned int));
-        return fail(B200_ERR_DEVICE_CHECK, "device-side check failed (flags 0x%x:%s%s%s%s)", err,
+        return fail(B200_ERR_DEVICE_CHECK, "device-side check failed (flags 0x%x:%s%s%s%s%s)", err,
                     (err & ERR_SPIKE_OVERFLOW) ? " spike list overflow" : "",
                     (err & ERR_IND_RANGE) ? " index or row length out of range" : "",
                     (err & ERR_DELAY_RANGE) ? " delay out of range" : "",
-                    (err & ERR_BARRIER_TIMEOUT) ? " grid barrier timed out" : "");
+                    (err & ERR_BARRIER_TIMEOUT) ? " grid barrier timed out" : "",
+                    (err & ERR_EXCHANGE_TIMEOUT) ? " spikes of another process did not arrive in time" : "");
     }
     return B200_OK;
 }

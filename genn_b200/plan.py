@@ -21,11 +21,33 @@ from .resolve import Net, RPop, RSyn
 TIME_MIN = np.float32(-3.402823466e+38)     # initial spike time: -TIME_MAX (definitions.h)
 
 
+def shard_bounds(n: int, world: int):
+    """Boundaries of the contiguous slices of a population of ``n`` neurons owned
+    by ``world`` processes: multiples of 32 (a warp writes one spike-recording
+    word), the last one ``n``."""
+    b = [((n * r) // world) & ~31 for r in range(world)]
+    return b + [n]
+
+
+class _View:
+    """A window into an array handle (same memory, offset pointer)."""
+
+    def __init__(self, parent, offset: int, nbytes: int):
+        self.parent, self.offset, self.nbytes = parent, offset, nbytes
+        self.ptr = parent.ptr + offset
+        if hasattr(parent, "buf"):
+            self.buf = parent.buf[offset:offset + nbytes]
+
+
 class ArrayFactory:
     """Where arrays live.  ``alloc`` returns a handle with an integer ``ptr``."""
 
     def alloc(self, nbytes: int):
         raise NotImplementedError
+
+    def alloc_exchange(self, nbytes: int):
+        """Memory that peers of a sharded model can map (spike lists and flags)."""
+        return self.alloc(nbytes)
 
     def push(self, handle, host: np.ndarray):
         raise NotImplementedError
@@ -76,6 +98,8 @@ class Plan:
         self.neuron_descs: List[abi.NeuronGroupDesc] = []
         self.synapse_descs: List[abi.SynapseGroupDesc] = []
         self._next_stream = 1
+        self.exchange = None                # arena of a sharded model
+        self.flags_offset = 0
         self._build()
 
     # ------------------------------------------------------------------
@@ -115,10 +139,29 @@ class Plan:
         net, B = self.net, self.net.batch_size
         pop_index = {p.name: i for i, p in enumerate(net.pops)}
 
+        # a sharded model keeps every population's spike lists (one section per
+        # process) and the arrival flags in ONE arena that peers can map
+        world = self.shard[1] if self.shard else 1
+        for p in net.pops:
+            p.runtime_slots = p.num_delay_slots + 2     # two spare slots: see include/genn_b200.h
+            bounds = shard_bounds(p.n, world)
+            p.shard_bounds = bounds
+            p.list_capacity = p.n if world == 1 else max(32, max(bounds[r + 1] - bounds[r] for r in range(world)))
+        if world > 1:
+            offset = 256                                 # flags first
+            layout = {}
+            for p in net.pops:
+                for name, count in ((f"{p.name}.spk_cnt", world * B * p.runtime_slots),
+                                    (f"{p.name}.spk", world * B * p.runtime_slots * p.list_capacity)):
+                    layout[name] = (offset, count * 4)
+                    offset = (offset + count * 4 + 255) & ~255
+            self.exchange = self.factory.alloc_exchange(offset)
+            self.factory.memset(self.exchange, 0, offset)
+            self._exchange_layout = layout
+
         # neuron-side arrays
         for p in net.pops:
-            slots = p.num_delay_slots + 2     # two spare slots: see include/genn_b200.h
-            p.runtime_slots = slots
+            slots = p.runtime_slots
             for v, arr in p.vars.items():
                 dtype = np.uint32 if p.kind == "SpikeSourceArray" else np.float32
                 a = self._new(f"{p.name}.{v}", dtype, (B, p.n), arr if arr is not None else 0)
@@ -131,8 +174,14 @@ class Plan:
                 if len(times) == 0:
                     times = np.zeros(1, np.float32)
                 self._new(f"{p.name}.spikeTimes", np.float32, times.shape, times)
-            self._new(f"{p.name}.spk_cnt", np.uint32, (B, slots))
-            self._new(f"{p.name}.spk", np.uint32, (B, slots, p.n))
+            if world == 1:
+                self._new(f"{p.name}.spk_cnt", np.uint32, (B, slots))
+                self._new(f"{p.name}.spk", np.uint32, (B, slots, p.n))
+            else:
+                for name, shape in ((f"{p.name}.spk_cnt", (world, B, slots)),
+                                    (f"{p.name}.spk", (world, B, slots, p.list_capacity))):
+                    off, nbytes = self._exchange_layout[name]
+                    self.arrays[name] = PlannedArray(name, _View(self.exchange, off, nbytes), np.dtype(np.uint32), shape)
             if p.spike_time_required:
                 self._new(f"{p.name}.sT", np.float32, (B, slots, p.n), TIME_MIN)
             if p.record and self.num_recording_timesteps:
@@ -225,8 +274,8 @@ class Plan:
         d.rng_stream = self._stream()
         if self.shard is not None:
             rank, world = self.shard
-            a, b = (p.n * rank) // world, (p.n * (rank + 1)) // world
-            d.first_neuron, d.num_update = a, b - a
+            d.first_neuron, d.num_update = p.shard_bounds[rank], p.shard_bounds[rank + 1] - p.shard_bounds[rank]
+            d.spk_slot_stride = p.list_capacity
         else:
             d.first_neuron, d.num_update = 0, p.n
         if p.kind == "LIF":
@@ -247,6 +296,10 @@ class Plan:
             d.vars[i] = self._ptr(f"{p.name}.{v}")
         d.spk_cnt = self._ptr(f"{p.name}.spk_cnt")
         d.spk = self._ptr(f"{p.name}.spk")
+        if self.shard is not None:          # this process writes its own section
+            rank = self.shard[0]
+            d.spk_cnt += rank * net.batch_size * p.runtime_slots * 4
+            d.spk += rank * net.batch_size * p.runtime_slots * p.list_capacity * 4
         d.spike_times = self._ptr(f"{p.name}.sT")
         d.record_spk = self._ptr(f"{p.name}.record")
         k = 0
@@ -313,6 +366,11 @@ class Plan:
         for f in ("row_length", "ind", "g", "d", "gp", "col_length", "remap"):
             setattr(d, f, self._ptr(f"{s.name}.{f}"))
         d.src_spk_cnt, d.src_spk = self._ptr(f"{src.name}.spk_cnt"), self._ptr(f"{src.name}.spk")
+        if self.shard is not None:
+            d.src_sections = self.shard[1]
+            d.src_spk_slot_stride = src.list_capacity
+            d.src_cnt_section_stride = net.batch_size * src.runtime_slots
+            d.src_spk_section_stride = net.batch_size * src.runtime_slots * src.list_capacity
         d.trg_spk_cnt, d.trg_spk = self._ptr(f"{trg.name}.spk_cnt"), self._ptr(f"{trg.name}.spk")
         d.src_spike_times = self._ptr(f"{src.name}.sT")
         d.trg_spike_times = self._ptr(f"{trg.name}.sT")

@@ -42,6 +42,13 @@ class DeviceFactory(ArrayFactory):
     def alloc(self, nbytes: int) -> DeviceArray:
         return DeviceArray(self, nbytes)
 
+    def alloc_exchange(self, nbytes: int):
+        p = C.c_void_p()
+        check(self.lib.b200_exchange_alloc(self.handle, nbytes, C.byref(p)))
+        arr = DeviceArray.__new__(DeviceArray)
+        arr._rt, arr.nbytes, arr.ptr = self, nbytes, p.value
+        return arr
+
     def push(self, handle: DeviceArray, host: np.ndarray):
         host = np.ascontiguousarray(host)
         check(self.lib.b200_array_push(self.handle, handle.ptr, host.ctypes.data, host.nbytes))
@@ -54,6 +61,15 @@ class DeviceFactory(ArrayFactory):
 
     def memset(self, handle: DeviceArray, value: int, nbytes: int):
         check(self.lib.b200_array_memset(self.handle, handle.ptr, value, nbytes))
+
+
+def all_gather_bytes(payload: bytes):
+    """All-gather a small byte string over the default ``torch.distributed`` group
+    (any backend: this is bootstrap plumbing, not the data path)."""
+    import torch.distributed as dist
+    out = [None] * dist.get_world_size()
+    dist.all_gather_object(out, payload)
+    return out
 
 
 class _LazyRecording:
@@ -81,7 +97,7 @@ class Runtime:
     """One loaded model on one GPU."""
 
     def __init__(self, model, num_recording_timesteps: Optional[int] = None, device: int = 0,
-                 shard: Optional[Tuple[int, int]] = None, net: Optional[Net] = None):
+                 shard: Optional[Tuple[int, int]] = None, net: Optional[Net] = None, exchange=None):
         self.lib = abi.load_library()
         self.model = model
         self.net = net if net is not None else resolve(model)
@@ -93,7 +109,10 @@ class Runtime:
         self._pinned = []
         self._rec_host = {}
         self._rec_timestep = 0
+        self.shard = shard
         self.plan = Plan(self.net, self.factory, self.num_recording_timesteps, shard=shard)
+        if shard is not None and shard[1] > 1:
+            self._connect_peers(exchange)
         self._run_init_tasks()
         for i, d in enumerate(self.plan.neuron_descs):
             check(self.lib.b200_push_neuron_update_group(self.handle, i, C.byref(d)))
@@ -106,6 +125,21 @@ class Runtime:
             if getattr(model, "timing_enabled", False):
                 check(self.lib.b200_enable_timing(self.handle, 1))
         self.synchronize()
+
+    # -- sharded models: map every peer's exchange arena ---------------------------
+    def _connect_peers(self, exchange):
+        """``exchange(bytes) -> [bytes per rank]`` all-gathers the 64-byte IPC handle
+        of this process's arena; the default uses ``torch.distributed``."""
+        rank, world = self.shard
+        handle = C.create_string_buffer(64)
+        check(self.lib.b200_exchange_get_handle(self.handle, handle))
+        handles = (exchange or all_gather_bytes)(handle.raw)
+        if len(handles) != world:
+            raise abi.B200Error(f"expected {world} arena handles, got {len(handles)}")
+        for peer, h in enumerate(handles):
+            if peer != rank:
+                check(self.lib.b200_exchange_open_peer(self.handle, peer, C.create_string_buffer(h, 64)))
+        check(self.lib.b200_exchange_configure(self.handle, rank, world, self.plan.flags_offset))
 
     # -- initialisation kernels -------------------------------------------------
     def _run_init_tasks(self):
@@ -277,8 +311,11 @@ class Runtime:
         name = pop if isinstance(pop, str) else pop.name
         p = self.net.pop(name)
         slot = self.steps_done % p.runtime_slots
-        cnt = int(self.array(f"{name}.spk_cnt")[batch, slot])
-        return self.array(f"{name}.spk")[batch, slot, :cnt].copy()
+        cnt, spk = self.array(f"{name}.spk_cnt"), self.array(f"{name}.spk")
+        if cnt.ndim == 2:
+            return spk[batch, slot, :int(cnt[batch, slot])].copy()
+        # sharded: one section per process (peers' sections hold what they delivered)
+        return np.concatenate([spk[s, batch, slot, :int(cnt[s, batch, slot])] for s in range(cnt.shape[0])])
 
     def pinned_empty(self, shape, dtype) -> np.ndarray:
         """Page-locked host array (cudaHostAlloc) owned by this runtime."""

@@ -196,15 +196,25 @@ def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
             # NormalClippedDelay: truncated normal in time steps, then rint
             d = np.rint(truncated_normal(rng, md / dt, sd / dt, 0.0, mxd / dt, num)).astype(np.uint8)
             if shard is not None:
+                from .plan import shard_bounds
                 rank, world = shard
-                a, b = (nt * rank) // world, (nt * (rank + 1)) // world
-                keep = (post >= a) & (post < b)
+                bounds = shard_bounds(nt, world)
+                keep = (post >= bounds[rank]) & (post < bounds[rank + 1])
                 pre, post, g, d = pre[keep], post[keep], g[keep], d[keep]
             wu = init_weight_update("StaticPulseDendriticDelay", {}, {"g": g, "d": d})
             sg = m.add_synapse_population(f"{src}_{trg}", "SPARSE", pops[src], pops[trg], wu,
                                           init_postsynaptic("ExpCurr", {"tau": 0.5}))
             sg.set_sparse_connections(pre, post)
         else:
+            trg_range = None
+            if shard is not None:
+                # this process draws only the sub-matrix onto its own slice of the
+                # targets: same in-degree, so its share of the synapses
+                from .plan import shard_bounds
+                rank, world = shard
+                bounds = shard_bounds(nt, world)
+                trg_range = (bounds[rank], bounds[rank + 1])
+                num = int(round(num * (trg_range[1] - trg_range[0]) / float(nt)))
             wu = init_weight_update("StaticPulseDendriticDelay", {}, {
                 "g": init_var("NormalClipped", {"mean": mean_w, "sd": sd_w, "min": lo, "max": hi}),
                 "d": init_var("NormalClippedDelay", {"mean": md, "sd": sd, "min": 0.0, "max": mxd})})
@@ -212,6 +222,6 @@ def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
                 f"{src}_{trg}", "SPARSE", pops[src], pops[trg], wu,
                 init_postsynaptic("ExpCurr", {"tau": 0.5}),
                 init_sparse_connectivity("FixedNumberTotalWithReplacement", {"num": num}))
-            sg.shard = shard
+            sg.trg_range = trg_range
         sg.max_dendritic_delay_timesteps = slots
     return m

@@ -39,6 +39,7 @@ extern "C" {
 #define B200_MAX_CS      4   /* current sources per neuron group */
 #define B200_MAX_PARAMS  8
 #define B200_MAX_VARS    4
+#define B200_MAX_RANKS   8   /* processes (one per GPU) a sharded model may span */
 
 typedef enum b200_status {
     B200_OK = 0,
@@ -149,6 +150,9 @@ typedef struct b200_neuron_group {
     uint32_t *record_spk;      /* [recordingTimesteps][batch][ceil(N/32)] or NULL; bit i%32 of word i/32 */
     b200_psm psm[B200_MAX_PSM];
     b200_current_source cs[B200_MAX_CS];
+    uint32_t spk_slot_stride;  /* elements between two slots of `spk`; 0 = num_neurons.  A process that
+                                  updates a slice of the group keeps a list sized for the slice. */
+    uint32_t reserved;
 } b200_neuron_group;
 
 /* One element of the merged presynaptic-update group array and, when the
@@ -190,6 +194,13 @@ typedef struct b200_synapse_group {
     uint32_t reserved;
     float    proc_connect_params[4];
     float    proc_weight_params[4];
+    /* Sharded source population: the spike lists of `src_sections` processes lie one after another,
+     * section s at src_spk_cnt + s*src_cnt_section_stride and src_spk + s*src_spk_section_stride
+     * (elements); ids are indices into the whole population.  0 or 1: a single list. */
+    uint32_t src_sections;
+    uint32_t src_spk_slot_stride;      /* elements between two slots of one list; 0 = num_src */
+    uint64_t src_cnt_section_stride;
+    uint64_t src_spk_section_stride;
 } b200_synapse_group;
 
 /* Batch-reduce custom update (backendSIMT.cc:888-927, 1109-1147):
@@ -223,6 +234,19 @@ int  b200_host_free(b200_runner *r, void *host_ptr);
 int  b200_array_push(b200_runner *r, void *device_ptr, const void *host, size_t bytes);
 int  b200_array_pull(b200_runner *r, void *host, const void *device_ptr, size_t bytes);
 int  b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes);
+
+/* ---- spike exchange between processes (no counterpart in the reference, which has no model
+ *      sharding: SURVEY of backendCUDAHIP.cc shows NCCL all-reduce of custom-update results only).
+ * A model sharded by postsynaptic neuron over several GPUs of one node exchanges each step's spike
+ * lists.  Every process allocates ONE exchange arena, places its spike arrays (all sections) and the
+ * arrival flags in it at identical offsets, shares the arena's IPC handle with its peers and opens
+ * theirs.  The persistent kernel then writes its own lists straight into every peer's arena with
+ * peer stores and raises a flag; a peer reads only its own memory. ------------------------------ */
+int  b200_exchange_alloc(b200_runner *r, size_t bytes, void **device_ptr);
+int  b200_exchange_get_handle(b200_runner *r, void *handle_64_bytes);
+int  b200_exchange_open_peer(b200_runner *r, uint32_t peer_rank, const void *handle_64_bytes);
+/* flags_offset: byte offset in the arena of B200_MAX_RANKS uint64 arrival flags (zero-initialised) */
+int  b200_exchange_configure(b200_runner *r, uint32_t rank, uint32_t world, size_t flags_offset);
 
 /* ---- merged-group registration: pushMerged<Kind>Group<i>ToDevice
  *      (backendCUDAHIP.h:206-238, runtime.h:573-669) -------------------------- */

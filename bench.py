@@ -286,28 +286,56 @@ def main():
         n_local = rt.plan.neuron_descs[[q.name for q in net.pops].index(p.name)].num_update
         rates[p.name] = round(len(ids) / max(1, n_local) / (block * DT_MS * 1e-3), 3)
 
-    # ---- roofline of the presynaptic kernel, live, per-kernel CUDA events ---------------
-    rt.enable_timing(True)
-    rt.reset_timers()
-    tev0, tsp0 = rt.counter("synaptic_events"), rt.counter("spikes")
+    # ---- where a step's time goes inside the persistent kernel (clock64 per phase, CTA 0) ---
     probe_steps = min(args.steps * block, 2000)
+    rt.set_option("fused_profile", 1)
+    names = ["cycles_presynaptic", "cycles_barrier_a", "cycles_neuron", "cycles_barrier_b"]
+    before = [rt.counter(n) for n in names]
+    pev0, psp0 = rt.counter("synaptic_events"), rt.counter("spikes")
+    barrier()
     rt.step_time(probe_steps)
     rt.synchronize()
-    tev, tsp = rt.counter("synaptic_events") - tev0, rt.counter("spikes") - tsp0
-    pre_s, neu_s = rt.timer("presynaptic_update"), rt.timer("neuron_update")
-    rt.enable_timing(False)
-    nat_bytes = tev * bpe + tsp * ALGO_BYTES_PER_SPIKE
-    nat_gbs = nat_bytes / pre_s / 1e9 if pre_s > 0 else 0.0
-    roofline = {"kernel": "presynapticSparseKernel", "bound": "hbm", "achieved": nat_gbs, "peak": hbm_peak,
-                "unit": "GB/s", "frac": nat_gbs / hbm_peak, "traffic": None, "peak_source": peak_kind,
-                "launches": probe_steps, "avg_launch_us": pre_s / probe_steps * 1e6,
-                "neuron_kernel_avg_launch_us": neu_s / probe_steps * 1e6,
-                "algorithmic_bytes_per_launch": nat_bytes / probe_steps,
-                "note": "natural firing rates: ~0.1 MB per launch, latency-bound by construction"}
+    barrier()
+    pev, psp = rt.counter("synaptic_events") - pev0, rt.counter("spikes") - psp0
+    phase_cycles = {n: (rt.counter(n) - b) / probe_steps for n, b in zip(names, before)}
+    rt.set_option("fused_profile", 0)
+    sm_hz = (clocks.get("sm_mhz") or 1965.0) * 1e6
+
+    # ---- roofline of the presynaptic kernel, live, per-kernel CUDA events ---------------
+    if world == 1:
+        rt.enable_timing(True)
+        rt.reset_timers()
+        tev0, tsp0 = rt.counter("synaptic_events"), rt.counter("spikes")
+        rt.step_time(probe_steps)
+        rt.synchronize()
+        tev, tsp = rt.counter("synaptic_events") - tev0, rt.counter("spikes") - tsp0
+        pre_s, neu_s = rt.timer("presynaptic_update"), rt.timer("neuron_update")
+        rt.enable_timing(False)
+        nat_bytes = tev * bpe + tsp * ALGO_BYTES_PER_SPIKE
+        nat_gbs = nat_bytes / pre_s / 1e9 if pre_s > 0 else 0.0
+        roofline = {"kernel": "presynapticSparseKernel", "bound": "hbm", "achieved": nat_gbs, "peak": hbm_peak,
+                    "unit": "GB/s", "frac": nat_gbs / hbm_peak, "traffic": None, "peak_source": peak_kind,
+                    "launches": probe_steps, "avg_launch_us": pre_s / probe_steps * 1e6,
+                    "neuron_kernel_avg_launch_us": neu_s / probe_steps * 1e6,
+                    "algorithmic_bytes_per_launch": nat_bytes / probe_steps,
+                    "persistent_kernel_phase_cycles_per_step": phase_cycles,
+                    "note": "natural firing rates: under 1 MB per launch, latency-bound by construction; timed on the "
+                            "one-launch-per-kernel path (CUDA event pair around every launch)"}
+    else:
+        # a sharded model runs on the persistent kernel only: its presynaptic phase is timed with clock64
+        pre_s = phase_cycles["cycles_presynaptic"] * probe_steps / sm_hz
+        nat_bytes = pev * bpe + psp * ALGO_BYTES_PER_SPIKE
+        nat_gbs = nat_bytes / pre_s / 1e9 if pre_s > 0 else 0.0
+        roofline = {"kernel": "fusedStepKernel (presynaptic phase)", "bound": "hbm", "achieved": nat_gbs,
+                    "peak": hbm_peak, "unit": "GB/s", "frac": nat_gbs / hbm_peak, "traffic": None,
+                    "peak_source": peak_kind, "launches": probe_steps,
+                    "persistent_kernel_phase_cycles_per_step": phase_cycles,
+                    "note": "rank 0; phase time from clock64 inside the persistent kernel (no kernel boundary to put "
+                            "CUDA events on)"}
 
     # ---- same kernel at saturation: a quarter of every population spikes in one step ----
     roofline_sat = None
-    if not args.no_saturated:
+    if not args.no_saturated and world == 1:
         rng = np.random.default_rng(99)
         sat_events = 0
         out_deg = {}

@@ -51,7 +51,8 @@ class NeuronGroupDesc(C.Structure):
                 ("egp", C.c_void_p), ("spk_cnt", C.c_void_p), ("spk", C.c_void_p),
                 ("spike_times", C.c_void_p), ("record_spk", C.c_void_p),
                 ("psm", Psm * MAX_PSM), ("cs", CurrentSourceDesc * MAX_CS),
-                ("spk_slot_stride", C.c_uint32), ("reserved", C.c_uint32)]
+                ("spk_slot_stride", C.c_uint32), ("reserved", C.c_uint32), ("spk_tag", C.c_void_p),
+                ("spk_wire", C.c_void_p)]
 
 
 class SynapseGroupDesc(C.Structure):
@@ -71,7 +72,8 @@ class SynapseGroupDesc(C.Structure):
                 ("rng_stream", C.c_uint32), ("reserved", C.c_uint32),
                 ("proc_connect_params", C.c_float * 4), ("proc_weight_params", C.c_float * 4),
                 ("src_sections", C.c_uint32), ("src_spk_slot_stride", C.c_uint32),
-                ("src_cnt_section_stride", C.c_uint64), ("src_spk_section_stride", C.c_uint64)]
+                ("src_cnt_section_stride", C.c_uint64), ("src_spk_section_stride", C.c_uint64),
+                ("src_spk_tag", C.c_void_p), ("src_spk_wire", C.c_void_p)]
 
 
 class CustomUpdateDesc(C.Structure):
@@ -101,7 +103,7 @@ _PROTOTYPES = {
     "b200_exchange_alloc": [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)],
     "b200_exchange_get_handle": [C.c_void_p, C.c_void_p],
     "b200_exchange_open_peer": [C.c_void_p, C.c_uint32, C.c_void_p],
-    "b200_exchange_configure": [C.c_void_p, C.c_uint32, C.c_uint32, C.c_size_t],
+    "b200_exchange_configure": [C.c_void_p, C.c_uint32, C.c_uint32],
     "b200_push_neuron_update_group": [C.c_void_p, C.c_uint32, C.POINTER(NeuronGroupDesc)],
     "b200_push_synapse_group": [C.c_void_p, C.c_uint32, C.POINTER(SynapseGroupDesc)],
     "b200_push_custom_update": [C.c_void_p, C.c_char_p, C.c_uint32, C.POINTER(CustomUpdateDesc)],

@@ -54,6 +54,8 @@ struct FusedSource
     unsigned int item_begin;
     unsigned int item_count;
     unsigned int pad;
+    const unsigned long long *spk_tag;   // sharded models: (step << 32 | count) per slot, else NULL
+    const unsigned long long *spk_wire;  // sharded models: (step << 32 | id) lists, else NULL
 };
 
 struct FusedLaunch
@@ -77,7 +79,6 @@ struct FusedLaunch
     unsigned int world;
     unsigned char *arena;                // this process's exchange arena
     unsigned char *const *peer_table;    // device table [B200_MAX_RANKS]: the same arena of every peer, mapped here
-    unsigned long long *flags;           // in the local arena: flags[r] = steps whose spikes rank r has delivered
 };
 
 constexpr unsigned long long EXCHANGE_SPIN_LIMIT = 1ull << 23;
@@ -90,9 +91,30 @@ __device__ __forceinline__ unsigned long long loadAcquireSys(const unsigned long
     return v;
 }
 
-__device__ __forceinline__ void storeReleaseSys(unsigned long long *p, unsigned long long v)
+__device__ __forceinline__ unsigned long long loadRelaxedSys(const unsigned long long *p)
 {
-    asm volatile("st.release.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+    unsigned long long v;
+    asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+    return v;
+}
+
+__device__ __forceinline__ void storeRelaxedSys(unsigned long long *p, unsigned long long v)
+{
+    asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(p), "l"(v) : "memory");
+}
+
+// Poll a word written by another process into this process's memory until its
+// high half is the step we expect.  Bounded; returns the low half (0 on time-out).
+__device__ __forceinline__ unsigned int awaitWord(const unsigned long long *p, unsigned long long expected, StepState *state)
+{
+    unsigned long long w = 0, polls = 0;
+    while(((w = loadRelaxedSys(p)) >> 32) != expected) {
+        if(++polls > EXCHANGE_SPIN_LIMIT) {
+            atomicOr(&state->error, ERR_EXCHANGE_TIMEOUT);
+            return 0u;
+        }
+    }
+    return (unsigned int)w;
 }
 
 __device__ __forceinline__ unsigned long long loadAcquire(const unsigned long long *p)
@@ -167,6 +189,14 @@ fusedStepKernel(FusedLaunch L)
     __shared__ unsigned int headCnt[32], headSlot[32], headIds[32][FUSED_PREFETCH_IDS];
     __shared__ unsigned char *peerArena[B200_MAX_RANKS];
     if(threadIdx.x < B200_MAX_RANKS) peerArena[threadIdx.x] = L.peer_table ? L.peer_table[threadIdx.x] : nullptr;
+    __shared__ ExchangeCtx exchange;
+    if(threadIdx.x == 0) {
+        exchange.world = L.world;
+        exchange.rank = L.rank;
+        exchange.arena = L.arena;
+        exchange.peers = peerArena;
+    }
+    const ExchangeCtx *xp = (L.world > 1) ? &exchange : nullptr;
     if(L.stage_in_smem) {
         unsigned char *p = fusedSmem;
         const size_t nb = sizeof(b200_neuron_group) * L.neuron.num_groups;
@@ -231,24 +261,6 @@ fusedStepKernel(FusedLaunch L)
     for(unsigned long long step = 0; step < L.num_steps; step++) {
         if(prof) c0 = clock64();
 
-        // ---------------- spikes of the other processes must have landed -----------------
-        // Each peer wrote its lists of the previous step into THIS process's arena and
-        // then raised its flag; only local memory is polled and read.  Bounded wait.
-        if(L.world > 1) {
-            if(threadIdx.x < L.world && threadIdx.x != L.rank) {
-                const unsigned long long need = done0 + step;
-                unsigned long long polls = 0;
-                while(loadAcquireSys(&L.flags[threadIdx.x]) < need) {
-                    if(++polls > EXCHANGE_SPIN_LIMIT) {
-                        atomicOr(&state->error, ERR_EXCHANGE_TIMEOUT);
-                        break;
-                    }
-                }
-            }
-            __syncthreads();
-            if(__ldcg(&state->error) & ERR_EXCHANGE_TIMEOUT) return;
-        }
-
         // ---------------- phase A: presynaptic update ------------------------------
         for(unsigned int base = 0; base < L.num_sources; base += 32u) {
             // ONE warp per CTA fetches every source's spike count together with its
@@ -266,10 +278,28 @@ fusedStepKernel(FusedLaunch L)
                     // all loads into registers first: a shared-memory store between two
                     // loads through generic pointers would serialise them
                     unsigned int ids[FUSED_PREFETCH_IDS];
-                    cnt = __ldcg(&src.spk_cnt[rslot]);
-                    #pragma unroll
-                    for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
-                        ids[j] = (j < src.num_src) ? __ldcg(&list[j]) : 0u;
+                    if(src.spk_tag) {
+                        // Sharded model: count and ids are 64-bit words the list's owner wrote
+                        // into THIS process's memory, each carrying the step it belongs to.
+                        // Poll (bounded) until the words of the step we need are there.
+                        const long long expected = (long long)(done0 + step) - (long long)src.delay;
+                        #pragma unroll
+                        for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) ids[j] = 0u;
+                        if(expected > 0) {
+                            cnt = awaitWord(&src.spk_tag[rslot], (unsigned long long)expected, state);
+                            const unsigned long long *wire = src.spk_wire + (unsigned long long)rslot * src.num_src;
+                            #pragma unroll
+                            for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
+                                if(j < cnt) ids[j] = awaitWord(&wire[j], (unsigned long long)expected, state);
+                            }
+                        }
+                    }
+                    else {
+                        cnt = __ldcg(&src.spk_cnt[rslot]);
+                        #pragma unroll
+                        for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
+                            ids[j] = (j < src.num_src) ? __ldcg(&list[j]) : 0u;
+                        }
                     }
                     #pragma unroll
                     for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) headIds[lane][j] = ids[j];
@@ -278,6 +308,7 @@ fusedStepKernel(FusedLaunch L)
                 headSlot[lane] = rslot;
             }
             __syncthreads();
+            if(L.world > 1 && (__ldcg(&state->error) & ERR_EXCHANGE_TIMEOUT)) return;
             if(prof && L.cta_cycles) L.cta_cycles[4ull * gridDim.x + blockIdx.x] += (unsigned long long)(clock64() - c0);
             const unsigned int cnt = headCnt[lane];
             const unsigned int per = (base + lane < L.num_sources) ? L.sources[base + lane].item_count : 0u;
@@ -297,9 +328,18 @@ fusedStepKernel(FusedLaunch L)
                 const unsigned int s = rel / ownPer;
                 const unsigned int c = rel - s * ownPer;
                 const FusedSource &src = L.sources[base + owner];
-                const unsigned int pre = (s < FUSED_PREFETCH_IDS)
-                    ? headIds[owner][s]
-                    : __ldcg(&src.spk[(unsigned long long)headSlot[owner] * src.num_src + s]);
+                unsigned int pre;
+                if(s < FUSED_PREFETCH_IDS) {
+                    pre = headIds[owner][s];
+                }
+                else if(src.spk_wire) {
+                    const long long expected = (long long)(done0 + step) - (long long)src.delay;
+                    pre = awaitWord(&src.spk_wire[(unsigned long long)headSlot[owner] * src.num_src + s],
+                                    (unsigned long long)expected, state);
+                }
+                else {
+                    pre = __ldcg(&src.spk[(unsigned long long)headSlot[owner] * src.num_src + s]);
+                }
                 const uint2 item = L.items[src.item_begin + c];
                 const b200_synapse_group &g = L.sgroups[item.x];
                 if(pre < g.num_src) {
@@ -319,6 +359,7 @@ fusedStepKernel(FusedLaunch L)
             if(base + 32u < L.num_sources) __syncthreads();     // the header arrays are reused by the next pass
         }
         if(prof) c1 = clock64();
+        if(L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 1;    // read after the barrier's __syncthreads
         gridArrive(L.barrier, epoch);
         // in the shadow of the barrier: this step's random draws
         unsigned int csCount[NCS > 0 ? NCS : 1] = {0};
@@ -347,14 +388,14 @@ fusedStepKernel(FusedLaunch L)
                         if(p < g.num_psm && !g.psm[p].max_den_delay) g.psm[p].out_post[myIndex] = regs.lin[p];
                     }
                 }
-                neuronEmit<true>(L.neuron, g, 0u, myLocal, spiked, k, t0 + step, t);
+                neuronEmit<true>(L.neuron, g, 0u, myLocal, spiked, k, t0 + step, t, xp);
             }
         }
         else {
             for(unsigned int slot = gthread; slot < totalSlots; slot += totalThreads) {
                 const unsigned int gi = findGroup(L.slot_start, numGroups, slot);
                 const b200_neuron_group &g = L.neuron.groups[gi];
-                neuronStep<true, NPSM, NCS>(L.neuron, g, 0u, slot - L.slot_start[gi], k, t0 + step);
+                neuronStep<true, NPSM, NCS>(L.neuron, g, 0u, slot - L.slot_start[gi], k, t0 + step, xp);
             }
         }
         // spike-queue update for the next step (neuronUpdateGroupMerged.cc:947-975)
@@ -366,35 +407,20 @@ fusedStepKernel(FusedLaunch L)
         gridArrive(L.barrier, epoch);
         if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
 
-        // ---------------- deliver this step's spikes to the other processes ----------------
-        // The local lists are final (barrier above).  One warp per peer copies every
-        // population's list into the peer's arena at the same offset with plain peer
-        // stores, fences, and raises this process's flag there.
-        if(L.world > 1 && blockIdx.x == 0) {
-            const unsigned int peer = threadIdx.x >> 5;
-            if(peer < L.world && peer != L.rank) {
-                for(unsigned int gi = 0; gi < numGroups; gi++) {
-                    const b200_neuron_group &g = L.neuron.groups[gi];
-                    const unsigned int wslot = ringSlot(k + 1, g.num_delay_slots);
-                    const unsigned int stride = g.spk_slot_stride ? g.spk_slot_stride : g.num_neurons;
-                    const unsigned int *cntLocal = &g.spk_cnt[wslot];
-                    const unsigned int *listLocal = g.spk + (unsigned long long)wslot * stride;
-                    unsigned int *cntRemote = reinterpret_cast<unsigned int*>(
-                        peerArena[peer] + (reinterpret_cast<const unsigned char*>(cntLocal) - L.arena));
-                    unsigned int *listRemote = reinterpret_cast<unsigned int*>(
-                        peerArena[peer] + (reinterpret_cast<const unsigned char*>(listLocal) - L.arena));
-                    const unsigned int cnt = __ldcg(cntLocal);
-                    for(unsigned int i = lane; i < cnt; i += 32u) listRemote[i] = __ldcg(&listLocal[i]);
-                    if(lane == 0) *cntRemote = cnt;
-                }
-                __syncwarp();
-                if(lane == 0) {
-                    __threadfence_system();
-                    unsigned long long *flagRemote = reinterpret_cast<unsigned long long*>(
-                        peerArena[peer] + (reinterpret_cast<unsigned char*>(L.flags) - L.arena)) + L.rank;
-                    storeReleaseSys(flagRemote, done0 + step + 1);
-                }
+        // ---------------- publish this step's spike counts to every process ---------------------
+        // The ids already sit in every arena (stored and fenced as they were emitted, before
+        // the barrier above).  One 64-bit store per (process, population) now says
+        // "step s: n spikes"; it is what the reader polls.
+        if(L.world > 1 && blockIdx.x == 0 && threadIdx.x < L.world * numGroups) {
+            const unsigned int peer = threadIdx.x / numGroups, gi = threadIdx.x - peer * numGroups;
+            const b200_neuron_group &g = L.neuron.groups[gi];
+            const unsigned int wslot = ringSlot(k + 1, g.num_delay_slots);
+            const unsigned long long tag = ((done0 + step + 1) << 32) | (unsigned long long)__ldcg(&g.spk_cnt[wslot]);
+            unsigned long long *cell = reinterpret_cast<unsigned long long*>(&g.spk_tag[wslot]);
+            if(peer != L.rank) {
+                cell = reinterpret_cast<unsigned long long*>(peerArena[peer] + (reinterpret_cast<unsigned char*>(cell) - L.arena));
             }
+            storeRelaxedSys(cell, tag);
         }
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {

@@ -27,6 +27,17 @@ namespace b200
 {
 constexpr int NEURON_BLOCK = 128;
 
+// Peers of a sharded model as the neuron update sees them: every spike id is also
+// stored into each peer's exchange arena, at the offset it has in this process's.
+struct ExchangeCtx
+{
+    unsigned int world;
+    unsigned int rank;
+    unsigned char *arena;
+    unsigned char *const *peers;        // [B200_MAX_RANKS], shared or global memory
+    unsigned long long tag;             // step number the words of this step carry in their high half
+};
+
 struct NeuronLaunch
 {
     const b200_neuron_group *groups;
@@ -273,7 +284,7 @@ __device__ __forceinline__ bool neuronCompute(const NeuronLaunch &L, const b200_
 template<bool COHERENT>
 __device__ __forceinline__ void neuronEmit(const NeuronLaunch &L, const b200_neuron_group &g, unsigned int b,
                                            unsigned int local, bool spiked, unsigned int k,
-                                           unsigned long long timestep, float t)
+                                           unsigned long long timestep, float t, const ExchangeCtx *x = nullptr)
 {
     const unsigned int N = g.num_neurons;
     const unsigned int i = g.first_neuron + local;
@@ -293,7 +304,21 @@ __device__ __forceinline__ void neuronEmit(const NeuronLaunch &L, const b200_neu
         if(spiked) {
             const unsigned int pos = base + __popc(ballot & ((1u << lane) - 1u));
             if(pos < listStride) {
-                g.spk[((unsigned long long)b * slots + wslot) * listStride + pos] = i;
+                unsigned int *cell = &g.spk[((unsigned long long)b * slots + wslot) * listStride + pos];
+                *cell = i;
+                if(x) {
+                    // the travelling copy: (step << 32 | id) into the same cell of every
+                    // process's arena, this one included.  Each word validates itself,
+                    // so the stores need no ordering and nothing waits for them.
+                    unsigned long long *wire = reinterpret_cast<unsigned long long*>(g.spk_wire) +
+                                               ((unsigned long long)b * slots + wslot) * listStride + pos;
+                    const unsigned long long word = (x->tag << 32) | (unsigned long long)i;
+                    for(unsigned int p = 0; p < x->world; p++) {
+                        unsigned long long *dst = (p == x->rank) ? wire
+                            : reinterpret_cast<unsigned long long*>(x->peers[p] + (reinterpret_cast<unsigned char*>(wire) - x->arena));
+                        asm volatile("st.relaxed.sys.global.u64 [%0], %1;" :: "l"(dst), "l"(word) : "memory");
+                    }
+                }
             }
             else {
                 atomicOr(&L.state->error, ERR_SPIKE_OVERFLOW);
@@ -322,7 +347,8 @@ __device__ __forceinline__ void neuronEmit(const NeuronLaunch &L, const b200_neu
 // the ballot).  `k` is the number of completed steps, `timestep` the model step.
 template<bool COHERENT, int NPSM, int NCS>
 __device__ __forceinline__ void neuronStep(const NeuronLaunch &L, const b200_neuron_group &g, unsigned int b,
-                                           unsigned int local, unsigned int k, unsigned long long timestep)
+                                           unsigned int local, unsigned int k, unsigned long long timestep,
+                                           const ExchangeCtx *x = nullptr)
 {
     const unsigned int i = g.first_neuron + local;
     const float t = B200_FMUL((float)timestep, L.dt);
@@ -338,7 +364,7 @@ __device__ __forceinline__ void neuronStep(const NeuronLaunch &L, const b200_neu
         spiked = neuronCompute(L, g, b, i, timestep, t, r, front, csCount);
         storeNeuron(g, bi, r, false);
     }
-    neuronEmit<COHERENT>(L, g, b, local, spiked, k, timestep, t);
+    neuronEmit<COHERENT>(L, g, b, local, spiked, k, timestep, t, x);
 }
 
 template<int NPSM, int NCS>

@@ -486,6 +486,10 @@ int prepare(b200_runner *r)
                     src.num_src = g.src_spk_slot_stride ? g.src_spk_slot_stride : g.num_src;   // list capacity
                     src.slots = g.src_delay_slots;
                     src.delay = g.axonal_delay;
+                    src.spk_tag = g.src_spk_tag
+                        ? reinterpret_cast<const unsigned long long*>(g.src_spk_tag + sec * g.src_cnt_section_stride) : nullptr;
+                    src.spk_wire = g.src_spk_wire
+                        ? reinterpret_cast<const unsigned long long*>(g.src_spk_wire + sec * g.src_spk_section_stride) : nullptr;
                     sources.push_back(src);
                     perSource.emplace_back();
                 }
@@ -644,14 +648,16 @@ int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long 
     L.world = r->world;
     L.arena = r->arena;
     L.peer_table = r->peerTable;
-    L.flags = r->arena ? reinterpret_cast<unsigned long long*>(r->arena + r->flagsOffset) : nullptr;
     if(r->sharded()) {
         for(unsigned int p = 0; p < r->world; p++) {
             if(p != r->rank && !r->peerArena[p]) return fail(B200_ERR_STATE, "exchange arena of rank %u has not been opened", p);
         }
         for(const auto &g : r->neuronGroups) {
             const unsigned char *c = reinterpret_cast<const unsigned char*>(g.spk_cnt), *s = reinterpret_cast<const unsigned char*>(g.spk);
-            if(c < r->arena || c >= r->arena + r->arenaBytes || s < r->arena || s >= r->arena + r->arenaBytes) {
+            const unsigned char *t = reinterpret_cast<const unsigned char*>(g.spk_tag);
+            const unsigned char *w = reinterpret_cast<const unsigned char*>(g.spk_wire);
+            if(c < r->arena || c >= r->arena + r->arenaBytes || s < r->arena || s >= r->arena + r->arenaBytes ||
+               t < r->arena || t >= r->arena + r->arenaBytes || w < r->arena || w >= r->arena + r->arenaBytes) {
                 return fail(B200_ERR_INVALID, "spike arrays of a sharded model must live in the exchange arena");
             }
         }
@@ -916,15 +922,12 @@ int b200_exchange_open_peer(b200_runner *r, uint32_t peer_rank, const void *hand
     return B200_OK;
 }
 
-int b200_exchange_configure(b200_runner *r, uint32_t rank, uint32_t world, size_t flags_offset)
+int b200_exchange_configure(b200_runner *r, uint32_t rank, uint32_t world)
 {
     if(!r || world == 0 || world > B200_MAX_RANKS || rank >= world) return fail(B200_ERR_INVALID, "bad rank/world");
-    if(world > 1 && (!r->arena || flags_offset + sizeof(unsigned long long) * B200_MAX_RANKS > r->arenaBytes || (flags_offset & 7))) {
-        return fail(B200_ERR_INVALID, "flags do not fit the exchange arena");
-    }
+    if(world > 1 && !r->arena) return fail(B200_ERR_STATE, "no exchange arena");
     r->rank = rank;
     r->world = world;
-    r->flagsOffset = flags_offset;
     r->dirty = true;
     return B200_OK;
 }

@@ -148,13 +148,15 @@ class Plan:
             p.shard_bounds = bounds
             p.list_capacity = p.n if world == 1 else max(32, max(bounds[r + 1] - bounds[r] for r in range(world)))
         if world > 1:
-            offset = 256                                 # flags first
+            offset = 256
             layout = {}
             for p in net.pops:
-                for name, count in ((f"{p.name}.spk_cnt", world * B * p.runtime_slots),
-                                    (f"{p.name}.spk", world * B * p.runtime_slots * p.list_capacity)):
-                    layout[name] = (offset, count * 4)
-                    offset = (offset + count * 4 + 255) & ~255
+                for name, nbytes in ((f"{p.name}.spk_cnt", world * B * p.runtime_slots * 4),
+                                     (f"{p.name}.spk_tag", world * B * p.runtime_slots * 8),
+                                     (f"{p.name}.spk_wire", world * B * p.runtime_slots * p.list_capacity * 8),
+                                     (f"{p.name}.spk", world * B * p.runtime_slots * p.list_capacity * 4)):
+                    layout[name] = (offset, nbytes)
+                    offset = (offset + nbytes + 255) & ~255
             self.exchange = self.factory.alloc_exchange(offset)
             self.factory.memset(self.exchange, 0, offset)
             self._exchange_layout = layout
@@ -178,10 +180,12 @@ class Plan:
                 self._new(f"{p.name}.spk_cnt", np.uint32, (B, slots))
                 self._new(f"{p.name}.spk", np.uint32, (B, slots, p.n))
             else:
-                for name, shape in ((f"{p.name}.spk_cnt", (world, B, slots)),
-                                    (f"{p.name}.spk", (world, B, slots, p.list_capacity))):
+                for name, shape, dtype in ((f"{p.name}.spk_cnt", (world, B, slots), np.uint32),
+                                           (f"{p.name}.spk_tag", (world, B, slots), np.uint64),
+                                           (f"{p.name}.spk_wire", (world, B, slots, p.list_capacity), np.uint64),
+                                           (f"{p.name}.spk", (world, B, slots, p.list_capacity), np.uint32)):
                     off, nbytes = self._exchange_layout[name]
-                    self.arrays[name] = PlannedArray(name, _View(self.exchange, off, nbytes), np.dtype(np.uint32), shape)
+                    self.arrays[name] = PlannedArray(name, _View(self.exchange, off, nbytes), np.dtype(dtype), shape)
             if p.spike_time_required:
                 self._new(f"{p.name}.sT", np.float32, (B, slots, p.n), TIME_MIN)
             if p.record and self.num_recording_timesteps:
@@ -300,6 +304,9 @@ class Plan:
             rank = self.shard[0]
             d.spk_cnt += rank * net.batch_size * p.runtime_slots * 4
             d.spk += rank * net.batch_size * p.runtime_slots * p.list_capacity * 4
+            d.spk_tag = self._ptr(f"{p.name}.spk_tag") + rank * net.batch_size * p.runtime_slots * 8
+            d.spk_wire = (self._ptr(f"{p.name}.spk_wire") +
+                          rank * net.batch_size * p.runtime_slots * p.list_capacity * 8)
         d.spike_times = self._ptr(f"{p.name}.sT")
         d.record_spk = self._ptr(f"{p.name}.record")
         k = 0
@@ -371,6 +378,8 @@ class Plan:
             d.src_spk_slot_stride = src.list_capacity
             d.src_cnt_section_stride = net.batch_size * src.runtime_slots
             d.src_spk_section_stride = net.batch_size * src.runtime_slots * src.list_capacity
+            d.src_spk_tag = self._ptr(f"{src.name}.spk_tag")
+            d.src_spk_wire = self._ptr(f"{src.name}.spk_wire")
         d.trg_spk_cnt, d.trg_spk = self._ptr(f"{trg.name}.spk_cnt"), self._ptr(f"{trg.name}.spk")
         d.src_spike_times = self._ptr(f"{src.name}.sT")
         d.trg_spike_times = self._ptr(f"{trg.name}.sT")

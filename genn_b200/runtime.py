@@ -139,7 +139,7 @@ class Runtime:
         for peer, h in enumerate(handles):
             if peer != rank:
                 check(self.lib.b200_exchange_open_peer(self.handle, peer, C.create_string_buffer(h, 64)))
-        check(self.lib.b200_exchange_configure(self.handle, rank, world, self.plan.flags_offset))
+        check(self.lib.b200_exchange_configure(self.handle, rank, world))
 
     # -- initialisation kernels -------------------------------------------------
     def _run_init_tasks(self):
@@ -314,8 +314,16 @@ class Runtime:
         cnt, spk = self.array(f"{name}.spk_cnt"), self.array(f"{name}.spk")
         if cnt.ndim == 2:
             return spk[batch, slot, :int(cnt[batch, slot])].copy()
-        # sharded: one section per process (peers' sections hold what they delivered)
-        return np.concatenate([spk[s, batch, slot, :int(cnt[s, batch, slot])] for s in range(cnt.shape[0])])
+        # sharded: one section per process; a section's count travels in the low half
+        # of its (step, count) word
+        tag, wire = self.array(f"{name}.spk_tag"), self.array(f"{name}.spk_wire")
+        out = []
+        for s in range(tag.shape[0]):
+            n = int(tag[s, batch, slot] & 0xFFFFFFFF)
+            words = wire[s, batch, slot, :n]
+            assert np.all((words >> 32) == (tag[s, batch, slot] >> 32)), "spike words of another step in the list"
+            out.append((words & 0xFFFFFFFF).astype(np.uint32))
+        return np.concatenate(out)
 
     def pinned_empty(self, shape, dtype) -> np.ndarray:
         """Page-locked host array (cudaHostAlloc) owned by this runtime."""

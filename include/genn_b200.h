@@ -153,6 +153,9 @@ typedef struct b200_neuron_group {
     uint32_t spk_slot_stride;  /* elements between two slots of `spk`; 0 = num_neurons.  A process that
                                   updates a slice of the group keeps a list sized for the slice. */
     uint32_t reserved;
+    uint64_t *spk_tag;         /* sharded models: [slots] (step << 32 | count) of this process's section; else NULL */
+    uint64_t *spk_wire;        /* sharded models: [slots][spk_slot_stride] (step << 32 | neuron id), the copy of the
+                                  spike list that travels between processes; else NULL */
 } b200_neuron_group;
 
 /* One element of the merged presynaptic-update group array and, when the
@@ -201,6 +204,8 @@ typedef struct b200_synapse_group {
     uint32_t src_spk_slot_stride;      /* elements between two slots of one list; 0 = num_src */
     uint64_t src_cnt_section_stride;
     uint64_t src_spk_section_stride;
+    const uint64_t *src_spk_tag;       /* sharded: tagged counts, laid out like src_spk_cnt; else NULL */
+    const uint64_t *src_spk_wire;      /* sharded: tagged ids, laid out like src_spk; else NULL */
 } b200_synapse_group;
 
 /* Batch-reduce custom update (backendSIMT.cc:888-927, 1109-1147):
@@ -239,14 +244,16 @@ int  b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes
  *      sharding: SURVEY of backendCUDAHIP.cc shows NCCL all-reduce of custom-update results only).
  * A model sharded by postsynaptic neuron over several GPUs of one node exchanges each step's spike
  * lists.  Every process allocates ONE exchange arena, places its spike arrays (all sections) and the
- * arrival flags in it at identical offsets, shares the arena's IPC handle with its peers and opens
- * theirs.  The persistent kernel then writes its own lists straight into every peer's arena with
- * peer stores and raises a flag; a peer reads only its own memory. ------------------------------ */
+ * tagged counts in it at identical offsets, shares the arena's IPC handle with its peers and opens
+ * theirs.  The persistent kernel then writes each spike straight into every peer's arena with peer
+ * stores as it is emitted and, once the step's list is final, one count word per population.  Every
+ * word on the wire is 64 bits, (step << 32 | payload): a reader polls its OWN memory until the word
+ * carries the step it expects, so no ordering between the stores (and no system-scope fence, 1.5 us
+ * on this hardware) is needed. -------------------------------------------------------------------- */
 int  b200_exchange_alloc(b200_runner *r, size_t bytes, void **device_ptr);
 int  b200_exchange_get_handle(b200_runner *r, void *handle_64_bytes);
 int  b200_exchange_open_peer(b200_runner *r, uint32_t peer_rank, const void *handle_64_bytes);
-/* flags_offset: byte offset in the arena of B200_MAX_RANKS uint64 arrival flags (zero-initialised) */
-int  b200_exchange_configure(b200_runner *r, uint32_t rank, uint32_t world, size_t flags_offset);
+int  b200_exchange_configure(b200_runner *r, uint32_t rank, uint32_t world);
 
 /* ---- merged-group registration: pushMerged<Kind>Group<i>ToDevice
  *      (backendCUDAHIP.h:206-238, runtime.h:573-669) -------------------------- */

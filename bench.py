@@ -393,6 +393,8 @@ def main():
                                    f"published in-degrees, SPARSE with dendritic delays, PoissonExp background, "
                                    f"dt=0.1 ms; one bench step = {block} time steps (0.1 s biological)",
                        "parallelism": f"postsynaptic sharding over {world} GPU(s)" if world > 1 else "single GPU",
+                       "schedule": ("persistent kernel, spikes delivered one step late (every dendritic delay >= 1 step): "
+                                    "one grid barrier per step") if rt.lagging else "persistent kernel, two grid barriers per step",
                        "l2": "working set (2.5 GB of synapses) exceeds L2; no flush needed",
                        "spikes_per_s_biological": spikes / sim_seconds,
                        "mean_rates_hz": rates, "bytes_per_event": bpe},

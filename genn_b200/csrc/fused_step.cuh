@@ -25,6 +25,19 @@
 // is a monotonic 64-bit arrival counter in global memory; every wait is bounded
 // and a time-out sets an error flag and ends the kernel on all CTAs.
 //
+// One-step lag.  When EVERY synapse of every group has a dendritic delay of at
+// least one step (the host scans the delay arrays), a spike emitted in step s
+// may be delivered in the presynaptic phase of step s+2 instead of s+1, into
+// the ring slot one position nearer: the value lands in the same slot before
+// the neuron update that reads it, so the result is unchanged.  The spike lists
+// a presynaptic phase reads were then completed before the PREVIOUS barrier, and
+// the ring slots it writes are never the one a lagging CTA still reads, so the
+// second barrier of the step disappears; in a sharded model the spike words
+// have a whole step to cross NVLink.  The first pass of a launch has nothing to
+// deliver (the launch before drained it) and one delivery pass runs after the
+// last neuron update, so memory between launches is exactly what the two-barrier
+// schedule leaves.
+//
 // Data written by other SMs between barriers (postsynaptic input, spike lists)
 // is read with ld.global.cg so a stale L1 line can never be used.
 #pragma once
@@ -37,6 +50,7 @@ namespace b200
 {
 constexpr int FUSED_BLOCK = 768;          // one CTA per SM, 85 registers per thread
 constexpr unsigned int FUSED_CHUNK = 32 * PRE_VEC;          // synapses per warp item
+constexpr unsigned int FUSED_MAX_SOURCES = 256;             // (population, process, delay) spike sources per model
 constexpr unsigned int FUSED_PREFETCH_IDS = 8;              // spike ids fetched together with each count
 constexpr unsigned int ERR_BARRIER_TIMEOUT = 8u;
 constexpr unsigned long long BARRIER_SPIN_LIMIT = 1ull << 24; // polls (tens of ms) before giving up
@@ -79,6 +93,7 @@ struct FusedLaunch
     unsigned int world;
     unsigned char *arena;                // this process's exchange arena
     unsigned char *const *peer_table;    // device table [B200_MAX_RANKS]: the same arena of every peer, mapped here
+    unsigned int lag;                    // 1: deliver spikes one step late into the ring slot one nearer (see above)
 };
 
 constexpr unsigned long long EXCHANGE_SPIN_LIMIT = 1ull << 23;
@@ -159,11 +174,11 @@ __device__ __forceinline__ bool gridWait(const unsigned long long *barrier, cons
 
 template<typename IndT>
 __device__ __forceinline__ void fusedChunk(const b200_synapse_group &g, unsigned int pre, unsigned int chunk,
-                                           unsigned int k, StepState *state)
+                                           unsigned int front, unsigned int minDelay, StepState *state)
 {
     const unsigned int D = g.max_den_delay;
     float *target = D ? g.den_delay : g.out_post;
-    sparseQuad<IndT>(g, pre, chunk * 32u + (threadIdx.x & 31u), target, D ? ringSlot(k + 1, D) : 0u, state);
+    sparseQuad<IndT>(g, pre, chunk * 32u + (threadIdx.x & 31u), target, D ? ringSlot(front, D) : 0u, state, minDelay);
 }
 
 // Copy `bytes` (a multiple of 4) from global to shared memory with the whole CTA.
@@ -186,7 +201,7 @@ fusedStepKernel(FusedLaunch L)
 {
     extern __shared__ __align__(16) unsigned char fusedSmem[];
     __shared__ bool barrierOk;
-    __shared__ unsigned int headCnt[32], headSlot[32], headIds[32][FUSED_PREFETCH_IDS];
+    __shared__ unsigned int headCnt[FUSED_MAX_SOURCES], headSlot[FUSED_MAX_SOURCES], headIds[FUSED_MAX_SOURCES][FUSED_PREFETCH_IDS];
     __shared__ unsigned char *peerArena[B200_MAX_RANKS];
     if(threadIdx.x < B200_MAX_RANKS) peerArena[threadIdx.x] = L.peer_table ? L.peer_table[threadIdx.x] : nullptr;
     __shared__ ExchangeCtx exchange;
@@ -221,6 +236,7 @@ fusedStepKernel(FusedLaunch L)
         __syncthreads();
     }
     const unsigned int lane = threadIdx.x & 31u;
+    const unsigned int warp = threadIdx.x >> 5;
     const unsigned int warpsPerBlock = blockDim.x >> 5;
     // work items go round-robin over CTAs first: a handful of items per step must
     // spread over every SM, because one SM retires scattered reductions slowly
@@ -258,59 +274,91 @@ fusedStepKernel(FusedLaunch L)
 
     const bool prof = L.profile && threadIdx.x == 0;
     long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
-    for(unsigned long long step = 0; step < L.num_steps; step++) {
+    const unsigned int lag = L.lag;
+    // lists: one 64-bit store per (process, population) says "step s: n spikes"; it is
+    // what the readers poll.  The ids already sit in every arena (stored as they were
+    // emitted).  Called by the whole grid after a barrier that follows the emission.
+    auto publishCounts = [&](unsigned int writtenAt, unsigned long long tagStep) {
+        if(L.world > 1 && blockIdx.x == 0 && threadIdx.x < L.world * numGroups) {
+            const unsigned int peer = threadIdx.x / numGroups, gi = threadIdx.x - peer * numGroups;
+            const b200_neuron_group &g = L.neuron.groups[gi];
+            const unsigned int wslot = ringSlot(writtenAt, g.num_delay_slots);
+            const unsigned long long tag = (tagStep << 32) | (unsigned long long)__ldcg(&g.spk_cnt[wslot]);
+            unsigned long long *cell = reinterpret_cast<unsigned long long*>(&g.spk_tag[wslot]);
+            if(peer != L.rank) {
+                cell = reinterpret_cast<unsigned long long*>(peerArena[peer] + (reinterpret_cast<unsigned char*>(cell) - L.arena));
+            }
+            storeRelaxedSys(cell, tag);
+        }
+    };
+    // with the one-step lag a last pass delivers what the final neuron update left pending
+    const unsigned long long passes = L.num_steps + lag;
+    for(unsigned long long step = 0; step < passes; step++) {
         if(prof) c0 = clock64();
+        const bool drain = (step == L.num_steps);
+        // every CTA has to finish the last neuron update before its counts go out
+        if(drain && L.world > 1) gridArrive(L.barrier, epoch);
+        if(!lag || step > 0) {
 
-        // ---------------- phase A: presynaptic update ------------------------------
-        for(unsigned int base = 0; base < L.num_sources; base += 32u) {
-            // ONE warp per CTA fetches every source's spike count together with its
-            // first spike ids (fetched before the count is known: entries past the
-            // count are stale but valid memory) and shares them through shared
-            // memory.  If every warp of the grid read these few words itself, the
-            // L2 slices holding them would serialise thousands of requests.
-            if(threadIdx.x < 32u) {
-                const unsigned int si = base + lane;
-                unsigned int cnt = 0, rslot = 0;
-                if(si < L.num_sources) {
-                    const FusedSource &src = L.sources[si];
-                    rslot = ringSlot(k + src.slots - src.delay, src.slots);
-                    const unsigned int *list = src.spk + (unsigned long long)rslot * src.num_src;
-                    // all loads into registers first: a shared-memory store between two
-                    // loads through generic pointers would serialise them
-                    unsigned int ids[FUSED_PREFETCH_IDS];
-                    if(src.spk_tag) {
-                        // Sharded model: count and ids are 64-bit words the list's owner wrote
-                        // into THIS process's memory, each carrying the step it belongs to.
-                        // Poll (bounded) until the words of the step we need are there.
-                        const long long expected = (long long)(done0 + step) - (long long)src.delay;
+        // ---------------- spike headers: counts and first ids of every source -----------------
+        // A few warps of each CTA (one per 32 sources) fetch every source's spike count
+        // together with its first spike ids and share them through shared memory.  If
+        // every warp of the grid read these few words itself, the L2 slices holding them
+        // would serialise thousands of requests.
+        if(warp < (L.num_sources + 31u) / 32u) {
+            const unsigned int si = warp * 32u + lane;
+            unsigned int cnt = 0, rslot = 0;
+            // all loads into registers first: a shared-memory store between two loads
+            // through generic pointers would serialise them
+            unsigned int ids[FUSED_PREFETCH_IDS];
+            #pragma unroll
+            for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) ids[j] = 0u;
+            if(si < L.num_sources) {
+                const FusedSource &src = L.sources[si];
+                rslot = ringSlot(k + src.slots - src.delay - lag, src.slots);
+                if(src.spk_tag) {
+                    // Sharded model: count and ids are 64-bit words the list's owner wrote
+                    // into THIS process's memory, each carrying the step it belongs to.
+                    // Poll (bounded) until the count word of the step we need is there;
+                    // the id words were sent long before it, so they are fetched together
+                    // and only a word that is not there yet is polled for.
+                    const long long expected = (long long)(done0 + step) - (long long)(src.delay + lag);
+                    if(expected > 0) {
+                        cnt = awaitWord(&src.spk_tag[rslot], (unsigned long long)expected, state);
+                        const unsigned long long *wire = src.spk_wire + (unsigned long long)rslot * src.num_src;
+                        unsigned long long words[FUSED_PREFETCH_IDS];
                         #pragma unroll
-                        for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) ids[j] = 0u;
-                        if(expected > 0) {
-                            cnt = awaitWord(&src.spk_tag[rslot], (unsigned long long)expected, state);
-                            const unsigned long long *wire = src.spk_wire + (unsigned long long)rslot * src.num_src;
-                            #pragma unroll
-                            for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
-                                if(j < cnt) ids[j] = awaitWord(&wire[j], (unsigned long long)expected, state);
+                        for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) words[j] = (j < cnt) ? loadRelaxedSys(&wire[j]) : 0ull;
+                        #pragma unroll
+                        for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
+                            if(j < cnt) {
+                                ids[j] = ((words[j] >> 32) == (unsigned long long)expected)
+                                    ? (unsigned int)words[j] : awaitWord(&wire[j], (unsigned long long)expected, state);
                             }
                         }
                     }
-                    else {
-                        cnt = __ldcg(&src.spk_cnt[rslot]);
-                        #pragma unroll
-                        for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
-                            ids[j] = (j < src.num_src) ? __ldcg(&list[j]) : 0u;
-                        }
-                    }
-                    #pragma unroll
-                    for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) headIds[lane][j] = ids[j];
                 }
-                headCnt[lane] = cnt;
-                headSlot[lane] = rslot;
+                else {
+                    // fetched before the count is known: entries past the count are
+                    // stale but valid memory
+                    const unsigned int *list = src.spk + (unsigned long long)rslot * src.num_src;
+                    cnt = __ldcg(&src.spk_cnt[rslot]);
+                    #pragma unroll
+                    for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) ids[j] = (j < src.num_src) ? __ldcg(&list[j]) : 0u;
+                }
+                #pragma unroll
+                for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) headIds[si][j] = ids[j];
+                headCnt[si] = cnt;
+                headSlot[si] = rslot;
             }
-            __syncthreads();
-            if(L.world > 1 && (__ldcg(&state->error) & ERR_EXCHANGE_TIMEOUT)) return;
-            if(prof && L.cta_cycles) L.cta_cycles[4ull * gridDim.x + blockIdx.x] += (unsigned long long)(clock64() - c0);
-            const unsigned int cnt = headCnt[lane];
+        }
+        __syncthreads();
+        if(L.world > 1 && (__ldcg(&state->error) & ERR_EXCHANGE_TIMEOUT)) return;
+        if(prof && L.cta_cycles) L.cta_cycles[4ull * gridDim.x + blockIdx.x] += (unsigned long long)(clock64() - c0);
+
+        // ---------------- phase A: presynaptic update ------------------------------
+        for(unsigned int base = 0; base < L.num_sources; base += 32u) {
+            const unsigned int cnt = (base + lane < L.num_sources) ? headCnt[base + lane] : 0u;
             const unsigned int per = (base + lane < L.num_sources) ? L.sources[base + lane].item_count : 0u;
             unsigned int incl = cnt * per;
             #pragma unroll
@@ -323,30 +371,30 @@ fusedStepKernel(FusedLaunch L)
                 const unsigned int owner = __ffs(__ballot_sync(0xFFFFFFFFu, incl > it)) - 1u;
                 const unsigned int ownIncl = __shfl_sync(0xFFFFFFFFu, incl, owner);
                 const unsigned int ownPer = __shfl_sync(0xFFFFFFFFu, per, owner);
-                const unsigned int ownCnt = headCnt[owner];
+                const unsigned int ownCnt = headCnt[base + owner];
                 const unsigned int rel = it - (ownIncl - ownCnt * ownPer);
                 const unsigned int s = rel / ownPer;
                 const unsigned int c = rel - s * ownPer;
                 const FusedSource &src = L.sources[base + owner];
                 unsigned int pre;
                 if(s < FUSED_PREFETCH_IDS) {
-                    pre = headIds[owner][s];
+                    pre = headIds[base + owner][s];
                 }
                 else if(src.spk_wire) {
-                    const long long expected = (long long)(done0 + step) - (long long)src.delay;
-                    pre = awaitWord(&src.spk_wire[(unsigned long long)headSlot[owner] * src.num_src + s],
+                    const long long expected = (long long)(done0 + step) - (long long)(src.delay + lag);
+                    pre = awaitWord(&src.spk_wire[(unsigned long long)headSlot[base + owner] * src.num_src + s],
                                     (unsigned long long)expected, state);
                 }
                 else {
-                    pre = __ldcg(&src.spk[(unsigned long long)headSlot[owner] * src.num_src + s]);
+                    pre = __ldcg(&src.spk[(unsigned long long)headSlot[base + owner] * src.num_src + s]);
                 }
                 const uint2 item = L.items[src.item_begin + c];
                 const b200_synapse_group &g = L.sgroups[item.x];
                 if(pre < g.num_src) {
                     switch(g.ind_bytes) {
-                    case 1: fusedChunk<uint8_t>(g, pre, item.y, k, state); break;
-                    case 2: fusedChunk<uint16_t>(g, pre, item.y, k, state); break;
-                    default: fusedChunk<uint32_t>(g, pre, item.y, k, state); break;
+                    case 1: fusedChunk<uint8_t>(g, pre, item.y, k + 1u - lag, lag, state); break;
+                    case 2: fusedChunk<uint16_t>(g, pre, item.y, k + 1u - lag, lag, state); break;
+                    default: fusedChunk<uint32_t>(g, pre, item.y, k + 1u - lag, lag, state); break;
                     }
                     if(L.count_events && item.y == 0 && lane == 0) {
                         atomicAdd(&state->synaptic_events, (unsigned long long)__ldg(&g.row_length[pre]));
@@ -356,8 +404,9 @@ fusedStepKernel(FusedLaunch L)
                     atomicOr(&state->error, ERR_IND_RANGE);
                 }
             }
-            if(base + 32u < L.num_sources) __syncthreads();     // the header arrays are reused by the next pass
         }
+        }   // delivery pass
+        if(drain) break;
         if(prof) c1 = clock64();
         if(L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 1;    // read after the barrier's __syncthreads
         gridArrive(L.barrier, epoch);
@@ -367,6 +416,8 @@ fusedStepKernel(FusedLaunch L)
             drawCurrentSources<NCS>(L.neuron, L.neuron.groups[myGroup], 0u, (unsigned int)myIndex, t0 + step, csCount);
         }
         if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
+        // lagging schedule: the lists of the step before are complete now
+        if(lag && step > 0) publishCounts(k, done0 + step);
         if(prof) c2 = clock64();
 
         // ---------------- phase B: neuron update -----------------------------------
@@ -404,23 +455,10 @@ fusedStepKernel(FusedLaunch L)
             o.spk_cnt[ringSlot(k + 2, o.num_delay_slots)] = 0;
         }
         if(prof) c3 = clock64();
-        gridArrive(L.barrier, epoch);
-        if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
-
-        // ---------------- publish this step's spike counts to every process ---------------------
-        // The ids already sit in every arena (stored and fenced as they were emitted, before
-        // the barrier above).  One 64-bit store per (process, population) now says
-        // "step s: n spikes"; it is what the reader polls.
-        if(L.world > 1 && blockIdx.x == 0 && threadIdx.x < L.world * numGroups) {
-            const unsigned int peer = threadIdx.x / numGroups, gi = threadIdx.x - peer * numGroups;
-            const b200_neuron_group &g = L.neuron.groups[gi];
-            const unsigned int wslot = ringSlot(k + 1, g.num_delay_slots);
-            const unsigned long long tag = ((done0 + step + 1) << 32) | (unsigned long long)__ldcg(&g.spk_cnt[wslot]);
-            unsigned long long *cell = reinterpret_cast<unsigned long long*>(&g.spk_tag[wslot]);
-            if(peer != L.rank) {
-                cell = reinterpret_cast<unsigned long long*>(peerArena[peer] + (reinterpret_cast<unsigned char*>(cell) - L.arena));
-            }
-            storeRelaxedSys(cell, tag);
+        if(!lag) {
+            gridArrive(L.barrier, epoch);
+            if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
+            publishCounts(k + 1u, done0 + step + 1);
         }
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {
@@ -439,6 +477,10 @@ fusedStepKernel(FusedLaunch L)
                 mine4[3] += (unsigned long long)(c4 - c3);
             }
         }
+    }
+    if(lag && L.world > 1) {
+        if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
+        publishCounts(k, done0 + L.num_steps);
     }
     if(mine && myActive) storeNeuron(L.neuron.groups[myGroup], myIndex, regs, true);
     if(gthread == 0) {

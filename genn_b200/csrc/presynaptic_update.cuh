@@ -79,7 +79,7 @@ template<> struct IndLoad<uint32_t>
 template<typename IndT>
 __device__ __forceinline__ void sparseQuad(const b200_synapse_group &g, unsigned int pre, unsigned int quad,
                                            float *__restrict__ target, unsigned int denFront,
-                                           StepState *state)
+                                           StepState *state, unsigned int minDelay = 0u)
 {
     // The row length and the row data are fetched TOGETHER (one memory round
     // trip, not two): the quad's address does not depend on the length, and a
@@ -116,7 +116,14 @@ __device__ __forceinline__ void sparseQuad(const b200_synapse_group &g, unsigned
                 continue;
             }
             if(D) {
-                unsigned int slot = denFront + ((dw >> (8 * j)) & 0xFFu);
+                const unsigned int delay = (dw >> (8 * j)) & 0xFFu;
+                // the caller relies on every delay being at least minDelay steps and, if that
+                // is not zero, on none wrapping around the ring
+                if(delay < minDelay || (minDelay && delay >= D)) {
+                    atomicOr(&state->error, ERR_DELAY_RANGE);
+                    continue;
+                }
+                unsigned int slot = denFront + delay;
                 while(slot >= D) slot -= D;
                 redAdd(target + (unsigned long long)slot * numTrg + p, w[j]);
             }

@@ -127,6 +127,14 @@ struct b200_runner
     unsigned long long fusedLaunches = 0;
     bool fusedProfile = false;
     unsigned long long *fusedCtaCycles = nullptr;
+    // one-step lag of the persistent kernel (fused_step.cuh): allowed while every
+    // synapse has a dendritic delay of at least one step
+    bool useLag = true;
+    bool lagAgreed = false;         // sharded model: the host checked that every process is eligible
+    bool lagStale = true;           // delay arrays may have changed since the last scan
+    bool lagEligible = false;
+    unsigned int *lagScan = nullptr;
+    std::vector<b200_synapse_group> fusedGroups;    // host copy of the SPARSE groups the kernel serves
 
     // spike exchange of a sharded model
     unsigned char *arena = nullptr;
@@ -463,6 +471,8 @@ int prepare(b200_runner *r)
     if(r->fusedSources) { cudaFree(r->fusedSources); r->fusedSources = nullptr; }
     if(r->fusedItems) { cudaFree(r->fusedItems); r->fusedItems = nullptr; }
     r->fusedEligible = (r->batch == 1 && postSpan.empty() && learn.empty() && !r->neuronGroups.empty());
+    r->fusedGroups = sparse;
+    r->lagStale = true;
     if(r->fusedEligible) {
         std::vector<unsigned int> slotStart{0};
         for(const auto &g : r->neuronGroups) slotStart.push_back(slotStart.back() + ((g.num_update + 31u) & ~31u));
@@ -501,6 +511,10 @@ int prepare(b200_runner *r)
             sources[si].item_begin = (unsigned int)items.size();
             sources[si].item_count = (unsigned int)perSource[si].size();
             items.insert(items.end(), perSource[si].begin(), perSource[si].end());
+        }
+        if(sources.size() > FUSED_MAX_SOURCES) {
+            return fail(B200_ERR_INVALID, "%zu spike sources exceed the %u the persistent kernel handles",
+                        sources.size(), (unsigned int)FUSED_MAX_SOURCES);
         }
         r->fusedNumSources = (unsigned int)sources.size();
         r->fusedNumItems = (unsigned int)items.size();
@@ -615,9 +629,93 @@ int launchOwner(b200_runner *r, unsigned long long numSteps, unsigned long long 
     return B200_OK;
 }
 
+// Smallest dendritic delay over the synapses that exist, per SPARSE group.  A
+// delay that reaches the ring length counts as 0: it wraps around the ring and
+// arrives in the same step.  A group without dendritic delay reports 0.  One
+// warp per row.
+__global__ void minDelayKernel(const b200_synapse_group *groups, unsigned int *out)
+{
+    const b200_synapse_group &g = groups[blockIdx.y];
+    if(!g.max_den_delay) {
+        if(blockIdx.x == 0 && threadIdx.x == 0) out[blockIdx.y] = 0u;
+        return;
+    }
+    const unsigned int lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
+    const unsigned int D = g.max_den_delay;
+    unsigned int m = 0xFFFFFFFFu;
+    for(unsigned int row = blockIdx.x * warps + (threadIdx.x >> 5); row < g.num_src; row += gridDim.x * warps) {
+        const unsigned int len = min(g.row_length[row], g.row_stride);
+        const uint8_t *d = g.d + (unsigned long long)row * g.row_stride;
+        for(unsigned int j = lane; j < len; j += 32u) {
+            const unsigned int v = d[j];
+            m = min(m, (v >= D) ? 0u : v);
+        }
+    }
+    #pragma unroll
+    for(int o = 16; o; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+    if(lane == 0 && m != 0xFFFFFFFFu) atomicMin(&out[blockIdx.y], m);
+}
+
+// Decide whether the persistent kernel may deliver spikes one step late: every
+// SPARSE group needs a dendritic-delay ring and no synapse with delay zero.
+int scanDelays(b200_runner *r)
+{
+    r->lagStale = false;
+    r->lagEligible = false;
+    const unsigned int n = r->sparseTable.num;
+    if(n == 0) { r->lagEligible = true; return B200_OK; }
+    for(const auto &g : r->fusedGroups) {
+        if(g.max_den_delay < 2 || !g.d) return B200_OK;
+    }
+    // a list is read one step later and, in a sharded model, a peer may already be
+    // writing two steps ahead: the queue needs delay + 4 slots
+    for(const auto &s : r->fusedGroups) {
+        if(s.axonal_delay + 4 > s.src_delay_slots) return B200_OK;
+    }
+    if(!r->lagScan) CUDA_TRY(cudaMalloc(&r->lagScan, sizeof(unsigned int) * 4096));
+    if(n > 4096) return B200_OK;
+    CUDA_TRY(cudaMemsetAsync(r->lagScan, 0xFF, sizeof(unsigned int) * n, r->stream));
+    minDelayKernel<<<dim3(296, n), 256, 0, r->stream>>>(r->sparseTable.d, r->lagScan);
+    CUDA_TRY(cudaPeekAtLastError());
+    std::vector<unsigned int> mins(n);
+    CUDA_TRY(cudaMemcpyAsync(mins.data(), r->lagScan, sizeof(unsigned int) * n, cudaMemcpyDeviceToHost, r->stream));
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    r->launches++;
+    for(unsigned int m : mins) {
+        if(m == 0) return B200_OK;
+    }
+    r->lagEligible = true;
+    return B200_OK;
+}
+
+// true if [p, p + bytes) overlaps an array the delay scan depends on
+bool touchesDelays(const b200_runner *r, const void *p, size_t bytes)
+{
+    const unsigned char *a = static_cast<const unsigned char*>(p), *b = a + bytes;
+    for(const auto &g : r->fusedGroups) {
+        if(!g.max_den_delay || !g.d) continue;
+        const size_t synapses = (size_t)g.num_src * g.row_stride;
+        const unsigned char *d0 = reinterpret_cast<const unsigned char*>(g.d);
+        const unsigned char *l0 = reinterpret_cast<const unsigned char*>(g.row_length);
+        if(a < d0 + synapses && b > d0) return true;
+        if(a < l0 + sizeof(unsigned int) * g.num_src && b > l0) return true;
+    }
+    return false;
+}
+
 int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long numRec)
 {
+    if(r->useLag && r->lagStale) {
+        const bool was = r->lagEligible;
+        const int e = scanDelays(r);
+        if(e) return e;
+        if(r->sharded() && r->lagAgreed && was && !r->lagEligible) {
+            return fail(B200_ERR_STATE, "a synapse with dendritic delay 0 appeared after the processes of this sharded "
+                                        "model agreed to deliver spikes one step late");
+        }
+    }
     FusedLaunch L;
+    L.lag = (r->useLag && r->lagEligible && (!r->sharded() || r->lagAgreed)) ? 1u : 0u;
     L.neuron.groups = r->neuronTable.d;
     L.neuron.block_start = r->neuronTable.blockStart;
     L.neuron.num_groups = r->neuronTable.num;
@@ -838,6 +936,7 @@ int b200_runner_destroy(b200_runner *r)
     if(r->fusedSources) cudaFree(r->fusedSources);
     if(r->fusedItems) cudaFree(r->fusedItems);
     if(r->fusedBarrier) cudaFree(r->fusedBarrier);
+    if(r->lagScan) cudaFree(r->lagScan);
     if(r->fusedCtaCycles) cudaFree(r->fusedCtaCycles);
     r->dropOwner();
     for(unsigned int p = 0; p < B200_MAX_RANKS; p++) {
@@ -946,6 +1045,7 @@ int b200_array_push(b200_runner *r, void *device_ptr, const void *host, size_t b
 {
     CUDA_TRY(cudaMemcpyAsync(device_ptr, host, bytes, cudaMemcpyHostToDevice, r->stream));
     CUDA_TRY(cudaStreamSynchronize(r->stream));
+    if(touchesDelays(r, device_ptr, bytes)) r->lagStale = true;
     return B200_OK;
 }
 
@@ -959,6 +1059,7 @@ int b200_array_pull(b200_runner *r, void *host, const void *device_ptr, size_t b
 int b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes)
 {
     CUDA_TRY(cudaMemsetAsync(device_ptr, value, bytes, r->stream));
+    if(touchesDelays(r, device_ptr, bytes)) r->lagStale = true;
     return B200_OK;
 }
 
@@ -1025,6 +1126,9 @@ int b200_set_option(b200_runner *r, const char *name, double value)
     else if(n == "count_events") r->countEvents = (value != 0.0);
     else if(n == "use_graph") r->useGraph = (value != 0.0);
     else if(n == "use_fused") r->useFused = (value != 0.0);
+    else if(n == "use_lag") r->useLag = (value != 0.0);
+    else if(n == "lag_agreed") r->lagAgreed = (value != 0.0);
+    else if(n == "rescan_delays") r->lagStale = true;
     else if(n == "fused_profile") r->fusedProfile = (value != 0.0);
     else if(n == "use_owner") { r->useOwner = (value != 0.0); r->dirty = true; }
     else if(n == "owner_item_lanes") r->ownerItemLanes = (value <= 8.0) ? 8u : (value <= 16.0) ? 16u : 32u;
@@ -1050,6 +1154,7 @@ int b200_initialize_sparse(b200_runner *r)
 int b200_init_var(b200_runner *r, void *device_ptr, uint32_t elem_bytes, uint64_t count,
                   uint32_t snippet, const float *params, uint32_t rng_stream)
 {
+    r->lagStale = true;
     InitParams prm{};
     for(int i = 0; i < 4; i++) prm.p[i] = params ? params[i] : 0.0f;
     const unsigned int blocks = (unsigned int)std::min<uint64_t>((count + INIT_BLOCK - 1) / INIT_BLOCK, 148u * 32u);
@@ -1071,6 +1176,7 @@ int b200_init_sparse_connectivity(b200_runner *r, uint32_t snippet, const float 
                                   uint32_t ind_bytes, uint32_t trg_begin, uint32_t trg_end,
                                   uint32_t *row_length, void *ind, uint32_t rng_stream)
 {
+    r->lagStale = true;
     if(trg_end > num_trg || trg_begin >= trg_end) return fail(B200_ERR_INVALID, "bad target range");
     InitParams prm{};
     for(int i = 0; i < 4; i++) prm.p[i] = params ? params[i] : 0.0f;
@@ -1096,6 +1202,7 @@ int b200_init_sparse_vars(b200_runner *r, const uint32_t *row_length, uint32_t n
                           uint32_t row_stride, void *device_ptr, uint32_t elem_bytes,
                           uint32_t snippet, const float *params, uint32_t rng_stream)
 {
+    r->lagStale = true;
     InitParams prm{};
     for(int i = 0; i < 4; i++) prm.p[i] = params ? params[i] : 0.0f;
     const uint64_t total = (uint64_t)num_src * row_stride;
@@ -1246,10 +1353,23 @@ int b200_get_steps_done(b200_runner *r, uint64_t *steps)
 
 int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
 {
+    const std::string n(name);
+    if(n == "lag_eligible" || n == "lag") {
+        // whether this process may deliver spikes one step late (scans the delay arrays if
+        // they changed) / whether its next persistent launch will
+        int e = prepare(r);
+        if(e) return e;
+        if(r->useLag && r->fusedEligible && r->lagStale) {
+            e = scanDelays(r);
+            if(e) return e;
+        }
+        const bool can = r->useLag && r->fusedEligible && r->lagEligible;
+        *value = (n == "lag") ? (can && r->useFused && (!r->sharded() || r->lagAgreed)) : can;
+        return B200_OK;
+    }
     CUDA_TRY(cudaStreamSynchronize(r->stream));
     StepState s;
     CUDA_TRY(cudaMemcpy(&s, r->state, sizeof(s), cudaMemcpyDeviceToHost));
-    const std::string n(name);
     if(n == "synaptic_events") *value = s.synaptic_events;
     else if(n == "spikes") *value = s.spikes;
     else if(n == "cycles_presynaptic") *value = s.phase_cycles[0];

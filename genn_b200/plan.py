@@ -143,7 +143,7 @@ class Plan:
         # process) and the arrival flags in ONE arena that peers can map
         world = self.shard[1] if self.shard else 1
         for p in net.pops:
-            p.runtime_slots = p.num_delay_slots + 2     # two spare slots: see include/genn_b200.h
+            p.runtime_slots = p.num_delay_slots + 3     # three spare slots: see include/genn_b200.h
             bounds = shard_bounds(p.n, world)
             p.shard_bounds = bounds
             p.list_capacity = p.n if world == 1 else max(32, max(bounds[r + 1] - bounds[r] for r in range(world)))

@@ -54,7 +54,8 @@ def phases(args):
     """Per-phase SM cycles of the persistent fused-step kernel at natural rates."""
     from . import workloads
     from .runtime import Runtime
-    model = workloads.potjans(neuron_scale=args.scale, seed=1234)
+    model = workloads.potjans(neuron_scale=args.scale, seed=1234, min_delay=args.min_delay,
+                              extra_delay_slots=1 if args.min_delay > 0 else 0)
     model.build()
     rt = Runtime(model, None)
     rt.set_option("count_events", args.count_events)
@@ -62,6 +63,7 @@ def phases(args):
         rt.set_option("fused_blocks_per_sm", args.blocks_per_sm)
     rt.set_option("use_owner", args.owner)
     rt.set_option("owner_item_lanes", args.item_lanes)
+    rt.set_option("use_lag", args.lag)
     rt.step_time(args.warm)
     rt.synchronize()
     rt.set_option("fused_profile", 1)
@@ -70,7 +72,7 @@ def phases(args):
     ms = rt.step_time_timed(args.steps)
     after = [rt.counter(n) for n in names]
     out = {"probe": "phases", "scale": args.scale, "steps": args.steps, "us_per_step": ms * 1e3 / args.steps,
-           "step_path": rt.step_path()}
+           "step_path": rt.step_path(), "lagging": rt.lagging}
     for n, a, b in zip(names, before, after):
         out[n + "_per_step"] = (b - a) / args.steps
     cta = rt.cta_cycles().astype(np.float64) / args.steps
@@ -102,6 +104,8 @@ def main():
     p.add_argument("--count-events", type=int, default=0)
     p.add_argument("--blocks-per-sm", type=int, default=0)
     p.add_argument("--owner", type=int, default=0)
+    p.add_argument("--lag", type=int, default=1, help="deliver spikes one step late where every delay allows it")
+    p.add_argument("--min-delay", type=float, default=0.0, help="lower clip of the delay distribution in ms")
     p.add_argument("--item-lanes", type=int, default=32)
     p.add_argument("--dump", action="store_true", help="print the per-CTA phase cycles")
     p.set_defaults(fn=phases)

@@ -120,6 +120,11 @@ class Runtime:
             check(self.lib.b200_push_synapse_group(self.handle, i, C.byref(d)))
         check(self.lib.b200_initialize(self.handle))
         check(self.lib.b200_initialize_sparse(self.handle))
+        if shard is not None and shard[1] > 1:
+            # delivering spikes one step late needs every process to do it: agree
+            mine = bytes([1 if self.counter("lag_eligible") else 0])
+            everyone = (exchange or all_gather_bytes)(mine)
+            self.set_option("lag_agreed", 1.0 if all(b[0] for b in everyone) else 0.0)
         if model is not None:
             self._bind_model_views()
             if getattr(model, "timing_enabled", False):
@@ -282,6 +287,12 @@ class Runtime:
         why = C.create_string_buffer(256)
         check(self.lib.b200_get_step_path(self.handle, C.byref(path), why, 256))
         return path.value, why.value.decode()
+
+    @property
+    def lagging(self) -> bool:
+        """True if the persistent kernel delivers spikes one step late (every dendritic
+        delay is at least one step), which lets it drop the second grid barrier."""
+        return bool(self.counter("lag"))
 
     def cta_cycles(self) -> np.ndarray:
         """[num_ctas, 4] cycles per phase of the persistent kernel (option fused_profile)."""

@@ -149,9 +149,18 @@ def potjans_projections(neuron_scale: float = 1.0):
 
 def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
             host_connectivity: bool = False, background: str = "poisson",
-            shard: Optional[Tuple[int, int]] = None, record: bool = False) -> GeNNModel:
+            shard: Optional[Tuple[int, int]] = None, record: bool = False,
+            min_delay: float = 0.0, extra_delay_slots: int = 0) -> GeNNModel:
     """Potjans-Diesmann microcircuit architecture at ``neuron_scale`` times the
     published population sizes with the published in-degrees.
+
+    ``min_delay`` (ms) is the lower clip of the delay distribution: 0 as in the
+    reference's script (userproject/potjans_microcircuit.py:259), which rounds a
+    few per cent of the synapses to a delay of zero steps; ``dt`` gives every
+    synapse at least one step, as in the original model description.
+    ``extra_delay_slots`` lengthens the dendritic-delay ring beyond the script's
+    round(longest delay / dt): with exactly that many slots a synapse drawn at
+    the longest delay wraps around the ring and arrives in the same step.
 
     ``host_connectivity`` draws connectivity/weights/delays with numpy so the
     same arrays can be handed to a CPU checker (small scales only); otherwise
@@ -194,7 +203,7 @@ def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
             post = rng.integers(0, nt, size=num).astype(np.uint32)
             g = truncated_normal(rng, mean_w, sd_w, lo, hi, num).astype(np.float32)
             # NormalClippedDelay: truncated normal in time steps, then rint
-            d = np.rint(truncated_normal(rng, md / dt, sd / dt, 0.0, mxd / dt, num)).astype(np.uint8)
+            d = np.rint(truncated_normal(rng, md / dt, sd / dt, min_delay / dt, mxd / dt, num)).astype(np.uint8)
             if shard is not None:
                 from .plan import shard_bounds
                 rank, world = shard
@@ -217,11 +226,11 @@ def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
                 num = int(round(num * (trg_range[1] - trg_range[0]) / float(nt)))
             wu = init_weight_update("StaticPulseDendriticDelay", {}, {
                 "g": init_var("NormalClipped", {"mean": mean_w, "sd": sd_w, "min": lo, "max": hi}),
-                "d": init_var("NormalClippedDelay", {"mean": md, "sd": sd, "min": 0.0, "max": mxd})})
+                "d": init_var("NormalClippedDelay", {"mean": md, "sd": sd, "min": min_delay, "max": mxd})})
             sg = m.add_synapse_population(
                 f"{src}_{trg}", "SPARSE", pops[src], pops[trg], wu,
                 init_postsynaptic("ExpCurr", {"tau": 0.5}),
                 init_sparse_connectivity("FixedNumberTotalWithReplacement", {"num": num}))
             sg.trg_range = trg_range
-        sg.max_dendritic_delay_timesteps = slots
+        sg.max_dendritic_delay_timesteps = slots + extra_delay_slots
     return m

@@ -135,7 +135,8 @@ typedef struct b200_neuron_group {
     uint32_t model;            /* b200_neuron_model */
     uint32_t num_neurons;
     uint32_t num_delay_slots;  /* spike queue depth: at least longest axonal/back-propagation delay + 2;
-                                  + 3 lets the single-barrier persistent kernel be used */
+                                  + 3 lets the target-stationary persistent kernel be used, + 4 lets the
+                                  persistent kernel deliver spikes one step late (option "use_lag") */
     uint32_t num_psm;
     uint32_t num_cs;
     uint32_t rng_stream;
@@ -290,12 +291,20 @@ int  b200_synchronize(b200_runner *r);
 int  b200_get_timestep(b200_runner *r, uint64_t *timestep);
 int  b200_set_timestep(b200_runner *r, uint64_t timestep);
 int  b200_get_steps_done(b200_runner *r, uint64_t *steps);
-/* Device-side counters: "synaptic_events" and "spikes" (when option count_events is on), "timestep", "steps_done". */
+/* Device-side counters: "synaptic_events" and "spikes" (when option count_events is on), "timestep", "steps_done".
+ * Host-side answers: "lag_eligible" (1 if every SPARSE group has a dendritic-delay ring and no synapse with
+ * delay 0, so spikes may be delivered one step late; scans the delay arrays if they changed), "lag" (1 if the
+ * next persistent launch will do so). */
 int  b200_get_counter(b200_runner *r, const char *name, uint64_t *value);
 /* Tuning knobs (the counterpart of the backend Preferences, backends/cuda/backend.h:64-115):
  * "spike_lanes" (grid.y of the SPARSE kernel), "use_graph", "graph_steps", "count_events",
  * "use_fused" (persistent kernels), "use_owner" (target-stationary persistent kernel),
- * "fused_blocks_per_sm", "fused_profile". */
+ * "fused_blocks_per_sm", "fused_profile",
+ * "use_lag" (default 1: when no synapse has dendritic delay 0 the persistent kernel delivers each spike one
+ * step later into the ring slot one nearer, same result, one grid barrier per step instead of two),
+ * "lag_agreed" (sharded model: the caller has checked "lag_eligible" on EVERY process; without it a sharded
+ * model keeps the two-barrier schedule), "rescan_delays" (delay arrays were changed by something other than
+ * this library's push / init calls). */
 int  b200_set_option(b200_runner *r, const char *name, double value);
 
 /* Which time-step path b200_step_time takes for the registered model: 2 = target-stationary

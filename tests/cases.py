@@ -36,6 +36,15 @@ def potjans_mini():
     return m, 400, 100
 
 
+def potjans_mini_d1():
+    """The same with every delay at least one step (lower clip dt instead of 0) and
+    a ring one slot longer than the longest delay, so that no synapse wraps around
+    it: the persistent kernel may then deliver spikes one step late."""
+    m = workloads.potjans(neuron_scale=0.005, seed=7, host_connectivity=True, background="dc", record=True,
+                          min_delay=0.1, extra_delay_slots=1)
+    return m, 400, 100
+
+
 def cond_delay():
     """Recurrent conductance-based E/I network with a 1 ms axonal delay and
     constant weights (config 2 in miniature)."""
@@ -113,5 +122,5 @@ def poisson_drive():
 
 
 CASES = {"ff_sparse": ff_sparse, "ff_sparse_narrow": ff_sparse_narrow, "ff_bitmask": ff_bitmask,
-         "ff_dense": ff_dense, "potjans_mini": potjans_mini, "cond_delay": cond_delay, "stdp": stdp,
+         "ff_dense": ff_dense, "potjans_mini": potjans_mini, "potjans_mini_d1": potjans_mini_d1, "cond_delay": cond_delay, "stdp": stdp,
          "izhikevich": izhikevich}

@@ -1,7 +1,7 @@
 """Child process of tests/test_multi_gpu.py: one rank of a model sharded by
 postsynaptic neuron over several GPUs.
 
-    python -m torch.distributed.run --nproc-per-node 2 tests/multigpu_check.py <case>
+    python -m torch.distributed.run --nproc-per-node 2 tests/multigpu_check.py <case> [lag|two-barrier]
 
 Every rank builds the same network restricted to the synapses onto its slice,
 steps it with the persistent kernel (spike lists travel between the GPUs inside
@@ -26,16 +26,20 @@ def main():
     from tests import helpers
 
     name = sys.argv[1] if len(sys.argv) > 1 else "potjans_mini"
+    lag = (sys.argv[2] if len(sys.argv) > 2 else "lag") == "lag"
+    kw = dict(min_delay=0.1, extra_delay_slots=1) if name == "potjans_mini_d1" else {}
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
     torch.cuda.set_device(local)
     dist.init_process_group("gloo")           # bootstrap only: the spikes do not go through it
-    assert name == "potjans_mini"
+    assert name in ("potjans_mini", "potjans_mini_d1")
     model = workloads.potjans(neuron_scale=0.005, seed=7, host_connectivity=True, background="dc", record=True,
-                              shard=(rank, world))
+                              shard=(rank, world), **kw)
     steps, dump_every = 400, 100
     net = resolve(model)
     rt = Runtime(None, steps, device=local, shard=(rank, world), net=net)
+    rt.set_option("use_lag", 1 if lag else 0)
+    assert rt.lagging == (lag and name == "potjans_mini_d1"), f"rank {rank}: lagging {rt.lagging}"
     want = helpers.load_golden(name)
     spikes = {p.name: [] for p in net.pops}
     for s in range(steps):
@@ -58,7 +62,8 @@ def main():
     # the same again as ONE launch of many steps with recording
     rt2 = Runtime(None, steps, device=local, shard=(rank, world), net=resolve(
         workloads.potjans(neuron_scale=0.005, seed=7, host_connectivity=True, background="dc", record=True,
-                          shard=(rank, world))))
+                          shard=(rank, world), **kw)))
+    rt2.set_option("use_lag", 1 if lag else 0)
     dist.barrier()
     rt2.step_time(steps)
     rt2.synchronize()
@@ -74,7 +79,8 @@ def main():
     rt.close()
     rt2.close()
     if rank == 0:
-        print(f"multigpu_check ok: {world} ranks, {sum(len(v) for v in spikes.values())} spikes")
+        print(f"multigpu_check ok: {world} ranks, {'lagging' if lag else 'two-barrier'} schedule, "
+              f"{sum(len(v) for v in spikes.values())} spikes")
     dist.destroy_process_group()
 
 

@@ -17,17 +17,23 @@ pytestmark = pytest.mark.gpu
 
 RTOL, ATOL = 1e-5, 2e-6
 
-# the three time-step paths: target-stationary persistent kernel, persistent kernel
-# with global reductions, one launch per kernel
-PATHS = {"owner": (1, 1), "persistent": (1, 0), "per-kernel": (0, 0)}
+# the time-step paths: target-stationary persistent kernel, persistent kernel with
+# global reductions (delivering spikes one step late where no synapse has delay 0,
+# and with that switched off), one launch per kernel
+PATHS = {"owner": (1, 1, 1), "persistent": (1, 0, 1), "persistent-two-barrier": (1, 0, 0), "per-kernel": (0, 0, 1)}
+# networks whose every synapse has a dendritic delay of at least one step
+LAG_CASES = {"potjans_mini_d1"}
 # networks the target-stationary kernel must accept (SPARSE, sorted rows, no learning)
-OWNER_CASES = {"ff_sparse", "ff_sparse_narrow", "potjans_mini", "cond_delay", "izhikevich"}
+OWNER_CASES = {"ff_sparse", "ff_sparse_narrow", "potjans_mini", "potjans_mini_d1", "cond_delay", "izhikevich"}
 
 
 def _select(rt, path, name=None):
-    fused, owner = PATHS[path]
+    fused, owner, lag = PATHS[path]
     rt.set_option("use_fused", fused)
     rt.set_option("use_owner", owner)
+    rt.set_option("use_lag", lag)
+    if name is not None:
+        assert rt.lagging == (bool(lag) and name in LAG_CASES and rt.step_path()[0] >= 1), f"{name}: lag {rt.lagging}"
     if path == "owner" and name in OWNER_CASES:
         taken, why = rt.step_path()
         assert taken == 2, f"{name} should run on the target-stationary kernel: {why}"
@@ -69,7 +75,7 @@ def test_step_by_step_matches_reference_golden(name, path):
 
 
 @pytest.mark.parametrize("path", list(PATHS))
-@pytest.mark.parametrize("name", ["ff_sparse", "potjans_mini", "cond_delay", "stdp"])
+@pytest.mark.parametrize("name", ["ff_sparse", "potjans_mini", "potjans_mini_d1", "cond_delay", "stdp"])
 def test_many_steps_in_one_call_and_recording_match_reference_golden(name, path):
     """All steps in one call (one persistent launch, or replays of a captured
     graph) with spike recording on: the decoded recording equals the
@@ -170,3 +176,35 @@ def test_device_check_reports_bad_index():
         rt = _runtime(net, steps)           # the index check of the initialisation kernels may already catch it
         rt.step_time(50)
         rt.synchronize()
+
+
+def test_launch_boundaries_of_the_lagging_schedule_leave_the_usual_state():
+    """Persistent launches of odd lengths (spikes delivered one step late inside a
+    launch) alternate with steps on the per-kernel path: memory between launches
+    must be what the two-barrier schedule leaves, or the hand-over would lose or
+    double-deliver spikes."""
+    model, steps, dump_every = CASES["potjans_mini_d1"]()
+    net = resolve(model)
+    rt = _runtime(net, steps)
+    assert rt.lagging
+    done, chunk = 0, [1, 2, 1, 5, 3, 17, 1, 1, 40]
+    i = 0
+    while done < steps:
+        n = min(chunk[i % len(chunk)], steps - done)
+        rt.set_option("use_fused", 0 if (i % 3 == 2) else 1)
+        rt.step_time(n)
+        done += n
+        i += 1
+    rt.synchronize()
+    rt.pull_recording_buffers()
+    want = helpers.load_golden("potjans_mini_d1")
+    for p in net.pops:
+        if not p.record:
+            continue
+        times, ids = rt.recorded_spikes(p.name)[0]
+        got = helpers.sorted_pairs(np.stack([np.rint(times / net.dt).astype(np.uint32), ids], axis=1))
+        assert np.array_equal(got, want[f"spikes_{p.name}"]), f"recorded spikes of {p.name} differ"
+    final = helpers.snapshot(_Adapter(rt), net, steps)
+    helpers.compare(final, {k: v for k, v in want.items() if k.endswith(f"_{steps}")}, exact_state=False,
+                    rtol=RTOL, atol=ATOL)
+    rt.close()

@@ -87,13 +87,15 @@ def test_handle_exchange_over_gloo_two_processes():
 
 
 @pytest.mark.gpu
-def test_two_gpus_match_the_unsharded_reference():
+@pytest.mark.parametrize("name,schedule", [("potjans_mini_d1", "lag"), ("potjans_mini_d1", "two-barrier"),
+                                           ("potjans_mini", "lag")])
+def test_two_gpus_match_the_unsharded_reference(name, schedule):
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
     env = dict(os.environ, NCCL_NVLS_ENABLE="0")
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr", "127.0.0.1",
-           "--master-port", str(29700 + os.getpid() % 200), os.path.join(REPO, "tests", "multigpu_check.py"), "potjans_mini"]
+           "--master-port", str(29700 + os.getpid() % 200), os.path.join(REPO, "tests", "multigpu_check.py"), name, schedule]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=REPO)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "multigpu_check ok" in res.stdout

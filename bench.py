@@ -197,6 +197,10 @@ def main():
     ap.add_argument("--block", type=int, default=1000, help="simulation time steps per bench step")
     ap.add_argument("--ref-scale", type=float, default=0.05, help="neuron scale of the CPU sample")
     ap.add_argument("--neuron-scale", type=float, default=None, help="override the workload size (debugging)")
+    ap.add_argument("--min-delay", type=float, default=0.0,
+                    help="lower clip of the delay distribution in ms (0: the reference script's; not the headline if changed)")
+    ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
+                    help="runner option to set before timing (experiments; see b200_set_option)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-saturated", action="store_true")
     args = ap.parse_args()
@@ -228,13 +232,17 @@ def main():
 
     # ---- build through the public API ---------------------------------------------
     model = workloads.potjans(neuron_scale=scale, seed=1234, record=True,
-                              shard=(rank, world) if world > 1 else None)
+                              shard=(rank, world) if world > 1 else None,
+                              min_delay=args.min_delay, extra_delay_slots=1 if args.min_delay > 0 else 0)
     model.build()
     model.load(num_recording_timesteps=block, device=local_rank, shard=(rank, world) if world > 1 else None)
     rt = model._runtime
     net = rt.net
     rt.set_option("count_events", 1)
     rt.set_option("graph_steps", min(block, 100))
+    for item in args.option:
+        opt_name, opt_value = item.split("=")
+        rt.set_option(opt_name, float(opt_value))
     bpe = bytes_per_event(net)
 
     def barrier():
@@ -289,7 +297,7 @@ def main():
     # ---- where a step's time goes inside the persistent kernel (clock64 per phase, CTA 0) ---
     probe_steps = min(args.steps * block, 2000)
     rt.set_option("fused_profile", 1)
-    names = ["cycles_presynaptic", "cycles_barrier_a", "cycles_neuron", "cycles_barrier_b"]
+    names = ["cycles_presynaptic", "cycles_barrier_a", "cycles_neuron", "cycles_barrier_b"] + [f"probe{i}" for i in range(8)]
     before = [rt.counter(n) for n in names]
     pev0, psp0 = rt.counter("synaptic_events"), rt.counter("spikes")
     barrier()
@@ -298,6 +306,14 @@ def main():
     barrier()
     pev, psp = rt.counter("synaptic_events") - pev0, rt.counter("spikes") - psp0
     phase_cycles = {n: (rt.counter(n) - b) / probe_steps for n, b in zip(names, before)}
+    cta = rt.cta_cycles().astype(np.float64) / probe_steps
+    if len(cta):
+        # spike-header wait (counts and first ids of every source) inside the presynaptic phase, per CTA
+        head = np.asarray(rt.header_cycles, dtype=np.float64) / probe_steps
+        phase_cycles["header_median"] = float(np.median(head))
+        phase_cycles["header_max"] = float(head.max())
+        phase_cycles["cta_presynaptic_min_median_max"] = [float(cta[:, 0].min()), float(np.median(cta[:, 0])),
+                                                          float(cta[:, 0].max())]
     rt.set_option("fused_profile", 0)
     sm_hz = (clocks.get("sm_mhz") or 1965.0) * 1e6
 
@@ -393,8 +409,12 @@ def main():
                                    f"published in-degrees, SPARSE with dendritic delays, PoissonExp background, "
                                    f"dt=0.1 ms; one bench step = {block} time steps (0.1 s biological)",
                        "parallelism": f"postsynaptic sharding over {world} GPU(s)" if world > 1 else "single GPU",
-                       "schedule": ("persistent kernel, spikes delivered one step late (every dendritic delay >= 1 step): "
-                                    "one grid barrier per step") if rt.lagging else "persistent kernel, two grid barriers per step",
+                       "schedule": ["persistent kernel, every synapse delivered before the neuron update",
+                                    "persistent kernel, split delivery: synapses that arrive in the same step before the "
+                                    "neuron update, all others behind it in the shadow of the second grid barrier",
+                                    "persistent kernel, spikes delivered one step late (no synapse arrives in the same "
+                                    "step): one grid barrier per step"][rt.schedule],
+                       "min_delay_ms": args.min_delay,
                        "l2": "working set (2.5 GB of synapses) exceeds L2; no flush needed",
                        "spikes_per_s_biological": spikes / sim_seconds,
                        "mean_rates_hz": rates, "bytes_per_event": bpe},

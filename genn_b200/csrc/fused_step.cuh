@@ -25,6 +25,27 @@
 // is a monotonic 64-bit arrival counter in global memory; every wait is bounded
 // and a time-out sets an error flag and ends the kernel on all CTAs.
 //
+// Split delivery.  Only a synapse whose dendritic delay is zero steps (or a
+// multiple of the ring length: it wraps around the ring) feeds the neuron update
+// of the SAME step; for a typical cortical model that is a few per cent of the
+// synapses.  The host copies exactly those into a small padded table per group
+// ("urgent" synapses) and the step becomes
+//
+//   header    spike counts and ids of the step before
+//   phase A0  urgent synapses of those spikes (+ every synapse of a group that
+//             has no dendritic-delay ring)
+//   barrier A
+//   phase B   neuron update
+//   barrier B arrive ... wait, and in between
+//   phase A1  all OTHER synapses of the same spikes, same ring slots as always:
+//             a slot one or more steps ahead is not read before the next neuron
+//             update, and barrier A of the next step orders it.
+//
+// The bulk of the memory traffic thus overlaps the barrier (and, in a sharded
+// model, the flight of the spike words between GPUs) instead of sitting on the
+// critical path.  Results are those of the plain schedule: every contribution
+// lands in the same slot before the same reader.
+//
 // One-step lag.  When EVERY synapse of every group has a dendritic delay of at
 // least one step (the host scans the delay arrays), a spike emitted in step s
 // may be delivered in the presynaptic phase of step s+2 instead of s+1, into
@@ -65,12 +86,27 @@ struct FusedSource
     unsigned int num_src;
     unsigned int slots;
     unsigned int delay;
-    unsigned int item_begin;
+    unsigned int item_begin;             // items that may run after the neuron update (phase A1)
     unsigned int item_count;
+    unsigned int urgent_begin;           // items that must run before it (phase A0)
+    unsigned int urgent_count;
     unsigned int pad;
     const unsigned long long *spk_tag;   // sharded models: (step << 32 | count) per slot, else NULL
     const unsigned long long *spk_wire;  // sharded models: (step << 32 | id) lists, else NULL
 };
+
+// The urgent synapses of one SPARSE group, compressed rows.
+struct FusedUrgent
+{
+    const unsigned int *offsets;         // [num_src + 1] into entries
+    const uint2 *entries;                // (target index, weight bits)
+    unsigned int stride;                 // longest row (0: the group has no urgent synapses)
+    unsigned int pad;
+};
+
+// item.y of an urgent item: chunk index, with this bit set for a chunk of the
+// urgent table (clear: a chunk of the full row of a group without delay ring)
+constexpr unsigned int FUSED_URGENT_TABLE = 0x80000000u;
 
 struct FusedLaunch
 {
@@ -78,7 +114,8 @@ struct FusedLaunch
     const unsigned int *slot_start;      // [num_groups+1] first thread slot of each neuron group (multiples of 32)
     const b200_synapse_group *sgroups;
     const FusedSource *sources;
-    const uint2 *items;                  // (synapse group index, chunk index)
+    const uint2 *items;                  // (synapse group index, chunk index); urgent items follow the others
+    const FusedUrgent *urgent;           // [num_sgroups] or NULL (no group has an urgent table)
     unsigned int num_sources;
     unsigned int num_sgroups;
     unsigned int num_items;
@@ -94,6 +131,10 @@ struct FusedLaunch
     unsigned char *arena;                // this process's exchange arena
     unsigned char *const *peer_table;    // device table [B200_MAX_RANKS]: the same arena of every peer, mapped here
     unsigned int lag;                    // 1: deliver spikes one step late into the ring slot one nearer (see above)
+    unsigned int skip_urgent;            // 1: full-row items leave out the synapses the urgent tables hold
+    // warp-specialised kernel (stream_step.cuh) only
+    unsigned int stream_warps;           // warps per CTA that do nothing but deliver non-urgent synapses
+    unsigned int slots_per_cta;          // neuron slots per CTA (a multiple of 32)
 };
 
 constexpr unsigned long long EXCHANGE_SPIN_LIMIT = 1ull << 23;
@@ -149,8 +190,8 @@ __device__ __forceinline__ void gridArrive(unsigned long long *barrier, unsigned
     if(threadIdx.x == 0) {
         // release + arrive in one fire-and-forget reduction: nothing waits for its return
         asm volatile("red.release.gpu.global.add.u64 [%0], %1;" :: "l"(barrier), "l"(1ull) : "memory");
-        epoch += gridDim.x;
     }
+    epoch += gridDim.x;     // every thread keeps the count: any of them may have to poll
 }
 
 __device__ __forceinline__ bool gridWait(const unsigned long long *barrier, const unsigned long long &epoch, bool *ok,
@@ -174,11 +215,26 @@ __device__ __forceinline__ bool gridWait(const unsigned long long *barrier, cons
 
 template<typename IndT>
 __device__ __forceinline__ void fusedChunk(const b200_synapse_group &g, unsigned int pre, unsigned int chunk,
-                                           unsigned int front, unsigned int minDelay, StepState *state)
+                                           unsigned int front, unsigned int zeroDelay, StepState *state)
 {
     const unsigned int D = g.max_den_delay;
     float *target = D ? g.den_delay : g.out_post;
-    sparseQuad<IndT>(g, pre, chunk * 32u + (threadIdx.x & 31u), target, D ? ringSlot(front, D) : 0u, state, minDelay);
+    sparseQuad<IndT>(g, pre, chunk * 32u + (threadIdx.x & 31u), target, D ? ringSlot(front, D) : 0u, state, zeroDelay);
+}
+
+// 32 entries of one row of a group's urgent table into the front slot of its ring.
+__device__ __forceinline__ void fusedUrgentChunk(const b200_synapse_group &g, const FusedUrgent &u, unsigned int pre,
+                                                 unsigned int chunk, unsigned int front, StepState *state)
+{
+    const unsigned int begin = __ldg(&u.offsets[pre]), end = __ldg(&u.offsets[pre + 1]);
+    const unsigned int at = begin + chunk * 32u + (threadIdx.x & 31u);
+    if(at >= end) return;
+    const uint2 e = __ldg(&u.entries[at]);
+    if(e.x >= g.num_trg) {
+        atomicOr(&state->error, ERR_IND_RANGE);
+        return;
+    }
+    redAdd(g.den_delay + (unsigned long long)ringSlot(front, g.max_den_delay) * g.num_trg + e.x, __uint_as_float(e.y));
 }
 
 // Copy `bytes` (a multiple of 4) from global to shared memory with the whole CTA.
@@ -201,6 +257,8 @@ fusedStepKernel(FusedLaunch L)
 {
     extern __shared__ __align__(16) unsigned char fusedSmem[];
     __shared__ bool barrierOk;
+    __shared__ long long publishedAt;        // profile mode: when the counts of the last step went out
+    if(threadIdx.x == 0) publishedAt = 0;
     __shared__ unsigned int headCnt[FUSED_MAX_SOURCES], headSlot[FUSED_MAX_SOURCES], headIds[FUSED_MAX_SOURCES][FUSED_PREFETCH_IDS];
     __shared__ unsigned char *peerArena[B200_MAX_RANKS];
     if(threadIdx.x < B200_MAX_RANKS) peerArena[threadIdx.x] = L.peer_table ? L.peer_table[threadIdx.x] : nullptr;
@@ -233,6 +291,11 @@ fusedStepKernel(FusedLaunch L)
         const size_t tb = sizeof(unsigned int) * (L.neuron.num_groups + 1);
         stageWords(p, L.slot_start, tb);
         L.slot_start = reinterpret_cast<const unsigned int*>(p);
+        p += align16(tb);
+        if(L.urgent) {
+            stageWords(p, L.urgent, sizeof(FusedUrgent) * L.num_sgroups);
+            L.urgent = reinterpret_cast<const FusedUrgent*>(p);
+        }
         __syncthreads();
     }
     const unsigned int lane = threadIdx.x & 31u;
@@ -278,9 +341,10 @@ fusedStepKernel(FusedLaunch L)
     // lists: one 64-bit store per (process, population) says "step s: n spikes"; it is
     // what the readers poll.  The ids already sit in every arena (stored as they were
     // emitted).  Called by the whole grid after a barrier that follows the emission.
-    auto publishCounts = [&](unsigned int writtenAt, unsigned long long tagStep) {
-        if(L.world > 1 && blockIdx.x == 0 && threadIdx.x < L.world * numGroups) {
-            const unsigned int peer = threadIdx.x / numGroups, gi = threadIdx.x - peer * numGroups;
+    auto publishCounts = [&](unsigned int first, unsigned int writtenAt, unsigned long long tagStep) {
+        // called by one warp (first = lane) of block 0
+        for(unsigned int idx = first; L.world > 1 && blockIdx.x == 0 && idx < L.world * numGroups; idx += 32u) {
+            const unsigned int peer = idx / numGroups, gi = idx - peer * numGroups;
             const b200_neuron_group &g = L.neuron.groups[gi];
             const unsigned int wslot = ringSlot(writtenAt, g.num_delay_slots);
             const unsigned long long tag = (tagStep << 32) | (unsigned long long)__ldcg(&g.spk_cnt[wslot]);
@@ -291,10 +355,75 @@ fusedStepKernel(FusedLaunch L)
             storeRelaxedSys(cell, tag);
         }
     };
+    // Deliver the spikes the header holds through one of the two item lists of every source:
+    // the items the coming neuron update needs, or the ones that can follow it.
+    unsigned long long step = 0;
+    auto deliver = [&](const bool urgentList) {
+        for(unsigned int base = 0; base < L.num_sources; base += 32u) {
+            const unsigned int cnt = (base + lane < L.num_sources) ? headCnt[base + lane] : 0u;
+            const unsigned int per = (base + lane >= L.num_sources) ? 0u
+                : urgentList ? L.sources[base + lane].urgent_count : L.sources[base + lane].item_count;
+            unsigned int incl = cnt * per;
+            #pragma unroll
+            for(int o = 1; o < 32; o <<= 1) {
+                const unsigned int v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if(lane >= o) incl += v;
+            }
+            const unsigned int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+            for(unsigned int it = gwarp; it < total; it += totalWarps) {
+                const unsigned int owner = __ffs(__ballot_sync(0xFFFFFFFFu, incl > it)) - 1u;
+                const unsigned int ownIncl = __shfl_sync(0xFFFFFFFFu, incl, owner);
+                const unsigned int ownPer = __shfl_sync(0xFFFFFFFFu, per, owner);
+                const unsigned int ownCnt = headCnt[base + owner];
+                const unsigned int rel = it - (ownIncl - ownCnt * ownPer);
+                const unsigned int s = rel / ownPer;
+                const unsigned int c = rel - s * ownPer;
+                const FusedSource &src = L.sources[base + owner];
+                unsigned int pre;
+                if(s < FUSED_PREFETCH_IDS) {
+                    pre = headIds[base + owner][s];
+                }
+                else if(src.spk_wire) {
+                    const long long expected = (long long)(done0 + step) - (long long)(src.delay + lag);
+                    pre = awaitWord(&src.spk_wire[(unsigned long long)headSlot[base + owner] * src.num_src + s],
+                                    (unsigned long long)expected, state);
+                }
+                else {
+                    pre = __ldcg(&src.spk[(unsigned long long)headSlot[base + owner] * src.num_src + s]);
+                }
+                const uint2 item = L.items[(urgentList ? src.urgent_begin : src.item_begin) + c];
+                const b200_synapse_group &g = L.sgroups[item.x];
+                if(pre < g.num_src) {
+                    if(item.y & FUSED_URGENT_TABLE) {
+                        fusedUrgentChunk(g, L.urgent[item.x], pre, item.y & ~FUSED_URGENT_TABLE, k + 1u, state);
+                    }
+                    else {
+                        // synapses that arrive in the same step: delivered (plain schedule), an error
+                        // (the schedule relies on there being none) or left to the group's urgent table
+                        const unsigned int zeroDelay = urgentList ? 0u
+                            : (L.skip_urgent && L.urgent && L.urgent[item.x].stride) ? 2u : 1u;
+                        switch(g.ind_bytes) {
+                        case 1: fusedChunk<uint8_t>(g, pre, item.y, k + 1u - lag, zeroDelay, state); break;
+                        case 2: fusedChunk<uint16_t>(g, pre, item.y, k + 1u - lag, zeroDelay, state); break;
+                        default: fusedChunk<uint32_t>(g, pre, item.y, k + 1u - lag, zeroDelay, state); break;
+                        }
+                        if(L.count_events && item.y == 0 && lane == 0) {
+                            atomicAdd(&state->synaptic_events, (unsigned long long)__ldg(&g.row_length[pre]));
+                        }
+                    }
+                }
+                else if(lane == 0) {
+                    atomicOr(&state->error, ERR_IND_RANGE);
+                }
+            }
+        }
+    };
     // with the one-step lag a last pass delivers what the final neuron update left pending
     const unsigned long long passes = L.num_steps + lag;
-    for(unsigned long long step = 0; step < passes; step++) {
+    for(step = 0; step < passes; step++) {
         if(prof) c0 = clock64();
+        // probe 6: from the publication of the last step's counts to the start of this header
+        if(prof && blockIdx.x == 0 && publishedAt) state->probe[6] += (unsigned long long)(c0 - publishedAt);
         const bool drain = (step == L.num_steps);
         // every CTA has to finish the last neuron update before its counts go out
         if(drain && L.world > 1) gridArrive(L.barrier, epoch);
@@ -325,6 +454,8 @@ fusedStepKernel(FusedLaunch L)
                     const long long expected = (long long)(done0 + step) - (long long)(src.delay + lag);
                     if(expected > 0) {
                         cnt = awaitWord(&src.spk_tag[rslot], (unsigned long long)expected, state);
+                        // probe 4: header start to the count word of source 0 being there
+                        if(prof && blockIdx.x == 0 && si == 0) state->probe[4] += (unsigned long long)(clock64() - c0);
                         const unsigned long long *wire = src.spk_wire + (unsigned long long)rslot * src.num_src;
                         unsigned long long words[FUSED_PREFETCH_IDS];
                         #pragma unroll
@@ -356,55 +487,9 @@ fusedStepKernel(FusedLaunch L)
         if(L.world > 1 && (__ldcg(&state->error) & ERR_EXCHANGE_TIMEOUT)) return;
         if(prof && L.cta_cycles) L.cta_cycles[4ull * gridDim.x + blockIdx.x] += (unsigned long long)(clock64() - c0);
 
-        // ---------------- phase A: presynaptic update ------------------------------
-        for(unsigned int base = 0; base < L.num_sources; base += 32u) {
-            const unsigned int cnt = (base + lane < L.num_sources) ? headCnt[base + lane] : 0u;
-            const unsigned int per = (base + lane < L.num_sources) ? L.sources[base + lane].item_count : 0u;
-            unsigned int incl = cnt * per;
-            #pragma unroll
-            for(int o = 1; o < 32; o <<= 1) {
-                const unsigned int v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
-                if(lane >= o) incl += v;
-            }
-            const unsigned int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
-            for(unsigned int it = gwarp; it < total; it += totalWarps) {
-                const unsigned int owner = __ffs(__ballot_sync(0xFFFFFFFFu, incl > it)) - 1u;
-                const unsigned int ownIncl = __shfl_sync(0xFFFFFFFFu, incl, owner);
-                const unsigned int ownPer = __shfl_sync(0xFFFFFFFFu, per, owner);
-                const unsigned int ownCnt = headCnt[base + owner];
-                const unsigned int rel = it - (ownIncl - ownCnt * ownPer);
-                const unsigned int s = rel / ownPer;
-                const unsigned int c = rel - s * ownPer;
-                const FusedSource &src = L.sources[base + owner];
-                unsigned int pre;
-                if(s < FUSED_PREFETCH_IDS) {
-                    pre = headIds[base + owner][s];
-                }
-                else if(src.spk_wire) {
-                    const long long expected = (long long)(done0 + step) - (long long)(src.delay + lag);
-                    pre = awaitWord(&src.spk_wire[(unsigned long long)headSlot[base + owner] * src.num_src + s],
-                                    (unsigned long long)expected, state);
-                }
-                else {
-                    pre = __ldcg(&src.spk[(unsigned long long)headSlot[base + owner] * src.num_src + s]);
-                }
-                const uint2 item = L.items[src.item_begin + c];
-                const b200_synapse_group &g = L.sgroups[item.x];
-                if(pre < g.num_src) {
-                    switch(g.ind_bytes) {
-                    case 1: fusedChunk<uint8_t>(g, pre, item.y, k + 1u - lag, lag, state); break;
-                    case 2: fusedChunk<uint16_t>(g, pre, item.y, k + 1u - lag, lag, state); break;
-                    default: fusedChunk<uint32_t>(g, pre, item.y, k + 1u - lag, lag, state); break;
-                    }
-                    if(L.count_events && item.y == 0 && lane == 0) {
-                        atomicAdd(&state->synaptic_events, (unsigned long long)__ldg(&g.row_length[pre]));
-                    }
-                }
-                else if(lane == 0) {
-                    atomicOr(&state->error, ERR_IND_RANGE);
-                }
-            }
-        }
+        // ---------------- phase A (A0): what the coming neuron update needs ----------------
+        if(lag) deliver(false);
+        else deliver(true);
         }   // delivery pass
         if(drain) break;
         if(prof) c1 = clock64();
@@ -417,7 +502,7 @@ fusedStepKernel(FusedLaunch L)
         }
         if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
         // lagging schedule: the lists of the step before are complete now
-        if(lag && step > 0) publishCounts(k, done0 + step);
+        if(lag && step > 0 && warp == 0) publishCounts(lane, k, done0 + step);
         if(prof) c2 = clock64();
 
         // ---------------- phase B: neuron update -----------------------------------
@@ -457,8 +542,37 @@ fusedStepKernel(FusedLaunch L)
         if(prof) c3 = clock64();
         if(!lag) {
             gridArrive(L.barrier, epoch);
+            const long long arrivedAt = L.profile ? clock64() : 0;
+            // sharded model: one warp waits for the last CTA and tells every process how many
+            // spikes each population emitted; the readers poll those words, so nobody else
+            // has to see the barrier complete before going on
+            if(L.world > 1 && blockIdx.x == 0 && warp == warpsPerBlock - 1u) {
+                unsigned long long polls = 0;
+                while(loadAcquire(L.barrier) < epoch) {
+                    if(++polls > BARRIER_SPIN_LIMIT) {
+                        atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
+                        break;
+                    }
+                }
+                const long long seen = clock64();
+                publishCounts(lane, k + 1u, done0 + step + 1);
+                if(L.profile && lane == 0) {
+                    // probe 0: this CTA's arrival to the barrier seen complete; probe 1: reading and sending the counts
+                    const long long sent = clock64();
+                    state->probe[0] += (unsigned long long)(seen - arrivedAt);
+                    state->probe[1] += (unsigned long long)(sent - seen);
+                    publishedAt = sent;
+                }
+            }
+            // ---------------- phase A1: everything the next neuron update does not need ----------
+            deliver(false);
+            // probe 2: phase A1 on CTA 0; probe 3: what is left of the barrier after it
+            const long long deliveredAt = prof ? clock64() : 0;
             if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
-            publishCounts(k + 1u, done0 + step + 1);
+            if(prof && blockIdx.x == 0) {
+                state->probe[2] += (unsigned long long)(deliveredAt - arrivedAt);
+                state->probe[3] += (unsigned long long)(clock64() - deliveredAt);
+            }
         }
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {
@@ -480,7 +594,7 @@ fusedStepKernel(FusedLaunch L)
     }
     if(lag && L.world > 1) {
         if(!gridWait(L.barrier, epoch, &barrierOk, state)) return;
-        publishCounts(k, done0 + L.num_steps);
+        if(warp == 0) publishCounts(lane, k, done0 + L.num_steps);
     }
     if(mine && myActive) storeNeuron(L.neuron.groups[myGroup], myIndex, regs, true);
     if(gthread == 0) {

@@ -330,14 +330,14 @@ __device__ __forceinline__ void neuronEmit(const NeuronLaunch &L, const b200_neu
         float *st = g.spike_times + ((unsigned long long)b * slots) * N;
         st[(unsigned long long)wslot * N + i] = spiked ? t : loadShared<COHERENT>(&st[(unsigned long long)ringSlot(k, slots) * N + i]);
     }
-    // recording: bit i%32 of word i/32 (backendSIMT.cc:617-660)
+    // recording: the updated slice only, bit j%32 of word j/32 for its j-th neuron
+    // (backendSIMT.cc:617-660 for a whole population)
     if(g.record_spk && L.num_recording_timesteps) {
-        const unsigned int words = (N + 31u) / 32u;
-        // first_neuron is a multiple of 32, so a warp covers exactly one word;
-        // only the writing lane pays for the 64-bit modulo
-        if(lane == 0 && local < ((g.num_update + 31u) & ~31u) && (i / 32u) < words) {
+        const unsigned int words = (g.num_update + 31u) / 32u;
+        // a warp covers exactly one word; only the writing lane pays for the 64-bit modulo
+        if(lane == 0 && (local / 32u) < words) {
             unsigned int *rec = g.record_spk + ((timestep % L.num_recording_timesteps) * L.batch + b) * words;
-            rec[i / 32u] = ballot;
+            rec[local / 32u] = ballot;
         }
     }
 }

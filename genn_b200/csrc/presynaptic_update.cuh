@@ -79,7 +79,7 @@ template<> struct IndLoad<uint32_t>
 template<typename IndT>
 __device__ __forceinline__ void sparseQuad(const b200_synapse_group &g, unsigned int pre, unsigned int quad,
                                            float *__restrict__ target, unsigned int denFront,
-                                           StepState *state, unsigned int minDelay = 0u)
+                                           StepState *state, unsigned int zeroDelay = 0u)
 {
     // The row length and the row data are fetched TOGETHER (one memory round
     // trip, not two): the quad's address does not depend on the length, and a
@@ -116,15 +116,15 @@ __device__ __forceinline__ void sparseQuad(const b200_synapse_group &g, unsigned
                 continue;
             }
             if(D) {
-                const unsigned int delay = (dw >> (8 * j)) & 0xFFu;
-                // the caller relies on every delay being at least minDelay steps and, if that
-                // is not zero, on none wrapping around the ring
-                if(delay < minDelay || (minDelay && delay >= D)) {
-                    atomicOr(&state->error, ERR_DELAY_RANGE);
+                unsigned int slot = denFront + ((dw >> (8 * j)) & 0xFFu);
+                while(slot >= D) slot -= D;         // a delay of the ring length or more wraps around
+                // zeroDelay says what to do with a synapse that arrives in the same step (its
+                // slot is the front one): 0 deliver it, 1 the caller relies on there being
+                // none, 2 somebody else delivers it
+                if(zeroDelay && slot == denFront) {
+                    if(zeroDelay == 1u) atomicOr(&state->error, ERR_DELAY_RANGE);
                     continue;
                 }
-                unsigned int slot = denFront + delay;
-                while(slot >= D) slot -= D;
                 redAdd(target + (unsigned long long)slot * numTrg + p, w[j]);
             }
             else {

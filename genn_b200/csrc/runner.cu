@@ -22,6 +22,8 @@
 #include "postsynaptic_update.cuh"
 #include "init.cuh"
 #include "fused_step.cuh"
+#include "urgent.cuh"
+#include "stream_step.cuh"
 #include "owner_step.cuh"
 
 using namespace b200;
@@ -135,6 +137,26 @@ struct b200_runner
     bool lagEligible = false;
     unsigned int *lagScan = nullptr;
     std::vector<b200_synapse_group> fusedGroups;    // host copy of the SPARSE groups the kernel serves
+    // split delivery (fused_step.cuh): private tables of the synapses that arrive in the same step
+    bool useSplit = true;
+    int streamWarpsWanted = -1;                     // -1: as many as the neuron slots leave free, 0: none
+    unsigned int streamWarps = 0;                   // of the current tables (0: fusedStepKernel)
+    unsigned int slotsPerCta = 0;
+    std::vector<unsigned int> urgentStride;         // per SPARSE group: its longest urgent row (0: none)
+    unsigned int *urgentOffsets = nullptr;          // row offsets of all groups, one after the other
+    uint2 *urgentEntries = nullptr;
+    FusedUrgent *fusedUrgent = nullptr;             // device copy for the kernel, or NULL
+    enum Schedule { PLAIN = 0, SPLIT = 1, LAG = 2 };
+    Schedule schedule = PLAIN;
+
+    void dropUrgent()
+    {
+        urgentStride.clear();
+        if(urgentOffsets) cudaFree(urgentOffsets);
+        if(urgentEntries) cudaFree(urgentEntries);
+        if(fusedUrgent) cudaFree(fusedUrgent);
+        urgentOffsets = nullptr; urgentEntries = nullptr; fusedUrgent = nullptr;
+    }
 
     // spike exchange of a sharded model
     unsigned char *arena = nullptr;
@@ -429,6 +451,136 @@ int prepareOwner(b200_runner *r, const std::vector<b200_synapse_group> &sparse, 
     return B200_OK;
 }
 
+// Tables of the persistent fused-step kernel for the current schedule: spike
+// sources, the two item lists of each, thread slots, shared-memory budget, grid.
+int buildFusedTables(b200_runner *r)
+{
+    if(r->fusedSlotStart) { cudaFree(r->fusedSlotStart); r->fusedSlotStart = nullptr; }
+    if(r->fusedSources) { cudaFree(r->fusedSources); r->fusedSources = nullptr; }
+    if(r->fusedItems) { cudaFree(r->fusedItems); r->fusedItems = nullptr; }
+    if(!r->fusedEligible) return B200_OK;
+    const std::vector<b200_synapse_group> &sparse = r->fusedGroups;
+    std::vector<unsigned int> slotStart{0};
+    for(const auto &g : r->neuronGroups) slotStart.push_back(slotStart.back() + ((g.num_update + 31u) & ~31u));
+    std::vector<FusedSource> sources;
+    std::vector<std::vector<uint2>> perSource;
+    std::vector<std::vector<uint2>> perSourceUrgent;
+    for(size_t gi = 0; gi < sparse.size(); gi++) {
+        const auto &g = sparse[gi];
+        // which list the group's full-row chunks go to, and whether it has a table of urgent synapses
+        const bool ring = g.max_den_delay >= 2 && g.d;
+        const bool later = (r->schedule == b200_runner::LAG) || (r->schedule == b200_runner::SPLIT && ring);
+        const unsigned int urgentStride = (r->schedule == b200_runner::SPLIT && gi < r->urgentStride.size())
+            ? r->urgentStride[gi] : 0u;
+        // a sharded source population contributes one source per process section
+        const unsigned int sections = std::max(1u, g.src_sections);
+        const unsigned int chunks = (g.row_stride + 3 + FUSED_CHUNK - 1) / FUSED_CHUNK;
+        for(unsigned int sec = 0; sec < sections; sec++) {
+            const unsigned int *cntPtr = g.src_spk_cnt + sec * g.src_cnt_section_stride;
+            size_t si = 0;
+            for(; si < sources.size(); si++) {
+                if(sources[si].spk_cnt == cntPtr && sources[si].delay == g.axonal_delay) break;
+            }
+            if(si == sources.size()) {
+                FusedSource src{};
+                src.spk_cnt = cntPtr;
+                src.spk = g.src_spk + sec * g.src_spk_section_stride;
+                src.num_src = g.src_spk_slot_stride ? g.src_spk_slot_stride : g.num_src;   // list capacity
+                src.slots = g.src_delay_slots;
+                src.delay = g.axonal_delay;
+                src.spk_tag = g.src_spk_tag
+                    ? reinterpret_cast<const unsigned long long*>(g.src_spk_tag + sec * g.src_cnt_section_stride) : nullptr;
+                src.spk_wire = g.src_spk_wire
+                    ? reinterpret_cast<const unsigned long long*>(g.src_spk_wire + sec * g.src_spk_section_stride) : nullptr;
+                sources.push_back(src);
+                perSource.emplace_back();
+                perSourceUrgent.emplace_back();
+            }
+            auto &rows = later ? perSource[si] : perSourceUrgent[si];
+            for(unsigned int c = 0; c < chunks; c++) rows.push_back(make_uint2((unsigned int)gi, c));
+            for(unsigned int c = 0; c < (urgentStride + 31u) / 32u; c++) {
+                perSourceUrgent[si].push_back(make_uint2((unsigned int)gi, c | FUSED_URGENT_TABLE));
+            }
+        }
+    }
+    std::vector<uint2> items;
+    for(size_t si = 0; si < sources.size(); si++) {
+        sources[si].item_begin = (unsigned int)items.size();
+        sources[si].item_count = (unsigned int)perSource[si].size();
+        items.insert(items.end(), perSource[si].begin(), perSource[si].end());
+        sources[si].urgent_begin = (unsigned int)items.size();
+        sources[si].urgent_count = (unsigned int)perSourceUrgent[si].size();
+        items.insert(items.end(), perSourceUrgent[si].begin(), perSourceUrgent[si].end());
+    }
+    if(sources.size() > FUSED_MAX_SOURCES) {
+        return fail(B200_ERR_INVALID, "%zu spike sources exceed the %u the persistent kernel handles",
+                    sources.size(), (unsigned int)FUSED_MAX_SOURCES);
+    }
+    r->fusedNumSources = (unsigned int)sources.size();
+    r->fusedNumItems = (unsigned int)items.size();
+    r->fusedSmemBytes = align16(sizeof(b200_neuron_group) * r->neuronGroups.size()) +
+                        align16(sizeof(b200_synapse_group) * sparse.size()) +
+                        align16(sizeof(FusedSource) * sources.size()) + align16(sizeof(uint2) * items.size()) +
+                        align16(sizeof(unsigned int) * slotStart.size()) +
+                        (r->fusedUrgent ? align16(sizeof(FusedUrgent) * sparse.size()) : 0);
+    r->fusedStage = r->fusedSmemBytes <= 200 * 1024;
+    {
+        // SPLIT schedule: the warp-specialised kernel, if the neuron slots (dealt out evenly over one
+        // CTA per SM) leave at least four warps per CTA free for streaming
+        r->streamWarps = 0;
+        r->slotsPerCta = 0;
+        int sms = 0;
+        CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device));
+        if(r->schedule == b200_runner::SPLIT && r->fusedStage && r->streamWarpsWanted != 0 && sms > 0) {
+            const unsigned int perCta = ((slotStart.back() + sms - 1) / sms + 31u) & ~31u;
+            const unsigned int warps = FUSED_BLOCK / 32;
+            const unsigned int chainMin = std::max(8u, perCta / 32u);
+            if(chainMin + 4u <= warps) {
+                unsigned int stream = warps - chainMin;
+                if(r->streamWarpsWanted > 0) stream = std::min(stream, (unsigned int)r->streamWarpsWanted);
+                r->streamWarps = stream;
+                r->slotsPerCta = perCta;
+            }
+        }
+        int e = withNeuronShape(r, [&](auto P, auto C) -> int {
+            auto fused = fusedStepKernel<decltype(P)::value, decltype(C)::value>;
+            auto stream = streamStepKernel<decltype(P)::value, decltype(C)::value>;
+            auto kernel = r->streamWarps ? stream : fused;
+            r->fusedKernel = (const void*)kernel;
+            if(r->fusedStage) {
+                CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->fusedSmemBytes));
+            }
+            int perSM = 0;
+            CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSM, kernel, FUSED_BLOCK,
+                                                                   r->fusedStage ? r->fusedSmemBytes : 0));
+            r->fusedPerSM = perSM;
+            return B200_OK;
+        });
+        if(e) return e;
+    }
+    CUDA_TRY(cudaMalloc(&r->fusedSlotStart, sizeof(unsigned int) * slotStart.size()));
+    CUDA_TRY(cudaMemcpy(r->fusedSlotStart, slotStart.data(), sizeof(unsigned int) * slotStart.size(), cudaMemcpyHostToDevice));
+    if(!sources.empty()) {
+        CUDA_TRY(cudaMalloc(&r->fusedSources, sizeof(FusedSource) * sources.size()));
+        CUDA_TRY(cudaMemcpy(r->fusedSources, sources.data(), sizeof(FusedSource) * sources.size(), cudaMemcpyHostToDevice));
+        CUDA_TRY(cudaMalloc(&r->fusedItems, sizeof(uint2) * items.size()));
+        CUDA_TRY(cudaMemcpy(r->fusedItems, items.data(), sizeof(uint2) * items.size(), cudaMemcpyHostToDevice));
+    }
+    if(!r->fusedBarrier) CUDA_TRY(cudaMalloc(&r->fusedBarrier, sizeof(unsigned long long)));
+    int perSM = r->fusedPerSM, sms = 0, coop = 0;
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device));
+    CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, r->device));
+    if(perSM < 1 || !coop) {
+        r->fusedEligible = false;
+    }
+    else {
+        if(r->fusedBlocksPerSM) perSM = std::min<int>(perSM, (int)r->fusedBlocksPerSM);
+        if(r->streamWarps) perSM = 1;       // its neuron slots were dealt out for one CTA per SM
+        r->fusedGrid = (unsigned int)(perSM * sms);
+    }
+    return B200_OK;
+}
+
 int prepare(b200_runner *r)
 {
     if(!r->dirty) return B200_OK;
@@ -467,96 +619,14 @@ int prepare(b200_runner *r)
     CUDA_TRY(r->learnTable.upload(learn, learnStarts, r->stream));
 
     // ---- tables of the persistent fused-step kernel --------------------------------
-    if(r->fusedSlotStart) { cudaFree(r->fusedSlotStart); r->fusedSlotStart = nullptr; }
-    if(r->fusedSources) { cudaFree(r->fusedSources); r->fusedSources = nullptr; }
-    if(r->fusedItems) { cudaFree(r->fusedItems); r->fusedItems = nullptr; }
     r->fusedEligible = (r->batch == 1 && postSpan.empty() && learn.empty() && !r->neuronGroups.empty());
     r->fusedGroups = sparse;
     r->lagStale = true;
-    if(r->fusedEligible) {
-        std::vector<unsigned int> slotStart{0};
-        for(const auto &g : r->neuronGroups) slotStart.push_back(slotStart.back() + ((g.num_update + 31u) & ~31u));
-        std::vector<FusedSource> sources;
-        std::vector<std::vector<uint2>> perSource;
-        for(size_t gi = 0; gi < sparse.size(); gi++) {
-            const auto &g = sparse[gi];
-            // a sharded source population contributes one source per process section
-            const unsigned int sections = std::max(1u, g.src_sections);
-            const unsigned int chunks = (g.row_stride + 3 + FUSED_CHUNK - 1) / FUSED_CHUNK;
-            for(unsigned int sec = 0; sec < sections; sec++) {
-                const unsigned int *cntPtr = g.src_spk_cnt + sec * g.src_cnt_section_stride;
-                size_t si = 0;
-                for(; si < sources.size(); si++) {
-                    if(sources[si].spk_cnt == cntPtr && sources[si].delay == g.axonal_delay) break;
-                }
-                if(si == sources.size()) {
-                    FusedSource src{};
-                    src.spk_cnt = cntPtr;
-                    src.spk = g.src_spk + sec * g.src_spk_section_stride;
-                    src.num_src = g.src_spk_slot_stride ? g.src_spk_slot_stride : g.num_src;   // list capacity
-                    src.slots = g.src_delay_slots;
-                    src.delay = g.axonal_delay;
-                    src.spk_tag = g.src_spk_tag
-                        ? reinterpret_cast<const unsigned long long*>(g.src_spk_tag + sec * g.src_cnt_section_stride) : nullptr;
-                    src.spk_wire = g.src_spk_wire
-                        ? reinterpret_cast<const unsigned long long*>(g.src_spk_wire + sec * g.src_spk_section_stride) : nullptr;
-                    sources.push_back(src);
-                    perSource.emplace_back();
-                }
-                for(unsigned int c = 0; c < chunks; c++) perSource[si].push_back(make_uint2((unsigned int)gi, c));
-            }
-        }
-        std::vector<uint2> items;
-        for(size_t si = 0; si < sources.size(); si++) {
-            sources[si].item_begin = (unsigned int)items.size();
-            sources[si].item_count = (unsigned int)perSource[si].size();
-            items.insert(items.end(), perSource[si].begin(), perSource[si].end());
-        }
-        if(sources.size() > FUSED_MAX_SOURCES) {
-            return fail(B200_ERR_INVALID, "%zu spike sources exceed the %u the persistent kernel handles",
-                        sources.size(), (unsigned int)FUSED_MAX_SOURCES);
-        }
-        r->fusedNumSources = (unsigned int)sources.size();
-        r->fusedNumItems = (unsigned int)items.size();
-        r->fusedSmemBytes = align16(sizeof(b200_neuron_group) * r->neuronGroups.size()) +
-                            align16(sizeof(b200_synapse_group) * sparse.size()) +
-                            align16(sizeof(FusedSource) * sources.size()) + align16(sizeof(uint2) * items.size()) +
-                            align16(sizeof(unsigned int) * slotStart.size());
-        r->fusedStage = r->fusedSmemBytes <= 200 * 1024;
-        {
-            int e = withNeuronShape(r, [&](auto P, auto C) -> int {
-                auto kernel = fusedStepKernel<decltype(P)::value, decltype(C)::value>;
-                r->fusedKernel = (const void*)kernel;
-                if(r->fusedStage) {
-                    CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->fusedSmemBytes));
-                }
-                int perSM = 0;
-                CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSM, kernel, FUSED_BLOCK,
-                                                                       r->fusedStage ? r->fusedSmemBytes : 0));
-                r->fusedPerSM = perSM;
-                return B200_OK;
-            });
-            if(e) return e;
-        }
-        CUDA_TRY(cudaMalloc(&r->fusedSlotStart, sizeof(unsigned int) * slotStart.size()));
-        CUDA_TRY(cudaMemcpy(r->fusedSlotStart, slotStart.data(), sizeof(unsigned int) * slotStart.size(), cudaMemcpyHostToDevice));
-        if(!sources.empty()) {
-            CUDA_TRY(cudaMalloc(&r->fusedSources, sizeof(FusedSource) * sources.size()));
-            CUDA_TRY(cudaMemcpy(r->fusedSources, sources.data(), sizeof(FusedSource) * sources.size(), cudaMemcpyHostToDevice));
-            CUDA_TRY(cudaMalloc(&r->fusedItems, sizeof(uint2) * items.size()));
-            CUDA_TRY(cudaMemcpy(r->fusedItems, items.data(), sizeof(uint2) * items.size(), cudaMemcpyHostToDevice));
-        }
-        if(!r->fusedBarrier) CUDA_TRY(cudaMalloc(&r->fusedBarrier, sizeof(unsigned long long)));
-        int perSM = r->fusedPerSM, sms = 0, coop = 0;
-        CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device));
-        CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, r->device));
-        if(perSM < 1 || !coop) {
-            r->fusedEligible = false;
-        }
-        else {
-            if(r->fusedBlocksPerSM) perSM = std::min<int>(perSM, (int)r->fusedBlocksPerSM);
-            r->fusedGrid = (unsigned int)(perSM * sms);
-        }
+    r->schedule = b200_runner::PLAIN;
+    r->dropUrgent();
+    {
+        const int e = buildFusedTables(r);
+        if(e) return e;
     }
     // ---- tables of the target-stationary persistent kernel -------------------------------
     {
@@ -629,93 +699,144 @@ int launchOwner(b200_runner *r, unsigned long long numSteps, unsigned long long 
     return B200_OK;
 }
 
-// Smallest dendritic delay over the synapses that exist, per SPARSE group.  A
-// delay that reaches the ring length counts as 0: it wraps around the ring and
-// arrives in the same step.  A group without dendritic delay reports 0.  One
-// warp per row.
-__global__ void minDelayKernel(const b200_synapse_group *groups, unsigned int *out)
-{
-    const b200_synapse_group &g = groups[blockIdx.y];
-    if(!g.max_den_delay) {
-        if(blockIdx.x == 0 && threadIdx.x == 0) out[blockIdx.y] = 0u;
-        return;
-    }
-    const unsigned int lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
-    const unsigned int D = g.max_den_delay;
-    unsigned int m = 0xFFFFFFFFu;
-    for(unsigned int row = blockIdx.x * warps + (threadIdx.x >> 5); row < g.num_src; row += gridDim.x * warps) {
-        const unsigned int len = min(g.row_length[row], g.row_stride);
-        const uint8_t *d = g.d + (unsigned long long)row * g.row_stride;
-        for(unsigned int j = lane; j < len; j += 32u) {
-            const unsigned int v = d[j];
-            m = min(m, (v >= D) ? 0u : v);
-        }
-    }
-    #pragma unroll
-    for(int o = 16; o; o >>= 1) m = min(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
-    if(lane == 0 && m != 0xFFFFFFFFu) atomicMin(&out[blockIdx.y], m);
-}
-
-// Decide whether the persistent kernel may deliver spikes one step late: every
-// SPARSE group needs a dendritic-delay ring and no synapse with delay zero.
-int scanDelays(b200_runner *r)
+// Choose the schedule of the persistent kernel from the dendritic delays that
+// are actually in the arrays, and build what it needs:
+//   LAG    every SPARSE group has a delay ring and no synapse arrives in the same
+//          step: spikes are delivered one step late, one grid barrier per step;
+//   SPLIT  the synapses that do arrive in the same step are copied into tables of
+//          their own and delivered before the neuron update, all others after it;
+//   PLAIN  everything before the neuron update.
+int refreshSchedule(b200_runner *r)
 {
     r->lagStale = false;
     r->lagEligible = false;
-    const unsigned int n = r->sparseTable.num;
-    if(n == 0) { r->lagEligible = true; return B200_OK; }
-    for(const auto &g : r->fusedGroups) {
-        if(g.max_den_delay < 2 || !g.d) return B200_OK;
+    r->schedule = b200_runner::PLAIN;
+    r->dropUrgent();
+    if(!r->fusedEligible) return B200_OK;
+    const auto &groups = r->fusedGroups;
+    const size_t n = groups.size();
+    // rows of every group with a delay ring, one after the other, each group with one extra
+    // cell so that offsets[row + 1] exists for its last row
+    std::vector<size_t> rowBase(n, 0);
+    size_t totalRows = 0;
+    bool anyRing = false;
+    for(size_t gi = 0; gi < n; gi++) {
+        const auto &g = groups[gi];
+        if(g.max_den_delay < 2 || !g.d || g.num_src == 0) continue;
+        anyRing = true;
+        rowBase[gi] = totalRows;
+        totalRows += (size_t)g.num_src + 1;
     }
-    // a list is read one step later and, in a sharded model, a peer may already be
-    // writing two steps ahead: the queue needs delay + 4 slots
-    for(const auto &s : r->fusedGroups) {
-        if(s.axonal_delay + 4 > s.src_delay_slots) return B200_OK;
+    if((r->useLag || r->useSplit) && anyRing && totalRows < (1ull << 31)) {
+        CUDA_TRY(cudaMalloc(&r->urgentOffsets, sizeof(unsigned int) * (totalRows + 1)));
+        CUDA_TRY(cudaMemsetAsync(r->urgentOffsets, 0, sizeof(unsigned int) * (totalRows + 1), r->stream));
+        for(size_t gi = 0; gi < n; gi++) {
+            const auto &g = groups[gi];
+            if(g.max_den_delay < 2 || !g.d || g.num_src == 0) continue;
+            urgentCountKernel<<<std::min(1184u, (g.num_src + 7u) / 8u), 256, 0, r->stream>>>(g, r->urgentOffsets + rowBase[gi]);
+            CUDA_TRY(cudaPeekAtLastError());
+            r->launches++;
+        }
+        // counts -> offsets on the host (a few MB once per change of the delay arrays)
+        std::vector<unsigned int> cells(totalRows + 1);
+        CUDA_TRY(cudaMemcpyAsync(cells.data(), r->urgentOffsets, sizeof(unsigned int) * (totalRows + 1),
+                                 cudaMemcpyDeviceToHost, r->stream));
+        CUDA_TRY(cudaStreamSynchronize(r->stream));
+        r->urgentStride.assign(n, 0u);
+        unsigned long long total = 0;
+        for(size_t gi = 0; gi < n; gi++) {
+            const auto &g = groups[gi];
+            if(g.max_den_delay < 2 || !g.d || g.num_src == 0) continue;
+            unsigned int longest = 0;
+            for(size_t row = 0; row <= g.num_src; row++) {
+                unsigned int &cell = cells[rowBase[gi] + row];
+                const unsigned int len = (row < g.num_src) ? cell : 0u;
+                longest = std::max(longest, len);
+                cell = (unsigned int)total;
+                total += len;
+            }
+            r->urgentStride[gi] = longest;
+        }
+        // a list read one step late, with a peer possibly writing two steps ahead, needs delay + 4 slots
+        bool lagOk = (total == 0);
+        for(size_t gi = 0; gi < n; gi++) {
+            const auto &g = groups[gi];
+            if(g.max_den_delay < 2 || !g.d || g.axonal_delay + 4 > g.src_delay_slots) lagOk = false;
+        }
+        r->lagEligible = lagOk;
+        if(r->useLag && lagOk && (!r->sharded() || r->lagAgreed)) {
+            r->schedule = b200_runner::LAG;
+        }
+        else if(r->useSplit && total < (1ull << 31)) {
+            r->schedule = b200_runner::SPLIT;
+            if(total) {
+                CUDA_TRY(cudaMemcpyAsync(r->urgentOffsets, cells.data(), sizeof(unsigned int) * (totalRows + 1),
+                                         cudaMemcpyHostToDevice, r->stream));
+                CUDA_TRY(cudaMalloc(&r->urgentEntries, sizeof(uint2) * total));
+                std::vector<FusedUrgent> table(n);
+                for(size_t gi = 0; gi < n; gi++) {
+                    const auto &g = groups[gi];
+                    table[gi] = FusedUrgent{r->urgentOffsets + rowBase[gi], r->urgentEntries, r->urgentStride[gi], 0u};
+                    if(!r->urgentStride[gi]) continue;
+                    const unsigned int blocks = std::min(1184u, (g.num_src + 7u) / 8u);
+                    const int e = withIndType(g.ind_bytes, [&](auto tag) -> int {
+                        using IndT = decltype(tag);
+                        urgentFillKernel<IndT><<<blocks, 256, 0, r->stream>>>(g, r->urgentOffsets + rowBase[gi], r->urgentEntries);
+                        return B200_OK;
+                    });
+                    if(e) return e;
+                    CUDA_TRY(cudaPeekAtLastError());
+                    r->launches++;
+                }
+                CUDA_TRY(cudaMalloc(&r->fusedUrgent, sizeof(FusedUrgent) * n));
+                CUDA_TRY(cudaMemcpyAsync(r->fusedUrgent, table.data(), sizeof(FusedUrgent) * n, cudaMemcpyHostToDevice, r->stream));
+                CUDA_TRY(cudaStreamSynchronize(r->stream));
+            }
+        }
+        if(!r->urgentEntries) {
+            cudaFree(r->urgentOffsets);
+            r->urgentOffsets = nullptr;
+            r->urgentStride.assign(n, 0u);
+        }
     }
-    if(!r->lagScan) CUDA_TRY(cudaMalloc(&r->lagScan, sizeof(unsigned int) * 4096));
-    if(n > 4096) return B200_OK;
-    CUDA_TRY(cudaMemsetAsync(r->lagScan, 0xFF, sizeof(unsigned int) * n, r->stream));
-    minDelayKernel<<<dim3(296, n), 256, 0, r->stream>>>(r->sparseTable.d, r->lagScan);
-    CUDA_TRY(cudaPeekAtLastError());
-    std::vector<unsigned int> mins(n);
-    CUDA_TRY(cudaMemcpyAsync(mins.data(), r->lagScan, sizeof(unsigned int) * n, cudaMemcpyDeviceToHost, r->stream));
-    CUDA_TRY(cudaStreamSynchronize(r->stream));
-    r->launches++;
-    for(unsigned int m : mins) {
-        if(m == 0) return B200_OK;
-    }
-    r->lagEligible = true;
-    return B200_OK;
+    return buildFusedTables(r);
 }
 
 // true if [p, p + bytes) overlaps an array the delay scan depends on
 bool touchesDelays(const b200_runner *r, const void *p, size_t bytes)
 {
     const unsigned char *a = static_cast<const unsigned char*>(p), *b = a + bytes;
+    auto overlaps = [&](const void *start, size_t size) {
+        const unsigned char *s0 = static_cast<const unsigned char*>(start);
+        return s0 && a < s0 + size && b > s0;
+    };
     for(const auto &g : r->fusedGroups) {
         if(!g.max_den_delay || !g.d) continue;
         const size_t synapses = (size_t)g.num_src * g.row_stride;
-        const unsigned char *d0 = reinterpret_cast<const unsigned char*>(g.d);
-        const unsigned char *l0 = reinterpret_cast<const unsigned char*>(g.row_length);
-        if(a < d0 + synapses && b > d0) return true;
-        if(a < l0 + sizeof(unsigned int) * g.num_src && b > l0) return true;
+        // the urgent tables copy indices and weights, the schedule depends on delays and row lengths
+        if(overlaps(g.d, synapses) || overlaps(g.row_length, sizeof(unsigned int) * g.num_src) ||
+           overlaps(g.ind, synapses * g.ind_bytes) || overlaps(g.g, synapses * sizeof(float))) return true;
     }
     return false;
 }
 
 int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long numRec)
 {
-    if(r->useLag && r->lagStale) {
+    if(r->lagStale) {
         const bool was = r->lagEligible;
-        const int e = scanDelays(r);
+        const int e = refreshSchedule(r);
         if(e) return e;
-        if(r->sharded() && r->lagAgreed && was && !r->lagEligible) {
+        if(r->sharded() && r->lagAgreed && r->useLag && was && !r->lagEligible) {
             return fail(B200_ERR_STATE, "a synapse with dendritic delay 0 appeared after the processes of this sharded "
                                         "model agreed to deliver spikes one step late");
         }
     }
     FusedLaunch L;
-    L.lag = (r->useLag && r->lagEligible && (!r->sharded() || r->lagAgreed)) ? 1u : 0u;
+    L.lag = (r->schedule == b200_runner::LAG) ? 1u : 0u;
+    L.skip_urgent = (r->schedule == b200_runner::SPLIT) ? 1u : 0u;
+    L.urgent = r->fusedUrgent;
+    L.stream_warps = r->streamWarps;
+    L.slots_per_cta = r->slotsPerCta;
     L.neuron.groups = r->neuronTable.d;
     L.neuron.block_start = r->neuronTable.blockStart;
     L.neuron.num_groups = r->neuronTable.num;
@@ -937,6 +1058,7 @@ int b200_runner_destroy(b200_runner *r)
     if(r->fusedItems) cudaFree(r->fusedItems);
     if(r->fusedBarrier) cudaFree(r->fusedBarrier);
     if(r->lagScan) cudaFree(r->lagScan);
+    r->dropUrgent();
     if(r->fusedCtaCycles) cudaFree(r->fusedCtaCycles);
     r->dropOwner();
     for(unsigned int p = 0; p < B200_MAX_RANKS; p++) {
@@ -1126,8 +1248,10 @@ int b200_set_option(b200_runner *r, const char *name, double value)
     else if(n == "count_events") r->countEvents = (value != 0.0);
     else if(n == "use_graph") r->useGraph = (value != 0.0);
     else if(n == "use_fused") r->useFused = (value != 0.0);
-    else if(n == "use_lag") r->useLag = (value != 0.0);
-    else if(n == "lag_agreed") r->lagAgreed = (value != 0.0);
+    else if(n == "use_lag") { r->useLag = (value != 0.0); r->lagStale = true; }
+    else if(n == "use_split") { r->useSplit = (value != 0.0); r->lagStale = true; }
+    else if(n == "stream_warps") { r->streamWarpsWanted = (int)value; r->lagStale = true; }
+    else if(n == "lag_agreed") { r->lagAgreed = (value != 0.0); r->lagStale = true; }
     else if(n == "rescan_delays") r->lagStale = true;
     else if(n == "fused_profile") r->fusedProfile = (value != 0.0);
     else if(n == "use_owner") { r->useOwner = (value != 0.0); r->dirty = true; }
@@ -1323,7 +1447,7 @@ int b200_synchronize(b200_runner *r)
         return fail(B200_ERR_DEVICE_CHECK, "device-side check failed (flags 0x%x:%s%s%s%s%s)", err,
                     (err & ERR_SPIKE_OVERFLOW) ? " spike list overflow" : "",
                     (err & ERR_IND_RANGE) ? " index or row length out of range" : "",
-                    (err & ERR_DELAY_RANGE) ? " delay out of range" : "",
+                    (err & ERR_DELAY_RANGE) ? " a synapse arriving in the same step appeared after the schedule was chosen (option rescan_delays)" : "",
                     (err & ERR_BARRIER_TIMEOUT) ? " grid barrier timed out" : "",
                     (err & ERR_EXCHANGE_TIMEOUT) ? " spikes of another process did not arrive in time" : "");
     }
@@ -1354,17 +1478,39 @@ int b200_get_steps_done(b200_runner *r, uint64_t *steps)
 int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
 {
     const std::string n(name);
+    if(n == "stream_warps") {
+        int e = prepare(r);
+        if(e) return e;
+        if(r->fusedEligible && r->lagStale) {
+            e = refreshSchedule(r);
+            if(e) return e;
+        }
+        *value = r->streamWarps;
+        return B200_OK;
+    }
+    if(n == "schedule") {
+        // of the next persistent launch: 0 everything before the neuron update, 1 only the synapses that
+        // arrive in the same step before it (split delivery), 2 spikes one step late (one barrier per step)
+        int e = prepare(r);
+        if(e) return e;
+        if(r->fusedEligible && r->lagStale) {
+            e = refreshSchedule(r);
+            if(e) return e;
+        }
+        *value = (uint64_t)r->schedule;
+        return B200_OK;
+    }
     if(n == "lag_eligible" || n == "lag") {
         // whether this process may deliver spikes one step late (scans the delay arrays if
         // they changed) / whether its next persistent launch will
         int e = prepare(r);
         if(e) return e;
-        if(r->useLag && r->fusedEligible && r->lagStale) {
-            e = scanDelays(r);
+        if(r->fusedEligible && r->lagStale) {
+            e = refreshSchedule(r);
             if(e) return e;
         }
         const bool can = r->useLag && r->fusedEligible && r->lagEligible;
-        *value = (n == "lag") ? (can && r->useFused && (!r->sharded() || r->lagAgreed)) : can;
+        *value = (n == "lag") ? (r->useFused && r->fusedEligible && r->schedule == b200_runner::LAG) : can;
         return B200_OK;
     }
     CUDA_TRY(cudaStreamSynchronize(r->stream));
@@ -1376,6 +1522,7 @@ int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
     else if(n == "cycles_barrier_a") *value = s.phase_cycles[1];
     else if(n == "cycles_neuron") *value = s.phase_cycles[2];
     else if(n == "cycles_barrier_b") *value = s.phase_cycles[3];
+    else if(n.size() == 6 && n.compare(0, 5, "probe") == 0 && n[5] >= '0' && n[5] <= '7') *value = s.probe[n[5] - '0'];
     else if(n == "timestep") *value = s.timestep;
     else if(n == "steps_done") *value = s.steps_done;
     else return fail(B200_ERR_INVALID, "unknown counter %s", name);

@@ -189,7 +189,9 @@ class Plan:
             if p.spike_time_required:
                 self._new(f"{p.name}.sT", np.float32, (B, slots, p.n), TIME_MIN)
             if p.record and self.num_recording_timesteps:
-                self._new(f"{p.name}.record", np.uint32, (self.num_recording_timesteps, B, (p.n + 31) // 32))
+                # a process records the slice it updates
+                lo, hi = (p.shard_bounds[self.shard[0]], p.shard_bounds[self.shard[0] + 1]) if self.shard else (0, p.n)
+                self._new(f"{p.name}.record", np.uint32, (self.num_recording_timesteps, B, (hi - lo + 31) // 32))
         for c in net.css:
             for v, arr in c.vars.items():
                 self._new(f"{c.name}.{v}", np.float32, (B, net.pop(c.pop).n), arr)

@@ -294,6 +294,13 @@ class Runtime:
         delay is at least one step), which lets it drop the second grid barrier."""
         return bool(self.counter("lag"))
 
+    @property
+    def schedule(self) -> int:
+        """Schedule of the next persistent launch: 0 every synapse before the neuron update,
+        1 only the synapses that arrive in the same step before it (split delivery),
+        2 spikes delivered one step late (one grid barrier per step)."""
+        return self.counter("schedule")
+
     def cta_cycles(self) -> np.ndarray:
         """[num_ctas, 4] cycles per phase of the persistent kernel (option fused_profile)."""
         out = np.zeros((1024, 4), dtype=np.uint64)
@@ -374,14 +381,16 @@ class Runtime:
         if ts < T:
             raise Exception("Event recording data can only be accessed once buffer is full")
         p = self.net.pop(pop)
+        # a process of a sharded model records the slice of the population it updates
+        lo, hi = (p.shard_bounds[self.shard[0]], p.shard_bounds[self.shard[0] + 1]) if self.shard else (0, p.n)
         start = (ts - T) * self.net.dt
         # the buffer is a ring over timestep % T: rotate so index 0 is the oldest step
         words = np.roll(self._rec_host[pop], -(ts % T), axis=0)
         out = []
         for b in range(self.net.batch_size):
-            bits = np.unpackbits(np.ascontiguousarray(words[:, b, :]).view(np.uint8), axis=1, bitorder="little")[:, :p.n]
-            step, ids = np.nonzero(bits)
-            out.append((start + step * self.net.dt, ids.astype(np.uint32)))
+            bits = np.unpackbits(np.ascontiguousarray(words[:, b, :]).view(np.uint8), axis=1, bitorder="little")
+            step, ids = np.nonzero(bits[:, :hi - lo])
+            out.append((start + step * self.net.dt, (ids + lo).astype(np.uint32)))
         return out
 
     # -- measurement helpers ------------------------------------------------------

@@ -148,7 +148,8 @@ typedef struct b200_neuron_group {
     uint32_t *spk_cnt;         /* [batch][slots] */
     uint32_t *spk;             /* [batch][slots][N] */
     float    *spike_times;     /* sT [batch][slots][N] or NULL */
-    uint32_t *record_spk;      /* [recordingTimesteps][batch][ceil(N/32)] or NULL; bit i%32 of word i/32 */
+    uint32_t *record_spk;      /* [recordingTimesteps][batch][ceil(num_update/32)] or NULL; neuron first_neuron + j
+                                  is bit j%32 of word j/32 (the whole population when the process updates all of it) */
     b200_psm psm[B200_MAX_PSM];
     b200_current_source cs[B200_MAX_CS];
     uint32_t spk_slot_stride;  /* elements between two slots of `spk`; 0 = num_neurons.  A process that

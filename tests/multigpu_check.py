@@ -1,7 +1,7 @@
 """Child process of tests/test_multi_gpu.py: one rank of a model sharded by
 postsynaptic neuron over several GPUs.
 
-    python -m torch.distributed.run --nproc-per-node 2 tests/multigpu_check.py <case> [lag|two-barrier]
+    python -m torch.distributed.run --nproc-per-node 2 tests/multigpu_check.py <case> [lag|split|plain]
 
 Every rank builds the same network restricted to the synapses onto its slice,
 steps it with the persistent kernel (spike lists travel between the GPUs inside
@@ -26,7 +26,8 @@ def main():
     from tests import helpers
 
     name = sys.argv[1] if len(sys.argv) > 1 else "potjans_mini"
-    lag = (sys.argv[2] if len(sys.argv) > 2 else "lag") == "lag"
+    schedule = sys.argv[2] if len(sys.argv) > 2 else "lag"
+    lag = schedule == "lag"
     kw = dict(min_delay=0.1, extra_delay_slots=1) if name == "potjans_mini_d1" else {}
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     local = int(os.environ.get("LOCAL_RANK", rank))
@@ -39,7 +40,9 @@ def main():
     net = resolve(model)
     rt = Runtime(None, steps, device=local, shard=(rank, world), net=net)
     rt.set_option("use_lag", 1 if lag else 0)
-    assert rt.lagging == (lag and name == "potjans_mini_d1"), f"rank {rank}: lagging {rt.lagging}"
+    rt.set_option("use_split", 0 if schedule == "plain" else 1)
+    want_schedule = 0 if schedule == "plain" else 2 if (lag and name == "potjans_mini_d1") else 1
+    assert rt.schedule == want_schedule, f"rank {rank}: schedule {rt.schedule}, expected {want_schedule}"
     want = helpers.load_golden(name)
     spikes = {p.name: [] for p in net.pops}
     for s in range(steps):
@@ -64,6 +67,7 @@ def main():
         workloads.potjans(neuron_scale=0.005, seed=7, host_connectivity=True, background="dc", record=True,
                           shard=(rank, world), **kw)))
     rt2.set_option("use_lag", 1 if lag else 0)
+    rt2.set_option("use_split", 0 if schedule == "plain" else 1)
     dist.barrier()
     rt2.step_time(steps)
     rt2.synchronize()
@@ -79,7 +83,7 @@ def main():
     rt.close()
     rt2.close()
     if rank == 0:
-        print(f"multigpu_check ok: {world} ranks, {'lagging' if lag else 'two-barrier'} schedule, "
+        print(f"multigpu_check ok: {world} ranks, schedule {want_schedule}, "
               f"{sum(len(v) for v in spikes.values())} spikes")
     dist.destroy_process_group()
 

@@ -17,23 +17,34 @@ pytestmark = pytest.mark.gpu
 
 RTOL, ATOL = 1e-5, 2e-6
 
-# the time-step paths: target-stationary persistent kernel, persistent kernel with
-# global reductions (delivering spikes one step late where no synapse has delay 0,
-# and with that switched off), one launch per kernel
-PATHS = {"owner": (1, 1, 1), "persistent": (1, 0, 1), "persistent-two-barrier": (1, 0, 0), "per-kernel": (0, 0, 1)}
+# the time-step paths: target-stationary persistent kernel; persistent kernel with
+# global reductions in each of its schedules (spikes one step late where no synapse
+# arrives in the same step; only the same-step synapses before the neuron update;
+# everything before it; the split schedule on the warp-specialised kernel and on the
+# plain one); one launch per kernel.  (use_fused, use_owner, use_lag, use_split, stream_warps)
+PATHS = {"owner": (1, 1, 1, 1, -1), "persistent": (1, 0, 1, 1, -1), "persistent-split": (1, 0, 0, 1, -1),
+         "persistent-split-one-warp-set": (1, 0, 0, 1, 0), "persistent-plain": (1, 0, 0, 0, -1),
+         "per-kernel": (0, 0, 1, 1, -1)}
 # networks whose every synapse has a dendritic delay of at least one step
 LAG_CASES = {"potjans_mini_d1"}
+# networks with dendritic-delay rings (some of whose synapses may arrive in the same step)
+RING_CASES = {"potjans_mini", "potjans_mini_d1"}
 # networks the target-stationary kernel must accept (SPARSE, sorted rows, no learning)
 OWNER_CASES = {"ff_sparse", "ff_sparse_narrow", "potjans_mini", "potjans_mini_d1", "cond_delay", "izhikevich"}
 
 
 def _select(rt, path, name=None):
-    fused, owner, lag = PATHS[path]
+    fused, owner, lag, split, stream = PATHS[path]
     rt.set_option("use_fused", fused)
     rt.set_option("use_owner", owner)
     rt.set_option("use_lag", lag)
-    if name is not None:
-        assert rt.lagging == (bool(lag) and name in LAG_CASES and rt.step_path()[0] >= 1), f"{name}: lag {rt.lagging}"
+    rt.set_option("use_split", split)
+    rt.set_option("stream_warps", stream)
+    if name is not None and rt.step_path()[0] >= 1:
+        want = 2 if (lag and name in LAG_CASES) else 1 if (split and name in RING_CASES) else 0
+        assert rt.schedule == want, f"{name}: schedule {rt.schedule}, expected {want}"
+        assert rt.lagging == (want == 2 and bool(fused))
+        assert (rt.counter("stream_warps") > 0) == (want == 1 and stream != 0), "warp-specialised kernel expected for the split schedule"
     if path == "owner" and name in OWNER_CASES:
         taken, why = rt.step_path()
         assert taken == 2, f"{name} should run on the target-stationary kernel: {why}"
@@ -178,15 +189,16 @@ def test_device_check_reports_bad_index():
         rt.synchronize()
 
 
-def test_launch_boundaries_of_the_lagging_schedule_leave_the_usual_state():
+@pytest.mark.parametrize("name,schedule", [("potjans_mini_d1", 2), ("potjans_mini", 1)])
+def test_launch_boundaries_of_every_schedule_leave_the_usual_state(name, schedule):
     """Persistent launches of odd lengths (spikes delivered one step late inside a
-    launch) alternate with steps on the per-kernel path: memory between launches
-    must be what the two-barrier schedule leaves, or the hand-over would lose or
-    double-deliver spikes."""
-    model, steps, dump_every = CASES["potjans_mini_d1"]()
+    launch, or only partly before the neuron update) alternate with steps on the
+    per-kernel path: memory between launches must be what the plain schedule
+    leaves, or the hand-over would lose or double-deliver spikes."""
+    model, steps, dump_every = CASES[name]()
     net = resolve(model)
     rt = _runtime(net, steps)
-    assert rt.lagging
+    assert rt.schedule == schedule
     done, chunk = 0, [1, 2, 1, 5, 3, 17, 1, 1, 40]
     i = 0
     while done < steps:
@@ -197,7 +209,7 @@ def test_launch_boundaries_of_the_lagging_schedule_leave_the_usual_state():
         i += 1
     rt.synchronize()
     rt.pull_recording_buffers()
-    want = helpers.load_golden("potjans_mini_d1")
+    want = helpers.load_golden(name)
     for p in net.pops:
         if not p.record:
             continue

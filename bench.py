@@ -413,7 +413,10 @@ def main():
                                     "persistent kernel, split delivery: synapses that arrive in the same step before the "
                                     "neuron update, all others behind it in the shadow of the second grid barrier",
                                     "persistent kernel, spikes delivered one step late (no synapse arrives in the same "
-                                    "step): one grid barrier per step"][rt.schedule],
+                                    "step): one grid barrier per step",
+                                    "warp-specialised persistent kernel: synapses with a delay of 0 or 1 step delivered by "
+                                    "the spiking thread inside the neuron update, all others streamed by dedicated warps "
+                                    "over the next two steps; one grid barrier per step"][rt.schedule],
                        "min_delay_ms": args.min_delay,
                        "l2": "working set (2.5 GB of synapses) exceeds L2; no flush needed",
                        "spikes_per_s_biological": spikes / sim_seconds,

@@ -58,10 +58,12 @@ __device__ __forceinline__ unsigned int findGroup(const unsigned int *__restrict
     return lo;
 }
 
-// fp32 add to global memory with no return value (compiles to a reduction)
+// fp32 add to GLOBAL memory with no return value.  The address space is spelled out: after a
+// reduction through a generic pointer the load/store unit holds back later generic accesses
+// (the staged tables in shared memory are read through generic pointers) until it completes.
 __device__ __forceinline__ void redAdd(float *addr, float v)
 {
-    atomicAdd(addr, v);
+    asm volatile("red.global.add.f32 [%0], %1;" :: "l"(__cvta_generic_to_global(addr)), "f"(v));
 }
 
 __device__ __forceinline__ unsigned int ringSlot(unsigned int k, unsigned int slots)

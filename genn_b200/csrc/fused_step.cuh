@@ -69,6 +69,8 @@
 
 namespace b200
 {
+struct NearRing;
+struct NearSpace;
 constexpr int FUSED_BLOCK = 768;          // one CTA per SM, 85 registers per thread
 constexpr unsigned int FUSED_CHUNK = 32 * PRE_VEC;          // synapses per warp item
 constexpr unsigned int FUSED_MAX_SOURCES = 256;             // (population, process, delay) spike sources per model
@@ -135,6 +137,12 @@ struct FusedLaunch
     // warp-specialised kernel (stream_step.cuh) only
     unsigned int stream_warps;           // warps per CTA that do nothing but deliver non-urgent synapses
     unsigned int slots_per_cta;          // neuron slots per CTA (a multiple of 32)
+    // "deliver at emission" mode of that kernel (near.cuh)
+    unsigned int emit;                   // 1: the spiking thread delivers its near synapses, one barrier per step
+    unsigned int num_rings;
+    const uint2 *near_table;
+    const struct NearRing *near_rings;   // [num_rings]
+    const struct NearSpace *near_spaces; // [neuron groups]
 };
 
 constexpr unsigned long long EXCHANGE_SPIN_LIMIT = 1ull << 23;

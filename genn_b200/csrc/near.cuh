@@ -1,0 +1,139 @@
+// Near-synapse tables of the warp-specialised kernel's "deliver at emission" mode.
+//
+// A synapse whose dendritic delay is 0 or 1 step (modulo the ring length: the
+// ring index is (front + d) mod D, as in the reference,
+// presynapticUpdateStrategySIMT.cc:57-389) is "near": its weight is needed by
+// one of the next two neuron updates.  For a cortical model that is one to
+// three synapses in a hundred.  These kernels copy the near synapses of ALL
+// SPARSE groups into one table keyed by the spiking neuron (one row per neuron
+// of every source population, whatever group the synapse belongs to):
+//
+//     entry = (target index << 8 | ring << 1 | delay (0 or 1),  weight bits)
+//
+// where `ring` numbers the dendritic-delay rings of the model (one per
+// postsynaptic model of a neuron group).  Rows of one source population have a
+// fixed power-of-two length (its longest row, rounded up) and are padded with
+// zero entries, so the id of a spiking neuron leads to its entries in ONE
+// memory round trip, with no row length or offset to fetch first.
+//
+// The thread that makes a neuron spike delivers these few synapses itself,
+// inside the neuron update, straight into the ring slots of the next two steps:
+// they are in place when the grid barrier that ends the step completes, and no
+// second barrier is needed between "spikes known" and "next neuron update".
+// Everything else has two steps of slack and is streamed by other warps.
+// The table is a private copy; it is rebuilt whenever the arrays it came from
+// may have changed.
+#pragma once
+
+#include "common.cuh"
+
+namespace b200
+{
+// One dendritic-delay ring: den_delay[D][num_neurons] of a postsynaptic model.
+struct NearRing
+{
+    float *den_delay;
+    unsigned int D;
+    unsigned int num_neurons;
+};
+
+// Where the rows of one neuron group's spikes are (a group that is no spike source: shift 0xFFFFFFFF).
+struct NearSpace
+{
+    unsigned long long first_cell;   // index of the first entry of the population's first row
+    unsigned int shift;              // rows hold 1 << shift entries
+    unsigned int pad;
+};
+
+constexpr unsigned int NEAR_MAX_RINGS = 64;
+
+__device__ __forceinline__ unsigned int nearDelay(unsigned int d, unsigned int D)
+{
+    return d % D;
+}
+
+// counts[row] += near synapses of the row.  One warp per row.
+__global__ void nearCountKernel(const b200_synapse_group g, unsigned int *counts)
+{
+    const unsigned int lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
+    const unsigned int D = g.max_den_delay;
+    for(unsigned int row = blockIdx.x * warps + (threadIdx.x >> 5); row < g.num_src; row += gridDim.x * warps) {
+        const unsigned int n = min(g.row_length[row], g.row_stride);
+        const uint8_t *d = g.d + (unsigned long long)row * g.row_stride;
+        unsigned int c = 0;
+        for(unsigned int j = lane; j < n; j += 32u) c += (nearDelay(d[j], D) < 2u) ? 1u : 0u;
+        #pragma unroll
+        for(int o = 16; o; o >>= 1) c += __shfl_xor_sync(0xFFFFFFFFu, c, o);
+        if(lane == 0 && c) atomicAdd(&counts[row], c);      // several groups may share the row
+    }
+}
+
+// Append the row's near synapses to its row of the table (cursor[row] counts what is there).
+template<typename IndT>
+__global__ void nearFillKernel(const b200_synapse_group g, unsigned int ring, unsigned int *cursor, uint2 *rows,
+                               unsigned int shift, unsigned int *bad)
+{
+    const unsigned int lane = threadIdx.x & 31u, warps = blockDim.x >> 5;
+    const unsigned int D = g.max_den_delay;
+    const bool constantWeight = (g.wu_model == B200_WU_STATIC_PULSE_CONSTANT_WEIGHT);
+    for(unsigned int row = blockIdx.x * warps + (threadIdx.x >> 5); row < g.num_src; row += gridDim.x * warps) {
+        const unsigned int n = min(g.row_length[row], g.row_stride);
+        const unsigned long long rowStart = (unsigned long long)row * g.row_stride;
+        for(unsigned int j0 = 0; j0 < n; j0 += 32u) {
+            const unsigned int j = j0 + lane;
+            unsigned int e = 2u;
+            if(j < n) e = nearDelay(g.d[rowStart + j], D);
+            const bool take = e < 2u;
+            const unsigned int ballot = __ballot_sync(0xFFFFFFFFu, take);
+            if(!ballot) continue;
+            unsigned int base = 0;
+            if(lane == 0) base = atomicAdd(&cursor[row], (unsigned int)__popc(ballot));
+            base = __shfl_sync(0xFFFFFFFFu, base, 0);
+            if(take) {
+                const unsigned int post = static_cast<const IndT*>(g.ind)[rowStart + j];
+                const unsigned int pos = base + __popc(ballot & ((1u << lane) - 1u));
+                if(post >= g.num_trg || post >= (1u << 24) || pos >= (1u << shift)) {
+                    atomicOr(bad, 1u);
+                }
+                else {
+                    const float w = constantWeight ? g.wu_params[0] : g.g[rowStart + j];
+                    rows[((unsigned long long)row << shift) + pos] = make_uint2((post << 8) | (ring << 1) | e, __float_as_uint(w));
+                }
+            }
+        }
+    }
+}
+
+// The near synapses of one spiking neuron, delivered by its warp: `cell0` is the first entry of
+// its row, `front` the phase of the step in which it spiked.  A synapse of delay e lands in the
+// slot the neuron update e + 1 steps later reads.
+__device__ __forceinline__ void nearDeliverRow(const uint2 *__restrict__ table, unsigned long long cell0, unsigned int shift,
+                                               const NearRing *rings, unsigned int front, StepState *state)
+{
+    const unsigned int lane = threadIdx.x & 31u;
+    const unsigned int cells = 1u << shift;
+    for(unsigned int c0 = 0; c0 < cells; c0 += 256u) {
+        // up to eight loads per lane in flight before the first reduction
+        uint2 entry[8];
+        #pragma unroll
+        for(unsigned int u = 0; u < 8u; u++) {
+            const unsigned int c = c0 + u * 32u + lane;
+            entry[u] = (c < cells) ? __ldg(&table[cell0 + c]) : make_uint2(0u, 0u);
+        }
+        #pragma unroll
+        for(unsigned int u = 0; u < 8u; u++) {
+            if(entry[u].y != 0u) {
+                const NearRing &ring = rings[(entry[u].x >> 1) & 0x7Fu];
+                const unsigned int post = entry[u].x >> 8;
+                if(post < ring.num_neurons) {
+                    redAdd(ring.den_delay + (unsigned long long)ringSlot(front + 2u + (entry[u].x & 1u), ring.D) * ring.num_neurons + post,
+                           __uint_as_float(entry[u].y));
+                }
+                else {
+                    atomicOr(&state->error, ERR_IND_RANGE);
+                }
+            }
+        }
+    }
+}
+}   // namespace b200

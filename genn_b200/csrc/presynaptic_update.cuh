@@ -120,10 +120,14 @@ __device__ __forceinline__ void sparseQuad(const b200_synapse_group &g, unsigned
                 while(slot >= D) slot -= D;         // a delay of the ring length or more wraps around
                 // zeroDelay says what to do with a synapse that arrives in the same step (its
                 // slot is the front one): 0 deliver it, 1 the caller relies on there being
-                // none, 2 somebody else delivers it
-                if(zeroDelay && slot == denFront) {
-                    if(zeroDelay == 1u) atomicOr(&state->error, ERR_DELAY_RANGE);
-                    continue;
+                // none, 2 somebody else delivers it, 3 somebody else delivers it and those
+                // that arrive one step later
+                if(zeroDelay) {
+                    if(slot == denFront) {
+                        if(zeroDelay == 1u) atomicOr(&state->error, ERR_DELAY_RANGE);
+                        continue;
+                    }
+                    if(zeroDelay == 3u && slot == ((denFront + 1u == D) ? 0u : denFront + 1u)) continue;
                 }
                 redAdd(target + (unsigned long long)slot * numTrg + p, w[j]);
             }

@@ -146,7 +146,13 @@ struct b200_runner
     unsigned int *urgentOffsets = nullptr;          // row offsets of all groups, one after the other
     uint2 *urgentEntries = nullptr;
     FusedUrgent *fusedUrgent = nullptr;             // device copy for the kernel, or NULL
-    enum Schedule { PLAIN = 0, SPLIT = 1, LAG = 2 };
+    enum Schedule { PLAIN = 0, SPLIT = 1, LAG = 2, EMIT = 3 };
+    // "deliver at emission" mode (near.cuh): near synapses of all groups, one row per source neuron
+    bool useEmit = true;
+    uint2 *nearTable = nullptr;
+    NearRing *nearRings = nullptr;          // device copies
+    NearSpace *nearSpaces = nullptr;
+    unsigned int numRings = 0;
     Schedule schedule = PLAIN;
 
     void dropUrgent()
@@ -156,6 +162,10 @@ struct b200_runner
         if(urgentEntries) cudaFree(urgentEntries);
         if(fusedUrgent) cudaFree(fusedUrgent);
         urgentOffsets = nullptr; urgentEntries = nullptr; fusedUrgent = nullptr;
+        if(nearTable) cudaFree(nearTable);
+        if(nearRings) cudaFree(nearRings);
+        if(nearSpaces) cudaFree(nearSpaces);
+        nearTable = nullptr; nearRings = nullptr; nearSpaces = nullptr; numRings = 0;
     }
 
     // spike exchange of a sharded model
@@ -469,7 +479,8 @@ int buildFusedTables(b200_runner *r)
         const auto &g = sparse[gi];
         // which list the group's full-row chunks go to, and whether it has a table of urgent synapses
         const bool ring = g.max_den_delay >= 2 && g.d;
-        const bool later = (r->schedule == b200_runner::LAG) || (r->schedule == b200_runner::SPLIT && ring);
+        const bool later = (r->schedule == b200_runner::LAG) || (r->schedule == b200_runner::EMIT) ||
+                           (r->schedule == b200_runner::SPLIT && ring);
         const unsigned int urgentStride = (r->schedule == b200_runner::SPLIT && gi < r->urgentStride.size())
             ? r->urgentStride[gi] : 0u;
         // a sharded source population contributes one source per process section
@@ -522,7 +533,9 @@ int buildFusedTables(b200_runner *r)
                         align16(sizeof(b200_synapse_group) * sparse.size()) +
                         align16(sizeof(FusedSource) * sources.size()) + align16(sizeof(uint2) * items.size()) +
                         align16(sizeof(unsigned int) * slotStart.size()) +
-                        (r->fusedUrgent ? align16(sizeof(FusedUrgent) * sparse.size()) : 0);
+                        (r->fusedUrgent ? align16(sizeof(FusedUrgent) * sparse.size()) : 0) +
+                        (r->schedule == b200_runner::EMIT
+                            ? align16(sizeof(NearRing) * r->numRings) + align16(sizeof(NearSpace) * r->neuronGroups.size()) : 0);
     r->fusedStage = r->fusedSmemBytes <= 200 * 1024;
     {
         // SPLIT schedule: the warp-specialised kernel, if the neuron slots (dealt out evenly over one
@@ -531,7 +544,8 @@ int buildFusedTables(b200_runner *r)
         r->slotsPerCta = 0;
         int sms = 0;
         CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device));
-        if(r->schedule == b200_runner::SPLIT && r->fusedStage && r->streamWarpsWanted != 0 && sms > 0) {
+        if((r->schedule == b200_runner::SPLIT || r->schedule == b200_runner::EMIT) && r->fusedStage &&
+           r->streamWarpsWanted != 0 && sms > 0) {
             const unsigned int perCta = ((slotStart.back() + sms - 1) / sms + 31u) & ~31u;
             const unsigned int warps = FUSED_BLOCK / 32;
             const unsigned int chainMin = std::max(8u, perCta / 32u);
@@ -541,6 +555,11 @@ int buildFusedTables(b200_runner *r)
                 r->streamWarps = stream;
                 r->slotsPerCta = perCta;
             }
+        }
+        if(r->schedule == b200_runner::EMIT && !r->streamWarps) {
+            // no room for the warp-specialised kernel after all: plain schedule
+            r->schedule = b200_runner::PLAIN;
+            return buildFusedTables(r);
         }
         int e = withNeuronShape(r, [&](auto P, auto C) -> int {
             auto fused = fusedStepKernel<decltype(P)::value, decltype(C)::value>;
@@ -699,6 +718,134 @@ int launchOwner(b200_runner *r, unsigned long long numSteps, unsigned long long 
     return B200_OK;
 }
 
+// Near-synapse table of the "deliver at emission" schedule; leaves r->schedule alone if the model
+// does not qualify (a group without a delay ring of three slots or more, an axonal delay, a ring
+// that is not a postsynaptic model of a neuron group, too few free warps for streaming).
+int buildNearTables(b200_runner *r)
+{
+    const auto &groups = r->fusedGroups;
+    const size_t n = groups.size(), numNeuronGroups = r->neuronGroups.size();
+    if(n == 0) return B200_OK;
+    unsigned int slots = 0;
+    for(const auto &g : r->neuronGroups) slots += (g.num_update + 31u) & ~31u;
+    int sms = 0;
+    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device));
+    const unsigned int perCta = ((slots + sms - 1) / sms + 31u) & ~31u;
+    if(std::max(8u, perCta / 32u) + 4u > FUSED_BLOCK / 32) return B200_OK;      // no room for stream warps
+    std::vector<NearRing> rings;
+    std::vector<unsigned int> ringOf(n), sourceOf(n);
+    for(size_t gi = 0; gi < n; gi++) {
+        const auto &g = groups[gi];
+        // the stream reads a spike list up to two steps after it was written: delay 0 and four slots
+        if(g.max_den_delay < 3 || !g.d || g.axonal_delay != 0 || g.src_delay_slots < 4 || g.num_src >= (1u << 24)) return B200_OK;
+        bool found = false;
+        for(size_t ni = 0; ni < numNeuronGroups && !found; ni++) {
+            const auto &ng = r->neuronGroups[ni];
+            for(unsigned int p = 0; p < ng.num_psm && !found; p++) {
+                if(ng.psm[p].den_delay == g.den_delay && ng.psm[p].max_den_delay == g.max_den_delay &&
+                   ng.num_neurons == g.num_trg) {
+                    size_t ri = 0;
+                    for(; ri < rings.size(); ri++) if(rings[ri].den_delay == g.den_delay) break;
+                    if(ri == rings.size()) rings.push_back(NearRing{g.den_delay, g.max_den_delay, g.num_trg});
+                    ringOf[gi] = (unsigned int)ri;
+                    found = true;
+                }
+            }
+        }
+        if(!found || rings.size() > NEAR_MAX_RINGS) return B200_OK;
+        found = false;
+        for(size_t ni = 0; ni < numNeuronGroups && !found; ni++) {
+            const auto &ng = r->neuronGroups[ni];
+            // the whole population must be updated here: the spiking thread looks its row up by neuron id
+            if(ng.spk_cnt == g.src_spk_cnt && ng.num_neurons == g.num_src && ng.first_neuron == 0 &&
+               ng.num_update == ng.num_neurons) {
+                sourceOf[gi] = (unsigned int)ni;
+                found = true;
+            }
+        }
+        if(!found) return B200_OK;
+    }
+    // rows of every source population, counted first: the longest fixes the population's row length
+    std::vector<unsigned long long> rowBase(numNeuronGroups + 1, 0);
+    for(size_t ni = 0; ni < numNeuronGroups; ni++) rowBase[ni + 1] = rowBase[ni] + r->neuronGroups[ni].num_neurons;
+    const unsigned long long totalRows = rowBase[numNeuronGroups];
+    if(totalRows == 0 || totalRows >= (1ull << 31)) return B200_OK;
+    unsigned int *cursor = nullptr, *bad = nullptr;
+    CUDA_TRY(cudaMalloc(&cursor, sizeof(unsigned int) * totalRows));
+    CUDA_TRY(cudaMemsetAsync(cursor, 0, sizeof(unsigned int) * totalRows, r->stream));
+    for(size_t gi = 0; gi < n; gi++) {
+        const auto &g = groups[gi];
+        if(!g.num_src) continue;
+        nearCountKernel<<<std::min(1184u, (g.num_src + 7u) / 8u), 256, 0, r->stream>>>(g, cursor + rowBase[sourceOf[gi]]);
+        CUDA_TRY(cudaPeekAtLastError());
+        r->launches++;
+    }
+    std::vector<unsigned int> counts(totalRows);
+    CUDA_TRY(cudaMemcpyAsync(counts.data(), cursor, sizeof(unsigned int) * totalRows, cudaMemcpyDeviceToHost, r->stream));
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    std::vector<NearSpace> spaces(numNeuronGroups);
+    unsigned long long cells = 0;
+    for(size_t ni = 0; ni < numNeuronGroups; ni++) {
+        bool isSource = false;
+        for(size_t gi = 0; gi < n; gi++) isSource = isSource || sourceOf[gi] == ni;
+        spaces[ni] = NearSpace{0ull, 0xFFFFFFFFu, 0u};
+        if(!isSource) continue;
+        unsigned int longest = 0;
+        for(unsigned long long row = rowBase[ni]; row < rowBase[ni + 1]; row++) longest = std::max(longest, counts[row]);
+        unsigned int shift = 5;
+        while((1u << shift) < longest) shift++;
+        // a population most of whose synapses are near gains nothing from this schedule
+        if(shift > 10) {
+            cudaFree(cursor);
+            return B200_OK;
+        }
+        spaces[ni].first_cell = cells;
+        spaces[ni].shift = shift;
+        cells += (unsigned long long)r->neuronGroups[ni].num_neurons << shift;
+    }
+    if(cells >= (1ull << 33)) {      // 64 GB of table: not worth it
+        cudaFree(cursor);
+        return B200_OK;
+    }
+    CUDA_TRY(cudaMemsetAsync(cursor, 0, sizeof(unsigned int) * totalRows, r->stream));
+    CUDA_TRY(cudaMalloc(&bad, sizeof(unsigned int)));
+    CUDA_TRY(cudaMemsetAsync(bad, 0, sizeof(unsigned int), r->stream));
+    CUDA_TRY(cudaMalloc(&r->nearTable, sizeof(uint2) * (cells + 1)));
+    CUDA_TRY(cudaMemsetAsync(r->nearTable, 0, sizeof(uint2) * (cells + 1), r->stream));
+    for(size_t gi = 0; gi < n; gi++) {
+        const auto &g = groups[gi];
+        if(!g.num_src) continue;
+        const unsigned int blocks = std::min(1184u, (g.num_src + 7u) / 8u);
+        const NearSpace &space = spaces[sourceOf[gi]];
+        const int e = withIndType(g.ind_bytes, [&](auto tag) -> int {
+            using IndT = decltype(tag);
+            nearFillKernel<IndT><<<blocks, 256, 0, r->stream>>>(g, ringOf[gi], cursor + rowBase[sourceOf[gi]],
+                                                                r->nearTable + space.first_cell, space.shift, bad);
+            return B200_OK;
+        });
+        if(e) return e;
+        CUDA_TRY(cudaPeekAtLastError());
+        r->launches++;
+    }
+    unsigned int isBad = 0;
+    CUDA_TRY(cudaMemcpyAsync(&isBad, bad, sizeof(unsigned int), cudaMemcpyDeviceToHost, r->stream));
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    cudaFree(cursor);
+    cudaFree(bad);
+    if(isBad) {
+        cudaFree(r->nearTable);
+        r->nearTable = nullptr;
+        return B200_OK;
+    }
+    r->numRings = (unsigned int)rings.size();
+    CUDA_TRY(cudaMalloc(&r->nearRings, sizeof(NearRing) * rings.size()));
+    CUDA_TRY(cudaMemcpy(r->nearRings, rings.data(), sizeof(NearRing) * rings.size(), cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMalloc(&r->nearSpaces, sizeof(NearSpace) * spaces.size()));
+    CUDA_TRY(cudaMemcpy(r->nearSpaces, spaces.data(), sizeof(NearSpace) * spaces.size(), cudaMemcpyHostToDevice));
+    r->schedule = b200_runner::EMIT;
+    return B200_OK;
+}
+
 // Choose the schedule of the persistent kernel from the dendritic delays that
 // are actually in the arrays, and build what it needs:
 //   LAG    every SPARSE group has a delay ring and no synapse arrives in the same
@@ -766,6 +913,13 @@ int refreshSchedule(b200_runner *r)
         r->lagEligible = lagOk;
         if(r->useLag && lagOk && (!r->sharded() || r->lagAgreed)) {
             r->schedule = b200_runner::LAG;
+        }
+        else if(r->useEmit && !r->sharded() && r->streamWarpsWanted != 0 && r->fusedStage) {
+            const int e = buildNearTables(r);
+            if(e) return e;
+        }
+        if(r->schedule != b200_runner::PLAIN) {
+            // decided
         }
         else if(r->useSplit && total < (1ull << 31)) {
             r->schedule = b200_runner::SPLIT;
@@ -837,6 +991,11 @@ int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long 
     L.urgent = r->fusedUrgent;
     L.stream_warps = r->streamWarps;
     L.slots_per_cta = r->slotsPerCta;
+    L.emit = (r->schedule == b200_runner::EMIT) ? 1u : 0u;
+    L.num_rings = r->numRings;
+    L.near_table = r->nearTable;
+    L.near_rings = r->nearRings;
+    L.near_spaces = r->nearSpaces;
     L.neuron.groups = r->neuronTable.d;
     L.neuron.block_start = r->neuronTable.blockStart;
     L.neuron.num_groups = r->neuronTable.num;
@@ -1250,6 +1409,7 @@ int b200_set_option(b200_runner *r, const char *name, double value)
     else if(n == "use_fused") r->useFused = (value != 0.0);
     else if(n == "use_lag") { r->useLag = (value != 0.0); r->lagStale = true; }
     else if(n == "use_split") { r->useSplit = (value != 0.0); r->lagStale = true; }
+    else if(n == "use_emit") { r->useEmit = (value != 0.0); r->lagStale = true; }
     else if(n == "stream_warps") { r->streamWarpsWanted = (int)value; r->lagStale = true; }
     else if(n == "lag_agreed") { r->lagAgreed = (value != 0.0); r->lagStale = true; }
     else if(n == "rescan_delays") r->lagStale = true;

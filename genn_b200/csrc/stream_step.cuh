@@ -28,6 +28,7 @@
 #pragma once
 
 #include "fused_step.cuh"
+#include "near.cuh"
 
 namespace b200
 {
@@ -49,14 +50,69 @@ struct StreamShared
     volatile unsigned int headReady;                 // steps whose header has been published
     volatile unsigned int stop;                      // the chain gave up: stream warps leave
     volatile unsigned int streamDone[32];            // per stream warp: steps fully delivered
+    volatile unsigned int stepPassed;                // emit mode: grid barriers of the launch that have completed
+    volatile unsigned int streamGo[2];               // emit mode: the first stream warp's decision for a pass (pass number: go)
     bool barrierOk;
 };
+
+// Barrier over the stream warps only (named barrier 2).
+__device__ __forceinline__ void streamSync(unsigned int streamThreads)
+{
+    asm volatile("bar.sync 2, %0;" :: "r"(streamThreads) : "memory");
+}
+
+// Spike count and first ids of source `si` for the step whose phase is `k` (`stepsDone` steps
+// completed before it), into header buffer `buf`.  One lane per source.
+__device__ __forceinline__ void fetchHeader(const FusedLaunch &L, StreamShared &sh, unsigned int buf, unsigned int si,
+                                            unsigned int k, unsigned long long stepsDone, StepState *state)
+{
+    if(si >= L.num_sources) return;
+    unsigned int cnt = 0;
+    // all loads into registers first: a shared-memory store between two loads through generic
+    // pointers would serialise them
+    unsigned int ids[FUSED_PREFETCH_IDS];
+    #pragma unroll
+    for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) ids[j] = 0u;
+    const FusedSource &src = L.sources[si];
+    const unsigned int rslot = ringSlot(k + src.slots - src.delay, src.slots);
+    if(src.spk_tag) {
+        // sharded model: (step, count) and (step, id) words written by the list's owner into THIS
+        // process's memory; poll (bounded) for the count of the step we need
+        const long long expected = (long long)stepsDone - (long long)src.delay;
+        if(expected > 0) {
+            cnt = awaitWord(&src.spk_tag[rslot], (unsigned long long)expected, state);
+            const unsigned long long *wire = src.spk_wire + (unsigned long long)rslot * src.num_src;
+            unsigned long long words[FUSED_PREFETCH_IDS];
+            #pragma unroll
+            for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) words[j] = (j < cnt) ? loadRelaxedSys(&wire[j]) : 0ull;
+            #pragma unroll
+            for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
+                if(j < cnt) {
+                    ids[j] = ((words[j] >> 32) == (unsigned long long)expected)
+                        ? (unsigned int)words[j] : awaitWord(&wire[j], (unsigned long long)expected, state);
+                }
+            }
+        }
+    }
+    else {
+        // ids fetched before the count is known: entries past it are stale but valid memory
+        const unsigned int *list = src.spk + (unsigned long long)rslot * src.num_src;
+        cnt = __ldcg(&src.spk_cnt[rslot]);
+        #pragma unroll
+        for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) ids[j] = (j < src.num_src) ? __ldcg(&list[j]) : 0u;
+    }
+    #pragma unroll
+    for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) sh.headIds[buf][si][j] = ids[j];
+    sh.headCnt[buf][si] = cnt;
+    sh.headSlot[buf][si] = rslot;
+}
 
 // One pass over one of the two item lists of every source, for the spikes whose
 // header sits in buffer `buf`: warp `first` of `stride` takes every stride-th item.
 __device__ __forceinline__ void deliverItems(const FusedLaunch &L, const StreamShared &sh, unsigned int buf,
                                              bool urgentList, unsigned int first, unsigned int stride,
-                                             unsigned int k, unsigned long long stepsDone, StepState *state)
+                                             unsigned int k, unsigned long long stepsDone, StepState *state,
+                                             int farMode = -1)
 {
     const unsigned int lane = threadIdx.x & 31u;
     for(unsigned int base = 0; base < L.num_sources; base += 32u) {
@@ -100,7 +156,9 @@ __device__ __forceinline__ void deliverItems(const FusedLaunch &L, const StreamS
                 else {
                     // a synapse that arrives in the same step: delivered here (urgent list), in the
                     // group's urgent table (skipped here), or an error (no table: none may exist)
-                    const unsigned int zeroDelay = urgentList ? 0u : (L.urgent && L.urgent[item.x].stride) ? 2u : 1u;
+                    // (farMode overrides: 0 deliver every synapse, 3 leave out delays 0 and 1)
+                    const unsigned int zeroDelay = (farMode >= 0) ? (unsigned int)farMode
+                        : urgentList ? 0u : (L.urgent && L.urgent[item.x].stride) ? 2u : 1u;
                     switch(g.ind_bytes) {
                     case 1: fusedChunk<uint8_t>(g, pre, item.y, k + 1u, zeroDelay, state); break;
                     case 2: fusedChunk<uint16_t>(g, pre, item.y, k + 1u, zeroDelay, state); break;
@@ -113,6 +171,152 @@ __device__ __forceinline__ void deliverItems(const FusedLaunch &L, const StreamS
             }
             else if(lane == 0) {
                 atomicOr(&state->error, ERR_IND_RANGE);
+            }
+        }
+    }
+}
+
+// What one lane holds of one (spike, 128-synapse chunk) item between its loads and its reductions.
+struct StreamQuad
+{
+    unsigned int group;          // index of the synapse group, 0xFFFFFFFF: nothing to do
+    unsigned int pre;
+    unsigned int len;
+    unsigned int post[4];
+    float w[4];
+    unsigned int dw;             // four delays
+    unsigned long long idx;      // index of the quad's first synapse in the group's arrays
+};
+
+__device__ __forceinline__ void streamQuadLoad(const b200_synapse_group &g, unsigned int pre, unsigned int quad, StreamQuad &q)
+{
+    const unsigned long long rowStart = (unsigned long long)pre * g.row_stride;
+    q.idx = (rowStart & ~3ull) + (unsigned long long)quad * PRE_VEC;
+    q.pre = pre;
+    if(q.idx >= (unsigned long long)g.num_src * g.row_stride) {
+        q.group = 0xFFFFFFFFu;
+        return;
+    }
+    // row length and row data together: the quad's address does not depend on the length, and a
+    // quad past the end of its row still lies inside the array (or its tail padding)
+    q.len = __ldg(&g.row_length[pre]);
+    switch(g.ind_bytes) {
+    case 1: IndLoad<uint8_t>::load4(g.ind, q.idx, q.post); break;
+    case 2: IndLoad<uint16_t>::load4(g.ind, q.idx, q.post); break;
+    default: IndLoad<uint32_t>::load4(g.ind, q.idx, q.post); break;
+    }
+    if(g.wu_model == B200_WU_STATIC_PULSE_CONSTANT_WEIGHT) {
+        q.w[0] = q.w[1] = q.w[2] = q.w[3] = g.wu_params[0];
+    }
+    else {
+        const float4 wv = __ldg(reinterpret_cast<const float4*>(g.g + q.idx));
+        q.w[0] = wv.x; q.w[1] = wv.y; q.w[2] = wv.z; q.w[3] = wv.w;
+    }
+    q.dw = g.max_den_delay ? __ldg(reinterpret_cast<const unsigned int*>(g.d + q.idx)) : 0u;
+}
+
+// The reductions of a loaded quad; `zeroDelay` as in sparseQuad.
+__device__ __forceinline__ void streamQuadApply(const b200_synapse_group &g, const StreamQuad &q, unsigned int front,
+                                                unsigned int zeroDelay, StepState *state)
+{
+    const unsigned long long rowStart = (unsigned long long)q.pre * g.row_stride;
+    const unsigned long long rowEnd = rowStart + q.len;
+    const unsigned int D = g.max_den_delay, numTrg = g.num_trg;
+    float *target = D ? g.den_delay : g.out_post;
+    const unsigned int denFront = D ? ringSlot(front, D) : 0u;
+    #pragma unroll
+    for(int j = 0; j < PRE_VEC; j++) {
+        const unsigned long long sIdx = q.idx + j;
+        if(sIdx >= rowStart && sIdx < rowEnd) {
+            const unsigned int p = q.post[j];
+            if(p >= numTrg) {
+                atomicOr(&state->error, ERR_IND_RANGE);
+                continue;
+            }
+            if(D) {
+                unsigned int slot = denFront + ((q.dw >> (8 * j)) & 0xFFu);
+                while(slot >= D) slot -= D;
+                if(zeroDelay) {
+                    if(slot == denFront) {
+                        if(zeroDelay == 1u) atomicOr(&state->error, ERR_DELAY_RANGE);
+                        continue;
+                    }
+                    if(zeroDelay == 3u && slot == ((denFront + 1u == D) ? 0u : denFront + 1u)) continue;
+                }
+                redAdd(target + (unsigned long long)slot * numTrg + p, q.w[j]);
+            }
+            else {
+                redAdd(target + p, q.w[j]);
+            }
+        }
+    }
+}
+
+constexpr unsigned int STREAM_BATCH = 2;     // items a stream warp keeps in flight
+
+// deliverItems for the stream warps: the same items, STREAM_BATCH at a time with the loads of all
+// of them issued before the first reduction (a stream warp is bound by memory latency, and there
+// are only a few of them per SM).  Full-row items only.
+__device__ __forceinline__ void streamItems(const FusedLaunch &L, const StreamShared &sh, unsigned int buf,
+                                            unsigned int first, unsigned int stride, unsigned int k,
+                                            unsigned long long stepsDone, StepState *state, int farMode)
+{
+    const unsigned int lane = threadIdx.x & 31u;
+    for(unsigned int base = 0; base < L.num_sources; base += 32u) {
+        const unsigned int cnt = (base + lane < L.num_sources) ? sh.headCnt[buf][base + lane] : 0u;
+        const unsigned int per = (base + lane >= L.num_sources) ? 0u : L.sources[base + lane].item_count;
+        unsigned int incl = cnt * per;
+        #pragma unroll
+        for(int o = 1; o < 32; o <<= 1) {
+            const unsigned int v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+            if(lane >= o) incl += v;
+        }
+        const unsigned int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
+        for(unsigned int it0 = first; it0 < total; it0 += stride * STREAM_BATCH) {
+            StreamQuad q[STREAM_BATCH];
+            #pragma unroll
+            for(unsigned int u = 0; u < STREAM_BATCH; u++) {
+                const unsigned int it = it0 + u * stride;
+                q[u].group = 0xFFFFFFFFu;
+                if(it >= total) continue;                       // the same for every lane
+                const unsigned int owner = __ffs(__ballot_sync(0xFFFFFFFFu, incl > it)) - 1u;
+                const unsigned int ownIncl = __shfl_sync(0xFFFFFFFFu, incl, owner);
+                const unsigned int ownPer = __shfl_sync(0xFFFFFFFFu, per, owner);
+                const unsigned int ownCnt = sh.headCnt[buf][base + owner];
+                const unsigned int rel = it - (ownIncl - ownCnt * ownPer);
+                const unsigned int sp = rel / ownPer;
+                const unsigned int c = rel - sp * ownPer;
+                const FusedSource &src = L.sources[base + owner];
+                unsigned int pre;
+                if(sp < FUSED_PREFETCH_IDS) {
+                    pre = sh.headIds[buf][base + owner][sp];
+                }
+                else if(src.spk_wire) {
+                    const long long expected = (long long)stepsDone - (long long)src.delay;
+                    pre = awaitWord(&src.spk_wire[(unsigned long long)sh.headSlot[buf][base + owner] * src.num_src + sp],
+                                    (unsigned long long)expected, state);
+                }
+                else {
+                    pre = __ldcg(&src.spk[(unsigned long long)sh.headSlot[buf][base + owner] * src.num_src + sp]);
+                }
+                const uint2 item = L.items[src.item_begin + c];
+                const b200_synapse_group &g = L.sgroups[item.x];
+                if(pre >= g.num_src) {
+                    if(lane == 0) atomicOr(&state->error, ERR_IND_RANGE);
+                    continue;
+                }
+                q[u].group = item.x;
+                streamQuadLoad(g, pre, item.y * 32u + lane, q[u]);
+                if(L.count_events && item.y == 0 && lane == 0) {
+                    atomicAdd(&state->synaptic_events, (unsigned long long)__ldg(&g.row_length[pre]));
+                }
+            }
+            #pragma unroll
+            for(unsigned int u = 0; u < STREAM_BATCH; u++) {
+                if(q[u].group == 0xFFFFFFFFu) continue;
+                const unsigned int zeroDelay = (farMode >= 0) ? (unsigned int)farMode
+                    : (L.urgent && L.urgent[q[u].group].stride) ? 2u : 1u;
+                streamQuadApply(L.sgroups[q[u].group], q[u], k + 1u, zeroDelay, state);
             }
         }
     }
@@ -165,8 +369,17 @@ streamStepKernel(FusedLaunch L)
         if(L.urgent) {
             stageWords(p, L.urgent, sizeof(FusedUrgent) * L.num_sgroups);
             L.urgent = reinterpret_cast<const FusedUrgent*>(p);
+            p += align16(sizeof(FusedUrgent) * L.num_sgroups);
+        }
+        if(L.emit) {
+            stageWords(p, L.near_rings, sizeof(NearRing) * L.num_rings);
+            L.near_rings = reinterpret_cast<const NearRing*>(p);
+            p += align16(sizeof(NearRing) * L.num_rings);
+            stageWords(p, L.near_spaces, sizeof(NearSpace) * L.neuron.num_groups);
+            L.near_spaces = reinterpret_cast<const NearSpace*>(p);
         }
     }
+    if(threadIdx.x == 0) sh.stepPassed = 0u;
     __syncthreads();        // the last barrier every warp of the CTA takes part in
 
     const unsigned int lane = threadIdx.x & 31u;
@@ -182,6 +395,62 @@ streamStepKernel(FusedLaunch L)
     const unsigned long long done0 = state->steps_done;
 
     // =========================== stream warps ==================================================
+    if(warp >= chainWarps && L.emit) {
+        // Emit mode.  The spikes of launch step c-1 (c = 1 .. steps-1) are complete once the grid
+        // barrier that ends that step has been passed; a pass of the stream warps fetches their
+        // header and delivers every synapse with a delay of two steps or more, as the presynaptic
+        // phase of step c would.  The chain waits for pass c before it arrives at the barrier that
+        // ends step c+1: a pass has two steps of time.  One item costs several thousand cycles
+        // (a random row: TLB and DRAM misses), more than a step, so the stream warps form two
+        // sets that take the odd and the even passes: a pass starts the moment its spikes are there.
+        const unsigned int me = warp - chainWarps;
+        const unsigned int set = me & 1u;
+        const unsigned int setWarps = (streamWarps + 1u - set) / 2u;       // warps me = set, set + 2, ...
+        const unsigned int setThreads = setWarps * 32u;
+        const unsigned int first = (me >> 1) * gridDim.x + blockIdx.x, stride = setWarps * gridDim.x;
+        unsigned long long spent[4] = {0, 0, 0, 0};     // profile mode: waiting, header, items, fence
+        // passes c with c % 2 == set; phase of step c
+        unsigned long long c = set ? 1ull : 2ull;
+        for(unsigned int a = 0; a < (unsigned int)c; a++) k = (k + 1 == period) ? 0u : k + 1;
+        for(; c < L.num_steps; c += 2) {
+            const long long since = clock64();
+            bool alive = true;
+            while(sh.stepPassed < (unsigned int)c) {
+                if(sh.stop || clock64() - since > STREAM_WAIT_CYCLES) { alive = false; break; }
+                __nanosleep(40);
+            }
+            // go on or leave TOGETHER (a warp that left alone would hang the others of its set on their
+            // barrier): the set's first warp decides, the others read its decision behind the barrier
+            const unsigned int buf = set;
+            const long long t1 = clock64();
+            if((me >> 1) == 0 && lane == 0) sh.streamGo[buf] = (alive && !sh.stop) ? (unsigned int)c : 0u;
+            __threadfence_block();
+            for(unsigned int si = (me >> 1) * 32u + lane; si < ((L.num_sources + 31u) & ~31u); si += setThreads) {
+                fetchHeader(L, sh, buf, si, k, done0 + c, state);
+            }
+            asm volatile("bar.sync %0, %1;" :: "r"(2u + set), "r"(setThreads) : "memory");
+            if(sh.streamGo[buf] != (unsigned int)c) return;
+            const long long t2 = clock64();
+            streamItems(L, sh, buf, first, stride, k, done0 + c, state, 3);
+            const long long t3 = clock64();
+            __threadfence();
+            __syncwarp();
+            if(lane == 0) sh.streamDone[me] = (unsigned int)c;
+            k = (k + 1 == period) ? 0u : k + 1;
+            k = (k + 1 == period) ? 0u : k + 1;
+            spent[0] += (unsigned long long)(t1 - since);
+            spent[1] += (unsigned long long)(t2 - t1);
+            spent[2] += (unsigned long long)(t3 - t2);
+            spent[3] += (unsigned long long)(clock64() - t3);
+        }
+        if(L.profile && blockIdx.x == 0 && me == 1 && lane == 0) {
+            state->probe[0] += spent[0];
+            state->probe[1] += spent[1];
+            state->probe[3] += spent[2];
+            state->probe[4] += spent[3];
+        }
+        return;
+    }
     if(warp >= chainWarps) {
         const unsigned int me = warp - chainWarps;
         const unsigned int first = me * gridDim.x + blockIdx.x, stride = streamWarps * gridDim.x;
@@ -199,7 +468,7 @@ streamStepKernel(FusedLaunch L)
             __threadfence_block();
             __syncwarp();
             const long long began = clock64();
-            deliverItems(L, sh, (unsigned int)(step & 1u), false, first, stride, k, done0 + step, state);
+            streamItems(L, sh, (unsigned int)(step & 1u), first, stride, k, done0 + step, state, -1);
             // reductions of every lane visible device-wide, then say so
             __threadfence();
             __syncwarp();
@@ -270,52 +539,31 @@ streamStepKernel(FusedLaunch L)
     const bool prof = L.profile && threadIdx.x == 0;
     long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
     unsigned long long cyc[6] = {0, 0, 0, 0, 0, 0};
+    const bool emit = L.emit != 0;
+    unsigned int csCount[NCS > 0 ? NCS : 1] = {0};
+    if(emit) {
+        // The spikes of the step before this launch: every synapse of theirs, as the plain schedule's
+        // presynaptic phase would deliver them, then a grid barrier.  (The last step of a launch leaves
+        // its spikes undelivered, so that memory between launches is what every other path expects.)
+        if(warp < (L.num_sources + 31u) / 32u) fetchHeader(L, sh, 0u, warp * 32u + lane, k, done0, state);
+        chainSync(chainThreads);
+        deliverItems(L, sh, 0u, false, chainFirst, chainStride, k, done0, state, 0);
+        arrive();
+        if(mine && myActive) {
+            drawCurrentSources<NCS>(L.neuron, L.neuron.groups[myGroup], 0u, (unsigned int)myIndex, t0, csCount);
+        }
+        if(!wait()) B200_CHAIN_ABORT();
+    }
     for(unsigned long long step = 0; step < L.num_steps; step++) {
         if(prof) c0 = clock64();
         const unsigned int buf = (unsigned int)(step & 1u);
+        if(emit) {
+            if(prof) { c1 = clock64(); c2 = c1; }
+        }
+        else {
 
         // ---------------- header: spike counts and first ids of every source ----------------------
-        if(warp < (L.num_sources + 31u) / 32u) {
-            const unsigned int si = warp * 32u + lane;
-            unsigned int cnt = 0, rslot = 0;
-            unsigned int ids[FUSED_PREFETCH_IDS];
-            #pragma unroll
-            for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) ids[j] = 0u;
-            if(si < L.num_sources) {
-                const FusedSource &src = L.sources[si];
-                rslot = ringSlot(k + src.slots - src.delay, src.slots);
-                if(src.spk_tag) {
-                    // sharded model: (step, count) and (step, id) words written by the list's owner
-                    // into THIS process's memory; poll (bounded) for the count of the step we need
-                    const long long expected = (long long)(done0 + step) - (long long)src.delay;
-                    if(expected > 0) {
-                        cnt = awaitWord(&src.spk_tag[rslot], (unsigned long long)expected, state);
-                        const unsigned long long *wire = src.spk_wire + (unsigned long long)rslot * src.num_src;
-                        unsigned long long words[FUSED_PREFETCH_IDS];
-                        #pragma unroll
-                        for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) words[j] = (j < cnt) ? loadRelaxedSys(&wire[j]) : 0ull;
-                        #pragma unroll
-                        for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) {
-                            if(j < cnt) {
-                                ids[j] = ((words[j] >> 32) == (unsigned long long)expected)
-                                    ? (unsigned int)words[j] : awaitWord(&wire[j], (unsigned long long)expected, state);
-                            }
-                        }
-                    }
-                }
-                else {
-                    // ids fetched before the count is known: entries past it are stale but valid memory
-                    const unsigned int *list = src.spk + (unsigned long long)rslot * src.num_src;
-                    cnt = __ldcg(&src.spk_cnt[rslot]);
-                    #pragma unroll
-                    for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) ids[j] = (j < src.num_src) ? __ldcg(&list[j]) : 0u;
-                }
-                #pragma unroll
-                for(unsigned int j = 0; j < FUSED_PREFETCH_IDS; j++) sh.headIds[buf][si][j] = ids[j];
-                sh.headCnt[buf][si] = cnt;
-                sh.headSlot[buf][si] = rslot;
-            }
-        }
+        if(warp < (L.num_sources + 31u) / 32u) fetchHeader(L, sh, buf, warp * 32u + lane, k, done0 + step, state);
         chainSync(chainThreads);
         if(threadIdx.x == 0) {
             __threadfence_block();
@@ -346,12 +594,12 @@ streamStepKernel(FusedLaunch L)
         if(L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 1;    // read after the barrier below
         arrive();
         // in the shadow of the barrier: this step's random draws
-        unsigned int csCount[NCS > 0 ? NCS : 1] = {0};
         if(mine && myActive) {
             drawCurrentSources<NCS>(L.neuron, L.neuron.groups[myGroup], 0u, (unsigned int)myIndex, t0 + step, csCount);
         }
         if(!wait()) B200_CHAIN_ABORT();
         if(prof) c2 = clock64();
+        }   // header, urgent synapses and first barrier (not in emit mode)
 
         // ---------------- phase B: neuron update ----------------------------------------------
         if(mine) {
@@ -372,6 +620,20 @@ streamStepKernel(FusedLaunch L)
                 }
             }
             neuronEmit<true>(L.neuron, g, 0u, myLocal, spiked, k, t0 + step, t, xp);
+            if(emit && step + 1 < L.num_steps) {
+                // the warp delivers the near synapses of its spiking neurons, one row after the other
+                unsigned int ballot = __ballot_sync(0xFFFFFFFFu, spiked);
+                const NearSpace space = L.near_spaces[myGroup];
+                while(ballot) {
+                    const unsigned int b = __ffs(ballot) - 1u;
+                    ballot &= ballot - 1u;
+                    const unsigned int id = __shfl_sync(0xFFFFFFFFu, (unsigned int)myIndex, b);
+                    if(space.shift != 0xFFFFFFFFu) {
+                        nearDeliverRow(L.near_table, space.first_cell + ((unsigned long long)id << space.shift), space.shift,
+                                       L.near_rings, k, state);
+                    }
+                }
+            }
         }
         // spike-queue update for the next step (neuronUpdateGroupMerged.cc:947-975)
         if(blockIdx.x == 0 && threadIdx.x < numGroups) {
@@ -379,7 +641,26 @@ streamStepKernel(FusedLaunch L)
             o.spk_cnt[ringSlot(k + 2, o.num_delay_slots)] = 0;
         }
         if(prof) c3 = clock64();
+        if(emit && threadIdx.x == 0 && step >= 2) {
+            // the stream warps that took pass step-1 (the spikes of the step before last) must be through
+            // it: the barrier below is the last one ahead of the first neuron update that may read
+            // what they delivered
+            const long long since = clock64();
+            for(unsigned int w = (unsigned int)((step - 1) & 1u); w < streamWarps; w += 2u) {
+                while(sh.streamDone[w] < (unsigned int)(step - 1)) {
+                    if(clock64() - since > STREAM_WAIT_CYCLES) {
+                        atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
+                        break;
+                    }
+                }
+            }
+            __threadfence_block();
+            if(prof) cyc[5] += (unsigned long long)(clock64() - since);
+        }
         arrive();
+        if(emit && mine && myActive && step + 1 < L.num_steps) {
+            drawCurrentSources<NCS>(L.neuron, L.neuron.groups[myGroup], 0u, (unsigned int)myIndex, t0 + step + 1, csCount);
+        }
         // sharded model: one warp waits for the last CTA and tells every process how many spikes
         // each population emitted ("step s: n spikes", one 64-bit store per process and population);
         // the ids already sit in every arena
@@ -404,6 +685,7 @@ streamStepKernel(FusedLaunch L)
             }
         }
         if(!wait()) B200_CHAIN_ABORT();
+        if(emit && threadIdx.x == 0) sh.stepPassed = (unsigned int)(step + 1);    // the stream may read this step's spikes
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {
             const long long c4 = clock64();

@@ -65,6 +65,7 @@ def phases(args):
     rt.set_option("owner_item_lanes", args.item_lanes)
     rt.set_option("use_lag", args.lag)
     rt.set_option("use_split", args.split)
+    rt.set_option("use_emit", args.emit)
     rt.set_option("stream_warps", args.stream_warps)
     rt.step_time(args.warm)
     rt.synchronize()
@@ -75,7 +76,7 @@ def phases(args):
     after = [rt.counter(n) for n in names]
     out = {"probe": "phases", "scale": args.scale, "steps": args.steps, "us_per_step": ms * 1e3 / args.steps,
            "step_path": rt.step_path(), "lagging": rt.lagging, "schedule": rt.schedule, "stream_warps": rt.counter("stream_warps"),
-           "probes_per_step": [rt.counter(f"probe{i}") / (args.steps + args.warm) for i in range(4)]}
+           "probes_per_step": [rt.counter(f"probe{i}") / (args.steps + args.warm) for i in range(8)]}
     for n, a, b in zip(names, before, after):
         out[n + "_per_step"] = (b - a) / args.steps
     cta = rt.cta_cycles().astype(np.float64) / args.steps
@@ -109,6 +110,7 @@ def main():
     p.add_argument("--owner", type=int, default=0)
     p.add_argument("--lag", type=int, default=1, help="deliver spikes one step late where every delay allows it")
     p.add_argument("--split", type=int, default=1, help="deliver only same-step synapses before the neuron update")
+    p.add_argument("--emit", type=int, default=1, help="near synapses delivered by the spiking thread, one barrier per step")
     p.add_argument("--stream-warps", type=int, default=-1, help="-1 auto, 0 one warp set, n warps per CTA that only stream")
     p.add_argument("--min-delay", type=float, default=0.0, help="lower clip of the delay distribution in ms")
     p.add_argument("--item-lanes", type=int, default=32)

@@ -20,11 +20,12 @@ RTOL, ATOL = 1e-5, 2e-6
 # the time-step paths: target-stationary persistent kernel; persistent kernel with
 # global reductions in each of its schedules (spikes one step late where no synapse
 # arrives in the same step; only the same-step synapses before the neuron update;
-# everything before it; the split schedule on the warp-specialised kernel and on the
-# plain one); one launch per kernel.  (use_fused, use_owner, use_lag, use_split, stream_warps)
-PATHS = {"owner": (1, 1, 1, 1, -1), "persistent": (1, 0, 1, 1, -1), "persistent-split": (1, 0, 0, 1, -1),
-         "persistent-split-one-warp-set": (1, 0, 0, 1, 0), "persistent-plain": (1, 0, 0, 0, -1),
-         "per-kernel": (0, 0, 1, 1, -1)}
+# everything before it; near synapses delivered by the spiking thread itself; the
+# split schedule on the warp-specialised kernel and on the plain one); one launch per
+# kernel.  (use_fused, use_owner, use_lag, use_emit, use_split, stream_warps)
+PATHS = {"owner": (1, 1, 1, 1, 1, -1), "persistent": (1, 0, 1, 1, 1, -1), "persistent-emit": (1, 0, 0, 1, 1, -1),
+         "persistent-split": (1, 0, 0, 0, 1, -1), "persistent-split-one-warp-set": (1, 0, 0, 0, 1, 0),
+         "persistent-plain": (1, 0, 0, 0, 0, -1), "per-kernel": (0, 0, 1, 1, 1, -1)}
 # networks whose every synapse has a dendritic delay of at least one step
 LAG_CASES = {"potjans_mini_d1"}
 # networks with dendritic-delay rings (some of whose synapses may arrive in the same step)
@@ -34,17 +35,19 @@ OWNER_CASES = {"ff_sparse", "ff_sparse_narrow", "potjans_mini", "potjans_mini_d1
 
 
 def _select(rt, path, name=None):
-    fused, owner, lag, split, stream = PATHS[path]
+    fused, owner, lag, emit, split, stream = PATHS[path]
     rt.set_option("use_fused", fused)
     rt.set_option("use_owner", owner)
     rt.set_option("use_lag", lag)
+    rt.set_option("use_emit", emit)
     rt.set_option("use_split", split)
     rt.set_option("stream_warps", stream)
     if name is not None and rt.step_path()[0] >= 1:
-        want = 2 if (lag and name in LAG_CASES) else 1 if (split and name in RING_CASES) else 0
+        want = (2 if (lag and name in LAG_CASES) else 3 if (emit and stream != 0 and name in RING_CASES)
+                else 1 if (split and name in RING_CASES) else 0)
         assert rt.schedule == want, f"{name}: schedule {rt.schedule}, expected {want}"
         assert rt.lagging == (want == 2 and bool(fused))
-        assert (rt.counter("stream_warps") > 0) == (want == 1 and stream != 0), "warp-specialised kernel expected for the split schedule"
+        assert (rt.counter("stream_warps") > 0) == (want in (1, 3) and stream != 0), "warp-specialised kernel expected"
     if path == "owner" and name in OWNER_CASES:
         taken, why = rt.step_path()
         assert taken == 2, f"{name} should run on the target-stationary kernel: {why}"
@@ -189,7 +192,7 @@ def test_device_check_reports_bad_index():
         rt.synchronize()
 
 
-@pytest.mark.parametrize("name,schedule", [("potjans_mini_d1", 2), ("potjans_mini", 1)])
+@pytest.mark.parametrize("name,schedule", [("potjans_mini_d1", 2), ("potjans_mini", 3), ("potjans_mini", 1)])
 def test_launch_boundaries_of_every_schedule_leave_the_usual_state(name, schedule):
     """Persistent launches of odd lengths (spikes delivered one step late inside a
     launch, or only partly before the neuron update) alternate with steps on the
@@ -198,6 +201,8 @@ def test_launch_boundaries_of_every_schedule_leave_the_usual_state(name, schedul
     model, steps, dump_every = CASES[name]()
     net = resolve(model)
     rt = _runtime(net, steps)
+    if schedule == 1:
+        rt.set_option("use_emit", 0)
     assert rt.schedule == schedule
     done, chunk = 0, [1, 2, 1, 5, 3, 17, 1, 1, 40]
     i = 0

@@ -69,7 +69,7 @@ class SynapseGroupDesc(C.Structure):
                 ("src_spike_times", C.c_void_p), ("trg_spike_times", C.c_void_p),
                 ("out_post", C.c_void_p), ("den_delay", C.c_void_p),
                 ("proc_connect", C.c_uint32), ("proc_weight_init", C.c_uint32),
-                ("rng_stream", C.c_uint32), ("reserved", C.c_uint32),
+                ("rng_stream", C.c_uint32), ("proc_weight_stream", C.c_uint32),
                 ("proc_connect_params", C.c_float * 4), ("proc_weight_params", C.c_float * 4),
                 ("src_sections", C.c_uint32), ("src_spk_slot_stride", C.c_uint32),
                 ("src_cnt_section_stride", C.c_uint64), ("src_spk_section_stride", C.c_uint64),

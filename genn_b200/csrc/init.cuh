@@ -95,6 +95,52 @@ __device__ __forceinline__ void storeInd(void *ind, unsigned long long idx, unsi
 //     from the multinomial, :300-336); targets ascend by sampling successive
 //     first-order statistics x += (1-x)*(1 - u^(1/c)) (:283-291).
 //   FixedNumberPostWithReplacement: `num` ascending targets per row likewise.
+// The targets of one presynaptic row, in row order: emit(n, target) for n = 0, 1, ...; returns how
+// many there are.  One Philox stream per row, so a row can be regenerated at any time from
+// (seed, stream, pre): the initialisation kernel below stores what this yields, the PROCEDURAL
+// presynaptic kernel (presynaptic_update.cuh) replays it for every spike.  `fixedLength` is the
+// row length for the snippets that take it as an input.
+template<typename F>
+__host__ __device__ __forceinline__ unsigned int generateRow(unsigned int snippet, const float *p, unsigned int pre,
+                                                             unsigned int trg_begin, unsigned int trg_end,
+                                                             unsigned int fixedLength, unsigned long long seed,
+                                                             unsigned int stream, F emit)
+{
+    const unsigned int numPost = trg_end - trg_begin;
+    b200_rng rng = b200_rng_init(seed, stream, pre);
+    unsigned int n = 0;
+    if(snippet == B200_CONNECT_FIXED_PROBABILITY || snippet == B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE) {
+        const float probLogRecip = p[1];       // 1 / log(1 - prob), computed on the host in double
+        int prevJ = -1;
+        while(true) {
+            const float u = b200_rng_uniform(&rng);
+            prevJ += 1 + (int)B200_FMUL(b200_logf(u), probLogRecip);
+            if(snippet == B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE && (unsigned int)prevJ + trg_begin == pre) continue;
+            if(prevJ >= 0 && (unsigned int)prevJ < numPost) {
+                emit(n, (unsigned int)prevJ + trg_begin);
+                n++;
+            }
+            else {
+                break;
+            }
+        }
+    }
+    else {
+        float x = 0.0f;
+        for(unsigned int c = fixedLength; c != 0; c--) {
+            const float u = b200_rng_uniform(&rng);
+            // 1 - u^(1/c) with u^(1/c) = exp(log(u)/c)
+            const float root = b200_expf(B200_FDIV(b200_logf(u), (float)c));
+            x = B200_FADD(x, B200_FMUL(B200_FSUB(1.0f, x), B200_FSUB(1.0f, root)));
+            unsigned int postIdx = (unsigned int)B200_FMUL(x, (float)numPost);
+            postIdx = (postIdx < numPost) ? postIdx : (numPost - 1);
+            emit(n, postIdx + trg_begin);
+            n++;
+        }
+    }
+    return n;
+}
+
 template<typename IndT>
 __global__ void __launch_bounds__(INIT_BLOCK)
 initSparseConnectivityKernel(unsigned int snippet, InitParams prm, unsigned int num_src,
@@ -104,55 +150,25 @@ initSparseConnectivityKernel(unsigned int snippet, InitParams prm, unsigned int 
 {
     const unsigned int pre = blockIdx.x * blockDim.x + threadIdx.x;
     if(pre >= num_src) return;
-    const unsigned int numPost = trg_end - trg_begin;
     const unsigned long long base = (unsigned long long)pre * row_stride;
-    b200_rng rng = b200_rng_init(seed, stream, pre);
-
-    if(snippet == B200_CONNECT_FIXED_PROBABILITY || snippet == B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE) {
-        const float probLogRecip = prm.p[1];       // 1 / log(1 - prob), computed on the host in double
-        int prevJ = -1;
-        unsigned int n = 0;
-        while(true) {
-            const float u = b200_rng_uniform(&rng);
-            prevJ += 1 + (int)B200_FMUL(b200_logf(u), probLogRecip);
-            if(snippet == B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE && (unsigned int)prevJ + trg_begin == pre) continue;
-            if(prevJ >= 0 && (unsigned int)prevJ < numPost) {
-                if(n < row_stride) {
-                    storeInd<IndT>(ind, base + n, (unsigned int)prevJ + trg_begin);
-                }
-                n++;
-            }
-            else {
-                break;
-            }
-        }
-        if(n > row_stride) {
-            atomicOr(&state->error, ERR_IND_RANGE);
-            n = row_stride;
-        }
-        row_length[pre] = n;
-    }
-    else {
-        unsigned int c = (snippet == B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT)
-            ? (unsigned int)prm.p[0] : row_length[pre];
+    const bool lengthIsOutput = (snippet == B200_CONNECT_FIXED_PROBABILITY || snippet == B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE);
+    unsigned int c = 0;
+    if(!lengthIsOutput) {
+        c = (snippet == B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT) ? (unsigned int)prm.p[0] : row_length[pre];
         if(c > row_stride) {
             atomicOr(&state->error, ERR_IND_RANGE);
             c = row_stride;
         }
-        if(snippet == B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT) row_length[pre] = c;
-        float x = 0.0f;
-        unsigned int n = 0;
-        for(; c != 0; c--) {
-            const float u = b200_rng_uniform(&rng);
-            // 1 - u^(1/c) with u^(1/c) = exp(log(u)/c)
-            const float root = b200_expf(B200_FDIV(b200_logf(u), (float)c));
-            x = B200_FADD(x, B200_FMUL(B200_FSUB(1.0f, x), B200_FSUB(1.0f, root)));
-            unsigned int postIdx = (unsigned int)B200_FMUL(x, (float)numPost);
-            postIdx = (postIdx < numPost) ? postIdx : (numPost - 1);
-            storeInd<IndT>(ind, base + n, postIdx + trg_begin);
-            n++;
-        }
     }
+    unsigned int n = generateRow(snippet, prm.p, pre, trg_begin, trg_end, c, seed, stream,
+                                 [&](unsigned int at, unsigned int target) {
+                                     if(at < row_stride) storeInd<IndT>(ind, base + at, target);
+                                 });
+    if(n > row_stride) {
+        atomicOr(&state->error, ERR_IND_RANGE);
+        n = row_stride;
+    }
+    if(lengthIsOutput || snippet == B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT) row_length[pre] = n;
 }
 
 // Column-build connectivity with a fixed in-degree: one thread per target

@@ -27,6 +27,7 @@
 #pragma once
 
 #include "common.cuh"
+#include "init.cuh"
 
 namespace b200
 {
@@ -279,5 +280,48 @@ presynapticPostSpanKernel(const SynapseLaunch L)
     }
     if(valid && events) redAdd(g.out_post + (unsigned long long)b * numTrg + post, acc);
     if(L.count_events && events) atomicAdd(&L.state->synaptic_events, (unsigned long long)events);
+}
+
+// PROCEDURAL connectivity (presynapticUpdateStrategySIMT.cc:394-566): nothing of the matrix is
+// stored; the row of every spiking neuron is regenerated from its Philox stream, exactly as the
+// initialisation kernel would have written it (generateRow, init.cuh), and so is every weight that
+// is not a constant (the stream of a weight is keyed on pre * row_stride + position, as in
+// initSparseVarKernel).  One thread per spike walks its row; grid (group, 1, batch).
+__global__ void __launch_bounds__(PRE_BLOCK)
+presynapticProceduralKernel(const SynapseLaunch L)
+{
+    const b200_synapse_group &g = L.groups[blockIdx.x];
+    const unsigned int b = blockIdx.z;
+    const unsigned int k = L.state->phase;
+    const unsigned int slots = g.src_delay_slots;
+    const unsigned int rslot = ringSlot(k + slots - g.axonal_delay, slots);
+    const unsigned int count = g.src_spk_cnt[b * slots + rslot];
+    const unsigned int *spk = g.src_spk + ((unsigned long long)b * slots + rslot) * g.num_src;
+    const unsigned int numTrg = g.num_trg;
+    const unsigned int D = g.max_den_delay;
+    float *target = (D ? g.den_delay + (unsigned long long)b * D * numTrg : g.out_post + (unsigned long long)b * numTrg);
+    const bool constant = (g.wu_model == B200_WU_STATIC_PULSE_CONSTANT_WEIGHT);
+    for(unsigned int s = threadIdx.x; s < count; s += blockDim.x) {
+        const unsigned int pre = spk[s];
+        if(pre >= g.num_src) {
+            atomicOr(&L.state->error, ERR_IND_RANGE);
+            continue;
+        }
+        const unsigned int fixedLength = (g.proc_connect == B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT)
+            ? (unsigned int)g.proc_connect_params[0] : (g.row_length ? g.row_length[pre] : 0u);
+        const unsigned int n = generateRow(g.proc_connect, g.proc_connect_params, pre, 0u, numTrg, fixedLength, L.seed, g.rng_stream,
+            [&](unsigned int at, unsigned int post) {
+                if(at >= g.row_stride) return;      // the row the initialisation kernel would have stored ends here
+                float w = g.wu_params[0];
+                if(!constant) {
+                    b200_rng rng = b200_rng_init(L.seed, g.proc_weight_stream, (unsigned long long)pre * g.row_stride + at);
+                    w = drawInitValue(g.proc_weight_init, g.proc_weight_params, &rng);
+                }
+                // dendritic delay is not generated procedurally: slot 0 of a ring is the front
+                redAdd(target + (D ? (unsigned long long)ringSlot(k + 1, D) * numTrg : 0ull) + post, w);
+            });
+        if(n > g.row_stride) atomicOr(&L.state->error, ERR_IND_RANGE);
+        if(L.count_events) atomicAdd(&L.state->synaptic_events, (unsigned long long)min(n, g.row_stride));
+    }
 }
 }   // namespace b200

@@ -109,7 +109,7 @@ struct b200_runner
     bool dirty = true;
 
     DeviceTable<b200_neuron_group> neuronTable;
-    DeviceTable<b200_synapse_group> sparseTable, postSpanTable, learnTable;
+    DeviceTable<b200_synapse_group> sparseTable, postSpanTable, learnTable, proceduralTable;
 
     // persistent fused-step path (batch 1, SPARSE non-learning groups only)
     bool fusedEligible = false;
@@ -612,8 +612,8 @@ int prepare(b200_runner *r)
         }
         CUDA_TRY(r->neuronTable.upload(r->neuronGroups, starts, r->stream));
     }
-    std::vector<b200_synapse_group> sparse, postSpan, learn;
-    std::vector<unsigned int> sparseStarts{0}, postSpanStarts{0}, learnStarts{0};
+    std::vector<b200_synapse_group> sparse, postSpan, learn, procedural;
+    std::vector<unsigned int> sparseStarts{0}, postSpanStarts{0}, learnStarts{0}, proceduralStarts{0};
     for(const auto &g : r->synapseGroups) {
         if(g.connectivity == B200_CONN_SPARSE) {
             sparse.push_back(g);
@@ -623,6 +623,10 @@ int prepare(b200_runner *r)
         else if(g.connectivity == B200_CONN_BITMASK || g.connectivity == B200_CONN_DENSE) {
             postSpan.push_back(g);
             postSpanStarts.push_back(postSpanStarts.back() + (g.row_stride + PRE_BLOCK - 1) / PRE_BLOCK);
+        }
+        else if(g.connectivity == B200_CONN_PROCEDURAL) {
+            procedural.push_back(g);
+            proceduralStarts.push_back(proceduralStarts.back() + 1);
         }
         else {
             return fail(B200_ERR_INVALID, "connectivity %u is not supported by this build", g.connectivity);
@@ -636,9 +640,11 @@ int prepare(b200_runner *r)
     CUDA_TRY(r->sparseTable.upload(sparse, sparseStarts, r->stream));
     CUDA_TRY(r->postSpanTable.upload(postSpan, postSpanStarts, r->stream));
     CUDA_TRY(r->learnTable.upload(learn, learnStarts, r->stream));
+    CUDA_TRY(r->proceduralTable.upload(procedural, proceduralStarts, r->stream));
 
     // ---- tables of the persistent fused-step kernel --------------------------------
-    r->fusedEligible = (r->batch == 1 && postSpan.empty() && learn.empty() && !r->neuronGroups.empty());
+    r->fusedEligible = (r->batch == 1 && postSpan.empty() && learn.empty() && procedural.empty() &&
+                        !r->neuronGroups.empty());
     r->fusedGroups = sparse;
     r->lagStale = true;
     r->schedule = b200_runner::PLAIN;
@@ -1098,6 +1104,12 @@ int enqueueSynapses(b200_runner *r, bool capturing)
         presynapticPostSpanKernel<<<grid, PRE_BLOCK, 0, r->stream>>>(synapseLaunch(r, r->postSpanTable));
         r->launches++;
     }
+    if(r->proceduralTable.num) {
+        ScopedTimer tm(r, "presynaptic_update", capturing);
+        const dim3 grid(r->proceduralTable.num, 1, r->batch);
+        presynapticProceduralKernel<<<grid, PRE_BLOCK, 0, r->stream>>>(synapseLaunch(r, r->proceduralTable));
+        r->launches++;
+    }
     if(r->learnTable.num) {
         ScopedTimer tm(r, "postsynaptic_update", capturing);
         const dim3 grid(r->learnTable.blocks, r->spikeLanes, r->batch);
@@ -1142,7 +1154,8 @@ int enqueueStep(b200_runner *r, unsigned long long numRec, bool capturing)
 
 unsigned int kernelsPerStep(const b200_runner *r)
 {
-    return 1u + (r->sparseTable.num ? 1u : 0u) + (r->postSpanTable.num ? 1u : 0u) + (r->learnTable.num ? 1u : 0u);
+    return 1u + (r->sparseTable.num ? 1u : 0u) + (r->postSpanTable.num ? 1u : 0u) + (r->learnTable.num ? 1u : 0u) +
+           (r->proceduralTable.num ? 1u : 0u);
 }
 
 int buildGraph(b200_runner *r, unsigned int len, unsigned long long numRec)
@@ -1211,6 +1224,7 @@ int b200_runner_destroy(b200_runner *r)
     r->neuronTable.release();
     r->sparseTable.release();
     r->postSpanTable.release();
+    r->proceduralTable.release();
     r->learnTable.release();
     if(r->fusedSlotStart) cudaFree(r->fusedSlotStart);
     if(r->fusedSources) cudaFree(r->fusedSources);
@@ -1368,6 +1382,16 @@ int b200_push_synapse_group(b200_runner *r, uint32_t idx, const b200_synapse_gro
     if(g->connectivity == B200_CONN_BITMASK) {
         if(!g->gp || (g->row_stride & 31u)) return fail(B200_ERR_INVALID, "BITMASK needs gp and a row stride padded to 32");
         if(g->wu_model != B200_WU_STATIC_PULSE_CONSTANT_WEIGHT) return fail(B200_ERR_INVALID, "BITMASK carries no per-synapse variables");
+    }
+    if(g->connectivity == B200_CONN_PROCEDURAL) {
+        if(g->proc_connect != B200_CONNECT_FIXED_PROBABILITY && g->proc_connect != B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE &&
+           g->proc_connect != B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT) {
+            return fail(B200_ERR_INVALID, "PROCEDURAL connectivity needs a snippet that builds rows without stored lengths");
+        }
+        if(g->wu_model != B200_WU_STATIC_PULSE && g->wu_model != B200_WU_STATIC_PULSE_CONSTANT_WEIGHT) {
+            return fail(B200_ERR_INVALID, "PROCEDURAL connectivity supports StaticPulse and StaticPulseConstantWeight");
+        }
+        if(!g->row_stride) return fail(B200_ERR_INVALID, "PROCEDURAL group without a row stride (longest row)");
     }
     if(g->wu_model != B200_WU_STATIC_PULSE_CONSTANT_WEIGHT && g->connectivity != B200_CONN_PROCEDURAL && !g->g) {
         return fail(B200_ERR_INVALID, "weight array missing");

@@ -254,6 +254,9 @@ class Plan:
                 self._new(f"{s.name}.col_length", np.uint32, (nt,))
                 self._new(f"{s.name}.remap", np.uint32, (nt * s.col_stride,))
                 self.init_tasks.append(InitTask("remap", s.name))
+        elif s.procedural:
+            # nothing to allocate: two Philox streams, the ones a SPARSE twin's initialisation would use
+            s.proc_streams = (self._stream(), self._stream() if s.wum == "STATIC" else 0)
         elif s.matrix == "BITMASK":
             words = (ns * s.row_stride) // 32
             self._new(f"{s.name}.gp", np.uint32, (words,), s.gp)
@@ -388,4 +391,20 @@ class Plan:
         d.out_post = self._ptr(f"psm{s.psm}.out_post")
         d.den_delay = self._ptr(f"psm{s.psm}.den_delay")
         d.rng_stream = self._stream()
+        if s.procedural:
+            import math
+            if s.wum not in ("STATIC", "CONST"):
+                raise ValueError(f"{s.name}: procedural connectivity supports StaticPulse and StaticPulseConstantWeight")
+            d.proc_connect = abi.CONNECT_KINDS[s.connect.snippet]
+            cp = [float(v) for v in s.connect.params.values()] + [0.0] * 4
+            if s.connect.snippet in ("FixedProbability", "FixedProbabilityNoAutapse"):
+                cp[1] = 1.0 / math.log(1.0 - cp[0])
+            for i in range(4):
+                d.proc_connect_params[i] = _f32(cp[i])
+            d.rng_stream, d.proc_weight_stream = s.proc_streams
+            if s.wum == "STATIC":
+                init = s.var_inits["g"]
+                d.proc_weight_init = abi.INIT_KINDS[init.snippet]
+                for i, v in enumerate(self._init_params(init)):
+                    d.proc_weight_params[i] = _f32(v)
         return d

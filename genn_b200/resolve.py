@@ -256,7 +256,12 @@ def resolve(model: GeNNModel) -> Net:
             r.row_stride = num_post
             r.g = per_syn.get("g")
         else:
-            r.row_stride = int(sg.max_connections or 0)
+            # PROCEDURAL: nothing is stored, but rows are regenerated exactly as the initialisation
+            # kernel would have written them, row stride (longest row) included
+            if sg.connect is None:
+                raise ValueError(f"{sg.name}: procedural connectivity needs a connectivity initialiser")
+            r.row_stride = int(sg.max_connections or
+                               calc_max_row_length(sg.connect.snippet, sg.connect.params, num_pre, num_post))
         syns.append(r)
     return Net(model.name, dt, int(model.seed), batch, bool(model.fuse_postsynaptic_models),
                bool(model.default_narrow_sparse_ind_enabled), pops, css, psms, syns)

@@ -195,8 +195,8 @@ typedef struct b200_synapse_group {
     /* PROCEDURAL: connectivity and weights regenerated per spike */
     uint32_t proc_connect;     /* b200_connect_init */
     uint32_t proc_weight_init; /* b200_var_init */
-    uint32_t rng_stream;
-    uint32_t reserved;
+    uint32_t rng_stream;       /* Philox stream of the connectivity (row r: element r of the stream) */
+    uint32_t proc_weight_stream; /* Philox stream of the weights (synapse pre*row_stride + position) */
     float    proc_connect_params[4];
     float    proc_weight_params[4];
     /* Sharded source population: the spike lists of `src_sections` processes lie one after another,

@@ -122,6 +122,8 @@ _PROTOTYPES = {
     "b200_update_neurons": [C.c_void_p, C.c_uint64],
     "b200_step_time": [C.c_void_p, C.c_uint64, C.c_uint64],
     "b200_custom_update": [C.c_void_p, C.c_char_p],
+    "b200_custom_update_reduce": [C.c_void_p, C.c_char_p],
+    "b200_custom_update_broadcast": [C.c_void_p, C.c_char_p],
     "b200_synchronize": [C.c_void_p],
     "b200_get_timestep": [C.c_void_p, C.POINTER(C.c_uint64)],
     "b200_set_timestep": [C.c_void_p, C.c_uint64],

@@ -71,18 +71,27 @@ postsynapticUpdateKernel(const SynapseLaunch L)
 
 constexpr int REDUCE_BLOCK = 256;
 
+// `phases`: bit 0 reduce, bit 1 broadcast.  Both in one pass on one GPU; a data-parallel run
+// reduces, combines the targets of all processes (an all-reduce outside this kernel) and
+// broadcasts in a second pass.
 __global__ void __launch_bounds__(REDUCE_BLOCK)
-batchReduceKernel(const b200_custom_update_group u, unsigned int batch)
+batchReduceKernel(const b200_custom_update_group u, unsigned int batch, unsigned int phases)
 {
     const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
     for(unsigned long long e = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; e < u.num_elements; e += stride) {
-        float acc = (u.op == B200_REDUCE_SUM) ? 0.0f : -3.402823466e+38f;
-        for(unsigned int b = 0; b < batch; b++) {
-            const float v = u.source[(unsigned long long)b * u.num_elements + e];
-            acc = (u.op == B200_REDUCE_SUM) ? B200_FADD(acc, v) : fmaxf(acc, v);
+        float acc;
+        if(phases & 1u) {
+            acc = (u.op == B200_REDUCE_SUM) ? 0.0f : -3.402823466e+38f;
+            for(unsigned int b = 0; b < batch; b++) {
+                const float v = u.source[(unsigned long long)b * u.num_elements + e];
+                acc = (u.op == B200_REDUCE_SUM) ? B200_FADD(acc, v) : fmaxf(acc, v);
+            }
+            u.target[e] = acc;
         }
-        u.target[e] = acc;
-        if(u.broadcast) {
+        else {
+            acc = u.target[e];
+        }
+        if(u.broadcast && (phases & 2u)) {
             const float w = B200_FMUL(acc, u.scale);
             for(unsigned int b = 0; b < batch; b++) u.source[(unsigned long long)b * u.num_elements + e] = w;
         }

@@ -1605,7 +1605,7 @@ int b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_ti
     return B200_OK;
 }
 
-int b200_custom_update(b200_runner *r, const char *name)
+static int runCustomUpdate(b200_runner *r, const char *name, unsigned int phases)
 {
     auto it = r->customUpdates.find(name);
     if(it == r->customUpdates.end()) return fail(B200_ERR_INVALID, "no custom update group '%s'", name);
@@ -1613,11 +1613,26 @@ int b200_custom_update(b200_runner *r, const char *name)
     for(const auto &u : it->second) {
         if(u.num_elements == 0) continue;
         const unsigned int blocks = (unsigned int)std::min<uint64_t>((u.num_elements + REDUCE_BLOCK - 1) / REDUCE_BLOCK, 148u * 16u);
-        batchReduceKernel<<<blocks, REDUCE_BLOCK, 0, r->stream>>>(u, r->batch);
+        batchReduceKernel<<<blocks, REDUCE_BLOCK, 0, r->stream>>>(u, r->batch, phases);
         r->launches++;
     }
     CUDA_TRY(cudaPeekAtLastError());
     return B200_OK;
+}
+
+int b200_custom_update(b200_runner *r, const char *name)
+{
+    return runCustomUpdate(r, name, 3u);
+}
+
+int b200_custom_update_reduce(b200_runner *r, const char *name)
+{
+    return runCustomUpdate(r, name, 1u);
+}
+
+int b200_custom_update_broadcast(b200_runner *r, const char *name)
+{
+    return runCustomUpdate(r, name, 2u);
 }
 
 int b200_synchronize(b200_runner *r)

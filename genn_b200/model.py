@@ -387,14 +387,17 @@ class CustomUpdate:
     variable and writes a REDUCE_BATCH_SUM / REDUCE_BATCH_MAX target
     (customUpdateModels.h, backendSIMT.cc:888-927, 1109-1147)."""
 
-    def __init__(self, name: str, group_name: str, operation: str, source, target: str):
+    def __init__(self, name: str, group_name: str, operation: str, source, target: str,
+                 broadcast: bool = False, scale: float = 1.0):
         if operation not in ("SUM", "MAX"):
             raise ValueError("operation must be SUM or MAX")
         self.name = name
         self.group_name = group_name
         self.operation = operation
-        self.source = source        # (SynapseGroup|NeuronGroup, var name)
+        self.source = source        # (SynapseGroup|NeuronGroup|CurrentSource, var name)
         self.target_name = target
+        self.broadcast = bool(broadcast)    # write scale * reduced value back into every batch copy
+        self.scale = float(scale)
         self.vars: Dict[str, Variable] = {}
 
 
@@ -481,10 +484,11 @@ class GeNNModel:
         self.current_sources[cs_name] = cs
         return cs
 
-    def add_custom_update(self, cu_name: str, group_name: str, operation: str, source, target: str = "reduction"):
+    def add_custom_update(self, cu_name: str, group_name: str, operation: str, source, target: str = "reduction",
+                          broadcast: bool = False, scale: float = 1.0):
         if self._built:
             raise Exception("GeNN model already built")
-        cu = CustomUpdate(cu_name, group_name, operation, source, target)
+        cu = CustomUpdate(cu_name, group_name, operation, source, target, broadcast, scale)
         self.custom_updates[cu_name] = cu
         return cu
 
@@ -523,10 +527,12 @@ class GeNNModel:
             raise Exception("GeNN model has to be loaded before stepping")
         self._runtime.step_time(num_steps)
 
-    def custom_update(self, name: str):
+    def custom_update(self, name: str, all_reduce: bool = False):
+        """Run custom update group ``name``.  ``all_reduce``: combine the reduced values of all processes
+        of a data-parallel run (every process holds a share of the batch) before writing them back."""
         if not self._loaded:
             raise Exception("GeNN model has to be loaded before performing custom update")
-        self._runtime.custom_update(name)
+        self._runtime.custom_update(name, all_reduce)
 
     def pull_recording_buffers_from_device(self):
         if not self._loaded:

@@ -100,6 +100,7 @@ class Runtime:
                  shard: Optional[Tuple[int, int]] = None, net: Optional[Net] = None, exchange=None):
         self.lib = abi.load_library()
         self.model = model
+        self.device = int(device)
         self.net = net if net is not None else resolve(model)
         self.num_recording_timesteps = int(num_recording_timesteps or 0)
         h = C.c_void_p()
@@ -125,8 +126,10 @@ class Runtime:
             mine = bytes([1 if self.counter("lag_eligible") else 0])
             everyone = (exchange or all_gather_bytes)(mine)
             self.set_option("lag_agreed", 1.0 if all(b[0] for b in everyone) else 0.0)
+        self._cu_targets = {}
         if model is not None:
             self._bind_model_views()
+            self._push_custom_updates()
             if getattr(model, "timing_enabled", False):
                 check(self.lib.b200_enable_timing(self.handle, 1))
         self.synchronize()
@@ -244,8 +247,43 @@ class Runtime:
     def update_neurons(self):
         check(self.lib.b200_update_neurons(self.handle, self.num_recording_timesteps))
 
-    def custom_update(self, name: str):
-        check(self.lib.b200_custom_update(self.handle, name.encode()))
+    def _push_custom_updates(self):
+        """One batch-reduce descriptor per custom update of the model, merged by group name."""
+        from .model import Variable
+        per_group = {}
+        for cu in self.model.custom_updates.values():
+            obj, var = cu.source
+            src = self.plan.arrays[f"{obj.name}.{var}"]
+            if src.dtype != np.float32 or src.shape[0] != self.net.batch_size:
+                raise abi.B200Error(f"custom update {cu.name}: {obj.name}.{var} is not a per-batch fp32 variable")
+            elements = int(np.prod(src.shape[1:], dtype=np.int64))
+            trg = self.plan._new(f"cu.{cu.name}.{cu.target_name}", np.float32, (elements,))
+            d = abi.CustomUpdateDesc()
+            d.op = abi.REDUCE_SUM if cu.operation == "SUM" else abi.REDUCE_MAX
+            d.broadcast, d.scale, d.num_elements = int(cu.broadcast), cu.scale, elements
+            d.source, d.target = src.ptr, trg.ptr
+            idx = per_group.get(cu.group_name, 0)
+            per_group[cu.group_name] = idx + 1
+            check(self.lib.b200_push_custom_update(self.handle, cu.group_name.encode(), idx, C.byref(d)))
+            self._cu_targets.setdefault(cu.group_name, []).append((trg, cu.operation))
+            v = Variable(cu.target_name, np.float32, None, (elements,))
+            v._array = trg.handle
+            cu.vars[cu.target_name] = v
+
+    def custom_update(self, name: str, all_reduce: bool = False):
+        """``all_reduce``: a data-parallel run (every process holds a share of the batch): reduce this
+        share, combine the targets of all processes with NCCL, write the combined value back."""
+        if not all_reduce:
+            check(self.lib.b200_custom_update(self.handle, name.encode()))
+            return
+        import torch
+        from .collectives import all_reduce_targets, device_tensor
+        check(self.lib.b200_custom_update_reduce(self.handle, name.encode()))
+        self.synchronize()
+        targets = self._cu_targets.get(name, [])
+        all_reduce_targets([device_tensor(t.ptr, t.shape, self.device) for t, _ in targets], [op for _, op in targets])
+        torch.cuda.synchronize(self.device)
+        check(self.lib.b200_custom_update_broadcast(self.handle, name.encode()))
 
     def synchronize(self):
         check(self.lib.b200_synchronize(self.handle))

@@ -285,6 +285,13 @@ int  b200_update_synapses(b200_runner *r);
 int  b200_update_neurons(b200_runner *r, uint64_t num_recording_timesteps);
 int  b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_timesteps);
 int  b200_custom_update(b200_runner *r, const char *name);
+/* The two halves of a custom update group for data-parallel runs (every process holds a share of the
+ * batch): reduce this process's share into the targets, let the caller combine the targets of all
+ * processes (an all-reduce over NCCL on the device arrays), then write the combined value back
+ * into every batch copy.  The reference generates one NCCL reduction per such group
+ * (backends/cuda/backend.cc, genNCCLReduction). */
+int  b200_custom_update_reduce(b200_runner *r, const char *name);
+int  b200_custom_update_broadcast(b200_runner *r, const char *name);
 /* Same, bracketed by CUDA events recorded on the runner's stream; waits for completion. */
 int  b200_step_time_timed(b200_runner *r, uint64_t num_steps, uint64_t num_recording_timesteps, float *milliseconds);
 /* Waits for the stream and reports failed device-side checks (out-of-range index, row overflow). */

@@ -161,6 +161,23 @@ class OracleRunner:
     def step(self, n: int = 1):
         self._l.oracle_step(self._h, n, self.num_recording_timesteps)
 
+    def add_custom_update(self, operation: str, source: str, broadcast: bool = False, scale: float = 1.0) -> str:
+        """Batch-reduce `source` ([batch, ...] fp32 array of the plan); returns the target array's name."""
+        src = self.plan.arrays[source]
+        elements = int(np.prod(src.shape[1:], dtype=np.int64))
+        idx = getattr(self, "_num_custom", 0)
+        trg = self.plan._new(f"cu.{idx}.reduction", np.float32, (elements,))
+        d = abi.CustomUpdateDesc()
+        d.op = abi.REDUCE_SUM if operation == "SUM" else abi.REDUCE_MAX
+        d.broadcast, d.scale, d.num_elements = int(broadcast), scale, elements
+        d.source, d.target = src.ptr, trg.ptr
+        self._l.oracle_push_custom_update(self._h, idx, C.byref(d))
+        self._num_custom = idx + 1
+        return trg.name
+
+    def custom_update(self):
+        self._l.oracle_custom_update(self._h, 0, getattr(self, "_num_custom", 0))
+
     @property
     def timestep(self) -> int:
         return self._l.oracle_timestep(self._h)

@@ -39,6 +39,9 @@ if REPO not in sys.path:
 
 DT_MS = 0.1
 ALGO_BYTES_PER_SPIKE = 8           # spike id + row length
+# dram__bytes_read.sum + dram__bytes_write.sum of one 300-step launch of streamStepKernel on the
+# Potjans x1 workload, per time step (profiles/stream_step_potjans.md)
+NCU_DRAM_BYTES_PER_TIME_STEP = (344135424 + 4409856) / 300.0
 
 
 def measured_peaks():
@@ -329,14 +332,29 @@ def main():
         rt.enable_timing(False)
         nat_bytes = tev * bpe + tsp * ALGO_BYTES_PER_SPIKE
         nat_gbs = nat_bytes / pre_s / 1e9 if pre_s > 0 else 0.0
-        roofline = {"kernel": "presynapticSparseKernel", "bound": "hbm", "achieved": nat_gbs, "peak": hbm_peak,
-                    "unit": "GB/s", "frac": nat_gbs / hbm_peak, "traffic": None, "peak_source": peak_kind,
-                    "launches": probe_steps, "avg_launch_us": pre_s / probe_steps * 1e6,
-                    "neuron_kernel_avg_launch_us": neu_s / probe_steps * 1e6,
-                    "algorithmic_bytes_per_launch": nat_bytes / probe_steps,
+        per_kernel = {"kernel": "presynapticSparseKernel", "achieved": nat_gbs, "unit": "GB/s", "frac": nat_gbs / hbm_peak,
+                      "launches": probe_steps, "avg_launch_us": pre_s / probe_steps * 1e6,
+                      "neuron_kernel_avg_launch_us": neu_s / probe_steps * 1e6,
+                      "algorithmic_bytes_per_launch": nat_bytes / probe_steps,
+                      "note": "the one-launch-per-kernel path at the same firing rates (CUDA event pair around every launch)"}
+        # the kernel of the timed region: ONE persistent launch runs all its time steps
+        launch_bytes = float(ev1 - ev0) * bpe + float(sp1 - sp0) * ALGO_BYTES_PER_SPIKE
+        launch_gbs = launch_bytes / seconds / 1e9
+        timed_steps = args.steps * block
+        traffic = (NCU_DRAM_BYTES_PER_TIME_STEP * timed_steps
+                   if (scale == 1.0 and args.min_delay == 0.0 and rt.schedule == 3) else None)
+        roofline = {"kernel": ["fusedStepKernel", "fusedStepKernel", "fusedStepKernel", "streamStepKernel"][rt.schedule]
+                              + f" (persistent: {timed_steps} time steps in one launch)",
+                    "bound": "hbm", "achieved": launch_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": launch_gbs / hbm_peak,
+                    "traffic": traffic, "peak_source": peak_kind, "launches": 1, "avg_launch_ms": ms,
+                    "algorithmic_bytes_per_launch": launch_bytes,
                     "persistent_kernel_phase_cycles_per_step": phase_cycles,
-                    "note": "natural firing rates: under 1 MB per launch, latency-bound by construction; timed on the "
-                            "one-launch-per-kernel path (CUDA event pair around every launch)"}
+                    "per_kernel_path": per_kernel,
+                    "note": "natural firing rates: about 0.7 MB of synapse rows per time step, so a step is bound by "
+                            "latency (grid barrier, dependent loads), not by HBM; roofline_saturated shows the same "
+                            "delivery code with enough spikes to be bandwidth-relevant.  traffic: dram bytes of a "
+                            "300-step launch under ncu, scaled to this launch by the number of time steps "
+                            "(profiles/stream_step_potjans.md)"}
     else:
         # a sharded model runs on the persistent kernel only: its presynaptic phase is timed with clock64
         pre_s = phase_cycles["cycles_presynaptic"] * probe_steps / sm_hz

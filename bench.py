@@ -300,7 +300,7 @@ def main():
     # ---- where a step's time goes inside the persistent kernel (clock64 per phase, CTA 0) ---
     probe_steps = min(args.steps * block, 2000)
     rt.set_option("fused_profile", 1)
-    names = ["cycles_presynaptic", "cycles_barrier_a", "cycles_neuron", "cycles_barrier_b"] + [f"probe{i}" for i in range(8)]
+    names = ["cycles_presynaptic", "cycles_barrier_a", "cycles_neuron", "cycles_barrier_b"] + [f"probe{i}" for i in range(12)]
     before = [rt.counter(n) for n in names]
     pev0, psp0 = rt.counter("synaptic_events"), rt.counter("spikes")
     barrier()

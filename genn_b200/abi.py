@@ -121,6 +121,9 @@ _PROTOTYPES = {
     "b200_update_synapses": [C.c_void_p],
     "b200_update_neurons": [C.c_void_p, C.c_uint64],
     "b200_step_time": [C.c_void_p, C.c_uint64, C.c_uint64],
+    "b200_near_export": [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint64), C.c_uint32],
+    "b200_near_import": [C.c_void_p, C.c_uint32, C.c_void_p, C.POINTER(C.c_uint64), C.POINTER(C.c_uint32)],
+    "b200_near_finish": [C.c_void_p, C.c_int],
     "b200_custom_update": [C.c_void_p, C.c_char_p],
     "b200_custom_update_reduce": [C.c_void_p, C.c_char_p],
     "b200_custom_update_broadcast": [C.c_void_p, C.c_char_p],

@@ -30,7 +30,7 @@ struct StepState
     // SM clock cycles CTA 0 spent in each phase of the persistent kernel:
     // presynaptic work, barrier after it, neuron work, barrier after it
     unsigned long long phase_cycles[4];
-    unsigned long long probe[8];        // finer clock64 sums of the persistent kernel's profile mode
+    unsigned long long probe[12];        // finer clock64 sums of the persistent kernel's profile mode
 };
 
 constexpr unsigned int ERR_SPIKE_OVERFLOW = 1u;

@@ -140,8 +140,7 @@ struct FusedLaunch
     // "deliver at emission" mode of that kernel (near.cuh)
     unsigned int emit;                   // 1: the spiking thread delivers its near synapses, one barrier per step
     unsigned int num_rings;
-    const uint2 *near_table;
-    const struct NearRing *near_rings;   // [num_rings]
+    const struct NearRing *near_rings;   // [world][num_rings]: the rings of every process, as mapped here
     const struct NearSpace *near_spaces; // [neuron groups]
 };
 

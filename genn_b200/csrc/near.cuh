@@ -38,10 +38,15 @@ struct NearRing
 };
 
 // Where the rows of one neuron group's spikes are (a group that is no spike source: shift 0xFFFFFFFF).
+// In a sharded model a row holds the synapses onto EVERY process's neurons, one block of
+// 1 << peer_shift entries per process (process p: entries [p << peer_shift, (p + 1) << peer_shift)),
+// and only the rows of this process's own neurons are here.
 struct NearSpace
 {
-    unsigned long long first_cell;   // index of the first entry of the population's first row
+    const uint2 *rows;               // first entry of the row of neuron `first_row`
     unsigned int shift;              // rows hold 1 << shift entries
+    unsigned int first_row;          // neuron id of the first row held
+    unsigned int peer_shift;         // one process's block of a row (one process: = shift)
     unsigned int pad;
 };
 
@@ -104,30 +109,41 @@ __global__ void nearFillKernel(const b200_synapse_group g, unsigned int ring, un
     }
 }
 
-// The near synapses of one spiking neuron, delivered by its warp: `cell0` is the first entry of
-// its row, `front` the phase of the step in which it spiked.  A synapse of delay e lands in the
-// slot the neuron update e + 1 steps later reads.
-__device__ __forceinline__ void nearDeliverRow(const uint2 *__restrict__ table, unsigned long long cell0, unsigned int shift,
-                                               const NearRing *rings, unsigned int front, StepState *state)
+// The near synapses of one spiking neuron, delivered by its warp: one memory round trip for the
+// whole row (`row`: its first entry), up to eight loads per lane in flight.  In a sharded model the
+// row has one block per process and `rings` one set of rings per process, the other processes'
+// mapped here: reductions into those travel over NVLink.  `front` is the phase of the step in
+// which the neuron spiked: a synapse of delay e lands in the slot the neuron update e + 1 steps
+// later reads.  Additions into another process's ring are made with atomics that RETURN the old
+// value, and the sum of those values is handed back: once the caller has consumed it, every one
+// of them has been performed at that GPU, which is all the ordering the exchange needs (a
+// system-wide fence after fire-and-forget reductions took 7 k cycles; measured).
+__device__ __forceinline__ float nearDeliverRow(const uint2 *__restrict__ row, unsigned int shift, unsigned int peerShift,
+                                               const NearRing *rings, unsigned int numRings, unsigned int rank,
+                                               unsigned int front, StepState *state)
 {
     const unsigned int lane = threadIdx.x & 31u;
     const unsigned int cells = 1u << shift;
+    float returned = 0.0f;
     for(unsigned int c0 = 0; c0 < cells; c0 += 256u) {
         // up to eight loads per lane in flight before the first reduction
         uint2 entry[8];
         #pragma unroll
         for(unsigned int u = 0; u < 8u; u++) {
             const unsigned int c = c0 + u * 32u + lane;
-            entry[u] = (c < cells) ? __ldg(&table[cell0 + c]) : make_uint2(0u, 0u);
+            entry[u] = (c < cells) ? __ldg(&row[c]) : make_uint2(0u, 0u);
         }
         #pragma unroll
         for(unsigned int u = 0; u < 8u; u++) {
             if(entry[u].y != 0u) {
-                const NearRing &ring = rings[(entry[u].x >> 1) & 0x7Fu];
+                // whose neurons this block of the row targets: that process's rings, as mapped here
+                const unsigned int owner = (c0 + u * 32u + lane) >> peerShift;
+                const NearRing &ring = rings[owner * numRings + ((entry[u].x >> 1) & 0x7Fu)];
                 const unsigned int post = entry[u].x >> 8;
                 if(post < ring.num_neurons) {
-                    redAdd(ring.den_delay + (unsigned long long)ringSlot(front + 2u + (entry[u].x & 1u), ring.D) * ring.num_neurons + post,
-                           __uint_as_float(entry[u].y));
+                    float *cell = ring.den_delay + (unsigned long long)ringSlot(front + 2u + (entry[u].x & 1u), ring.D) * ring.num_neurons + post;
+                    if(owner == rank) redAdd(cell, __uint_as_float(entry[u].y));
+                    else returned += atomicAdd(cell, __uint_as_float(entry[u].y));
                 }
                 else {
                     atomicOr(&state->error, ERR_IND_RANGE);
@@ -135,5 +151,6 @@ __device__ __forceinline__ void nearDeliverRow(const uint2 *__restrict__ table, 
             }
         }
     }
+    return returned;
 }
 }   // namespace b200

@@ -7,7 +7,9 @@
 #include <cuda_runtime.h>
 
 #include <algorithm>
+#include <cctype>
 #include <cstdarg>
+#include <cstdlib>
 #include <cstdio>
 #include <cstring>
 #include <map>
@@ -149,11 +151,31 @@ struct b200_runner
     enum Schedule { PLAIN = 0, SPLIT = 1, LAG = 2, EMIT = 3 };
     // "deliver at emission" mode (near.cuh): near synapses of all groups, one row per source neuron
     bool useEmit = true;
-    uint2 *nearTable = nullptr;
-    NearRing *nearRings = nullptr;          // device copies
+    uint2 *nearTable = nullptr;             // rows of every source neuron (synapses onto THIS process's neurons)
+    NearRing *nearRings = nullptr;          // device copies, [world][numRings] and [world][neuron groups]
     NearSpace *nearSpaces = nullptr;
     unsigned int numRings = 0;
+    // sharded model: built by b200_near_export / b200_near_import / b200_near_finish
+    std::vector<NearRing> nearRingsHost;            // this process's rings
+    std::vector<unsigned long long> nearCellHost;   // per neuron group: first entry of its rows in nearTable
+    std::vector<unsigned int> nearShiftHost;        // per neuron group: row length shift (0xFFFFFFFF: no rows)
+    std::vector<uint2*> nearImported;               // per neuron group: the rows of this process's neurons, one block per process
+    std::vector<NearSpace> nearSpacesAll;           // [neuron groups]
+    std::vector<bool> nearPeerDone;                 // per process: its blocks have been copied in
+    bool emitAgreed = false;                        // every process exported, imported and qualified
+    bool nearDataStale = false;                     // synapse arrays changed after the exchange
     Schedule schedule = PLAIN;
+
+    void dropNear()
+    {
+        if(nearTable) cudaFree(nearTable);
+        if(nearRings) cudaFree(nearRings);
+        if(nearSpaces) cudaFree(nearSpaces);
+        for(uint2 *p : nearImported) if(p) cudaFree(p);
+        nearImported.clear();
+        nearTable = nullptr; nearRings = nullptr; nearSpaces = nullptr; numRings = 0;
+        emitAgreed = false;
+    }
 
     void dropUrgent()
     {
@@ -162,10 +184,7 @@ struct b200_runner
         if(urgentEntries) cudaFree(urgentEntries);
         if(fusedUrgent) cudaFree(fusedUrgent);
         urgentOffsets = nullptr; urgentEntries = nullptr; fusedUrgent = nullptr;
-        if(nearTable) cudaFree(nearTable);
-        if(nearRings) cudaFree(nearRings);
-        if(nearSpaces) cudaFree(nearSpaces);
-        nearTable = nullptr; nearRings = nullptr; nearSpaces = nullptr; numRings = 0;
+        if(!emitAgreed) dropNear();
     }
 
     // spike exchange of a sharded model
@@ -535,7 +554,8 @@ int buildFusedTables(b200_runner *r)
                         align16(sizeof(unsigned int) * slotStart.size()) +
                         (r->fusedUrgent ? align16(sizeof(FusedUrgent) * sparse.size()) : 0) +
                         (r->schedule == b200_runner::EMIT
-                            ? align16(sizeof(NearRing) * r->numRings) + align16(sizeof(NearSpace) * r->neuronGroups.size()) : 0);
+                            ? align16(sizeof(NearRing) * r->numRings * r->world) +
+                              align16(sizeof(NearSpace) * r->neuronGroups.size()) : 0);
     r->fusedStage = r->fusedSmemBytes <= 200 * 1024;
     {
         // SPLIT schedule: the warp-specialised kernel, if the neuron slots (dealt out evenly over one
@@ -727,7 +747,7 @@ int launchOwner(b200_runner *r, unsigned long long numSteps, unsigned long long 
 // Near-synapse table of the "deliver at emission" schedule; leaves r->schedule alone if the model
 // does not qualify (a group without a delay ring of three slots or more, an axonal delay, a ring
 // that is not a postsynaptic model of a neuron group, too few free warps for streaming).
-int buildNearTables(b200_runner *r)
+int buildNearTables(b200_runner *r, bool forExport = false)
 {
     const auto &groups = r->fusedGroups;
     const size_t n = groups.size(), numNeuronGroups = r->neuronGroups.size();
@@ -759,12 +779,21 @@ int buildNearTables(b200_runner *r)
             }
         }
         if(!found || rings.size() > NEAR_MAX_RINGS) return B200_OK;
+        if(forExport) {
+            // the other processes reduce into this ring over NVLink: it has to lie in the exchange arena
+            const unsigned char *ring = reinterpret_cast<const unsigned char*>(g.den_delay);
+            if(ring < r->arena || ring >= r->arena + r->arenaBytes) return B200_OK;
+        }
         found = false;
         for(size_t ni = 0; ni < numNeuronGroups && !found; ni++) {
             const auto &ng = r->neuronGroups[ni];
-            // the whole population must be updated here: the spiking thread looks its row up by neuron id
-            if(ng.spk_cnt == g.src_spk_cnt && ng.num_neurons == g.num_src && ng.first_neuron == 0 &&
-               ng.num_update == ng.num_neurons) {
+            // the spiking thread looks its row up by neuron id.  One process: it updates the whole
+            // population.  Sharded: the rows are built for all source neurons here and handed to
+            // the processes that own them (b200_near_import); this process's own list section
+            // is `rank` sections into the population's lists.
+            const unsigned int *own = g.src_spk_cnt + (forExport ? (size_t)r->rank * g.src_cnt_section_stride : 0);
+            if(ng.spk_cnt == own && ng.num_neurons == g.num_src &&
+               (forExport || (ng.first_neuron == 0 && ng.num_update == ng.num_neurons))) {
                 sourceOf[gi] = (unsigned int)ni;
                 found = true;
             }
@@ -789,12 +818,12 @@ int buildNearTables(b200_runner *r)
     std::vector<unsigned int> counts(totalRows);
     CUDA_TRY(cudaMemcpyAsync(counts.data(), cursor, sizeof(unsigned int) * totalRows, cudaMemcpyDeviceToHost, r->stream));
     CUDA_TRY(cudaStreamSynchronize(r->stream));
-    std::vector<NearSpace> spaces(numNeuronGroups);
+    std::vector<unsigned long long> firstCell(numNeuronGroups, 0ull);
+    std::vector<unsigned int> shifts(numNeuronGroups, 0xFFFFFFFFu);
     unsigned long long cells = 0;
     for(size_t ni = 0; ni < numNeuronGroups; ni++) {
         bool isSource = false;
         for(size_t gi = 0; gi < n; gi++) isSource = isSource || sourceOf[gi] == ni;
-        spaces[ni] = NearSpace{0ull, 0xFFFFFFFFu, 0u};
         if(!isSource) continue;
         unsigned int longest = 0;
         for(unsigned long long row = rowBase[ni]; row < rowBase[ni + 1]; row++) longest = std::max(longest, counts[row]);
@@ -805,8 +834,8 @@ int buildNearTables(b200_runner *r)
             cudaFree(cursor);
             return B200_OK;
         }
-        spaces[ni].first_cell = cells;
-        spaces[ni].shift = shift;
+        firstCell[ni] = cells;
+        shifts[ni] = shift;
         cells += (unsigned long long)r->neuronGroups[ni].num_neurons << shift;
     }
     if(cells >= (1ull << 33)) {      // 64 GB of table: not worth it
@@ -822,11 +851,11 @@ int buildNearTables(b200_runner *r)
         const auto &g = groups[gi];
         if(!g.num_src) continue;
         const unsigned int blocks = std::min(1184u, (g.num_src + 7u) / 8u);
-        const NearSpace &space = spaces[sourceOf[gi]];
+        const unsigned int src = sourceOf[gi];
         const int e = withIndType(g.ind_bytes, [&](auto tag) -> int {
             using IndT = decltype(tag);
-            nearFillKernel<IndT><<<blocks, 256, 0, r->stream>>>(g, ringOf[gi], cursor + rowBase[sourceOf[gi]],
-                                                                r->nearTable + space.first_cell, space.shift, bad);
+            nearFillKernel<IndT><<<blocks, 256, 0, r->stream>>>(g, ringOf[gi], cursor + rowBase[src],
+                                                                r->nearTable + firstCell[src], shifts[src], bad);
             return B200_OK;
         });
         if(e) return e;
@@ -844,6 +873,12 @@ int buildNearTables(b200_runner *r)
         return B200_OK;
     }
     r->numRings = (unsigned int)rings.size();
+    r->nearRingsHost = rings;
+    r->nearCellHost = firstCell;
+    r->nearShiftHost = shifts;
+    if(forExport) return B200_OK;       // the owners of the source neurons take their rows from here
+    std::vector<NearSpace> spaces(numNeuronGroups);
+    for(size_t ni = 0; ni < numNeuronGroups; ni++) spaces[ni] = NearSpace{r->nearTable + firstCell[ni], shifts[ni], 0u, shifts[ni], 0u};
     CUDA_TRY(cudaMalloc(&r->nearRings, sizeof(NearRing) * rings.size()));
     CUDA_TRY(cudaMemcpy(r->nearRings, rings.data(), sizeof(NearRing) * rings.size(), cudaMemcpyHostToDevice));
     CUDA_TRY(cudaMalloc(&r->nearSpaces, sizeof(NearSpace) * spaces.size()));
@@ -919,6 +954,13 @@ int refreshSchedule(b200_runner *r)
         r->lagEligible = lagOk;
         if(r->useLag && lagOk && (!r->sharded() || r->lagAgreed)) {
             r->schedule = b200_runner::LAG;
+        }
+        else if(r->useEmit && r->sharded() && r->emitAgreed) {
+            if(r->nearDataStale) {
+                return fail(B200_ERR_STATE, "synapse arrays of a sharded model changed after its processes exchanged "
+                                            "their near-synapse tables: run b200_near_export / import / finish again");
+            }
+            r->schedule = b200_runner::EMIT;        // tables exchanged between the processes beforehand
         }
         else if(r->useEmit && !r->sharded() && r->streamWarpsWanted != 0 && r->fusedStage) {
             const int e = buildNearTables(r);
@@ -999,7 +1041,6 @@ int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long 
     L.slots_per_cta = r->slotsPerCta;
     L.emit = (r->schedule == b200_runner::EMIT) ? 1u : 0u;
     L.num_rings = r->numRings;
-    L.near_table = r->nearTable;
     L.near_rings = r->nearRings;
     L.near_spaces = r->nearSpaces;
     L.neuron.groups = r->neuronTable.d;
@@ -1232,6 +1273,7 @@ int b200_runner_destroy(b200_runner *r)
     if(r->fusedBarrier) cudaFree(r->fusedBarrier);
     if(r->lagScan) cudaFree(r->lagScan);
     r->dropUrgent();
+    r->dropNear();
     if(r->fusedCtaCycles) cudaFree(r->fusedCtaCycles);
     r->dropOwner();
     for(unsigned int p = 0; p < B200_MAX_RANKS; p++) {
@@ -1316,6 +1358,121 @@ int b200_exchange_open_peer(b200_runner *r, uint32_t peer_rank, const void *hand
     return B200_OK;
 }
 
+/* ---- sharded "deliver at emission": every process builds the near-synapse rows of ALL source neurons
+ *      onto its own neurons, then hands each process the rows of that process's neurons ------------- */
+int b200_near_export(b200_runner *r, void *handle_64_bytes, uint64_t *meta, uint32_t meta_words)
+{
+    if(!r || !handle_64_bytes || !meta) return fail(B200_ERR_INVALID, "null argument");
+    CUDA_TRY(cudaSetDevice(r->device));
+    int e = prepare(r);
+    if(e) return e;
+    r->emitAgreed = false;
+    r->dropNear();
+    memset(handle_64_bytes, 0, 64);
+    const size_t groups = r->neuronGroups.size();
+    if(meta_words < 3 + 2 * groups) return fail(B200_ERR_INVALID, "meta array too short: %zu words needed", 3 + 2 * groups);
+    meta[0] = 0; meta[1] = groups; meta[2] = 0;
+    if(!r->sharded() || !r->fusedEligible || !r->useEmit || r->streamWarpsWanted == 0 || !r->fusedStage) return B200_OK;
+    e = buildNearTables(r, true);
+    if(e) return e;
+    if(!r->nearTable) return B200_OK;       // does not qualify
+    cudaIpcMemHandle_t h;
+    CUDA_TRY(cudaIpcGetMemHandle(&h, r->nearTable));
+    memcpy(handle_64_bytes, &h, sizeof(h));
+    meta[0] = 1; meta[2] = r->numRings;
+    for(size_t ni = 0; ni < groups; ni++) {
+        meta[3 + 2 * ni] = r->nearCellHost[ni];
+        meta[4 + 2 * ni] = r->nearShiftHost[ni];
+    }
+    r->nearImported.assign(groups, nullptr);
+    r->nearSpacesAll.assign(groups, NearSpace{nullptr, 0xFFFFFFFFu, 0u, 0u, 0u});
+    r->nearPeerDone.assign(r->world, false);
+    r->nearDataStale = false;
+    return B200_OK;
+}
+
+int b200_near_import(b200_runner *r, uint32_t peer_rank, const void *handle_64_bytes, const uint64_t *meta,
+                     const uint32_t *common_shift)
+{
+    if(!r || !handle_64_bytes || !meta || !common_shift || peer_rank >= r->world) return fail(B200_ERR_INVALID, "bad arguments to b200_near_import");
+    const size_t groups = r->neuronGroups.size();
+    if(r->nearImported.size() != groups || r->nearPeerDone.size() != r->world) return fail(B200_ERR_STATE, "b200_near_export has to come first");
+    if(!meta[0] || meta[1] != groups || meta[2] != r->numRings) return fail(B200_ERR_STATE, "process %u does not qualify or runs another model", peer_rank);
+    CUDA_TRY(cudaSetDevice(r->device));
+    const uint2 *table = r->nearTable;
+    void *mapped = nullptr;
+    if(peer_rank != r->rank) {
+        cudaIpcMemHandle_t h;
+        memcpy(&h, handle_64_bytes, sizeof(h));
+        CUDA_TRY(cudaIpcOpenMemHandle(&mapped, h, cudaIpcMemLazyEnablePeerAccess));
+        table = static_cast<const uint2*>(mapped);
+    }
+    unsigned int worldShift = 0;
+    while((1u << worldShift) < r->world) worldShift++;
+    // Rows of this process's neurons: [neuron][process][1 << common shift] entries, zero padded.  The
+    // block of process `peer_rank` is copied out of that process's table, whose rows may be shorter.
+    for(size_t ni = 0; ni < groups; ni++) {
+        const uint32_t shift = (uint32_t)meta[4 + 2 * ni], common = common_shift[ni];
+        if(shift == 0xFFFFFFFFu || common == 0xFFFFFFFFu) continue;
+        if(shift > common || common + worldShift > 12) return fail(B200_ERR_INVALID, "bad common row length for neuron group %zu", ni);
+        const auto &ng = r->neuronGroups[ni];
+        const size_t rowCells = (size_t)1 << (common + worldShift);
+        if(!r->nearImported[ni]) {
+            CUDA_TRY(cudaMalloc(&r->nearImported[ni], sizeof(uint2) * (rowCells * ng.num_update + 1)));
+            CUDA_TRY(cudaMemset(r->nearImported[ni], 0, sizeof(uint2) * (rowCells * ng.num_update + 1)));
+            r->nearSpacesAll[ni] = NearSpace{r->nearImported[ni], common + worldShift, ng.first_neuron, common, 0u};
+        }
+        if(ng.num_update) {
+            CUDA_TRY(cudaMemcpy2D(r->nearImported[ni] + ((size_t)peer_rank << common), sizeof(uint2) * rowCells,
+                                  table + meta[3 + 2 * ni] + ((size_t)ng.first_neuron << shift), sizeof(uint2) << shift,
+                                  sizeof(uint2) << shift, ng.num_update, cudaMemcpyDeviceToDevice));
+        }
+    }
+    CUDA_TRY(cudaDeviceSynchronize());
+    if(mapped) CUDA_TRY(cudaIpcCloseMemHandle(mapped));
+    r->nearPeerDone[peer_rank] = true;
+    return B200_OK;
+}
+
+/* After EVERY process has imported from every process (the caller synchronises them): free the full table
+ * and switch the schedule on (`agreed` != 0) or drop everything. */
+int b200_near_finish(b200_runner *r, int agreed)
+{
+    if(!r) return fail(B200_ERR_INVALID, "null runner");
+    CUDA_TRY(cudaSetDevice(r->device));
+    if(!agreed || r->nearPeerDone.size() != r->world) {
+        r->dropNear();
+        r->lagStale = true;
+        return B200_OK;
+    }
+    for(uint32_t p = 0; p < r->world; p++) {
+        if(!r->nearPeerDone[p]) return fail(B200_ERR_STATE, "the rows held by process %u have not been imported", p);
+        if(p != r->rank && !r->peerArena[p]) return fail(B200_ERR_STATE, "exchange arena of rank %u has not been opened", p);
+    }
+    if(r->nearTable) cudaFree(r->nearTable);
+    r->nearTable = nullptr;
+    // the rings of every process as this process sees them: same offset in the peer's arena
+    std::vector<NearRing> rings((size_t)r->world * r->numRings);
+    for(uint32_t p = 0; p < r->world; p++) {
+        for(uint32_t i = 0; i < r->numRings; i++) {
+            NearRing ring = r->nearRingsHost[i];
+            if(p != r->rank) {
+                ring.den_delay = reinterpret_cast<float*>(r->peerArena[p] + (reinterpret_cast<unsigned char*>(ring.den_delay) - r->arena));
+            }
+            rings[(size_t)p * r->numRings + i] = ring;
+        }
+    }
+    if(r->nearRings) cudaFree(r->nearRings);
+    if(r->nearSpaces) cudaFree(r->nearSpaces);
+    CUDA_TRY(cudaMalloc(&r->nearRings, sizeof(NearRing) * rings.size()));
+    CUDA_TRY(cudaMemcpy(r->nearRings, rings.data(), sizeof(NearRing) * rings.size(), cudaMemcpyHostToDevice));
+    CUDA_TRY(cudaMalloc(&r->nearSpaces, sizeof(NearSpace) * r->nearSpacesAll.size()));
+    CUDA_TRY(cudaMemcpy(r->nearSpaces, r->nearSpacesAll.data(), sizeof(NearSpace) * r->nearSpacesAll.size(), cudaMemcpyHostToDevice));
+    r->emitAgreed = true;
+    r->lagStale = true;
+    return B200_OK;
+}
+
 int b200_exchange_configure(b200_runner *r, uint32_t rank, uint32_t world)
 {
     if(!r || world == 0 || world > B200_MAX_RANKS || rank >= world) return fail(B200_ERR_INVALID, "bad rank/world");
@@ -1340,7 +1497,7 @@ int b200_array_push(b200_runner *r, void *device_ptr, const void *host, size_t b
 {
     CUDA_TRY(cudaMemcpyAsync(device_ptr, host, bytes, cudaMemcpyHostToDevice, r->stream));
     CUDA_TRY(cudaStreamSynchronize(r->stream));
-    if(touchesDelays(r, device_ptr, bytes)) r->lagStale = true;
+    if(touchesDelays(r, device_ptr, bytes)) { r->lagStale = true; r->nearDataStale = true; }
     return B200_OK;
 }
 
@@ -1354,7 +1511,7 @@ int b200_array_pull(b200_runner *r, void *host, const void *device_ptr, size_t b
 int b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes)
 {
     CUDA_TRY(cudaMemsetAsync(device_ptr, value, bytes, r->stream));
-    if(touchesDelays(r, device_ptr, bytes)) r->lagStale = true;
+    if(touchesDelays(r, device_ptr, bytes)) { r->lagStale = true; r->nearDataStale = true; }
     return B200_OK;
 }
 
@@ -1721,7 +1878,8 @@ int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
     else if(n == "cycles_barrier_a") *value = s.phase_cycles[1];
     else if(n == "cycles_neuron") *value = s.phase_cycles[2];
     else if(n == "cycles_barrier_b") *value = s.phase_cycles[3];
-    else if(n.size() == 6 && n.compare(0, 5, "probe") == 0 && n[5] >= '0' && n[5] <= '7') *value = s.probe[n[5] - '0'];
+    else if(n.size() >= 6 && n.size() <= 7 && n.compare(0, 5, "probe") == 0 && atoi(n.c_str() + 5) >= 0 && atoi(n.c_str() + 5) < 12 &&
+            isdigit((unsigned char)n[5])) *value = s.probe[atoi(n.c_str() + 5)];
     else if(n == "timestep") *value = s.timestep;
     else if(n == "steps_done") *value = s.steps_done;
     else return fail(B200_ERR_INVALID, "unknown counter %s", name);

@@ -51,6 +51,8 @@ struct StreamShared
     volatile unsigned int stop;                      // the chain gave up: stream warps leave
     volatile unsigned int streamDone[32];            // per stream warp: steps fully delivered
     volatile unsigned int stepPassed;                // emit mode: grid barriers of the launch that have completed
+    volatile float sink[32];                         // takes the values atomics on another GPU's memory returned
+    unsigned long long waited[2];                    // profile mode: cycles CTA 0 waited for the grid barrier / for the other processes
     volatile unsigned int streamGo[2];               // emit mode: the first stream warp's decision for a pass (pass number: go)
     bool barrierOk;
 };
@@ -339,6 +341,7 @@ streamStepKernel(FusedLaunch L)
         exchange.peers = peerArena;
         sh.headReady = 0u;
         sh.stop = 0u;
+        exchange.tag = L.neuron.state->steps_done + 1;     // emit mode: tag of the first step's spike words
     }
     const ExchangeCtx *xp = (L.world > 1) ? &exchange : nullptr;
     {
@@ -372,9 +375,9 @@ streamStepKernel(FusedLaunch L)
             p += align16(sizeof(FusedUrgent) * L.num_sgroups);
         }
         if(L.emit) {
-            stageWords(p, L.near_rings, sizeof(NearRing) * L.num_rings);
+            stageWords(p, L.near_rings, sizeof(NearRing) * L.num_rings * L.world);
             L.near_rings = reinterpret_cast<const NearRing*>(p);
-            p += align16(sizeof(NearRing) * L.num_rings);
+            p += align16(sizeof(NearRing) * L.num_rings * L.world);
             stageWords(p, L.near_spaces, sizeof(NearSpace) * L.neuron.num_groups);
             L.near_spaces = reinterpret_cast<const NearSpace*>(p);
         }
@@ -510,6 +513,8 @@ streamStepKernel(FusedLaunch L)
     // leave, taking the stream warps along
     #define B200_CHAIN_ABORT() do { sh.stop = 1u; return; } while(0)
 
+    const bool prof = L.profile && threadIdx.x == 0;
+    if(threadIdx.x == 0) { sh.waited[0] = 0; sh.waited[1] = 0; }
     auto arrive = [&]() {
         chainSync(chainThreads);
         if(threadIdx.x == 0) {
@@ -517,26 +522,54 @@ streamStepKernel(FusedLaunch L)
         }
         epoch += gridDim.x;
     };
-    auto wait = [&]() -> bool {
-        if(threadIdx.x == 0) {
-            unsigned long long polls = 0;
+    // `peersAt`: if not zero, also wait until every other process has announced that step (its count
+    // word of the first population, in queue slot `peersSlot`, carries the step): everything it sent before that, the
+    // reductions of its near synapses into THIS process's rings included, has landed.
+    auto wait = [&](unsigned long long peersAt = 0ull, unsigned int peersSlot = 0u) -> bool {
+        if(warp == 0) {
             bool good = true;
-            while(loadAcquire(L.barrier) < epoch) {
-                if(++polls > BARRIER_SPIN_LIMIT) {
-                    atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
-                    good = false;
-                    break;
+            const long long w0 = prof ? clock64() : 0;
+            if(lane == 0) {
+                unsigned long long polls = 0;
+                while(loadAcquire(L.barrier) < epoch) {
+                    if(++polls > BARRIER_SPIN_LIMIT) {
+                        atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
+                        good = false;
+                        break;
+                    }
                 }
             }
+            good = __shfl_sync(0xFFFFFFFFu, good ? 1u : 0u, 0) != 0u;
+            const long long w1 = prof ? clock64() : 0;
+            if(good && peersAt && lane < L.world && lane != L.rank) {
+                // the sections of a population's count words lie one process after the other; this
+                // process's own pointer is in its descriptor
+                const b200_neuron_group &g0 = L.neuron.groups[0];
+                const unsigned long long *word = reinterpret_cast<const unsigned long long*>(g0.spk_tag) +
+                    ((long long)lane - (long long)L.rank) * (long long)g0.num_delay_slots + peersSlot;
+                unsigned long long polls = 0;
+                while((loadRelaxedSys(word) >> 32) != peersAt) {
+                    if(++polls > EXCHANGE_SPIN_LIMIT) {
+                        atomicOr(&state->error, ERR_EXCHANGE_TIMEOUT);
+                        break;
+                    }
+                }
+            }
+            __syncwarp();
+            if(prof) {      // probe 5: this CTA's wait for the grid barrier, probe 6: for the other processes
+                sh.waited[0] += (unsigned long long)(w1 - w0);
+                sh.waited[1] += (unsigned long long)(clock64() - w1);
+            }
             // one thread decides for all: a CTA whose chain threads disagreed would hang on its barrier
-            if(__ldcg(&state->error) & (ERR_BARRIER_TIMEOUT | ERR_EXCHANGE_TIMEOUT)) good = false;
-            sh.barrierOk = good;
+            if(lane == 0) {
+                if(__ldcg(&state->error) & (ERR_BARRIER_TIMEOUT | ERR_EXCHANGE_TIMEOUT)) good = false;
+                sh.barrierOk = good;
+            }
         }
         chainSync(chainThreads);
         return sh.barrierOk;
     };
 
-    const bool prof = L.profile && threadIdx.x == 0;
     long long c0 = 0, c1 = 0, c2 = 0, c3 = 0;
     unsigned long long cyc[6] = {0, 0, 0, 0, 0, 0};
     const bool emit = L.emit != 0;
@@ -623,15 +656,28 @@ streamStepKernel(FusedLaunch L)
             if(emit && step + 1 < L.num_steps) {
                 // the warp delivers the near synapses of its spiking neurons, one row after the other
                 unsigned int ballot = __ballot_sync(0xFFFFFFFFu, spiked);
+                float returned = 0.0f;
                 const NearSpace space = L.near_spaces[myGroup];
+                const bool timeIt = L.profile && ballot;
+                const long long n0 = timeIt ? clock64() : 0;
                 while(ballot) {
                     const unsigned int b = __ffs(ballot) - 1u;
                     ballot &= ballot - 1u;
                     const unsigned int id = __shfl_sync(0xFFFFFFFFu, (unsigned int)myIndex, b);
                     if(space.shift != 0xFFFFFFFFu) {
-                        nearDeliverRow(L.near_table, space.first_cell + ((unsigned long long)id << space.shift), space.shift,
-                                       L.near_rings, k, state);
+                        returned += nearDeliverRow(space.rows + ((unsigned long long)(id - space.first_row) << space.shift), space.shift,
+                                                   space.peer_shift, L.near_rings, L.num_rings, L.rank, k, state);
                     }
+                }
+                // additions into another GPU's rings must have landed there before that GPU is told (after
+                // the barrier below) that this step is complete: consuming what those atomics returned
+                // waits for exactly that
+                const long long n1 = timeIt ? clock64() : 0;
+                if(L.world > 1) sh.sink[lane] = returned;
+                if(timeIt && lane == 0) {       // probes 8-10: near delivery, the fence behind it, spiking warps
+                    atomicAdd(&state->probe[8], (unsigned long long)(n1 - n0));
+                    atomicAdd(&state->probe[9], (unsigned long long)(clock64() - n1));
+                    atomicAdd(&state->probe[10], 1ull);
                 }
             }
         }
@@ -658,6 +704,8 @@ streamStepKernel(FusedLaunch L)
             if(prof) cyc[5] += (unsigned long long)(clock64() - since);
         }
         arrive();
+        // every chain thread is past its neuron update: the tag of the NEXT step's spike words may change
+        if(emit && L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 2;
         if(emit && mine && myActive && step + 1 < L.num_steps) {
             drawCurrentSources<NCS>(L.neuron, L.neuron.groups[myGroup], 0u, (unsigned int)myIndex, t0 + step + 1, csCount);
         }
@@ -684,7 +732,9 @@ streamStepKernel(FusedLaunch L)
                 storeRelaxedSys(cell, tag);
             }
         }
-        if(!wait()) B200_CHAIN_ABORT();
+        // emit mode of a sharded model: the next neuron update reads what the other processes' spiking
+        // threads pushed into this process's rings, so their step must be complete too
+        if(!((emit && L.world > 1) ? wait(done0 + step + 1, ringSlot(k + 1u, L.neuron.groups[0].num_delay_slots)) : wait())) B200_CHAIN_ABORT();
         if(emit && threadIdx.x == 0) sh.stepPassed = (unsigned int)(step + 1);    // the stream may read this step's spikes
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {
@@ -700,6 +750,8 @@ streamStepKernel(FusedLaunch L)
         if(blockIdx.x == 0) {
             for(int i = 0; i < 4; i++) state->phase_cycles[i] += cyc[i];
             state->probe[2] += cyc[5];      // probe 2: chain waiting for the stream warps
+            state->probe[5] += sh.waited[0];
+            state->probe[6] += sh.waited[1];
         }
         if(L.cta_cycles) {
             for(int i = 0; i < 4; i++) L.cta_cycles[4ull * blockIdx.x + i] += cyc[i];

@@ -157,6 +157,13 @@ class Plan:
                                      (f"{p.name}.spk", world * B * p.runtime_slots * p.list_capacity * 4)):
                     layout[name] = (offset, nbytes)
                     offset = (offset + nbytes + 255) & ~255
+            # the dendritic-delay rings too: the process that owns a spiking neuron may reduce its
+            # nearest synapses straight into the rings of the process that owns the targets
+            for i, psm in enumerate(net.psms):
+                if psm.max_den_delay:
+                    nbytes = B * psm.max_den_delay * net.pop(psm.trg).n * 4
+                    layout[f"psm{i}.den_delay"] = (offset, nbytes)
+                    offset = (offset + nbytes + 255) & ~255
             self.exchange = self.factory.alloc_exchange(offset)
             self.factory.memset(self.exchange, 0, offset)
             self._exchange_layout = layout
@@ -200,7 +207,11 @@ class Plan:
         for i, psm in enumerate(net.psms):
             n = net.pop(psm.trg).n
             self._new(f"psm{i}.out_post", np.float32, (B, n))
-            if psm.max_den_delay:
+            if psm.max_den_delay and world > 1:
+                off, nbytes = self._exchange_layout[f"psm{i}.den_delay"]
+                self.arrays[f"psm{i}.den_delay"] = PlannedArray(f"psm{i}.den_delay", _View(self.exchange, off, nbytes),
+                                                                np.dtype(np.float32), (B, psm.max_den_delay, n))
+            elif psm.max_den_delay:
                 self._new(f"psm{i}.den_delay", np.float32, (B, psm.max_den_delay, n))
 
         # synapse-side arrays

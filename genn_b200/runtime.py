@@ -126,6 +126,7 @@ class Runtime:
             mine = bytes([1 if self.counter("lag_eligible") else 0])
             everyone = (exchange or all_gather_bytes)(mine)
             self.set_option("lag_agreed", 1.0 if all(b[0] for b in everyone) else 0.0)
+            self._exchange_near_tables(exchange or all_gather_bytes)
         self._cu_targets = {}
         if model is not None:
             self._bind_model_views()
@@ -148,6 +149,30 @@ class Runtime:
             if peer != rank:
                 check(self.lib.b200_exchange_open_peer(self.handle, peer, C.create_string_buffer(h, 64)))
         check(self.lib.b200_exchange_configure(self.handle, rank, world))
+
+    def _exchange_near_tables(self, gather):
+        """Sharded "deliver at emission" schedule: every process builds the nearest synapses (dendritic
+        delay 0 or 1) of all source neurons onto its own neurons and hands every process the rows of
+        that process's neurons (include/genn_b200.h: b200_near_export / import / finish)."""
+        groups = len(self.plan.neuron_descs)
+        handle = C.create_string_buffer(64)
+        meta = (C.c_uint64 * (3 + 2 * groups))()
+        check(self.lib.b200_near_export(self.handle, handle, meta, len(meta)))
+        everyone = gather(handle.raw + bytes(meta))
+        agreed = all(int.from_bytes(p[64:72], "little") == 1 for p in everyone)
+        if agreed:
+            metas = [(C.c_uint64 * (3 + 2 * groups)).from_buffer_copy(p[64:]) for p in everyone]
+            # one row length per neuron group for all processes: the longest any of them needs
+            common = (C.c_uint32 * groups)()
+            for g in range(groups):
+                shifts = [int(m[4 + 2 * g]) & 0xFFFFFFFF for m in metas]
+                real = [x for x in shifts if x != 0xFFFFFFFF]
+                common[g] = max(real) if len(real) == len(shifts) else 0xFFFFFFFF
+            for peer, payload in enumerate(everyone):
+                check(self.lib.b200_near_import(self.handle, peer, C.create_string_buffer(payload[:64], 64), metas[peer],
+                                                common))
+        gather(b"imported")          # nobody frees its table before everybody has copied from it
+        check(self.lib.b200_near_finish(self.handle, int(agreed)))
 
     # -- initialisation kernels -------------------------------------------------
     def _run_init_tasks(self):

@@ -256,6 +256,20 @@ int  b200_exchange_alloc(b200_runner *r, size_t bytes, void **device_ptr);
 int  b200_exchange_get_handle(b200_runner *r, void *handle_64_bytes);
 int  b200_exchange_open_peer(b200_runner *r, uint32_t peer_rank, const void *handle_64_bytes);
 int  b200_exchange_configure(b200_runner *r, uint32_t rank, uint32_t world);
+/* Sharded models, "deliver at emission" schedule (no reference counterpart: the reference does not shard a
+ * model).  The thread that makes a neuron spike delivers that neuron's synapses of dendritic delay 0 and
+ * 1 itself, into the rings of whichever process holds the target; so every process needs those synapses
+ * of ITS neurons onto every process's neurons.  Each process builds them for all source neurons onto its
+ * own targets (b200_near_export: 64-byte CUDA IPC handle + meta words 3 + 2 * neuron groups, meta[0] = 1
+ * if the model qualifies), the caller all-gathers handle and meta, every process copies the rows of its
+ * own neurons out of every process's table (b200_near_import, once per rank, itself included; common_shift[g] =
+ * the largest meta[4 + 2 g] over all processes, 0xFFFFFFFF if the group is no spike source), the caller
+ * synchronises the processes and every one calls b200_near_finish(agreed = all qualified).  Delay rings
+ * must lie in the exchange arena.  All processes must then step in launches of the same lengths. */
+int  b200_near_export(b200_runner *r, void *handle_64_bytes, uint64_t *meta, uint32_t meta_words);
+int  b200_near_import(b200_runner *r, uint32_t peer_rank, const void *handle_64_bytes, const uint64_t *meta,
+                      const uint32_t *common_shift);
+int  b200_near_finish(b200_runner *r, int agreed);
 
 /* ---- merged-group registration: pushMerged<Kind>Group<i>ToDevice
  *      (backendCUDAHIP.h:206-238, runtime.h:573-669) -------------------------- */

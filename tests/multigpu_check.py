@@ -1,7 +1,7 @@
 """Child process of tests/test_multi_gpu.py: one rank of a model sharded by
 postsynaptic neuron over several GPUs.
 
-    python -m torch.distributed.run --nproc-per-node 2 tests/multigpu_check.py <case> [lag|split|plain]
+    python -m torch.distributed.run --nproc-per-node 2 tests/multigpu_check.py <case> [lag|emit|split|plain]
 
 Every rank builds the same network restricted to the synapses onto its slice,
 steps it with the persistent kernel (spike lists travel between the GPUs inside
@@ -41,7 +41,9 @@ def main():
     rt = Runtime(None, steps, device=local, shard=(rank, world), net=net)
     rt.set_option("use_lag", 1 if lag else 0)
     rt.set_option("use_split", 0 if schedule == "plain" else 1)
-    want_schedule = 0 if schedule == "plain" else 2 if (lag and name == "potjans_mini_d1") else 1
+    rt.set_option("use_emit", 1 if schedule in ("lag", "emit") else 0)
+    want_schedule = (0 if schedule == "plain" else 2 if (lag and name == "potjans_mini_d1")
+                     else 1 if schedule == "split" else 3)
     assert rt.schedule == want_schedule, f"rank {rank}: schedule {rt.schedule}, expected {want_schedule}"
     want = helpers.load_golden(name)
     spikes = {p.name: [] for p in net.pops}
@@ -68,6 +70,7 @@ def main():
                           shard=(rank, world), **kw)))
     rt2.set_option("use_lag", 1 if lag else 0)
     rt2.set_option("use_split", 0 if schedule == "plain" else 1)
+    rt2.set_option("use_emit", 1 if schedule in ("lag", "emit") else 0)
     dist.barrier()
     rt2.step_time(steps)
     rt2.synchronize()

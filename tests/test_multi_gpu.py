@@ -88,7 +88,8 @@ def test_handle_exchange_over_gloo_two_processes():
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("name,schedule", [("potjans_mini_d1", "lag"), ("potjans_mini_d1", "split"),
-                                           ("potjans_mini", "lag"), ("potjans_mini", "plain")])
+                                           ("potjans_mini", "emit"), ("potjans_mini", "split"),
+                                           ("potjans_mini", "plain")])
 def test_two_gpus_match_the_unsharded_reference(name, schedule):
     import torch
     if torch.cuda.device_count() < 2:

@@ -204,6 +204,8 @@ def main():
                     help="lower clip of the delay distribution in ms (0: the reference script's; not the headline if changed)")
     ap.add_argument("--option", action="append", default=[], metavar="NAME=VALUE",
                     help="runner option to set before timing (experiments; see b200_set_option)")
+    ap.add_argument("--sharded-emit", action="store_true",
+                    help="N > 1: spiking threads push their nearest synapses into the other GPUs' rings (experiment)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-saturated", action="store_true")
     args = ap.parse_args()
@@ -238,7 +240,8 @@ def main():
                               shard=(rank, world) if world > 1 else None,
                               min_delay=args.min_delay, extra_delay_slots=1 if args.min_delay > 0 else 0)
     model.build()
-    model.load(num_recording_timesteps=block, device=local_rank, shard=(rank, world) if world > 1 else None)
+    model.load(num_recording_timesteps=block, device=local_rank, shard=(rank, world) if world > 1 else None,
+               sharded_emit=(True if args.sharded_emit else None))
     rt = model._runtime
     net = rt.net
     rt.set_option("count_events", 1)
@@ -281,6 +284,9 @@ def main():
 
     # ---- end to end through the public API: step + recording to pinned host memory ---
     d2h = sum(a.nbytes for n, a in rt.plan.arrays.items() if n.endswith(".record"))
+    # (one untimed round first: the first pull allocates the page-locked host buffers)
+    model.step_time(block)
+    model.pull_recording_buffers_from_device()
     e2e_ev0 = rt.counter("synaptic_events")
     barrier()
     t0 = time.perf_counter()

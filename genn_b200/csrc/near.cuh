@@ -118,6 +118,7 @@ __global__ void nearFillKernel(const b200_synapse_group g, unsigned int ring, un
 // value, and the sum of those values is handed back: once the caller has consumed it, every one
 // of them has been performed at that GPU, which is all the ordering the exchange needs (a
 // system-wide fence after fire-and-forget reductions took 7 k cycles; measured).
+template<bool SHARDED>
 __device__ __forceinline__ float nearDeliverRow(const uint2 *__restrict__ row, unsigned int shift, unsigned int peerShift,
                                                const NearRing *rings, unsigned int numRings, unsigned int rank,
                                                unsigned int front, StepState *state)
@@ -137,12 +138,14 @@ __device__ __forceinline__ float nearDeliverRow(const uint2 *__restrict__ row, u
         for(unsigned int u = 0; u < 8u; u++) {
             if(entry[u].y != 0u) {
                 // whose neurons this block of the row targets: that process's rings, as mapped here
-                const unsigned int owner = (c0 + u * 32u + lane) >> peerShift;
+                // (one process: everything is its own; spelled out because the extra work below sits on
+                // the step's critical path)
+                const unsigned int owner = SHARDED ? ((c0 + u * 32u + lane) >> peerShift) : rank;
                 const NearRing &ring = rings[owner * numRings + ((entry[u].x >> 1) & 0x7Fu)];
                 const unsigned int post = entry[u].x >> 8;
                 if(post < ring.num_neurons) {
                     float *cell = ring.den_delay + (unsigned long long)ringSlot(front + 2u + (entry[u].x & 1u), ring.D) * ring.num_neurons + post;
-                    if(owner == rank) redAdd(cell, __uint_as_float(entry[u].y));
+                    if(!SHARDED || owner == rank) redAdd(cell, __uint_as_float(entry[u].y));
                     else returned += atomicAdd(cell, __uint_as_float(entry[u].y));
                 }
                 else {

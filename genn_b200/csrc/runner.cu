@@ -564,8 +564,11 @@ int buildFusedTables(b200_runner *r)
         r->slotsPerCta = 0;
         int sms = 0;
         CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device));
-        if((r->schedule == b200_runner::SPLIT || r->schedule == b200_runner::EMIT) && r->fusedStage &&
-           r->streamWarpsWanted != 0 && sms > 0) {
+        // (a sharded model on the split schedule measured faster on one set of warps: its chain waits
+        // for the other GPUs anyway, and the stream warps' fences compete with it)
+        const bool wanted = r->streamWarpsWanted > 0 ||
+                            (r->streamWarpsWanted < 0 && !(r->sharded() && r->schedule == b200_runner::SPLIT));
+        if((r->schedule == b200_runner::SPLIT || r->schedule == b200_runner::EMIT) && r->fusedStage && wanted && sms > 0) {
             const unsigned int perCta = ((slotStart.back() + sms - 1) / sms + 31u) & ~31u;
             const unsigned int warps = FUSED_BLOCK / 32;
             const unsigned int chainMin = std::max(8u, perCta / 32u);
@@ -583,7 +586,8 @@ int buildFusedTables(b200_runner *r)
         }
         int e = withNeuronShape(r, [&](auto P, auto C) -> int {
             auto fused = fusedStepKernel<decltype(P)::value, decltype(C)::value>;
-            auto stream = streamStepKernel<decltype(P)::value, decltype(C)::value>;
+            auto stream = r->sharded() ? streamStepKernel<decltype(P)::value, decltype(C)::value, true>
+                                       : streamStepKernel<decltype(P)::value, decltype(C)::value, false>;
             auto kernel = r->streamWarps ? stream : fused;
             r->fusedKernel = (const void*)kernel;
             if(r->fusedStage) {

@@ -324,10 +324,13 @@ __device__ __forceinline__ void streamItems(const FusedLaunch &L, const StreamSh
     }
 }
 
-template<int NPSM, int NCS>
+// SHARDED: the model is spread over several processes (spike exchange, count words, waiting for the other
+// processes).  A separate instance, so that one process pays for none of it on its critical path.
+template<int NPSM, int NCS, bool SHARDED>
 __global__ void __launch_bounds__(FUSED_BLOCK, 1)
 streamStepKernel(FusedLaunch L)
 {
+    if(!SHARDED) L.world = 1u;
     extern __shared__ __align__(16) unsigned char fusedSmem[];
     __shared__ StreamShared sh;
     __shared__ unsigned char *peerArena[B200_MAX_RANKS];
@@ -343,7 +346,7 @@ streamStepKernel(FusedLaunch L)
         sh.stop = 0u;
         exchange.tag = L.neuron.state->steps_done + 1;     // emit mode: tag of the first step's spike words
     }
-    const ExchangeCtx *xp = (L.world > 1) ? &exchange : nullptr;
+    const ExchangeCtx *xp = (SHARDED && L.world > 1) ? &exchange : nullptr;
     {
         // all merged-group tables into shared memory (the host made sure they fit): the acquire
         // side of a grid barrier invalidates L1, so descriptors in global memory would cost an
@@ -541,7 +544,7 @@ streamStepKernel(FusedLaunch L)
             }
             good = __shfl_sync(0xFFFFFFFFu, good ? 1u : 0u, 0) != 0u;
             const long long w1 = prof ? clock64() : 0;
-            if(good && peersAt && lane < L.world && lane != L.rank) {
+            if(SHARDED && good && peersAt && lane < L.world && lane != L.rank) {
                 // the sections of a population's count words lie one process after the other; this
                 // process's own pointer is in its descriptor
                 const b200_neuron_group &g0 = L.neuron.groups[0];
@@ -621,10 +624,11 @@ streamStepKernel(FusedLaunch L)
                     }
                 }
             }
-            __threadfence_block();
+            // (no fence of its own: the release at the barrier below follows in program order and is
+            // cumulative over what this thread has just observed)
             if(prof) cyc[5] += (unsigned long long)(clock64() - since);
         }
-        if(L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 1;    // read after the barrier below
+        if(SHARDED && L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 1;    // read after the barrier below
         arrive();
         // in the shadow of the barrier: this step's random draws
         if(mine && myActive) {
@@ -665,15 +669,20 @@ streamStepKernel(FusedLaunch L)
                     ballot &= ballot - 1u;
                     const unsigned int id = __shfl_sync(0xFFFFFFFFu, (unsigned int)myIndex, b);
                     if(space.shift != 0xFFFFFFFFu) {
-                        returned += nearDeliverRow(space.rows + ((unsigned long long)(id - space.first_row) << space.shift), space.shift,
-                                                   space.peer_shift, L.near_rings, L.num_rings, L.rank, k, state);
+                        const uint2 *row = space.rows + ((unsigned long long)(id - space.first_row) << space.shift);
+                        if(SHARDED && L.world > 1) {
+                            returned += nearDeliverRow<true>(row, space.shift, space.peer_shift, L.near_rings, L.num_rings, L.rank, k, state);
+                        }
+                        else {
+                            nearDeliverRow<false>(row, space.shift, space.peer_shift, L.near_rings, L.num_rings, 0u, k, state);
+                        }
                     }
                 }
                 // additions into another GPU's rings must have landed there before that GPU is told (after
                 // the barrier below) that this step is complete: consuming what those atomics returned
                 // waits for exactly that
                 const long long n1 = timeIt ? clock64() : 0;
-                if(L.world > 1) sh.sink[lane] = returned;
+                if(SHARDED && L.world > 1) sh.sink[lane] = returned;
                 if(timeIt && lane == 0) {       // probes 8-10: near delivery, the fence behind it, spiking warps
                     atomicAdd(&state->probe[8], (unsigned long long)(n1 - n0));
                     atomicAdd(&state->probe[9], (unsigned long long)(clock64() - n1));
@@ -700,26 +709,30 @@ streamStepKernel(FusedLaunch L)
                     }
                 }
             }
-            __threadfence_block();
+            // (no fence of its own: the release at the barrier below follows in program order and is
+            // cumulative over what this thread has just observed)
             if(prof) cyc[5] += (unsigned long long)(clock64() - since);
         }
         arrive();
         // every chain thread is past its neuron update: the tag of the NEXT step's spike words may change
-        if(emit && L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 2;
+        if(SHARDED && emit && L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 2;
         if(emit && mine && myActive && step + 1 < L.num_steps) {
             drawCurrentSources<NCS>(L.neuron, L.neuron.groups[myGroup], 0u, (unsigned int)myIndex, t0 + step + 1, csCount);
         }
         // sharded model: one warp waits for the last CTA and tells every process how many spikes
         // each population emitted ("step s: n spikes", one 64-bit store per process and population);
         // the ids already sit in every arena
-        if(L.world > 1 && blockIdx.x == 0 && warp == chainWarps - 1u) {
-            unsigned long long polls = 0;
-            while(loadAcquire(L.barrier) < epoch) {
-                if(++polls > BARRIER_SPIN_LIMIT) {
-                    atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
-                    break;
+        if(SHARDED && L.world > 1 && blockIdx.x == 0 && warp == chainWarps - 1u) {
+            if(lane == 0) {
+                unsigned long long polls = 0;
+                while(loadAcquire(L.barrier) < epoch) {
+                    if(++polls > BARRIER_SPIN_LIMIT) {
+                        atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
+                        break;
+                    }
                 }
             }
+            __syncwarp();
             for(unsigned int idx = lane; idx < L.world * numGroups; idx += 32u) {
                 const unsigned int peer = idx / numGroups, gi = idx - peer * numGroups;
                 const b200_neuron_group &g = L.neuron.groups[gi];
@@ -734,7 +747,7 @@ streamStepKernel(FusedLaunch L)
         }
         // emit mode of a sharded model: the next neuron update reads what the other processes' spiking
         // threads pushed into this process's rings, so their step must be complete too
-        if(!((emit && L.world > 1) ? wait(done0 + step + 1, ringSlot(k + 1u, L.neuron.groups[0].num_delay_slots)) : wait())) B200_CHAIN_ABORT();
+        if(!((SHARDED && emit && L.world > 1) ? wait(done0 + step + 1, ringSlot(k + 1u, L.neuron.groups[0].num_delay_slots)) : wait())) B200_CHAIN_ABORT();
         if(emit && threadIdx.x == 0) sh.stepPassed = (unsigned int)(step + 1);    // the stream may read this step's spikes
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {

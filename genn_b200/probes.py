@@ -92,6 +92,38 @@ def phases(args):
     rt.close()
 
 
+def e2e(args):
+    """Where the end-to-end step (launch of `block` time steps + recording pull) spends its time."""
+    import time
+    from . import workloads
+    model = workloads.potjans(neuron_scale=args.scale, seed=1234, record=True)
+    model.build()
+    model.load(num_recording_timesteps=args.block)
+    rt = model._runtime
+    rt.set_option("count_events", args.count_events)
+    rt.step_time(3 * args.block)
+    rt.synchronize()
+    kernel_ms, launch_s, sync_s, pull_s = [], [], [], []
+    for _ in range(args.reps):
+        kernel_ms.append(rt.step_time_timed(args.block))
+    for _ in range(args.reps):
+        t0 = time.perf_counter()
+        model.step_time(args.block)
+        t1 = time.perf_counter()
+        rt.synchronize()
+        t2 = time.perf_counter()
+        model.pull_recording_buffers_from_device()
+        t3 = time.perf_counter()
+        launch_s.append(t1 - t0)
+        sync_s.append(t2 - t1)
+        pull_s.append(t3 - t2)
+    one_launch = rt.step_time_timed(args.reps * args.block) / args.reps
+    print(json.dumps({"probe": "e2e", "block": args.block, "kernel_ms_per_block_separate_launches": kernel_ms,
+                      "kernel_ms_per_block_one_launch": one_launch, "launch_call_ms": [x * 1e3 for x in launch_s],
+                      "wait_ms": [x * 1e3 for x in sync_s], "pull_ms": [x * 1e3 for x in pull_s]}))
+    rt.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="cmd", required=True)
@@ -116,6 +148,12 @@ def main():
     p.add_argument("--item-lanes", type=int, default=32)
     p.add_argument("--dump", action="store_true", help="print the per-CTA phase cycles")
     p.set_defaults(fn=phases)
+    p = sub.add_parser("e2e")
+    p.add_argument("--scale", type=float, default=1.0)
+    p.add_argument("--block", type=int, default=1000)
+    p.add_argument("--reps", type=int, default=4)
+    p.add_argument("--count-events", type=int, default=1)
+    p.set_defaults(fn=e2e)
     args = ap.parse_args()
     args.fn(args)
 

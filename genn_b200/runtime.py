@@ -6,6 +6,7 @@ this module without the built library raises.
 from __future__ import annotations
 
 import ctypes as C
+import os
 import math
 from typing import Dict, Optional, Tuple
 
@@ -97,7 +98,8 @@ class Runtime:
     """One loaded model on one GPU."""
 
     def __init__(self, model, num_recording_timesteps: Optional[int] = None, device: int = 0,
-                 shard: Optional[Tuple[int, int]] = None, net: Optional[Net] = None, exchange=None):
+                 shard: Optional[Tuple[int, int]] = None, net: Optional[Net] = None, exchange=None,
+                 sharded_emit: Optional[bool] = None):
         self.lib = abi.load_library()
         self.model = model
         self.device = int(device)
@@ -126,7 +128,12 @@ class Runtime:
             mine = bytes([1 if self.counter("lag_eligible") else 0])
             everyone = (exchange or all_gather_bytes)(mine)
             self.set_option("lag_agreed", 1.0 if all(b[0] for b in everyone) else 0.0)
-            self._exchange_near_tables(exchange or all_gather_bytes)
+            # "deliver at emission" across processes is opt-in (sharded_emit=True or
+            # GENN_B200_SHARDED_EMIT=1, the same on every process): see DESIGN.md, multi-GPU
+            if sharded_emit is None:
+                sharded_emit = os.environ.get("GENN_B200_SHARDED_EMIT", "0") == "1"
+            if sharded_emit:
+                self._exchange_near_tables(exchange or all_gather_bytes)
         self._cu_targets = {}
         if model is not None:
             self._bind_model_views()

@@ -38,10 +38,10 @@ def main():
                               shard=(rank, world), **kw)
     steps, dump_every = 400, 100
     net = resolve(model)
-    rt = Runtime(None, steps, device=local, shard=(rank, world), net=net)
+    rt = Runtime(None, steps, device=local, shard=(rank, world), net=net, sharded_emit=(schedule == "emit"))
     rt.set_option("use_lag", 1 if lag else 0)
     rt.set_option("use_split", 0 if schedule == "plain" else 1)
-    rt.set_option("use_emit", 1 if schedule in ("lag", "emit") else 0)
+    rt.set_option("use_emit", 1 if schedule == "emit" else 0)
     want_schedule = (0 if schedule == "plain" else 2 if (lag and name == "potjans_mini_d1")
                      else 1 if schedule == "split" else 3)
     assert rt.schedule == want_schedule, f"rank {rank}: schedule {rt.schedule}, expected {want_schedule}"
@@ -67,10 +67,10 @@ def main():
     # the same again as ONE launch of many steps with recording
     rt2 = Runtime(None, steps, device=local, shard=(rank, world), net=resolve(
         workloads.potjans(neuron_scale=0.005, seed=7, host_connectivity=True, background="dc", record=True,
-                          shard=(rank, world), **kw)))
+                          shard=(rank, world), **kw)), sharded_emit=(schedule == "emit"))
     rt2.set_option("use_lag", 1 if lag else 0)
     rt2.set_option("use_split", 0 if schedule == "plain" else 1)
-    rt2.set_option("use_emit", 1 if schedule in ("lag", "emit") else 0)
+    rt2.set_option("use_emit", 1 if schedule == "emit" else 0)
     dist.barrier()
     rt2.step_time(steps)
     rt2.synchronize()

@@ -114,10 +114,10 @@ __global__ void nearFillKernel(const b200_synapse_group g, unsigned int ring, un
 // row has one block per process and `rings` one set of rings per process, the other processes'
 // mapped here: reductions into those travel over NVLink.  `front` is the phase of the step in
 // which the neuron spiked: a synapse of delay e lands in the slot the neuron update e + 1 steps
-// later reads.  Additions into another process's ring are made with atomics that RETURN the old
-// value, and the sum of those values is handed back: once the caller has consumed it, every one
-// of them has been performed at that GPU, which is all the ordering the exchange needs (a
-// system-wide fence after fire-and-forget reductions took 7 k cycles; measured).
+// later reads.  Returns non-zero if a ring of another process was written: the caller then owes a
+// system-wide fence before that process is told the step is complete.  (Measured on two GPUs: that
+// fence costs a spiking warp 7.2 k cycles behind about 50 reductions; making the additions with
+// atomics that return the old value and consuming the returns instead cost 9.6 k, they do not overlap.)
 template<bool SHARDED>
 __device__ __forceinline__ float nearDeliverRow(const uint2 *__restrict__ row, unsigned int shift, unsigned int peerShift,
                                                const NearRing *rings, unsigned int numRings, unsigned int rank,
@@ -141,12 +141,13 @@ __device__ __forceinline__ float nearDeliverRow(const uint2 *__restrict__ row, u
                 // (one process: everything is its own; spelled out because the extra work below sits on
                 // the step's critical path)
                 const unsigned int owner = SHARDED ? ((c0 + u * 32u + lane) >> peerShift) : rank;
-                const NearRing &ring = rings[owner * numRings + ((entry[u].x >> 1) & 0x7Fu)];
-                const unsigned int post = entry[u].x >> 8;
+                const unsigned int word = entry[u].x;
+                const NearRing &ring = rings[owner * numRings + ((word >> 1) & 0x7Fu)];
+                const unsigned int post = word >> 8;
                 if(post < ring.num_neurons) {
-                    float *cell = ring.den_delay + (unsigned long long)ringSlot(front + 2u + (entry[u].x & 1u), ring.D) * ring.num_neurons + post;
-                    if(!SHARDED || owner == rank) redAdd(cell, __uint_as_float(entry[u].y));
-                    else returned += atomicAdd(cell, __uint_as_float(entry[u].y));
+                    float *cell = ring.den_delay + (unsigned long long)ringSlot(front + 2u + (word & 1u), ring.D) * ring.num_neurons + post;
+                    redAdd(cell, __uint_as_float(entry[u].y));
+                    if(SHARDED && owner != rank) returned = 1.0f;
                 }
                 else {
                     atomicOr(&state->error, ERR_IND_RANGE);

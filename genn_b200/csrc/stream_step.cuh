@@ -51,7 +51,6 @@ struct StreamShared
     volatile unsigned int stop;                      // the chain gave up: stream warps leave
     volatile unsigned int streamDone[32];            // per stream warp: steps fully delivered
     volatile unsigned int stepPassed;                // emit mode: grid barriers of the launch that have completed
-    volatile float sink[32];                         // takes the values atomics on another GPU's memory returned
     unsigned long long waited[2];                    // profile mode: cycles CTA 0 waited for the grid barrier / for the other processes
     volatile unsigned int streamGo[2];               // emit mode: the first stream warp's decision for a pass (pass number: go)
     bool barrierOk;
@@ -679,10 +678,9 @@ streamStepKernel(FusedLaunch L)
                     }
                 }
                 // additions into another GPU's rings must have landed there before that GPU is told (after
-                // the barrier below) that this step is complete: consuming what those atomics returned
-                // waits for exactly that
+                // the barrier below) that this step is complete
                 const long long n1 = timeIt ? clock64() : 0;
-                if(SHARDED && L.world > 1) sh.sink[lane] = returned;
+                if(SHARDED && __any_sync(0xFFFFFFFFu, returned != 0.0f)) __threadfence_system();
                 if(timeIt && lane == 0) {       // probes 8-10: near delivery, the fence behind it, spiking warps
                     atomicAdd(&state->probe[8], (unsigned long long)(n1 - n0));
                     atomicAdd(&state->probe[9], (unsigned long long)(clock64() - n1));

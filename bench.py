@@ -76,7 +76,12 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append([time.perf_counter()] + [x.strip() for x in line.split(",")])
+
+    def mark(self):
+        """The timed region starts here; samples taken before it (the warm-up steps: the same kernel
+        under the same load) are only used if the region is too short to catch one."""
+        self.t_mark = time.perf_counter()
 
     def stop(self):
         if self.proc is None:
@@ -89,7 +94,11 @@ class ClockSampler:
             self.proc.kill()
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        inside = [r[1:] for r in self.rows if r[0] >= getattr(self, "t_mark", 0.0)]
+        window = "timed region"
+        if not any(len(r) >= 9 for r in inside):
+            inside, window = [r[1:] for r in self.rows], "warm-up and timed region (the timed region was shorter than a sample)"
+        for r in inside:
             if len(r) < 9:
                 continue
             try:
@@ -101,7 +110,7 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(name)
         return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+                "reasons": sorted(reasons), "samples": len(sm), "window": window}
 
 
 def bytes_per_event(net) -> float:
@@ -264,13 +273,14 @@ def main():
         return float(t.item())
 
     # ---- device-resident throughput: W warm-up, K timed steps -------------------------
+    sampler = ClockSampler(local_rank)
+    sampler.start()
     for _ in range(args.warmup):
         rt.step_time(block)
     rt.synchronize()
     ev0, sp0, l0 = rt.counter("synaptic_events"), rt.counter("spikes"), rt.kernel_launches
-    sampler = ClockSampler(local_rank)
-    sampler.start()
     barrier()
+    sampler.mark()
     ms = rt.step_time_timed(args.steps * block)        # CUDA events on the runner's own stream
     barrier()
     clocks = sampler.stop()

@@ -55,28 +55,72 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """nvidia-smi sampling of SM clocks and throttle reasons during a timed region."""
+    """SM clock and throttle reasons of one GPU, sampled in a thread while the bench runs.
 
+    NVML is read in-process every 5 ms (a bench step of this workload lasts a few milliseconds and
+    nvidia-smi needs longer than the whole timed region to start); nvidia-smi is the fallback.
+    Reading only: nothing is set."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap"}
     QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index: int):
         self.gpu = gpu_index
-        self.rows = []
+        self.rows = []          # (time, sm MHz, max MHz, [reason names])
         self.proc = None
+        self.thread = None
+        self.running = False
+        self.t_mark = 0.0
+        self.source = None
+
+    def _nvml_loop(self, handle, nvml):
+        max_mhz = float(nvml.nvmlDeviceGetMaxClockInfo(handle, nvml.NVML_CLOCK_SM))
+        while self.running:
+            try:
+                mhz = float(nvml.nvmlDeviceGetClockInfo(handle, nvml.NVML_CLOCK_SM))
+                get = getattr(nvml, "nvmlDeviceGetCurrentClocksEventReasons", None) or nvml.nvmlDeviceGetCurrentClocksThrottleReasons
+                mask = int(get(handle))
+                self.rows.append((time.perf_counter(), mhz, max_mhz, [n for b, n in self.REASONS.items() if mask & b]))
+            except Exception:
+                pass
+            time.sleep(0.005)
+
+    def _smi_loop(self):
+        for line in self.proc.stdout:
+            r = [x.strip() for x in line.split(",")]
+            if len(r) < 9:
+                continue
+            try:
+                names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+                self.rows.append((time.perf_counter(), float(r[1]), float(r[2]),
+                                  [n for n, v in zip(names, r[5:9]) if v.lower().startswith("active")]))
+            except ValueError:
+                continue
 
     def start(self):
+        self.running = True
+        try:
+            import pynvml as nvml
+            nvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = int(visible.split(",")[self.gpu]) if visible and visible.split(",")[self.gpu].isdigit() else self.gpu
+            handle = nvml.nvmlDeviceGetHandleByIndex(index)
+            self.thread = threading.Thread(target=self._nvml_loop, args=(handle, nvml), daemon=True)
+            self.thread.start()
+            self.source = "nvml"
+            return
+        except Exception:
+            pass
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
                                           "-i", str(self.gpu), "-lms", "100"], stdout=subprocess.PIPE, text=True)
-            threading.Thread(target=self._read, daemon=True).start()
+            self.thread = threading.Thread(target=self._smi_loop, daemon=True)
+            self.thread.start()
+            self.source = "nvidia-smi"
         except Exception:
             self.proc = None
-
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([time.perf_counter()] + [x.strip() for x in line.split(",")])
 
     def mark(self):
         """The timed region starts here; samples taken before it (the warm-up steps: the same kernel
@@ -84,33 +128,25 @@ class ClockSampler:
         self.t_mark = time.perf_counter()
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        time.sleep(0.15)
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        inside = [r[1:] for r in self.rows if r[0] >= getattr(self, "t_mark", 0.0)]
-        window = "timed region"
-        if not any(len(r) >= 9 for r in inside):
-            inside, window = [r[1:] for r in self.rows], "warm-up and timed region (the timed region was shorter than a sample)"
-        for r in inside:
-            if len(r) < 9:
-                continue
+        t_end = time.perf_counter()
+        self.running = False
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
             try:
-                sm.append(float(r[1]))
-                mx.append(float(r[2]))
-            except ValueError:
-                continue
-            for name, v in zip(names, r[5:9]):
-                if v.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm), "window": window}
+                self.proc.wait(timeout=5)
+            except Exception:
+                self.proc.kill()
+        if self.source is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no clock source (NVML and nvidia-smi unavailable)"]}
+        inside = [r for r in self.rows if self.t_mark <= r[0] <= t_end + (0.2 if self.proc is not None else 0.0)]
+        window = "timed region"
+        if not inside:
+            inside, window = list(self.rows), "warm-up and timed region (the timed region was shorter than a sample)"
+        reasons = sorted({n for r in inside for n in r[3]})
+        return {"sm_mhz": float(np.median([r[1] for r in inside])) if inside else None,
+                "sm_max_mhz": max(r[2] for r in inside) if inside else None,
+                "reasons": reasons, "samples": len(inside), "window": window, "source": self.source}
 
 
 def bytes_per_event(net) -> float:
@@ -215,6 +251,8 @@ def main():
                     help="runner option to set before timing (experiments; see b200_set_option)")
     ap.add_argument("--sharded-emit", action="store_true",
                     help="N > 1: spiking threads push their nearest synapses into the other GPUs' rings (experiment)")
+    ap.add_argument("--cpu-sample-blocks", type=int, default=100,
+                    help="length of the CPU baseline sample in bench steps (1000 time steps each) at --ref-scale")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-saturated", action="store_true")
     args = ap.parse_args()
@@ -422,7 +460,8 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
-            r = run_reference_sample(args.ref_scale, block, 1, 0)
+            # a bounded sample of the same architecture: about ten seconds of CPU time
+            r = run_reference_sample(args.ref_scale, block, args.cpu_sample_blocks, 0)
             cpu = {"value": r["events_per_s"], "unit": "synaptic events/s", "cores": 1, "kind": r["kind"],
                    "realtime_factor": r["rtf"],
                    "sample": f"Potjans neuron_scale={args.ref_scale} (published in-degrees, {r['synapses']} synapses), "

@@ -406,18 +406,21 @@ streamStepKernel(FusedLaunch L)
         // header and delivers every synapse with a delay of two steps or more, as the presynaptic
         // phase of step c would.  The chain waits for pass c before it arrives at the barrier that
         // ends step c+1: a pass has two steps of time.  One item costs several thousand cycles
-        // (a random row: TLB and DRAM misses), more than a step, so the stream warps form two
-        // sets that take the odd and the even passes: a pass starts the moment its spikes are there.
+        // (a few hundred dependent instructions around a random row), more than a step, so the stream
+        // warps form two sets that take the odd and the even passes: a pass starts the moment its
+        // spikes are there.  The sets are the CTAs with odd and with even index: equal halves of the
+        // grid, and every stream warp of a CTA serves the same pass.
         const unsigned int me = warp - chainWarps;
-        const unsigned int set = me & 1u;
-        const unsigned int setWarps = (streamWarps + 1u - set) / 2u;       // warps me = set, set + 2, ...
-        const unsigned int setThreads = setWarps * 32u;
-        const unsigned int first = (me >> 1) * gridDim.x + blockIdx.x, stride = setWarps * gridDim.x;
+        const bool alone = gridDim.x < 2u;                                 // a single CTA serves every pass
+        const unsigned int set = blockIdx.x & 1u;
+        const unsigned int setCtas = alone ? 1u : (gridDim.x + 1u - set) / 2u;     // CTAs set, set + 2, ...
+        const unsigned int setThreads = streamWarps * 32u;
+        const unsigned int first = me * setCtas + (blockIdx.x >> 1), stride = streamWarps * setCtas;
         unsigned long long spent[4] = {0, 0, 0, 0};     // profile mode: waiting, header, items, fence
         // passes c with c % 2 == set; phase of step c
-        unsigned long long c = set ? 1ull : 2ull;
+        unsigned long long c = (set || alone) ? 1ull : 2ull;
         for(unsigned int a = 0; a < (unsigned int)c; a++) k = (k + 1 == period) ? 0u : k + 1;
-        for(; c < L.num_steps; c += 2) {
+        for(; c < L.num_steps; c += alone ? 1 : 2) {
             const long long since = clock64();
             bool alive = true;
             while(sh.stepPassed < (unsigned int)c) {
@@ -426,14 +429,14 @@ streamStepKernel(FusedLaunch L)
             }
             // go on or leave TOGETHER (a warp that left alone would hang the others of its set on their
             // barrier): the set's first warp decides, the others read its decision behind the barrier
-            const unsigned int buf = set;
+            const unsigned int buf = (unsigned int)(c & 1u);
             const long long t1 = clock64();
-            if((me >> 1) == 0 && lane == 0) sh.streamGo[buf] = (alive && !sh.stop) ? (unsigned int)c : 0u;
+            if(me == 0 && lane == 0) sh.streamGo[buf] = (alive && !sh.stop) ? (unsigned int)c : 0u;
             __threadfence_block();
-            for(unsigned int si = (me >> 1) * 32u + lane; si < ((L.num_sources + 31u) & ~31u); si += setThreads) {
+            for(unsigned int si = me * 32u + lane; si < ((L.num_sources + 31u) & ~31u); si += setThreads) {
                 fetchHeader(L, sh, buf, si, k, done0 + c, state);
             }
-            asm volatile("bar.sync %0, %1;" :: "r"(2u + set), "r"(setThreads) : "memory");
+            streamSync(setThreads);
             if(sh.streamGo[buf] != (unsigned int)c) return;
             const long long t2 = clock64();
             streamItems(L, sh, buf, first, stride, k, done0 + c, state, 3);
@@ -442,13 +445,13 @@ streamStepKernel(FusedLaunch L)
             __syncwarp();
             if(lane == 0) sh.streamDone[me] = (unsigned int)c;
             k = (k + 1 == period) ? 0u : k + 1;
-            k = (k + 1 == period) ? 0u : k + 1;
+            if(!alone) k = (k + 1 == period) ? 0u : k + 1;
             spent[0] += (unsigned long long)(t1 - since);
             spent[1] += (unsigned long long)(t2 - t1);
             spent[2] += (unsigned long long)(t3 - t2);
             spent[3] += (unsigned long long)(clock64() - t3);
         }
-        if(L.profile && blockIdx.x == 0 && me == 1 && lane == 0) {
+        if(L.profile && blockIdx.x == 1 && me == 0 && lane == 0) {
             state->probe[0] += spent[0];
             state->probe[1] += spent[1];
             state->probe[3] += spent[2];
@@ -695,11 +698,11 @@ streamStepKernel(FusedLaunch L)
         }
         if(prof) c3 = clock64();
         if(emit && threadIdx.x == 0 && step >= 2) {
-            // the stream warps that took pass step-1 (the spikes of the step before last) must be through
-            // it: the barrier below is the last one ahead of the first neuron update that may read
-            // what they delivered
+            // the stream warps that took pass step-1 (the spikes of the step before last; this CTA's
+            // if the parities match) must be through it: the barrier below is the last one ahead of
+            // the first neuron update that may read what they delivered
             const long long since = clock64();
-            for(unsigned int w = (unsigned int)((step - 1) & 1u); w < streamWarps; w += 2u) {
+            for(unsigned int w = 0; w < streamWarps && (gridDim.x < 2u || ((step - 1) & 1u) == (blockIdx.x & 1u)); w++) {
                 while(sh.streamDone[w] < (unsigned int)(step - 1)) {
                     if(clock64() - since > STREAM_WAIT_CYCLES) {
                         atomicOr(&state->error, ERR_BARRIER_TIMEOUT);

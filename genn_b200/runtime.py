@@ -129,7 +129,8 @@ class Runtime:
             everyone = (exchange or all_gather_bytes)(mine)
             self.set_option("lag_agreed", 1.0 if all(b[0] for b in everyone) else 0.0)
             # "deliver at emission" across processes is opt-in (sharded_emit=True or
-            # GENN_B200_SHARDED_EMIT=1, the same on every process): see DESIGN.md, multi-GPU
+            # GENN_B200_SHARDED_EMIT=1, the same on every process): measured slower than the split
+            # schedule on 2 and 8 GPUs, because the pushed additions need a system-wide fence
             if sharded_emit is None:
                 sharded_emit = os.environ.get("GENN_B200_SHARDED_EMIT", "0") == "1"
             if sharded_emit:

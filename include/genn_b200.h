@@ -243,7 +243,7 @@ int  b200_array_pull(b200_runner *r, void *host, const void *device_ptr, size_t 
 int  b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes);
 
 /* ---- spike exchange between processes (no counterpart in the reference, which has no model
- *      sharding: SURVEY of backendCUDAHIP.cc shows NCCL all-reduce of custom-update results only).
+ *      sharding: backendCUDAHIP.cc uses NCCL for the all-reduce of custom-update results only).
  * A model sharded by postsynaptic neuron over several GPUs of one node exchanges each step's spike
  * lists.  Every process allocates ONE exchange arena, places its spike arrays (all sections) and the
  * tagged counts in it at identical offsets, shares the arena's IPC handle with its peers and opens

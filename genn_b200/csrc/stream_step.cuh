@@ -425,7 +425,7 @@ streamStepKernel(FusedLaunch L)
             bool alive = true;
             while(sh.stepPassed < (unsigned int)c) {
                 if(sh.stop || clock64() - since > STREAM_WAIT_CYCLES) { alive = false; break; }
-                __nanosleep(40);
+                __nanosleep(200);
             }
             // go on or leave TOGETHER (a warp that left alone would hang the others of its set on their
             // barrier): the set's first warp decides, the others read its decision behind the barrier
@@ -471,7 +471,7 @@ streamStepKernel(FusedLaunch L)
                     if(lane == 0) atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
                     return;
                 }
-                __nanosleep(40);
+                __nanosleep(200);
             }
             __threadfence_block();
             __syncwarp();

@@ -59,6 +59,14 @@ def test_sharded_plan_lays_out_one_section_per_process():
         assert (db.spk - b.exchange.ptr) - (da.spk - a.exchange.ptr) == p.runtime_slots * p.list_capacity * 4
     for d in a.synapse_descs:
         assert d.src_sections == world and d.src_spk_slot_stride >= 32
+    # the delay rings too: a process that owns a spiking neuron may add into its peers' rings, whose
+    # address it derives from its own ring's offset in the arena
+    rings = [n for n in a.arrays if n.endswith(".den_delay")]
+    assert rings
+    for name in rings:
+        ra, rb = a.arrays[name], b.arrays[name]
+        assert ra.handle.offset == rb.handle.offset and ra.shape == rb.shape
+        assert a.exchange.ptr <= ra.ptr < a.exchange.ptr + a.exchange.buf.nbytes
 
 
 def _gloo_worker(rank, world, port, out):

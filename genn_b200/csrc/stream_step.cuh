@@ -658,6 +658,21 @@ streamStepKernel(FusedLaunch L)
                     if(p < g.num_psm && !g.psm[p].max_den_delay) g.psm[p].out_post[myIndex] = regs.lin[p];
                 }
             }
+            if(emit && step + 1 < L.num_steps) {
+                // the near rows of this warp's spiking neurons are needed in a moment: start them on
+                // their way into L2 while the spike lists are being written (an atomic round trip)
+                unsigned int ahead = __ballot_sync(0xFFFFFFFFu, spiked);
+                const NearSpace space = L.near_spaces[myGroup];
+                while(ahead && space.shift != 0xFFFFFFFFu) {
+                    const unsigned int b = __ffs(ahead) - 1u;
+                    ahead &= ahead - 1u;
+                    const unsigned int id = __shfl_sync(0xFFFFFFFFu, (unsigned int)myIndex, b);
+                    if((lane << 4) < (1u << space.shift)) {         // one 128-byte line (16 entries) per lane
+                        const uint2 *line = space.rows + ((unsigned long long)(id - space.first_row) << space.shift) + (lane << 4);
+                        asm volatile("prefetch.global.L2 [%0];" :: "l"(line));
+                    }
+                }
+            }
             neuronEmit<true>(L.neuron, g, 0u, myLocal, spiked, k, t0 + step, t, xp);
             if(emit && step + 1 < L.num_steps) {
                 // the warp delivers the near synapses of its spiking neurons, one row after the other

@@ -2,22 +2,25 @@
 Potjans-Diesmann microcircuit architecture on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python bench.py --probe presyn|phases|e2e [...]      # bounded single-kernel workloads for ncu
 
 A bench STEP is a block of ``--block`` (default 1000) simulation time steps of
-dt = 0.1 ms, i.e. 0.1 s of biological time replayed as captured CUDA graphs.
-At N GPUs the network has N times the neurons with the published in-degrees
-(weak scaling) and each rank owns a contiguous slice of every population's
-postsynaptic neurons together with their incoming synapses.
+dt = 0.1 ms, i.e. 0.1 s of biological time, run by ONE launch of the persistent
+time-step kernel.  At N GPUs the network has N times the neurons with the
+published in-degrees (weak scaling) and each rank owns a contiguous slice of
+every population's postsynaptic neurons together with their incoming synapses.
 
 One JSON line is printed by rank 0.  ``value`` is whole-job synaptic events per
 second with all state resident in HBM; ``e2e`` is the same metric through the
 public ``GeNNModel`` API with the spike recording copied to page-locked host
-memory every step; ``roofline`` is the presynaptic-update kernel measured live
-with CUDA events at the network's natural firing rates and
-``roofline_saturated`` the same kernel driven with a quarter of all neurons
-spiking in one step (inputs far larger than L2); ``cpu_baseline`` times the
-reference's own single-threaded CPU backend (or, where it cannot run, the C
-port of its algorithm) on this box's host cores.
+memory every step; ``roofline`` is the persistent kernel of the timed region
+(algorithmic bytes of the launch over its CUDA-event time) and
+``roofline_saturated`` the SPARSE delivery kernel driven with a quarter of all
+neurons spiking in one step (inputs far larger than L2); ``parity`` compares
+the population firing rates and CV-ISI of a 10 s run with those the reference's
+CPU backend produced for the same architecture; ``cpu_baseline`` times the
+reference's own single-threaded CPU backend (or, where its build is absent and
+labelled as such, the C port of its algorithm) on this box's host cores.
 """
 from __future__ import annotations
 
@@ -39,9 +42,36 @@ if REPO not in sys.path:
 
 DT_MS = 0.1
 ALGO_BYTES_PER_SPIKE = 8           # spike id + row length
-# dram__bytes_read.sum + dram__bytes_write.sum of one 300-step launch of streamStepKernel on the
-# Potjans x1 workload, per time step (profiles/stream_step_potjans.md)
-NCU_DRAM_BYTES_PER_TIME_STEP = (344135424 + 4409856) / 300.0
+
+
+def kernel_sources_digest() -> str:
+    """SHA-256 over the kernel sources and the ABI headers: identifies the build a profiler
+    figure was taken on."""
+    import hashlib
+    h = hashlib.sha256()
+    for d in (os.path.join(REPO, "genn_b200", "csrc"), os.path.join(REPO, "include")):
+        for name in sorted(os.listdir(d)):
+            if name.endswith((".cu", ".cuh", ".h")):
+                h.update(name.encode())
+                h.update(open(os.path.join(d, name), "rb").read())
+    return h.hexdigest()
+
+
+def captured_traffic(kernel: str):
+    """DRAM bytes per time step of `kernel` from the tracked record of an ncu capture
+    (dram__bytes_read.sum + dram__bytes_write.sum of one short launch), or (None, why) when the
+    record was taken on other kernel sources than the ones in the tree."""
+    path = os.path.join(REPO, "profiles", "dram_traffic.txt")
+    if not os.path.exists(path):
+        return None, "no ncu capture recorded"
+    digest = kernel_sources_digest()
+    for line in open(path):
+        f = line.split()
+        if len(f) >= 5 and not line.startswith("#") and f[0] == kernel:
+            if f[1] != digest:
+                return None, "the recorded ncu capture was taken on other kernel sources"
+            return (float(f[2]) + float(f[3])) / float(f[4]), f"ncu capture of a {f[4]}-step launch, scaled by the number of time steps"
+    return None, "no ncu capture recorded for this kernel"
 
 
 def measured_peaks():
@@ -204,9 +234,52 @@ def run_reference_sample(scale: float, block: int, steps: int, warmup: int, seed
         runner.close()
     sim_seconds = total_steps * DT_MS * 1e-3
     return {"kind": kind, "events": events, "spikes": spikes, "seconds": seconds,
-            "events_per_s": events / seconds, "rtf": seconds / sim_seconds,
+            "events_per_s": events / seconds, "rtf": sim_seconds / seconds,
             "neurons": sum(p.n for p in net.pops), "synapses": int(sum(int(s.row_length.sum()) for s in net.syns)),
             "total_steps": total_steps}
+
+
+def parity_leg(model, rt, net, block, seconds, world, all_reduce):
+    """Simulate `seconds` more of biological time with spike recording, decode every block and
+    compare per-population firing rate and CV-ISI with the statistics the reference's CPU backend
+    produced for this architecture at x1 over 10 s (tests/golden/stats_potjans_x1.json: the xN
+    network has the same in-degrees and hence the same population statistics).  Every rank
+    decodes the slice of each population it updates; the sums are combined across ranks."""
+    from genn_b200 import stats
+    path = os.path.join(REPO, "tests", "golden", "stats_potjans_x1.json")
+    if not os.path.exists(path):
+        return {"ok": None, "note": "no reference statistics on disk"}
+    want = json.load(open(path))["populations"]
+    blocks = max(1, int(round(seconds / (block * DT_MS * 1e-3))))
+    spikes = {p.name: ([], []) for p in net.pops}
+    for _ in range(blocks):
+        model.step_time(block)
+        model.pull_recording_buffers_from_device()
+        for p in net.pops:
+            times, ids = rt.recorded_spikes(p.name)[0]
+            spikes[p.name][0].append(np.rint(times / net.dt).astype(np.int64))
+            spikes[p.name][1].append(ids)
+    names = [p.name for p in net.pops]
+    sums = np.zeros((len(names), 4))
+    for j, p in enumerate(net.pops):
+        lo, hi = (p.shard_bounds[rt.shard[0]], p.shard_bounds[rt.shard[0] + 1]) if rt.shard else (0, p.n)
+        sums[j] = stats.partial(np.concatenate(spikes[p.name][0]), np.concatenate(spikes[p.name][1]), hi - lo, first_id=lo)
+    if all_reduce is not None:
+        import torch
+        t = torch.tensor(sums, dtype=torch.float64, device="cuda")
+        all_reduce(t)
+        sums = t.cpu().numpy()
+    duration = blocks * block * DT_MS * 1e-3
+    got = {n: stats.merge([sums[j]], duration) for j, n in enumerate(names)}
+    rate_err, cv_err = stats.compare(got, want)
+    return {"rates_max_rel_err": rate_err, "cv_isi_max_rel_err": cv_err, "tolerance": 0.02,
+            "ok": bool(rate_err <= 0.02 and cv_err <= 0.02), "simulated_seconds": duration,
+            "rates_hz": {n: round(got[n]["rate_hz"], 4) for n in names},
+            "reference_rates_hz": {n: round(want[n]["rate_hz"], 4) for n in names},
+            "cv_isi": {n: round(got[n]["cv_isi"], 4) for n in names},
+            "reference_cv_isi": {n: round(want[n]["cv_isi"], 4) for n in names},
+            "note": "reference: GeNN single_threaded_cpu backend, x1 network with host-drawn connectivity, 10 s simulated "
+                    "(chaotic network: statistics, not spike trains, are comparable)"}
 
 
 def reference_arm(args):
@@ -224,9 +297,12 @@ def reference_arm(args):
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "realtime_factor": r["rtf"],
-        "config": {"workload": f"Potjans-Diesmann microcircuit architecture, neuron_scale={args.ref_scale} "
-                               f"(published in-degrees), {r['neurons']} neurons, {r['synapses']} synapses, "
-                               f"dt=0.1 ms, {args.block} time steps per bench step",
+        "config": {"workload": f"Potjans-Diesmann microcircuit architecture x{args.ref_scale:g}: {r['neurons']} LIF neurons, "
+                               f"published in-degrees ({r['synapses']} synapses, drawn on the host), SPARSE with dendritic "
+                               f"delays, PoissonExp background, dt=0.1 ms; one bench step = {args.block} time steps "
+                               f"(0.1 s biological)",
+                   "parallelism": "the reference's CPU backend is single-threaded; at N > 1 it runs the x1 network "
+                                  "(a bounded sample of the xN workload: same in-degrees, same per-neuron work)",
                    "timing": "wall clock around the reference's stepTime loop (all warm-up and timed steps)"},
         "cpu_baseline": {"value": r["events_per_s"], "unit": "synaptic events/s", "cores": 1, "kind": r["kind"],
                          "sample": f"neuron_scale={args.ref_scale}, {r['total_steps']} time steps"},
@@ -236,6 +312,100 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_probe(args):
+    """Bounded single-kernel workloads, sized for a profiler capture that ends by itself.
+
+    presyn: Potjans architecture at --probe-scale (default 0.5) times the neurons (in-degrees and
+            therefore row lengths unchanged), --probe-fraction of every population marked as having
+            spiked, --probe-reps launches of the presynaptic update.  The device holds about
+            2.6 GB x scale; one launch reads about scale x fraction x 2.1 GB (twice L2 at the defaults).
+    phases: --probe-warm + --probe-steps time steps of the persistent kernel at natural rates with its
+            clock64 phase counters on.
+    e2e:    where one GeNNModel.step_time + recording pull spends its time."""
+    from genn_b200 import workloads
+    from genn_b200.runtime import Runtime
+    if args.probe == "presyn":
+        scale = args.probe_scale if args.probe_scale is not None else 0.5
+        model = workloads.potjans(neuron_scale=scale, seed=1234)
+        model.build()
+        rt = Runtime(model, None)
+        net = rt.net
+        for item in args.option:
+            k, v = item.split("=")
+            rt.set_option(k, float(v))
+        rng = np.random.default_rng(99)
+        out_deg = {}
+        for s in net.syns:
+            out_deg[s.src] = out_deg.get(s.src, 0) + rt.array(f"{s.name}.row_length").astype(np.int64)
+        events = spikes = 0
+        for p in net.pops:
+            ids = np.sort(rng.choice(p.n, size=max(1, int(p.n * args.probe_fraction)), replace=False)).astype(np.uint32)
+            rt.set_spike_list(p.name, ids)
+            events += int(out_deg[p.name][ids].sum()) if p.name in out_deg else 0
+            spikes += len(ids)
+        for _ in range(2):
+            rt.update_synapses()
+        rt.enable_timing(True)
+        rt.reset_timers()
+        for _ in range(args.probe_reps):
+            rt.update_synapses()
+        rt.synchronize()
+        sec = rt.timer("presynaptic_update") / args.probe_reps
+        bpe = bytes_per_event(net)
+        print(json.dumps({"probe": "presyn", "scale": scale, "fraction": args.probe_fraction,
+                          "events_per_launch": events, "spikes_per_launch": spikes, "launch_ms": sec * 1e3,
+                          "events_per_s": events / sec, "bytes_per_event": bpe,
+                          "GBps": (events * bpe + spikes * ALGO_BYTES_PER_SPIKE) / sec / 1e9}))
+        rt.close()
+    elif args.probe == "phases":
+        scale = args.probe_scale if args.probe_scale is not None else 1.0
+        model = workloads.potjans(neuron_scale=scale, seed=1234, min_delay=args.min_delay,
+                                  extra_delay_slots=1 if args.min_delay > 0 else 0)
+        model.build()
+        rt = Runtime(model, None)
+        for item in args.option:
+            k, v = item.split("=")
+            rt.set_option(k, float(v))
+        rt.step_time(args.probe_warm)
+        rt.synchronize()
+        rt.set_option("fused_profile", 1)
+        names = ["cycles_presynaptic", "cycles_barrier_a", "cycles_neuron", "cycles_barrier_b"]
+        before = [rt.counter(n) for n in names]
+        ms = rt.step_time_timed(args.probe_steps)
+        after = [rt.counter(n) for n in names]
+        out = {"probe": "phases", "scale": scale, "steps": args.probe_steps, "us_per_step": ms * 1e3 / args.probe_steps,
+               "step_path": rt.step_path(), "schedule": rt.schedule, "stream_warps": rt.counter("stream_warps")}
+        for n, a, b in zip(names, before, after):
+            out[n + "_per_step"] = (b - a) / args.probe_steps
+        print(json.dumps(out))
+        rt.close()
+    else:
+        scale = args.probe_scale if args.probe_scale is not None else 1.0
+        model = workloads.potjans(neuron_scale=scale, seed=1234, record=True)
+        model.build()
+        model.load(num_recording_timesteps=args.block)
+        rt = model._runtime
+        rt.step_time(3 * args.block)
+        rt.synchronize()
+        kernel_ms = [rt.step_time_timed(args.block) for _ in range(args.probe_reps)]
+        launch_s, sync_s, pull_s = [], [], []
+        for _ in range(args.probe_reps):
+            t0 = time.perf_counter()
+            model.step_time(args.block)
+            t1 = time.perf_counter()
+            rt.synchronize()
+            t2 = time.perf_counter()
+            model.pull_recording_buffers_from_device()
+            t3 = time.perf_counter()
+            launch_s.append(t1 - t0)
+            sync_s.append(t2 - t1)
+            pull_s.append(t3 - t2)
+        print(json.dumps({"probe": "e2e", "block": args.block, "kernel_ms_per_block": kernel_ms,
+                          "launch_call_ms": [x * 1e3 for x in launch_s], "wait_ms": [x * 1e3 for x in sync_s],
+                          "pull_ms": [x * 1e3 for x in pull_s]}))
+        model.unload()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -243,7 +413,20 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--block", type=int, default=1000, help="simulation time steps per bench step")
-    ap.add_argument("--ref-scale", type=float, default=0.05, help="neuron scale of the CPU sample")
+    ap.add_argument("--ref-scale", type=float, default=1.0,
+                    help="--impl reference: neuron scale of the network the reference runs (1 = the bench's own x1 workload; "
+                         "smaller values for quick runs)")
+    ap.add_argument("--cpu-sample-scale", type=float, default=0.05,
+                    help="neuron scale of the bounded cpu_baseline sample inside the GPU arm's run")
+    ap.add_argument("--parity-seconds", type=float, default=10.0,
+                    help="simulated seconds of the rate / CV-ISI comparison with the reference's statistics (0: skip)")
+    ap.add_argument("--probe", choices=["presyn", "phases", "e2e"], default=None,
+                    help="run a bounded single-kernel workload (for profiling) instead of the benchmark")
+    ap.add_argument("--probe-scale", type=float, default=None)
+    ap.add_argument("--probe-fraction", type=float, default=0.25)
+    ap.add_argument("--probe-steps", type=int, default=2000)
+    ap.add_argument("--probe-warm", type=int, default=2000)
+    ap.add_argument("--probe-reps", type=int, default=3)
     ap.add_argument("--neuron-scale", type=float, default=None, help="override the workload size (debugging)")
     ap.add_argument("--min-delay", type=float, default=0.0,
                     help="lower clip of the delay distribution in ms (0: the reference script's; not the headline if changed)")
@@ -260,6 +443,9 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         reference_arm(args)
+        return
+    if args.probe:
+        run_probe(args)
         return
 
     rank = int(os.environ.get("RANK", "0"))
@@ -351,6 +537,12 @@ def main():
         n_local = rt.plan.neuron_descs[[q.name for q in net.pops].index(p.name)].num_update
         rates[p.name] = round(len(ids) / max(1, n_local) / (block * DT_MS * 1e-3), 3)
 
+    # ---- parity: population statistics over --parity-seconds against the reference's ----------
+    parity = None
+    if args.parity_seconds > 0 and args.min_delay == 0.0:
+        parity = parity_leg(model, rt, net, block, args.parity_seconds, world,
+                            (lambda t: dist.all_reduce(t)) if world > 1 else None)
+
     # ---- where a step's time goes inside the persistent kernel (clock64 per phase, CTA 0) ---
     probe_steps = min(args.steps * block, 2000)
     rt.set_option("fused_profile", 1)
@@ -395,8 +587,10 @@ def main():
         launch_bytes = float(ev1 - ev0) * bpe + float(sp1 - sp0) * ALGO_BYTES_PER_SPIKE
         launch_gbs = launch_bytes / seconds / 1e9
         timed_steps = args.steps * block
-        traffic = (NCU_DRAM_BYTES_PER_TIME_STEP * timed_steps
-                   if (scale == 1.0 and args.min_delay == 0.0 and rt.schedule == 3) else None)
+        per_step, traffic_note = (captured_traffic("streamStepKernel")
+                                  if (scale == 1.0 and args.min_delay == 0.0 and rt.schedule == 3)
+                                  else (None, "no capture for this configuration"))
+        traffic = per_step * timed_steps if per_step is not None else None
         roofline = {"kernel": ["fusedStepKernel", "fusedStepKernel", "fusedStepKernel", "streamStepKernel"][rt.schedule]
                               + f" (persistent: {timed_steps} time steps in one launch)",
                     "bound": "hbm", "achieved": launch_gbs, "peak": hbm_peak, "unit": "GB/s", "frac": launch_gbs / hbm_peak,
@@ -406,9 +600,7 @@ def main():
                     "per_kernel_path": per_kernel,
                     "note": "natural firing rates: about 0.7 MB of synapse rows per time step, so a step is bound by "
                             "latency (grid barrier, dependent loads), not by HBM; roofline_saturated shows the same "
-                            "delivery code with enough spikes to be bandwidth-relevant.  traffic: dram bytes of a "
-                            "300-step launch under ncu, scaled to this launch by the number of time steps "
-                            "(profiles/stream_step_potjans.md)"}
+                            "delivery code with enough spikes to be bandwidth-relevant.  traffic: " + traffic_note}
     else:
         # a sharded model runs on the persistent kernel only: its presynaptic phase is timed with clock64
         pre_s = phase_cycles["cycles_presynaptic"] * probe_steps / sm_hz
@@ -461,10 +653,10 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         try:
             # a bounded sample of the same architecture: about ten seconds of CPU time
-            r = run_reference_sample(args.ref_scale, block, args.cpu_sample_blocks, 0)
+            r = run_reference_sample(args.cpu_sample_scale, block, args.cpu_sample_blocks, 0)
             cpu = {"value": r["events_per_s"], "unit": "synaptic events/s", "cores": 1, "kind": r["kind"],
                    "realtime_factor": r["rtf"],
-                   "sample": f"Potjans neuron_scale={args.ref_scale} (published in-degrees, {r['synapses']} synapses), "
+                   "sample": f"Potjans neuron_scale={args.cpu_sample_scale} (published in-degrees, {r['synapses']} synapses), "
                              f"{r['total_steps']} time steps, {r['seconds']:.2f} s of CPU time"}
         except Exception as e:      # the baseline is reported, never required
             cpu = {"value": None, "unit": "synaptic events/s", "cores": 1, "kind": "port", "sample": f"failed: {e}"}
@@ -476,7 +668,7 @@ def main():
             "value": value, "unit": "synaptic events/s", "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": "f32", "data": "synthetic",
-            "realtime_factor": seconds / sim_seconds,
+            "realtime_factor": sim_seconds / seconds,
             "us_per_timestep": ms * 1e3 / (args.steps * block),
             "config": {"workload": f"Potjans-Diesmann microcircuit architecture x{scale:g}: {n_neurons} LIF neurons, "
                                    f"published in-degrees, SPARSE with dendritic delays, PoissonExp background, "
@@ -496,13 +688,14 @@ def main():
                        "mean_rates_hz": rates, "bytes_per_event": bpe},
             "clocks": clocks,
             "e2e": {"value": e2e_events / e2e_seconds, "unit": "synaptic events/s", "h2d_bytes_per_step": 0,
-                    "d2h_bytes_per_step": d2h, "realtime_factor": e2e_seconds / sim_seconds,
+                    "d2h_bytes_per_step": d2h, "realtime_factor": sim_seconds / e2e_seconds,
                     "note": "GeNNModel.step_time + pull_recording_buffers_from_device into page-locked memory; "
                             "the model takes no per-step host input (background drive is drawn on the device, as in "
                             "the reference script)"},
             "gpu_launches": int(l1 - l0),
             "roofline": roofline,
             "roofline_saturated": roofline_sat,
+            "parity": parity,
             "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)

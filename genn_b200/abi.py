@@ -15,6 +15,7 @@ INIT_CONSTANT, INIT_UNIFORM, INIT_NORMAL, INIT_NORMAL_CLIPPED, INIT_NORMAL_CLIPP
 (CONNECT_FIXED_PROBABILITY, CONNECT_FIXED_PROBABILITY_NO_AUTAPSE, CONNECT_FIXED_NUMBER_TOTAL,
  CONNECT_FIXED_NUMBER_PRE, CONNECT_FIXED_NUMBER_POST) = range(5)
 REDUCE_SUM, REDUCE_MAX = range(2)
+OK, ERR_CUDA, ERR_INVALID, ERR_STATE, ERR_DEVICE_CHECK = range(5)
 
 NEURON_KINDS = {"LIF": NEURON_LIF, "Izhikevich": NEURON_IZHIKEVICH,
                 "SpikeSourceArray": NEURON_SPIKE_SOURCE_ARRAY, "Poisson": NEURON_POISSON}
@@ -106,6 +107,7 @@ _PROTOTYPES = {
     "b200_exchange_configure": [C.c_void_p, C.c_uint32, C.c_uint32],
     "b200_push_neuron_update_group": [C.c_void_p, C.c_uint32, C.POINTER(NeuronGroupDesc)],
     "b200_push_synapse_group": [C.c_void_p, C.c_uint32, C.POINTER(SynapseGroupDesc)],
+    "b200_validate_synapse_group": [C.POINTER(SynapseGroupDesc)],
     "b200_push_custom_update": [C.c_void_p, C.c_char_p, C.c_uint32, C.POINTER(CustomUpdateDesc)],
     "b200_initialize": [C.c_void_p],
     "b200_initialize_sparse": [C.c_void_p],
@@ -142,6 +144,7 @@ _PROTOTYPES = {
     "b200_get_step_path": [C.c_void_p, C.POINTER(C.c_int), C.c_char_p, C.c_size_t],
     "b200_update_neurons_noalloc": [C.c_int, C.c_void_p, C.POINTER(NeuronGroupDesc), C.c_uint32, C.c_uint32,
                                     C.c_double, C.c_uint64, C.c_uint64, C.c_uint64, C.c_uint64],
+    "b200_noalloc_check": [C.c_int, C.c_void_p],
 }
 
 _lib = None

@@ -13,13 +13,20 @@
 // same neuron update with its scratch in `g_scratch` below.
 //
 // What it costs.  Every GPU that loads the library carries the array
-// (B200_NOALLOC_SCRATCH_BYTES, about 36 KB) until the process exits, and the
+// (B200_NOALLOC_SCRATCH_BYTES, 40 KB) until the process exits, and the
 // number of neuron groups per call is capped (B200_NOALLOC_MAX_GROUPS).
 //
 // Rules of use.
 //  * The first call on a device looks up the array's device address
 //    (cudaGetSymbolAddress, which may load the module).  Make that first call
 //    before starting any stream capture.
+//  * A call on a stream that is being captured is refused (B200_ERR_STATE):
+//    every call copies its tables and counters from host memory that is gone
+//    by the time a captured graph would replay.
+//  * A kernel-side bounds check that fails (a spike list too short for the
+//    spikes of the step) sets a word in the array.  b200_noalloc_check waits
+//    for the stream and reports it; the next update clears it.
+//  * The caller's current device is left as it was found.
 //  * All calls on one device share the one array, and the array keeps what the
 //    last call left in it.  Everything that must start from a known value (the
 //    block ticket, the error word, the step counters) is rewritten by every
@@ -88,6 +95,20 @@ int scratchAddress(int device, unsigned char **out)
     return B200_OK;
 }
 
+// Makes `device` current for the length of a call and puts the caller's device back.
+struct DeviceGuard
+{
+    int previous = -1;
+    cudaError_t enter(int device)
+    {
+        cudaError_t e = cudaGetDevice(&previous);
+        if(e != cudaSuccess) { previous = -1; return e; }
+        if(previous == device) { previous = -1; return cudaSuccess; }
+        return cudaSetDevice(device);
+    }
+    ~DeviceGuard() { if(previous >= 0) cudaSetDevice(previous); }
+};
+
 unsigned long long foldPeriod(unsigned long long period, unsigned int n)
 {
     if(n < 2) return period;
@@ -120,8 +141,15 @@ int b200_update_neurons_noalloc(int device, void *stream, const b200_neuron_grou
                     num_groups, (unsigned int)B200_NOALLOC_MAX_GROUPS);
     }
     if(device < 0 || device >= MAX_DEVICES) return fail(B200_ERR_INVALID, "device index %d out of range", device);
-    cudaError_t e = cudaSetDevice(device);
+    DeviceGuard guard;
+    cudaError_t e = guard.enter(device);
     if(e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaSetDevice(%d) failed: %s", device, cudaGetErrorString(e));
+    cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+    e = cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &capture);
+    if(e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaStreamIsCapturing failed: %s", cudaGetErrorString(e));
+    if(capture != cudaStreamCaptureStatusNone) {
+        return fail(B200_ERR_STATE, "the stream is being captured: this call copies from host memory and cannot be part of a graph");
+    }
 
     // host-side image of the scratch contents for this call (stack only)
     unsigned int blockStart[B200_NOALLOC_MAX_GROUPS + 1];
@@ -190,6 +218,29 @@ int b200_update_neurons_noalloc(int device, void *stream, const b200_neuron_grou
     else launch<B200_MAX_PSM, B200_MAX_CS>(L, grid, st);
     e = cudaPeekAtLastError();
     if(e != cudaSuccess) return fail(B200_ERR_CUDA, "kernel launch failed: %s", cudaGetErrorString(e));
+    return B200_OK;
+}
+
+int b200_noalloc_check(int device, void *stream)
+{
+    if(device < 0 || device >= MAX_DEVICES) return fail(B200_ERR_INVALID, "device index %d out of range", device);
+    DeviceGuard guard;
+    cudaError_t e = guard.enter(device);
+    if(e != cudaSuccess) return fail(B200_ERR_CUDA, "cudaSetDevice(%d) failed: %s", device, cudaGetErrorString(e));
+    unsigned char *base = nullptr;
+    const int s = scratchAddress(device, &base);
+    if(s) return s;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    unsigned int word = 0;      // on the stack: nothing is allocated
+    e = cudaMemcpyAsync(&word, &reinterpret_cast<Scratch*>(base)->state.error, sizeof(word), cudaMemcpyDeviceToHost, st);
+    if(e == cudaSuccess) e = cudaStreamSynchronize(st);
+    if(e != cudaSuccess) return fail(B200_ERR_CUDA, "reading the check word failed: %s", cudaGetErrorString(e));
+    if(word) {
+        return fail(B200_ERR_DEVICE_CHECK, "device-side check failed (0x%x):%s%s%s", word,
+                    (word & ERR_SPIKE_OVERFLOW) ? " more spikes in a step than the spike list holds" : "",
+                    (word & ERR_IND_RANGE) ? " index out of range" : "",
+                    (word & ERR_DELAY_RANGE) ? " delay out of range" : "");
+    }
     return B200_OK;
 }
 

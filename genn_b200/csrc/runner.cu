@@ -1533,9 +1533,9 @@ int b200_push_neuron_update_group(b200_runner *r, uint32_t idx, const b200_neuro
     return B200_OK;
 }
 
-int b200_push_synapse_group(b200_runner *r, uint32_t idx, const b200_synapse_group *g)
+int b200_validate_synapse_group(const b200_synapse_group *g)
 {
-    if(!r || !g) return fail(B200_ERR_INVALID, "null argument");
+    if(!g) return fail(B200_ERR_INVALID, "null argument");
     if(g->connectivity == B200_CONN_SPARSE) {
         if(!g->row_length || !g->ind) return fail(B200_ERR_INVALID, "SPARSE group without row_length/ind");
         if(g->ind_bytes != 1 && g->ind_bytes != 2 && g->ind_bytes != 4) return fail(B200_ERR_INVALID, "bad ind_bytes");
@@ -1560,7 +1560,24 @@ int b200_push_synapse_group(b200_runner *r, uint32_t idx, const b200_synapse_gro
     if(g->wu_model == B200_WU_STATIC_PULSE_DENDRITIC_DELAY && (!g->d || !g->den_delay || !g->max_den_delay)) {
         return fail(B200_ERR_INVALID, "dendritic delay group without d/den_delay");
     }
-    if(g->wu_model != B200_WU_STATIC_PULSE_DENDRITIC_DELAY && !g->out_post) return fail(B200_ERR_INVALID, "out_post missing");
+    // the kernels switch on max_den_delay: a ring depth means "read d, add into den_delay"
+    if(g->max_den_delay && (!g->den_delay || (!g->d && g->connectivity != B200_CONN_PROCEDURAL))) {
+        return fail(B200_ERR_INVALID, "max_den_delay set but d or den_delay missing");
+    }
+    if(g->max_den_delay && g->wu_model != B200_WU_STATIC_PULSE_DENDRITIC_DELAY && g->connectivity != B200_CONN_PROCEDURAL) {
+        return fail(B200_ERR_INVALID, "max_den_delay set on a weight update model that does not call addToPostDelay");
+    }
+    if((g->max_den_delay || g->wu_model == B200_WU_STATIC_PULSE_DENDRITIC_DELAY) &&
+       (g->connectivity == B200_CONN_BITMASK || g->connectivity == B200_CONN_DENSE)) {
+        return fail(B200_ERR_INVALID, "dendritic delay is supported on SPARSE connectivity only");
+    }
+    if(!g->max_den_delay && !g->out_post) return fail(B200_ERR_INVALID, "out_post missing");
+    if(g->connectivity == B200_CONN_SPARSE) {
+        // rows are read as aligned groups of four synapses counted from the array base
+        if(g->g && ((uintptr_t)g->g & 15u)) return fail(B200_ERR_INVALID, "g must be 16-byte aligned");
+        if((uintptr_t)g->ind & (4u * g->ind_bytes - 1u)) return fail(B200_ERR_INVALID, "ind must be aligned to four indices");
+        if(g->d && ((uintptr_t)g->d & 3u)) return fail(B200_ERR_INVALID, "d must be 4-byte aligned");
+    }
     if(g->wu_model == B200_WU_STDP) {
         if(!g->src_spike_times || !g->trg_spike_times || !g->trg_spk || !g->trg_spk_cnt) {
             return fail(B200_ERR_INVALID, "learning group without spike times");
@@ -1568,8 +1585,18 @@ int b200_push_synapse_group(b200_runner *r, uint32_t idx, const b200_synapse_gro
         if(g->connectivity == B200_CONN_SPARSE && (!g->col_length || !g->remap)) {
             return fail(B200_ERR_INVALID, "learning SPARSE group without remap");
         }
+        if(g->back_prop_delay + 2 > g->trg_delay_slots) {
+            return fail(B200_ERR_INVALID, "back-propagation delay exceeds the target spike queue");
+        }
     }
     if(g->axonal_delay + 2 > g->src_delay_slots) return fail(B200_ERR_INVALID, "axonal delay exceeds the source spike queue");
+    return B200_OK;
+}
+
+int b200_push_synapse_group(b200_runner *r, uint32_t idx, const b200_synapse_group *g)
+{
+    if(!r || !g) return fail(B200_ERR_INVALID, "null argument");
+    if(const int e = b200_validate_synapse_group(g)) return e;
     if(idx >= r->synapseGroups.size()) r->synapseGroups.resize(idx + 1);
     r->synapseGroups[idx] = *g;
     r->dirty = true;

@@ -234,3 +234,53 @@ def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
             sg.trg_range = trg_range
         sg.max_dendritic_delay_timesteps = slots + extra_delay_slots
     return m
+
+
+# ---------------------------------------------------------------------------
+# Recurrent conductance-based E/I network (config 2)
+# ---------------------------------------------------------------------------
+def cond_ei(neuron_scale: float = 1.0, seed: int = 4321, dt: float = 0.1, in_degree: int = 1000,
+            i_offset: float = 0.35, record: bool = True,
+            shard: Optional[Tuple[int, int]] = None) -> GeNNModel:
+    """80 000 excitatory + 20 000 inhibitory LIF neurons (times ``neuron_scale``)
+    with a fixed in-degree: every neuron draws ``in_degree`` presynaptic partners
+    uniformly (with replacement) from the whole network.  Constant weights
+    0.6 nS (excitatory) and 6.7 nS (inhibitory), exponential conductances with
+    tau 5 / 10 ms and reversal 0 / -80 mV, 1 ms axonal delay, initial potentials
+    U[-60, -50) mV.  Conductances are in uS (potentials in mV, currents in nA, as
+    in neuronModels.h:225-256).  ``i_offset`` is the constant current that keeps
+    the network firing (the published description names no drive; without one
+    every potential decays to rest).  Connectivity is drawn on the host so that
+    a CPU checker can be handed identical arrays."""
+    rng = np.random.default_rng(seed)
+    m = GeNNModel("float", "cond_ei")
+    m.dt = dt
+    m.seed = seed
+    ne, ni = int(round(80000 * neuron_scale)), int(round(20000 * neuron_scale))
+    lif = {"C": 0.2, "TauM": 20.0, "Vrest": -60.0, "Vreset": -60.0, "Vthresh": -50.0, "Ioffset": i_offset,
+           "TauRefrac": 5.0}
+    pops = {}
+    for name, n in (("E", ne), ("I", ni)):
+        v0 = rng.uniform(-60.0, -50.0, size=n).astype(np.float32)
+        pops[name] = m.add_neuron_population(name, n, "LIF", lif, {"V": v0, "RefracTime": 0.0})
+        pops[name].spike_recording_enabled = record
+    delay_steps = int(round(1.0 / dt))
+    for trg_name, nt in (("E", ne), ("I", ni)):
+        lo, hi = 0, nt
+        if shard is not None:
+            from .plan import shard_bounds
+            bounds = shard_bounds(nt, shard[1])
+            lo, hi = bounds[shard[0]], bounds[shard[0] + 1]
+        # one stream of draws per target population, the same on every rank
+        pre_all = rng.integers(0, ne + ni, size=(nt, in_degree), dtype=np.int64)[lo:hi]
+        post_all = np.repeat(np.arange(lo, hi, dtype=np.uint32), in_degree)
+        pre_all = pre_all.reshape(-1)
+        for src_name, w, tau, erev in (("E", 0.6e-3, 5.0, 0.0), ("I", 6.7e-3, 10.0, -80.0)):
+            sel = (pre_all < ne) if src_name == "E" else (pre_all >= ne)
+            pre = (pre_all[sel] - (0 if src_name == "E" else ne)).astype(np.uint32)
+            sg = m.add_synapse_population(f"{src_name}{trg_name}", "SPARSE", pops[src_name], pops[trg_name],
+                                          init_weight_update("StaticPulseConstantWeight", {"g": w}),
+                                          init_postsynaptic("ExpCond", {"tau": tau, "E": erev}))
+            sg.set_sparse_connections(pre, post_all[sel])
+            sg.axonal_delay_steps = delay_steps
+    return m

@@ -275,6 +275,11 @@ int  b200_near_finish(b200_runner *r, int agreed);
  *      (backendCUDAHIP.h:206-238, runtime.h:573-669) -------------------------- */
 int  b200_push_neuron_update_group(b200_runner *r, uint32_t idx, const b200_neuron_group *g);
 int  b200_push_synapse_group(b200_runner *r, uint32_t idx, const b200_synapse_group *g);
+/* The checks b200_push_synapse_group applies, on their own (no runner, no GPU): missing arrays for the
+ * connectivity / weight update model, a ring depth without d / den_delay, dendritic delay on BITMASK or
+ * DENSE, pointers the vector loads cannot take (g 16-byte, ind four indices, d 4-byte aligned), delays
+ * longer than the spike queues.  A descriptor that fails is never handed to a kernel. */
+int  b200_validate_synapse_group(const b200_synapse_group *g);
 int  b200_push_custom_update(b200_runner *r, const char *name, uint32_t idx, const b200_custom_update_group *u);
 
 /* ---- initialisation kernels (backendSIMT.cc:1368-1779) --------------------- */
@@ -361,14 +366,23 @@ int  b200_get_cta_cycles(b200_runner *r, uint64_t *out, uint32_t max_ctas, uint3
  * `stream` is a cudaStream_t (NULL for the default stream); `timestep` and
  * `steps_done` are the values the regular path would hold on the device.
  * The first call on a device resolves the array's address and should be made
- * before any stream capture begins.  Calls on one device share the array: calls
- * whose GPU work may overlap must be ordered by the caller.  No host or device
- * memory is allocated or freed.  Errors: b200_noalloc_last_error(). */
+ * before any stream capture begins.  A call on a stream that is being captured
+ * is refused with B200_ERR_STATE: every call copies its tables and counters from
+ * host memory that no longer exists when a graph would replay.  Calls on one
+ * device share the array: calls whose GPU work may overlap must be ordered by
+ * the caller.  No host or device memory is allocated or freed, and the caller's
+ * current device is restored before returning.  Errors: b200_noalloc_last_error().
+ *
+ * b200_noalloc_check waits for `stream` and returns B200_ERR_DEVICE_CHECK if the
+ * last update on that device failed a kernel-side bounds check (more spikes in
+ * a step than the spike list holds: the surplus spikes were dropped); it
+ * allocates nothing either.  The next update clears the condition. */
 #define B200_NOALLOC_MAX_GROUPS     64
 #define B200_NOALLOC_SCRATCH_BYTES  40960
 int  b200_update_neurons_noalloc(int device, void *stream, const b200_neuron_group *groups, uint32_t num_groups,
                                  uint32_t batch_size, double dt, uint64_t seed, uint64_t timestep,
                                  uint64_t steps_done, uint64_t num_recording_timesteps);
+int  b200_noalloc_check(int device, void *stream);
 const char *b200_noalloc_last_error(void);
 
 #ifdef __cplusplus

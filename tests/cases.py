@@ -14,6 +14,13 @@ def ff_sparse():
     return workloads.feedforward(seed=3, num_pre=200, num_post=500, prob=0.1, rate_hz=200.0, steps=300), 300, 50
 
 
+def c1_full():
+    """Benchmark config 1 at its stated size: 1 000 spike sources at 20 Hz (host-generated trains)
+    -> 10 000 LIF through SPARSE p = 0.1 (about 1 M synapses), weights U[0, 0.05) nA, exponential
+    current synapses with tau 5 ms, 1 000 steps of 0.1 ms."""
+    return workloads.feedforward(seed=1, num_pre=1000, num_post=10000, prob=0.1, rate_hz=20.0, steps=1000), 1000, 250
+
+
 def ff_sparse_narrow():
     m = workloads.feedforward(seed=4, num_pre=150, num_post=200, prob=0.2, rate_hz=200.0, steps=300, narrow=True)
     return m, 300, 50
@@ -121,6 +128,28 @@ def poisson_drive():
     return m, 300, 100
 
 
-CASES = {"ff_sparse": ff_sparse, "ff_sparse_narrow": ff_sparse_narrow, "ff_bitmask": ff_bitmask,
+CASES = {"ff_sparse": ff_sparse, "c1_full": c1_full, "ff_sparse_narrow": ff_sparse_narrow, "ff_bitmask": ff_bitmask,
          "ff_dense": ff_dense, "potjans_mini": potjans_mini, "potjans_mini_d1": potjans_mini_d1, "cond_delay": cond_delay, "stdp": stdp,
          "izhikevich": izhikevich}
+
+
+# ---------------------------------------------------------------------------
+# Config-scale networks compared on population statistics (rates and CV-ISI over
+# 10 s of simulated time): recurrent networks are chaotic, so two correct
+# simulators agree on those, not spike by spike.  Each builder returns
+# (GeNNModel, steps); connectivity, weights, delays and initial potentials are
+# drawn on the host from the seed so that the reference's CPU backend and the
+# CUDA kernels are loaded with identical arrays.
+# ---------------------------------------------------------------------------
+def stats_potjans_x1(shard=None):
+    m = workloads.potjans(neuron_scale=1.0, seed=2024, host_connectivity=True, background="poisson", record=True,
+                          shard=shard)
+    return m, 100000
+
+
+def stats_cond_ei(shard=None):
+    m = workloads.cond_ei(neuron_scale=1.0, seed=4321, shard=shard)
+    return m, 100000
+
+
+STATS_CASES = {"potjans_x1": stats_potjans_x1, "cond_ei": stats_cond_ei}

@@ -1,7 +1,7 @@
 """Regenerate tests/golden/*.npz by running the UNMODIFIED reference
 (GeNN 5.4.0 single_threaded_cpu backend) on the networks of tests/cases.py.
 
-    make -f oracle/Makefile.ref -j8         # builds oracle/_ref/ from /root/reference
+    make -f oracle/Makefile.ref -j8 [REF=<reference tree>]   # builds oracle/_ref/
     python tests/golden/make_golden.py
 
 Each fixture holds the per-step spike (step, id) pairs of every population and

@@ -54,17 +54,64 @@ def snapshot(runner, net, step):
     return out
 
 
-def input_scale(net, name):
-    """Sum of |weight| that can reach one postsynaptic buffer: the scale the
-    1e-5 tolerance on summed input is relative to (contributions of opposite
-    sign cancel, so the error is relative to what was added, not to what is left)."""
-    return 1.0
+class ContributionScale:
+    """Per postsynaptic buffer and target neuron, the running sum of |weight| of everything that was
+    added into the buffer, decayed as the buffer itself decays: the magnitude the 1e-5 tolerance on
+    a summed input is relative to.  Contributions of opposite sign cancel, so the rounding error of
+    an unordered fp32 sum scales with what was added, not with what is left of it.
+
+    Call :meth:`step` once per simulated step with the spikes emitted in the step BEFORE it (the ones
+    that step's synapse update propagates), in the order of the simulator: synapses into buffer or
+    ring slot, then the neuron update consumes the front slot and decays the buffer."""
+
+    def __init__(self, net):
+        self.net = net
+        self.k = 0
+        self.history = []           # spikes by population, newest last
+        self.acc = [np.zeros(net.pop(p.trg).n) for p in net.psms]
+        self.ring = [np.zeros((p.max_den_delay, net.pop(p.trg).n)) if p.max_den_delay else None for p in net.psms]
+        self.decay = [float(p.derived.get("expDecay", 0.0)) for p in net.psms]
+
+    def step(self, spikes_by_pop):
+        net = self.net
+        self.history.append({k: np.asarray(v, dtype=np.int64) for k, v in spikes_by_pop.items()})
+        for s in net.syns:
+            if s.matrix != "SPARSE" or s.ind is None or len(self.history) <= s.ax_delay:
+                continue
+            psm = net.psms[s.psm]
+            for pre in self.history[-1 - s.ax_delay].get(s.src, ()):
+                lo = int(pre) * s.row_stride
+                n = int(s.row_length[pre])
+                post = np.asarray(s.ind[lo:lo + n], dtype=np.int64)
+                w = (np.abs(np.asarray(s.g[lo:lo + n], dtype=np.float64)) if s.g is not None
+                     else np.full(n, abs(float(s.wum_params["g"]))))
+                if s.max_den_delay:
+                    D = psm.max_den_delay
+                    slot = (self.k + 1 + np.asarray(s.d[lo:lo + n], dtype=np.int64)) % D
+                    np.add.at(self.ring[s.psm], (slot, post), w)
+                else:
+                    np.add.at(self.acc[s.psm], post, w)
+        self.k += 1
+        for i, psm in enumerate(net.psms):
+            if self.ring[i] is not None:
+                front = self.k % psm.max_den_delay
+                self.acc[i] += self.ring[i][front]
+                self.ring[i][front] = 0.0
+            self.acc[i] *= self.decay[i]
+
+    def scale(self, psm_index):
+        return self.acc[psm_index]
 
 
-def assert_close(got, want, key, rtol, atol):
+def assert_close(got, want, key, rtol, atol, scale=None):
+    """|got - want| <= atol + rtol * max(|want|, scale): `scale` (per element) widens the relative
+    bound to the magnitude of what was summed into the element."""
     assert got.shape == want.shape, f"{key}: shape {got.shape} vs {want.shape}"
     err = np.abs(got.astype(np.float64) - want.astype(np.float64))
-    bound = atol + rtol * np.abs(want.astype(np.float64))
+    ref = np.abs(want.astype(np.float64))
+    if scale is not None:
+        ref = np.maximum(ref, np.broadcast_to(scale, ref.shape))
+    bound = atol + rtol * ref
     bad = np.nonzero(err > bound)[0]
     assert len(bad) == 0, (f"{key}: {len(bad)} of {len(want)} elements differ, worst |err|={err.max():.3e} "
                            f"at {int(err.argmax())} (got {got[err.argmax()]}, want {want[err.argmax()]})")

@@ -68,3 +68,89 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(abi, "library_path", lambda: "/nonexistent/libgenn_b200.so")
     with pytest.raises(abi.B200Error):
         abi.load_library()
+
+
+# ---------------------------------------------------------------------------
+# Descriptors the kernels could not take are refused when they are pushed
+# (checked here without a GPU; none of them is ever handed to a kernel)
+# ---------------------------------------------------------------------------
+def _good_sparse():
+    d = abi.SynapseGroupDesc()
+    d.connectivity, d.wu_model = abi.CONN_SPARSE, abi.WU_STATIC_PULSE
+    d.num_src, d.num_trg, d.row_stride, d.ind_bytes = 10, 20, 8, 4
+    d.src_delay_slots, d.trg_delay_slots = 4, 4
+    # any non-null, suitably aligned addresses: validation never dereferences them
+    d.row_length, d.ind, d.g, d.out_post = 0x1000, 0x2000, 0x3000, 0x4000
+    d.src_spk_cnt, d.src_spk = 0x5000, 0x6000
+    return d
+
+
+def _validate(library, d):
+    library.b200_validate_synapse_group.argtypes = [ctypes.POINTER(abi.SynapseGroupDesc)]
+    library.b200_validate_synapse_group.restype = ctypes.c_int
+    return library.b200_validate_synapse_group(ctypes.byref(d))
+
+
+def test_a_well_formed_descriptor_passes(library):
+    assert _validate(library, _good_sparse()) == abi.OK
+
+
+def _ring_without_delays(d):
+    d.max_den_delay, d.den_delay = 16, 0x7000          # d missing
+
+
+def _ring_on_static_pulse(d):
+    d.max_den_delay, d.den_delay, d.d = 16, 0x7000, 0x8000
+
+
+def _dendritic_delay_on_dense(d):
+    d.connectivity, d.wu_model = abi.CONN_DENSE, abi.WU_DENDRITIC_DELAY
+    d.max_den_delay, d.den_delay, d.d, d.out_post = 16, 0x7000, 0x8000, 0
+
+
+def _ring_on_bitmask(d):
+    d.connectivity, d.wu_model, d.gp, d.row_stride = abi.CONN_BITMASK, abi.WU_CONSTANT_WEIGHT, 0x9000, 32
+    d.max_den_delay, d.den_delay, d.d = 16, 0x7000, 0x8000
+
+
+def _no_out_post(d):
+    d.out_post = 0
+
+
+def _misaligned_g(d):
+    d.g = 0x3004
+
+
+def _misaligned_ind(d):
+    d.ind = 0x2004
+
+
+def _misaligned_narrow_ind(d):
+    d.ind_bytes, d.ind = 2, 0x2002
+
+
+def _misaligned_d(d):
+    d.wu_model, d.max_den_delay, d.den_delay, d.d = abi.WU_DENDRITIC_DELAY, 16, 0x7000, 0x8001
+
+
+def _back_prop_delay_too_long(d):
+    d.wu_model = abi.WU_STDP
+    d.src_spike_times, d.trg_spike_times, d.trg_spk, d.trg_spk_cnt = 0xA000, 0xB000, 0xC000, 0xD000
+    d.col_length, d.remap = 0xE000, 0xF000
+    d.back_prop_delay = 3                               # needs 5 slots, the queue has 4
+
+
+def _axonal_delay_too_long(d):
+    d.axonal_delay = 3
+
+
+@pytest.mark.parametrize("spoil", [_ring_without_delays, _ring_on_static_pulse, _dendritic_delay_on_dense,
+                                   _ring_on_bitmask, _no_out_post, _misaligned_g, _misaligned_ind,
+                                   _misaligned_narrow_ind, _misaligned_d, _back_prop_delay_too_long,
+                                   _axonal_delay_too_long], ids=lambda f: f.__name__.strip("_"))
+def test_bad_descriptors_are_refused(library, spoil):
+    d = _good_sparse()
+    spoil(d)
+    assert _validate(library, d) == abi.ERR_INVALID
+    library.b200_last_error.restype = ctypes.c_char_p
+    assert library.b200_last_error()

@@ -31,6 +31,10 @@ struct StepState
     // presynaptic work, barrier after it, neuron work, barrier after it
     unsigned long long phase_cycles[4];
     unsigned long long probe[12];        // finer clock64 sums of the persistent kernel's profile mode
+    // verdict of tiledDecideKernel for the step being delivered: 1 = enough events for the
+    // target-tiled kernel, 0 = the one-reduction-per-event kernel delivers
+    unsigned int heavy;
+    unsigned int reserved;
 };
 
 constexpr unsigned int ERR_SPIKE_OVERFLOW = 1u;

@@ -45,6 +45,7 @@ struct SynapseLaunch
     unsigned long long seed;
     StepState *state;
     unsigned int count_events;
+    const unsigned char *tiled_served;  // per SPARSE group: 1 if the target-tiled kernel delivers it in heavy steps; or NULL
 };
 
 template<typename T> struct IndLoad;
@@ -179,6 +180,7 @@ presynapticSparseKernel(const SynapseLaunch L)
     const b200_synapse_group &g = L.groups[gi];
     const unsigned int tile = blockIdx.x - __ldg(&L.block_start[gi]);
     const unsigned int b = blockIdx.z;
+    if(L.tiled_served && L.tiled_served[gi] && L.state->heavy) return;
     const unsigned int k = L.state->phase;
     const unsigned int slots = g.src_delay_slots;
     const unsigned int rslot = ringSlot(k + slots - g.axonal_delay, slots);

@@ -27,6 +27,9 @@
 #include "urgent.cuh"
 #include "stream_step.cuh"
 #include "owner_step.cuh"
+#include "tiled.cuh"
+
+#include <cub/device/device_scan.cuh>
 
 using namespace b200;
 
@@ -216,6 +219,33 @@ struct b200_runner
         for(void *p : ownerBuffers) cudaFree(p);
         ownerCtas = nullptr; ownerEntries = nullptr; ownerBuffers.clear();
         ownerEligible = false;
+    }
+
+    // target-tiled delivery of heavy steps on the one-launch-per-kernel path (tiled.cuh): private
+    // re-packed copy of the non-learning SPARSE groups
+    bool useTiled = true;
+    float tiledMinEvents = 1.0e6f;          // estimated events of a step from which the tiled kernel takes it
+    bool tiledReady = false, tiledStale = true;
+    std::string tiledWhyNot;
+    TiledTile *tiledTiles = nullptr;
+    TiledSource *tiledSources = nullptr;
+    unsigned int *tiledRunStart = nullptr, *tiledCtaFirst = nullptr;
+    void *tiledKeys = nullptr;
+    float *tiledWeights = nullptr;
+    unsigned short *tiledItemTile = nullptr;
+    unsigned char *tiledItemShare = nullptr, *tiledServed = nullptr;
+    unsigned int tiledItemsPerBatch = 0, tiledNumSources = 0, tiledPostBits = 10, tiledGrid = 0;
+    size_t tiledSmemBytes = 0;
+    unsigned long long tiledSynapses = 0;
+
+    void dropTiled()
+    {
+        void *bufs[] = {tiledTiles, tiledSources, tiledRunStart, tiledCtaFirst, tiledKeys, tiledWeights, tiledItemTile,
+                        tiledItemShare, tiledServed};
+        for(void *b : bufs) if(b) cudaFree(b);
+        tiledTiles = nullptr; tiledSources = nullptr; tiledRunStart = nullptr; tiledCtaFirst = nullptr;
+        tiledKeys = nullptr; tiledWeights = nullptr; tiledItemTile = nullptr; tiledItemShare = nullptr; tiledServed = nullptr;
+        tiledReady = false;
     }
 
     // options
@@ -671,6 +701,7 @@ int prepare(b200_runner *r)
                         !r->neuronGroups.empty());
     r->fusedGroups = sparse;
     r->lagStale = true;
+    r->tiledStale = true;
     r->schedule = b200_runner::PLAIN;
     r->dropUrgent();
     {
@@ -1026,6 +1057,23 @@ bool touchesDelays(const b200_runner *r, const void *p, size_t bytes)
     return false;
 }
 
+// true if [p, p + bytes) overlaps an array the tile-major copy of the SPARSE groups was made from
+bool touchesSparse(const b200_runner *r, const void *p, size_t bytes)
+{
+    const unsigned char *a = static_cast<const unsigned char*>(p), *b = a + bytes;
+    auto overlaps = [&](const void *start, size_t size) {
+        const unsigned char *s0 = static_cast<const unsigned char*>(start);
+        return s0 && a < s0 + size && b > s0;
+    };
+    for(const auto &g : r->synapseGroups) {
+        if(g.connectivity != B200_CONN_SPARSE || g.wu_model == B200_WU_STDP) continue;
+        const size_t synapses = (size_t)g.num_src * g.row_stride;
+        if(overlaps(g.d, synapses) || overlaps(g.row_length, sizeof(unsigned int) * g.num_src) ||
+           overlaps(g.ind, synapses * g.ind_bytes) || overlaps(g.g, synapses * sizeof(float))) return true;
+    }
+    return false;
+}
+
 int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long numRec)
 {
     if(r->lagStale) {
@@ -1111,6 +1159,7 @@ SynapseLaunch synapseLaunch(const b200_runner *r, const DeviceTable<b200_synapse
     L.seed = r->seed;
     L.state = r->state;
     L.count_events = r->countEvents ? 1u : 0u;
+    L.tiled_served = nullptr;
     return L;
 }
 
@@ -1135,12 +1184,268 @@ struct ScopedTimer
     }
 };
 
+// Device buffer that is freed on every early return of a build function unless it was handed over.
+struct ScopedDevice
+{
+    void *p = nullptr;
+    ~ScopedDevice() { if(p) cudaFree(p); }
+    template<typename T> T *as() const { return static_cast<T*>(p); }
+    void *release() { void *q = p; p = nullptr; return q; }
+};
+
+// (Re)build the private tile-major copy of the non-learning SPARSE groups (tiled.cuh).  Not on the
+// time-step path: runs when the per-kernel path is first used and after the arrays it copies changed.
+int buildTiled(b200_runner *r)
+{
+    r->dropTiled();
+    r->tiledStale = false;
+    r->tiledWhyNot.clear();
+    if(!r->useTiled) { r->tiledWhyNot = "switched off"; return B200_OK; }
+    if(r->sharded()) { r->tiledWhyNot = "sharded models run on the persistent kernel"; return B200_OK; }
+    // the SPARSE groups in the order of sparseTable; the non-learning ones are served
+    std::vector<b200_synapse_group> sparse;
+    for(const auto &g : r->synapseGroups) if(g.connectivity == B200_CONN_SPARSE) sparse.push_back(g);
+    std::vector<unsigned char> served(sparse.size(), 0);
+    struct Target { float *ptr; unsigned int n, depth, stride, tiles, firstTile, firstTable, rows, firstSource; std::vector<size_t> groups; };
+    std::vector<Target> targets;
+    unsigned int maxDepth = 1;
+    unsigned long long slots = 0;
+    bool anyWeights = false;
+    for(size_t i = 0; i < sparse.size(); i++) {
+        const auto &g = sparse[i];
+        if(g.wu_model == B200_WU_STDP || g.src_sections > 1) continue;
+        float *ptr = g.max_den_delay ? g.den_delay : g.out_post;
+        const unsigned int depth = std::max(1u, g.max_den_delay);
+        auto it = std::find_if(targets.begin(), targets.end(), [&](const Target &t) { return t.ptr == ptr; });
+        if(it == targets.end()) {
+            targets.push_back(Target{ptr, g.num_trg, depth, 0, 0, 0, 0, 0, 0, {}});
+            it = targets.end() - 1;
+        }
+        if(it->n != g.num_trg || it->depth != depth) { r->tiledWhyNot = "groups disagree on the shape of a shared target"; return B200_OK; }
+        it->groups.push_back(i);
+        served[i] = 1;
+        maxDepth = std::max(maxDepth, depth);
+        slots += (unsigned long long)g.num_src * g.row_stride;
+        anyWeights = anyWeights || (g.g != nullptr && g.wu_model != B200_WU_STATIC_PULSE_CONSTANT_WEIGHT);
+    }
+    if(targets.empty()) { r->tiledWhyNot = "no non-learning SPARSE group"; return B200_OK; }
+    if(slots >= (1ull << 32)) { r->tiledWhyNot = "more than 2^32 synapse slots"; return B200_OK; }
+    if(maxDepth > TILED_ACC_FLOATS || maxDepth > 4096u) { r->tiledWhyNot = "delay ring too deep for a shared-memory tile"; return B200_OK; }
+    const bool key16 = (maxDepth <= 64u);
+    const unsigned int postBits = key16 ? 10u : 20u;
+    unsigned int numTiles = 0, entries = 0, numSources = 0;
+    for(auto &t : targets) {
+        t.stride = std::min(std::min(1u << postBits, TILED_ACC_FLOATS / t.depth), std::max(t.n, 1u));
+        t.tiles = (t.n + t.stride - 1) / t.stride;
+        t.rows = 1;
+        for(size_t gi : t.groups) t.rows += sparse[gi].num_src;
+        t.firstTile = numTiles;
+        t.firstTable = entries;
+        t.firstSource = numSources;
+        const unsigned long long e = (unsigned long long)entries + (unsigned long long)t.tiles * t.rows;
+        if(e >= (1ull << 32)) { r->tiledWhyNot = "run-start tables exceed 2^32 entries"; return B200_OK; }
+        entries = (unsigned int)e;
+        numTiles += t.tiles;
+        numSources += (unsigned int)t.groups.size();
+    }
+    if(numTiles > 65535u) { r->tiledWhyNot = "more than 65535 tiles"; return B200_OK; }
+
+    // ---- count, scan, place ---------------------------------------------------------------------
+    ScopedDevice count, runStart, scanTemp, keys, weights;
+    CUDA_TRY(cudaMalloc(&count.p, sizeof(unsigned int) * ((size_t)entries + 1)));
+    CUDA_TRY(cudaMalloc(&runStart.p, sizeof(unsigned int) * ((size_t)entries + 1)));
+    CUDA_TRY(cudaMemsetAsync(count.p, 0, sizeof(unsigned int) * ((size_t)entries + 1), r->stream));
+    std::vector<TiledBuildGroup> build;
+    std::vector<TiledSource> sources;
+    for(auto &t : targets) {
+        unsigned int rowBase = 0;
+        for(size_t gi : t.groups) {
+            const auto &g = sparse[gi];
+            TiledBuildGroup B{};
+            B.row_length = g.row_length; B.ind = g.ind; B.d = g.max_den_delay ? g.d : nullptr;
+            B.g = (g.wu_model == B200_WU_STATIC_PULSE_CONSTANT_WEIGHT) ? nullptr : g.g;
+            B.num_src = g.num_src; B.row_stride = g.row_stride; B.ind_bytes = g.ind_bytes; B.num_trg = g.num_trg;
+            B.depth = t.depth; B.first_tile = t.firstTile; B.stride = t.stride; B.row_base = rowBase;
+            B.rows_per_tile = t.rows; B.first_table = t.firstTable; B.const_weight = g.wu_params[0];
+            build.push_back(B);
+            TiledSource S{};
+            S.spk_cnt = g.src_spk_cnt; S.spk = g.src_spk; S.num_src = g.num_src; S.src_delay_slots = g.src_delay_slots;
+            S.axonal_delay = g.axonal_delay; S.row_base = rowBase; S.const_weight = g.wu_params[0]; S.mean_row = 0.0f;
+            sources.push_back(S);
+            rowBase += g.num_src;
+        }
+    }
+    auto launchBuild = [&](int pass) -> int {
+        for(const auto &B : build) {
+            const unsigned long long total = (unsigned long long)B.num_src * B.row_stride;
+            if(!total) continue;
+            const unsigned int blocks = (unsigned int)std::min<unsigned long long>((total + 255) / 256, 148ull * 16ull);
+            if(key16) tiledBuildKernel<uint16_t><<<blocks, 256, 0, r->stream>>>(B, pass, count.as<unsigned int>(), runStart.as<unsigned int>(),
+                                                                            keys.as<uint16_t>(), weights.as<float>(), postBits, r->state);
+            else tiledBuildKernel<uint32_t><<<blocks, 256, 0, r->stream>>>(B, pass, count.as<unsigned int>(), runStart.as<unsigned int>(),
+                                                                       keys.as<uint32_t>(), weights.as<float>(), postBits, r->state);
+            r->launches++;
+        }
+        CUDA_TRY(cudaPeekAtLastError());
+        return B200_OK;
+    };
+    if(const int e = launchBuild(0)) return e;
+    size_t tempBytes = 0;
+    CUDA_TRY(cub::DeviceScan::ExclusiveSum(nullptr, tempBytes, count.as<unsigned int>(), runStart.as<unsigned int>(), (int)(entries + 1), r->stream));
+    CUDA_TRY(cudaMalloc(&scanTemp.p, std::max<size_t>(tempBytes, 16)));
+    CUDA_TRY(cub::DeviceScan::ExclusiveSum(scanTemp.p, tempBytes, count.as<unsigned int>(), runStart.as<unsigned int>(), (int)(entries + 1), r->stream));
+    unsigned int total = 0;
+    CUDA_TRY(cudaMemcpyAsync(&total, runStart.as<unsigned int>() + entries, sizeof(total), cudaMemcpyDeviceToHost, r->stream));
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    CUDA_TRY(cudaMalloc(&keys.p, std::max<size_t>((size_t)total * (key16 ? 2 : 4), 16)));
+    if(anyWeights) CUDA_TRY(cudaMalloc(&weights.p, std::max<size_t>((size_t)total * sizeof(float), 16)));
+    CUDA_TRY(cudaMemsetAsync(count.p, 0, sizeof(unsigned int) * ((size_t)entries + 1), r->stream));
+    if(const int e = launchBuild(1)) return e;
+
+    // ---- tiles, sources, work items -----------------------------------------------------------------
+    std::vector<TiledTile> tiles(numTiles);
+    std::vector<unsigned int> tileStart(numTiles + 1);
+    for(auto &t : targets) {
+        for(unsigned int i = 0; i < t.tiles; i++) {
+            TiledTile &T = tiles[t.firstTile + i];
+            T.target = t.ptr; T.num_trg = t.n; T.depth = t.depth; T.first_trg = i * t.stride;
+            T.num_tile = std::min(t.stride, t.n - i * t.stride); T.stride = t.stride;
+            T.first_source = t.firstSource; T.num_sources = (unsigned int)t.groups.size();
+            T.table = t.firstTable + i * t.rows;
+            CUDA_TRY(cudaMemcpyAsync(&tileStart[t.firstTile + i], runStart.as<unsigned int>() + T.table, sizeof(unsigned int),
+                                     cudaMemcpyDeviceToHost, r->stream));
+        }
+    }
+    // per source: synapses per source neuron, for the event estimate of a step
+    std::vector<unsigned int> sourceFirst(numSources + 1, 0);
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    tileStart[numTiles] = total;
+    {
+        // synapses of a group = sum over the tiles of its target of (run_start at its last row + 1 - run_start at its first row)
+        size_t si = 0;
+        for(auto &t : targets) {
+            for(size_t gi : t.groups) {
+                const auto &g = sparse[gi];
+                unsigned long long syn = 0;
+                for(unsigned int i = 0; i < t.tiles; i++) {
+                    unsigned int ab[2];
+                    const unsigned int base = t.firstTable + i * t.rows + sources[si].row_base;
+                    CUDA_TRY(cudaMemcpy(&ab[0], runStart.as<unsigned int>() + base, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+                    CUDA_TRY(cudaMemcpy(&ab[1], runStart.as<unsigned int>() + base + g.num_src, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+                    syn += ab[1] - ab[0];
+                }
+                sources[si].mean_row = g.num_src ? (float)((double)syn / g.num_src) : 0.0f;
+                si++;
+            }
+        }
+    }
+    std::vector<unsigned short> itemTile;
+    std::vector<unsigned char> itemShare;
+    std::vector<double> itemWeight;
+    for(unsigned int t = 0; t < numTiles; t++) {
+        const unsigned int syn = tileStart[t + 1] - tileStart[t];
+        if(!syn) continue;
+        for(unsigned int s = 0; s < TILED_SPLIT; s++) {
+            itemTile.push_back((unsigned short)t);
+            itemShare.push_back((unsigned char)s);
+            itemWeight.push_back((double)syn / TILED_SPLIT + 4096.0);      // + the fixed cost of an item
+        }
+    }
+    if(itemTile.empty()) { r->tiledWhyNot = "no synapses"; return B200_OK; }
+    cudaDeviceProp prop;
+    CUDA_TRY(cudaGetDeviceProperties(&prop, r->device));
+    const unsigned int grid = (unsigned int)prop.multiProcessorCount;
+    const unsigned int perBatch = (unsigned int)itemTile.size();
+    std::vector<unsigned int> ctaFirst(grid + 1, perBatch * r->batch);
+    {
+        double all = 0.0;
+        for(double w : itemWeight) all += w;
+        all *= r->batch;
+        double acc = 0.0;
+        unsigned int c = 0;
+        for(unsigned int item = 0; item < perBatch * r->batch; item++) {
+            // item starts the share of CTA c once the work before it reaches c / grid of the whole
+            while(c <= grid && acc >= all * c / grid - 1e-9) ctaFirst[c++] = item;
+            acc += itemWeight[item % perBatch];
+        }
+        for(; c <= grid; c++) ctaFirst[c] = perBatch * r->batch;
+        ctaFirst[0] = 0;
+    }
+    size_t smem = 0;
+    for(const auto &T : tiles) smem = std::max(smem, sizeof(float) * T.depth * T.stride);
+    auto toDevice = [&](const void *host, size_t bytes, void **out) -> int {
+        CUDA_TRY(cudaMalloc(out, std::max<size_t>(bytes, 16)));
+        CUDA_TRY(cudaMemcpy(*out, host, bytes, cudaMemcpyHostToDevice));
+        return B200_OK;
+    };
+    int e = toDevice(tiles.data(), sizeof(TiledTile) * tiles.size(), (void**)&r->tiledTiles);
+    if(!e) e = toDevice(sources.data(), sizeof(TiledSource) * sources.size(), (void**)&r->tiledSources);
+    if(!e) e = toDevice(ctaFirst.data(), sizeof(unsigned int) * ctaFirst.size(), (void**)&r->tiledCtaFirst);
+    if(!e) e = toDevice(itemTile.data(), sizeof(unsigned short) * itemTile.size(), (void**)&r->tiledItemTile);
+    if(!e) e = toDevice(itemShare.data(), itemShare.size(), (void**)&r->tiledItemShare);
+    if(!e) e = toDevice(served.data(), served.size(), (void**)&r->tiledServed);
+    if(e) { r->dropTiled(); return e; }
+    if(key16) {
+        if(anyWeights) CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint16_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint16_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
+    else {
+        if(anyWeights) CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint32_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        else CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint32_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    }
+    r->tiledRunStart = static_cast<unsigned int*>(runStart.release());
+    r->tiledKeys = keys.release();
+    r->tiledWeights = static_cast<float*>(weights.release());
+    r->tiledItemsPerBatch = perBatch;
+    r->tiledNumSources = numSources;
+    r->tiledPostBits = postBits;
+    r->tiledGrid = grid;
+    r->tiledSmemBytes = smem;
+    r->tiledSynapses = total;
+    r->tiledReady = true;
+    return B200_OK;
+}
+
+TiledLaunch tiledLaunch(const b200_runner *r)
+{
+    TiledLaunch L;
+    L.tiles = r->tiledTiles; L.sources = r->tiledSources; L.run_start = r->tiledRunStart; L.keys = r->tiledKeys;
+    L.weights = r->tiledWeights; L.cta_first_item = r->tiledCtaFirst; L.item_tile = r->tiledItemTile;
+    L.item_share = r->tiledItemShare; L.items_per_batch = r->tiledItemsPerBatch; L.num_sources = r->tiledNumSources;
+    L.batch = r->batch; L.post_bits = r->tiledPostBits; L.min_events = r->tiledMinEvents; L.state = r->state;
+    L.count_events = r->countEvents ? 1u : 0u;
+    return L;
+}
+
+// Before steps are enqueued (or captured) on the one-launch-per-kernel path.
+int ensureTiled(b200_runner *r)
+{
+    if(r->sparseTable.num && (r->tiledStale || (r->useTiled && !r->tiledReady && r->tiledWhyNot.empty()))) {
+        r->dropGraph();
+        return buildTiled(r);
+    }
+    return B200_OK;
+}
+
 int enqueueSynapses(b200_runner *r, bool capturing)
 {
     if(r->sparseTable.num) {
         ScopedTimer tm(r, "presynaptic_update", capturing);
+        SynapseLaunch S = synapseLaunch(r, r->sparseTable);
+        if(r->tiledReady) {
+            // the step's estimated events decide which of the two kernels delivers the served groups
+            const TiledLaunch T = tiledLaunch(r);
+            tiledDecideKernel<<<1, 256, 0, r->stream>>>(T);
+            const bool key16 = (r->tiledPostBits == 10u);
+            if(key16 && r->tiledWeights) tiledDeliverKernel<uint16_t, true><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
+            else if(key16) tiledDeliverKernel<uint16_t, false><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
+            else if(r->tiledWeights) tiledDeliverKernel<uint32_t, true><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
+            else tiledDeliverKernel<uint32_t, false><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
+            r->launches += 2;
+            S.tiled_served = r->tiledServed;
+        }
         const dim3 grid(r->sparseTable.blocks, r->spikeLanes, r->batch);
-        presynapticSparseKernel<<<grid, PRE_BLOCK, 0, r->stream>>>(synapseLaunch(r, r->sparseTable));
+        presynapticSparseKernel<<<grid, PRE_BLOCK, 0, r->stream>>>(S);
         r->launches++;
     }
     if(r->postSpanTable.num) {
@@ -1199,7 +1504,7 @@ int enqueueStep(b200_runner *r, unsigned long long numRec, bool capturing)
 
 unsigned int kernelsPerStep(const b200_runner *r)
 {
-    return 1u + (r->sparseTable.num ? 1u : 0u) + (r->postSpanTable.num ? 1u : 0u) + (r->learnTable.num ? 1u : 0u) +
+    return 1u + (r->sparseTable.num ? (r->tiledReady ? 3u : 1u) : 0u) + (r->postSpanTable.num ? 1u : 0u) + (r->learnTable.num ? 1u : 0u) +
            (r->proceduralTable.num ? 1u : 0u);
 }
 
@@ -1279,6 +1584,7 @@ int b200_runner_destroy(b200_runner *r)
     r->dropUrgent();
     r->dropNear();
     if(r->fusedCtaCycles) cudaFree(r->fusedCtaCycles);
+    r->dropTiled();
     r->dropOwner();
     for(unsigned int p = 0; p < B200_MAX_RANKS; p++) {
         if(r->peerArena[p]) cudaIpcCloseMemHandle(r->peerArena[p]);
@@ -1502,6 +1808,7 @@ int b200_array_push(b200_runner *r, void *device_ptr, const void *host, size_t b
     CUDA_TRY(cudaMemcpyAsync(device_ptr, host, bytes, cudaMemcpyHostToDevice, r->stream));
     CUDA_TRY(cudaStreamSynchronize(r->stream));
     if(touchesDelays(r, device_ptr, bytes)) { r->lagStale = true; r->nearDataStale = true; }
+    if(touchesSparse(r, device_ptr, bytes)) r->tiledStale = true;
     return B200_OK;
 }
 
@@ -1516,6 +1823,7 @@ int b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes)
 {
     CUDA_TRY(cudaMemsetAsync(device_ptr, value, bytes, r->stream));
     if(touchesDelays(r, device_ptr, bytes)) { r->lagStale = true; r->nearDataStale = true; }
+    if(touchesSparse(r, device_ptr, bytes)) r->tiledStale = true;
     return B200_OK;
 }
 
@@ -1630,6 +1938,8 @@ int b200_set_option(b200_runner *r, const char *name, double value)
     else if(n == "owner_item_lanes") r->ownerItemLanes = (value <= 8.0) ? 8u : (value <= 16.0) ? 16u : 32u;
     else if(n == "fused_blocks_per_sm") { r->fusedBlocksPerSM = (unsigned int)value; r->dirty = true; }
     else if(n == "graph_steps") r->graphSteps = std::max(1u, (unsigned int)value);
+    else if(n == "use_tiled") { r->useTiled = (value != 0.0); r->tiledStale = true; }
+    else if(n == "tiled_min_events") r->tiledMinEvents = (float)value;
     else return fail(B200_ERR_INVALID, "unknown option %s", name);
     r->dropGraph();
     return B200_OK;
@@ -1651,6 +1961,7 @@ int b200_init_var(b200_runner *r, void *device_ptr, uint32_t elem_bytes, uint64_
                   uint32_t snippet, const float *params, uint32_t rng_stream)
 {
     r->lagStale = true;
+    r->tiledStale = true;
     InitParams prm{};
     for(int i = 0; i < 4; i++) prm.p[i] = params ? params[i] : 0.0f;
     const unsigned int blocks = (unsigned int)std::min<uint64_t>((count + INIT_BLOCK - 1) / INIT_BLOCK, 148u * 32u);
@@ -1673,6 +1984,7 @@ int b200_init_sparse_connectivity(b200_runner *r, uint32_t snippet, const float 
                                   uint32_t *row_length, void *ind, uint32_t rng_stream)
 {
     r->lagStale = true;
+    r->tiledStale = true;
     if(trg_end > num_trg || trg_begin >= trg_end) return fail(B200_ERR_INVALID, "bad target range");
     InitParams prm{};
     for(int i = 0; i < 4; i++) prm.p[i] = params ? params[i] : 0.0f;
@@ -1699,6 +2011,7 @@ int b200_init_sparse_vars(b200_runner *r, const uint32_t *row_length, uint32_t n
                           uint32_t snippet, const float *params, uint32_t rng_stream)
 {
     r->lagStale = true;
+    r->tiledStale = true;
     InitParams prm{};
     for(int i = 0; i < 4; i++) prm.p[i] = params ? params[i] : 0.0f;
     const uint64_t total = (uint64_t)num_src * row_stride;
@@ -1738,6 +2051,8 @@ int b200_update_synapses(b200_runner *r)
 {
     int e = prepare(r);
     if(e) return e;
+    e = ensureTiled(r);
+    if(e) return e;
     return enqueueSynapses(r, false);
 }
 
@@ -1770,6 +2085,9 @@ int b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_ti
             if(e) return e;
             left -= n;
         }
+    }
+    else if((e = ensureTiled(r)) != B200_OK) {
+        return e;
     }
     else if(r->useGraph && !r->timing && num_steps >= 2) {
         const unsigned int len = (unsigned int)std::min<uint64_t>(num_steps, r->graphSteps);
@@ -1885,6 +2203,22 @@ int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
             if(e) return e;
         }
         *value = (uint64_t)r->schedule;
+        return B200_OK;
+    }
+    if(n == "tiled_ready" || n == "tiled_synapses" || n == "heavy") {
+        // the target-tiled copy of the SPARSE groups (built when the one-launch-per-kernel path is first
+        // used) / the verdict of the last step's event estimate
+        if(n == "heavy") {
+            unsigned int h = 0;
+            CUDA_TRY(cudaStreamSynchronize(r->stream));
+            CUDA_TRY(cudaMemcpy(&h, &r->state->heavy, sizeof(h), cudaMemcpyDeviceToHost));
+            *value = h;
+            return B200_OK;
+        }
+        int e = prepare(r);
+        if(!e) e = ensureTiled(r);
+        if(e) return e;
+        *value = (n == "tiled_ready") ? (r->tiledReady ? 1u : 0u) : r->tiledSynapses;
         return B200_OK;
     }
     if(n == "lag_eligible" || n == "lag") {

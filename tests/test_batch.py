@@ -44,6 +44,45 @@ def _model(seed=9, batch=BATCH, v_seed=77):
     return m, sg
 
 
+def _static_batched(batch=2):
+    """Potjans miniature (dendritic delays, constant-current background) with a different initial
+    potential for every batch element."""
+    m = workloads.potjans(neuron_scale=0.005, seed=7, host_connectivity=True, background="dc", record=True)
+    m.batch_size = batch
+    net = resolve(m)
+    rng = np.random.default_rng(21)
+    for p in net.pops:
+        p.vars["V"] = (p.vars["V"] + rng.normal(0.0, 2.0, size=p.vars["V"].shape)).astype(np.float32)
+    return net
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tiled", [0, 1])
+def test_batched_static_network_matches_the_cpu_checker(tiled):
+    """Batch > 1 through the SPARSE kernels of the one-launch-per-kernel path: one reduction per event
+    (tiled 0) and the target-tiled kernel forced on for every step (tiled 1)."""
+    from genn_b200.runtime import Runtime
+    from oracle.oracle import OracleRunner
+    net, onet = _static_batched(), _static_batched()
+    rt, orc = Runtime(None, 300, net=net), OracleRunner(onet, 300)
+    rt.set_option("tiled_min_events", 0 if tiled else 1e30)
+    different = False
+    for step in range(300):
+        rt.step_time(1)
+        orc.step(1)
+        for p in net.pops:
+            a, b = np.sort(rt.current_spikes(p.name, 0)), np.sort(rt.current_spikes(p.name, 1))
+            different = different or not np.array_equal(a, b)
+            for e, got in enumerate((a, b)):
+                assert np.array_equal(got, np.sort(orc.current_spikes(p.name, e))), f"step {step} {p.name}[{e}]"
+    for p in net.pops:
+        helpers.assert_close(rt.array(f"{p.name}.V").reshape(-1), orc.array(f"{p.name}.V").reshape(-1), f"V {p.name}", 1e-5, 2e-6)
+    assert different, "the batch elements were meant to diverge"
+    assert rt.counter("heavy") == tiled
+    rt.close()
+    orc.close()
+
+
 @pytest.mark.gpu
 def test_every_batch_element_matches_the_cpu_checker_and_the_weights_reduce():
     from genn_b200.runtime import Runtime

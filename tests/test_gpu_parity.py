@@ -25,7 +25,12 @@ RTOL, ATOL = 1e-5, 2e-6
 # kernel.  (use_fused, use_owner, use_lag, use_emit, use_split, stream_warps)
 PATHS = {"owner": (1, 1, 1, 1, 1, -1), "persistent": (1, 0, 1, 1, 1, -1), "persistent-emit": (1, 0, 0, 1, 1, -1),
          "persistent-split": (1, 0, 0, 0, 1, -1), "persistent-split-one-warp-set": (1, 0, 0, 0, 1, 0),
-         "persistent-plain": (1, 0, 0, 0, 0, -1), "per-kernel": (0, 0, 1, 1, 1, -1)}
+         "persistent-plain": (1, 0, 0, 0, 0, -1), "per-kernel": (0, 0, 1, 1, 1, -1),
+         # one launch per kernel with EVERY step delivered by the target-tiled kernel (shared-memory
+         # accumulation over the private tile-major copy), which production takes only for heavy steps
+         "per-kernel-tiled": (0, 0, 1, 1, 1, -1)}
+# networks whose SPARSE groups the target-tiled kernel serves (non-learning)
+TILED_CASES = {"ff_sparse", "c1_full", "ff_sparse_narrow", "potjans_mini", "potjans_mini_d1", "cond_delay", "izhikevich"}
 # networks whose every synapse has a dendritic delay of at least one step
 LAG_CASES = {"potjans_mini_d1"}
 # networks with dendritic-delay rings (some of whose synapses may arrive in the same step)
@@ -42,6 +47,10 @@ def _select(rt, path, name=None):
     rt.set_option("use_emit", emit)
     rt.set_option("use_split", split)
     rt.set_option("stream_warps", stream)
+    if path == "per-kernel-tiled":
+        rt.set_option("tiled_min_events", 0)
+        if name in TILED_CASES:
+            assert rt.counter("tiled_ready") == 1 and rt.counter("tiled_synapses") > 0
     if name is not None and rt.step_path()[0] >= 1:
         want = (2 if (lag and name in LAG_CASES) else 3 if (emit and stream != 0 and name in RING_CASES)
                 else 1 if (split and name in RING_CASES) else 0)
@@ -85,7 +94,26 @@ def test_step_by_step_matches_reference_golden(name, path):
     _select(rt, path, name)
     got = helpers.run_and_collect(_Adapter(rt), net, steps, dump_every)
     helpers.compare(got, helpers.load_golden(name), exact_state=False, rtol=RTOL, atol=ATOL)
+    if path == "per-kernel-tiled" and name in TILED_CASES:
+        assert rt.counter("heavy") == 1, "the tiled kernel was meant to deliver every step"
     rt.close()
+
+
+def test_tiled_copy_follows_pushed_weights():
+    """The tile-major copy is private: pushing new weights into the caller's array must reach it."""
+    model, steps, _ = CASES["ff_sparse"]()
+    net = resolve(model)
+    outs = []
+    for tiled in (1, 0):
+        rt = _runtime(net, steps)
+        _select(rt, "per-kernel-tiled" if tiled else "per-kernel")
+        rt.step_time(20)
+        rt.plan.push("syn.g", (net.syn("syn").g * 0.5).astype(np.float32))
+        rt.step_time(80)
+        outs.append((rt.array("psm0.out_post")[0], rt.array("post.V")[0]))
+        rt.close()
+    helpers.assert_close(outs[0][0], outs[1][0], "out_post after a weight push", RTOL, ATOL)
+    helpers.assert_close(outs[0][1], outs[1][1], "V after a weight push", RTOL, ATOL)
 
 
 @pytest.mark.parametrize("path", list(PATHS))

@@ -1,0 +1,1267 @@
+// B200 code-generation backend: implementation.  See backend.h for the design.
+//
+// Reference counterparts, by function (paths relative to the GeNN 5.4.0 tree):
+//   genNeuronUpdate    backendSIMT.cc:320-662 + backendCUDAHIP.cc:306-449
+//   genSynapseUpdate   backendSIMT.cc:664-866, presynapticUpdateStrategySIMT.cc, backendCUDAHIP.cc:451-621
+//   genCustomUpdate    backendSIMT.cc:868-1154, backendCUDAHIP.cc:623-884
+//   genInit            backendSIMT.cc:1368-1779, backendCUDAHIP.cc:886-1071
+//   Array, State       src/genn/backends/cuda/backend.cc:73-259
+// The per-group model code (sim code, threshold, reset, postsynaptic and weight-update
+// snippets, initialisation snippets) is emitted by GeNN's own group classes, called back
+// from here exactly as every GeNN backend does; the kernel scaffolds around it are this
+// file's own.
+#include "backend.h"
+
+#include <algorithm>
+#include <cassert>
+#include <cstring>
+#include <numeric>
+#include <sstream>
+
+#include <cuda_runtime.h>
+#include <dlfcn.h>
+
+#include <plog/Log.h>
+
+#include "gennUtils.h"
+#include "logging.h"
+#include "type.h"
+#include "code_generator/codeGenUtils.h"
+#include "code_generator/codeStream.h"
+#include "code_generator/customUpdateGroupMerged.h"
+#include "code_generator/initGroupMerged.h"
+#include "code_generator/modelSpecMerged.h"
+#include "code_generator/neuronUpdateGroupMerged.h"
+#include "code_generator/standardLibrary.h"
+#include "code_generator/synapseUpdateGroupMerged.h"
+
+using namespace GeNN;
+using namespace GeNN::CodeGenerator;
+
+namespace
+{
+#define B200_CHECK_CUDA(call)                                                                               \
+    do {                                                                                                    \
+        const cudaError_t b200Error = (call);                                                               \
+        if(b200Error != cudaSuccess) {                                                                      \
+            throw std::runtime_error(std::string(__FILE__) + ": " + std::to_string(__LINE__) +              \
+                                     ": cuda error " + std::to_string((int)b200Error) + ": " +              \
+                                     cudaGetErrorString(b200Error));                                        \
+        }                                                                                                   \
+    } while(0)
+
+// Random number functions of the model code (gennrand_*): the per-thread generator `_rng` is a
+// counter-based Philox stream created in the kernel prologue (genn_b200_gen.cuh); it has no state
+// in memory.
+const EnvironmentLibrary::Library floatRandomFunctions = {
+    {"gennrand", {Type::ResolvedType::createFunction(Type::Uint32, {}), "b200gen::u32($(_rng))"}},
+    {"gennrand_uniform", {Type::ResolvedType::createFunction(Type::Float, {}), "b200gen::uniform($(_rng))"}},
+    {"gennrand_normal", {Type::ResolvedType::createFunction(Type::Float, {}), "b200gen::normal($(_rng))"}},
+    {"gennrand_exponential", {Type::ResolvedType::createFunction(Type::Float, {}), "b200gen::exponential($(_rng))"}},
+    {"gennrand_log_normal", {Type::ResolvedType::createFunction(Type::Float, {Type::Float, Type::Float}), "b200gen::logNormal($(_rng), $(0), $(1))"}},
+    {"gennrand_gamma", {Type::ResolvedType::createFunction(Type::Float, {Type::Float}), "b200gen::gamma($(_rng), $(0))"}},
+    {"gennrand_binomial", {Type::ResolvedType::createFunction(Type::Uint32, {Type::Uint32, Type::Float}), "b200gen::binomial($(_rng), $(0), $(1))"}},
+};
+const EnvironmentLibrary::Library doubleRandomFunctions = {
+    {"gennrand", {Type::ResolvedType::createFunction(Type::Uint32, {}), "b200gen::u32($(_rng))"}},
+    {"gennrand_uniform", {Type::ResolvedType::createFunction(Type::Double, {}), "(double)b200gen::uniform($(_rng))"}},
+    {"gennrand_normal", {Type::ResolvedType::createFunction(Type::Double, {}), "(double)b200gen::normal($(_rng))"}},
+    {"gennrand_exponential", {Type::ResolvedType::createFunction(Type::Double, {}), "(double)b200gen::exponential($(_rng))"}},
+    {"gennrand_log_normal", {Type::ResolvedType::createFunction(Type::Double, {Type::Double, Type::Double}), "(double)b200gen::logNormal($(_rng), (float)$(0), (float)$(1))"}},
+    {"gennrand_gamma", {Type::ResolvedType::createFunction(Type::Double, {Type::Double}), "(double)b200gen::gamma($(_rng), (float)$(0))"}},
+    {"gennrand_binomial", {Type::ResolvedType::createFunction(Type::Uint32, {Type::Uint32, Type::Double}), "b200gen::binomial($(_rng), $(0), (float)$(1))"}},
+};
+
+const EnvironmentLibrary::Library &randomFunctions(const Type::ResolvedType &precision)
+{
+    return (precision == Type::Float) ? floatRandomFunctions : doubleRandomFunctions;
+}
+
+// device functions the backend adds to every kernel environment
+const EnvironmentLibrary::Library backendFunctions = {
+    {"clz", {Type::ResolvedType::createFunction(Type::Int32, {Type::Uint32}), "__clz($(0))"}},
+    {"atomic_or", {Type::ResolvedType::createFunction(Type::Void, {Type::Uint32.createPointer(), Type::Uint32}), "atomicOr($(0), $(1))"}},
+};
+
+size_t padTo(size_t n, size_t multiple)
+{
+    return ((n + multiple - 1) / multiple) * multiple;
+}
+
+//! Distinguishes the random streams of the kernels of one model: every merged group of every
+//! kernel kind gets its own stream id
+enum StreamKind : unsigned int
+{
+    STREAM_NEURON = 0x10000u, STREAM_PRESYNAPTIC = 0x20000u, STREAM_POSTSYNAPTIC = 0x30000u, STREAM_DYNAMICS = 0x40000u,
+    STREAM_CUSTOM = 0x50000u, STREAM_CUSTOM_WU = 0x60000u, STREAM_INIT_NEURON = 0x70000u, STREAM_INIT_SYNAPSE = 0x80000u,
+    STREAM_INIT_CONNECT = 0x90000u, STREAM_INIT_SPARSE = 0xA0000u, STREAM_INIT_CUSTOM = 0xB0000u,
+    STREAM_INIT_CUSTOM_WU = 0xC0000u, STREAM_INIT_CUSTOM_WU_SPARSE = 0xD0000u
+};
+
+//! One generated kernel of one merged group: its start-id table and launch geometry
+struct KernelLaunch
+{
+    std::string name;           // kernel name
+    size_t numThreads = 0;      // padded total over the groups
+    bool batched = false;       // grid.y = batch size
+};
+
+//! Emits `__device__ unsigned int <name>[] = {...};` with the first thread id of every group
+template<typename G, typename S>
+size_t genStartIDs(CodeStream &os, const std::string &name, const G &mergedGroup, size_t block, S getNumThreads)
+{
+    os << "__device__ unsigned int " << name << "[] = {";
+    size_t id = 0;
+    for(const auto &g : mergedGroup.getGroups()) {
+        os << id << ", ";
+        id += padTo(std::max<size_t>(1, getNumThreads(g.get())), block);
+    }
+    os << id << "};" << std::endl;
+    return id;
+}
+
+//! Kernel prologue: global thread id, the group this thread serves and its id inside the group
+void genFindGroup(CodeStream &os, const std::string &structName, const std::string &arrayName, const std::string &startName,
+                  size_t numGroups)
+{
+    os << "const unsigned int b200Thread = (blockIdx.x * blockDim.x) + threadIdx.x;" << std::endl;
+    if(numGroups == 1) {
+        os << "const " << structName << " *group = &" << arrayName << "[0];" << std::endl;
+        os << "const unsigned int b200Group = 0;" << std::endl;
+        os << "const unsigned int b200Local = b200Thread;" << std::endl;
+    }
+    else {
+        os << "unsigned int b200Lo = 0, b200Hi = " << numGroups << ";" << std::endl;
+        os << "while((b200Hi - b200Lo) > 1)";
+        {
+            CodeStream::Scope b(os);
+            os << "const unsigned int b200Mid = (b200Lo + b200Hi) / 2;" << std::endl;
+            os << "if(b200Thread >= " << startName << "[b200Mid]) b200Lo = b200Mid; else b200Hi = b200Mid;" << std::endl;
+        }
+        os << "const " << structName << " *group = &" << arrayName << "[b200Lo];" << std::endl;
+        os << "const unsigned int b200Group = b200Lo;" << std::endl;
+        os << "const unsigned int b200Local = b200Thread - " << startName << "[b200Lo];" << std::endl;
+    }
+}
+
+//! `__device__` array of merged-group structs plus the push function the runtime calls through
+//! libffi (runtime.h:573-669); fields in the order GroupMerged::getSortedFields gives
+template<typename T>
+void genDeviceStructArrayPush(CodeStream &os, const BackendBase &backend, const std::vector<T> &groups)
+{
+    for(const auto &g : groups) {
+        const std::string structName = "Merged" + T::name + "Group" + std::to_string(g.getIndex());
+        os << "__device__ " << structName << " d_merged" << T::name << "Group" << g.getIndex() << "[" << g.getGroups().size() << "];" << std::endl;
+        if(g.getFields().empty()) {
+            continue;
+        }
+        os << "void pushMerged" << T::name << "Group" << g.getIndex() << "ToDevice(unsigned int idx, ";
+        g.generateStructFieldArgumentDefinitions(os, backend);
+        os << ")";
+        {
+            CodeStream::Scope b(os);
+            os << structName << " group = {";
+            for(const auto &f : g.getSortedFields(backend)) {
+                os << f.name << ", ";
+            }
+            os << "};" << std::endl;
+            os << "CHECK_RUNTIME_ERRORS(cudaMemcpyToSymbolAsync(d_merged" << T::name << "Group" << g.getIndex() << ", &group, sizeof(" << structName << "), ";
+            os << "idx * sizeof(" << structName << "), cudaMemcpyHostToDevice, 0));" << std::endl;
+        }
+    }
+}
+
+//! Host-side launch of a generated kernel on stream 0
+void genLaunch(CodeStream &os, const KernelLaunch &k, size_t block, unsigned int batchSize, const std::string &args)
+{
+    if(k.numThreads == 0) {
+        return;
+    }
+    CodeStream::Scope b(os);
+    os << "const dim3 threads(" << block << ", 1);" << std::endl;
+    os << "const dim3 grid(" << (k.numThreads / block) << ", " << (k.batched ? batchSize : 1u) << ");" << std::endl;
+    os << k.name << "<<<grid, threads>>>(" << args << ");" << std::endl;
+    os << "CHECK_RUNTIME_ERRORS(cudaPeekAtLastError());" << std::endl;
+}
+
+void genKernelTimerStart(CodeStream &os, const std::string &name, bool enabled)
+{
+    if(enabled) {
+        os << "CHECK_RUNTIME_ERRORS(cudaEventRecord(" << name << "Start));" << std::endl;
+    }
+}
+
+void genKernelTimerStop(CodeStream &os, const std::string &name, bool enabled, bool readBack)
+{
+    if(enabled) {
+        os << "CHECK_RUNTIME_ERRORS(cudaEventRecord(" << name << "Stop));" << std::endl;
+        if(readBack) {
+            os << "CHECK_RUNTIME_ERRORS(cudaEventSynchronize(" << name << "Stop));" << std::endl;
+            os << "float b200Elapsed;" << std::endl;
+            os << "CHECK_RUNTIME_ERRORS(cudaEventElapsedTime(&b200Elapsed, " << name << "Start, " << name << "Stop));" << std::endl;
+            os << name << "Time += b200Elapsed / 1000.0;" << std::endl;
+        }
+    }
+}
+}   // anonymous namespace
+
+namespace GeNN::CodeGenerator::B200
+{
+//--------------------------------------------------------------------------
+// Preferences
+//--------------------------------------------------------------------------
+void Preferences::updateHash(boost::uuids::detail::sha1 &hash) const
+{
+    PreferencesBase::updateHash(hash);
+    Utils::updateHash(deviceID, hash);
+    Utils::updateHash(blockSize, hash);
+}
+
+//--------------------------------------------------------------------------
+// Array
+//--------------------------------------------------------------------------
+Array::Array(const Type::ResolvedType &type, size_t count, VarLocation location, bool uninitialized)
+:   Runtime::ArrayBase(type, count, location, uninitialized)
+{
+    if(count > 0) {
+        allocate(count);
+    }
+}
+
+Array::~Array()
+{
+    if(getCount() > 0) {
+        free();
+    }
+}
+
+void Array::allocate(size_t count)
+{
+    setCount(count);
+    // the runtime wraps the host pointer in views for every location with a host side
+    // (pygenn/src/runtime.cc:31-36); page-locked so that pushes and pulls run at link speed
+    if(getLocation() & VarLocationAttribute::HOST) {
+        std::byte *host = nullptr;
+        B200_CHECK_CUDA(cudaHostAlloc(reinterpret_cast<void**>(&host), getSizeBytes(), cudaHostAllocPortable));
+        setHostPointer(host);
+    }
+    if(getLocation() & VarLocationAttribute::DEVICE) {
+        // 256 bytes of slack: kernels may read whole vectors that straddle the end of an unaligned row
+        B200_CHECK_CUDA(cudaMalloc(reinterpret_cast<void**>(&m_DevicePointer), getSizeBytes() + 256));
+    }
+}
+
+void Array::free()
+{
+    if(getHostPointer()) {
+        B200_CHECK_CUDA(cudaFreeHost(getHostPointer()));
+        setHostPointer(nullptr);
+    }
+    if(m_DevicePointer) {
+        B200_CHECK_CUDA(cudaFree(m_DevicePointer));
+        m_DevicePointer = nullptr;
+    }
+    setCount(0);
+}
+
+void Array::pushToDevice()
+{
+    if(!(getLocation() & VarLocationAttribute::HOST) || !(getLocation() & VarLocationAttribute::DEVICE)) {
+        throw std::runtime_error("Cannot push array that isn't present on host and device");
+    }
+    B200_CHECK_CUDA(cudaMemcpy(m_DevicePointer, getHostPointer(), getSizeBytes(), cudaMemcpyHostToDevice));
+}
+
+void Array::pullFromDevice()
+{
+    if(!(getLocation() & VarLocationAttribute::HOST) || !(getLocation() & VarLocationAttribute::DEVICE)) {
+        throw std::runtime_error("Cannot pull array that isn't present on host and device");
+    }
+    B200_CHECK_CUDA(cudaMemcpy(getHostPointer(), m_DevicePointer, getSizeBytes(), cudaMemcpyDeviceToHost));
+}
+
+void Array::pushSlice1DToDevice(size_t offset, size_t count)
+{
+    if(offset + count > getCount()) {
+        throw std::runtime_error("Cannot push slice that overflows array");
+    }
+    const size_t bytes = getType().getValue().size;
+    B200_CHECK_CUDA(cudaMemcpy(m_DevicePointer + (offset * bytes), getHostPointer() + (offset * bytes), count * bytes, cudaMemcpyHostToDevice));
+}
+
+void Array::pullSlice1DFromDevice(size_t offset, size_t count)
+{
+    if(offset + count > getCount()) {
+        throw std::runtime_error("Cannot pull slice that overflows array");
+    }
+    const size_t bytes = getType().getValue().size;
+    B200_CHECK_CUDA(cudaMemcpy(getHostPointer() + (offset * bytes), m_DevicePointer + (offset * bytes), count * bytes, cudaMemcpyDeviceToHost));
+}
+
+void Array::memsetDeviceObject(int value)
+{
+    B200_CHECK_CUDA(cudaMemset(m_DevicePointer, value, getSizeBytes()));
+}
+
+void Array::serialiseDeviceObject(std::vector<std::byte> &bytes, bool pointerToPointer) const
+{
+    std::byte vBytes[sizeof(void*)];
+    if(pointerToPointer) {
+        std::byte *const *devicePointerPointer = &m_DevicePointer;
+        std::memcpy(vBytes, &devicePointerPointer, sizeof(void*));
+    }
+    else {
+        std::memcpy(vBytes, &m_DevicePointer, sizeof(void*));
+    }
+    std::copy(std::begin(vBytes), std::end(vBytes), std::back_inserter(bytes));
+}
+
+void Array::serialiseHostObject(std::vector<std::byte>&, bool) const
+{
+    throw std::runtime_error("The B200 backend has no host objects");
+}
+
+//--------------------------------------------------------------------------
+// Factory
+//--------------------------------------------------------------------------
+Backend createBackend(const ModelSpecInternal&, const filesystem::path&, plog::Severity backendLevel,
+                      plog::IAppender *backendAppender, const Preferences &preferences)
+{
+    if(plog::get<Logging::CHANNEL_BACKEND>() == nullptr) {
+        plog::init<Logging::CHANNEL_BACKEND>(backendLevel, backendAppender);
+    }
+    else {
+        plog::get<Logging::CHANNEL_BACKEND>()->setMaxSeverity(backendLevel);
+    }
+    if(preferences.blockSize == 0 || (preferences.blockSize % 32) != 0 || preferences.blockSize > 1024) {
+        throw std::runtime_error("B200 backend: blockSize must be a multiple of 32 up to 1024");
+    }
+    return Backend(preferences);
+}
+
+//--------------------------------------------------------------------------
+// Backend: construction, simple virtuals
+//--------------------------------------------------------------------------
+Backend::Backend(const Preferences &preferences)
+:   BackendBase(preferences)
+{
+    setPointerBytes(sizeof(void*));
+}
+
+std::string Backend::includeDirectory() const
+{
+    const auto &p = getPreferences<Preferences>();
+    if(!p.includePath.empty()) {
+        return p.includePath;
+    }
+    // <repo>/genn_b200/backend/libgenn_b200_backend.so -> <repo>/include
+    Dl_info info;
+    if(dladdr(reinterpret_cast<const void*>(&createBackend), &info) && info.dli_fname) {
+        std::string path(info.dli_fname);
+        for(int up = 0; up < 3; up++) {
+            const size_t slash = path.find_last_of('/');
+            path = (slash == std::string::npos) ? "." : path.substr(0, slash);
+        }
+        return path + "/include";
+    }
+    return "include";
+}
+
+size_t Backend::getSynapticMatrixRowStride(const SynapseGroupInternal &sg) const
+{
+    // the row strides PyGeNN assumes when it fills host views (pygenn/genn_groups.py:41-48)
+    if((sg.getMatrixType() & SynapseMatrixConnectivity::SPARSE) || (sg.getMatrixType() & SynapseMatrixConnectivity::TOEPLITZ)) {
+        return sg.getMaxConnections();
+    }
+    else if(sg.getMatrixType() & SynapseMatrixConnectivity::BITMASK) {
+        return padTo(sg.getTrgNeuronGroup()->getNumNeurons(), 32);
+    }
+    else {
+        return sg.getTrgNeuronGroup()->getNumNeurons();
+    }
+}
+
+void Backend::genDefinitionsPreamble(CodeStream &os, const ModelSpecMerged&) const
+{
+    os << "// Standard C++ includes" << std::endl;
+    os << "#include <random>" << std::endl;
+    os << "#include <string>" << std::endl;
+    os << "#include <stdexcept>" << std::endl;
+    os << std::endl;
+    os << "// Standard C includes" << std::endl;
+    os << "#include <cassert>" << std::endl;
+    os << "#include <cmath>" << std::endl;
+    os << "#include <cstdint>" << std::endl;
+    os << "#include <cstring>" << std::endl;
+    os << std::endl;
+    os << "// CUDA" << std::endl;
+    os << "#include <cuda_runtime.h>" << std::endl;
+    os << std::endl;
+    os << "#define CHECK_RUNTIME_ERRORS(call) {\\" << std::endl;
+    os << "    cudaError_t error = call;\\" << std::endl;
+    os << "    if (error != cudaSuccess) {\\" << std::endl;
+    os << "        throw std::runtime_error(__FILE__\": \" + std::to_string(__LINE__) + \": cuda error \" + std::to_string(error) + \": \" + cudaGetErrorString(error));\\" << std::endl;
+    os << "    }\\" << std::endl;
+    os << "}" << std::endl;
+    os << std::endl;
+    os << "// seed of every Philox stream: the model's seed, or drawn from the system when that is zero" << std::endl;
+    os << "extern unsigned long long b200Seed;" << std::endl;
+    os << "// Device helpers of the B200 backend (spike compaction, Philox streams)" << std::endl;
+    os << "#if defined(__CUDACC__)" << std::endl;
+    os << "#include \"genn_b200_gen.cuh\"" << std::endl;
+    os << "#endif" << std::endl;
+    os << std::endl;
+}
+
+void Backend::genRunnerPreamble(CodeStream &os, const ModelSpecMerged&) const
+{
+    os << "unsigned long long b200Seed = 0;" << std::endl;
+}
+
+void Backend::genAllocateMemPreamble(CodeStream &os, const ModelSpecMerged &modelMerged) const
+{
+    os << "CHECK_RUNTIME_ERRORS(cudaSetDevice(" << getPreferences<Preferences>().deviceID << "));" << std::endl;
+    if(modelMerged.getModel().getSeed() == 0) {
+        os << "{ std::random_device b200SeedSource; b200Seed = ((unsigned long long)b200SeedSource() << 32) | b200SeedSource(); }" << std::endl;
+    }
+    else {
+        os << "b200Seed = " << modelMerged.getModel().getSeed() << "ull;" << std::endl;
+    }
+}
+
+void Backend::genFreeMemPreamble(CodeStream&, const ModelSpecMerged&) const
+{
+}
+
+void Backend::genStepTimeFinalisePreamble(CodeStream &os, const ModelSpecMerged &modelMerged) const
+{
+    // kernel timers are read back once per step, as the reference does (backendCUDAHIP.cc:1400-1411)
+    if(modelMerged.getModel().isTimingEnabled()) {
+        os << "CHECK_RUNTIME_ERRORS(cudaDeviceSynchronize());" << std::endl;
+    }
+}
+
+std::unique_ptr<GeNN::Runtime::StateBase> Backend::createState(const Runtime::Runtime&) const
+{
+    B200_CHECK_CUDA(cudaSetDevice(getPreferences<Preferences>().deviceID));
+    return std::make_unique<State>();
+}
+
+std::unique_ptr<GeNN::Runtime::ArrayBase> Backend::createArray(const Type::ResolvedType &type, size_t count,
+                                                               VarLocation location, bool uninitialized) const
+{
+    return std::make_unique<Array>(type, count, location, uninitialized);
+}
+
+std::unique_ptr<GeNN::Runtime::ArrayBase> Backend::createPopulationRNG(size_t) const
+{
+    // random streams are stateless (keyed on seed, group, neuron, time step): one placeholder word
+    return std::make_unique<Array>(Type::Uint32, 1, VarLocation::DEVICE, false);
+}
+
+void Backend::genLazyVariableDynamicAllocation(CodeStream &os, const Type::ResolvedType &type, const std::string &name,
+                                               VarLocation loc, const std::string &countVarName) const
+{
+    const auto &underlyingType = type.isPointer() ? *type.getPointer().valueType : type;
+    const std::string hostPointer = type.isPointer() ? ("*$(_" + name + ")") : ("$(_" + name + ")");
+    const std::string hostPointerToPointer = type.isPointer() ? ("$(_" + name + ")") : ("&$(_" + name + ")");
+    const std::string devicePointerToPointer = type.isPointer() ? ("$(_d_" + name + ")") : ("&$(_d_" + name + ")");
+    if(loc & VarLocationAttribute::HOST) {
+        os << "CHECK_RUNTIME_ERRORS(cudaHostAlloc(" << hostPointerToPointer << ", " << countVarName << " * sizeof(" << underlyingType.getName() << "), cudaHostAllocPortable));" << std::endl;
+    }
+    if(loc & VarLocationAttribute::DEVICE) {
+        os << "CHECK_RUNTIME_ERRORS(cudaMalloc(" << devicePointerToPointer << ", " << countVarName << " * sizeof(" << underlyingType.getName() << ")));" << std::endl;
+    }
+    (void)hostPointer;
+}
+
+void Backend::genLazyVariableDynamicPush(CodeStream &os, const Type::ResolvedType &type, const std::string &name,
+                                         VarLocation loc, const std::string &countVarName) const
+{
+    if(loc & VarLocationAttribute::HOST) {
+        if(type.isPointer()) {
+            os << "CHECK_RUNTIME_ERRORS(cudaMemcpy(*$(_d_" << name << "), *$(_" << name << "), ";
+            os << countVarName << " * sizeof(" << type.getPointer().valueType->getName() << "), cudaMemcpyHostToDevice));" << std::endl;
+        }
+        else {
+            os << "CHECK_RUNTIME_ERRORS(cudaMemcpy($(_d_" << name << "), $(_" << name << "), ";
+            os << countVarName << " * sizeof(" << type.getName() << "), cudaMemcpyHostToDevice));" << std::endl;
+        }
+    }
+}
+
+void Backend::genLazyVariableDynamicPull(CodeStream &os, const Type::ResolvedType &type, const std::string &name,
+                                         VarLocation loc, const std::string &countVarName) const
+{
+    if(loc & VarLocationAttribute::HOST) {
+        if(type.isPointer()) {
+            os << "CHECK_RUNTIME_ERRORS(cudaMemcpy(*$(_" << name << "), *$(_d_" << name << "), ";
+            os << countVarName << " * sizeof(" << type.getPointer().valueType->getName() << "), cudaMemcpyDeviceToHost));" << std::endl;
+        }
+        else {
+            os << "CHECK_RUNTIME_ERRORS(cudaMemcpy($(_" << name << "), $(_d_" << name << "), ";
+            os << countVarName << " * sizeof(" << type.getName() << "), cudaMemcpyDeviceToHost));" << std::endl;
+        }
+    }
+}
+
+void Backend::genMergedDynamicVariablePush(CodeStream &os, const std::string &suffix, size_t mergedGroupIdx,
+                                           const std::string &groupIdx, const std::string &fieldName,
+                                           const std::string &egpName) const
+{
+    const std::string structName = "Merged" + suffix + "Group" + std::to_string(mergedGroupIdx);
+    os << "CHECK_RUNTIME_ERRORS(cudaMemcpyToSymbolAsync(d_merged" << suffix << "Group" << mergedGroupIdx;
+    os << ", &" << egpName << ", sizeof(" << egpName << ")";
+    os << ", (sizeof(" << structName << ") * (" << groupIdx << ")) + offsetof(" << structName << ", " << fieldName << ")";
+    os << ", cudaMemcpyHostToDevice, 0));" << std::endl;
+}
+
+std::string Backend::getAtomicOperation(const std::string &lhsPointer, const std::string &rhsValue,
+                                        const Type::ResolvedType &type, AtomicOperation op) const
+{
+    if(op == AtomicOperation::ADD) {
+        return "atomicAdd(" + lhsPointer + ", " + rhsValue + ")";
+    }
+    else {
+        assert(op == AtomicOperation::OR);
+        assert(type == Type::Uint32 || type == Type::Int32);
+        return "atomicOr(" + lhsPointer + ", " + rhsValue + ")";
+    }
+}
+
+void Backend::genGlobalDeviceRNG(CodeStream&, CodeStream&, CodeStream&, CodeStream&) const
+{
+    // no global generator object: every thread derives its Philox stream from the model seed
+}
+
+void Backend::genTimer(CodeStream &definitions, CodeStream &runner, CodeStream &allocations, CodeStream &free,
+                       CodeStream&, const std::string &name, bool) const
+{
+    definitions << "extern cudaEvent_t " << name << "Start;" << std::endl;
+    definitions << "extern cudaEvent_t " << name << "Stop;" << std::endl;
+    runner << "cudaEvent_t " << name << "Start;" << std::endl;
+    runner << "cudaEvent_t " << name << "Stop;" << std::endl;
+    allocations << "CHECK_RUNTIME_ERRORS(cudaEventCreate(&" << name << "Start));" << std::endl;
+    allocations << "CHECK_RUNTIME_ERRORS(cudaEventCreate(&" << name << "Stop));" << std::endl;
+    free << "CHECK_RUNTIME_ERRORS(cudaEventDestroy(" << name << "Start));" << std::endl;
+    free << "CHECK_RUNTIME_ERRORS(cudaEventDestroy(" << name << "Stop));" << std::endl;
+}
+
+void Backend::genReturnFreeDeviceMemoryBytes(CodeStream &os) const
+{
+    os << "size_t free; size_t total;" << std::endl;
+    os << "CHECK_RUNTIME_ERRORS(cudaMemGetInfo(&free, &total));" << std::endl;
+    os << "return free;" << std::endl;
+}
+
+void Backend::genAssert(CodeStream &os, const std::string &condition) const
+{
+    os << "assert(" << condition << ");" << std::endl;
+}
+
+//--------------------------------------------------------------------------
+// Build rules: every module is CUDA, compiled for sm_100a only
+//--------------------------------------------------------------------------
+void Backend::genMakefilePreamble(std::ostream &os) const
+{
+    const auto &p = getPreferences<Preferences>();
+    std::string flags = "-gencode arch=compute_100a,code=sm_100a -std=c++17 -x cu -rdc=false -Xcompiler -fPIC -lineinfo";
+    flags += " -diag-suppress 177,550 -I\"" + includeDirectory() + "\"";
+    flags += p.debugCode ? " -O0 -g -G" : " -O3";
+    if(p.optimizeCode) {
+        flags += " -use_fast_math";
+    }
+    else {
+        // model arithmetic is compared with the CPU backend: no contraction into fused multiply-adds
+        flags += " -fmad=false";
+    }
+    flags += " " + p.userNvccFlagsGNU;
+    os << "NVCC := " << p.nvccPath << std::endl;
+    os << "NVCCFLAGS := " << flags << std::endl;
+    os << "LINKFLAGS := -gencode arch=compute_100a,code=sm_100a --shared -Xcompiler -fPIC" << std::endl;
+    os << std::endl;
+}
+
+void Backend::genMakefileLinkRule(std::ostream &os) const
+{
+    os << "\t@$(NVCC) $(LINKFLAGS) -o $@ $(OBJECTS)" << std::endl;
+}
+
+void Backend::genMakefileCompileRule(std::ostream &os) const
+{
+    os << "%.d: ;" << std::endl;
+    os << "%.o: %.cc %.d" << std::endl;
+    os << "\t@$(NVCC) -dc $(NVCCFLAGS) -o $@ $<" << std::endl;
+}
+
+void Backend::genNMakefilePreamble(std::ostream&) const { assert(false); }
+void Backend::genNMakefileLinkRule(std::ostream&) const { assert(false); }
+void Backend::genNMakefileCompileRule(std::ostream&) const { assert(false); }
+void Backend::genMSBuildConfigProperties(std::ostream&) const { assert(false); }
+void Backend::genMSBuildImportProps(std::ostream&) const { assert(false); }
+void Backend::genMSBuildItemDefinitions(std::ostream&) const { assert(false); }
+void Backend::genMSBuildCompileModule(const std::string&, std::ostream&) const { assert(false); }
+void Backend::genMSBuildImportTarget(std::ostream&) const { assert(false); }
+
+bool Backend::isGlobalHostRNGRequired(const ModelSpecInternal &model) const
+{
+    // host-side connectivity initialisation snippets draw from the host generator
+    return std::any_of(model.getSynapseGroups().cbegin(), model.getSynapseGroups().cend(),
+                       [](const ModelSpec::SynapseGroupValueType &s)
+                       {
+                           return s.second.getSparseConnectivityInitialiser().isHostRNGRequired();
+                       });
+}
+
+bool Backend::isGlobalDeviceRNGRequired(const ModelSpecInternal&) const
+{
+    return false;
+}
+
+size_t Backend::getDeviceMemoryBytes() const
+{
+    size_t free = 0, total = 0;
+    if(cudaMemGetInfo(&free, &total) != cudaSuccess) {
+        return 0;
+    }
+    return total;
+}
+
+Backend::MemorySpaces Backend::getMergedGroupMemorySpaces(const ModelSpecMerged&) const
+{
+    // merged-group arrays live in __device__ memory (L2-resident and read through the
+    // read-only path); there is no small memory space to ration
+    return {};
+}
+
+boost::uuids::detail::sha1::digest_type Backend::getHashDigest() const
+{
+    boost::uuids::detail::sha1 hash;
+    Utils::updateHash("B200", hash);
+    getPreferences<Preferences>().updateHash(hash);
+    return hash.get_digest();
+}
+
+//--------------------------------------------------------------------------
+// Neuron update
+//--------------------------------------------------------------------------
+void Backend::genNeuronUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerged &modelMerged,
+                              BackendBase::MemorySpaces &memorySpaces, HostHandler preambleHandler) const
+{
+    const ModelSpecInternal &model = modelMerged.getModel();
+    const unsigned int batchSize = model.getBatchSize();
+    const size_t block = blockSize();
+    const std::string timeType = model.getTimePrecision().getName();
+    const std::string dtLiteral = Type::writeNumeric(model.getDT(), model.getTimePrecision());
+    const std::string kernelArgs = timeType + " t, unsigned int recordingTimestep, unsigned long long b200Step, unsigned long long b200Seed";
+
+    std::ostringstream kernelStream;
+    CodeStream kernels(kernelStream);
+    std::vector<KernelLaunch> prevLaunches, queueLaunches, neuronLaunches;
+
+    EnvironmentLibrary backendEnv(kernels, backendFunctions);
+    EnvironmentLibrary mathsEnv(backendEnv, StandardLibrary::getMathsFunctions());
+    EnvironmentLibrary kernelLibEnv(mathsEnv, randomFunctions(model.getPrecision()));
+
+    // opens a kernel: signature, the names every group emitter expects, the thread's group
+    auto beginKernel = [&](EnvironmentExternal &env, const std::string &structName, const std::string &arrayName,
+                           const std::string &startName, size_t numGroups)
+    {
+        env.getStream() << "const unsigned int batch = blockIdx.y;" << std::endl;
+        env.add(model.getTimePrecision().addConst(), "t", "t");
+        env.add(Type::Uint32.addConst(), "batch", "batch");
+        env.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
+        genFindGroup(env.getStream(), structName, arrayName, startName, numGroups);
+        env.add(Type::Uint32.addConst(), "id", "b200Local");
+    };
+
+    // ---- previous spike times: one thread per neuron, set prevST of last step's spikes -----------------
+    modelMerged.genMergedNeuronPrevSpikeTimeUpdateGroups(
+        *this, memorySpaces,
+        [&](auto &n)
+        {
+            const std::string idx = std::to_string(n.getIndex());
+            KernelLaunch launch;
+            launch.name = "neuronPrevSpikeTimeUpdateKernel" + idx;
+            launch.batched = true;
+            launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedNeuronPrevSpikeTimeUpdateGroupStartID" + idx, n, block,
+                                            [](const NeuronGroupInternal &ng){ return ng.getNumNeurons(); });
+            kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
+            {
+                CodeStream::Scope b(kernelLibEnv.getStream());
+                EnvironmentExternal kernelEnv(kernelLibEnv);
+                beginKernel(kernelEnv, "MergedNeuronPrevSpikeTimeUpdateGroup" + idx, "d_mergedNeuronPrevSpikeTimeUpdateGroup" + idx,
+                            "d_mergedNeuronPrevSpikeTimeUpdateGroupStartID" + idx, n.getGroups().size());
+                EnvironmentGroupMergedField<NeuronPrevSpikeTimeUpdateGroupMerged> groupEnv(kernelEnv, n);
+                buildStandardEnvironment(groupEnv, batchSize);
+                if(n.getArchetype().isDelayRequired()) {
+                    // the queue pointer still points at the slot written last step
+                    if(batchSize == 1) {
+                        groupEnv.printLine("const unsigned int lastTimestepDelaySlot = *$(_spk_que_ptr);");
+                    }
+                    else {
+                        groupEnv.printLine("const unsigned int lastTimestepDelaySlot = *$(_spk_que_ptr) + ($(batch) * " + std::to_string(n.getArchetype().getNumDelaySlots()) + ");");
+                    }
+                    groupEnv.printLine("const unsigned int lastTimestepDelayOffset = lastTimestepDelaySlot * $(num_neurons);");
+                }
+                auto genUpdate = [&](EnvironmentExternalBase &env, bool trueSpike)
+                {
+                    const std::string suffix = trueSpike ? "" : "_event";
+                    const std::string time = trueSpike ? "st" : "set";
+                    const bool delay = trueSpike ? n.getArchetype().isSpikeDelayRequired() : n.getArchetype().isSpikeEventDelayRequired();
+                    if(delay) {
+                        env.print("if($(id) < $(_spk_cnt" + suffix + ")[lastTimestepDelaySlot])");
+                        {
+                            CodeStream::Scope b(env.getStream());
+                            env.printLine("$(_prev_" + time + ")[lastTimestepDelayOffset + $(_spk" + suffix + ")[lastTimestepDelayOffset + $(id)]] = $(t) - $(dt);");
+                        }
+                    }
+                    else {
+                        env.print("if($(id) < $(_spk_cnt" + suffix + ")[$(batch)])");
+                        {
+                            CodeStream::Scope b(env.getStream());
+                            if(batchSize == 1) {
+                                env.printLine("$(_prev_" + time + ")[$(_spk" + suffix + ")[$(id)]] = $(t) - $(dt);");
+                            }
+                            else {
+                                env.printLine("$(_prev_" + time + ")[$(_batch_offset) + $(_spk" + suffix + ")[$(_batch_offset) + $(id)]] = $(t) - $(dt);");
+                            }
+                        }
+                    }
+                };
+                if(n.getArchetype().isPrevSpikeTimeRequired()) {
+                    n.generateSpikes(groupEnv, [&](EnvironmentExternalBase &env){ genUpdate(env, true); });
+                }
+                if(n.getArchetype().isPrevSpikeEventTimeRequired()) {
+                    n.generateSpikeEvents(groupEnv, [&](EnvironmentExternalBase &env){ genUpdate(env, false); });
+                }
+            }
+            prevLaunches.push_back(launch);
+        });
+
+    // ---- spike queue update: one thread per group advances the queue pointer and clears the counts ----
+    modelMerged.genMergedNeuronSpikeQueueUpdateGroups(
+        *this, memorySpaces,
+        [&](auto &n)
+        {
+            const std::string idx = std::to_string(n.getIndex());
+            KernelLaunch launch;
+            launch.name = "neuronSpikeQueueUpdateKernel" + idx;
+            launch.numThreads = padTo(n.getGroups().size(), 32);
+            kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "()";
+            {
+                CodeStream::Scope b(kernelLibEnv.getStream());
+                kernelLibEnv.getStream() << "const unsigned int b200Thread = (blockIdx.x * blockDim.x) + threadIdx.x;" << std::endl;
+                kernelLibEnv.getStream() << "if(b200Thread < " << n.getGroups().size() << ")";
+                {
+                    CodeStream::Scope b(kernelLibEnv.getStream());
+                    EnvironmentExternal kernelEnv(kernelLibEnv);
+                    kernelEnv.getStream() << "const MergedNeuronSpikeQueueUpdateGroup" << idx << " *group = &d_mergedNeuronSpikeQueueUpdateGroup" << idx << "[b200Thread];" << std::endl;
+                    EnvironmentGroupMergedField<NeuronSpikeQueueUpdateGroupMerged> groupEnv(kernelEnv, n);
+                    buildStandardEnvironment(groupEnv, batchSize);
+                    n.genSpikeQueueUpdate(groupEnv, batchSize);
+                }
+            }
+            queueLaunches.push_back(launch);
+        });
+
+    // ---- neuron update ------------------------------------------------------------------------------------------
+    modelMerged.genMergedNeuronUpdateGroups(
+        *this, memorySpaces,
+        [&](auto &n)
+        {
+            const std::string idx = std::to_string(n.getIndex());
+            KernelLaunch launch;
+            launch.name = "updateNeuronsKernel" + idx;
+            launch.batched = true;
+            launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedNeuronUpdateGroupStartID" + idx, n, block,
+                                            [](const NeuronGroupInternal &ng){ return ng.getNumNeurons(); });
+            const size_t numEventGroups = n.getMergedSpikeEventGroups().size();
+            kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
+            {
+                CodeStream::Scope b(kernelLibEnv.getStream());
+                EnvironmentExternal kernelEnv(kernelLibEnv);
+                beginKernel(kernelEnv, "MergedNeuronUpdateGroup" + idx, "d_mergedNeuronUpdateGroup" + idx,
+                            "d_mergedNeuronUpdateGroupStartID" + idx, n.getGroups().size());
+                EnvironmentGroupMergedField<NeuronUpdateGroupMerged> groupEnv(kernelEnv, n);
+                buildStandardEnvironment(groupEnv, batchSize);
+
+                // whether this thread's neuron emitted a spike / each kind of spike-like event this step
+                groupEnv.getStream() << "bool b200Spiked = false;" << std::endl;
+                for(size_t e = 0; e < numEventGroups; e++) {
+                    groupEnv.getStream() << "bool b200Event" << e << " = false;" << std::endl;
+                }
+                groupEnv.print("if($(id) < $(num_neurons))");
+                {
+                    CodeStream::Scope b(groupEnv.getStream());
+                    EnvironmentGroupMergedField<NeuronUpdateGroupMerged> validEnv(groupEnv, n);
+                    // stateless Philox stream of (group, neuron, batch element, time step); only created if the model draws
+                    validEnv.add(Type::Void, "_rng", "b200Rng",
+                                 {validEnv.addInitialiser("b200gen::Rng b200Rng = b200gen::simRng(b200Seed, " + std::to_string(STREAM_NEURON + n.getIndex()) +
+                                                          "u + (b200Group << 20), $(id), $(batch), b200Step);")});
+                    n.generateNeuronUpdate(
+                        validEnv, batchSize,
+                        // true spike: flag it; everything tied to the spiking neuron's state happens here
+                        [&n, batchSize](EnvironmentExternalBase &env)
+                        {
+                            env.printLine("b200Spiked = true;");
+                            n.generateWUVarUpdate(env, batchSize);
+                            if(n.getArchetype().isSpikeTimeRequired()) {
+                                env.printLine("$(_st)[" + n.getWriteVarIndex(n.getArchetype().isSpikeDelayRequired(), batchSize,
+                                                                            VarAccessDim::BATCH | VarAccessDim::ELEMENT, "$(id)") + "] = $(t);");
+                            }
+                        },
+                        // spike-like event
+                        [&n, batchSize](EnvironmentExternalBase &env, NeuronUpdateGroupMerged::SynSpikeEvent &sg)
+                        {
+                            env.printLine("b200Event" + std::to_string(sg.getIndex()) + " = true;");
+                            if(n.getArchetype().isSpikeEventTimeRequired()) {
+                                env.printLine("$(_set)[" + n.getWriteVarIndex(n.getArchetype().isSpikeEventDelayRequired(), batchSize,
+                                                                             VarAccessDim::BATCH | VarAccessDim::ELEMENT, "$(id)") + "] = $(t);");
+                            }
+                        });
+                }
+
+                // all lanes of the warp are back together: compact the warp's events into the lists
+                // (one atomic per warp that has any; ids ascend within a warp)
+                auto genCompaction = [&](EnvironmentExternalBase &env, const std::string &flag, bool trueSpike)
+                {
+                    const std::string suffix = trueSpike ? "" : "_event";
+                    const bool delay = trueSpike ? n.getArchetype().isSpikeDelayRequired() : n.getArchetype().isSpikeEventDelayRequired();
+                    std::string countIndex;
+                    if(delay) {
+                        countIndex = "*$(_spk_que_ptr)";
+                        if(batchSize > 1) {
+                            countIndex += " + ($(batch) * " + std::to_string(n.getArchetype().getNumDelaySlots()) + ")";
+                        }
+                    }
+                    else {
+                        countIndex = "$(batch)";
+                    }
+                    const std::string listOffset = n.getWriteVarIndex(delay, batchSize, VarAccessDim::BATCH | VarAccessDim::ELEMENT, "");
+                    env.printLine("b200gen::emitEvents(" + flag + ", $(id), &$(_spk_cnt" + suffix + ")[" + countIndex + "], &$(_spk" + suffix + ")[" + listOffset + "0]);");
+                };
+                const bool emitsSpikes = n.getArchetype().isTrueSpikeRequired() || !n.getMergedSpikeGroups().empty();
+                if(emitsSpikes) {
+                    n.generateSpikes(groupEnv, [&](EnvironmentExternalBase &env){ genCompaction(env, "b200Spiked", true); });
+                }
+                n.generateSpikeEvents(groupEnv,
+                                      [&](EnvironmentExternalBase &env, NeuronUpdateGroupMerged::SynSpikeEvent &sg)
+                                      {
+                                          genCompaction(env, "b200Event" + std::to_string(sg.getIndex()), false);
+                                      });
+
+                // recording: a warp covers exactly one 32-neuron word (groups start on block boundaries)
+                if(n.getArchetype().isSpikeRecordingEnabled() || n.getArchetype().isSpikeEventRecordingEnabled()) {
+                    groupEnv.printLine("const unsigned int numRecordingWords = ($(num_neurons) + 31) / 32;");
+                    std::string globalIndex = "(recordingTimestep * numRecordingWords * " + std::to_string(batchSize) + ") + ($(id) / 32)";
+                    if(batchSize > 1) {
+                        globalIndex += " + ($(batch) * numRecordingWords)";
+                    }
+                    if(n.getArchetype().isSpikeRecordingEnabled()) {
+                        groupEnv.printLine("b200gen::recordEvents(b200Spiked, $(id), numRecordingWords, &$(_record_spk)[" + globalIndex + "]);");
+                    }
+                    if(n.getArchetype().isSpikeEventRecordingEnabled()) {
+                        n.generateSpikeEvents(groupEnv,
+                                              [&](EnvironmentExternalBase &env, NeuronUpdateGroupMerged::SynSpikeEvent &sg)
+                                              {
+                                                  env.printLine("b200gen::recordEvents(b200Event" + std::to_string(sg.getIndex()) + ", $(id), numRecordingWords, &$(_record_spk_event)[" + globalIndex + "]);");
+                                              });
+                    }
+                }
+            }
+            neuronLaunches.push_back(launch);
+        });
+
+    // ---- file: structs, device arrays + push functions, dynamic-field pushes, kernels, host function ----
+    modelMerged.genMergedNeuronUpdateGroupStructs(os, *this);
+    modelMerged.genMergedNeuronSpikeQueueUpdateStructs(os, *this);
+    modelMerged.genMergedNeuronPrevSpikeTimeUpdateStructs(os, *this);
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedNeuronUpdateGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedNeuronSpikeQueueUpdateGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedNeuronPrevSpikeTimeUpdateGroups());
+    preambleHandler(os);
+    os << kernelStream.str();
+
+    os << "void updateNeurons(" << timeType << " t";
+    if(model.isRecordingInUse()) {
+        os << ", unsigned int recordingTimestep";
+    }
+    os << ")";
+    {
+        CodeStream::Scope b(os);
+        if(!model.isRecordingInUse()) {
+            os << "const unsigned int recordingTimestep = 0;" << std::endl;
+        }
+        os << "const unsigned long long b200Step = (unsigned long long)llround((double)t / " << Type::writeNumeric(model.getDT(), Type::Double) << ");" << std::endl;
+        const std::string args = "t, recordingTimestep, b200Step, b200Seed";
+        for(const auto &k : prevLaunches) {
+            genLaunch(os, k, block, batchSize, args);
+        }
+        for(const auto &k : queueLaunches) {
+            genLaunch(os, k, 32, 1, "");
+        }
+        genKernelTimerStart(os, "neuronUpdate", model.isTimingEnabled());
+        for(const auto &k : neuronLaunches) {
+            genLaunch(os, k, block, batchSize, args);
+        }
+        genKernelTimerStop(os, "neuronUpdate", model.isTimingEnabled(), true);
+    }
+}
+
+//--------------------------------------------------------------------------
+// Synapse update
+//--------------------------------------------------------------------------
+namespace
+{
+constexpr unsigned int SPIKE_LANES = 8;     // gridDim.z: a group's spike list is dealt to this many blocks per column block
+
+//! Environment entries a presynaptic / synapse-dynamics body needs to deposit its output: fire-and-forget
+//! fp32 additions (they compile to reductions; nothing reads the old value)
+template<typename G>
+void addOutputFunctions(EnvironmentGroupMergedField<G> &env, G &sg, unsigned int batchSize)
+{
+    env.add(Type::getAddToPrePostDelay(sg.getScalarType()), "addToPostDelay",
+            "atomicAdd(&$(_den_delay)[" + sg.getPostDenDelayIndex(batchSize, "$(id_post)", "$(1)") + "], $(0))");
+    env.add(Type::getAddToPrePost(sg.getScalarType()), "addToPost",
+            "atomicAdd(&$(_out_post)[" + sg.getPostISynIndex(batchSize, "$(id_post)") + "], $(0))");
+    env.add(Type::getAddToPrePost(sg.getScalarType()), "addToPre",
+            "atomicAdd(&$(_out_pre)[" + sg.getPreISynIndex(batchSize, "$(id_pre)") + "], $(0))");
+}
+}   // anonymous namespace
+
+void Backend::genSynapseUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerged &modelMerged,
+                               BackendBase::MemorySpaces &memorySpaces, HostHandler preambleHandler) const
+{
+    const ModelSpecInternal &model = modelMerged.getModel();
+    const unsigned int batchSize = model.getBatchSize();
+    const size_t block = blockSize();
+    const std::string timeType = model.getTimePrecision().getName();
+    const std::string dtLiteral = Type::writeNumeric(model.getDT(), model.getTimePrecision());
+    const std::string kernelArgs = timeType + " t, unsigned long long b200Step, unsigned long long b200Seed";
+
+    std::ostringstream kernelStream;
+    CodeStream kernels(kernelStream);
+    std::vector<KernelLaunch> delayLaunches, dynamicsLaunches, preLaunches, postLaunches;
+
+    EnvironmentLibrary backendEnv(kernels, backendFunctions);
+    EnvironmentLibrary mathsEnv(backendEnv, StandardLibrary::getMathsFunctions());
+    EnvironmentLibrary kernelLibEnv(mathsEnv, randomFunctions(model.getPrecision()));
+
+    auto beginKernel = [&](EnvironmentExternal &env, const std::string &structName, const std::string &arrayName,
+                           const std::string &startName, size_t numGroups)
+    {
+        env.getStream() << "const unsigned int batch = blockIdx.y;" << std::endl;
+        env.add(model.getTimePrecision().addConst(), "t", "t");
+        env.add(Type::Uint32.addConst(), "batch", "batch");
+        env.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
+        genFindGroup(env.getStream(), structName, arrayName, startName, numGroups);
+        env.add(Type::Uint32.addConst(), "id", "b200Local");
+    };
+    auto rngInitialiser = [](unsigned int stream, size_t index)
+    {
+        return "b200gen::Rng b200Rng = b200gen::simRng(b200Seed, " + std::to_string(stream + index) + "u + (b200Group << 20), b200Thread, $(batch), b200Step);";
+    };
+
+    // ---- dendritic delay pointers: one thread per group -------------------------------------------------------
+    modelMerged.genMergedSynapseDendriticDelayUpdateGroups(
+        *this, memorySpaces,
+        [&](auto &sg)
+        {
+            const std::string idx = std::to_string(sg.getIndex());
+            KernelLaunch launch;
+            launch.name = "synapseDendriticDelayUpdateKernel" + idx;
+            launch.numThreads = padTo(sg.getGroups().size(), 32);
+            kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "()";
+            {
+                CodeStream::Scope b(kernelLibEnv.getStream());
+                kernelLibEnv.getStream() << "const unsigned int b200Thread = (blockIdx.x * blockDim.x) + threadIdx.x;" << std::endl;
+                kernelLibEnv.getStream() << "if(b200Thread < " << sg.getGroups().size() << ")";
+                {
+                    CodeStream::Scope b(kernelLibEnv.getStream());
+                    EnvironmentExternal kernelEnv(kernelLibEnv);
+                    kernelEnv.getStream() << "const MergedSynapseDendriticDelayUpdateGroup" << idx << " *group = &d_mergedSynapseDendriticDelayUpdateGroup" << idx << "[b200Thread];" << std::endl;
+                    EnvironmentGroupMergedField<SynapseDendriticDelayUpdateGroupMerged> groupEnv(kernelEnv, sg);
+                    buildStandardEnvironment(groupEnv, batchSize);
+                    sg.generateSynapseUpdate(groupEnv);
+                }
+            }
+            delayLaunches.push_back(launch);
+        });
+
+    // ---- synapse dynamics: one thread per synapse slot --------------------------------------------------------
+    modelMerged.genMergedSynapseDynamicsGroups(
+        *this, memorySpaces,
+        [&](auto &sg)
+        {
+            const std::string idx = std::to_string(sg.getIndex());
+            KernelLaunch launch;
+            launch.name = "updateSynapseDynamicsKernel" + idx;
+            launch.batched = true;
+            launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedSynapseDynamicsGroupStartID" + idx, sg, block,
+                                            [this](const SynapseGroupInternal &g)
+                                            {
+                                                return (size_t)g.getSrcNeuronGroup()->getNumNeurons() * getSynapticMatrixRowStride(g);
+                                            });
+            kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
+            {
+                CodeStream::Scope b(kernelLibEnv.getStream());
+                EnvironmentExternal kernelEnv(kernelLibEnv);
+                beginKernel(kernelEnv, "MergedSynapseDynamicsGroup" + idx, "d_mergedSynapseDynamicsGroup" + idx,
+                            "d_mergedSynapseDynamicsGroupStartID" + idx, sg.getGroups().size());
+                EnvironmentGroupMergedField<SynapseDynamicsGroupMerged> groupEnv(kernelEnv, sg);
+                buildStandardEnvironment(groupEnv, batchSize);
+                const bool sparse = (sg.getArchetype().getMatrixType() & SynapseMatrixConnectivity::SPARSE);
+                if(!sparse && !(sg.getArchetype().getMatrixType() & SynapseMatrixConnectivity::DENSE)) {
+                    throw std::runtime_error("B200 backend: synapse dynamics need SPARSE or DENSE connectivity");
+                }
+                groupEnv.print("if($(id) < ($(num_pre) * $(_row_stride)))");
+                {
+                    CodeStream::Scope b(groupEnv.getStream());
+                    EnvironmentGroupMergedField<SynapseDynamicsGroupMerged> synEnv(groupEnv, sg);
+                    synEnv.add(Type::Void, "_rng", "b200Rng", {synEnv.addInitialiser(rngInitialiser(STREAM_DYNAMICS, sg.getIndex()))});
+                    synEnv.printLine("const unsigned int b200Row = $(id) / $(_row_stride);");
+                    synEnv.printLine("const unsigned int b200Col = $(id) - (b200Row * $(_row_stride));");
+                    synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Row");
+                    synEnv.add(Type::Uint32.addConst(), "id_syn", "$(id)");
+                    if(sparse) {
+                        synEnv.add(Type::Uint32.addConst(), "id_post", "$(_ind)[$(id)]");
+                        synEnv.print("if(b200Col < $(_row_length)[b200Row])");
+                    }
+                    else {
+                        synEnv.add(Type::Uint32.addConst(), "id_post", "b200Col");
+                    }
+                    {
+                        CodeStream::Scope b(synEnv.getStream());
+                        EnvironmentGroupMergedField<SynapseDynamicsGroupMerged> bodyEnv(synEnv, sg);
+                        addOutputFunctions(bodyEnv, sg, batchSize);
+                        sg.generateSynapseUpdate(*this, bodyEnv, batchSize, model.getDT());
+                    }
+                }
+            }
+            dynamicsLaunches.push_back(launch);
+        });
+
+    // ---- presynaptic update --------------------------------------------------------------------------------------------
+    // A block column covers `block` synapses of a row (SPARSE: positions in the ragged row; DENSE / BITMASK:
+    // target neurons); blockIdx.z = lane l takes spikes l, l + SPIKE_LANES, ...: the parallel width is
+    // SPIKE_LANES x row stride, and each thread reads its synapse of every row it visits coalesced.
+    modelMerged.genMergedPresynapticUpdateGroups(
+        *this, memorySpaces,
+        [&](auto &sg)
+        {
+            const std::string idx = std::to_string(sg.getIndex());
+            const auto matrixType = sg.getArchetype().getMatrixType();
+            if((matrixType & SynapseMatrixConnectivity::PROCEDURAL) || (matrixType & SynapseMatrixConnectivity::TOEPLITZ)) {
+                throw std::runtime_error("B200 backend: PROCEDURAL and TOEPLITZ connectivity are not generated yet (synapse group '"
+                                         + sg.getArchetype().getName() + "')");
+            }
+            const bool sparse = (matrixType & SynapseMatrixConnectivity::SPARSE);
+            const bool bitmask = (matrixType & SynapseMatrixConnectivity::BITMASK);
+            KernelLaunch launch;
+            launch.name = "updatePresynapticKernel" + idx;
+            launch.batched = true;
+            launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedPresynapticUpdateGroupStartID" + idx, sg, block,
+                                            [this](const SynapseGroupInternal &g){ return getSynapticMatrixRowStride(g); });
+            kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
+            {
+                CodeStream::Scope b(kernelLibEnv.getStream());
+                EnvironmentExternal kernelEnv(kernelLibEnv);
+                beginKernel(kernelEnv, "MergedPresynapticUpdateGroup" + idx, "d_mergedPresynapticUpdateGroup" + idx,
+                            "d_mergedPresynapticUpdateGroupStartID" + idx, sg.getGroups().size());
+                EnvironmentGroupMergedField<PresynapticUpdateGroupMerged> groupEnv(kernelEnv, sg);
+                buildStandardEnvironment(groupEnv, batchSize);
+                groupEnv.add(Type::Void, "_rng", "b200Rng", {groupEnv.addInitialiser(rngInitialiser(STREAM_PRESYNAPTIC, sg.getIndex()))});
+
+                auto genEvents = [&](bool trueSpike)
+                {
+                    const std::string eventSuffix = trueSpike ? "" : "_event";
+                    const bool delay = trueSpike ? sg.getArchetype().getSrcNeuronGroup()->isSpikeQueueRequired()
+                                                 : sg.getArchetype().getSrcNeuronGroup()->isSpikeEventQueueRequired();
+                    CodeStream::Scope b(groupEnv.getStream());
+                    groupEnv.printLine("const unsigned int b200NumSpikes = $(_src_spk_cnt" + eventSuffix + ")[" + sg.getPreSlot(delay, batchSize) + "];");
+                    groupEnv.print("if($(id) < $(_row_stride))");
+                    {
+                        CodeStream::Scope b(groupEnv.getStream());
+                        groupEnv.getStream() << "for(unsigned int b200Spike = blockIdx.z; b200Spike < b200NumSpikes; b200Spike += gridDim.z)";
+                        {
+                            CodeStream::Scope b(groupEnv.getStream());
+                            EnvironmentGroupMergedField<PresynapticUpdateGroupMerged> synEnv(groupEnv, sg);
+                            synEnv.printLine("const unsigned int b200Pre = $(_src_spk" + eventSuffix + ")["
+                                             + sg.getPreVarIndex(delay, batchSize, VarAccessDim::BATCH | VarAccessDim::ELEMENT, "b200Spike") + "];");
+                            synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre");
+                            const auto indexType = getSynapseIndexType(sg);
+                            const std::string indexTypeName = indexType.getName();
+                            synEnv.add(indexType.addConst(), "id_syn", "b200Syn",
+                                       {synEnv.addInitialiser("const " + indexTypeName + " b200Syn = ((" + indexTypeName + ")b200Pre * $(_row_stride)) + $(id);")});
+                            if(sparse) {
+                                synEnv.print("if($(id) < $(_row_length)[b200Pre])");
+                                synEnv.add(Type::Uint32.addConst(), "id_post", "b200Post",
+                                           {synEnv.addInitialiser("const unsigned int b200Post = $(_ind)[$(id_syn)];")});
+                            }
+                            else if(bitmask) {
+                                synEnv.printLine("const " + indexTypeName + " b200Gid = ((" + indexTypeName + ")b200Pre * $(_row_stride)) + $(id);");
+                                synEnv.print("if(($(id) < $(num_post)) && ($(_gp)[b200Gid / 32] & (0x80000000 >> (b200Gid & 31))))");
+                                synEnv.add(Type::Uint32.addConst(), "id_post", "$(id)");
+                            }
+                            else {
+                                synEnv.print("if($(id) < $(num_post))");
+                                synEnv.add(Type::Uint32.addConst(), "id_post", "$(id)");
+                            }
+                            {
+                                CodeStream::Scope b(synEnv.getStream());
+                                EnvironmentGroupMergedField<PresynapticUpdateGroupMerged> bodyEnv(synEnv, sg);
+                                addOutputFunctions(bodyEnv, sg, batchSize);
+                                if(trueSpike) {
+                                    sg.generateSpikeUpdate(*this, bodyEnv, batchSize, model.getDT());
+                                }
+                                else {
+                                    sg.generateSpikeEventUpdate(*this, bodyEnv, batchSize, model.getDT());
+                                }
+                            }
+                        }
+                    }
+                };
+                if(sg.getArchetype().isPreSpikeEventRequired()) {
+                    genEvents(false);
+                }
+                if(sg.getArchetype().isPreSpikeRequired()) {
+                    genEvents(true);
+                }
+            }
+            preLaunches.push_back(launch);
+        });
+
+    // ---- postsynaptic update: thread = position in the spiking target's column ---------------------------------
+    modelMerged.genMergedPostsynapticUpdateGroups(
+        *this, memorySpaces,
+        [&](auto &sg)
+        {
+            const std::string idx = std::to_string(sg.getIndex());
+            const bool sparse = (sg.getArchetype().getMatrixType() & SynapseMatrixConnectivity::SPARSE);
+            KernelLaunch launch;
+            launch.name = "updatePostsynapticKernel" + idx;
+            launch.batched = true;
+            launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedPostsynapticUpdateGroupStartID" + idx, sg, block,
+                                            [](const SynapseGroupInternal &g)
+                                            {
+                                                return (g.getMatrixType() & SynapseMatrixConnectivity::SPARSE)
+                                                    ? (size_t)g.getMaxSourceConnections() : (size_t)g.getSrcNeuronGroup()->getNumNeurons();
+                                            });
+            kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
+            {
+                CodeStream::Scope b(kernelLibEnv.getStream());
+                EnvironmentExternal kernelEnv(kernelLibEnv);
+                beginKernel(kernelEnv, "MergedPostsynapticUpdateGroup" + idx, "d_mergedPostsynapticUpdateGroup" + idx,
+                            "d_mergedPostsynapticUpdateGroupStartID" + idx, sg.getGroups().size());
+                EnvironmentGroupMergedField<PostsynapticUpdateGroupMerged> groupEnv(kernelEnv, sg);
+                buildStandardEnvironment(groupEnv, batchSize);
+                groupEnv.add(Type::Void, "_rng", "b200Rng", {groupEnv.addInitialiser(rngInitialiser(STREAM_POSTSYNAPTIC, sg.getIndex()))});
+
+                auto genEvents = [&](bool trueSpike)
+                {
+                    const std::string eventSuffix = trueSpike ? "" : "_event";
+                    const bool delay = trueSpike ? sg.getArchetype().getTrgNeuronGroup()->isSpikeQueueRequired()
+                                                 : sg.getArchetype().getTrgNeuronGroup()->isSpikeEventQueueRequired();
+                    CodeStream::Scope b(groupEnv.getStream());
+                    groupEnv.printLine("const unsigned int b200NumSpikes = $(_trg_spk_cnt" + eventSuffix + ")[" + sg.getPostSlot(delay, batchSize) + "];");
+                    groupEnv.print(sparse ? "if($(id) < $(_col_stride))" : "if($(id) < $(num_pre))");
+                    {
+                        CodeStream::Scope b(groupEnv.getStream());
+                        groupEnv.getStream() << "for(unsigned int b200Spike = blockIdx.z; b200Spike < b200NumSpikes; b200Spike += gridDim.z)";
+                        {
+                            CodeStream::Scope b(groupEnv.getStream());
+                            EnvironmentGroupMergedField<PostsynapticUpdateGroupMerged> synEnv(groupEnv, sg);
+                            synEnv.printLine("const unsigned int b200Post = $(_trg_spk" + eventSuffix + ")["
+                                             + sg.getPostVarIndex(delay, batchSize, VarAccessDim::BATCH | VarAccessDim::ELEMENT, "b200Spike") + "];");
+                            synEnv.add(Type::Uint32.addConst(), "id_post", "b200Post");
+                            if(sparse) {
+                                synEnv.print("if($(id) < $(_col_length)[b200Post])");
+                                synEnv.add(Type::Uint32.addConst(), "id_syn", "b200Syn",
+                                           {synEnv.addInitialiser("const unsigned int b200Syn = $(_remap)[(b200Post * $(_col_stride)) + $(id)];")});
+                                synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre",
+                                           {synEnv.addInitialiser("const unsigned int b200Pre = $(id_syn) / $(_row_stride);")});
+                            }
+                            else {
+                                synEnv.add(Type::Uint32.addConst(), "id_syn", "b200Syn",
+                                           {synEnv.addInitialiser("const unsigned int b200Syn = ($(id) * $(num_post)) + b200Post;")});
+                                synEnv.add(Type::Uint32.addConst(), "id_pre", "$(id)");
+                            }
+                            {
+                                CodeStream::Scope b(synEnv.getStream());
+                                EnvironmentGroupMergedField<PostsynapticUpdateGroupMerged> bodyEnv(synEnv, sg);
+                                bodyEnv.add(Type::getAddToPrePost(sg.getScalarType()), "addToPre",
+                                            "atomicAdd(&$(_out_pre)[" + sg.getPreISynIndex(batchSize, "$(id_pre)") + "], $(0))");
+                                if(trueSpike) {
+                                    sg.generateSpikeUpdate(*this, bodyEnv, batchSize, model.getDT());
+                                }
+                                else {
+                                    sg.generateSpikeEventUpdate(*this, bodyEnv, batchSize, model.getDT());
+                                }
+                            }
+                        }
+                    }
+                };
+                if(sg.getArchetype().isPostSpikeEventRequired()) {
+                    genEvents(false);
+                }
+                if(sg.getArchetype().isPostSpikeRequired()) {
+                    genEvents(true);
+                }
+            }
+            postLaunches.push_back(launch);
+        });
+
+    // ---- file -----------------------------------------------------------------------------------------------------------
+    modelMerged.genMergedSynapseDendriticDelayUpdateStructs(os, *this);
+    modelMerged.genMergedPresynapticUpdateGroupStructs(os, *this);
+    modelMerged.genMergedPostsynapticUpdateGroupStructs(os, *this);
+    modelMerged.genMergedSynapseDynamicsGroupStructs(os, *this);
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedSynapseDendriticDelayUpdateGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedPresynapticUpdateGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedPostsynapticUpdateGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedSynapseDynamicsGroups());
+    preambleHandler(os);
+    os << kernelStream.str();
+
+    auto genLaneLaunch = [&](const KernelLaunch &k)
+    {
+        if(k.numThreads == 0) {
+            return;
+        }
+        CodeStream::Scope b(os);
+        os << "const dim3 threads(" << block << ", 1, 1);" << std::endl;
+        os << "const dim3 grid(" << (k.numThreads / block) << ", " << batchSize << ", " << SPIKE_LANES << ");" << std::endl;
+        os << k.name << "<<<grid, threads>>>(t, b200Step, b200Seed);" << std::endl;
+        os << "CHECK_RUNTIME_ERRORS(cudaPeekAtLastError());" << std::endl;
+    };
+    os << "void updateSynapses(" << timeType << " t)";
+    {
+        CodeStream::Scope b(os);
+        os << "const unsigned long long b200Step = (unsigned long long)llround((double)t / " << Type::writeNumeric(model.getDT(), Type::Double) << ");" << std::endl;
+        for(const auto &k : delayLaunches) {
+            genLaunch(os, k, 32, 1, "");
+        }
+        if(!dynamicsLaunches.empty()) {
+            genKernelTimerStart(os, "synapseDynamics", model.isTimingEnabled());
+            for(const auto &k : dynamicsLaunches) {
+                genLaunch(os, k, block, batchSize, "t, b200Step, b200Seed");
+            }
+            genKernelTimerStop(os, "synapseDynamics", model.isTimingEnabled(), true);
+        }
+        if(!preLaunches.empty()) {
+            genKernelTimerStart(os, "presynapticUpdate", model.isTimingEnabled());
+            for(const auto &k : preLaunches) {
+                genLaneLaunch(k);
+            }
+            genKernelTimerStop(os, "presynapticUpdate", model.isTimingEnabled(), true);
+        }
+        if(!postLaunches.empty()) {
+            genKernelTimerStart(os, "postsynapticUpdate", model.isTimingEnabled());
+            for(const auto &k : postLaunches) {
+                genLaneLaunch(k);
+            }
+            genKernelTimerStop(os, "postsynapticUpdate", model.isTimingEnabled(), true);
+        }
+    }
+}

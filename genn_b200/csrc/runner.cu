@@ -229,22 +229,24 @@ struct b200_runner
     std::string tiledWhyNot;
     TiledTile *tiledTiles = nullptr;
     TiledSource *tiledSources = nullptr;
-    unsigned int *tiledRunStart = nullptr, *tiledCtaFirst = nullptr;
+    unsigned int *tiledRunStart = nullptr, *tiledCtaStart = nullptr, *tiledPairBatches = nullptr;
     void *tiledKeys = nullptr;
     float *tiledWeights = nullptr;
-    unsigned short *tiledItemTile = nullptr;
-    unsigned char *tiledItemShare = nullptr, *tiledServed = nullptr;
-    unsigned int tiledItemsPerBatch = 0, tiledNumSources = 0, tiledPostBits = 10, tiledGrid = 0;
+    TiledPair *tiledPairs = nullptr;
+    double *tiledPairPrefix = nullptr;
+    unsigned char *tiledServed = nullptr;
+    unsigned int tiledNumPairs = 0, tiledNumSources = 0, tiledPostBits = 10, tiledGrid = 0;
     size_t tiledSmemBytes = 0;
     unsigned long long tiledSynapses = 0;
 
     void dropTiled()
     {
-        void *bufs[] = {tiledTiles, tiledSources, tiledRunStart, tiledCtaFirst, tiledKeys, tiledWeights, tiledItemTile,
-                        tiledItemShare, tiledServed};
+        void *bufs[] = {tiledTiles, tiledSources, tiledRunStart, tiledCtaStart, tiledPairBatches, tiledKeys, tiledWeights,
+                        tiledPairs, tiledPairPrefix, tiledServed};
         for(void *b : bufs) if(b) cudaFree(b);
-        tiledTiles = nullptr; tiledSources = nullptr; tiledRunStart = nullptr; tiledCtaFirst = nullptr;
-        tiledKeys = nullptr; tiledWeights = nullptr; tiledItemTile = nullptr; tiledItemShare = nullptr; tiledServed = nullptr;
+        tiledTiles = nullptr; tiledSources = nullptr; tiledRunStart = nullptr; tiledCtaStart = nullptr;
+        tiledPairBatches = nullptr; tiledKeys = nullptr; tiledWeights = nullptr; tiledPairs = nullptr;
+        tiledPairPrefix = nullptr; tiledServed = nullptr;
         tiledReady = false;
     }
 
@@ -1229,6 +1231,9 @@ int buildTiled(b200_runner *r)
         anyWeights = anyWeights || (g.g != nullptr && g.wu_model != B200_WU_STATIC_PULSE_CONSTANT_WEIGHT);
     }
     if(targets.empty()) { r->tiledWhyNot = "no non-learning SPARSE group"; return B200_OK; }
+    for(const auto &t : targets) {
+        if(t.groups.size() > TILED_MAX_SOURCES) { r->tiledWhyNot = "too many synapse groups onto one target"; return B200_OK; }
+    }
     if(slots >= (1ull << 32)) { r->tiledWhyNot = "more than 2^32 synapse slots"; return B200_OK; }
     if(maxDepth > TILED_ACC_FLOATS || maxDepth > 4096u) { r->tiledWhyNot = "delay ring too deep for a shared-memory tile"; return B200_OK; }
     const bool key16 = (maxDepth <= 64u);
@@ -1302,75 +1307,46 @@ int buildTiled(b200_runner *r)
     CUDA_TRY(cudaMemsetAsync(count.p, 0, sizeof(unsigned int) * ((size_t)entries + 1), r->stream));
     if(const int e = launchBuild(1)) return e;
 
-    // ---- tiles, sources, work items -----------------------------------------------------------------
-    std::vector<TiledTile> tiles(numTiles);
-    std::vector<unsigned int> tileStart(numTiles + 1);
-    for(auto &t : targets) {
-        for(unsigned int i = 0; i < t.tiles; i++) {
-            TiledTile &T = tiles[t.firstTile + i];
-            T.target = t.ptr; T.num_trg = t.n; T.depth = t.depth; T.first_trg = i * t.stride;
-            T.num_tile = std::min(t.stride, t.n - i * t.stride); T.stride = t.stride;
-            T.first_source = t.firstSource; T.num_sources = (unsigned int)t.groups.size();
-            T.table = t.firstTable + i * t.rows;
-            CUDA_TRY(cudaMemcpyAsync(&tileStart[t.firstTile + i], runStart.as<unsigned int>() + T.table, sizeof(unsigned int),
-                                     cudaMemcpyDeviceToHost, r->stream));
-        }
-    }
-    // per source: synapses per source neuron, for the event estimate of a step
-    std::vector<unsigned int> sourceFirst(numSources + 1, 0);
+    // ---- tiles, sources and (tile, source) pairs -----------------------------------------------------
+    std::vector<unsigned int> hostRuns((size_t)entries + 1);
+    CUDA_TRY(cudaMemcpyAsync(hostRuns.data(), runStart.p, sizeof(unsigned int) * hostRuns.size(), cudaMemcpyDeviceToHost, r->stream));
     CUDA_TRY(cudaStreamSynchronize(r->stream));
-    tileStart[numTiles] = total;
+    std::vector<TiledTile> tiles(numTiles);
+    std::vector<TiledPair> pairs;
     {
-        // synapses of a group = sum over the tiles of its target of (run_start at its last row + 1 - run_start at its first row)
-        size_t si = 0;
+        size_t firstSource = 0;
         for(auto &t : targets) {
-            for(size_t gi : t.groups) {
-                const auto &g = sparse[gi];
-                unsigned long long syn = 0;
-                for(unsigned int i = 0; i < t.tiles; i++) {
-                    unsigned int ab[2];
-                    const unsigned int base = t.firstTable + i * t.rows + sources[si].row_base;
-                    CUDA_TRY(cudaMemcpy(&ab[0], runStart.as<unsigned int>() + base, sizeof(unsigned int), cudaMemcpyDeviceToHost));
-                    CUDA_TRY(cudaMemcpy(&ab[1], runStart.as<unsigned int>() + base + g.num_src, sizeof(unsigned int), cudaMemcpyDeviceToHost));
-                    syn += ab[1] - ab[0];
+            std::vector<unsigned long long> groupSynapses(t.groups.size(), 0);
+            for(unsigned int i = 0; i < t.tiles; i++) {
+                TiledTile &T = tiles[t.firstTile + i];
+                T.target = t.ptr; T.num_trg = t.n; T.depth = t.depth; T.first_trg = i * t.stride;
+                T.num_tile = std::min(t.stride, t.n - i * t.stride); T.stride = t.stride;
+                T.first_source = t.firstSource; T.num_sources = (unsigned int)t.groups.size();
+                T.table = t.firstTable + i * t.rows;
+                for(size_t si = 0; si < t.groups.size(); si++) {
+                    const auto &g = sparse[t.groups[si]];
+                    const size_t base = (size_t)T.table + sources[firstSource + si].row_base;
+                    const unsigned long long syn = hostRuns[base + g.num_src] - hostRuns[base];
+                    groupSynapses[si] += syn;
+                    if(syn) {
+                        pairs.push_back(TiledPair{(unsigned short)(t.firstTile + i), (unsigned short)si,
+                                                  (float)((double)syn / std::max(1u, g.num_src))});
+                    }
                 }
-                sources[si].mean_row = g.num_src ? (float)((double)syn / g.num_src) : 0.0f;
-                si++;
             }
+            // per source: synapses per source neuron, for the event estimate of a step
+            for(size_t si = 0; si < t.groups.size(); si++) {
+                const auto &g = sparse[t.groups[si]];
+                sources[firstSource + si].mean_row = g.num_src ? (float)((double)groupSynapses[si] / g.num_src) : 0.0f;
+            }
+            firstSource += t.groups.size();
         }
     }
-    std::vector<unsigned short> itemTile;
-    std::vector<unsigned char> itemShare;
-    std::vector<double> itemWeight;
-    for(unsigned int t = 0; t < numTiles; t++) {
-        const unsigned int syn = tileStart[t + 1] - tileStart[t];
-        if(!syn) continue;
-        for(unsigned int s = 0; s < TILED_SPLIT; s++) {
-            itemTile.push_back((unsigned short)t);
-            itemShare.push_back((unsigned char)s);
-            itemWeight.push_back((double)syn / TILED_SPLIT + 4096.0);      // + the fixed cost of an item
-        }
-    }
-    if(itemTile.empty()) { r->tiledWhyNot = "no synapses"; return B200_OK; }
+    if(pairs.empty()) { r->tiledWhyNot = "no synapses"; return B200_OK; }
+    if((unsigned long long)pairs.size() * r->batch >= (1ull << 31)) { r->tiledWhyNot = "too many (tile, source, batch) pairs"; return B200_OK; }
     cudaDeviceProp prop;
     CUDA_TRY(cudaGetDeviceProperties(&prop, r->device));
     const unsigned int grid = (unsigned int)prop.multiProcessorCount;
-    const unsigned int perBatch = (unsigned int)itemTile.size();
-    std::vector<unsigned int> ctaFirst(grid + 1, perBatch * r->batch);
-    {
-        double all = 0.0;
-        for(double w : itemWeight) all += w;
-        all *= r->batch;
-        double acc = 0.0;
-        unsigned int c = 0;
-        for(unsigned int item = 0; item < perBatch * r->batch; item++) {
-            // item starts the share of CTA c once the work before it reaches c / grid of the whole
-            while(c <= grid && acc >= all * c / grid - 1e-9) ctaFirst[c++] = item;
-            acc += itemWeight[item % perBatch];
-        }
-        for(; c <= grid; c++) ctaFirst[c] = perBatch * r->batch;
-        ctaFirst[0] = 0;
-    }
     size_t smem = 0;
     for(const auto &T : tiles) smem = std::max(smem, sizeof(float) * T.depth * T.stride);
     auto toDevice = [&](const void *host, size_t bytes, void **out) -> int {
@@ -1380,11 +1356,17 @@ int buildTiled(b200_runner *r)
     };
     int e = toDevice(tiles.data(), sizeof(TiledTile) * tiles.size(), (void**)&r->tiledTiles);
     if(!e) e = toDevice(sources.data(), sizeof(TiledSource) * sources.size(), (void**)&r->tiledSources);
-    if(!e) e = toDevice(ctaFirst.data(), sizeof(unsigned int) * ctaFirst.size(), (void**)&r->tiledCtaFirst);
-    if(!e) e = toDevice(itemTile.data(), sizeof(unsigned short) * itemTile.size(), (void**)&r->tiledItemTile);
-    if(!e) e = toDevice(itemShare.data(), itemShare.size(), (void**)&r->tiledItemShare);
+    if(!e) e = toDevice(pairs.data(), sizeof(TiledPair) * pairs.size(), (void**)&r->tiledPairs);
     if(!e) e = toDevice(served.data(), served.size(), (void**)&r->tiledServed);
     if(e) { r->dropTiled(); return e; }
+    // scratch of the per-step work partition
+    {
+        const size_t perStep = pairs.size() * r->batch;
+        cudaError_t ce = cudaMalloc(&r->tiledPairBatches, sizeof(unsigned int) * perStep);
+        if(ce == cudaSuccess) ce = cudaMalloc(&r->tiledPairPrefix, sizeof(double) * perStep);
+        if(ce == cudaSuccess) ce = cudaMalloc(&r->tiledCtaStart, sizeof(unsigned int) * 2 * (grid + 1));
+        if(ce != cudaSuccess) { r->dropTiled(); CUDA_TRY(ce); }
+    }
     if(key16) {
         if(anyWeights) CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint16_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         else CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint16_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -1396,7 +1378,7 @@ int buildTiled(b200_runner *r)
     r->tiledRunStart = static_cast<unsigned int*>(runStart.release());
     r->tiledKeys = keys.release();
     r->tiledWeights = static_cast<float*>(weights.release());
-    r->tiledItemsPerBatch = perBatch;
+    r->tiledNumPairs = (unsigned int)pairs.size();
     r->tiledNumSources = numSources;
     r->tiledPostBits = postBits;
     r->tiledGrid = grid;
@@ -1410,8 +1392,9 @@ TiledLaunch tiledLaunch(const b200_runner *r)
 {
     TiledLaunch L;
     L.tiles = r->tiledTiles; L.sources = r->tiledSources; L.run_start = r->tiledRunStart; L.keys = r->tiledKeys;
-    L.weights = r->tiledWeights; L.cta_first_item = r->tiledCtaFirst; L.item_tile = r->tiledItemTile;
-    L.item_share = r->tiledItemShare; L.items_per_batch = r->tiledItemsPerBatch; L.num_sources = r->tiledNumSources;
+    L.weights = r->tiledWeights; L.pairs = r->tiledPairs; L.pair_batches = r->tiledPairBatches;
+    L.pair_prefix = r->tiledPairPrefix; L.cta_start = r->tiledCtaStart; L.num_pairs = r->tiledNumPairs;
+    L.num_sources = r->tiledNumSources; L.grid = r->tiledGrid;
     L.batch = r->batch; L.post_bits = r->tiledPostBits; L.min_events = r->tiledMinEvents; L.state = r->state;
     L.count_events = r->countEvents ? 1u : 0u;
     return L;
@@ -1435,7 +1418,7 @@ int enqueueSynapses(b200_runner *r, bool capturing)
         if(r->tiledReady) {
             // the step's estimated events decide which of the two kernels delivers the served groups
             const TiledLaunch T = tiledLaunch(r);
-            tiledDecideKernel<<<1, 256, 0, r->stream>>>(T);
+            tiledDecideKernel<<<1, TILED_BLOCK, 0, r->stream>>>(T);
             const bool key16 = (r->tiledPostBits == 10u);
             if(key16 && r->tiledWeights) tiledDeliverKernel<uint16_t, true><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
             else if(key16) tiledDeliverKernel<uint16_t, false><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);

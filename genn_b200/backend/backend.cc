@@ -196,6 +196,7 @@ void genKernelTimerStop(CodeStream &os, const std::string &name, bool enabled, b
     if(enabled) {
         os << "CHECK_RUNTIME_ERRORS(cudaEventRecord(" << name << "Stop));" << std::endl;
         if(readBack) {
+            CodeStream::Scope b(os);
             os << "CHECK_RUNTIME_ERRORS(cudaEventSynchronize(" << name << "Stop));" << std::endl;
             os << "float b200Elapsed;" << std::endl;
             os << "CHECK_RUNTIME_ERRORS(cudaEventElapsedTime(&b200Elapsed, " << name << "Start, " << name << "Stop));" << std::endl;
@@ -565,7 +566,7 @@ void Backend::genAssert(CodeStream &os, const std::string &condition) const
 void Backend::genMakefilePreamble(std::ostream &os) const
 {
     const auto &p = getPreferences<Preferences>();
-    std::string flags = "-gencode arch=compute_100a,code=sm_100a -std=c++17 -x cu -rdc=false -Xcompiler -fPIC -lineinfo";
+    std::string flags = "-gencode arch=compute_100a,code=sm_100a -std=c++17 -x cu -Xcompiler -fPIC -lineinfo";
     flags += " -diag-suppress 177,550 -I\"" + includeDirectory() + "\"";
     flags += p.debugCode ? " -O0 -g -G" : " -O3";
     if(p.optimizeCode) {
@@ -591,7 +592,7 @@ void Backend::genMakefileCompileRule(std::ostream &os) const
 {
     os << "%.d: ;" << std::endl;
     os << "%.o: %.cc %.d" << std::endl;
-    os << "\t@$(NVCC) -dc $(NVCCFLAGS) -o $@ $<" << std::endl;
+    os << "\t@$(NVCC) -c $(NVCCFLAGS) -o $@ $<" << std::endl;
 }
 
 void Backend::genNMakefilePreamble(std::ostream&) const { assert(false); }
@@ -1087,20 +1088,21 @@ void Backend::genSynapseUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerge
                         {
                             CodeStream::Scope b(groupEnv.getStream());
                             EnvironmentGroupMergedField<PresynapticUpdateGroupMerged> synEnv(groupEnv, sg);
-                            synEnv.printLine("const unsigned int b200Pre = $(_src_spk" + eventSuffix + ")["
-                                             + sg.getPreVarIndex(delay, batchSize, VarAccessDim::BATCH | VarAccessDim::ELEMENT, "b200Spike") + "];");
-                            synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre");
+                            // (initialisers are emitted before the body of an environment, in the order they were added)
+                            synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre",
+                                       {synEnv.addInitialiser("const unsigned int b200Pre = $(_src_spk" + eventSuffix + ")["
+                                                              + sg.getPreVarIndex(delay, batchSize, VarAccessDim::BATCH | VarAccessDim::ELEMENT, "b200Spike") + "];")});
                             const auto indexType = getSynapseIndexType(sg);
                             const std::string indexTypeName = indexType.getName();
                             synEnv.add(indexType.addConst(), "id_syn", "b200Syn",
-                                       {synEnv.addInitialiser("const " + indexTypeName + " b200Syn = ((" + indexTypeName + ")b200Pre * $(_row_stride)) + $(id);")});
+                                       {synEnv.addInitialiser("const " + indexTypeName + " b200Syn = ((" + indexTypeName + ")$(id_pre) * $(_row_stride)) + $(id);")});
                             if(sparse) {
-                                synEnv.print("if($(id) < $(_row_length)[b200Pre])");
+                                synEnv.print("if($(id) < $(_row_length)[$(id_pre)])");
                                 synEnv.add(Type::Uint32.addConst(), "id_post", "b200Post",
                                            {synEnv.addInitialiser("const unsigned int b200Post = $(_ind)[$(id_syn)];")});
                             }
                             else if(bitmask) {
-                                synEnv.printLine("const " + indexTypeName + " b200Gid = ((" + indexTypeName + ")b200Pre * $(_row_stride)) + $(id);");
+                                synEnv.printLine("const " + indexTypeName + " b200Gid = ((" + indexTypeName + ")$(id_pre) * $(_row_stride)) + $(id);");
                                 synEnv.print("if(($(id) < $(num_post)) && ($(_gp)[b200Gid / 32] & (0x80000000 >> (b200Gid & 31))))");
                                 synEnv.add(Type::Uint32.addConst(), "id_post", "$(id)");
                             }
@@ -1172,19 +1174,19 @@ void Backend::genSynapseUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerge
                         {
                             CodeStream::Scope b(groupEnv.getStream());
                             EnvironmentGroupMergedField<PostsynapticUpdateGroupMerged> synEnv(groupEnv, sg);
-                            synEnv.printLine("const unsigned int b200Post = $(_trg_spk" + eventSuffix + ")["
-                                             + sg.getPostVarIndex(delay, batchSize, VarAccessDim::BATCH | VarAccessDim::ELEMENT, "b200Spike") + "];");
-                            synEnv.add(Type::Uint32.addConst(), "id_post", "b200Post");
+                            synEnv.add(Type::Uint32.addConst(), "id_post", "b200Post",
+                                       {synEnv.addInitialiser("const unsigned int b200Post = $(_trg_spk" + eventSuffix + ")["
+                                                              + sg.getPostVarIndex(delay, batchSize, VarAccessDim::BATCH | VarAccessDim::ELEMENT, "b200Spike") + "];")});
                             if(sparse) {
-                                synEnv.print("if($(id) < $(_col_length)[b200Post])");
+                                synEnv.print("if($(id) < $(_col_length)[$(id_post)])");
                                 synEnv.add(Type::Uint32.addConst(), "id_syn", "b200Syn",
-                                           {synEnv.addInitialiser("const unsigned int b200Syn = $(_remap)[(b200Post * $(_col_stride)) + $(id)];")});
+                                           {synEnv.addInitialiser("const unsigned int b200Syn = $(_remap)[($(id_post) * $(_col_stride)) + $(id)];")});
                                 synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre",
                                            {synEnv.addInitialiser("const unsigned int b200Pre = $(id_syn) / $(_row_stride);")});
                             }
                             else {
                                 synEnv.add(Type::Uint32.addConst(), "id_syn", "b200Syn",
-                                           {synEnv.addInitialiser("const unsigned int b200Syn = ($(id) * $(num_post)) + b200Post;")});
+                                           {synEnv.addInitialiser("const unsigned int b200Syn = ($(id) * $(num_post)) + $(id_post);")});
                                 synEnv.add(Type::Uint32.addConst(), "id_pre", "$(id)");
                             }
                             {
@@ -1265,3 +1267,693 @@ void Backend::genSynapseUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerge
         }
     }
 }
+
+//--------------------------------------------------------------------------
+// Initialisation
+//--------------------------------------------------------------------------
+// Loop shapes the group emitters ask for.  The parallel dimension is the thread: a neuron for
+// neuron variables, a target neuron (dense) or a position in the ragged row (sparse) for
+// per-synapse variables; the emitters loop over the other dimension themselves.
+void Backend::genPopVariableInit(EnvironmentExternalBase &env, HandlerEnv handler) const
+{
+    env.getStream() << "if(" << env["id"] << " == 0)";
+    {
+        CodeStream::Scope b(env.getStream());
+        handler(env);
+    }
+}
+
+void Backend::genVariableInit(EnvironmentExternalBase &env, const std::string&, const std::string&, HandlerEnv handler) const
+{
+    handler(env);       // the thread is the element
+}
+
+void Backend::genSparseSynapseVariableRowInit(EnvironmentExternalBase &env, HandlerEnv handler) const
+{
+    EnvironmentExternal varEnv(env);
+    varEnv.add(Type::Uint32.addConst(), "id_syn", "b200InitSyn",
+               {varEnv.addInitialiser("const unsigned int b200InitSyn = ($(id_pre) * $(_row_stride)) + $(id);")});
+    handler(varEnv);
+}
+
+void Backend::genDenseSynapseVariableRowInit(EnvironmentExternalBase &env, HandlerEnv handler) const
+{
+    genSparseSynapseVariableRowInit(env, handler);
+}
+
+void Backend::genKernelSynapseVariableInit(EnvironmentExternalBase &env, SynapseInitGroupMerged&, HandlerEnv handler) const
+{
+    EnvironmentExternal varEnv(env);
+    varEnv.add(Type::Uint32.addConst(), "id_syn", "$(id)");
+    handler(varEnv);
+}
+
+void Backend::genKernelCustomUpdateVariableInit(EnvironmentExternalBase &env, CustomWUUpdateInitGroupMerged&, HandlerEnv handler) const
+{
+    EnvironmentExternal varEnv(env);
+    varEnv.add(Type::Uint32.addConst(), "id_syn", "$(id)");
+    handler(varEnv);
+}
+
+namespace
+{
+//! Expression for the flattened size of dimension `d` of a kernel-weight group
+template<typename G>
+std::string kernelDimension(const G &g, size_t d)
+{
+    return getKernelSize(g, d);
+}
+
+//! Body shared by synapse groups and custom WU updates with DENSE or KERNEL weights: thread = target
+//! neuron (or flattened kernel element), the emitter loops over the source neurons
+template<typename G>
+void genDenseVarInit(const BackendBase &backend, EnvironmentExternalBase &env, G &g, unsigned int batchSize,
+                     bool kernel, size_t kernelDimensions, const std::string &rngInit)
+{
+    env.print(kernel ? "if($(id) < $(_kernel_size))" : "if($(id) < $(num_post))");
+    CodeStream::Scope b(env.getStream());
+    EnvironmentGroupMergedField<G> initEnv(env, g);
+    initEnv.add(Type::Void, "_rng", "b200Rng", {initEnv.addInitialiser(rngInit)});
+    if(kernel) {
+        for(size_t i = 0; i < kernelDimensions; i++) {
+            std::ostringstream init;
+            init << "const unsigned int b200Kernel" << i << " = ($(id)";
+            if(i < (kernelDimensions - 1)) {
+                init << " / (";
+                for(size_t j = (kernelDimensions - 1); j > i; j--) {
+                    init << kernelDimension(g, j);
+                    if(j != (i + 1)) {
+                        init << " * ";
+                    }
+                }
+                init << ")";
+            }
+            init << ")";
+            if(i > 0) {
+                init << " % " << kernelDimension(g, i);
+            }
+            init << ";";
+            initEnv.add(Type::Uint32.addConst(), "id_kernel_" + std::to_string(i), "b200Kernel" + std::to_string(i),
+                        {initEnv.addInitialiser(init.str())});
+        }
+    }
+    else {
+        initEnv.add(Type::Uint32.addConst(), "id_post", "$(id)");
+    }
+    g.generateInit(backend, initEnv, batchSize);
+}
+
+//! Body shared by the SPARSE per-synapse initialisers: thread = position in the ragged row, loop over
+//! the rows; `handler` adds per-synapse work of the backend's own (the column-major remap)
+template<typename G, typename H>
+void genSparseVarInit(const BackendBase &backend, EnvironmentExternalBase &env, G &g, unsigned int batchSize,
+                      bool varInitRequired, H handler)
+{
+    env.printLine("unsigned int idx = $(id);");
+    env.print("for(unsigned int b200Row = 0; b200Row < $(num_pre); b200Row++)");
+    {
+        CodeStream::Scope b(env.getStream());
+        env.print("if($(id) < $(_row_length)[b200Row])");
+        {
+            CodeStream::Scope b(env.getStream());
+            if(varInitRequired) {
+                EnvironmentExternal initEnv(env);
+                initEnv.add(Type::Uint32.addConst(), "id_pre", "b200Row");
+                initEnv.add(Type::Uint32.addConst(), "id_post", "$(_ind)[idx]");
+                g.generateInit(backend, initEnv, batchSize);
+            }
+            handler(env);
+        }
+        env.printLine("idx += $(_row_stride);");
+    }
+}
+}   // anonymous namespace
+
+void Backend::genInit(CodeStream &os, FileStreamCreator, ModelSpecMerged &modelMerged,
+                      BackendBase::MemorySpaces &memorySpaces, HostHandler preambleHandler) const
+{
+    const ModelSpecInternal &model = modelMerged.getModel();
+    const unsigned int batchSize = model.getBatchSize();
+    const size_t block = blockSize();
+    const std::string dtLiteral = Type::writeNumeric(model.getDT(), model.getTimePrecision());
+
+    std::ostringstream kernelStream;
+    CodeStream kernels(kernelStream);
+    std::vector<KernelLaunch> initLaunches, sparseLaunches;
+
+    EnvironmentLibrary backendEnv(kernels, backendFunctions);
+    EnvironmentLibrary mathsEnv(backendEnv, StandardLibrary::getMathsFunctions());
+    EnvironmentLibrary kernelLibEnv(mathsEnv, randomFunctions(model.getPrecision()));
+
+    auto rngInit = [](unsigned int stream, size_t index)
+    {
+        return "b200gen::Rng b200Rng = b200gen::initRng(b200Seed, " + std::to_string(stream + index) + "u + (b200Group << 20), b200Thread);";
+    };
+    // one kernel of one merged group: prologue + body
+    auto genKernel = [&](auto &g, const std::string &kernelName, const std::string &typeName, auto getNumThreads,
+                         std::vector<KernelLaunch> &launches, auto body)
+    {
+        const std::string idx = std::to_string(g.getIndex());
+        KernelLaunch launch;
+        launch.name = kernelName + idx;
+        launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_merged" + typeName + "GroupStartID" + idx, g, block, getNumThreads);
+        kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(unsigned long long b200Seed)";
+        {
+            CodeStream::Scope b(kernelLibEnv.getStream());
+            EnvironmentExternal kernelEnv(kernelLibEnv);
+            kernelEnv.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
+            genFindGroup(kernelEnv.getStream(), "Merged" + typeName + "Group" + idx, "d_merged" + typeName + "Group" + idx,
+                         "d_merged" + typeName + "GroupStartID" + idx, g.getGroups().size());
+            kernelEnv.add(Type::Uint32.addConst(), "id", "b200Local");
+            body(kernelEnv);
+        }
+        launches.push_back(launch);
+    };
+
+    // ---- neuron variables ------------------------------------------------------------------------------------
+    modelMerged.genMergedNeuronInitGroups(
+        *this, memorySpaces,
+        [&](auto &n)
+        {
+            genKernel(n, "initializeNeuronKernel", "NeuronInit", [](const NeuronGroupInternal &ng){ return (size_t)ng.getNumNeurons(); }, initLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<NeuronInitGroupMerged> groupEnv(kernelEnv, n);
+                          buildStandardEnvironment(groupEnv, batchSize);
+                          groupEnv.print("if($(id) < $(num_neurons))");
+                          {
+                              CodeStream::Scope b(groupEnv.getStream());
+                              EnvironmentGroupMergedField<NeuronInitGroupMerged> initEnv(groupEnv, n);
+                              initEnv.add(Type::Void, "_rng", "b200Rng", {initEnv.addInitialiser(rngInit(STREAM_INIT_NEURON, n.getIndex()))});
+                              n.generateInit(*this, initEnv, batchSize);
+                          }
+                      });
+        });
+
+    // ---- DENSE / KERNEL weight update variables -----------------------------------------------------------------
+    modelMerged.genMergedSynapseInitGroups(
+        *this, memorySpaces,
+        [&](auto &s)
+        {
+            const bool kernel = (s.getArchetype().getMatrixType() & SynapseMatrixWeight::KERNEL);
+            genKernel(s, "initializeSynapseKernel", "SynapseInit",
+                      [](const SynapseGroupInternal &sg)
+                      {
+                          return (sg.getMatrixType() & SynapseMatrixWeight::KERNEL) ? (size_t)sg.getKernelSizeFlattened()
+                                                                                    : (size_t)sg.getTrgNeuronGroup()->getNumNeurons();
+                      },
+                      initLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<SynapseInitGroupMerged> groupEnv(kernelEnv, s);
+                          buildStandardEnvironment(groupEnv, batchSize);
+                          genDenseVarInit(*this, groupEnv, s, batchSize, kernel, s.getArchetype().getKernelSize().size(),
+                                          rngInit(STREAM_INIT_SYNAPSE, s.getIndex()));
+                      });
+        });
+
+    // ---- custom update variables ---------------------------------------------------------------------------------
+    modelMerged.genMergedCustomUpdateInitGroups(
+        *this, memorySpaces,
+        [&](auto &c)
+        {
+            genKernel(c, "initializeCustomUpdateKernel", "CustomUpdateInit", [](const CustomUpdateInternal &cg){ return (size_t)cg.getNumNeurons(); }, initLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<CustomUpdateInitGroupMerged> groupEnv(kernelEnv, c);
+                          buildStandardEnvironment(groupEnv, batchSize);
+                          groupEnv.print("if($(id) < $(num_neurons))");
+                          {
+                              CodeStream::Scope b(groupEnv.getStream());
+                              EnvironmentGroupMergedField<CustomUpdateInitGroupMerged> initEnv(groupEnv, c);
+                              initEnv.add(Type::Void, "_rng", "b200Rng", {initEnv.addInitialiser(rngInit(STREAM_INIT_CUSTOM, c.getIndex()))});
+                              c.generateInit(*this, initEnv, batchSize);
+                          }
+                      });
+        });
+    modelMerged.genMergedCustomWUUpdateInitGroups(
+        *this, memorySpaces,
+        [&](auto &c)
+        {
+            const SynapseGroupInternal *sgInternal = c.getArchetype().getSynapseGroup();
+            const bool kernel = (sgInternal->getMatrixType() & SynapseMatrixWeight::KERNEL);
+            genKernel(c, "initializeCustomWUUpdateKernel", "CustomWUUpdateInit",
+                      [](const CustomUpdateWUInternal &cg)
+                      {
+                          const auto *sg = cg.getSynapseGroup();
+                          return (sg->getMatrixType() & SynapseMatrixWeight::KERNEL) ? (size_t)sg->getKernelSizeFlattened()
+                                                                                     : (size_t)sg->getTrgNeuronGroup()->getNumNeurons();
+                      },
+                      initLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<CustomWUUpdateInitGroupMerged> groupEnv(kernelEnv, c);
+                          buildStandardEnvironment(groupEnv, batchSize);
+                          genDenseVarInit(*this, groupEnv, c, batchSize, kernel, sgInternal->getKernelSize().size(),
+                                          rngInit(STREAM_INIT_CUSTOM_WU, c.getIndex()));
+                      });
+        });
+    if(!modelMerged.getMergedCustomConnectivityUpdatePreInitGroups().empty() || !modelMerged.getMergedCustomConnectivityUpdatePostInitGroups().empty()
+       || !modelMerged.getMergedCustomConnectivityUpdateSparseInitGroups().empty())
+    {
+        throw std::runtime_error("B200 backend: custom connectivity updates are not generated yet");
+    }
+
+    // ---- sparse / bitmask connectivity built on the device ------------------------------------------------------------
+    modelMerged.genMergedSynapseConnectivityInitGroups(
+        *this, memorySpaces,
+        [&](auto &s)
+        {
+            const auto &connectInit = s.getArchetype().getSparseConnectivityInitialiser();
+            const bool rowBuild = !Utils::areTokensEmpty(connectInit.getRowBuildCodeTokens());
+            const bool sparse = (s.getArchetype().getMatrixType() & SynapseMatrixConnectivity::SPARSE);
+            if(!sparse && !(s.getArchetype().getMatrixType() & SynapseMatrixConnectivity::BITMASK)) {
+                throw std::runtime_error("Only BITMASK and SPARSE format connectivity can be generated using a connectivity initialiser");
+            }
+            genKernel(s, "initializeConnectivityKernel", "SynapseConnectivityInit",
+                      [](const SynapseGroupInternal &sg)
+                      {
+                          return Utils::areTokensEmpty(sg.getSparseConnectivityInitialiser().getRowBuildCodeTokens())
+                              ? (size_t)sg.getTrgNeuronGroup()->getNumNeurons() : (size_t)sg.getSrcNeuronGroup()->getNumNeurons();
+                      },
+                      initLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<SynapseConnectivityInitGroupMerged> groupEnv(kernelEnv, s);
+                          buildStandardEnvironment(groupEnv, batchSize);
+                          if(rowBuild) {
+                              groupEnv.print("if($(id) < $(num_pre))");
+                              groupEnv.add(Type::Uint32.addConst(), "id_pre", "$(id)");
+                              groupEnv.add(Type::Uint32.addConst(), "id_post_begin", "0");
+                          }
+                          else {
+                              groupEnv.print("if($(id) < $(num_post))");
+                              groupEnv.add(Type::Uint32.addConst(), "id_post", "$(id)");
+                              groupEnv.add(Type::Uint32.addConst(), "id_pre_begin", "0");
+                          }
+                          groupEnv.add(Type::Uint32.addConst(), "id_thread", "0");
+                          groupEnv.add(Type::Uint32.addConst(), "num_threads", "1");
+                          CodeStream::Scope b(groupEnv.getStream());
+
+                          // what addSynapse(j[, kernel indices]) expands to
+                          std::ostringstream addSynapseStream;
+                          CodeStream addSynapse(addSynapseStream);
+                          {
+                              CodeStream::Scope b(addSynapse);
+                              EnvironmentExternal addSynapseEnv(groupEnv, addSynapse);
+                              if(rowBuild) {
+                                  addSynapseEnv.add(Type::Uint32.addConst(), "id_post", "b200NewPost",
+                                                    {addSynapseEnv.addInitialiser("const unsigned int b200NewPost = $(0);")});
+                              }
+                              else {
+                                  addSynapseEnv.add(Type::Uint32.addConst(), "id_pre", "b200NewPre",
+                                                    {addSynapseEnv.addInitialiser("const unsigned int b200NewPre = $(0);")});
+                              }
+                              if(sparse) {
+                                  if(rowBuild) {
+                                      // the thread owns the row: plain increment
+                                      addSynapseEnv.add(Type::Uint32.addConst(), "id_syn", "b200NewSyn",
+                                                        {addSynapseEnv.addInitialiser("const unsigned int b200NewSyn = ($(id_pre) * $(_row_stride)) + $(_row_length)[$(id_pre)];")});
+                                      addSynapseEnv.printLine("$(_row_length)[$(id_pre)]++;");
+                                  }
+                                  else {
+                                      addSynapseEnv.add(Type::Uint32.addConst(), "id_syn", "b200NewSyn",
+                                                        {addSynapseEnv.addInitialiser("const unsigned int b200RowPos = atomicAdd(&$(_row_length)[$(id_pre)], 1);"),
+                                                         addSynapseEnv.addInitialiser("const unsigned int b200NewSyn = ($(id_pre) * $(_row_stride)) + b200RowPos;")});
+                                  }
+                                  addSynapseEnv.printLine("$(_ind)[$(id_syn)] = $(id_post);");
+                                  if(!s.getArchetype().getKernelSize().empty()) {
+                                      EnvironmentGroupMergedField<SynapseConnectivityInitGroupMerged> kernelInitEnv(addSynapseEnv, s);
+                                      for(size_t i = 0; i < s.getArchetype().getKernelSize().size(); i++) {
+                                          const std::string iStr = std::to_string(i);
+                                          kernelInitEnv.add(Type::Uint32.addConst(), "id_kernel_" + iStr, "b200NewKernel" + iStr,
+                                                            {kernelInitEnv.addInitialiser("const unsigned int b200NewKernel" + iStr + " = $(" + std::to_string(i + 1) + ");")});
+                                      }
+                                      s.generateKernelInit(kernelInitEnv, 1);
+                                  }
+                              }
+                              else {
+                                  // word-packed bits, MSB first (single_threaded_cpu/backend.cc:2003-2006)
+                                  const std::string indexTypeName = getSynapseIndexType(s).getName();
+                                  if(rowBuild) {
+                                      addSynapseEnv.printLine("const " + indexTypeName + " b200Gid = ((" + indexTypeName + ")$(id) * $(_row_stride)) + ($(0));");
+                                  }
+                                  else {
+                                      addSynapseEnv.printLine("const " + indexTypeName + " b200Gid = ((" + indexTypeName + ")($(0)) * $(_row_stride)) + $(id);");
+                                  }
+                                  addSynapseEnv.printLine("atomicOr(&$(_gp)[b200Gid / 32], 0x80000000 >> (b200Gid & 31));");
+                              }
+                          }
+                          const auto addSynapseType = Type::ResolvedType::createFunction(
+                              Type::Void, std::vector<Type::ResolvedType>{1ull + s.getArchetype().getKernelSize().size(), Type::Uint32});
+                          groupEnv.add(addSynapseType, "addSynapse", addSynapseStream.str());
+                          groupEnv.add(Type::Void, "_rng", "b200Rng", {groupEnv.addInitialiser(rngInit(STREAM_INIT_CONNECT, s.getIndex()))});
+                          if(rowBuild) {
+                              if(sparse) {
+                                  groupEnv.printLine("$(_row_length)[$(id)] = 0;");
+                              }
+                              s.generateSparseRowInit(groupEnv);
+                          }
+                          else {
+                              s.generateSparseColumnInit(groupEnv);      // row lengths were zeroed when the array was created
+                          }
+                      });
+        });
+
+    // ---- after the connectivity exists (initializeSparse): per-synapse variables of SPARSE groups, remap -------
+    modelMerged.genMergedSynapseSparseInitGroups(
+        *this, memorySpaces,
+        [&](auto &s)
+        {
+            genKernel(s, "initializeSparseKernel", "SynapseSparseInit", [](const SynapseGroupInternal &sg){ return (size_t)sg.getMaxConnections(); }, sparseLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<SynapseSparseInitGroupMerged> groupEnv(kernelEnv, s);
+                          buildStandardEnvironment(groupEnv, batchSize);
+                          groupEnv.add(Type::Void, "_rng", "b200Rng", {groupEnv.addInitialiser(rngInit(STREAM_INIT_SPARSE, s.getIndex()))});
+                          const bool remap = s.getArchetype().isPostSpikeRequired() || s.getArchetype().isPostSpikeEventRequired();
+                          genSparseVarInit(*this, groupEnv, s, batchSize, s.getArchetype().isWUVarInitRequired(),
+                                           [&](EnvironmentExternalBase &env)
+                                           {
+                                               if(remap) {
+                                                   // column-major view of the ragged matrix for postsynaptic learning
+                                                   CodeStream::Scope b(env.getStream());
+                                                   env.printLine("const unsigned int b200PostIndex = $(_ind)[idx];");
+                                                   env.printLine("const unsigned int b200ColPos = atomicAdd(&$(_col_length)[b200PostIndex], 1);");
+                                                   env.printLine("$(_remap)[(b200PostIndex * $(_col_stride)) + b200ColPos] = idx;");
+                                               }
+                                           });
+                      });
+        });
+    modelMerged.genMergedCustomWUUpdateSparseInitGroups(
+        *this, memorySpaces,
+        [&](auto &c)
+        {
+            genKernel(c, "initializeCustomWUUpdateSparseKernel", "CustomWUUpdateSparseInit",
+                      [](const CustomUpdateWUInternal &cg){ return (size_t)cg.getSynapseGroup()->getMaxConnections(); }, sparseLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<CustomWUUpdateSparseInitGroupMerged> groupEnv(kernelEnv, c);
+                          buildStandardEnvironment(groupEnv, batchSize);
+                          groupEnv.add(Type::Void, "_rng", "b200Rng", {groupEnv.addInitialiser(rngInit(STREAM_INIT_CUSTOM_WU_SPARSE, c.getIndex()))});
+                          genSparseVarInit(*this, groupEnv, c, batchSize, true, [](EnvironmentExternalBase&){});
+                      });
+        });
+
+    // ---- file -----------------------------------------------------------------------------------------------------------
+    os << "#include <iostream>" << std::endl;
+    os << "#include <random>" << std::endl;
+    os << "#include <cstdint>" << std::endl;
+    os << std::endl;
+    modelMerged.genMergedNeuronInitGroupStructs(os, *this);
+    modelMerged.genMergedSynapseInitGroupStructs(os, *this);
+    modelMerged.genMergedSynapseConnectivityInitGroupStructs(os, *this);
+    modelMerged.genMergedSynapseSparseInitGroupStructs(os, *this);
+    modelMerged.genMergedCustomUpdateInitGroupStructs(os, *this);
+    modelMerged.genMergedCustomWUUpdateInitGroupStructs(os, *this);
+    modelMerged.genMergedCustomWUUpdateSparseInitGroupStructs(os, *this);
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedNeuronInitGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedSynapseInitGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedSynapseConnectivityInitGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedSynapseSparseInitGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomUpdateInitGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomWUUpdateInitGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomWUUpdateSparseInitGroups());
+    preambleHandler(os);
+    os << kernelStream.str();
+
+    os << "void initialize()";
+    {
+        CodeStream::Scope b(os);
+        genKernelTimerStart(os, "init", model.isTimingEnabled());
+        for(const auto &k : initLaunches) {
+            genLaunch(os, k, block, 1, "b200Seed");
+        }
+        genKernelTimerStop(os, "init", model.isTimingEnabled(), true);
+    }
+    os << std::endl;
+    os << "void initializeSparse()";
+    {
+        CodeStream::Scope b(os);
+        if(!sparseLaunches.empty()) {
+            const bool timer = model.isTimingEnabled() && !modelMerged.getMergedSynapseSparseInitGroups().empty();
+            genKernelTimerStart(os, "initSparse", timer);
+            for(const auto &k : sparseLaunches) {
+                genLaunch(os, k, block, 1, "b200Seed");
+            }
+            genKernelTimerStop(os, "initSparse", timer, true);
+        }
+    }
+}
+
+//--------------------------------------------------------------------------
+// Custom updates
+//--------------------------------------------------------------------------
+void Backend::genCustomUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerged &modelMerged,
+                              BackendBase::MemorySpaces &memorySpaces, HostHandler preambleHandler) const
+{
+    const ModelSpecInternal &model = modelMerged.getModel();
+    const unsigned int batchSize = model.getBatchSize();
+    const size_t block = blockSize();
+    const std::string timeType = model.getTimePrecision().getName();
+    const std::string dtLiteral = Type::writeNumeric(model.getDT(), model.getTimePrecision());
+
+    if(!modelMerged.getMergedCustomUpdateTransposeWUGroups().empty() || !modelMerged.getMergedCustomConnectivityUpdateGroups().empty()
+       || !modelMerged.getMergedCustomConnectivityRemapUpdateGroups().empty() || !modelMerged.getMergedCustomConnectivityHostUpdateGroups().empty())
+    {
+        throw std::runtime_error("B200 backend: transpose and custom connectivity updates are not generated yet");
+    }
+
+    std::ostringstream kernelStream;
+    CodeStream kernels(kernelStream);
+    EnvironmentLibrary backendEnv(kernels, backendFunctions);
+    EnvironmentLibrary mathsEnv(backendEnv, StandardLibrary::getMathsFunctions());
+    EnvironmentLibrary kernelLibEnv(mathsEnv, randomFunctions(model.getPrecision()));
+
+    // names of all custom update groups
+    std::set<std::string> updateGroups;
+    for(const auto &c : model.getCustomUpdates()) {
+        updateGroups.insert(c.second.getUpdateGroupName());
+    }
+    for(const auto &c : model.getCustomWUUpdates()) {
+        updateGroups.insert(c.second.getUpdateGroupName());
+    }
+
+    std::map<std::string, std::vector<KernelLaunch>> launches;
+    for(const auto &g : updateGroups) {
+        // ---- neuron-shaped custom updates ---------------------------------------------------------------------------
+        modelMerged.genMergedCustomUpdateGroups(
+            *this, memorySpaces, g,
+            [&](auto &cg)
+            {
+                const std::string idx = std::to_string(cg.getIndex());
+                const bool batchReduce = cg.getArchetype().isBatchReduction();
+                const bool neuronReduce = cg.getArchetype().isNeuronReduction();
+                const bool perElement = (cg.getArchetype().getDims() & VarAccessDim::ELEMENT);
+                const bool batched = (cg.getArchetype().getDims() & VarAccessDim::BATCH) && (batchSize > 1);
+                KernelLaunch launch;
+                launch.name = "customUpdate" + g + "Kernel" + idx;
+                // grid.y spans the batch unless the batch is what is being reduced
+                launch.batched = batched && !batchReduce;
+                launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedCustomUpdateGroupStartID" + idx, cg, block,
+                                                [&](const CustomUpdateInternal &cu)
+                                                {
+                                                    return (neuronReduce || !perElement) ? (size_t)32 : (size_t)cu.getNumNeurons();
+                                                });
+                kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << timeType << " t)";
+                {
+                    CodeStream::Scope b(kernelLibEnv.getStream());
+                    EnvironmentExternal kernelEnv(kernelLibEnv);
+                    kernelEnv.add(model.getTimePrecision().addConst(), "t", "t");
+                    kernelEnv.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
+                    genFindGroup(kernelEnv.getStream(), "MergedCustomUpdateGroup" + idx, "d_mergedCustomUpdateGroup" + idx,
+                                 "d_mergedCustomUpdateGroupStartID" + idx, cg.getGroups().size());
+                    kernelEnv.add(Type::Uint32.addConst(), "id", "b200Local");
+                    EnvironmentGroupMergedField<CustomUpdateGroupMerged> groupEnv(kernelEnv, cg);
+                    buildSizeEnvironment(groupEnv);
+                    if(batchReduce) {
+                        // one thread per element walks the batch (values of one element are a stride apart,
+                        // neighbouring threads read neighbouring addresses)
+                        groupEnv.print("if($(id) < $(num_neurons))");
+                        CodeStream::Scope b(groupEnv.getStream());
+                        const auto reductionTargets = genInitReductionTargets(groupEnv.getStream(), cg, batchSize, groupEnv["id"]);
+                        groupEnv.getStream() << "for(unsigned int batch = 0; batch < " << batchSize << "; batch++)";
+                        {
+                            CodeStream::Scope b(groupEnv.getStream());
+                            EnvironmentGroupMergedField<CustomUpdateGroupMerged> batchEnv(groupEnv, cg);
+                            batchEnv.add(Type::Uint32.addConst(), "batch", "batch");
+                            buildStandardEnvironment(batchEnv, batchSize);
+                            cg.generateCustomUpdate(batchEnv, batchSize,
+                                                    [&reductionTargets, this](auto &env, const auto&)
+                                                    {
+                                                        for(const auto &r : reductionTargets) {
+                                                            env.printLine(getReductionOperation("_lr" + r.name, "$(" + r.name + ")", r.access, r.type) + ";");
+                                                        }
+                                                    });
+                        }
+                        for(const auto &r : reductionTargets) {
+                            groupEnv.printLine("group->" + r.name + "[" + r.index + "] = _lr" + r.name + ";");
+                        }
+                    }
+                    else if(neuronReduce) {
+                        // one warp per batch element strides over the neurons, then combines its lanes
+                        groupEnv.getStream() << "const unsigned int batch = blockIdx.y;" << std::endl;
+                        groupEnv.add(Type::Uint32.addConst(), "batch", batched ? "batch" : "0");
+                        groupEnv.print("if($(id) < 32)");
+                        CodeStream::Scope b(groupEnv.getStream());
+                        groupEnv.printLine("const unsigned int b200Lane = $(id);");
+                        EnvironmentGroupMergedField<CustomUpdateGroupMerged> batchEnv(groupEnv, cg);
+                        buildStandardEnvironment(batchEnv, batchSize);
+                        const auto reductionTargets = genInitReductionTargets(batchEnv.getStream(), cg, batchSize);
+                        batchEnv.print("for(unsigned int b200Index = b200Lane; b200Index < $(num_neurons); b200Index += 32)");
+                        {
+                            CodeStream::Scope b(batchEnv.getStream());
+                            batchEnv.add(Type::Uint32.addConst(), "id", "b200Index");
+                            cg.generateCustomUpdate(batchEnv, batchSize,
+                                                    [&reductionTargets, this](auto &env, const auto&)
+                                                    {
+                                                        for(const auto &r : reductionTargets) {
+                                                            env.printLine(getReductionOperation("_lr" + r.name, "$(" + r.name + ")", r.access, r.type) + ";");
+                                                        }
+                                                    });
+                        }
+                        for(const auto &r : reductionTargets) {
+                            for(int offset = 16; offset > 0; offset /= 2) {
+                                batchEnv.getStream() << getReductionOperation("_lr" + r.name, "__shfl_down_sync(0xFFFFFFFF, _lr" + r.name + ", " + std::to_string(offset) + ")",
+                                                                              r.access, r.type) << ";" << std::endl;
+                            }
+                        }
+                        batchEnv.getStream() << "if(b200Lane == 0)";
+                        {
+                            CodeStream::Scope b(batchEnv.getStream());
+                            for(const auto &r : reductionTargets) {
+                                batchEnv.printLine("group->" + r.name + "[" + r.index + "] = _lr" + r.name + ";");
+                            }
+                        }
+                    }
+                    else {
+                        groupEnv.getStream() << "const unsigned int batch = blockIdx.y;" << std::endl;
+                        groupEnv.add(Type::Uint32.addConst(), "batch", batched ? "batch" : "0");
+                        if(!perElement) {
+                            // one value per population (and batch element): the first thread does it
+                            groupEnv.print("if($(id) == 0)");
+                        }
+                        else {
+                            groupEnv.print("if($(id) < $(num_neurons))");
+                        }
+                        CodeStream::Scope b(groupEnv.getStream());
+                        EnvironmentGroupMergedField<CustomUpdateGroupMerged> batchEnv(groupEnv, cg);
+                        buildStandardEnvironment(batchEnv, batchSize);
+                        cg.generateCustomUpdate(batchEnv, batchSize, [](auto&, auto&){});
+                    }
+                }
+                launches[g].push_back(launch);
+            });
+
+        // ---- per-synapse custom updates -------------------------------------------------------------------------------
+        modelMerged.genMergedCustomUpdateWUGroups(
+            *this, memorySpaces, g,
+            [&](auto &cg)
+            {
+                const std::string idx = std::to_string(cg.getIndex());
+                const SynapseGroupInternal *sg = cg.getArchetype().getSynapseGroup();
+                const bool batchReduce = cg.getArchetype().isBatchReduction();
+                const bool batched = (cg.getArchetype().getDims() & VarAccessDim::BATCH) && (batchSize > 1);
+                KernelLaunch launch;
+                launch.name = "customUpdateWU" + g + "Kernel" + idx;
+                launch.batched = batched && !batchReduce;
+                launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedCustomUpdateWUGroupStartID" + idx, cg, block,
+                                                [this](const CustomUpdateWUInternal &cu)
+                                                {
+                                                    const auto *s = cu.getSynapseGroup();
+                                                    return (s->getMatrixType() & SynapseMatrixWeight::KERNEL)
+                                                        ? (size_t)s->getKernelSizeFlattened()
+                                                        : (size_t)s->getSrcNeuronGroup()->getNumNeurons() * getSynapticMatrixRowStride(*s);
+                                                });
+                kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << timeType << " t)";
+                {
+                    CodeStream::Scope b(kernelLibEnv.getStream());
+                    EnvironmentExternal kernelEnv(kernelLibEnv);
+                    kernelEnv.add(model.getTimePrecision().addConst(), "t", "t");
+                    kernelEnv.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
+                    genFindGroup(kernelEnv.getStream(), "MergedCustomUpdateWUGroup" + idx, "d_mergedCustomUpdateWUGroup" + idx,
+                                 "d_mergedCustomUpdateWUGroupStartID" + idx, cg.getGroups().size());
+                    kernelEnv.add(Type::Uint32.addConst(), "id", "b200Local");
+                    EnvironmentGroupMergedField<CustomUpdateWUGroupMerged> groupEnv(kernelEnv, cg);
+                    buildSizeEnvironment(groupEnv);
+                    if(!batchReduce) {
+                        groupEnv.getStream() << "const unsigned int batch = blockIdx.y;" << std::endl;
+                        groupEnv.add(Type::Uint32.addConst(), "batch", batched ? "batch" : "0");
+                    }
+                    groupEnv.print("if($(id) < $(_size))");
+                    {
+                        CodeStream::Scope b(groupEnv.getStream());
+                        EnvironmentGroupMergedField<CustomUpdateWUGroupMerged> synEnv(groupEnv, cg);
+                        if(sg->getMatrixType() & SynapseMatrixWeight::KERNEL) {
+                            synEnv.add(Type::Uint32.addConst(), "id_kernel", "$(id)");
+                        }
+                        else if(sg->getMatrixType() & SynapseMatrixConnectivity::SPARSE) {
+                            synEnv.printLine("const unsigned int b200Row = $(id) / $(_row_stride);");
+                            synEnv.printLine("const unsigned int b200Col = $(id) - (b200Row * $(_row_stride));");
+                            synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Row");
+                            synEnv.add(Type::Uint32.addConst(), "id_post", "$(_ind)[$(id)]");
+                            synEnv.print("if(b200Col < $(_row_length)[b200Row])");
+                        }
+                        else {
+                            synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre",
+                                       {synEnv.addInitialiser("const unsigned int b200Pre = $(id) / $(_row_stride);")});
+                            synEnv.add(Type::Uint32.addConst(), "id_post", "b200Post",
+                                       {synEnv.addInitialiser("const unsigned int b200Post = $(id) % $(_row_stride);")});
+                        }
+                        CodeStream::Scope b2(synEnv.getStream());
+                        synEnv.add(Type::Uint32.addConst(), "id_syn", "$(id)");
+                        const auto reductionTargets = genInitReductionTargets(synEnv.getStream(), cg, batchSize, synEnv["id_syn"]);
+                        if(batchReduce) {
+                            synEnv.getStream() << "for(unsigned int batch = 0; batch < " << batchSize << "; batch++)";
+                            synEnv.getStream() << CodeStream::OB(9100);
+                            synEnv.add(Type::Uint32.addConst(), "batch", "batch");
+                        }
+                        {
+                            EnvironmentGroupMergedField<CustomUpdateWUGroupMerged> batchEnv(synEnv, cg);
+                            buildStandardEnvironment(batchEnv, batchSize);
+                            cg.generateCustomUpdate(batchEnv, batchSize,
+                                                    [&reductionTargets, this](auto &env, auto &c)
+                                                    {
+                                                        if(c.getArchetype().isBatchReduction()) {
+                                                            for(const auto &r : reductionTargets) {
+                                                                env.printLine(getReductionOperation("_lr" + r.name, "$(" + r.name + ")", r.access, r.type) + ";");
+                                                            }
+                                                        }
+                                                    });
+                        }
+                        if(batchReduce) {
+                            synEnv.getStream() << CodeStream::CB(9100);
+                            for(const auto &r : reductionTargets) {
+                                synEnv.printLine("group->" + r.name + "[" + r.index + "] = _lr" + r.name + ";");
+                            }
+                        }
+                    }
+                }
+                launches[g].push_back(launch);
+            });
+    }
+
+    // ---- file -----------------------------------------------------------------------------------------------------------
+    modelMerged.genMergedCustomUpdateStructs(os, *this);
+    modelMerged.genMergedCustomUpdateWUStructs(os, *this);
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomUpdateGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomUpdateWUGroups());
+    preambleHandler(os);
+    os << kernelStream.str();
+    for(const auto &g : updateGroups) {
+        os << "void update" << g << "(unsigned long long timestep)";
+        CodeStream::Scope b(os);
+        os << "const " << timeType << " t = timestep * " << dtLiteral << ";" << std::endl;
+        genKernelTimerStart(os, "customUpdate" + g, model.isTimingEnabled());
+        for(const auto &k : launches[g]) {
+            genLaunch(os, k, block, batchSize, "t");
+        }
+        genKernelTimerStop(os, "customUpdate" + g, model.isTimingEnabled(), true);
+    }
+}
+}   // namespace GeNN::CodeGenerator::B200

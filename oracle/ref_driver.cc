@@ -5,7 +5,14 @@
 //
 // Test infrastructure only: the product never links, loads or executes it.
 //
-//   ref_driver <spec.txt> <work_dir> <out_dir>
+//   ref_driver <spec.txt> <work_dir> <out_dir> [generate]
+//
+// Compiled a second time with -DGENN_B200_BACKEND (-> b200_driver) the same
+// program selects the B200 code-generation backend (genn_b200/backend) instead
+// of the CPU one: identical model description, identical GeNN runtime, only the
+// backend differs.  That binary is how the tests drive the plug-in.  With a
+// fourth argument `generate` the program stops after generating and compiling
+// the model's code (needs no GPU).
 //
 // The spec is the line-based text format written by genn_b200.netspec
 // (one item per line, whitespace-separated tokens, arrays as raw
@@ -36,10 +43,53 @@
 #include "code_generator/generateModules.h"
 #include "code_generator/modelSpecMerged.h"
 #include "runtime/runtime.h"
+#ifdef GENN_B200_BACKEND
+#include "../genn_b200/backend/backend.h"
+#else
 #include "optimiser.h"
+#endif
 
 using namespace GeNN;
+#ifdef GENN_B200_BACKEND
+namespace SelectedBackend = GeNN::CodeGenerator::B200;
+#else
 namespace CPU = GeNN::CodeGenerator::SingleThreadedCPU;
+#endif
+
+// Models that are NOT among GeNN's built-in ones: their code strings reach a backend only
+// through the transpiler and the group emitters, which is what a drop-in backend must handle.
+//
+// Quadratic integrate-and-fire neuron with an adaptation current
+class AdaptiveQIF : public NeuronModels::Base
+{
+public:
+    DECLARE_SNIPPET(AdaptiveQIF);
+
+    SET_SIM_CODE(
+        "const scalar drive = (k * (V - Vrest) * (V - Vcrit)) + Isyn + Ioffset - W;\n"
+        "V += dt * drive / C;\n"
+        "W += dt * ((a * (V - Vrest)) - W) / tauW;\n");
+    SET_THRESHOLD_CONDITION_CODE("V >= Vpeak");
+    SET_RESET_CODE(
+        "V = Vreset;\n"
+        "W += b;\n");
+    SET_PARAMS({"C", "k", "Vrest", "Vcrit", "Vpeak", "Vreset", "a", "b", "tauW", "Ioffset"});
+    SET_VARS({{"V", "scalar"}, {"W", "scalar"}});
+    SET_NEEDS_AUTO_REFRACTORY(false);
+};
+IMPLEMENT_SNIPPET(AdaptiveQIF);
+
+// Pulse coupling whose weight is scaled by a parameter and saturates
+class ScaledSaturatingPulse : public WeightUpdateModels::Base
+{
+public:
+    DECLARE_SNIPPET(ScaledSaturatingPulse);
+
+    SET_PARAMS({"gScale", "gMax"});
+    SET_VARS({{"g", "scalar", VarAccess::READ_ONLY}});
+    SET_PRE_SPIKE_SYN_CODE("addToPost(fmin(g * gScale, gMax));\n");
+};
+IMPLEMENT_SNIPPET(ScaledSaturatingPulse);
 
 namespace
 {
@@ -105,10 +155,11 @@ std::vector<std::string> tokens(const std::string &line)
 int main(int argc, char *argv[])
 {
     try {
-        if(argc != 4) {
-            std::cerr << "usage: ref_driver <spec.txt> <work_dir> <out_dir>" << std::endl;
+        if(argc != 4 && argc != 5) {
+            std::cerr << "usage: ref_driver <spec.txt> <work_dir> <out_dir> [generate]" << std::endl;
             return EXIT_FAILURE;
         }
+        const bool generateOnly = (argc == 5) && (std::string(argv[4]) == "generate");
         const std::string specPath = argv[1];
         const filesystem::path workDir(argv[2]);
         const std::string outDir = argv[3];
@@ -141,7 +192,8 @@ int main(int argc, char *argv[])
                     PopSpec p;
                     p.name = t[1]; p.n = (unsigned int)std::stoul(t[2]); p.kind = t[3];
                     size_t i = 4;
-                    const size_t numP = (p.kind == "LIF") ? 7 : (p.kind == "IZH") ? 4 : (p.kind == "POISSON") ? 1 : 0;
+                    const size_t numP = (p.kind == "LIF") ? 7 : (p.kind == "IZH") ? 4 : (p.kind == "POISSON") ? 1
+                                        : (p.kind == "AQIF") ? 10 : 0;
                     for(size_t k = 0; k < numP; k++) p.p.push_back(std::stod(t.at(i++)));
                     for(; i < t.size(); i++) p.files.push_back(t[i]);
                     pops.push_back(p);
@@ -160,7 +212,7 @@ int main(int argc, char *argv[])
                         const std::string k = t[i++];
                         if(k == "wum") {
                             s.wum = t.at(i++);
-                            const size_t n = (s.wum == "CONST") ? 1 : (s.wum == "STDP") ? 6 : 0;
+                            const size_t n = (s.wum == "CONST") ? 1 : (s.wum == "STDP") ? 6 : (s.wum == "SCALED") ? 2 : 0;
                             for(size_t j = 0; j < n; j++) s.wumP.push_back(std::stod(t.at(i++)));
                         }
                         else if(k == "psm") {
@@ -187,7 +239,11 @@ int main(int argc, char *argv[])
 
         // ---- build the model through the reference's public API ---------------
         plog::ConsoleAppender<plog::TxtFormatter> consoleAppender;
+#ifdef GENN_B200_BACKEND
+        SelectedBackend::Preferences prefs;
+#else
         CPU::Preferences prefs;
+#endif
         Logging::init(plog::warning, plog::warning, plog::warning, plog::warning,
                       &consoleAppender, &consoleAppender, &consoleAppender, &consoleAppender);
 
@@ -211,6 +267,12 @@ int main(int argc, char *argv[])
                 ParamValues pv{{"a", p.p[0]}, {"b", p.p[1]}, {"c", p.p[2]}, {"d", p.p[3]}};
                 VarValues vv{{"V", uninitialisedVar()}, {"U", uninitialisedVar()}};
                 p.ng = model.addNeuronPopulation<NeuronModels::Izhikevich>(p.name, p.n, pv, vv);
+            }
+            else if(p.kind == "AQIF") {
+                ParamValues pv{{"C", p.p[0]}, {"k", p.p[1]}, {"Vrest", p.p[2]}, {"Vcrit", p.p[3]}, {"Vpeak", p.p[4]},
+                               {"Vreset", p.p[5]}, {"a", p.p[6]}, {"b", p.p[7]}, {"tauW", p.p[8]}, {"Ioffset", p.p[9]}};
+                VarValues vv{{"V", uninitialisedVar()}, {"W", uninitialisedVar()}};
+                p.ng = model.addNeuronPopulation<AdaptiveQIF>(p.name, p.n, pv, vv);
             }
             else if(p.kind == "SSA") {
                 VarValues vv{{"startSpike", uninitialisedVar()}, {"endSpike", uninitialisedVar()}};
@@ -262,6 +324,11 @@ int main(int argc, char *argv[])
                     initWeightUpdate<WeightUpdateModels::StaticPulseDendriticDelay>(
                         {}, {{"g", uninitialisedVar()}, {"d", uninitialisedVar()}}), psm);
             }
+            else if(s.wum == "SCALED") {
+                s.sg = model.addSynapsePopulation(s.name, mt, src, trg,
+                    initWeightUpdate<ScaledSaturatingPulse>({{"gScale", s.wumP[0]}, {"gMax", s.wumP[1]}},
+                                                            {{"g", uninitialisedVar()}}), psm);
+            }
             else if(s.wum == "STDP") {
                 s.sg = model.addSynapsePopulation(s.name, mt, src, trg,
                     initWeightUpdate<WeightUpdateModels::STDP>(
@@ -283,7 +350,11 @@ int main(int argc, char *argv[])
         filesystem::create_directory(workDir);
         const filesystem::path outputPath = workDir / (model.getName() + "_CODE");
         filesystem::create_directory(outputPath);
+#ifdef GENN_B200_BACKEND
+        auto backend = SelectedBackend::createBackend(model, outputPath, plog::warning, &consoleAppender, prefs);
+#else
         auto backend = CPU::Optimiser::createBackend(model, outputPath, plog::warning, &consoleAppender, prefs);
+#endif
         CodeGenerator::ModelSpecMerged modelMerged(backend, model);
         const auto moduleNames = CodeGenerator::generateAll(modelMerged, backend, outputPath, false);
         {
@@ -298,6 +369,10 @@ int main(int argc, char *argv[])
         if(system(buildCommand.c_str()) != 0) {
             throw std::runtime_error("building generated code failed: " + buildCommand);
         }
+        if(generateOnly) {
+            std::cout << "generated and compiled " << outputPath.str() << std::endl;
+            return EXIT_SUCCESS;
+        }
 
         Runtime::Runtime runtime(workDir, modelMerged, backend);
         runtime.allocate(steps);
@@ -305,8 +380,8 @@ int main(int argc, char *argv[])
 
         // ---- host-supplied state and connectivity -----------------------------
         for(auto &p : pops) {
-            if(p.kind == "LIF" || p.kind == "IZH") {
-                const char *v1 = (p.kind == "LIF") ? "RefracTime" : "U";
+            if(p.kind == "LIF" || p.kind == "IZH" || p.kind == "AQIF") {
+                const char *v1 = (p.kind == "LIF") ? "RefracTime" : (p.kind == "IZH") ? "U" : "W";
                 auto V = readFile<float>(p.files.at(0), p.n);
                 auto R = readFile<float>(p.files.at(1), p.n);
                 std::copy(V.begin(), V.end(), runtime.getArray(*p.ng, "V")->getHostPointer<float>());
@@ -364,30 +439,38 @@ int main(int argc, char *argv[])
         runtime.initializeSparse();
 
         // ---- simulate ----------------------------------------------------------
+        // a device backend's arrays are pulled before they are read (no-op on the CPU backend)
+        auto pulled = [](Runtime::ArrayBase *arr)
+        {
+            if((arr->getLocation() & VarLocationAttribute::HOST) && (arr->getLocation() & VarLocationAttribute::DEVICE)) {
+                arr->pullFromDevice();
+            }
+            return arr;
+        };
         auto dump = [&](unsigned int step)
         {
             const std::string suffix = "_" + std::to_string(step) + ".bin";
             for(auto &p : pops) {
-                if(p.kind == "LIF" || p.kind == "IZH") {
-                    const char *v1 = (p.kind == "LIF") ? "RefracTime" : "U";
-                    writeFile(outDir + "/V_" + p.name + suffix, runtime.getArray(*p.ng, "V")->getHostPointer<float>(), p.n);
-                    writeFile(outDir + "/" + v1 + "_" + p.name + suffix, runtime.getArray(*p.ng, v1)->getHostPointer<float>(), p.n);
+                if(p.kind == "LIF" || p.kind == "IZH" || p.kind == "AQIF") {
+                    const char *v1 = (p.kind == "LIF") ? "RefracTime" : (p.kind == "IZH") ? "U" : "W";
+                    writeFile(outDir + "/V_" + p.name + suffix, pulled(runtime.getArray(*p.ng, "V"))->getHostPointer<float>(), p.n);
+                    writeFile(outDir + "/" + v1 + "_" + p.name + suffix, pulled(runtime.getArray(*p.ng, v1))->getHostPointer<float>(), p.n);
                 }
             }
             for(auto &s : syns) {
                 // with fused postsynaptic models only one group per fused set owns outPost
                 try {
-                    auto *arr = runtime.getArray(*s.sg, "outPost");
+                    auto *arr = pulled(runtime.getArray(*s.sg, "outPost"));
                     writeFile(outDir + "/outPost_" + s.name + suffix, arr->getHostPointer<float>(), arr->getCount());
                 }
                 catch(const std::out_of_range&) {}
                 try {
-                    auto *arr = runtime.getArray(*s.sg, "denDelay");
+                    auto *arr = pulled(runtime.getArray(*s.sg, "denDelay"));
                     writeFile(outDir + "/denDelay_" + s.name + suffix, arr->getHostPointer<float>(), arr->getCount());
                 }
                 catch(const std::out_of_range&) {}
                 if(s.wum == "STDP") {
-                    auto *arr = runtime.getArray(*s.sg, "g");
+                    auto *arr = pulled(runtime.getArray(*s.sg, "g"));
                     writeFile(outDir + "/g_" + s.name + suffix, arr->getHostPointer<float>(), arr->getCount());
                 }
             }

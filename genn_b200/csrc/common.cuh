@@ -35,6 +35,12 @@ struct StepState
     // target-tiled kernel, 0 = the one-reduction-per-event kernel delivers
     unsigned int heavy;
     unsigned int reserved;
+    // limits of every wait inside the persistent kernels (set by the host; a wait that runs out sets an
+    // error bit, all CTAs leave the kernel and the host reports it): polls of the grid barrier, polls for
+    // a word another process writes, SM cycles a warp waits for work from another warp of its CTA
+    unsigned long long barrier_spin_limit;
+    unsigned long long exchange_spin_limit;
+    long long stream_wait_cycles;
 };
 
 constexpr unsigned int ERR_SPIKE_OVERFLOW = 1u;

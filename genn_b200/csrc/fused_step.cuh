@@ -76,7 +76,7 @@ constexpr unsigned int FUSED_CHUNK = 32 * PRE_VEC;          // synapses per warp
 constexpr unsigned int FUSED_MAX_SOURCES = 256;             // (population, process, delay) spike sources per model
 constexpr unsigned int FUSED_PREFETCH_IDS = 8;              // spike ids fetched together with each count
 constexpr unsigned int ERR_BARRIER_TIMEOUT = 8u;
-constexpr unsigned long long BARRIER_SPIN_LIMIT = 1ull << 24; // polls (tens of ms) before giving up
+constexpr unsigned long long BARRIER_SPIN_LIMIT = 1ull << 24; // default: polls (tens of ms) before giving up
 
 // One spike source as the presynaptic phase sees it: a (population, axonal
 // delay) pair and the slice of the item table that lists every (group, chunk)
@@ -144,7 +144,7 @@ struct FusedLaunch
     const struct NearSpace *near_spaces; // [neuron groups]
 };
 
-constexpr unsigned long long EXCHANGE_SPIN_LIMIT = 1ull << 23;
+constexpr unsigned long long EXCHANGE_SPIN_LIMIT = 1ull << 23;  // default
 constexpr unsigned int ERR_EXCHANGE_TIMEOUT = 32u;
 
 __device__ __forceinline__ unsigned long long loadAcquireSys(const unsigned long long *p)
@@ -172,7 +172,7 @@ __device__ __forceinline__ unsigned int awaitWord(const unsigned long long *p, u
 {
     unsigned long long w = 0, polls = 0;
     while(((w = loadRelaxedSys(p)) >> 32) != expected) {
-        if(++polls > EXCHANGE_SPIN_LIMIT) {
+        if(++polls > state->exchange_spin_limit) {
             atomicOr(&state->error, ERR_EXCHANGE_TIMEOUT);
             return 0u;
         }
@@ -208,7 +208,7 @@ __device__ __forceinline__ bool gridWait(const unsigned long long *barrier, cons
         unsigned long long polls = 0;
         bool good = true;
         while(loadAcquire(barrier) < epoch) {
-            if(++polls > BARRIER_SPIN_LIMIT) {
+            if(++polls > state->barrier_spin_limit) {
                 atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
                 good = false;
                 break;
@@ -556,7 +556,7 @@ fusedStepKernel(FusedLaunch L)
             if(L.world > 1 && blockIdx.x == 0 && warp == warpsPerBlock - 1u) {
                 unsigned long long polls = 0;
                 while(loadAcquire(L.barrier) < epoch) {
-                    if(++polls > BARRIER_SPIN_LIMIT) {
+                    if(++polls > state->barrier_spin_limit) {
                         atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
                         break;
                     }

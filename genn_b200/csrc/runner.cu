@@ -26,7 +26,6 @@
 #include "fused_step.cuh"
 #include "urgent.cuh"
 #include "stream_step.cuh"
-#include "owner_step.cuh"
 #include "tiled.cuh"
 
 #include <cub/device/device_scan.cuh>
@@ -194,32 +193,11 @@ struct b200_runner
     unsigned char *arena = nullptr;
     size_t arenaBytes = 0;
     unsigned char *peerArena[B200_MAX_RANKS] = {};
+    bool peerLocal[B200_MAX_RANKS] = {};    // mapped by pointer (same process): nothing to close
     unsigned char **peerTable = nullptr;     // device copy of peerArena
     unsigned int rank = 0, world = 1;
     size_t flagsOffset = 0;
     bool sharded() const { return world > 1; }
-
-    // target-stationary persistent path (rings in shared memory, one grid barrier per step)
-    bool ownerEligible = false;
-    bool useOwner = false;       // measured slower than the global-reduction kernel on Potjans: opt-in
-    OwnerCta *ownerCtas = nullptr;
-    OwnerEntry *ownerEntries = nullptr;
-    std::vector<void*> ownerBuffers;        // offsets tables and boundary lists
-    unsigned int ownerTableBytes = 0;
-    size_t ownerSmemBytes = 0;
-    const void *ownerKernel = nullptr;
-    unsigned int ownerGrid = 0;
-    std::string ownerWhyNot;
-    unsigned int ownerItemLanes = 32;
-
-    void dropOwner()
-    {
-        if(ownerCtas) cudaFree(ownerCtas);
-        if(ownerEntries) cudaFree(ownerEntries);
-        for(void *p : ownerBuffers) cudaFree(p);
-        ownerCtas = nullptr; ownerEntries = nullptr; ownerBuffers.clear();
-        ownerEligible = false;
-    }
 
     // target-tiled delivery of heavy steps on the one-launch-per-kernel path (tiled.cuh): private
     // re-packed copy of the non-learning SPARSE groups
@@ -317,200 +295,6 @@ int withNeuronShape(const b200_runner *r, F f)
     return fail(B200_ERR_INVALID, "no kernel instance for this neuron shape");
 }
 
-// Tables of the target-stationary persistent kernel (owner_step.cuh).  Decides
-// eligibility; r->ownerWhyNot says why not.
-int prepareOwner(b200_runner *r, const std::vector<b200_synapse_group> &sparse, bool otherGroups)
-{
-    r->dropOwner();
-    r->ownerWhyNot.clear();
-    auto no = [r](const char *why) { r->ownerWhyNot = why; return B200_OK; };
-    if(!r->useOwner) return no("not requested (option use_owner)");
-    if(r->batch != 1) return no("batch size above 1");
-    if(otherGroups) return no("BITMASK, DENSE or learning groups present");
-    if(r->neuronGroups.empty()) return no("no neuron groups");
-    int sms = 0, coop = 0;
-    CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device));
-    CUDA_TRY(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, r->device));
-    if(!coop) return no("device without cooperative launch");
-    const unsigned int grid = (unsigned int)sms;
-
-    // neuron slots: groups padded to warps, dealt to CTAs in equal blocks
-    const size_t numNG = r->neuronGroups.size();
-    std::vector<unsigned int> slotStart{0};
-    for(const auto &g : r->neuronGroups) slotStart.push_back(slotStart.back() + ((g.num_update + 31u) & ~31u));
-    const unsigned int totalSlots = slotStart.back();
-    const unsigned int perCta = (((totalSlots + grid - 1) / grid) + 31u) & ~31u;
-    if(perCta == 0) return no("no neurons to update");
-    if(perCta > OWNER_BLOCK) return no("more neurons per SM than one CTA can own");
-
-    // spike sources, as the other persistent kernel keys them
-    std::vector<std::pair<const uint32_t*, uint32_t>> sourceKeys;
-    std::vector<unsigned int> sourceOf(sparse.size());
-    for(size_t gi = 0; gi < sparse.size(); gi++) {
-        const auto &g = sparse[gi];
-        if(g.axonal_delay + 3 > g.src_delay_slots) return no("spike queue has fewer than delay + 3 slots");
-        size_t si = 0;
-        for(; si < sourceKeys.size(); si++) {
-            if(sourceKeys[si].first == g.src_spk_cnt && sourceKeys[si].second == g.axonal_delay) break;
-        }
-        if(si == sourceKeys.size()) sourceKeys.emplace_back(g.src_spk_cnt, g.axonal_delay);
-        sourceOf[gi] = (unsigned int)si;
-    }
-    if(sourceKeys.size() > 32) return no("more than 32 spike sources");
-
-    // target neuron group and fused PSM of every synapse group
-    std::vector<unsigned int> trgOf(sparse.size()), psmOf(sparse.size());
-    for(size_t gi = 0; gi < sparse.size(); gi++) {
-        const auto &g = sparse[gi];
-        bool found = false;
-        for(size_t t = 0; t < numNG && !found; t++) {
-            const auto &ng = r->neuronGroups[t];
-            for(unsigned int m = 0; m < ng.num_psm && !found; m++) {
-                const bool same = g.max_den_delay ? (ng.psm[m].den_delay == g.den_delay && ng.psm[m].max_den_delay == g.max_den_delay)
-                                                  : (ng.psm[m].out_post == g.out_post && ng.psm[m].max_den_delay == 0);
-                if(same) { trgOf[gi] = (unsigned int)t; psmOf[gi] = m; found = true; }
-            }
-        }
-        if(!found) return no("a synapse group's target buffer belongs to no neuron group");
-    }
-
-    // pieces per CTA, owners per target group
-    std::vector<OwnerCta> ctas(grid);
-    std::vector<std::vector<unsigned int>> bounds(numNG);       // first post id of each owner, then the end
-    std::vector<std::vector<std::pair<unsigned int, unsigned int>>> owners(numNG);   // (cta, piece)
-    size_t maxTileFloats = 0;
-    for(unsigned int c = 0; c < grid; c++) {
-        OwnerCta &cta = ctas[c];
-        memset(&cta, 0, sizeof(cta));
-        const unsigned int lo = std::min(totalSlots, c * perCta), hi = std::min(totalSlots, (c + 1) * perCta);
-        unsigned int tileFloats = 0;
-        for(size_t t = 0; t < numNG; t++) {
-            const unsigned int a = std::max(lo, slotStart[t]), b = std::min(hi, slotStart[t + 1]);
-            if(a >= b) continue;
-            const auto &ng = r->neuronGroups[t];
-            const unsigned int first = a - slotStart[t];
-            if(first >= ng.num_update) continue;                 // only padding
-            const unsigned int n = std::min(b - slotStart[t], ng.num_update) - first;
-            if(cta.num_pieces == OWNER_MAX_PIECES) return no("a CTA's neurons span too many populations");
-            OwnerPiece &pc = cta.piece[cta.num_pieces];
-            pc.group = (unsigned int)t;
-            pc.lo = first;
-            pc.n = n;
-            pc.thread0 = a - lo;
-            for(unsigned int m = 0; m < ng.num_psm; m++) {
-                pc.tile[m] = tileFloats;
-                tileFloats += std::max(1u, ng.psm[m].max_den_delay) * n;
-            }
-            owners[t].emplace_back(c, cta.num_pieces);
-            bounds[t].push_back(ng.first_neuron + first);
-            cta.num_pieces++;
-        }
-        cta.tile_floats = tileFloats;
-        maxTileFloats = std::max<size_t>(maxTileFloats, tileFloats);
-    }
-    for(size_t t = 0; t < numNG; t++) bounds[t].push_back(r->neuronGroups[t].first_neuron + r->neuronGroups[t].num_update);
-
-    // device copies of the boundaries, segment-offset tables, sortedness check
-    std::vector<unsigned int*> dBounds(numNG, nullptr);
-    for(size_t t = 0; t < numNG; t++) {
-        CUDA_TRY(cudaMalloc(&dBounds[t], sizeof(unsigned int) * bounds[t].size()));
-        r->ownerBuffers.push_back(dBounds[t]);
-        CUDA_TRY(cudaMemcpyAsync(dBounds[t], bounds[t].data(), sizeof(unsigned int) * bounds[t].size(), cudaMemcpyHostToDevice, r->stream));
-    }
-    CUDA_TRY(cudaStreamSynchronize(r->stream));
-    unsigned int errBefore = 0;
-    CUDA_TRY(cudaMemcpy(&errBefore, &r->state->error, sizeof(unsigned int), cudaMemcpyDeviceToHost));
-    std::vector<unsigned int*> dOffsets(sparse.size(), nullptr);
-    for(size_t gi = 0; gi < sparse.size(); gi++) {
-        const auto &g = sparse[gi];
-        const unsigned int nb = (unsigned int)bounds[trgOf[gi]].size();
-        const unsigned long long count = (unsigned long long)g.num_src * nb;
-        CUDA_TRY(cudaMalloc(&dOffsets[gi], sizeof(unsigned int) * std::max<unsigned long long>(count, 1ull)));
-        r->ownerBuffers.push_back(dOffsets[gi]);
-        const unsigned long long total = (unsigned long long)g.num_src * g.row_stride;
-        const unsigned int blocksA = (unsigned int)std::min<unsigned long long>((total + 255) / 256, 148u * 32u);
-        const unsigned int blocksB = (unsigned int)std::min<unsigned long long>((count + 255) / 256, 148u * 32u);
-        int e = withIndType(g.ind_bytes, [&](auto tag) -> int {
-            using IndT = decltype(tag);
-            if(blocksA) ownerCheckSortedKernel<IndT><<<blocksA, 256, 0, r->stream>>>(g.row_length, g.ind, g.num_src, g.num_trg, g.row_stride, r->state);
-            if(blocksB) ownerBuildOffsetsKernel<IndT><<<blocksB, 256, 0, r->stream>>>(g.row_length, g.ind, g.num_src, g.row_stride,
-                                                                                     dBounds[trgOf[gi]], nb, dOffsets[gi]);
-            return B200_OK;
-        });
-        if(e) return e;
-        r->launches += 2;
-    }
-    CUDA_TRY(cudaStreamSynchronize(r->stream));
-    CUDA_TRY(cudaPeekAtLastError());
-    unsigned int errAfter = 0;
-    CUDA_TRY(cudaMemcpy(&errAfter, &r->state->error, sizeof(unsigned int), cudaMemcpyDeviceToHost));
-    if(errAfter & ERR_ROWS_UNSORTED) {
-        // not an error: the model simply takes another path
-        const unsigned int keep = (errAfter & ~ERR_ROWS_UNSORTED) | (errBefore & ERR_ROWS_UNSORTED);
-        CUDA_TRY(cudaMemcpy(&r->state->error, &keep, sizeof(unsigned int), cudaMemcpyHostToDevice));
-        r->dropOwner();
-        return no("rows are not sorted by postsynaptic index");
-    }
-
-    // entries: every (owned piece, incoming synapse group) pair of every CTA
-    std::vector<OwnerEntry> entries;
-    size_t maxEntries = 0;
-    for(unsigned int c = 0; c < grid; c++) {
-        OwnerCta &cta = ctas[c];
-        cta.entry_begin = (unsigned int)entries.size();
-        for(unsigned int q = 0; q < cta.num_pieces; q++) {
-            const unsigned int t = cta.piece[q].group;
-            unsigned int ordinal = 0;
-            for(; ordinal < owners[t].size(); ordinal++) {
-                if(owners[t][ordinal].first == c && owners[t][ordinal].second == q) break;
-            }
-            for(size_t gi = 0; gi < sparse.size(); gi++) {
-                if(trgOf[gi] != t) continue;
-                OwnerEntry en;
-                en.source = sourceOf[gi];
-                en.sgroup = (unsigned int)gi;
-                en.piece = q;
-                en.boundary = ordinal;
-                en.psm = psmOf[gi];
-                en.num_bounds = (unsigned int)bounds[t].size();
-                en.offsets = dOffsets[gi];
-                entries.push_back(en);
-            }
-        }
-        cta.num_entries = (unsigned int)entries.size() - cta.entry_begin;
-        maxEntries = std::max<size_t>(maxEntries, cta.num_entries);
-    }
-    r->ownerTableBytes = (unsigned int)(align16(sizeof(b200_neuron_group) * numNG) + align16(sizeof(b200_synapse_group) * sparse.size()) +
-                                        align16(sizeof(FusedSource) * sourceKeys.size()) + align16(sizeof(OwnerEntry) * maxEntries));
-    r->ownerSmemBytes = r->ownerTableBytes + maxTileFloats * sizeof(float);
-    if(r->ownerSmemBytes > 220 * 1024) {
-        r->dropOwner();
-        return no("dendritic-delay rings of one CTA's neurons do not fit shared memory");
-    }
-    CUDA_TRY(cudaMalloc(&r->ownerCtas, sizeof(OwnerCta) * grid));
-    CUDA_TRY(cudaMemcpy(r->ownerCtas, ctas.data(), sizeof(OwnerCta) * grid, cudaMemcpyHostToDevice));
-    CUDA_TRY(cudaMalloc(&r->ownerEntries, sizeof(OwnerEntry) * std::max<size_t>(entries.size(), 1)));
-    if(!entries.empty()) {
-        CUDA_TRY(cudaMemcpy(r->ownerEntries, entries.data(), sizeof(OwnerEntry) * entries.size(), cudaMemcpyHostToDevice));
-    }
-    int e = withNeuronShape(r, [&](auto P, auto C) -> int {
-        auto kernel = ownerStepKernel<decltype(P)::value, decltype(C)::value>;
-        r->ownerKernel = (const void*)kernel;
-        CUDA_TRY(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)r->ownerSmemBytes));
-        int perSM = 0;
-        CUDA_TRY(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&perSM, kernel, OWNER_BLOCK, r->ownerSmemBytes));
-        if(perSM < 1) r->ownerWhyNot = "kernel does not fit an SM";
-        return B200_OK;
-    });
-    if(e) return e;
-    if(!r->ownerWhyNot.empty()) {
-        r->dropOwner();
-        return B200_OK;
-    }
-    r->ownerGrid = grid;
-    r->ownerEligible = true;
-    return B200_OK;
-}
 
 // Tables of the persistent fused-step kernel for the current schedule: spike
 // sources, the two item lists of each, thread slots, shared-memory budget, grid.
@@ -710,11 +494,6 @@ int prepare(b200_runner *r)
         const int e = buildFusedTables(r);
         if(e) return e;
     }
-    // ---- tables of the target-stationary persistent kernel -------------------------------
-    {
-        const int e = prepareOwner(r, sparse, !postSpan.empty() || !learn.empty());
-        if(e) return e;
-    }
 
     // ---- ring period: least common multiple of every ring size ----------------------
     {
@@ -743,43 +522,6 @@ int prepare(b200_runner *r)
     return B200_OK;
 }
 
-int launchOwner(b200_runner *r, unsigned long long numSteps, unsigned long long numRec)
-{
-    OwnerLaunch L;
-    L.neuron.groups = r->neuronTable.d;
-    L.neuron.block_start = r->neuronTable.blockStart;
-    L.neuron.num_groups = r->neuronTable.num;
-    L.neuron.batch = 1;
-    L.neuron.dt = r->dt;
-    L.neuron.seed = r->seed;
-    L.neuron.num_recording_timesteps = numRec;
-    L.neuron.state = r->state;
-    L.neuron.count_events = r->countEvents ? 1u : 0u;
-    L.sgroups = r->sparseTable.d;
-    L.sources = r->fusedSources;
-    L.ctas = r->ownerCtas;
-    L.entries = r->ownerEntries;
-    L.num_sources = r->fusedNumSources;
-    L.num_sgroups = r->sparseTable.num;
-    L.table_bytes = r->ownerTableBytes;
-    L.item_lanes = r->ownerItemLanes;
-    L.count_events = r->countEvents ? 1u : 0u;
-    L.profile = r->fusedProfile ? 1u : 0u;
-    L.num_steps = numSteps;
-    L.barrier = r->fusedBarrier;
-    if(r->fusedProfile && !r->fusedCtaCycles) {
-        CUDA_TRY(cudaMalloc(&r->fusedCtaCycles, sizeof(unsigned long long) * 5 * r->fusedGrid));
-        CUDA_TRY(cudaMemsetAsync(r->fusedCtaCycles, 0, sizeof(unsigned long long) * 5 * r->fusedGrid, r->stream));
-    }
-    L.cta_cycles = r->fusedProfile ? r->fusedCtaCycles : nullptr;
-    CUDA_TRY(cudaMemsetAsync(r->fusedBarrier, 0, sizeof(unsigned long long), r->stream));
-    void *args[] = {&L};
-    CUDA_TRY(cudaLaunchCooperativeKernel(r->ownerKernel, dim3(r->ownerGrid), dim3(OWNER_BLOCK), args,
-                                         r->ownerSmemBytes, r->stream));
-    r->launches++;
-    r->fusedLaunches++;
-    return B200_OK;
-}
 
 // Near-synapse table of the "deliver at emission" schedule; leaves r->schedule alone if the model
 // does not qualify (a group without a delay ring of three slots or more, an axonal delay, a ring
@@ -1540,6 +1282,10 @@ int b200_runner_create(int device, double dt, uint64_t seed, uint32_t batch_size
     CUDA_TRY(cudaStreamCreateWithFlags(&r->stream, cudaStreamNonBlocking));
     CUDA_TRY(cudaMalloc(&r->state, sizeof(StepState)));
     CUDA_TRY(cudaMemset(r->state, 0, sizeof(StepState)));
+    {
+        const unsigned long long limits[3] = {BARRIER_SPIN_LIMIT, EXCHANGE_SPIN_LIMIT, (unsigned long long)STREAM_WAIT_CYCLES};
+        CUDA_TRY(cudaMemcpy(&r->state->barrier_spin_limit, limits, sizeof(limits), cudaMemcpyHostToDevice));
+    }
     CUDA_TRY(cudaEventCreate(&r->evA));
     CUDA_TRY(cudaEventCreate(&r->evB));
     CUDA_TRY(cudaEventCreate(&r->evC));
@@ -1568,9 +1314,8 @@ int b200_runner_destroy(b200_runner *r)
     r->dropNear();
     if(r->fusedCtaCycles) cudaFree(r->fusedCtaCycles);
     r->dropTiled();
-    r->dropOwner();
     for(unsigned int p = 0; p < B200_MAX_RANKS; p++) {
-        if(r->peerArena[p]) cudaIpcCloseMemHandle(r->peerArena[p]);
+        if(r->peerArena[p] && !r->peerLocal[p]) cudaIpcCloseMemHandle(r->peerArena[p]);
     }
     if(r->arena) cudaFree(r->arena);
     if(r->peerTable) cudaFree(r->peerTable);
@@ -1648,6 +1393,18 @@ int b200_exchange_open_peer(b200_runner *r, uint32_t peer_rank, const void *hand
     r->peerArena[peer_rank] = static_cast<unsigned char*>(p);
     if(!r->peerTable) CUDA_TRY(cudaMalloc(&r->peerTable, sizeof(unsigned char*) * B200_MAX_RANKS));
     CUDA_TRY(cudaMemcpy(r->peerTable, r->peerArena, sizeof(unsigned char*) * B200_MAX_RANKS, cudaMemcpyHostToDevice));
+    return B200_OK;
+}
+
+int b200_exchange_set_peer(b200_runner *r, uint32_t peer_rank, void *device_ptr)
+{
+    if(!r || peer_rank >= B200_MAX_RANKS || !device_ptr) return fail(B200_ERR_INVALID, "bad peer rank or pointer");
+    if(r->peerArena[peer_rank]) return fail(B200_ERR_STATE, "peer %u already opened", peer_rank);
+    CUDA_TRY(cudaSetDevice(r->device));
+    r->peerArena[peer_rank] = static_cast<unsigned char*>(device_ptr);
+    if(!r->peerTable) CUDA_TRY(cudaMalloc(&r->peerTable, sizeof(unsigned char*) * B200_MAX_RANKS));
+    CUDA_TRY(cudaMemcpy(r->peerTable, r->peerArena, sizeof(unsigned char*) * B200_MAX_RANKS, cudaMemcpyHostToDevice));
+    r->peerLocal[peer_rank] = true;
     return B200_OK;
 }
 
@@ -1917,10 +1674,19 @@ int b200_set_option(b200_runner *r, const char *name, double value)
     else if(n == "lag_agreed") { r->lagAgreed = (value != 0.0); r->lagStale = true; }
     else if(n == "rescan_delays") r->lagStale = true;
     else if(n == "fused_profile") r->fusedProfile = (value != 0.0);
-    else if(n == "use_owner") { r->useOwner = (value != 0.0); r->dirty = true; }
-    else if(n == "owner_item_lanes") r->ownerItemLanes = (value <= 8.0) ? 8u : (value <= 16.0) ? 16u : 32u;
     else if(n == "fused_blocks_per_sm") { r->fusedBlocksPerSM = (unsigned int)value; r->dirty = true; }
     else if(n == "graph_steps") r->graphSteps = std::max(1u, (unsigned int)value);
+    else if(n == "barrier_spin_limit" || n == "exchange_spin_limit" || n == "stream_wait_cycles") {
+        // limits of the waits inside the persistent kernels (polls, polls, SM cycles); a wait that runs out
+        // makes the launch return early and b200_synchronize report it
+        if(value < 1.0) return fail(B200_ERR_INVALID, "%s must be at least 1", name);
+        const unsigned long long v = (unsigned long long)value;
+        unsigned long long *dst = (n == "barrier_spin_limit") ? &r->state->barrier_spin_limit
+                                : (n == "exchange_spin_limit") ? &r->state->exchange_spin_limit
+                                : reinterpret_cast<unsigned long long*>(&r->state->stream_wait_cycles);
+        CUDA_TRY(cudaStreamSynchronize(r->stream));
+        CUDA_TRY(cudaMemcpy(dst, &v, sizeof(v), cudaMemcpyHostToDevice));
+    }
     else if(n == "use_tiled") { r->useTiled = (value != 0.0); r->tiledStale = true; }
     else if(n == "tiled_min_events") r->tiledMinEvents = (float)value;
     else return fail(B200_ERR_INVALID, "unknown option %s", name);
@@ -2061,10 +1827,9 @@ int b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_ti
                                     "non-learning groups, per-kernel timing off)");
     }
     if(r->useFused && r->fusedEligible && !r->timing) {
-        const bool owner = !r->sharded() && r->useOwner && r->ownerEligible;
         while(left) {
             const uint64_t n = std::min<uint64_t>(left, 1ull << 20);
-            e = owner ? launchOwner(r, n, num_recording_timesteps) : launchFused(r, n, num_recording_timesteps);
+            e = launchFused(r, n, num_recording_timesteps);
             if(e) return e;
             left -= n;
         }
@@ -2257,8 +2022,8 @@ int b200_get_step_path(b200_runner *r, int *path, char *why, size_t why_bytes)
 {
     const int e = prepare(r);
     if(e) return e;
-    *path = (r->useFused && r->fusedEligible) ? ((r->useOwner && r->ownerEligible) ? 2 : 1) : 0;
-    if(why && why_bytes) snprintf(why, why_bytes, "%s", r->ownerWhyNot.c_str());
+    *path = (r->useFused && r->fusedEligible) ? 1 : 0;
+    if(why && why_bytes) snprintf(why, why_bytes, "%s", r->fusedEligible ? "" : "batch > 1, or groups that are not SPARSE and non-learning");
     return B200_OK;
 }
 

@@ -34,7 +34,7 @@ namespace b200
 {
 // Backstop for the waits between the two sets of warps (clock cycles, about half a minute): every
 // wait of the other side is itself bounded and far shorter, so this only ends a CTA whose partner died.
-constexpr long long STREAM_WAIT_CYCLES = 1ll << 36;
+constexpr long long STREAM_WAIT_CYCLES = 4000000000ll;   // default: about two seconds
 
 // Barrier over the chain warps only (named barrier 1); the stream warps never join it.
 __device__ __forceinline__ void chainSync(unsigned int chainThreads)
@@ -424,7 +424,7 @@ streamStepKernel(FusedLaunch L)
             const long long since = clock64();
             bool alive = true;
             while(sh.stepPassed < (unsigned int)c) {
-                if(sh.stop || clock64() - since > STREAM_WAIT_CYCLES) { alive = false; break; }
+                if(sh.stop || clock64() - since > state->stream_wait_cycles) { alive = false; break; }
                 __nanosleep(200);
             }
             // go on or leave TOGETHER (a warp that left alone would hang the others of its set on their
@@ -467,7 +467,7 @@ streamStepKernel(FusedLaunch L)
             const long long since = clock64();
             while(sh.headReady < (unsigned int)(step + 1)) {
                 if(sh.stop) return;
-                if(clock64() - since > STREAM_WAIT_CYCLES) {
+                if(clock64() - since > state->stream_wait_cycles) {
                     if(lane == 0) atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
                     return;
                 }
@@ -537,7 +537,7 @@ streamStepKernel(FusedLaunch L)
             if(lane == 0) {
                 unsigned long long polls = 0;
                 while(loadAcquire(L.barrier) < epoch) {
-                    if(++polls > BARRIER_SPIN_LIMIT) {
+                    if(++polls > state->barrier_spin_limit) {
                         atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
                         good = false;
                         break;
@@ -554,7 +554,7 @@ streamStepKernel(FusedLaunch L)
                     ((long long)lane - (long long)L.rank) * (long long)g0.num_delay_slots + peersSlot;
                 unsigned long long polls = 0;
                 while((loadRelaxedSys(word) >> 32) != peersAt) {
-                    if(++polls > EXCHANGE_SPIN_LIMIT) {
+                    if(++polls > state->exchange_spin_limit) {
                         atomicOr(&state->error, ERR_EXCHANGE_TIMEOUT);
                         break;
                     }
@@ -620,7 +620,7 @@ streamStepKernel(FusedLaunch L)
             if(prof) c1 = since;
             for(unsigned int w = 0; w < streamWarps; w++) {
                 while(sh.streamDone[w] < (unsigned int)step) {
-                    if(clock64() - since > STREAM_WAIT_CYCLES) {
+                    if(clock64() - since > state->stream_wait_cycles) {
                         atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
                         break;
                     }
@@ -719,7 +719,7 @@ streamStepKernel(FusedLaunch L)
             const long long since = clock64();
             for(unsigned int w = 0; w < streamWarps && (gridDim.x < 2u || ((step - 1) & 1u) == (blockIdx.x & 1u)); w++) {
                 while(sh.streamDone[w] < (unsigned int)(step - 1)) {
-                    if(clock64() - since > STREAM_WAIT_CYCLES) {
+                    if(clock64() - since > state->stream_wait_cycles) {
                         atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
                         break;
                     }
@@ -742,7 +742,7 @@ streamStepKernel(FusedLaunch L)
             if(lane == 0) {
                 unsigned long long polls = 0;
                 while(loadAcquire(L.barrier) < epoch) {
-                    if(++polls > BARRIER_SPIN_LIMIT) {
+                    if(++polls > state->barrier_spin_limit) {
                         atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
                         break;
                     }

@@ -317,10 +317,12 @@ class SynapseGroup:
     def weight_kind(self) -> str:
         return "CONSTANT" if self.wu.snippet == "StaticPulseConstantWeight" else "INDIVIDUAL"
 
-    def set_sparse_connections(self, pre_indices, post_indices):
+    def set_sparse_connections(self, pre_indices, post_indices, presorted: bool = False):
         """Host-supplied connectivity (genn_groups.py:434-470): the pairs are
         sorted by (pre, post) and per-synapse variable arrays passed to
-        ``init_weight_update`` are re-ordered the same way; multapses are kept."""
+        ``init_weight_update`` are re-ordered the same way; multapses are kept.
+        ``presorted``: the pairs already come row by row (non-decreasing presynaptic
+        index) and are kept in the order given (no sort: large host-generated networks)."""
         if self.matrix_type not in ("SPARSE", "BITMASK"):
             raise Exception("set_sparse_connections only supports SPARSE and BITMASK format connectivity")
         pre = np.asarray(pre_indices, dtype=np.uint32)
@@ -329,9 +331,15 @@ class SynapseGroup:
             raise Exception("pre and post synaptic index lists must be 1D arrays of the same length")
         if len(pre) and (pre.max() >= self.src.num_neurons or post.max() >= self.trg.num_neurons):
             raise Exception("synaptic indices out of range")
-        order = np.lexsort((post, pre))
-        self._pre = pre[order]
-        self._post = post[order]
+        if presorted:
+            if len(pre) > 1 and np.any(pre[1:] < pre[:-1]):
+                raise Exception("presorted connectivity must have non-decreasing presynaptic indices")
+            order = None
+            self._pre, self._post = pre, post
+        else:
+            order = np.lexsort((post, pre))
+            self._pre = pre[order]
+            self._post = post[order]
         self._order = order
         row_lengths = np.bincount(self._pre, minlength=self.src.num_neurons).astype(np.uint32)
         self.row_lengths = row_lengths

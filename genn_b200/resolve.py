@@ -228,7 +228,7 @@ def resolve(model: GeNNModel) -> Net:
                     arr = np.full(n_syn, arr, dtype=dtype)
                 elif len(arr) != n_syn:
                     raise ValueError(f"{sg.name}.{name}: {len(arr)} values for {n_syn} synapses")
-                else:
+                elif sg._order is not None:
                     arr = arr[sg._order]
                 per_syn[name] = arr
             elif matrix == "DENSE":

@@ -99,7 +99,7 @@ class Runtime:
 
     def __init__(self, model, num_recording_timesteps: Optional[int] = None, device: int = 0,
                  shard: Optional[Tuple[int, int]] = None, net: Optional[Net] = None, exchange=None,
-                 sharded_emit: Optional[bool] = None):
+                 sharded_emit: Optional[bool] = None, local_peers=None):
         self.lib = abi.load_library()
         self.model = model
         self.device = int(device)
@@ -113,6 +113,8 @@ class Runtime:
         self._rec_host = {}
         self._rec_timestep = 0
         self.shard = shard
+        # rank -> device pointer of a peer arena that is already addressable in this process
+        self.local_peers = dict(local_peers or {})
         self.plan = Plan(self.net, self.factory, self.num_recording_timesteps, shard=shard)
         if shard is not None and shard[1] > 1:
             self._connect_peers(exchange)
@@ -154,7 +156,14 @@ class Runtime:
         if len(handles) != world:
             raise abi.B200Error(f"expected {world} arena handles, got {len(handles)}")
         for peer, h in enumerate(handles):
-            if peer != rank:
+            if peer == rank:
+                continue
+            if peer in self.local_peers:
+                # a pointer, or a callable that is given the arena size and returns one
+                where = self.local_peers[peer]
+                where = where(self.plan.exchange.nbytes) if callable(where) else where
+                check(self.lib.b200_exchange_set_peer(self.handle, peer, C.c_void_p(where)))
+            else:
                 check(self.lib.b200_exchange_open_peer(self.handle, peer, C.create_string_buffer(h, 64)))
         check(self.lib.b200_exchange_configure(self.handle, rank, world))
 

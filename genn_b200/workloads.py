@@ -33,11 +33,13 @@ def poisson_spike_trains(rng, n: int, rate_hz: float, duration_ms: float):
 
 def truncated_normal(rng, mean: float, sd: float, lo: float, hi: float, size: int) -> np.ndarray:
     """Normal draws re-sampled until they fall inside [lo, hi], the semantics of
-    the reference's NormalClipped snippets (initVarSnippet.h:163-172)."""
-    out = rng.normal(mean, sd, size=size)
+    the reference's NormalClipped snippets (initVarSnippet.h:163-172); fp32."""
+    out = rng.standard_normal(size=size, dtype=np.float32)
+    out *= np.float32(sd)
+    out += np.float32(mean)
     bad = np.nonzero((out > hi) | (out < lo))[0]
     while len(bad):
-        out[bad] = rng.normal(mean, sd, size=len(bad))
+        out[bad] = rng.standard_normal(size=len(bad), dtype=np.float32) * np.float32(sd) + np.float32(mean)
         bad = bad[(out[bad] > hi) | (out[bad] < lo)]
     return out
 
@@ -199,8 +201,11 @@ def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
         ns, nt = pops[src].num_neurons, pops[trg].num_neurons
         lo, hi = (0.0, float(np.finfo(np.float32).max)) if mean_w > 0 else (-float(np.finfo(np.float32).max), 0.0)
         if host_connectivity:
-            pre = rng.integers(0, ns, size=num).astype(np.uint32)
-            post = rng.integers(0, nt, size=num).astype(np.uint32)
+            # `num` synapses placed uniformly with replacement (FixedNumberTotalWithReplacement): the row
+            # lengths are multinomial; drawing them first gives the pairs row by row without a sort
+            counts = rng.multinomial(num, np.full(ns, 1.0 / ns))
+            pre = np.repeat(np.arange(ns, dtype=np.uint32), counts)
+            post = rng.integers(0, nt, size=num, dtype=np.uint32)
             g = truncated_normal(rng, mean_w, sd_w, lo, hi, num).astype(np.float32)
             # NormalClippedDelay: truncated normal in time steps, then rint
             d = np.rint(truncated_normal(rng, md / dt, sd / dt, min_delay / dt, mxd / dt, num)).astype(np.uint8)
@@ -213,7 +218,7 @@ def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
             wu = init_weight_update("StaticPulseDendriticDelay", {}, {"g": g, "d": d})
             sg = m.add_synapse_population(f"{src}_{trg}", "SPARSE", pops[src], pops[trg], wu,
                                           init_postsynaptic("ExpCurr", {"tau": 0.5}))
-            sg.set_sparse_connections(pre, post)
+            sg.set_sparse_connections(pre, post, presorted=True)
         else:
             trg_range = None
             if shard is not None:

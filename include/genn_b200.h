@@ -135,8 +135,7 @@ typedef struct b200_neuron_group {
     uint32_t model;            /* b200_neuron_model */
     uint32_t num_neurons;
     uint32_t num_delay_slots;  /* spike queue depth: at least longest axonal/back-propagation delay + 2;
-                                  + 3 lets the target-stationary persistent kernel be used, + 4 lets the
-                                  persistent kernel deliver spikes one step late (option "use_lag") */
+                                  + 4 lets the persistent kernel deliver spikes one step late (option "use_lag") */
     uint32_t num_psm;
     uint32_t num_cs;
     uint32_t rng_stream;
@@ -255,6 +254,9 @@ int  b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes
 int  b200_exchange_alloc(b200_runner *r, size_t bytes, void **device_ptr);
 int  b200_exchange_get_handle(b200_runner *r, void *handle_64_bytes);
 int  b200_exchange_open_peer(b200_runner *r, uint32_t peer_rank, const void *handle_64_bytes);
+/* A peer whose arena is already addressable in THIS process (another runner of the same process, on this
+ * device or on one with peer access enabled): registered by pointer instead of an IPC handle. */
+int  b200_exchange_set_peer(b200_runner *r, uint32_t peer_rank, void *device_ptr);
 int  b200_exchange_configure(b200_runner *r, uint32_t rank, uint32_t world);
 /* Sharded models, "deliver at emission" schedule (no reference counterpart: the reference does not shard a
  * model).  The thread that makes a neuron spike delivers that neuron's synapses of dendritic delay 0 and
@@ -325,19 +327,22 @@ int  b200_get_steps_done(b200_runner *r, uint64_t *steps);
 int  b200_get_counter(b200_runner *r, const char *name, uint64_t *value);
 /* Tuning knobs (the counterpart of the backend Preferences, backends/cuda/backend.h:64-115):
  * "spike_lanes" (grid.y of the SPARSE kernel), "use_graph", "graph_steps", "count_events",
- * "use_fused" (persistent kernels), "use_owner" (target-stationary persistent kernel),
+ * "use_fused" (persistent kernels),
  * "fused_blocks_per_sm", "fused_profile",
  * "use_lag" (default 1: when no synapse has dendritic delay 0 the persistent kernel delivers each spike one
  * step later into the ring slot one nearer, same result, one grid barrier per step instead of two),
  * "lag_agreed" (sharded model: the caller has checked "lag_eligible" on EVERY process; without it a sharded
  * model keeps the two-barrier schedule), "rescan_delays" (delay arrays were changed by something other than
- * this library's push / init calls). */
+ * this library's push / init calls), "use_tiled" / "tiled_min_events" (target-tiled SPARSE delivery of steps
+ * with at least that many estimated events on the one-launch-per-kernel path),
+ * "barrier_spin_limit" / "exchange_spin_limit" (polls) and "stream_wait_cycles" (SM cycles): how long a wait
+ * inside a persistent kernel lasts before the launch gives up and b200_synchronize reports
+ * B200_ERR_DEVICE_CHECK (defaults: tens of milliseconds; about two seconds). */
 int  b200_set_option(b200_runner *r, const char *name, double value);
 
-/* Which time-step path b200_step_time takes for the registered model: 2 = target-stationary
- * persistent kernel (rings in shared memory, one grid barrier per step), 1 = persistent kernel with
- * global reductions (two barriers per step), 0 = one launch per kernel (CUDA graph).  `why`
- * (may be NULL) receives the reason path 2 was not chosen. */
+/* Which time-step path b200_step_time takes for the registered model: 1 = persistent kernel (one
+ * cooperative launch runs all the steps), 0 = one launch per kernel (CUDA graph).  `why` (may be NULL)
+ * receives the reason the persistent kernel was not chosen. */
 int  b200_get_step_path(b200_runner *r, int *path, char *why, size_t why_bytes);
 
 /* ---- timers: neuronUpdateTime etc. (generateRunner.cc:159-222) ------------- */

@@ -17,32 +17,28 @@ pytestmark = pytest.mark.gpu
 
 RTOL, ATOL = 1e-5, 2e-6
 
-# the time-step paths: target-stationary persistent kernel; persistent kernel with
-# global reductions in each of its schedules (spikes one step late where no synapse
+# the time-step paths: the persistent kernel in each of its schedules (spikes one step late where no synapse
 # arrives in the same step; only the same-step synapses before the neuron update;
 # everything before it; near synapses delivered by the spiking thread itself; the
 # split schedule on the warp-specialised kernel and on the plain one); one launch per
-# kernel.  (use_fused, use_owner, use_lag, use_emit, use_split, stream_warps)
-PATHS = {"owner": (1, 1, 1, 1, 1, -1), "persistent": (1, 0, 1, 1, 1, -1), "persistent-emit": (1, 0, 0, 1, 1, -1),
-         "persistent-split": (1, 0, 0, 0, 1, -1), "persistent-split-one-warp-set": (1, 0, 0, 0, 1, 0),
-         "persistent-plain": (1, 0, 0, 0, 0, -1), "per-kernel": (0, 0, 1, 1, 1, -1),
+# kernel.  (use_fused, use_lag, use_emit, use_split, stream_warps)
+PATHS = {"persistent": (1, 1, 1, 1, -1), "persistent-emit": (1, 0, 1, 1, -1),
+         "persistent-split": (1, 0, 0, 1, -1), "persistent-split-one-warp-set": (1, 0, 0, 1, 0),
+         "persistent-plain": (1, 0, 0, 0, -1), "per-kernel": (0, 1, 1, 1, -1),
          # one launch per kernel with EVERY step delivered by the target-tiled kernel (shared-memory
          # accumulation over the private tile-major copy), which production takes only for heavy steps
-         "per-kernel-tiled": (0, 0, 1, 1, 1, -1)}
+         "per-kernel-tiled": (0, 1, 1, 1, -1)}
 # networks whose SPARSE groups the target-tiled kernel serves (non-learning)
 TILED_CASES = {"ff_sparse", "c1_full", "ff_sparse_narrow", "potjans_mini", "potjans_mini_d1", "cond_delay", "izhikevich"}
 # networks whose every synapse has a dendritic delay of at least one step
 LAG_CASES = {"potjans_mini_d1"}
 # networks with dendritic-delay rings (some of whose synapses may arrive in the same step)
 RING_CASES = {"potjans_mini", "potjans_mini_d1"}
-# networks the target-stationary kernel must accept (SPARSE, sorted rows, no learning)
-OWNER_CASES = {"ff_sparse", "ff_sparse_narrow", "potjans_mini", "potjans_mini_d1", "cond_delay", "izhikevich"}
 
 
 def _select(rt, path, name=None):
-    fused, owner, lag, emit, split, stream = PATHS[path]
+    fused, lag, emit, split, stream = PATHS[path]
     rt.set_option("use_fused", fused)
-    rt.set_option("use_owner", owner)
     rt.set_option("use_lag", lag)
     rt.set_option("use_emit", emit)
     rt.set_option("use_split", split)
@@ -57,9 +53,6 @@ def _select(rt, path, name=None):
         assert rt.schedule == want, f"{name}: schedule {rt.schedule}, expected {want}"
         assert rt.lagging == (want == 2 and bool(fused))
         assert (rt.counter("stream_warps") > 0) == (want in (1, 3) and stream != 0), "warp-specialised kernel expected"
-    if path == "owner" and name in OWNER_CASES:
-        taken, why = rt.step_path()
-        assert taken == 2, f"{name} should run on the target-stationary kernel: {why}"
 
 
 def _runtime(net, steps, **kw):

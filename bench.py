@@ -239,19 +239,33 @@ def run_reference_sample(scale: float, block: int, steps: int, warmup: int, seed
             "total_steps": total_steps}
 
 
-def parity_leg(model, rt, net, block, seconds, world, all_reduce):
-    """Simulate `seconds` more of biological time with spike recording, decode every block and
-    compare per-population firing rate and CV-ISI with the statistics the reference's CPU backend
-    produced for this architecture at x1 over 10 s (tests/golden/stats_potjans_x1.json: the xN
-    network has the same in-degrees and hence the same population statistics).  Every rank
-    decodes the slice of each population it updates; the sums are combined across ranks."""
-    from genn_b200 import stats
+def parity_leg(rank, world, device, block, seconds, all_reduce):
+    """Statistics parity at the workload's size, at this N: the EXACT x1 network the reference's CPU
+    backend was run on for tests/golden/stats_potjans_x1.json (same seed, connectivity, weights and
+    delays drawn on the host by workloads.potjans), split over the `world` GPUs by target neuron,
+    simulated for `seconds` with spike recording.  Per-population firing rate and CV-ISI are compared
+    with the reference's.  (The timed network is drawn on the device from another seed, and a
+    different draw of the connectivity alone moves the population rates by up to 3 %: only the same
+    network can be held to 2 %.)  Every rank decodes the slice of each population it updates; the
+    partial sums are combined across ranks."""
+    from genn_b200 import stats, workloads
     path = os.path.join(REPO, "tests", "golden", "stats_potjans_x1.json")
     if not os.path.exists(path):
         return {"ok": None, "note": "no reference statistics on disk"}
-    want = json.load(open(path))["populations"]
+    golden = json.load(open(path))
+    want = golden["populations"]
+    t0 = time.perf_counter()
+    shard = (rank, world) if world > 1 else None
+    model = workloads.potjans(neuron_scale=1.0, seed=int(golden.get("seed", 2024)), host_connectivity=True,
+                              background="poisson", record=True, shard=shard)
+    model.build()
+    model.load(num_recording_timesteps=block, device=device, shard=shard)
+    rt = model._runtime
+    net = rt.net
+    build_s = time.perf_counter() - t0
     blocks = max(1, int(round(seconds / (block * DT_MS * 1e-3))))
     spikes = {p.name: ([], []) for p in net.pops}
+    t0 = time.perf_counter()
     for _ in range(blocks):
         model.step_time(block)
         model.pull_recording_buffers_from_device()
@@ -259,11 +273,14 @@ def parity_leg(model, rt, net, block, seconds, world, all_reduce):
             times, ids = rt.recorded_spikes(p.name)[0]
             spikes[p.name][0].append(np.rint(times / net.dt).astype(np.int64))
             spikes[p.name][1].append(ids)
+    run_s = time.perf_counter() - t0
     names = [p.name for p in net.pops]
     sums = np.zeros((len(names), 4))
     for j, p in enumerate(net.pops):
-        lo, hi = (p.shard_bounds[rt.shard[0]], p.shard_bounds[rt.shard[0] + 1]) if rt.shard else (0, p.n)
+        lo, hi = (p.shard_bounds[rank], p.shard_bounds[rank + 1]) if shard else (0, p.n)
         sums[j] = stats.partial(np.concatenate(spikes[p.name][0]), np.concatenate(spikes[p.name][1]), hi - lo, first_id=lo)
+    schedule = rt.schedule
+    model.unload()
     if all_reduce is not None:
         import torch
         t = torch.tensor(sums, dtype=torch.float64, device="cuda")
@@ -274,11 +291,14 @@ def parity_leg(model, rt, net, block, seconds, world, all_reduce):
     rate_err, cv_err = stats.compare(got, want)
     return {"rates_max_rel_err": rate_err, "cv_isi_max_rel_err": cv_err, "tolerance": 0.02,
             "ok": bool(rate_err <= 0.02 and cv_err <= 0.02), "simulated_seconds": duration,
+            "network": f"Potjans x1, seed {int(golden.get('seed', 2024))}, host-drawn connectivity: the reference's own network, "
+                       f"sharded over {world} GPU(s)",
+            "schedule": int(schedule), "build_seconds": round(build_s, 1), "run_seconds": round(run_s, 1),
             "rates_hz": {n: round(got[n]["rate_hz"], 4) for n in names},
             "reference_rates_hz": {n: round(want[n]["rate_hz"], 4) for n in names},
             "cv_isi": {n: round(got[n]["cv_isi"], 4) for n in names},
             "reference_cv_isi": {n: round(want[n]["cv_isi"], 4) for n in names},
-            "note": "reference: GeNN single_threaded_cpu backend, x1 network with host-drawn connectivity, 10 s simulated "
+            "note": "reference: GeNN single_threaded_cpu backend on the identical network, 10 s simulated "
                     "(chaotic network: statistics, not spike trains, are comparable)"}
 
 
@@ -310,6 +330,192 @@ def reference_arm(args):
                 "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
+
+
+def run_c4(args):
+    """PROCEDURAL connectivity stress test (single GPU): nothing of the ~1e9-synapse matrix is stored,
+    every spike regenerates its row and weights.  One bench step = --block time steps of 1 ms (default
+    100).  Every synapse is one floating-point reduction into L2 and no HBM traffic: the figures of
+    merit are synaptic events/s and L2 reductions/s (the same number)."""
+    import torch
+    from genn_b200 import workloads
+    torch.cuda.set_device(0)
+    block = args.block if args.block != 1000 else 100
+    model = workloads.procedural_stress(num_neurons=args.c4_neurons, threads_per_spike=args.c4_threads, record=True)
+    model.build()
+    model.load(num_recording_timesteps=block, device=0)
+    rt = model._runtime
+    rt.set_option("count_events", 1)
+    for item in args.option:
+        opt_name, opt_value = item.split("=")
+        rt.set_option(opt_name, float(opt_value))
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(args.warmup):
+        rt.step_time(block)
+    rt.synchronize()
+    ev0, sp0, l0 = rt.counter("synaptic_events"), rt.counter("spikes"), rt.kernel_launches
+    sampler.mark()
+    ms = rt.step_time_timed(args.steps * block)
+    clocks = sampler.stop()
+    ev1, sp1, l1 = rt.counter("synaptic_events"), rt.counter("spikes"), rt.kernel_launches
+    seconds = ms * 1e-3
+    sim_seconds = args.steps * block * 1e-3
+    # the presynaptic kernel alone, per launch (CUDA event pairs)
+    rt.enable_timing(True)
+    rt.reset_timers()
+    tev0 = rt.counter("synaptic_events")
+    rt.step_time(block)
+    rt.synchronize()
+    tev = rt.counter("synaptic_events") - tev0
+    pre_s, neu_s = rt.timer("presynaptic_update"), rt.timer("neuron_update")
+    rt.enable_timing(False)
+    # end to end: steps plus the spike recording pulled into page-locked memory
+    d2h = sum(a.nbytes for n, a in rt.plan.arrays.items() if n.endswith(".record"))
+    model.step_time(block)
+    model.pull_recording_buffers_from_device()
+    e0 = rt.counter("synaptic_events")
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        model.step_time(block)
+        model.pull_recording_buffers_from_device()
+    e2e_s = time.perf_counter() - t0
+    e2e_ev = rt.counter("synaptic_events") - e0
+    n = sum(p.n for p in rt.net.pops)
+    line = {"metric": "synaptic events/s (PROCEDURAL connectivity stress test)", "value": (ev1 - ev0) / seconds,
+            "unit": "synaptic events/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "f32", "data": "synthetic", "realtime_factor": sim_seconds / seconds,
+            "config": {"workload": f"{n} LIF neurons, recurrent PROCEDURAL FixedProbability p=0.001, weights Normal(0.1, 0.01) nA "
+                                   f"regenerated per spike, Poisson drive 5 Hz onto 10 % of the neurons, dt = 1 ms; one bench "
+                                   f"step = {block} time steps",
+                       "threads_per_spike": args.c4_threads,
+                       "mean_rate_hz": (sp1 - sp0) / n / sim_seconds,
+                       "l2": "no synapse data exists; the reductions' targets (4 MB per postsynaptic buffer) live in L2"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_ev / e2e_s, "unit": "synaptic events/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(l1 - l0),
+            "l2_reductions_per_s": (ev1 - ev0) / seconds,
+            "roofline": {"kernel": "presynapticProceduralKernel", "bound": "hbm", "achieved": 0.0, "peak": measured_peaks()[0],
+                         "unit": "GB/s", "frac": 0.0, "traffic": None,
+                         "launches": block, "avg_launch_us": pre_s / block * 1e6, "neuron_kernel_avg_launch_us": neu_s / block * 1e6,
+                         "events_per_s_in_kernel": tev / pre_s if pre_s > 0 else None,
+                         "note": "0 algorithmic HBM bytes per event: the kernel is bound by Philox + log arithmetic and by "
+                                 "L2 reductions (events_per_s_in_kernel = reductions/s inside the presynaptic kernel)"}}
+    print(json.dumps(line), flush=True)
+    model.unload()
+
+
+def run_c5(args):
+    """Batched plasticity, data-parallel over the GPUs: every rank holds --c5-batch copies of the dynamic
+    state (own Poisson draws, own weights), connectivity replicated.  One bench step = 100 time steps of
+    1 ms followed by the custom update group "gradient": sum of the weights over the batch (batchReduceKernel),
+    ONE NCCL all-reduce of the packed sums over the ranks, mean written back into every copy.  `value` =
+    synaptic events/s of the whole job (pre-side and post-side STDP events); `roofline` = the batch-reduce
+    kernels (4 B x batch read + 4 B target + 4 B x batch written back per synapse slot)."""
+    import torch
+    import torch.distributed as dist
+    from genn_b200 import workloads
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    block = 100
+    model, sg = workloads.batched_stdp(num_pre=args.c5_neurons, num_post=args.c5_neurons, batch=args.c5_batch,
+                                       seed=55 + rank, world=world)
+    model.seed = 55                      # the same connectivity on every rank; the state differs through the batch streams
+    model.build()
+    model.load(device=local_rank)
+    rt = model._runtime
+    rt.set_option("count_events", 1)
+    if world > 1:
+        rt.init_data_parallel(rank, world)
+    hbm_peak, peak_kind = measured_peaks()
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def allreduce(value, op):
+        if world == 1:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device="cuda")
+        dist.all_reduce(t, op=op)
+        return float(t.item())
+
+    def bench_step():
+        rt.step_time(block)
+        rt.custom_update("gradient")
+
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    for _ in range(args.warmup):
+        bench_step()
+    rt.synchronize()
+    ev0, l0 = rt.counter("synaptic_events"), rt.kernel_launches
+    barrier()
+    sampler.mark()
+    rt.timed_begin()
+    for _ in range(args.steps):
+        bench_step()
+    ms = rt.timed_end()
+    barrier()
+    clocks = sampler.stop()
+    ev1, l1 = rt.counter("synaptic_events"), rt.kernel_launches
+    ms = allreduce(ms, dist.ReduceOp.MAX if world > 1 else None)
+    events = allreduce(float(ev1 - ev0), dist.ReduceOp.SUM if world > 1 else None)
+    # the custom update alone (CUDA event pair around reduce + all-reduce + write-back)
+    rt.enable_timing(True)
+    rt.reset_timers()
+    reps = 5
+    for _ in range(reps):
+        barrier()
+        rt.custom_update("gradient")
+    rt.synchronize()
+    cu_s = allreduce(rt.timer("custom_update_gradient") / reps, dist.ReduceOp.MAX if world > 1 else None)
+    rt.enable_timing(False)
+    slots = int(np.prod(rt.plan.arrays["syn.g"].shape[1:], dtype=np.int64))
+    cu_bytes = slots * (4.0 * args.c5_batch + 4.0 + 4.0 * args.c5_batch + 8.0)     # read batch, write target, write back, staged r/w
+    # end to end: the same steps plus the reduced weights pulled to the host after every update
+    red = model.custom_updates["mean_g"].vars["reduction"]
+    bench_step()
+    red.pull_from_device()
+    barrier()
+    t0 = time.perf_counter()
+    e0 = rt.counter("synaptic_events")
+    for _ in range(args.steps):
+        bench_step()
+        red.pull_from_device()
+    barrier()
+    e2e_s = allreduce(time.perf_counter() - t0, dist.ReduceOp.MAX if world > 1 else None)
+    e2e_ev = allreduce(float(rt.counter("synaptic_events") - e0), dist.ReduceOp.SUM if world > 1 else None)
+    if rank == 0:
+        seconds = ms * 1e-3
+        line = {"metric": "synaptic events/s (batched STDP, data-parallel)", "value": events / seconds, "unit": "synaptic events/s",
+                "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+                "realtime_factor": args.steps * block * 1e-3 / seconds,
+                "config": {"workload": f"{args.c5_neurons} Poisson inputs (25 Hz) -> {args.c5_neurons} LIF, SPARSE p=0.1 ({slots} synapse "
+                                       f"slots), additive STDP, {args.c5_batch} batch entries per GPU x {world} GPU(s); one bench step = "
+                                       f"{block} time steps of 1 ms + batch-reduce custom update with one packed NCCL all-reduce",
+                           "parallelism": f"data-parallel over {world} GPU(s), connectivity replicated",
+                           "l2": f"weights: {slots * 4 * args.c5_batch / 1e9:.2f} GB per GPU, larger than L2"},
+                "clocks": clocks,
+                "e2e": {"value": e2e_ev / e2e_s, "unit": "synaptic events/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": slots * 4},
+                "gpu_launches": int(l1 - l0),
+                "roofline": {"kernel": "batchReduceKernel (reduce, all-reduce, write back)", "bound": "hbm",
+                             "achieved": cu_bytes / cu_s / 1e9, "peak": hbm_peak, "unit": "GB/s", "frac": cu_bytes / cu_s / 1e9 / hbm_peak,
+                             "traffic": None, "peak_source": peak_kind, "launches": reps, "avg_launch_ms": cu_s * 1e3,
+                             "algorithmic_bytes_per_launch": cu_bytes,
+                             "all_reduce_bytes": slots * 4,
+                             "note": "CUDA events around the whole custom update: two kernels and the all-reduce between them"}}
+        print(json.dumps(line), flush=True)
+    model.unload()
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def run_probe(args):
@@ -422,6 +628,14 @@ def main():
                     help="simulated seconds of the rate / CV-ISI comparison with the reference's statistics (0: skip)")
     ap.add_argument("--probe", choices=["presyn", "phases", "e2e"], default=None,
                     help="run a bounded single-kernel workload (for profiling) instead of the benchmark")
+    ap.add_argument("--workload", choices=["potjans", "c4", "c5"], default="potjans",
+                    help="potjans: the headline workload; c4: the PROCEDURAL connectivity stress test (1 M LIF neurons, "
+                         "p = 0.001, dt = 1 ms; single GPU); c5: batched plasticity (10 k Poisson -> 10 k LIF, STDP, 32 batch "
+                         "entries per GPU, batch-reduce + all-reduce every 100 steps)")
+    ap.add_argument("--c5-batch", type=int, default=32, help="batch entries per GPU")
+    ap.add_argument("--c5-neurons", type=int, default=10000)
+    ap.add_argument("--c4-neurons", type=int, default=1_000_000)
+    ap.add_argument("--c4-threads", type=int, default=32, help="threads that share one regenerated row")
     ap.add_argument("--probe-scale", type=float, default=None)
     ap.add_argument("--probe-fraction", type=float, default=0.25)
     ap.add_argument("--probe-steps", type=int, default=2000)
@@ -446,6 +660,12 @@ def main():
         return
     if args.probe:
         run_probe(args)
+        return
+    if args.workload == "c4":
+        run_c4(args)
+        return
+    if args.workload == "c5":
+        run_c5(args)
         return
 
     rank = int(os.environ.get("RANK", "0"))
@@ -536,12 +756,6 @@ def main():
         t_, ids = rt.recorded_spikes(p.name)[0]
         n_local = rt.plan.neuron_descs[[q.name for q in net.pops].index(p.name)].num_update
         rates[p.name] = round(len(ids) / max(1, n_local) / (block * DT_MS * 1e-3), 3)
-
-    # ---- parity: population statistics over --parity-seconds against the reference's ----------
-    parity = None
-    if args.parity_seconds > 0 and args.min_delay == 0.0:
-        parity = parity_leg(model, rt, net, block, args.parity_seconds, world,
-                            (lambda t: dist.all_reduce(t)) if world > 1 else None)
 
     # ---- where a step's time goes inside the persistent kernel (clock64 per phase, CTA 0) ---
     probe_steps = min(args.steps * block, 2000)
@@ -695,11 +909,17 @@ def main():
             "gpu_launches": int(l1 - l0),
             "roofline": roofline,
             "roofline_saturated": roofline_sat,
-            "parity": parity,
             "cpu_baseline": cpu,
         }
-        print(json.dumps(line), flush=True)
     model.unload()
+    # ---- parity: population statistics over --parity-seconds against the reference's ----------
+    parity = None
+    if args.parity_seconds > 0:
+        parity = parity_leg(rank, world, local_rank, block, args.parity_seconds,
+                            (lambda t: dist.all_reduce(t)) if world > 1 else None)
+    if rank == 0:
+        line["parity"] = parity
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -95,7 +95,9 @@ enum StreamKind : unsigned int
     STREAM_NEURON = 0x10000u, STREAM_PRESYNAPTIC = 0x20000u, STREAM_POSTSYNAPTIC = 0x30000u, STREAM_DYNAMICS = 0x40000u,
     STREAM_CUSTOM = 0x50000u, STREAM_CUSTOM_WU = 0x60000u, STREAM_INIT_NEURON = 0x70000u, STREAM_INIT_SYNAPSE = 0x80000u,
     STREAM_INIT_CONNECT = 0x90000u, STREAM_INIT_SPARSE = 0xA0000u, STREAM_INIT_CUSTOM = 0xB0000u,
-    STREAM_INIT_CUSTOM_WU = 0xC0000u, STREAM_INIT_CUSTOM_WU_SPARSE = 0xD0000u
+    STREAM_INIT_CUSTOM_WU = 0xC0000u, STREAM_INIT_CUSTOM_WU_SPARSE = 0xD0000u, STREAM_PROCEDURAL = 0xE0000u,
+    // (the group index occupies the bits from 20 up: everything here stays below 1 << 20)
+    STREAM_INIT_CCU_PRE = 0xF0000u, STREAM_INIT_CCU_POST = 0xF4000u, STREAM_INIT_CCU_SPARSE = 0xF8000u, STREAM_CCU = 0xFC000u
 };
 
 //! One generated kernel of one merged group: its start-id table and launch geometry
@@ -167,6 +169,28 @@ void genDeviceStructArrayPush(CodeStream &os, const BackendBase &backend, const 
             os << "};" << std::endl;
             os << "CHECK_RUNTIME_ERRORS(cudaMemcpyToSymbolAsync(d_merged" << T::name << "Group" << g.getIndex() << ", &group, sizeof(" << structName << "), ";
             os << "idx * sizeof(" << structName << "), cudaMemcpyHostToDevice, 0));" << std::endl;
+        }
+    }
+}
+
+//! Merged groups whose code runs on the host: the array of group structures lives in host memory
+template<typename T>
+void genHostStructArrayPush(CodeStream &os, const BackendBase &backend, const std::vector<T> &groups)
+{
+    for(const auto &g : groups) {
+        const std::string structName = "Merged" + T::name + "Group" + std::to_string(g.getIndex());
+        os << "static " << structName << " merged" << T::name << "Group" << g.getIndex() << "[" << g.getGroups().size() << "];" << std::endl;
+        if(g.getFields().empty()) {
+            continue;
+        }
+        os << "void pushMerged" << T::name << "Group" << g.getIndex() << "ToDevice(unsigned int idx, ";
+        g.generateStructFieldArgumentDefinitions(os, backend);
+        os << ")";
+        {
+            CodeStream::Scope b(os);
+            for(const auto &f : g.getSortedFields(backend)) {
+                os << "merged" << T::name << "Group" << g.getIndex() << "[idx]." << f.name << " = " << f.name << ";" << std::endl;
+            }
         }
     }
 }
@@ -607,10 +631,19 @@ void Backend::genMSBuildImportTarget(std::ostream&) const { assert(false); }
 bool Backend::isGlobalHostRNGRequired(const ModelSpecInternal &model) const
 {
     // host-side connectivity initialisation snippets draw from the host generator
-    return std::any_of(model.getSynapseGroups().cbegin(), model.getSynapseGroups().cend(),
-                       [](const ModelSpec::SynapseGroupValueType &s)
+    if(std::any_of(model.getSynapseGroups().cbegin(), model.getSynapseGroups().cend(),
+                   [](const ModelSpec::SynapseGroupValueType &s)
+                   {
+                       return s.second.getSparseConnectivityInitialiser().isHostRNGRequired();
+                   }))
+    {
+        return true;
+    }
+    // ... and so does the host update code of custom connectivity updates
+    return std::any_of(model.getCustomConnectivityUpdates().cbegin(), model.getCustomConnectivityUpdates().cend(),
+                       [](const ModelSpec::CustomConnectivityUpdateValueType &c)
                        {
-                           return s.second.getSparseConnectivityInitialiser().isHostRNGRequired();
+                           return Utils::isRNGRequired(c.second.getHostUpdateCodeTokens());
                        });
 }
 
@@ -919,8 +952,8 @@ constexpr unsigned int SPIKE_LANES = 8;     // gridDim.z: a group's spike list i
 
 //! Environment entries a presynaptic / synapse-dynamics body needs to deposit its output: fire-and-forget
 //! fp32 additions (they compile to reductions; nothing reads the old value)
-template<typename G>
-void addOutputFunctions(EnvironmentGroupMergedField<G> &env, G &sg, unsigned int batchSize)
+template<typename E, typename G>
+void addOutputFunctions(E &env, G &sg, unsigned int batchSize)
 {
     env.add(Type::getAddToPrePostDelay(sg.getScalarType()), "addToPostDelay",
             "atomicAdd(&$(_den_delay)[" + sg.getPostDenDelayIndex(batchSize, "$(id_post)", "$(1)") + "], $(0))");
@@ -1053,17 +1086,17 @@ void Backend::genSynapseUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerge
         {
             const std::string idx = std::to_string(sg.getIndex());
             const auto matrixType = sg.getArchetype().getMatrixType();
-            if((matrixType & SynapseMatrixConnectivity::PROCEDURAL) || (matrixType & SynapseMatrixConnectivity::TOEPLITZ)) {
-                throw std::runtime_error("B200 backend: PROCEDURAL and TOEPLITZ connectivity are not generated yet (synapse group '"
-                                         + sg.getArchetype().getName() + "')");
-            }
+            const bool procedural = (matrixType & SynapseMatrixConnectivity::PROCEDURAL);
+            const bool toeplitz = (matrixType & SynapseMatrixConnectivity::TOEPLITZ);
             const bool sparse = (matrixType & SynapseMatrixConnectivity::SPARSE);
             const bool bitmask = (matrixType & SynapseMatrixConnectivity::BITMASK);
             KernelLaunch launch;
             launch.name = "updatePresynapticKernel" + idx;
             launch.batched = true;
+            // (PROCEDURAL: one block per group and spike lane; its threads walk the (spike, sub-row) items)
             launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedPresynapticUpdateGroupStartID" + idx, sg, block,
-                                            [this](const SynapseGroupInternal &g){ return getSynapticMatrixRowStride(g); });
+                                            [this, procedural, block](const SynapseGroupInternal &g)
+                                            { return procedural ? block : getSynapticMatrixRowStride(g); });
             kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
             {
                 CodeStream::Scope b(kernelLibEnv.getStream());
@@ -1124,11 +1157,131 @@ void Backend::genSynapseUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerge
                         }
                     }
                 };
+                // The body that handles ONE synapse, as a string in which $(0) is the target and $(1).. the kernel
+                // indices: connectivity that is regenerated on the fly (PROCEDURAL, TOEPLITZ) calls it as addSynapse(...)
+                const auto addSynapseType = Type::ResolvedType::createFunction(
+                    Type::Void, std::vector<Type::ResolvedType>{1ull + sg.getArchetype().getKernelSize().size(), Type::Uint32});
+                auto genSynapseBody = [&](EnvironmentExternalBase &parent, bool trueSpike)
+                {
+                    std::ostringstream bodyStream;
+                    CodeStream body(bodyStream);
+                    {
+                        CodeStream::Scope b(body);
+                        EnvironmentExternal bodyEnv(parent, body);
+                        bodyEnv.add(Type::Uint32.addConst(), "id_post", "b200Post",
+                                    {bodyEnv.addInitialiser("const unsigned int b200Post = $(0);")});
+                        for(size_t i = 0; i < sg.getArchetype().getKernelSize().size(); i++) {
+                            const std::string iStr = std::to_string(i);
+                            bodyEnv.add(Type::Uint32.addConst(), "id_kernel_" + iStr, "b200Kernel" + iStr,
+                                        {bodyEnv.addInitialiser("const unsigned int b200Kernel" + iStr + " = $(" + std::to_string(i + 1) + ");")});
+                        }
+                        addOutputFunctions(bodyEnv, sg, batchSize);
+                        if(trueSpike) {
+                            sg.generateSpikeUpdate(*this, bodyEnv, batchSize, model.getDT());
+                        }
+                        else {
+                            sg.generateSpikeEventUpdate(*this, bodyEnv, batchSize, model.getDT());
+                        }
+                    }
+                    return bodyStream.str();
+                };
+
+                // PROCEDURAL (presynapticUpdateStrategySIMT.cc:425-561): an item is (spike, sub-row t of T); the row
+                // of a spiking neuron is rebuilt by the snippet's row build code from a stream keyed on
+                // (row, sub-row) alone, so it is the same row at every spike
+                auto genProceduralEvents = [&](bool trueSpike)
+                {
+                    const std::string eventSuffix = trueSpike ? "" : "_event";
+                    const bool delay = trueSpike ? sg.getArchetype().getSrcNeuronGroup()->isSpikeQueueRequired()
+                                                 : sg.getArchetype().getSrcNeuronGroup()->isSpikeEventQueueRequired();
+                    const size_t T = sg.getArchetype().getNumThreadsPerSpike();
+                    const std::string Tstr = std::to_string(T) + "u";
+                    CodeStream::Scope b(groupEnv.getStream());
+                    groupEnv.printLine("const unsigned int b200NumSpikes = $(_src_spk_cnt" + eventSuffix + ")[" + sg.getPreSlot(delay, batchSize) + "];");
+                    groupEnv.printLine("for(unsigned int b200Item = (blockIdx.z * blockDim.x) + $(id); b200Item < (b200NumSpikes * " + Tstr
+                                       + "); b200Item += (gridDim.z * blockDim.x))");
+                    {
+                        CodeStream::Scope b(groupEnv.getStream());
+                        EnvironmentGroupMergedField<PresynapticUpdateGroupMerged> synEnv(groupEnv, sg);
+                        synEnv.add(Type::Uint32.addConst(), "_spike", "b200Spike",
+                                   {synEnv.addInitialiser("const unsigned int b200Spike = b200Item / " + Tstr + ";")});
+                        synEnv.add(Type::Uint32.addConst(), "_thread", "b200Sub",
+                                   {synEnv.addInitialiser("const unsigned int b200Sub = b200Item % " + Tstr + ";")});
+                        synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre",
+                                   {synEnv.addInitialiser("const unsigned int b200Pre = $(_src_spk" + eventSuffix + ")["
+                                                          + sg.getPreVarIndex(delay, batchSize, VarAccessDim::BATCH | VarAccessDim::ELEMENT, "$(_spike)") + "];")});
+                        synEnv.add(Type::Uint32.addConst(), "_num_post", "$(num_post)");
+                        synEnv.add(Type::Void, "_rng", "b200RowRng",
+                                   {synEnv.addInitialiser("b200gen::Rng b200RowRng = b200gen::initRng(b200Seed, " + std::to_string(STREAM_PROCEDURAL + sg.getIndex())
+                                                          + "u + (b200Group << 20), ($(id_pre) * " + Tstr + ") + $(_thread));")});
+                        const std::string body = genSynapseBody(synEnv, trueSpike);
+                        {
+                            EnvironmentExternal connEnv(synEnv);
+                            connEnv.add(Type::Uint32.addConst(), "num_threads", std::to_string(T));
+                            if(T > 1) {
+                                const size_t perInit = connEnv.addInitialiser("const unsigned int b200PostPerSub = ($(_num_post) + " + Tstr + " - 1u) / " + Tstr + ";");
+                                connEnv.add(Type::Uint32.addConst(), "id_post_begin", "b200PostBegin",
+                                            {perInit, connEnv.addInitialiser("const unsigned int b200PostBegin = $(_thread) * b200PostPerSub;")});
+                                connEnv.add(Type::Uint32.addConst(), "id_thread", "$(_thread)");
+                                connEnv.add(Type::Uint32.addConst(), "num_post", "b200SubPost",
+                                            {perInit, connEnv.addInitialiser("const unsigned int b200SubPost = (($(_thread) * b200PostPerSub) >= $(_num_post)) ? 0u : "
+                                                                             "min(b200PostPerSub, $(_num_post) - ($(_thread) * b200PostPerSub));")});
+                            }
+                            else {
+                                connEnv.add(Type::Uint32.addConst(), "id_post_begin", "0");
+                                connEnv.add(Type::Uint32.addConst(), "id_thread", "0");
+                            }
+                            connEnv.add(addSynapseType, "addSynapse", body);
+                            sg.generateProceduralConnectivity(connEnv);
+                        }
+                    }
+                };
+
+                // TOEPLITZ (presynapticUpdateStrategySIMT.cc:784-919): thread = diagonal of the kernel; the diagonal
+                // build code loops over the spikes through for_each_synapse and calls addSynapse for each target
+                auto genToeplitzEvents = [&](bool trueSpike)
+                {
+                    const std::string eventSuffix = trueSpike ? "" : "_event";
+                    const bool delay = trueSpike ? sg.getArchetype().getSrcNeuronGroup()->isSpikeQueueRequired()
+                                                 : sg.getArchetype().getSrcNeuronGroup()->isSpikeEventQueueRequired();
+                    CodeStream::Scope b(groupEnv.getStream());
+                    EnvironmentExternal toeplitzEnv(groupEnv);
+                    toeplitzEnv.add(Type::Uint32.addConst(), "id_diag", "$(id)");
+                    toeplitzEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre");
+                    const std::string body = genSynapseBody(toeplitzEnv, trueSpike);
+                    sg.generateToeplitzConnectivity(
+                        toeplitzEnv,
+                        [addSynapseType](auto &env, auto &errorHandler)
+                        {
+                            env.define(Transpiler::Token{Transpiler::Token::Type::IDENTIFIER, "addSynapse", 0}, addSynapseType, errorHandler);
+                            env.define(Transpiler::Token{Transpiler::Token::Type::IDENTIFIER, "id_pre", 0}, Type::Uint32.addConst(), errorHandler);
+                        },
+                        [&](auto &env, auto generateBody)
+                        {
+                            env.printLine("const unsigned int b200NumSpikes = $(_src_spk_cnt" + eventSuffix + ")[" + sg.getPreSlot(delay, batchSize) + "];");
+                            env.getStream() << "for(unsigned int b200Spike = blockIdx.z; b200Spike < b200NumSpikes; b200Spike += gridDim.z)";
+                            {
+                                CodeStream::Scope b(env.getStream());
+                                EnvironmentGroupMergedField<PresynapticUpdateGroupMerged> spikeEnv(env, sg);
+                                spikeEnv.printLine("const unsigned int b200Pre = $(_src_spk" + eventSuffix + ")["
+                                                   + sg.getPreVarIndex(delay, batchSize, VarAccessDim::BATCH | VarAccessDim::ELEMENT, "b200Spike") + "];");
+                                spikeEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre");
+                                spikeEnv.print("if($(id) < $(_row_stride))");
+                                {
+                                    CodeStream::Scope b(spikeEnv.getStream());
+                                    EnvironmentExternal bodyEnv(spikeEnv);
+                                    bodyEnv.add(addSynapseType, "addSynapse", body);
+                                    generateBody(bodyEnv);
+                                }
+                            }
+                        });
+                };
+
                 if(sg.getArchetype().isPreSpikeEventRequired()) {
-                    genEvents(false);
+                    procedural ? genProceduralEvents(false) : toeplitz ? genToeplitzEvents(false) : genEvents(false);
                 }
                 if(sg.getArchetype().isPreSpikeRequired()) {
-                    genEvents(true);
+                    procedural ? genProceduralEvents(true) : toeplitz ? genToeplitzEvents(true) : genEvents(true);
                 }
             }
             preLaunches.push_back(launch);
@@ -1513,11 +1666,45 @@ void Backend::genInit(CodeStream &os, FileStreamCreator, ModelSpecMerged &modelM
                                           rngInit(STREAM_INIT_CUSTOM_WU, c.getIndex()));
                       });
         });
-    if(!modelMerged.getMergedCustomConnectivityUpdatePreInitGroups().empty() || !modelMerged.getMergedCustomConnectivityUpdatePostInitGroups().empty()
-       || !modelMerged.getMergedCustomConnectivityUpdateSparseInitGroups().empty())
-    {
-        throw std::runtime_error("B200 backend: custom connectivity updates are not generated yet");
-    }
+    // ---- variables of custom connectivity updates: per source neuron, per target neuron -----------------------------
+    modelMerged.genMergedCustomConnectivityUpdatePreInitGroups(
+        *this, memorySpaces,
+        [&](auto &c)
+        {
+            genKernel(c, "initializeCustomConnectivityPreKernel", "CustomConnectivityUpdatePreInit",
+                      [](const CustomConnectivityUpdateInternal &cg){ return (size_t)cg.getSynapseGroup()->getSrcNeuronGroup()->getNumNeurons(); }, initLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<CustomConnectivityUpdatePreInitGroupMerged> groupEnv(kernelEnv, c);
+                          buildStandardEnvironment(groupEnv);
+                          groupEnv.print("if($(id) < $(num_neurons))");
+                          {
+                              CodeStream::Scope b(groupEnv.getStream());
+                              EnvironmentGroupMergedField<CustomConnectivityUpdatePreInitGroupMerged> initEnv(groupEnv, c);
+                              initEnv.add(Type::Void, "_rng", "b200Rng", {initEnv.addInitialiser(rngInit(STREAM_INIT_CCU_PRE, c.getIndex()))});
+                              c.generateInit(*this, initEnv, batchSize);
+                          }
+                      });
+        });
+    modelMerged.genMergedCustomConnectivityUpdatePostInitGroups(
+        *this, memorySpaces,
+        [&](auto &c)
+        {
+            genKernel(c, "initializeCustomConnectivityPostKernel", "CustomConnectivityUpdatePostInit",
+                      [](const CustomConnectivityUpdateInternal &cg){ return (size_t)cg.getSynapseGroup()->getTrgNeuronGroup()->getNumNeurons(); }, initLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<CustomConnectivityUpdatePostInitGroupMerged> groupEnv(kernelEnv, c);
+                          buildStandardEnvironment(groupEnv);
+                          groupEnv.print("if($(id) < $(num_neurons))");
+                          {
+                              CodeStream::Scope b(groupEnv.getStream());
+                              EnvironmentGroupMergedField<CustomConnectivityUpdatePostInitGroupMerged> initEnv(groupEnv, c);
+                              initEnv.add(Type::Void, "_rng", "b200Rng", {initEnv.addInitialiser(rngInit(STREAM_INIT_CCU_POST, c.getIndex()))});
+                              c.generateInit(*this, initEnv, batchSize);
+                          }
+                      });
+        });
 
     // ---- sparse / bitmask connectivity built on the device ------------------------------------------------------------
     modelMerged.genMergedSynapseConnectivityInitGroups(
@@ -1660,6 +1847,21 @@ void Backend::genInit(CodeStream &os, FileStreamCreator, ModelSpecMerged &modelM
                       });
         });
 
+    modelMerged.genMergedCustomConnectivityUpdateSparseInitGroups(
+        *this, memorySpaces,
+        [&](auto &c)
+        {
+            genKernel(c, "initializeCustomConnectivitySparseKernel", "CustomConnectivityUpdateSparseInit",
+                      [](const CustomConnectivityUpdateInternal &cg){ return (size_t)cg.getSynapseGroup()->getMaxConnections(); }, sparseLaunches,
+                      [&](EnvironmentExternal &kernelEnv)
+                      {
+                          EnvironmentGroupMergedField<CustomConnectivityUpdateSparseInitGroupMerged> groupEnv(kernelEnv, c);
+                          buildStandardEnvironment(groupEnv);
+                          groupEnv.add(Type::Void, "_rng", "b200Rng", {groupEnv.addInitialiser(rngInit(STREAM_INIT_CCU_SPARSE, c.getIndex()))});
+                          genSparseVarInit(*this, groupEnv, c, batchSize, true, [](EnvironmentExternalBase&){});
+                      });
+        });
+
     // ---- file -----------------------------------------------------------------------------------------------------------
     os << "#include <iostream>" << std::endl;
     os << "#include <random>" << std::endl;
@@ -1672,6 +1874,12 @@ void Backend::genInit(CodeStream &os, FileStreamCreator, ModelSpecMerged &modelM
     modelMerged.genMergedCustomUpdateInitGroupStructs(os, *this);
     modelMerged.genMergedCustomWUUpdateInitGroupStructs(os, *this);
     modelMerged.genMergedCustomWUUpdateSparseInitGroupStructs(os, *this);
+    modelMerged.genMergedCustomConnectivityUpdatePreInitStructs(os, *this);
+    modelMerged.genMergedCustomConnectivityUpdatePostInitStructs(os, *this);
+    modelMerged.genMergedCustomConnectivityUpdateSparseInitStructs(os, *this);
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomConnectivityUpdatePreInitGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomConnectivityUpdatePostInitGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomConnectivityUpdateSparseInitGroups());
     genDeviceStructArrayPush(os, *this, modelMerged.getMergedNeuronInitGroups());
     genDeviceStructArrayPush(os, *this, modelMerged.getMergedSynapseInitGroups());
     genDeviceStructArrayPush(os, *this, modelMerged.getMergedSynapseConnectivityInitGroups());
@@ -1717,12 +1925,7 @@ void Backend::genCustomUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerged
     const size_t block = blockSize();
     const std::string timeType = model.getTimePrecision().getName();
     const std::string dtLiteral = Type::writeNumeric(model.getDT(), model.getTimePrecision());
-
-    if(!modelMerged.getMergedCustomUpdateTransposeWUGroups().empty() || !modelMerged.getMergedCustomConnectivityUpdateGroups().empty()
-       || !modelMerged.getMergedCustomConnectivityRemapUpdateGroups().empty() || !modelMerged.getMergedCustomConnectivityHostUpdateGroups().empty())
-    {
-        throw std::runtime_error("B200 backend: transpose and custom connectivity updates are not generated yet");
-    }
+    const std::string kernelArgs = timeType + " t, unsigned long long b200Step, unsigned long long b200Seed";
 
     std::ostringstream kernelStream;
     CodeStream kernels(kernelStream);
@@ -1738,8 +1941,12 @@ void Backend::genCustomUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerged
     for(const auto &c : model.getCustomWUUpdates()) {
         updateGroups.insert(c.second.getUpdateGroupName());
     }
+    for(const auto &c : model.getCustomConnectivityUpdates()) {
+        updateGroups.insert(c.second.getUpdateGroupName());
+    }
 
-    std::map<std::string, std::vector<KernelLaunch>> launches;
+    std::map<std::string, std::vector<KernelLaunch>> launches, transposeLaunches, remapLaunches;
+    std::map<std::string, std::string> hostUpdates;
     for(const auto &g : updateGroups) {
         // ---- neuron-shaped custom updates ---------------------------------------------------------------------------
         modelMerged.genMergedCustomUpdateGroups(
@@ -1760,7 +1967,7 @@ void Backend::genCustomUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerged
                                                 {
                                                     return (neuronReduce || !perElement) ? (size_t)32 : (size_t)cu.getNumNeurons();
                                                 });
-                kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << timeType << " t)";
+                kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
                 {
                     CodeStream::Scope b(kernelLibEnv.getStream());
                     EnvironmentExternal kernelEnv(kernelLibEnv);
@@ -1870,7 +2077,7 @@ void Backend::genCustomUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerged
                                                         ? (size_t)s->getKernelSizeFlattened()
                                                         : (size_t)s->getSrcNeuronGroup()->getNumNeurons() * getSynapticMatrixRowStride(*s);
                                                 });
-                kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << timeType << " t)";
+                kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
                 {
                     CodeStream::Scope b(kernelLibEnv.getStream());
                     EnvironmentExternal kernelEnv(kernelLibEnv);
@@ -1936,24 +2143,208 @@ void Backend::genCustomUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerged
                 }
                 launches[g].push_back(launch);
             });
+
+        // ---- per-synapse custom updates that also write the transpose of one variable (DENSE only) -----------
+        // thread = synapse of the forward matrix; the transposed element is written straight from the register
+        // (rows of the transpose are a stride apart: the matrices these updates run on fit L2)
+        modelMerged.genMergedCustomUpdateTransposeWUGroups(
+            *this, memorySpaces, g,
+            [&](auto &cg)
+            {
+                const std::string idx = std::to_string(cg.getIndex());
+                const bool batched = (cg.getArchetype().getDims() & VarAccessDim::BATCH) && (batchSize > 1);
+                KernelLaunch launch;
+                launch.name = "customUpdateTransposeWU" + g + "Kernel" + idx;
+                launch.batched = batched;
+                launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedCustomUpdateTransposeWUGroupStartID" + idx, cg, block,
+                                                [](const CustomUpdateWUInternal &cu)
+                                                {
+                                                    const auto *s = cu.getSynapseGroup();
+                                                    return (size_t)s->getSrcNeuronGroup()->getNumNeurons() * s->getTrgNeuronGroup()->getNumNeurons();
+                                                });
+                kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
+                {
+                    CodeStream::Scope b(kernelLibEnv.getStream());
+                    EnvironmentExternal kernelEnv(kernelLibEnv);
+                    kernelEnv.add(model.getTimePrecision().addConst(), "t", "t");
+                    kernelEnv.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
+                    genFindGroup(kernelEnv.getStream(), "MergedCustomUpdateTransposeWUGroup" + idx, "d_mergedCustomUpdateTransposeWUGroup" + idx,
+                                 "d_mergedCustomUpdateTransposeWUGroupStartID" + idx, cg.getGroups().size());
+                    kernelEnv.add(Type::Uint32.addConst(), "id", "b200Local");
+                    EnvironmentGroupMergedField<CustomUpdateTransposeWUGroupMerged> groupEnv(kernelEnv, cg);
+                    buildSizeEnvironment(groupEnv);
+                    groupEnv.getStream() << "const unsigned int batch = blockIdx.y;" << std::endl;
+                    groupEnv.add(Type::Uint32.addConst(), "batch", batched ? "batch" : "0");
+                    EnvironmentGroupMergedField<CustomUpdateTransposeWUGroupMerged> batchEnv(groupEnv, cg);
+                    buildStandardEnvironment(batchEnv, batchSize);
+                    const std::string transposeVarName = cg.addTransposeField(batchEnv);
+                    batchEnv.print("if($(id) < ($(num_pre) * $(num_post)))");
+                    {
+                        CodeStream::Scope b(batchEnv.getStream());
+                        EnvironmentGroupMergedField<CustomUpdateTransposeWUGroupMerged> synEnv(batchEnv, cg);
+                        synEnv.add(Type::Uint32.addConst(), "id_pre", "b200Pre",
+                                   {synEnv.addInitialiser("const unsigned int b200Pre = $(id) / $(num_post);")});
+                        synEnv.add(Type::Uint32.addConst(), "id_post", "b200Post",
+                                   {synEnv.addInitialiser("const unsigned int b200Post = $(id) % $(num_post);")});
+                        synEnv.add(Type::Uint32.addConst(), "id_syn", "$(id)");
+                        cg.generateCustomUpdate(synEnv, batchSize,
+                                                [&transposeVarName, batched](auto &env, const auto&)
+                                                {
+                                                    env.print("$(" + transposeVarName + "_transpose)[");
+                                                    if(batched) {
+                                                        env.print("$(_batch_offset) + ");
+                                                    }
+                                                    env.printLine("($(id_post) * $(num_pre)) + $(id_pre)] = $(" + transposeVarName + ");");
+                                                });
+                    }
+                }
+                transposeLaunches[g].push_back(launch);
+            });
+
+        // ---- custom connectivity updates: thread = row; the row update code adds and removes synapses of its row ----
+        modelMerged.genMergedCustomConnectivityUpdateGroups(
+            *this, memorySpaces, g,
+            [&](auto &cg)
+            {
+                const std::string idx = std::to_string(cg.getIndex());
+                KernelLaunch launch;
+                launch.name = "customConnectivityUpdate" + g + "Kernel" + idx;
+                launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_mergedCustomConnectivityUpdateGroupStartID" + idx, cg, block,
+                                                [](const CustomConnectivityUpdateInternal &cu)
+                                                { return (size_t)cu.getSynapseGroup()->getSrcNeuronGroup()->getNumNeurons(); });
+                kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
+                {
+                    CodeStream::Scope b(kernelLibEnv.getStream());
+                    EnvironmentExternal kernelEnv(kernelLibEnv);
+                    kernelEnv.add(model.getTimePrecision().addConst(), "t", "t");
+                    kernelEnv.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
+                    genFindGroup(kernelEnv.getStream(), "MergedCustomConnectivityUpdateGroup" + idx, "d_mergedCustomConnectivityUpdateGroup" + idx,
+                                 "d_mergedCustomConnectivityUpdateGroupStartID" + idx, cg.getGroups().size());
+                    kernelEnv.add(Type::Uint32.addConst(), "id", "b200Local");
+                    EnvironmentGroupMergedField<CustomConnectivityUpdateGroupMerged> groupEnv(kernelEnv, cg);
+                    buildStandardEnvironment(groupEnv);
+                    groupEnv.print("if($(id) < $(num_pre))");
+                    {
+                        CodeStream::Scope b(groupEnv.getStream());
+                        EnvironmentGroupMergedField<CustomConnectivityUpdateGroupMerged> validEnv(groupEnv, cg);
+                        validEnv.add(Type::Uint32.addConst(), "id_pre", "$(id)");
+                        // a stream per (row, update): stateless, where the reference keeps a generator state per row
+                        validEnv.add(Type::Void, "_rng", "b200Rng",
+                                     {validEnv.addInitialiser("b200gen::Rng b200Rng = b200gen::simRng(b200Seed, " + std::to_string(STREAM_CCU + cg.getIndex())
+                                                              + "u + (b200Group << 20), b200Thread, 0u, b200Step);")});
+                        cg.generateUpdate(*this, validEnv, batchSize);
+                    }
+                }
+                launches[g].push_back(launch);
+            });
+
+        // ---- column-major view rebuilt after the rows changed: column lengths to zero, then one pass over the rows ----
+        modelMerged.genMergedCustomConnectivityRemapUpdateGroups(
+            *this, memorySpaces, g,
+            [&](auto &cg)
+            {
+                const std::string idx = std::to_string(cg.getIndex());
+                KernelLaunch zero, remap;
+                zero.name = "customConnectivityRemapZero" + g + "Kernel" + idx;
+                remap.name = "customConnectivityRemap" + g + "Kernel" + idx;
+                for(int pass = 0; pass < 2; pass++) {
+                    KernelLaunch &launch = pass ? remap : zero;
+                    launch.numThreads = genStartIDs(kernelLibEnv.getStream(), "d_" + launch.name + "StartID", cg, block,
+                                                    [pass](const CustomConnectivityUpdateInternal &cu)
+                                                    {
+                                                        return pass ? (size_t)cu.getSynapseGroup()->getMaxConnections()
+                                                                    : (size_t)cu.getSynapseGroup()->getTrgNeuronGroup()->getNumNeurons();
+                                                    });
+                    kernelLibEnv.getStream() << "extern \"C\" __global__ void " << launch.name << "(" << kernelArgs << ")";
+                    CodeStream::Scope b(kernelLibEnv.getStream());
+                    EnvironmentExternal kernelEnv(kernelLibEnv);
+                    genFindGroup(kernelEnv.getStream(), "MergedCustomConnectivityRemapUpdateGroup" + idx, "d_mergedCustomConnectivityRemapUpdateGroup" + idx,
+                                 "d_" + launch.name + "StartID", cg.getGroups().size());
+                    kernelEnv.add(Type::Uint32.addConst(), "id", "b200Local");
+                    EnvironmentGroupMergedField<CustomConnectivityRemapUpdateGroupMerged> groupEnv(kernelEnv, cg);
+                    buildStandardEnvironment(groupEnv);
+                    if(pass == 0) {
+                        groupEnv.print("if($(id) < $(num_post))");
+                        CodeStream::Scope b(groupEnv.getStream());
+                        groupEnv.printLine("$(_col_length)[$(id)] = 0;");
+                    }
+                    else {
+                        groupEnv.printLine("unsigned int idx = $(id);");
+                        groupEnv.print("for(unsigned int b200Row = 0; b200Row < $(num_pre); b200Row++)");
+                        CodeStream::Scope b(groupEnv.getStream());
+                        groupEnv.print("if($(id) < $(_row_length)[b200Row])");
+                        {
+                            CodeStream::Scope b(groupEnv.getStream());
+                            groupEnv.printLine("const unsigned int b200PostIndex = $(_ind)[idx];");
+                            groupEnv.printLine("const unsigned int b200ColPos = atomicAdd(&$(_col_length)[b200PostIndex], 1);");
+                            groupEnv.printLine("$(_remap)[(b200PostIndex * $(_col_stride)) + b200ColPos] = idx;");
+                        }
+                        groupEnv.printLine("idx += $(_row_stride);");
+                    }
+                }
+                remapLaunches[g].push_back(zero);
+                remapLaunches[g].push_back(remap);
+            });
+
+        // ---- host update code of custom connectivity updates: runs on the host before the kernels ------------------
+        {
+            std::ostringstream hostStream;
+            CodeStream host(hostStream);
+            EnvironmentExternal hostEnv(host);
+            hostEnv.add(model.getTimePrecision().addConst(), "t", "t");
+            hostEnv.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
+            modelMerged.genMergedCustomConnectivityHostUpdateGroups(
+                *this, memorySpaces, g,
+                [&](auto &c)
+                {
+                    c.generateUpdate(*this, hostEnv);
+                });
+            hostUpdates[g] = hostStream.str();
+        }
     }
 
     // ---- file -----------------------------------------------------------------------------------------------------------
     modelMerged.genMergedCustomUpdateStructs(os, *this);
     modelMerged.genMergedCustomUpdateWUStructs(os, *this);
+    modelMerged.genMergedCustomUpdateTransposeWUStructs(os, *this);
+    modelMerged.genMergedCustomConnectivityUpdateStructs(os, *this);
+    modelMerged.genMergedCustomConnectivityRemapUpdateStructs(os, *this);
+    modelMerged.genMergedCustomConnectivityHostUpdateStructs(os, *this);
     genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomUpdateGroups());
     genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomUpdateWUGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomUpdateTransposeWUGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomConnectivityUpdateGroups());
+    genDeviceStructArrayPush(os, *this, modelMerged.getMergedCustomConnectivityRemapUpdateGroups());
+    genHostStructArrayPush(os, *this, modelMerged.getMergedCustomConnectivityHostUpdateGroups());
     preambleHandler(os);
     os << kernelStream.str();
     for(const auto &g : updateGroups) {
         os << "void update" << g << "(unsigned long long timestep)";
         CodeStream::Scope b(os);
         os << "const " << timeType << " t = timestep * " << dtLiteral << ";" << std::endl;
+        os << "const unsigned long long b200Step = timestep;" << std::endl;
+        if(!hostUpdates[g].empty()) {
+            os << hostUpdates[g];
+        }
         genKernelTimerStart(os, "customUpdate" + g, model.isTimingEnabled());
         for(const auto &k : launches[g]) {
-            genLaunch(os, k, block, batchSize, "t");
+            genLaunch(os, k, block, batchSize, "t, b200Step, b200Seed");
         }
         genKernelTimerStop(os, "customUpdate" + g, model.isTimingEnabled(), true);
+        if(!transposeLaunches[g].empty()) {
+            genKernelTimerStart(os, "customUpdate" + g + "Transpose", model.isTimingEnabled());
+            for(const auto &k : transposeLaunches[g]) {
+                genLaunch(os, k, block, batchSize, "t, b200Step, b200Seed");
+            }
+            genKernelTimerStop(os, "customUpdate" + g + "Transpose", model.isTimingEnabled(), true);
+        }
+        if(!remapLaunches[g].empty()) {
+            genKernelTimerStart(os, "customUpdate" + g + "Remap", model.isTimingEnabled());
+            for(const auto &k : remapLaunches[g]) {
+                genLaunch(os, k, block, 1, "t, b200Step, b200Seed");
+            }
+            genKernelTimerStop(os, "customUpdate" + g + "Remap", model.isTimingEnabled(), true);
+        }
     }
 }
 }   // namespace GeNN::CodeGenerator::B200

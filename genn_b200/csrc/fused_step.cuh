@@ -142,6 +142,10 @@ struct FusedLaunch
     unsigned int num_rings;
     const struct NearRing *near_rings;   // [world][num_rings]: the rings of every process, as mapped here
     const struct NearSpace *near_spaces; // [neuron groups]
+    // queues for near synapses onto other processes' neurons (near.cuh); queue_words == 0: reduce directly
+    unsigned int queue_words;            // 64-bit words per queue, header included
+    unsigned int queue_count;            // queues per (step parity, sending process)
+    unsigned long long queue_offset;     // where the queues start in every process's arena
 };
 
 constexpr unsigned long long EXCHANGE_SPIN_LIMIT = 1ull << 23;  // default

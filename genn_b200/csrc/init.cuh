@@ -100,32 +100,53 @@ __device__ __forceinline__ void storeInd(void *ind, unsigned long long idx, unsi
 // (seed, stream, pre): the initialisation kernel below stores what this yields, the PROCEDURAL
 // presynaptic kernel (presynaptic_update.cuh) replays it for every spike.  `fixedLength` is the
 // row length for the snippets that take it as an input.
+//
+// Sub-rows (FixedProbability only, p[2] = T > 1; the reference's "threads per spike",
+// presynapticUpdateStrategySIMT.cc:425-561): the targets are cut into T equal ranges and the synapses
+// into range t are drawn from a stream of their own, element pre * T + t, so T threads can regenerate
+// one row side by side.  The row is the sub-rows one after the other; [subFirst, subLast) selects
+// which of them to generate (n then counts from the first one generated).
+__host__ __device__ __forceinline__ unsigned int connectSubRows(unsigned int snippet, const float *p)
+{
+    const bool prob = (snippet == B200_CONNECT_FIXED_PROBABILITY || snippet == B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE);
+    return (prob && p[2] > 1.0f) ? (unsigned int)p[2] : 1u;
+}
+
 template<typename F>
 __host__ __device__ __forceinline__ unsigned int generateRow(unsigned int snippet, const float *p, unsigned int pre,
                                                              unsigned int trg_begin, unsigned int trg_end,
                                                              unsigned int fixedLength, unsigned long long seed,
-                                                             unsigned int stream, F emit)
+                                                             unsigned int stream, F emit,
+                                                             unsigned int subFirst = 0u, unsigned int subLast = 0xFFFFFFFFu)
 {
     const unsigned int numPost = trg_end - trg_begin;
-    b200_rng rng = b200_rng_init(seed, stream, pre);
     unsigned int n = 0;
     if(snippet == B200_CONNECT_FIXED_PROBABILITY || snippet == B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE) {
         const float probLogRecip = p[1];       // 1 / log(1 - prob), computed on the host in double
-        int prevJ = -1;
-        while(true) {
-            const float u = b200_rng_uniform(&rng);
-            prevJ += 1 + (int)B200_FMUL(b200_logf(u), probLogRecip);
-            if(snippet == B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE && (unsigned int)prevJ + trg_begin == pre) continue;
-            if(prevJ >= 0 && (unsigned int)prevJ < numPost) {
-                emit(n, (unsigned int)prevJ + trg_begin);
-                n++;
-            }
-            else {
-                break;
+        const unsigned int T = connectSubRows(snippet, p);
+        const unsigned int per = (numPost + T - 1u) / T;
+        for(unsigned int t = subFirst; t < T && t < subLast; t++) {
+            const unsigned int lo = t * per;
+            if(lo >= numPost) break;
+            const unsigned int span = min(per, numPost - lo);
+            b200_rng rng = b200_rng_init(seed, stream, (unsigned long long)pre * T + t);
+            int prevJ = -1;
+            while(true) {
+                const float u = b200_rng_uniform(&rng);
+                prevJ += 1 + (int)B200_FMUL(b200_logf(u), probLogRecip);
+                if(snippet == B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE && (unsigned int)prevJ + lo + trg_begin == pre) continue;
+                if(prevJ >= 0 && (unsigned int)prevJ < span) {
+                    emit(n, (unsigned int)prevJ + lo + trg_begin);
+                    n++;
+                }
+                else {
+                    break;
+                }
             }
         }
     }
     else {
+        b200_rng rng = b200_rng_init(seed, stream, pre);
         float x = 0.0f;
         for(unsigned int c = fixedLength; c != 0; c--) {
             const float u = b200_rng_uniform(&rng);

@@ -52,6 +52,26 @@ struct NearSpace
 
 constexpr unsigned int NEAR_MAX_RINGS = 64;
 
+// Sharded model: near synapses onto ANOTHER process's neurons travel as 64-bit words (weight bits << 32 | entry
+// word) through queues in that process's exchange arena, one queue per (step parity, sending process, sending
+// CTA).  Word 0 of a queue is its header, (step << 32 | number of entries), written once the CTA's chain warps are
+// through the step; the entries follow from word 1.  The receiving process's CTA of the same index waits for the
+// header, takes every entry as soon as it is non-zero (an entry's weight bits are never zero), adds it into its own
+// rings and zeroes the word again.  No fence is needed on either side: every word validates itself.  A CTA that
+// produces more entries than a queue holds reduces the rest straight into the other process's rings and fences
+// before it sends the header.
+constexpr unsigned int NEAR_QUEUE_WORDS = 2048;     // default capacity of one queue, header included (16 KB)
+constexpr unsigned int NEAR_QUEUE_COUNT = 160;      // queues per (parity, sending process): at least the grid size
+
+struct NearOutbox
+{
+    unsigned long long *queue[B200_MAX_RANKS];      // this CTA's queue of step parity 0 in every process's arena
+    unsigned int count[B200_MAX_RANKS];             // entries queued for each process in the current step
+    unsigned int words;                             // capacity of a queue, header included; 0: no queues
+    unsigned int fenced;                            // an entry went the direct way: fence before the header
+    unsigned long long parity_words;                // distance between the queues of parity 0 and 1, in words
+};
+
 __device__ __forceinline__ unsigned int nearDelay(unsigned int d, unsigned int D)
 {
     return d % D;
@@ -114,14 +134,16 @@ __global__ void nearFillKernel(const b200_synapse_group g, unsigned int ring, un
 // row has one block per process and `rings` one set of rings per process, the other processes'
 // mapped here: reductions into those travel over NVLink.  `front` is the phase of the step in
 // which the neuron spiked: a synapse of delay e lands in the slot the neuron update e + 1 steps
-// later reads.  Returns non-zero if a ring of another process was written: the caller then owes a
+// later reads.  With an outbox (`box`), entries for another process go into this CTA's queue in that
+// process's arena.  Returns non-zero if a ring of another process was written directly: the caller then owes a
 // system-wide fence before that process is told the step is complete.  (Measured on two GPUs: that
 // fence costs a spiking warp 7.2 k cycles behind about 50 reductions; making the additions with
 // atomics that return the old value and consuming the returns instead cost 9.6 k, they do not overlap.)
 template<bool SHARDED>
 __device__ __forceinline__ float nearDeliverRow(const uint2 *__restrict__ row, unsigned int shift, unsigned int peerShift,
                                                const NearRing *rings, unsigned int numRings, unsigned int rank,
-                                               unsigned int front, StepState *state)
+                                               unsigned int front, StepState *state,
+                                               NearOutbox *box = nullptr, unsigned int parity = 0u)
 {
     const unsigned int lane = threadIdx.x & 31u;
     const unsigned int cells = 1u << shift;
@@ -145,6 +167,16 @@ __device__ __forceinline__ float nearDeliverRow(const uint2 *__restrict__ row, u
                 const NearRing &ring = rings[owner * numRings + ((word >> 1) & 0x7Fu)];
                 const unsigned int post = word >> 8;
                 if(post < ring.num_neurons) {
+                    if(SHARDED && owner != rank && box && box->words) {
+                        const unsigned int pos = atomicAdd(&box->count[owner], 1u);
+                        if(pos + 1u < box->words) {
+                            asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::
+                                         "l"(box->queue[owner] + parity * box->parity_words + 1u + pos),
+                                         "l"(((unsigned long long)entry[u].y << 32) | word) : "memory");
+                            continue;
+                        }
+                        box->fenced = 1u;
+                    }
                     float *cell = ring.den_delay + (unsigned long long)ringSlot(front + 2u + (word & 1u), ring.D) * ring.num_neurons + post;
                     redAdd(cell, __uint_as_float(entry[u].y));
                     if(SHARDED && owner != rank) returned = 1.0f;

@@ -71,11 +71,11 @@ postsynapticUpdateKernel(const SynapseLaunch L)
 
 constexpr int REDUCE_BLOCK = 256;
 
-// `phases`: bit 0 reduce, bit 1 broadcast.  Both in one pass on one GPU; a data-parallel run
-// reduces, combines the targets of all processes (an all-reduce outside this kernel) and
-// broadcasts in a second pass.
+// `phases`: bit 0 reduce, bit 1 write back.  Both in one pass on one GPU.  A data-parallel run reduces
+// into `staged` (a segment of the buffer that one all-reduce combines over the processes), and in a
+// second pass takes the combined value from there, stores it as the target and writes it back.
 __global__ void __launch_bounds__(REDUCE_BLOCK)
-batchReduceKernel(const b200_custom_update_group u, unsigned int batch, unsigned int phases)
+batchReduceKernel(const b200_custom_update_group u, unsigned int batch, unsigned int phases, float *staged)
 {
     const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
     for(unsigned long long e = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; e < u.num_elements; e += stride) {
@@ -86,10 +86,11 @@ batchReduceKernel(const b200_custom_update_group u, unsigned int batch, unsigned
                 const float v = u.source[(unsigned long long)b * u.num_elements + e];
                 acc = (u.op == B200_REDUCE_SUM) ? B200_FADD(acc, v) : fmaxf(acc, v);
             }
-            u.target[e] = acc;
+            (staged ? staged : u.target)[e] = acc;
         }
         else {
-            acc = u.target[e];
+            acc = staged ? staged[e] : u.target[e];
+            if(staged) u.target[e] = acc;
         }
         if(u.broadcast && (phases & 2u)) {
             const float w = B200_FMUL(acc, u.scale);

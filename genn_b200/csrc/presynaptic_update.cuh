@@ -285,15 +285,25 @@ presynapticPostSpanKernel(const SynapseLaunch L)
 }
 
 // PROCEDURAL connectivity (presynapticUpdateStrategySIMT.cc:394-566): nothing of the matrix is
-// stored; the row of every spiking neuron is regenerated from its Philox stream, exactly as the
+// stored; the row of every spiking neuron is regenerated from its Philox streams, exactly as the
 // initialisation kernel would have written it (generateRow, init.cuh), and so is every weight that
-// is not a constant (the stream of a weight is keyed on pre * row_stride + position, as in
-// initSparseVarKernel).  One thread per spike walks its row; grid (group, 1, batch).
-__global__ void __launch_bounds__(PRE_BLOCK)
+// is not a constant (the stream of a weight is keyed on pre * row_stride + position in the row, as in
+// initSparseVarKernel).
+//
+// A work item is (spike, sub-row): T = connectSubRows() threads share one row, each regenerating the
+// synapses onto its own range of targets from its own stream (T a power of two of at most 32, so the
+// T items of a spike are neighbouring lanes of one warp).  The items of a (group, batch entry) are
+// spread over the whole grid: grid (x, groups, batch) with a grid-stride loop over the items, since
+// the number of spikes is only known on the device.  Every synapse costs one reduction into L2 and
+// no HBM traffic at all.
+constexpr unsigned int PROC_BLOCK = 256;
+
+__global__ void __launch_bounds__(PROC_BLOCK)
 presynapticProceduralKernel(const SynapseLaunch L)
 {
-    const b200_synapse_group &g = L.groups[blockIdx.x];
+    const b200_synapse_group &g = L.groups[blockIdx.y];
     const unsigned int b = blockIdx.z;
+    const unsigned int lane = threadIdx.x & 31u;
     const unsigned int k = L.state->phase;
     const unsigned int slots = g.src_delay_slots;
     const unsigned int rslot = ringSlot(k + slots - g.axonal_delay, slots);
@@ -301,29 +311,58 @@ presynapticProceduralKernel(const SynapseLaunch L)
     const unsigned int *spk = g.src_spk + ((unsigned long long)b * slots + rslot) * g.num_src;
     const unsigned int numTrg = g.num_trg;
     const unsigned int D = g.max_den_delay;
-    float *target = (D ? g.den_delay + (unsigned long long)b * D * numTrg : g.out_post + (unsigned long long)b * numTrg);
+    // dendritic delay is not generated procedurally: slot 0 of a ring is the front
+    float *target = (D ? g.den_delay + ((unsigned long long)b * D + ringSlot(k + 1, D)) * numTrg : g.out_post + (unsigned long long)b * numTrg);
     const bool constant = (g.wu_model == B200_WU_STATIC_PULSE_CONSTANT_WEIGHT);
-    for(unsigned int s = threadIdx.x; s < count; s += blockDim.x) {
-        const unsigned int pre = spk[s];
-        if(pre >= g.num_src) {
+    const unsigned int T = connectSubRows(g.proc_connect, g.proc_connect_params);
+    const unsigned long long items = (unsigned long long)count * T;
+    // whole warps stay in the loop together: the sub-rows of a spike exchange their lengths by shuffle
+    const unsigned long long itemsPadded = (items + 31ull) & ~31ull;
+    for(unsigned long long item = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; item < itemsPadded;
+        item += (unsigned long long)gridDim.x * blockDim.x) {
+        const bool live = item < items;
+        const unsigned int s = (unsigned int)(item / T), t = (unsigned int)(item - (unsigned long long)s * T);
+        unsigned int pre = live ? spk[s] : 0u;
+        if(live && pre >= g.num_src) {
             atomicOr(&L.state->error, ERR_IND_RANGE);
-            continue;
+            pre = 0xFFFFFFFFu;
         }
-        const unsigned int fixedLength = (g.proc_connect == B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT)
+        const bool work = live && pre != 0xFFFFFFFFu;
+        const unsigned int fixedLength = !work ? 0u : (g.proc_connect == B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT)
             ? (unsigned int)g.proc_connect_params[0] : (g.row_length ? g.row_length[pre] : 0u);
-        const unsigned int n = generateRow(g.proc_connect, g.proc_connect_params, pre, 0u, numTrg, fixedLength, L.seed, g.rng_stream,
-            [&](unsigned int at, unsigned int post) {
-                if(at >= g.row_stride) return;      // the row the initialisation kernel would have stored ends here
-                float w = g.wu_params[0];
-                if(!constant) {
-                    b200_rng rng = b200_rng_init(L.seed, g.proc_weight_stream, (unsigned long long)pre * g.row_stride + at);
-                    w = drawInitValue(g.proc_weight_init, g.proc_weight_params, &rng);
-                }
-                // dendritic delay is not generated procedurally: slot 0 of a ring is the front
-                redAdd(target + (D ? (unsigned long long)ringSlot(k + 1, D) * numTrg : 0ull) + post, w);
-            });
-        if(n > g.row_stride) atomicOr(&L.state->error, ERR_IND_RANGE);
-        if(L.count_events) atomicAdd(&L.state->synaptic_events, (unsigned long long)min(n, g.row_stride));
+        // where this sub-row starts in the row: only drawn weights depend on it, and they cost a first
+        // pass that counts the sub-row's synapses
+        unsigned int base = 0, mine = 0;
+        if(!constant && T > 1u) {
+            if(work) mine = generateRow(g.proc_connect, g.proc_connect_params, pre, 0u, numTrg, fixedLength, L.seed, g.rng_stream,
+                                        [](unsigned int, unsigned int) {}, t, t + 1u);
+            unsigned int incl = mine;
+            for(unsigned int o = 1; o < T; o <<= 1) {
+                const unsigned int v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
+                if((lane & (T - 1u)) >= o) incl += v;
+            }
+            base = incl - mine;
+        }
+        unsigned int n = 0;
+        if(work) {
+            n = generateRow(g.proc_connect, g.proc_connect_params, pre, 0u, numTrg, fixedLength, L.seed, g.rng_stream,
+                [&](unsigned int at, unsigned int post) {
+                    if(base + at >= g.row_stride) return;      // the row the initialisation kernel would have stored ends here
+                    float w = g.wu_params[0];
+                    if(!constant) {
+                        b200_rng rng = b200_rng_init(L.seed, g.proc_weight_stream, (unsigned long long)pre * g.row_stride + base + at);
+                        w = drawInitValue(g.proc_weight_init, g.proc_weight_params, &rng);
+                    }
+                    redAdd(target + post, w);
+                }, t, t + 1u);
+        }
+        // the whole row's length: sum over the T lanes of the spike
+        unsigned int rowLen = n;
+        for(unsigned int o = 1; o < T; o <<= 1) rowLen += __shfl_xor_sync(0xFFFFFFFFu, rowLen, o);
+        if(work && t == 0u) {
+            if(rowLen > g.row_stride) atomicOr(&L.state->error, ERR_IND_RANGE);
+            if(L.count_events) atomicAdd(&L.state->synaptic_events, (unsigned long long)min(rowLen, g.row_stride));
+        }
     }
 }
 }   // namespace b200

@@ -5,6 +5,7 @@
 // and the captured step graph.  The time-step path allocates nothing and never
 // synchronises; the host only enqueues (one cudaGraphLaunch per block of steps).
 #include <cuda_runtime.h>
+#include <dlfcn.h>
 
 #include <algorithm>
 #include <cctype>
@@ -192,6 +193,18 @@ struct b200_runner
     // spike exchange of a sharded model
     unsigned char *arena = nullptr;
     size_t arenaBytes = 0;
+    // data-parallel runs: communicator for the all-reduce inside batch-reduce custom updates, and the
+    // buffer the reduced values of a group are packed into for it
+    void *ncclComm = nullptr;
+    unsigned int ncclWorld = 1;
+    float *reducePacked = nullptr;
+    size_t reducePackedElements = 0;
+    // queues for near synapses between processes (near.cuh), behind the caller's part of the arena
+    size_t queueOffset = 0;
+    unsigned int queueWords = NEAR_QUEUE_WORDS;
+    bool useNearQueues = true;
+    bool queuesAgreed = false;                  // every process runs the same grid, which the queues are numbered by
+    unsigned int peerGrid[B200_MAX_RANKS] = {};
     unsigned char *peerArena[B200_MAX_RANKS] = {};
     bool peerLocal[B200_MAX_RANKS] = {};    // mapped by pointer (same process): nothing to close
     unsigned char **peerTable = nullptr;     // device copy of peerArena
@@ -465,6 +478,8 @@ int prepare(b200_runner *r)
             postSpanStarts.push_back(postSpanStarts.back() + (g.row_stride + PRE_BLOCK - 1) / PRE_BLOCK);
         }
         else if(g.connectivity == B200_CONN_PROCEDURAL) {
+            const unsigned int T = connectSubRows(g.proc_connect, g.proc_connect_params);
+            if(T > 32u || (T & (T - 1u))) return fail(B200_ERR_INVALID, "procedural group: %u sub-rows per row (a power of two of at most 32 is supported)", T);
             procedural.push_back(g);
             proceduralStarts.push_back(proceduralStarts.back() + 1);
         }
@@ -839,6 +854,9 @@ int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long 
     L.num_rings = r->numRings;
     L.near_rings = r->nearRings;
     L.near_spaces = r->nearSpaces;
+    L.queue_words = (r->sharded() && L.emit && r->useNearQueues && r->queuesAgreed) ? r->queueWords : 0u;
+    L.queue_count = NEAR_QUEUE_COUNT;
+    L.queue_offset = r->queueOffset;
     L.neuron.groups = r->neuronTable.d;
     L.neuron.block_start = r->neuronTable.blockStart;
     L.neuron.num_groups = r->neuronTable.num;
@@ -1181,8 +1199,11 @@ int enqueueSynapses(b200_runner *r, bool capturing)
     }
     if(r->proceduralTable.num) {
         ScopedTimer tm(r, "presynaptic_update", capturing);
-        const dim3 grid(r->proceduralTable.num, 1, r->batch);
-        presynapticProceduralKernel<<<grid, PRE_BLOCK, 0, r->stream>>>(synapseLaunch(r, r->proceduralTable));
+        // (spike, sub-row) items spread over the whole device; the spike count is only known there
+        int sms = 0;
+        CUDA_TRY(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, r->device));
+        const dim3 grid((unsigned int)sms * 8u, r->proceduralTable.num, r->batch);
+        presynapticProceduralKernel<<<grid, PROC_BLOCK, 0, r->stream>>>(synapseLaunch(r, r->proceduralTable));
         r->launches++;
     }
     if(r->learnTable.num) {
@@ -1294,6 +1315,46 @@ int b200_runner_create(int device, double dt, uint64_t seed, uint32_t batch_size
     return B200_OK;
 }
 
+/* ---- NCCL, resolved when first needed: the library that is already in the process (a host application
+ *      that bootstraps with torch.distributed has loaded one) or the system's.  The reference's CUDA backend
+ *      exports ncclGenerateUniqueID / ncclGetUniqueID / ncclInitCommunicator from the generated library
+ *      and emits one ncclAllReduce per reduction target (backends/cuda/backend.cc:219-226, 1360-1389,
+ *      backendCUDAHIP.h:240-292); here the targets of a group travel as ONE buffer. ------------------- */
+namespace
+{
+struct NcclId { char internal[128]; };                  // ncclUniqueId
+struct NcclApi
+{
+    void *lib = nullptr;
+    int (*getUniqueId)(NcclId*) = nullptr;
+    int (*commInitRank)(void**, int, NcclId, int) = nullptr;
+    int (*allReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*commDestroy)(void*) = nullptr;
+    const char *(*getErrorString)(int) = nullptr;
+};
+constexpr int NCCL_FLOAT32 = 7, NCCL_SUM = 0, NCCL_MAX = 2;     // ncclDataType_t / ncclRedOp_t values of nccl.h
+
+NcclApi *ncclApi()
+{
+    static NcclApi api;
+    if(api.lib) return &api;
+    void *lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_NOLOAD);
+    if(!lib) lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_LOCAL);
+    if(!lib) lib = dlopen("libnccl.so", RTLD_NOW | RTLD_LOCAL);
+    if(!lib) return nullptr;
+    api.getUniqueId = reinterpret_cast<decltype(api.getUniqueId)>(dlsym(lib, "ncclGetUniqueId"));
+    api.commInitRank = reinterpret_cast<decltype(api.commInitRank)>(dlsym(lib, "ncclCommInitRank"));
+    api.allReduce = reinterpret_cast<decltype(api.allReduce)>(dlsym(lib, "ncclAllReduce"));
+    api.commDestroy = reinterpret_cast<decltype(api.commDestroy)>(dlsym(lib, "ncclCommDestroy"));
+    api.getErrorString = reinterpret_cast<decltype(api.getErrorString)>(dlsym(lib, "ncclGetErrorString"));
+    if(!api.getUniqueId || !api.commInitRank || !api.allReduce || !api.commDestroy || !api.getErrorString) return nullptr;
+    api.lib = lib;
+    return &api;
+}
+}   // namespace
+
+#define NCCL_TRY(api, call) do { const int e_ = (call); if(e_ != 0) return fail(B200_ERR_CUDA, "NCCL: %s (%s)", (api)->getErrorString(e_), #call); } while(0)
+
 int b200_runner_destroy(b200_runner *r)
 {
     if(!r) return B200_OK;
@@ -1317,6 +1378,8 @@ int b200_runner_destroy(b200_runner *r)
     for(unsigned int p = 0; p < B200_MAX_RANKS; p++) {
         if(r->peerArena[p] && !r->peerLocal[p]) cudaIpcCloseMemHandle(r->peerArena[p]);
     }
+    if(r->ncclComm && ncclApi()) ncclApi()->commDestroy(r->ncclComm);
+    if(r->reducePacked) cudaFree(r->reducePacked);
     if(r->arena) cudaFree(r->arena);
     if(r->peerTable) cudaFree(r->peerTable);
     for(auto &a : r->arrays) cudaFree(a.first);
@@ -1357,17 +1420,35 @@ int b200_host_free(b200_runner *r, void *host_ptr)
     return B200_OK;
 }
 
+// The arena a process allocates: the caller's bytes, then the near-synapse queues of both step parities
+// from every process (the same layout in every process: peers address each other's arenas by offset).
+static size_t exchangeQueueOffset(size_t bytes) { return (bytes + 255) & ~(size_t)255; }
+static size_t exchangeTotalBytes(size_t bytes)
+{
+    return exchangeQueueOffset(bytes) + (size_t)2 * B200_MAX_RANKS * NEAR_QUEUE_COUNT * NEAR_QUEUE_WORDS * sizeof(unsigned long long)
+        + ARRAY_TAIL_PAD;
+}
+
 int b200_exchange_alloc(b200_runner *r, size_t bytes, void **device_ptr)
 {
     if(!r || !device_ptr || bytes == 0) return fail(B200_ERR_INVALID, "bad arguments to b200_exchange_alloc");
     if(r->arena) return fail(B200_ERR_STATE, "the exchange arena has already been allocated");
     CUDA_TRY(cudaSetDevice(r->device));
     void *p = nullptr;
-    CUDA_TRY(cudaMalloc(&p, bytes + ARRAY_TAIL_PAD));
-    CUDA_TRY(cudaMemset(p, 0, bytes + ARRAY_TAIL_PAD));
+    const size_t total = exchangeTotalBytes(bytes);
+    CUDA_TRY(cudaMalloc(&p, total));
+    CUDA_TRY(cudaMemset(p, 0, total));
     r->arena = static_cast<unsigned char*>(p);
     r->arenaBytes = bytes;
+    r->queueOffset = exchangeQueueOffset(bytes);
     *device_ptr = p;
+    return B200_OK;
+}
+
+int b200_exchange_bytes(b200_runner *r, size_t *bytes)
+{
+    if(!r || !r->arena || !bytes) return fail(B200_ERR_STATE, "no exchange arena");
+    *bytes = exchangeTotalBytes(r->arenaBytes);
     return B200_OK;
 }
 
@@ -1429,7 +1510,7 @@ int b200_near_export(b200_runner *r, void *handle_64_bytes, uint64_t *meta, uint
     cudaIpcMemHandle_t h;
     CUDA_TRY(cudaIpcGetMemHandle(&h, r->nearTable));
     memcpy(handle_64_bytes, &h, sizeof(h));
-    meta[0] = 1; meta[2] = r->numRings;
+    meta[0] = 1; meta[2] = (uint64_t)r->numRings | ((uint64_t)r->fusedGrid << 32);
     for(size_t ni = 0; ni < groups; ni++) {
         meta[3 + 2 * ni] = r->nearCellHost[ni];
         meta[4 + 2 * ni] = r->nearShiftHost[ni];
@@ -1447,7 +1528,8 @@ int b200_near_import(b200_runner *r, uint32_t peer_rank, const void *handle_64_b
     if(!r || !handle_64_bytes || !meta || !common_shift || peer_rank >= r->world) return fail(B200_ERR_INVALID, "bad arguments to b200_near_import");
     const size_t groups = r->neuronGroups.size();
     if(r->nearImported.size() != groups || r->nearPeerDone.size() != r->world) return fail(B200_ERR_STATE, "b200_near_export has to come first");
-    if(!meta[0] || meta[1] != groups || meta[2] != r->numRings) return fail(B200_ERR_STATE, "process %u does not qualify or runs another model", peer_rank);
+    if(!meta[0] || meta[1] != groups || (uint32_t)meta[2] != r->numRings) return fail(B200_ERR_STATE, "process %u does not qualify or runs another model", peer_rank);
+    r->peerGrid[peer_rank] = (unsigned int)(meta[2] >> 32);
     CUDA_TRY(cudaSetDevice(r->device));
     const uint2 *table = r->nearTable;
     void *mapped = nullptr;
@@ -1519,6 +1601,10 @@ int b200_near_finish(b200_runner *r, int agreed)
     CUDA_TRY(cudaMalloc(&r->nearSpaces, sizeof(NearSpace) * r->nearSpacesAll.size()));
     CUDA_TRY(cudaMemcpy(r->nearSpaces, r->nearSpacesAll.data(), sizeof(NearSpace) * r->nearSpacesAll.size(), cudaMemcpyHostToDevice));
     r->emitAgreed = true;
+    r->queuesAgreed = r->fusedGrid <= NEAR_QUEUE_COUNT;
+    for(uint32_t p = 0; p < r->world; p++) {
+        if(r->peerGrid[p] != r->fusedGrid) r->queuesAgreed = false;
+    }
     r->lagStale = true;
     return B200_OK;
 }
@@ -1669,6 +1755,11 @@ int b200_set_option(b200_runner *r, const char *name, double value)
     else if(n == "use_fused") r->useFused = (value != 0.0);
     else if(n == "use_lag") { r->useLag = (value != 0.0); r->lagStale = true; }
     else if(n == "use_split") { r->useSplit = (value != 0.0); r->lagStale = true; }
+    else if(n == "use_near_queues") r->useNearQueues = (value != 0.0);
+    else if(n == "near_queue_words") {
+        if(value < 2.0 || value > (double)NEAR_QUEUE_WORDS) return fail(B200_ERR_INVALID, "near_queue_words must lie in [2, %u]", NEAR_QUEUE_WORDS);
+        r->queueWords = (unsigned int)value;
+    }
     else if(n == "use_emit") { r->useEmit = (value != 0.0); r->lagStale = true; }
     else if(n == "stream_warps") { r->streamWarpsWanted = (int)value; r->lagStale = true; }
     else if(n == "lag_agreed") { r->lagAgreed = (value != 0.0); r->lagStale = true; }
@@ -1859,15 +1950,86 @@ int b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_ti
     return B200_OK;
 }
 
+
+int b200_nccl_unique_id(void *id_128_bytes)
+{
+    if(!id_128_bytes) return fail(B200_ERR_INVALID, "null id buffer");
+    NcclApi *api = ncclApi();
+    if(!api) return fail(B200_ERR_STATE, "libnccl.so.2 could not be loaded: %s", dlerror());
+    NcclId id;
+    NCCL_TRY(api, api->getUniqueId(&id));
+    memcpy(id_128_bytes, &id, sizeof(id));
+    return B200_OK;
+}
+
+int b200_nccl_init(b200_runner *r, const void *id_128_bytes, uint32_t rank, uint32_t world)
+{
+    if(!r || !id_128_bytes || world == 0 || rank >= world) return fail(B200_ERR_INVALID, "bad arguments to b200_nccl_init");
+    if(r->ncclComm) return fail(B200_ERR_STATE, "the communicator has already been created");
+    NcclApi *api = ncclApi();
+    if(!api) return fail(B200_ERR_STATE, "libnccl.so.2 could not be loaded: %s", dlerror());
+    CUDA_TRY(cudaSetDevice(r->device));
+    NcclId id;
+    memcpy(&id, id_128_bytes, sizeof(id));
+    NCCL_TRY(api, api->commInitRank(&r->ncclComm, (int)world, id, (int)rank));
+    r->ncclWorld = world;
+    return B200_OK;
+}
+
+// A custom update group.  `phases`: bit 0 reduce over the batch, bit 1 write back.  With a communicator
+// (data-parallel run: every process holds a share of the batch) the reduced values of ALL updates of the
+// group are packed into one buffer, sums first, combined with one all-reduce per operation on the
+// runner's stream, and written back from there: no host synchronisation anywhere.
 static int runCustomUpdate(b200_runner *r, const char *name, unsigned int phases)
 {
     auto it = r->customUpdates.find(name);
     if(it == r->customUpdates.end()) return fail(B200_ERR_INVALID, "no custom update group '%s'", name);
     ScopedTimer tm(r, std::string("custom_update_") + name, false);
-    for(const auto &u : it->second) {
+    const bool combine = r->ncclComm && r->ncclWorld > 1 && phases == 3u;
+    auto blocksFor = [](uint64_t n) { return (unsigned int)std::min<uint64_t>((n + REDUCE_BLOCK - 1) / REDUCE_BLOCK, 148u * 16u); };
+    if(!combine) {
+        for(const auto &u : it->second) {
+            if(u.num_elements == 0) continue;
+            batchReduceKernel<<<blocksFor(u.num_elements), REDUCE_BLOCK, 0, r->stream>>>(u, r->batch, phases, nullptr);
+            r->launches++;
+        }
+        CUDA_TRY(cudaPeekAtLastError());
+        return B200_OK;
+    }
+    // layout of the packed buffer: every update's segment starts on a 16-byte boundary
+    std::vector<size_t> offset(it->second.size(), 0);
+    size_t total = 0, sums = 0;
+    for(int pass = 0; pass < 2; pass++) {
+        for(size_t i = 0; i < it->second.size(); i++) {
+            const auto &u = it->second[i];
+            if((u.op == B200_REDUCE_SUM) != (pass == 0)) continue;
+            offset[i] = total;
+            total += (u.num_elements + 3) & ~(uint64_t)3;
+        }
+        if(pass == 0) sums = total;
+    }
+    if(total > r->reducePackedElements) {
+        CUDA_TRY(cudaStreamSynchronize(r->stream));
+        if(r->reducePacked) CUDA_TRY(cudaFree(r->reducePacked));
+        r->reducePacked = nullptr;
+        CUDA_TRY(cudaMalloc(&r->reducePacked, sizeof(float) * total));
+        CUDA_TRY(cudaMemsetAsync(r->reducePacked, 0, sizeof(float) * total, r->stream));
+        r->reducePackedElements = total;
+    }
+    for(size_t i = 0; i < it->second.size(); i++) {
+        const auto &u = it->second[i];
         if(u.num_elements == 0) continue;
-        const unsigned int blocks = (unsigned int)std::min<uint64_t>((u.num_elements + REDUCE_BLOCK - 1) / REDUCE_BLOCK, 148u * 16u);
-        batchReduceKernel<<<blocks, REDUCE_BLOCK, 0, r->stream>>>(u, r->batch, phases);
+        batchReduceKernel<<<blocksFor(u.num_elements), REDUCE_BLOCK, 0, r->stream>>>(u, r->batch, 1u, r->reducePacked + offset[i]);
+        r->launches++;
+    }
+    CUDA_TRY(cudaPeekAtLastError());
+    NcclApi *api = ncclApi();
+    if(sums) NCCL_TRY(api, api->allReduce(r->reducePacked, r->reducePacked, sums, NCCL_FLOAT32, NCCL_SUM, r->ncclComm, r->stream));
+    if(total > sums) NCCL_TRY(api, api->allReduce(r->reducePacked + sums, r->reducePacked + sums, total - sums, NCCL_FLOAT32, NCCL_MAX, r->ncclComm, r->stream));
+    for(size_t i = 0; i < it->second.size(); i++) {
+        const auto &u = it->second[i];
+        if(u.num_elements == 0) continue;
+        batchReduceKernel<<<blocksFor(u.num_elements), REDUCE_BLOCK, 0, r->stream>>>(u, r->batch, 2u, r->reducePacked + offset[i]);
         r->launches++;
     }
     CUDA_TRY(cudaPeekAtLastError());
@@ -2062,6 +2224,25 @@ int b200_step_time_timed(b200_runner *r, uint64_t num_steps, uint64_t num_record
     CUDA_TRY(cudaEventRecord(r->evC, r->stream));
     e = b200_step_time(r, num_steps, num_recording_timesteps);
     if(e) return e;
+    CUDA_TRY(cudaEventRecord(r->evD, r->stream));
+    CUDA_TRY(cudaEventSynchronize(r->evD));
+    CUDA_TRY(cudaEventElapsedTime(milliseconds, r->evC, r->evD));
+    return B200_OK;
+}
+
+int b200_timed_begin(b200_runner *r)
+{
+    if(!r) return fail(B200_ERR_INVALID, "null runner");
+    int e = prepare(r);
+    if(e) return e;
+    CUDA_TRY(cudaStreamSynchronize(r->stream));
+    CUDA_TRY(cudaEventRecord(r->evC, r->stream));
+    return B200_OK;
+}
+
+int b200_timed_end(b200_runner *r, float *milliseconds)
+{
+    if(!r || !milliseconds) return fail(B200_ERR_INVALID, "null argument");
     CUDA_TRY(cudaEventRecord(r->evD, r->stream));
     CUDA_TRY(cudaEventSynchronize(r->evD));
     CUDA_TRY(cudaEventElapsedTime(milliseconds, r->evC, r->evD));

@@ -334,7 +334,23 @@ streamStepKernel(FusedLaunch L)
     __shared__ StreamShared sh;
     __shared__ unsigned char *peerArena[B200_MAX_RANKS];
     __shared__ ExchangeCtx exchange;
-    if(threadIdx.x < B200_MAX_RANKS) peerArena[threadIdx.x] = L.peer_table ? L.peer_table[threadIdx.x] : nullptr;
+    __shared__ NearOutbox outbox;
+    if(threadIdx.x < B200_MAX_RANKS) {
+        peerArena[threadIdx.x] = L.peer_table ? L.peer_table[threadIdx.x] : nullptr;
+        // this CTA's queue (step parity 0) in the arena of process threadIdx.x: written by this process, so
+        // in the section of L.rank there
+        unsigned char *base = (threadIdx.x == L.rank) ? L.arena : peerArena[threadIdx.x];
+        outbox.queue[threadIdx.x] = (SHARDED && L.queue_words && base && blockIdx.x < L.queue_count)
+            ? reinterpret_cast<unsigned long long*>(base + L.queue_offset) +
+              ((unsigned long long)L.rank * L.queue_count + blockIdx.x) * L.queue_words
+            : nullptr;
+        outbox.count[threadIdx.x] = 0u;
+    }
+    if(threadIdx.x == 0) {
+        outbox.words = (SHARDED && L.emit && L.world > 1 && blockIdx.x < L.queue_count) ? L.queue_words : 0u;
+        outbox.fenced = 0u;
+        outbox.parity_words = (unsigned long long)L.world * L.queue_count * L.queue_words;
+    }
     if(threadIdx.x < 32) sh.streamDone[threadIdx.x] = 0u;
     if(threadIdx.x == 0) {
         exchange.world = L.world;
@@ -688,7 +704,8 @@ streamStepKernel(FusedLaunch L)
                     if(space.shift != 0xFFFFFFFFu) {
                         const uint2 *row = space.rows + ((unsigned long long)(id - space.first_row) << space.shift);
                         if(SHARDED && L.world > 1) {
-                            returned += nearDeliverRow<true>(row, space.shift, space.peer_shift, L.near_rings, L.num_rings, L.rank, k, state);
+                            returned += nearDeliverRow<true>(row, space.shift, space.peer_shift, L.near_rings, L.num_rings, L.rank, k, state,
+                                                             &outbox, (unsigned int)((done0 + step + 1) & 1ull));
                         }
                         else {
                             nearDeliverRow<false>(row, space.shift, space.peer_shift, L.near_rings, L.num_rings, 0u, k, state);
@@ -698,7 +715,8 @@ streamStepKernel(FusedLaunch L)
                 // additions into another GPU's rings must have landed there before that GPU is told (after
                 // the barrier below) that this step is complete
                 const long long n1 = timeIt ? clock64() : 0;
-                if(SHARDED && __any_sync(0xFFFFFFFFu, returned != 0.0f)) __threadfence_system();
+                // (with queues the thread that sends the header fences, and only if some entry went the direct way)
+                if(SHARDED && !outbox.words && __any_sync(0xFFFFFFFFu, returned != 0.0f)) __threadfence_system();
                 if(timeIt && lane == 0) {       // probes 8-10: near delivery, the fence behind it, spiking warps
                     atomicAdd(&state->probe[8], (unsigned long long)(n1 - n0));
                     atomicAdd(&state->probe[9], (unsigned long long)(clock64() - n1));
@@ -729,7 +747,64 @@ streamStepKernel(FusedLaunch L)
             // cumulative over what this thread has just observed)
             if(prof) cyc[5] += (unsigned long long)(clock64() - since);
         }
+        const bool queued = SHARDED && emit && L.world > 1 && outbox.words != 0u;
+        if(queued && step + 1 < L.num_steps) {
+            // Near synapses between processes.  Out: the header of this CTA's queue in every other process's
+            // arena (the entries went out while the neurons were updated).  In: the queues the CTAs of this
+            // index in the other processes filled for this process, added into its rings BEFORE this CTA
+            // arrives at the barrier, so that the next neuron update finds them.  A queue of this step's
+            // parity is written again two steps on: by then its sender has passed a barrier that every CTA of
+            // this process reached only behind its own sends of the step in between, hence behind this read.
+            // (Across launches: a launch starts by fetching every process's spike counts of the step before,
+            // which those publish behind their last barrier.)
+            const long long x0 = prof ? clock64() : 0;
+            chainSync(chainThreads);
+            const unsigned long long tag = done0 + step + 1;
+            const unsigned long long parityWords = (tag & 1ull) * outbox.parity_words;
+            if(threadIdx.x < L.world && threadIdx.x != L.rank) {
+                if(outbox.fenced) __threadfence_system();
+                const unsigned int n = min(outbox.count[threadIdx.x], outbox.words - 1u);
+                storeRelaxedSys(outbox.queue[threadIdx.x] + parityWords, (tag << 32) | n);
+                outbox.count[threadIdx.x] = 0u;
+            }
+            for(unsigned int p = warp; p < L.world; p += chainWarps) {
+                if(p == L.rank) continue;
+                unsigned long long *queue = reinterpret_cast<unsigned long long*>(L.arena + L.queue_offset) + parityWords +
+                    ((unsigned long long)p * L.queue_count + blockIdx.x) * L.queue_words;
+                unsigned int n = 0;
+                if(lane == 0) {
+                    const long long h0 = L.profile ? clock64() : 0;
+                    n = min(awaitWord(queue, tag, state), outbox.words - 1u);
+                    // probe 7: CTA 0's wait for the headers of the other processes (summed over them)
+                    if(L.profile && blockIdx.x == 0) atomicAdd(&state->probe[7], (unsigned long long)(clock64() - h0));
+                }
+                n = __shfl_sync(0xFFFFFFFFu, n, 0);
+                for(unsigned int i = lane; i < n; i += 32u) {
+                    unsigned long long e = 0, polls = 0;
+                    while((e = loadRelaxedSys(queue + 1u + i)) == 0ull) {
+                        if(++polls > state->exchange_spin_limit) {
+                            atomicOr(&state->error, ERR_EXCHANGE_TIMEOUT);
+                            break;
+                        }
+                    }
+                    if(e == 0ull) continue;
+                    storeRelaxedSys(queue + 1u + i, 0ull);
+                    const unsigned int word = (unsigned int)e;
+                    const NearRing &ring = L.near_rings[L.rank * L.num_rings + ((word >> 1) & 0x7Fu)];
+                    const unsigned int post = word >> 8;
+                    if(post < ring.num_neurons) {
+                        redAdd(ring.den_delay + (unsigned long long)ringSlot(k + 2u + (word & 1u), ring.D) * ring.num_neurons + post,
+                               __uint_as_float((unsigned int)(e >> 32)));
+                    }
+                    else {
+                        atomicOr(&state->error, ERR_IND_RANGE);
+                    }
+                }
+            }
+            if(prof) sh.waited[1] += (unsigned long long)(clock64() - x0);
+        }
         arrive();
+        if(queued && threadIdx.x == 0) outbox.fenced = 0u;
         // every chain thread is past its neuron update: the tag of the NEXT step's spike words may change
         if(SHARDED && emit && L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 2;
         if(emit && mine && myActive && step + 1 < L.num_steps) {
@@ -763,7 +838,8 @@ streamStepKernel(FusedLaunch L)
         }
         // emit mode of a sharded model: the next neuron update reads what the other processes' spiking
         // threads pushed into this process's rings, so their step must be complete too
-        if(!((SHARDED && emit && L.world > 1) ? wait(done0 + step + 1, ringSlot(k + 1u, L.neuron.groups[0].num_delay_slots)) : wait())) B200_CHAIN_ABORT();
+        // (with queues, the headers this CTA has waited for above say the same of the CTAs that can reach it)
+        if(!((SHARDED && emit && L.world > 1 && !queued) ? wait(done0 + step + 1, ringSlot(k + 1u, L.neuron.groups[0].num_delay_slots)) : wait())) B200_CHAIN_ABORT();
         if(emit && threadIdx.x == 0) sh.stepPassed = (unsigned int)(step + 1);    // the stream may read this step's spikes
         k = (k + 1 == period) ? 0u : k + 1;
         if(prof) {

@@ -410,6 +410,7 @@ class Plan:
             cp = [float(v) for v in s.connect.params.values()] + [0.0] * 4
             if s.connect.snippet in ("FixedProbability", "FixedProbabilityNoAutapse"):
                 cp[1] = 1.0 / math.log(1.0 - cp[0])
+                cp[2] = float(s.num_threads_per_spike)      # sub-rows of a row, each with a stream of its own
             for i in range(4):
                 d.proc_connect_params[i] = _f32(cp[i])
             d.rng_stream, d.proc_weight_stream = s.proc_streams

@@ -161,7 +161,9 @@ class Runtime:
             if peer in self.local_peers:
                 # a pointer, or a callable that is given the arena size and returns one
                 where = self.local_peers[peer]
-                where = where(self.plan.exchange.nbytes) if callable(where) else where
+                total = C.c_size_t(0)
+                check(self.lib.b200_exchange_bytes(self.handle, C.byref(total)))
+                where = where(total.value) if callable(where) else where
                 check(self.lib.b200_exchange_set_peer(self.handle, peer, C.c_void_p(where)))
             else:
                 check(self.lib.b200_exchange_open_peer(self.handle, peer, C.create_string_buffer(h, 64)))
@@ -233,6 +235,7 @@ class Runtime:
             self.plan.push(f"{s.name}.row_length", rl)
         elif snippet in (abi.CONNECT_FIXED_PROBABILITY, abi.CONNECT_FIXED_PROBABILITY_NO_AUTAPSE):
             params[1] = 1.0 / math.log(1.0 - task.params[0])
+            params[2] = float(s.num_threads_per_spike)      # sub-rows of a row (init.cuh: generateRow)
         check(self.lib.b200_init_sparse_connectivity(self.handle, snippet, params, ns, nt, s.row_stride,
                                                      np.dtype(s.ind_dtype).itemsize, begin, end,
                                                      a[f"{s.name}.row_length"].ptr, a[f"{s.name}.ind"].ptr,
@@ -283,6 +286,15 @@ class Runtime:
         check(self.lib.b200_step_time_timed(self.handle, num_steps, self.num_recording_timesteps, C.byref(ms)))
         return float(ms.value)
 
+    def timed_begin(self):
+        """CUDA event on the runner's stream; ``timed_end`` returns the milliseconds since."""
+        check(self.lib.b200_timed_begin(self.handle))
+
+    def timed_end(self) -> float:
+        ms = C.c_float()
+        check(self.lib.b200_timed_end(self.handle, C.byref(ms)))
+        return float(ms.value)
+
     def update_synapses(self):
         check(self.lib.b200_update_synapses(self.handle))
 
@@ -312,20 +324,29 @@ class Runtime:
             v._array = trg.handle
             cu.vars[cu.target_name] = v
 
+    def init_data_parallel(self, rank: Optional[int] = None, world: Optional[int] = None, gather=None):
+        """Every process holds a share of the batch: create the NCCL communicator over which the batch-reduce
+        custom updates combine their values (the reference: enableNCCLReductions and the three ncclXxx symbols
+        of the generated library, genn_model.py / backends/cuda/backend.cc:219-226).  Rank 0 obtains the id;
+        ``gather(bytes) -> [bytes per rank]`` hands it round (default: ``torch.distributed``)."""
+        if rank is None or world is None:
+            import torch.distributed as dist
+            rank, world = dist.get_rank(), dist.get_world_size()
+        ident = C.create_string_buffer(128)
+        if rank == 0:
+            check(self.lib.b200_nccl_unique_id(ident))
+        everyone = (gather or all_gather_bytes)(ident.raw)
+        if len(everyone) != world:
+            raise abi.B200Error(f"expected {world} ids, got {len(everyone)}")
+        check(self.lib.b200_nccl_init(self.handle, C.create_string_buffer(everyone[0], 128), rank, world))
+        self.data_parallel = (rank, world)
+
     def custom_update(self, name: str, all_reduce: bool = False):
-        """``all_reduce``: a data-parallel run (every process holds a share of the batch): reduce this
-        share, combine the targets of all processes with NCCL, write the combined value back."""
-        if not all_reduce:
-            check(self.lib.b200_custom_update(self.handle, name.encode()))
-            return
-        import torch
-        from .collectives import all_reduce_targets, device_tensor
-        check(self.lib.b200_custom_update_reduce(self.handle, name.encode()))
-        self.synchronize()
-        targets = self._cu_targets.get(name, [])
-        all_reduce_targets([device_tensor(t.ptr, t.shape, self.device) for t, _ in targets], [op for _, op in targets])
-        torch.cuda.synchronize(self.device)
-        check(self.lib.b200_custom_update_broadcast(self.handle, name.encode()))
+        """``all_reduce``: a data-parallel run: the reduced values are combined over all processes before
+        they are written back (the communicator is created on first use if init_data_parallel was not called)."""
+        if all_reduce and getattr(self, "data_parallel", None) is None:
+            self.init_data_parallel()
+        check(self.lib.b200_custom_update(self.handle, name.encode()))
 
     def synchronize(self):
         check(self.lib.b200_synchronize(self.handle))

@@ -13,6 +13,8 @@ from __future__ import annotations
 import math
 from typing import Dict, Optional, Tuple
 
+import os
+
 import numpy as np
 
 from .model import (GeNNModel, init_postsynaptic, init_sparse_connectivity, init_var,
@@ -197,24 +199,42 @@ def potjans(neuron_scale: float = 1.0, seed: int = 1234, dt: float = 0.1,
                                  {"weight": POTJANS_MEAN_W, "tauSyn": 0.5, "rate": rate}, {"current": 0.0})
         pop.spike_recording_enabled = record
         pops[name] = pop
-    for src, trg, num, mean_w, sd_w, md, sd, mxd in potjans_projections(neuron_scale):
+    drawn = {}
+    if host_connectivity:
+        # every projection has a random stream of its own (seed, projection index), so the projections
+        # can be drawn side by side: numpy releases the interpreter lock inside its generators
+        from concurrent.futures import ThreadPoolExecutor
+        projections = list(potjans_projections(neuron_scale))
+
+        def draw(index):
+            src, trg, num, mean_w, sd_w, md, sd, mxd = projections[index]
+            ns, nt = pops[src].num_neurons, pops[trg].num_neurons
+            lo, hi = (0.0, float(np.finfo(np.float32).max)) if mean_w > 0 else (-float(np.finfo(np.float32).max), 0.0)
+            prng = np.random.default_rng([seed, 1000 + index])
+            # `num` synapses placed uniformly with replacement (FixedNumberTotalWithReplacement): the row
+            # lengths are multinomial; drawing them first gives the pairs row by row without a sort
+            counts = prng.multinomial(num, np.full(ns, 1.0 / ns))
+            pre = np.repeat(np.arange(ns, dtype=np.uint32), counts)
+            post = prng.integers(0, nt, size=num, dtype=np.uint32)
+            g = truncated_normal(prng, mean_w, sd_w, lo, hi, num)
+            # NormalClippedDelay: truncated normal in time steps, then rint
+            d = truncated_normal(prng, md / dt, sd / dt, min_delay / dt, mxd / dt, num)
+            np.rint(d, out=d)
+            d = d.astype(np.uint8)
+            if shard is not None:
+                from .plan import shard_bounds
+                bounds = shard_bounds(nt, shard[1])
+                keep = (post >= bounds[shard[0]]) & (post < bounds[shard[0] + 1])
+                pre, post, g, d = pre[keep], post[keep], g[keep], d[keep]
+            return pre, post, g, d
+
+        with ThreadPoolExecutor(max_workers=max(1, min(16, os.cpu_count() or 1))) as pool:
+            drawn = dict(enumerate(pool.map(draw, range(len(projections)))))
+    for index, (src, trg, num, mean_w, sd_w, md, sd, mxd) in enumerate(potjans_projections(neuron_scale)):
         ns, nt = pops[src].num_neurons, pops[trg].num_neurons
         lo, hi = (0.0, float(np.finfo(np.float32).max)) if mean_w > 0 else (-float(np.finfo(np.float32).max), 0.0)
         if host_connectivity:
-            # `num` synapses placed uniformly with replacement (FixedNumberTotalWithReplacement): the row
-            # lengths are multinomial; drawing them first gives the pairs row by row without a sort
-            counts = rng.multinomial(num, np.full(ns, 1.0 / ns))
-            pre = np.repeat(np.arange(ns, dtype=np.uint32), counts)
-            post = rng.integers(0, nt, size=num, dtype=np.uint32)
-            g = truncated_normal(rng, mean_w, sd_w, lo, hi, num).astype(np.float32)
-            # NormalClippedDelay: truncated normal in time steps, then rint
-            d = np.rint(truncated_normal(rng, md / dt, sd / dt, min_delay / dt, mxd / dt, num)).astype(np.uint8)
-            if shard is not None:
-                from .plan import shard_bounds
-                rank, world = shard
-                bounds = shard_bounds(nt, world)
-                keep = (post >= bounds[rank]) & (post < bounds[rank + 1])
-                pre, post, g, d = pre[keep], post[keep], g[keep], d[keep]
+            pre, post, g, d = drawn.pop(index)
             wu = init_weight_update("StaticPulseDendriticDelay", {}, {"g": g, "d": d})
             sg = m.add_synapse_population(f"{src}_{trg}", "SPARSE", pops[src], pops[trg], wu,
                                           init_postsynaptic("ExpCurr", {"tau": 0.5}))
@@ -289,3 +309,73 @@ def cond_ei(neuron_scale: float = 1.0, seed: int = 4321, dt: float = 0.1, in_deg
             sg.set_sparse_connections(pre, post_all[sel])
             sg.axonal_delay_steps = delay_steps
     return m
+
+
+# ---------------------------------------------------------------------------
+# PROCEDURAL connectivity stress test (config 4)
+# ---------------------------------------------------------------------------
+def procedural_stress(num_neurons: int = 1_000_000, prob: float = 0.001, driven_fraction: float = 0.1,
+                      drive_rate_hz: float = 5.0, threads_per_spike: int = 32, seed: int = 77,
+                      dt: float = 1.0, record: bool = False) -> GeNNModel:
+    """``num_neurons`` LIF neurons, recurrently connected with probability ``prob`` through PROCEDURAL
+    connectivity: no synapse is stored, every spike regenerates its row (about ``prob * num_neurons``
+    targets) and the weights (Normal, mean 0.1 nA, sd 0.01) from Philox streams keyed on the seed and
+    the presynaptic index.  ``driven_fraction`` of the neurons receive a Poisson drive of
+    ``drive_rate_hz`` (one PoissonExp source each, strong enough that every drive event makes a spike);
+    they form a population of their own, so the network has 2 x 2 recurrent projections.
+    ``threads_per_spike`` threads share each row.  Purely excitatory: the network runs up to the rate
+    its refractory period allows, which is what a stress test of the regeneration path wants."""
+    m = GeNNModel("float", "procedural_stress")
+    m.dt = dt
+    m.seed = seed
+    lif = {"C": 0.25, "TauM": 20.0, "Vrest": -65.0, "Vreset": -70.0, "Vthresh": -50.0, "Ioffset": 0.0, "TauRefrac": 5.0}
+    n_driven = int(round(num_neurons * driven_fraction))
+    pops = {}
+    for name, n in (("driven", n_driven), ("rest", num_neurons - n_driven)):
+        if n == 0:
+            continue
+        pops[name] = m.add_neuron_population(name, n, "LIF", lif, {"V": init_var("Uniform", {"min": -65.0, "max": -55.0}),
+                                                                   "RefracTime": 0.0})
+        pops[name].spike_recording_enabled = record
+    if "driven" in pops:
+        m.add_current_source("drive", "PoissonExp", pops["driven"], {"weight": 1.0, "tauSyn": 5.0, "rate": drive_rate_hz},
+                             {"current": 0.0})
+    for a in pops:
+        for b in pops:
+            sg = m.add_synapse_population(f"{a}_{b}", "PROCEDURAL", pops[a], pops[b],
+                                          init_weight_update("StaticPulse", {}, {"g": init_var("Normal", {"mean": 0.1, "sd": 0.01})}),
+                                          init_postsynaptic("ExpCurr", {"tau": 5.0}),
+                                          init_sparse_connectivity("FixedProbability", {"prob": prob}))
+            sg.num_threads_per_spike = threads_per_spike
+    return m
+
+
+# ---------------------------------------------------------------------------
+# Batched plasticity (config 5)
+# ---------------------------------------------------------------------------
+def batched_stdp(num_pre: int = 10000, num_post: int = 10000, prob: float = 0.1, batch: int = 32,
+                 rate_hz: float = 25.0, seed: int = 55, dt: float = 1.0, world: int = 1):
+    """``num_pre`` Poisson inputs -> ``num_post`` LIF neurons through SPARSE fixed-probability
+    connectivity (drawn on the device) with pair-based additive STDP (tau+ = tau- = 20 ms,
+    A+ = 0.01, A- = 0.0105, weights clipped to [0, 1] nA, initial weights U[0, 0.5)); ``batch``
+    independent copies of the dynamic state per process, every copy with its own weights.  The custom
+    update group "gradient" sums the weights over the batch (and, in a data-parallel run of ``world``
+    processes, over the processes) and writes the mean back into every copy.  Every input fires at
+    ``rate_hz`` (the mean of the published U[0, 50) Hz: the Poisson model here has one rate per
+    population), drawn independently per batch entry.  Returns (model, synapse group)."""
+    m = GeNNModel("float", "batched_stdp")
+    m.dt = dt
+    m.seed = seed
+    m.batch_size = batch
+    src = m.add_neuron_population("input", num_pre, "Poisson", {"rate": rate_hz}, {"timeStepToSpike": 0.0})
+    lif = {"C": 1.0, "TauM": 20.0, "Vrest": -65.0, "Vreset": -70.0, "Vthresh": -55.0, "Ioffset": 0.0, "TauRefrac": 2.0}
+    trg = m.add_neuron_population("output", num_post, "LIF", lif, {"V": init_var("Uniform", {"min": -70.0, "max": -56.0}),
+                                                                   "RefracTime": 0.0})
+    sg = m.add_synapse_population("syn", "SPARSE", src, trg,
+                                  init_weight_update("STDP", {"tauPlus": 20.0, "tauMinus": 20.0, "Aplus": 0.01, "Aminus": 0.0105,
+                                                              "Wmin": 0.0, "Wmax": 1.0},
+                                                     {"g": init_var("Uniform", {"min": 0.0, "max": 0.5})}),
+                                  init_postsynaptic("ExpCurr", {"tau": 5.0}),
+                                  init_sparse_connectivity("FixedProbability", {"prob": prob}))
+    m.add_custom_update("mean_g", "gradient", "SUM", (sg, "g"), broadcast=True, scale=1.0 / (batch * world))
+    return m, sg

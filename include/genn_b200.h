@@ -98,7 +98,9 @@ typedef enum b200_var_init {
 
 /* initSparseConnectivitySnippet.h:170-486 */
 typedef enum b200_connect_init {
-    B200_CONNECT_FIXED_PROBABILITY = 0,                  /* params: prob */
+    B200_CONNECT_FIXED_PROBABILITY = 0,                  /* params: prob, 1 / log(1 - prob), sub-rows per row (0 or 1: one;
+                                                          * T > 1: targets cut into T ranges, range t drawn from stream
+                                                          * element pre * T + t: the reference's threads per spike) */
     B200_CONNECT_FIXED_PROBABILITY_NO_AUTAPSE = 1,
     B200_CONNECT_FIXED_NUMBER_TOTAL_WITH_REPLACEMENT = 2,/* row lengths supplied by the host */
     B200_CONNECT_FIXED_NUMBER_PRE_WITH_REPLACEMENT = 3,  /* params: num (in-degree) */
@@ -252,6 +254,10 @@ int  b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes
  * carries the step it expects, so no ordering between the stores (and no system-scope fence, 1.5 us
  * on this hardware) is needed. -------------------------------------------------------------------- */
 int  b200_exchange_alloc(b200_runner *r, size_t bytes, void **device_ptr);
+/* The arena is larger than the `bytes` asked for: behind them lie the queues through which the "deliver at
+ * emission" schedule sends near synapses between processes.  `bytes` returns the whole size, which a peer
+ * registered with b200_exchange_set_peer must provide as well. */
+int  b200_exchange_bytes(b200_runner *r, size_t *bytes);
 int  b200_exchange_get_handle(b200_runner *r, void *handle_64_bytes);
 int  b200_exchange_open_peer(b200_runner *r, uint32_t peer_rank, const void *handle_64_bytes);
 /* A peer whose arena is already addressable in THIS process (another runner of the same process, on this
@@ -306,15 +312,25 @@ int  b200_update_synapses(b200_runner *r);
 int  b200_update_neurons(b200_runner *r, uint64_t num_recording_timesteps);
 int  b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_timesteps);
 int  b200_custom_update(b200_runner *r, const char *name);
-/* The two halves of a custom update group for data-parallel runs (every process holds a share of the
- * batch): reduce this process's share into the targets, let the caller combine the targets of all
- * processes (an all-reduce over NCCL on the device arrays), then write the combined value back
- * into every batch copy.  The reference generates one NCCL reduction per such group
- * (backends/cuda/backend.cc, genNCCLReduction). */
+/* Data-parallel runs (every process holds a share of the batch; the reference: enableNCCLReductions,
+ * backendCUDAHIP.cc:805-824, with ncclGenerateUniqueID / ncclGetUniqueID / ncclInitCommunicator exported by the
+ * generated library, backends/cuda/backend.cc:219-226): one process obtains an id, the host application hands
+ * it to every process, each creates its communicator.  From then on b200_custom_update reduces this process's
+ * share, combines the reduced values of ALL updates of the group over the processes with one all-reduce per
+ * operation (sum, max) on a packed buffer, and writes the combined value back, everything on the runner's
+ * stream.  NCCL is loaded when first needed (the copy already in the process, else libnccl.so.2). */
+int  b200_nccl_unique_id(void *id_128_bytes);
+int  b200_nccl_init(b200_runner *r, const void *id_128_bytes, uint32_t rank, uint32_t world);
+/* The two halves on their own (reduce this process's share into the targets; write the targets back),
+ * for a host application that combines the targets itself. */
 int  b200_custom_update_reduce(b200_runner *r, const char *name);
 int  b200_custom_update_broadcast(b200_runner *r, const char *name);
 /* Same, bracketed by CUDA events recorded on the runner's stream; waits for completion. */
 int  b200_step_time_timed(b200_runner *r, uint64_t num_steps, uint64_t num_recording_timesteps, float *milliseconds);
+/* A CUDA event pair on the runner's stream around whatever the caller enqueues in between (steps, custom
+ * updates): begin waits for the stream and records, end records, waits and returns the elapsed time. */
+int  b200_timed_begin(b200_runner *r);
+int  b200_timed_end(b200_runner *r, float *milliseconds);
 /* Waits for the stream and reports failed device-side checks (out-of-range index, row overflow). */
 int  b200_synchronize(b200_runner *r);
 int  b200_get_timestep(b200_runner *r, uint64_t *timestep);
@@ -333,7 +349,10 @@ int  b200_get_counter(b200_runner *r, const char *name, uint64_t *value);
  * step later into the ring slot one nearer, same result, one grid barrier per step instead of two),
  * "lag_agreed" (sharded model: the caller has checked "lag_eligible" on EVERY process; without it a sharded
  * model keeps the two-barrier schedule), "rescan_delays" (delay arrays were changed by something other than
- * this library's push / init calls), "use_tiled" / "tiled_min_events" (target-tiled SPARSE delivery of steps
+ * this library's push / init calls), "use_near_queues" (default 1: a sharded model on the
+ * "deliver at emission" schedule sends near synapses between processes through per-CTA queues of self-validating
+ * words; 0: reduces them straight into the other process's rings and fences) / "near_queue_words" (capacity of
+ * one queue, 2 .. 2048; what does not fit goes the direct way), "use_tiled" / "tiled_min_events" (target-tiled SPARSE delivery of steps
  * with at least that many estimated events on the one-launch-per-kernel path),
  * "barrier_spin_limit" / "exchange_spin_limit" (polls) and "stream_wait_cycles" (SM cycles): how long a wait
  * inside a persistent kernel lasts before the launch gives up and b200_synchronize reports

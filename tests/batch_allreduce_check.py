@@ -25,6 +25,8 @@ def main():
     dist.init_process_group("nccl")
     model, sg = _model(v_seed=100 + rank)       # same network, another share of the batch
     model.add_custom_update("mean_g", "gradient", "SUM", (sg, "g"), broadcast=True, scale=1.0 / (BATCH * world))
+    # a second update of the same group with the other operation: both travel in the one packed buffer
+    model.add_custom_update("max_v", "gradient", "MAX", (model.neuron_populations["post"], "V"))
     model.build()
     model.load(device=local)
     rt = model._runtime
@@ -34,7 +36,12 @@ def main():
     gathered = [None] * world
     dist.all_gather_object(gathered, local_sum)
     want = sum(gathered) / (BATCH * world)
-    model.custom_update("gradient", all_reduce=True)
+    v_all = [None] * world
+    dist.all_gather_object(v_all, rt.array("post.V").max(axis=0))
+    rt.init_data_parallel()
+    model.custom_update("gradient")
+    model.custom_updates["max_v"].vars["reduction"].pull_from_device()
+    assert np.array_equal(model.custom_updates["max_v"].vars["reduction"].view, np.max(np.stack(v_all), axis=0))
     after = rt.array("syn.g")
     for b in range(BATCH):
         np.testing.assert_allclose(after[b], want, rtol=1e-5, atol=1e-6)

@@ -47,7 +47,7 @@ def main():
                 pops[p.name] = stats.rate_and_cv(sp[:, 0], sp[:, 1], p.n, steps * net.dt * 1e-3)
         finally:
             shutil.rmtree(work, ignore_errors=True)
-        doc = {"case": name, "steps": steps, "dt_ms": net.dt,
+        doc = {"case": name, "seed": int(model.seed), "steps": steps, "dt_ms": net.dt,
                "neurons": int(sum(p.n for p in net.pops)),
                "synapses": int(sum(int(s.row_length.sum()) for s in net.syns)),
                "produced_by": "GeNN 5.4.0 single_threaded_cpu backend (oracle/_ref/ref_driver), g++ -O3",

@@ -1,7 +1,11 @@
 """Child process of tests/test_multi_gpu.py: one rank of a model sharded by
 postsynaptic neuron over several GPUs.
 
-    python -m torch.distributed.run --nproc-per-node 2 tests/multigpu_check.py <case> [lag|emit|split|plain]
+    python -m torch.distributed.run --nproc-per-node 2 tests/multigpu_check.py <case> [lag|emit|emit-direct|emit-tiny|split|plain]
+
+("emit": near synapses between processes travel through the per-CTA queues; "emit-direct": they are reduced
+straight into the other process's rings; "emit-tiny": queues of one entry, so that both ways are taken in the
+same step.)
 
 Every rank builds the same network restricted to the synapses onto its slice,
 steps it with the persistent kernel (spike lists travel between the GPUs inside
@@ -27,6 +31,8 @@ def main():
 
     name = sys.argv[1] if len(sys.argv) > 1 else "potjans_mini"
     schedule = sys.argv[2] if len(sys.argv) > 2 else "lag"
+    variant = schedule
+    schedule = schedule.split("-")[0]
     lag = schedule == "lag"
     kw = dict(min_delay=0.1, extra_delay_slots=1) if name == "potjans_mini_d1" else {}
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
@@ -42,6 +48,8 @@ def main():
     rt.set_option("use_lag", 1 if lag else 0)
     rt.set_option("use_split", 0 if schedule == "plain" else 1)
     rt.set_option("use_emit", 1 if schedule == "emit" else 0)
+    rt.set_option("use_near_queues", 0 if variant == "emit-direct" else 1)
+    rt.set_option("near_queue_words", 2 if variant == "emit-tiny" else 2048)
     want_schedule = (0 if schedule == "plain" else 2 if (lag and name == "potjans_mini_d1")
                      else 1 if schedule == "split" else 3)
     assert rt.schedule == want_schedule, f"rank {rank}: schedule {rt.schedule}, expected {want_schedule}"
@@ -71,6 +79,8 @@ def main():
     rt2.set_option("use_lag", 1 if lag else 0)
     rt2.set_option("use_split", 0 if schedule == "plain" else 1)
     rt2.set_option("use_emit", 1 if schedule == "emit" else 0)
+    rt2.set_option("use_near_queues", 0 if variant == "emit-direct" else 1)
+    rt2.set_option("near_queue_words", 2 if variant == "emit-tiny" else 2048)
     dist.barrier()
     rt2.step_time(steps)
     rt2.synchronize()
@@ -86,7 +96,7 @@ def main():
     rt.close()
     rt2.close()
     if rank == 0:
-        print(f"multigpu_check ok: {world} ranks, schedule {want_schedule}, "
+        print(f"multigpu_check ok: {name} {variant}, {world} ranks, schedule {want_schedule}, "
               f"{sum(len(v) for v in spikes.values())} spikes")
     dist.destroy_process_group()
 

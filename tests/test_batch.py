@@ -1,7 +1,7 @@
 """Batched simulation (batch size > 1: every kernel's batch dimension) and the
 batch-reduce custom update (backendSIMT.cc:888-927, 1109-1147), against the CPU
-checker; the cross-process half of a data-parallel reduction on CPU (gloo) and,
-with two GPUs, over NCCL."""
+checker; the host side of a data-parallel reduction on CPU (gloo) and, with two
+GPUs, the reduction itself (one packed NCCL all-reduce inside b200_custom_update)."""
 import os
 import subprocess
 import sys
@@ -135,19 +135,18 @@ def test_every_batch_element_matches_the_cpu_checker_and_the_weights_reduce():
 
 
 def _gloo_worker(rank, world, port, out):
-    import torch
+    """The host side of init_data_parallel: rank 0's 128-byte id reaches every rank."""
     import torch.distributed as dist
-    from genn_b200.collectives import all_reduce_targets
+    from genn_b200.runtime import all_gather_bytes
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
-    a = torch.arange(6, dtype=torch.float32) * (rank + 1)
-    b = torch.tensor([1.0, -2.0, 3.0]) * (1 if rank == 0 else -1)
-    all_reduce_targets([a, b], ["SUM", "MAX"])
-    out.put((rank, a.tolist(), b.tolist()))
+    ident = (bytes(range(128)) if rank == 0 else bytes(128))
+    everyone = all_gather_bytes(ident)
+    out.put((rank, len(everyone), everyone[0]))
     dist.destroy_process_group()
 
 
-def test_targets_of_two_processes_combine_over_gloo():
+def test_communicator_id_reaches_both_processes_over_gloo():
     import torch.multiprocessing as mp
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
@@ -158,9 +157,8 @@ def test_targets_of_two_processes_combine_over_gloo():
     results = [q.get(timeout=120) for _ in range(2)]
     for p in procs:
         p.join(timeout=60)
-    for _, a, b in results:
-        assert a == [0.0, 3.0, 6.0, 9.0, 12.0, 15.0]
-        assert b == [1.0, 2.0, 3.0]
+    for _, n, first in results:
+        assert n == 2 and first == bytes(range(128))
 
 
 @pytest.mark.gpu

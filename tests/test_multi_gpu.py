@@ -97,7 +97,8 @@ def test_handle_exchange_over_gloo_two_processes():
 @pytest.mark.gpu
 @pytest.mark.parametrize("world", [2, 4, 8])
 @pytest.mark.parametrize("name,schedule", [("potjans_mini_d1", "lag"), ("potjans_mini_d1", "split"),
-                                           ("potjans_mini", "emit"), ("potjans_mini", "split"),
+                                           ("potjans_mini", "emit"), ("potjans_mini", "emit-direct"),
+                                           ("potjans_mini", "emit-tiny"), ("potjans_mini", "split"),
                                            ("potjans_mini", "plain")])
 def test_sharded_over_gpus_matches_the_unsharded_reference(name, schedule, world):
     """`world` processes, one GPU each: every rank must see exactly the reference's spikes of the

@@ -777,6 +777,9 @@ def main():
         phase_cycles["header_max"] = float(head.max())
         phase_cycles["cta_presynaptic_min_median_max"] = [float(cta[:, 0].min()), float(np.median(cta[:, 0])),
                                                           float(cta[:, 0].max())]
+        phase_cycles["cta_neuron_min_median_max"] = [float(cta[:, 2].min()), float(np.median(cta[:, 2])), float(cta[:, 2].max())]
+        phase_cycles["cta_header_or_arrival_min_median_max"] = [float(head.min()), float(np.median(head)), float(head.max())]
+        phase_cycles["cta_latest"] = int(np.argmax(head))
     rt.set_option("fused_profile", 0)
     sm_hz = (clocks.get("sm_mhz") or 1965.0) * 1e6
 

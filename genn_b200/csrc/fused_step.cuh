@@ -143,6 +143,7 @@ struct FusedLaunch
     const struct NearRing *near_rings;   // [world][num_rings]: the rings of every process, as mapped here
     const struct NearSpace *near_spaces; // [neuron groups]
     // queues for near synapses onto other processes' neurons (near.cuh); queue_words == 0: reduce directly
+    unsigned int publisher;              // 1: the block's last warp publishes the spike counts (sharded models)
     unsigned int queue_words;            // 64-bit words per queue, header included
     unsigned int queue_count;            // queues per (step parity, sending process)
     unsigned long long queue_offset;     // where the queues start in every process's arena

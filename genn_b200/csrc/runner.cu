@@ -401,8 +401,10 @@ int buildFusedTables(b200_runner *r)
             const unsigned int perCta = ((slotStart.back() + sms - 1) / sms + 31u) & ~31u;
             const unsigned int warps = FUSED_BLOCK / 32;
             const unsigned int chainMin = std::max(8u, perCta / 32u);
-            if(chainMin + 4u <= warps) {
-                unsigned int stream = warps - chainMin;
+            // (a sharded model keeps the block's last warp for publishing its spike counts)
+            const unsigned int publisher = r->sharded() ? 1u : 0u;
+            if(chainMin + 4u + publisher <= warps) {
+                unsigned int stream = warps - chainMin - publisher;
                 if(r->streamWarpsWanted > 0) stream = std::min(stream, (unsigned int)r->streamWarpsWanted);
                 r->streamWarps = stream;
                 r->slotsPerCta = perCta;
@@ -856,6 +858,7 @@ int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long 
     L.near_spaces = r->nearSpaces;
     L.queue_words = (r->sharded() && L.emit && r->useNearQueues && r->queuesAgreed) ? r->queueWords : 0u;
     L.queue_count = NEAR_QUEUE_COUNT;
+    L.publisher = (r->sharded() && r->streamWarps) ? 1u : 0u;
     L.queue_offset = r->queueOffset;
     L.neuron.groups = r->neuronTable.d;
     L.neuron.block_start = r->neuronTable.blockStart;

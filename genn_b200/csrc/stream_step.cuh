@@ -407,13 +407,50 @@ streamStepKernel(FusedLaunch L)
     const unsigned int warp = threadIdx.x >> 5;
     const unsigned int warpsPerBlock = blockDim.x >> 5;
     const unsigned int streamWarps = L.stream_warps;
-    const unsigned int chainWarps = warpsPerBlock - streamWarps;
+    // (sharded model: the last warp of the block is neither: in CTA 0 it tells the other processes the spike
+    // counts of every step the moment the step's barrier completes, off every other warp's path)
+    const unsigned int publisherWarps = (SHARDED && L.world > 1 && L.publisher) ? 1u : 0u;
+    const unsigned int chainWarps = warpsPerBlock - streamWarps - publisherWarps;
     const unsigned int chainThreads = chainWarps * 32u;
     StepState *state = L.neuron.state;
     const unsigned int period = state->ring_period;
     unsigned int k = state->phase;
     const unsigned long long t0 = state->timestep;
     const unsigned long long done0 = state->steps_done;
+
+    // =========================== publisher warp ================================================
+    if(publisherWarps && warp == warpsPerBlock - 1u) {
+        if(blockIdx.x != 0) return;
+        // "step s: n spikes", one 64-bit store per process and population, once the barrier behind the
+        // neuron update of that step has completed (emit schedule: barrier number step + 2 of the launch,
+        // the first one ends the prologue; otherwise two barriers per step); the ids already sit in every arena
+        const unsigned int numGroups = L.neuron.num_groups;
+        for(unsigned long long step = 0; step < L.num_steps; step++) {
+            const unsigned long long target = (unsigned long long)gridDim.x * (L.emit ? step + 2ull : 2ull * step + 2ull);
+            bool good = true;
+            if(lane == 0) {
+                unsigned long long polls = 0;
+                while(loadAcquire(L.barrier) < target) {
+                    if(sh.stop || ++polls > state->barrier_spin_limit) { good = false; break; }
+                    __nanosleep(64);
+                }
+            }
+            if(!__shfl_sync(0xFFFFFFFFu, good ? 1u : 0u, 0)) return;
+            for(unsigned int idx = lane; idx < L.world * numGroups; idx += 32u) {
+                const unsigned int peer = idx / numGroups, gi = idx - peer * numGroups;
+                const b200_neuron_group &g = L.neuron.groups[gi];
+                const unsigned int wslot = ringSlot(k + 1u, g.num_delay_slots);
+                const unsigned long long tag = ((done0 + step + 1) << 32) | (unsigned long long)__ldcg(&g.spk_cnt[wslot]);
+                unsigned long long *cell = reinterpret_cast<unsigned long long*>(&g.spk_tag[wslot]);
+                if(peer != L.rank) {
+                    cell = reinterpret_cast<unsigned long long*>(peerArena[peer] + (reinterpret_cast<unsigned char*>(cell) - L.arena));
+                }
+                storeRelaxedSys(cell, tag);
+            }
+            k = (k + 1 == period) ? 0u : k + 1;
+        }
+        return;
+    }
 
     // =========================== stream warps ==================================================
     if(warp >= chainWarps && L.emit) {
@@ -550,7 +587,11 @@ streamStepKernel(FusedLaunch L)
         if(warp == 0) {
             bool good = true;
             const long long w0 = prof ? clock64() : 0;
+            // the error word travels while the barrier is being polled (sticky bits: a flag raised after this
+            // load is seen one step later)
+            unsigned int seen = 0;
             if(lane == 0) {
+                seen = __ldcg(&state->error);
                 unsigned long long polls = 0;
                 while(loadAcquire(L.barrier) < epoch) {
                     if(++polls > state->barrier_spin_limit) {
@@ -583,7 +624,7 @@ streamStepKernel(FusedLaunch L)
             }
             // one thread decides for all: a CTA whose chain threads disagreed would hang on its barrier
             if(lane == 0) {
-                if(__ldcg(&state->error) & (ERR_BARRIER_TIMEOUT | ERR_EXCHANGE_TIMEOUT)) good = false;
+                if(seen & (ERR_BARRIER_TIMEOUT | ERR_EXCHANGE_TIMEOUT)) good = false;
                 sh.barrierOk = good;
             }
         }
@@ -730,23 +771,6 @@ streamStepKernel(FusedLaunch L)
             o.spk_cnt[ringSlot(k + 2, o.num_delay_slots)] = 0;
         }
         if(prof) c3 = clock64();
-        if(emit && threadIdx.x == 0 && step >= 2) {
-            // the stream warps that took pass step-1 (the spikes of the step before last; this CTA's
-            // if the parities match) must be through it: the barrier below is the last one ahead of
-            // the first neuron update that may read what they delivered
-            const long long since = clock64();
-            for(unsigned int w = 0; w < streamWarps && (gridDim.x < 2u || ((step - 1) & 1u) == (blockIdx.x & 1u)); w++) {
-                while(sh.streamDone[w] < (unsigned int)(step - 1)) {
-                    if(clock64() - since > state->stream_wait_cycles) {
-                        atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
-                        break;
-                    }
-                }
-            }
-            // (no fence of its own: the release at the barrier below follows in program order and is
-            // cumulative over what this thread has just observed)
-            if(prof) cyc[5] += (unsigned long long)(clock64() - since);
-        }
         const bool queued = SHARDED && emit && L.world > 1 && outbox.words != 0u;
         if(queued && step + 1 < L.num_steps) {
             // Near synapses between processes.  Out: the header of this CTA's queue in every other process's
@@ -803,17 +827,39 @@ streamStepKernel(FusedLaunch L)
             }
             if(prof) sh.waited[1] += (unsigned long long)(clock64() - x0);
         }
+        if(emit && threadIdx.x == 0 && step >= 2) {
+            // the stream warps that took pass step-1 (the spikes of the step before last; this CTA's
+            // if the parities match) must be through it: the barrier below is the last one ahead of
+            // the first neuron update that may read what they delivered
+            const long long since = clock64();
+            for(unsigned int w = 0; w < streamWarps && (gridDim.x < 2u || ((step - 1) & 1u) == (blockIdx.x & 1u)); w++) {
+                while(sh.streamDone[w] < (unsigned int)(step - 1)) {
+                    if(clock64() - since > state->stream_wait_cycles) {
+                        atomicOr(&state->error, ERR_BARRIER_TIMEOUT);
+                        break;
+                    }
+                }
+            }
+            // (no fence of its own: the release at the barrier below follows in program order and is
+            // cumulative over what this thread has just observed)
+            if(prof) cyc[5] += (unsigned long long)(clock64() - since);
+        }
+        const long long a0 = prof ? clock64() : 0;
         arrive();
+        // probe 11: CTA 0's arrival (its warps' waits for the other processes' queues end here)
+        if(prof && blockIdx.x == 0) atomicAdd(&state->probe[11], (unsigned long long)(clock64() - a0));
+        // (emit schedule, per CTA, in the slot the other schedules use for the header wait: from the start of the
+        // step to this CTA's arrival)
+        if(prof && emit) cyc[4] += (unsigned long long)(clock64() - c0);
         if(queued && threadIdx.x == 0) outbox.fenced = 0u;
         // every chain thread is past its neuron update: the tag of the NEXT step's spike words may change
         if(SHARDED && emit && L.world > 1 && threadIdx.x == 0) exchange.tag = done0 + step + 2;
         if(emit && mine && myActive && step + 1 < L.num_steps) {
             drawCurrentSources<NCS>(L.neuron, L.neuron.groups[myGroup], 0u, (unsigned int)myIndex, t0 + step + 1, csCount);
         }
-        // sharded model: one warp waits for the last CTA and tells every process how many spikes
-        // each population emitted ("step s: n spikes", one 64-bit store per process and population);
-        // the ids already sit in every arena
-        if(SHARDED && L.world > 1 && blockIdx.x == 0 && warp == chainWarps - 1u) {
+        // (sharded model without a publisher warp: the chain's last warp of CTA 0 tells every process how many
+        // spikes each population emitted)
+        if(SHARDED && L.world > 1 && !publisherWarps && blockIdx.x == 0 && warp == chainWarps - 1u) {
             if(lane == 0) {
                 unsigned long long polls = 0;
                 while(loadAcquire(L.barrier) < epoch) {

@@ -356,7 +356,7 @@ def procedural_stress(num_neurons: int = 1_000_000, prob: float = 0.001, driven_
 def batched_stdp(num_pre: int = 10000, num_post: int = 10000, prob: float = 0.1, batch: int = 32,
                  rate_hz: float = 25.0, seed: int = 55, dt: float = 1.0, world: int = 1):
     """``num_pre`` Poisson inputs -> ``num_post`` LIF neurons through SPARSE fixed-probability
-    connectivity (drawn on the device) with pair-based additive STDP (tau+ = tau- = 20 ms,
+    connectivity with pair-based additive STDP (tau+ = tau- = 20 ms,
     A+ = 0.01, A- = 0.0105, weights clipped to [0, 1] nA, initial weights U[0, 0.5)); ``batch``
     independent copies of the dynamic state per process, every copy with its own weights.  The custom
     update group "gradient" sums the weights over the batch (and, in a data-parallel run of ``world``
@@ -371,11 +371,15 @@ def batched_stdp(num_pre: int = 10000, num_post: int = 10000, prob: float = 0.1,
     lif = {"C": 1.0, "TauM": 20.0, "Vrest": -65.0, "Vreset": -70.0, "Vthresh": -55.0, "Ioffset": 0.0, "TauRefrac": 2.0}
     trg = m.add_neuron_population("output", num_post, "LIF", lif, {"V": init_var("Uniform", {"min": -70.0, "max": -56.0}),
                                                                    "RefracTime": 0.0})
+    # (connectivity and initial weights drawn on the host: the column-major view that the postsynaptic half of
+    # STDP walks is built from host-supplied rows)
+    rng = np.random.default_rng(seed)
+    pre, post = np.nonzero(rng.random((num_pre, num_post), dtype=np.float32) < prob)
+    g = rng.uniform(0.0, 0.5, size=len(pre)).astype(np.float32)
     sg = m.add_synapse_population("syn", "SPARSE", src, trg,
                                   init_weight_update("STDP", {"tauPlus": 20.0, "tauMinus": 20.0, "Aplus": 0.01, "Aminus": 0.0105,
-                                                              "Wmin": 0.0, "Wmax": 1.0},
-                                                     {"g": init_var("Uniform", {"min": 0.0, "max": 0.5})}),
-                                  init_postsynaptic("ExpCurr", {"tau": 5.0}),
-                                  init_sparse_connectivity("FixedProbability", {"prob": prob}))
+                                                              "Wmin": 0.0, "Wmax": 1.0}, {"g": g}),
+                                  init_postsynaptic("ExpCurr", {"tau": 5.0}))
+    sg.set_sparse_connections(pre.astype(np.uint32), post.astype(np.uint32), presorted=True)
     m.add_custom_update("mean_g", "gradient", "SUM", (sg, "g"), broadcast=True, scale=1.0 / (batch * world))
     return m, sg

@@ -476,9 +476,18 @@ def run_c5(args):
         rt.custom_update("gradient")
     rt.synchronize()
     cu_s = allreduce(rt.timer("custom_update_gradient") / reps, dist.ReduceOp.MAX if world > 1 else None)
+    # ... and the kernels of a time step (a CUDA event pair around every launch)
+    rt.reset_timers()
+    sp0, pe0 = rt.counter("spikes"), rt.counter("synaptic_events")
+    rt.step_time(block)
+    rt.synchronize()
+    kernel_us = {n: rt.timer(n) / block * 1e6 for n in ("neuron_update", "presynaptic_update", "postsynaptic_update")}
+    spikes_per_step = (rt.counter("spikes") - sp0) / block
+    pre_events_per_step = (rt.counter("synaptic_events") - pe0) / block
     rt.enable_timing(False)
     slots = int(np.prod(rt.plan.arrays["syn.g"].shape[1:], dtype=np.int64))
-    cu_bytes = slots * (4.0 * args.c5_batch + 4.0 + 4.0 * args.c5_batch + 8.0)     # read batch, write target, write back, staged r/w
+    # read the batch, write the target, write the batch back (+ the packed buffer written and read when ranks combine)
+    cu_bytes = slots * (4.0 * args.c5_batch + 4.0 + 4.0 * args.c5_batch + (8.0 if world > 1 else 0.0))
     # end to end: the same steps plus the reduced weights pulled to the host after every update
     red = model.custom_updates["mean_g"].vars["reduction"]
     bench_step()
@@ -502,6 +511,8 @@ def run_c5(args):
                                        f"slots), additive STDP, {args.c5_batch} batch entries per GPU x {world} GPU(s); one bench step = "
                                        f"{block} time steps of 1 ms + batch-reduce custom update with one packed NCCL all-reduce",
                            "parallelism": f"data-parallel over {world} GPU(s), connectivity replicated",
+                           "kernel_us_per_time_step": kernel_us, "spikes_per_time_step": spikes_per_step,
+                           "presynaptic_events_per_time_step": pre_events_per_step,
                            "l2": f"weights: {slots * 4 * args.c5_batch / 1e9:.2f} GB per GPU, larger than L2"},
                 "clocks": clocks,
                 "e2e": {"value": e2e_ev / e2e_s, "unit": "synaptic events/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": slots * 4},

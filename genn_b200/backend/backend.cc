@@ -2290,15 +2290,18 @@ void Backend::genCustomUpdate(CodeStream &os, FileStreamCreator, ModelSpecMerged
         {
             std::ostringstream hostStream;
             CodeStream host(hostStream);
-            EnvironmentExternal hostEnv(host);
-            hostEnv.add(model.getTimePrecision().addConst(), "t", "t");
-            hostEnv.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
-            modelMerged.genMergedCustomConnectivityHostUpdateGroups(
-                *this, memorySpaces, g,
-                [&](auto &c)
-                {
-                    c.generateUpdate(*this, hostEnv);
-                });
+            {
+                // (an environment writes what it has gathered when it goes out of scope)
+                EnvironmentExternal hostEnv(host);
+                hostEnv.add(model.getTimePrecision().addConst(), "t", "t");
+                hostEnv.add(model.getTimePrecision().addConst(), "dt", dtLiteral);
+                modelMerged.genMergedCustomConnectivityHostUpdateGroups(
+                    *this, memorySpaces, g,
+                    [&](auto &c)
+                    {
+                        c.generateUpdate(*this, hostEnv);
+                    });
+            }
             hostUpdates[g] = hostStream.str();
         }
     }

@@ -368,7 +368,9 @@ def batched_stdp(num_pre: int = 10000, num_post: int = 10000, prob: float = 0.1,
     m.seed = seed
     m.batch_size = batch
     src = m.add_neuron_population("input", num_pre, "Poisson", {"rate": rate_hz}, {"timeStepToSpike": 0.0})
-    lif = {"C": 1.0, "TauM": 20.0, "Vrest": -65.0, "Vreset": -70.0, "Vthresh": -55.0, "Ioffset": 0.0, "TauRefrac": 2.0}
+    # (the published description gives no neuron constants; with 1 000 inputs of up to 1 nA each a membrane
+    # capacitance of 40 nF keeps the outputs at tens of Hz instead of at the limit their refractory period sets)
+    lif = {"C": 40.0, "TauM": 20.0, "Vrest": -65.0, "Vreset": -70.0, "Vthresh": -55.0, "Ioffset": 0.0, "TauRefrac": 2.0}
     trg = m.add_neuron_population("output", num_post, "LIF", lif, {"V": init_var("Uniform", {"min": -70.0, "max": -56.0}),
                                                                    "RefracTime": 0.0})
     # (connectivity and initial weights drawn on the host: the column-major view that the postsynaptic half of

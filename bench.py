@@ -574,6 +574,62 @@ def run_probe(args):
                           "events_per_s": events / sec, "bytes_per_event": bpe,
                           "GBps": (events * bpe + spikes * ALGO_BYTES_PER_SPIKE) / sec / 1e9}))
         rt.close()
+    elif args.probe == "dense":
+        # Batched DENSE presynaptic update: this library's row gather (4 x numPost bytes per spike and batch
+        # entry) beside the same update written as a contraction, spikes[B x numPre] (0/1) @ W[numPre x numPost],
+        # on the tensor cores through the vendor GEMM (comparison only: it reads all of W whatever the activity)
+        import torch
+        from genn_b200 import GeNNModel, init_postsynaptic, init_var, init_weight_update
+        n, rows = args.probe_dense_size, []
+        for batch in (1, 32, 256):
+            m = GeNNModel("float", "dense_probe")
+            m.dt = 1.0
+            m.batch_size = batch
+            src = m.add_neuron_population("pre", n, "Poisson", {"rate": 25.0}, {"timeStepToSpike": 0.0})
+            lif = {"C": 40.0, "TauM": 20.0, "Vrest": -65.0, "Vreset": -70.0, "Vthresh": -55.0, "Ioffset": 0.0, "TauRefrac": 2.0}
+            trg = m.add_neuron_population("post", n, "LIF", lif, {"V": -65.0, "RefracTime": 0.0})
+            m.add_synapse_population("syn", "DENSE", src, trg,
+                                     init_weight_update("StaticPulse", {}, {"g": init_var("Uniform", {"min": 0.0, "max": 0.01})}),
+                                     init_postsynaptic("ExpCurr", {"tau": 5.0}))
+            m.build()
+            rt = Runtime(m, None)
+            rng = np.random.default_rng(5)
+            active = max(1, int(n * args.probe_fraction))
+            spikes = torch.zeros((batch, n), dtype=torch.bfloat16, device="cuda")
+            for b in range(batch):
+                ids = np.sort(rng.choice(n, size=active, replace=False)).astype(np.uint32)
+                rt.set_spike_list("pre", ids, batch=b)
+                spikes[b, torch.from_numpy(ids.astype(np.int64)).cuda()] = 1
+            for _ in range(2):
+                rt.update_synapses()
+            rt.enable_timing(True)
+            rt.reset_timers()
+            for _ in range(args.probe_reps):
+                rt.update_synapses()
+            rt.synchronize()
+            gather_s = rt.timer("presynaptic_update") / args.probe_reps
+            rt.close()
+            w16 = torch.rand((n, n), device="cuda").to(torch.bfloat16)
+            w32 = torch.rand((n, n), device="cuda")
+            s32 = spikes.float()
+            out = {}
+            for name, a, w in (("bf16", spikes, w16), ("tf32", s32, w32)):
+                torch.backends.cuda.matmul.allow_tf32 = True
+                for _ in range(3):
+                    torch.matmul(a, w)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.probe_reps):
+                    torch.matmul(a, w)
+                e1.record()
+                torch.cuda.synchronize()
+                out[name] = e0.elapsed_time(e1) / args.probe_reps * 1e-3
+            rows.append({"batch": batch, "active_rows_per_batch_entry": active,
+                         "gather_us": gather_s * 1e6, "gather_GBps": batch * active * 4.0 * n / gather_s / 1e9,
+                         "gemm_bf16_us": out["bf16"] * 1e6, "gemm_tf32_us": out["tf32"] * 1e6,
+                         "gemm_bf16_TFLOPs": 2.0 * batch * n * n / out["bf16"] / 1e12})
+            del w16, w32, spikes, s32
+        print(json.dumps({"probe": "dense", "num_pre": n, "num_post": n, "fraction": args.probe_fraction, "rows": rows}))
     elif args.probe == "phases":
         scale = args.probe_scale if args.probe_scale is not None else 1.0
         model = workloads.potjans(neuron_scale=scale, seed=1234, min_delay=args.min_delay,
@@ -637,7 +693,8 @@ def main():
                     help="neuron scale of the bounded cpu_baseline sample inside the GPU arm's run")
     ap.add_argument("--parity-seconds", type=float, default=10.0,
                     help="simulated seconds of the rate / CV-ISI comparison with the reference's statistics (0: skip)")
-    ap.add_argument("--probe", choices=["presyn", "phases", "e2e"], default=None,
+    ap.add_argument("--probe-dense-size", type=int, default=8192)
+    ap.add_argument("--probe", choices=["presyn", "phases", "e2e", "dense"], default=None,
                     help="run a bounded single-kernel workload (for profiling) instead of the benchmark")
     ap.add_argument("--workload", choices=["potjans", "c4", "c5"], default="potjans",
                     help="potjans: the headline workload; c4: the PROCEDURAL connectivity stress test (1 M LIF neurons, "

@@ -98,6 +98,17 @@ struct Timer
 };
 }   // anonymous namespace
 
+// Device buffer that is freed on every early return of a build function unless it was handed over.
+struct ScopedDevice
+{
+    void *p = nullptr;
+    ~ScopedDevice() { if(p) cudaFree(p); }
+    template<typename T> T *as() const { return static_cast<T*>(p); }
+    void *release() { void *q = p; p = nullptr; return q; }
+};
+
+constexpr unsigned int PROFILE_MAX_CTAS = 1024;     // per-CTA cycle counters of option "fused_profile"
+
 struct b200_runner
 {
     int device = 0;
@@ -601,8 +612,11 @@ int buildNearTables(b200_runner *r, bool forExport = false)
     for(size_t ni = 0; ni < numNeuronGroups; ni++) rowBase[ni + 1] = rowBase[ni] + r->neuronGroups[ni].num_neurons;
     const unsigned long long totalRows = rowBase[numNeuronGroups];
     if(totalRows == 0 || totalRows >= (1ull << 31)) return B200_OK;
-    unsigned int *cursor = nullptr, *bad = nullptr;
-    CUDA_TRY(cudaMalloc(&cursor, sizeof(unsigned int) * totalRows));
+    // (both freed on every way out of this function; a table left behind by a failed build is dropped with the
+    // runner's other near tables)
+    ScopedDevice cursorHold, badHold;
+    CUDA_TRY(cudaMalloc(&cursorHold.p, sizeof(unsigned int) * totalRows));
+    unsigned int *const cursor = cursorHold.as<unsigned int>();
     CUDA_TRY(cudaMemsetAsync(cursor, 0, sizeof(unsigned int) * totalRows, r->stream));
     for(size_t gi = 0; gi < n; gi++) {
         const auto &g = groups[gi];
@@ -626,20 +640,15 @@ int buildNearTables(b200_runner *r, bool forExport = false)
         unsigned int shift = 5;
         while((1u << shift) < longest) shift++;
         // a population most of whose synapses are near gains nothing from this schedule
-        if(shift > 10) {
-            cudaFree(cursor);
-            return B200_OK;
-        }
+        if(shift > 10) return B200_OK;
         firstCell[ni] = cells;
         shifts[ni] = shift;
         cells += (unsigned long long)r->neuronGroups[ni].num_neurons << shift;
     }
-    if(cells >= (1ull << 33)) {      // 64 GB of table: not worth it
-        cudaFree(cursor);
-        return B200_OK;
-    }
+    if(cells >= (1ull << 33)) return B200_OK;      // 64 GB of table: not worth it
     CUDA_TRY(cudaMemsetAsync(cursor, 0, sizeof(unsigned int) * totalRows, r->stream));
-    CUDA_TRY(cudaMalloc(&bad, sizeof(unsigned int)));
+    CUDA_TRY(cudaMalloc(&badHold.p, sizeof(unsigned int)));
+    unsigned int *const bad = badHold.as<unsigned int>();
     CUDA_TRY(cudaMemsetAsync(bad, 0, sizeof(unsigned int), r->stream));
     CUDA_TRY(cudaMalloc(&r->nearTable, sizeof(uint2) * (cells + 1)));
     CUDA_TRY(cudaMemsetAsync(r->nearTable, 0, sizeof(uint2) * (cells + 1), r->stream));
@@ -661,8 +670,6 @@ int buildNearTables(b200_runner *r, bool forExport = false)
     unsigned int isBad = 0;
     CUDA_TRY(cudaMemcpyAsync(&isBad, bad, sizeof(unsigned int), cudaMemcpyDeviceToHost, r->stream));
     CUDA_TRY(cudaStreamSynchronize(r->stream));
-    cudaFree(cursor);
-    cudaFree(bad);
     if(isBad) {
         cudaFree(r->nearTable);
         r->nearTable = nullptr;
@@ -879,11 +886,7 @@ int launchFused(b200_runner *r, unsigned long long numSteps, unsigned long long 
     L.stage_in_smem = r->fusedStage ? 1u : 0u;
     L.count_events = r->countEvents ? 1u : 0u;
     L.profile = r->fusedProfile ? 1u : 0u;
-    if(r->fusedProfile && !r->fusedCtaCycles) {
-        CUDA_TRY(cudaMalloc(&r->fusedCtaCycles, sizeof(unsigned long long) * 5 * r->fusedGrid));
-        CUDA_TRY(cudaMemsetAsync(r->fusedCtaCycles, 0, sizeof(unsigned long long) * 5 * r->fusedGrid, r->stream));
-    }
-    L.cta_cycles = r->fusedProfile ? r->fusedCtaCycles : nullptr;
+    L.cta_cycles = (r->fusedProfile && r->fusedGrid <= PROFILE_MAX_CTAS) ? r->fusedCtaCycles : nullptr;
     L.num_steps = numSteps;
     L.barrier = r->fusedBarrier;
     L.rank = r->rank;
@@ -947,15 +950,6 @@ struct ScopedTimer
             r->timers[name].seconds += ms * 1e-3;
         }
     }
-};
-
-// Device buffer that is freed on every early return of a build function unless it was handed over.
-struct ScopedDevice
-{
-    void *p = nullptr;
-    ~ScopedDevice() { if(p) cudaFree(p); }
-    template<typename T> T *as() const { return static_cast<T*>(p); }
-    void *release() { void *q = p; p = nullptr; return q; }
 };
 
 // (Re)build the private tile-major copy of the non-learning SPARSE groups (tiled.cuh).  Not on the
@@ -1767,7 +1761,15 @@ int b200_set_option(b200_runner *r, const char *name, double value)
     else if(n == "stream_warps") { r->streamWarpsWanted = (int)value; r->lagStale = true; }
     else if(n == "lag_agreed") { r->lagAgreed = (value != 0.0); r->lagStale = true; }
     else if(n == "rescan_delays") r->lagStale = true;
-    else if(n == "fused_profile") r->fusedProfile = (value != 0.0);
+    else if(n == "fused_profile") {
+        // (the per-CTA cycle counters are allocated here, not on the time-step path)
+        r->fusedProfile = (value != 0.0);
+        if(r->fusedProfile && !r->fusedCtaCycles) {
+            CUDA_TRY(cudaSetDevice(r->device));
+            CUDA_TRY(cudaMalloc(&r->fusedCtaCycles, sizeof(unsigned long long) * 5 * PROFILE_MAX_CTAS));
+            CUDA_TRY(cudaMemset(r->fusedCtaCycles, 0, sizeof(unsigned long long) * 5 * PROFILE_MAX_CTAS));
+        }
+    }
     else if(n == "fused_blocks_per_sm") { r->fusedBlocksPerSM = (unsigned int)value; r->dirty = true; }
     else if(n == "graph_steps") r->graphSteps = std::max(1u, (unsigned int)value);
     else if(n == "barrier_spin_limit" || n == "exchange_spin_limit" || n == "stream_wait_cycles") {

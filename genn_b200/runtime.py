@@ -130,11 +130,13 @@ class Runtime:
             mine = bytes([1 if self.counter("lag_eligible") else 0])
             everyone = (exchange or all_gather_bytes)(mine)
             self.set_option("lag_agreed", 1.0 if all(b[0] for b in everyone) else 0.0)
-            # "deliver at emission" across processes is opt-in (sharded_emit=True or
-            # GENN_B200_SHARDED_EMIT=1, the same on every process): measured slower than the split
-            # schedule on 2 and 8 GPUs, because the pushed additions need a system-wide fence
+            # "deliver at emission" across processes (near synapses travel through per-CTA queues) is the default
+            # from 8 processes on, where it measured faster than the split schedule (13.1 against 14.4 us per
+            # step of the Potjans x8 network); on 2 and 4 GPUs the split schedule is ahead (11.1 / 11.4 against
+            # 12.2 / 11.9 us).  sharded_emit or GENN_B200_SHARDED_EMIT=0/1 (the same on every process) overrides.
             if sharded_emit is None:
-                sharded_emit = os.environ.get("GENN_B200_SHARDED_EMIT", "0") == "1"
+                env = os.environ.get("GENN_B200_SHARDED_EMIT")
+                sharded_emit = (env == "1") if env is not None else (shard[1] >= 8)
             if sharded_emit:
                 self._exchange_near_tables(exchange or all_gather_bytes)
         self._cu_targets = {}

@@ -34,7 +34,9 @@ struct StepState
     // verdict of tiledDecideKernel for the step being delivered: 1 = enough events for the
     // target-tiled kernel, 0 = the one-reduction-per-event kernel delivers
     unsigned int heavy;
-    unsigned int reserved;
+    // most spikes (all populations and batch entries together) any step has emitted since the host last
+    // read and cleared this word: tells the host whether launching the tiled kernels is worth it at all
+    unsigned int peak_spikes;
     // limits of every wait inside the persistent kernels (set by the host; a wait that runs out sets an
     // error bit, all CTAs leave the kernel and the host reports it): polls of the grid barrier, polls for
     // a word another process writes, SM cycles a warp waits for work from another warp of its CTA

@@ -388,12 +388,18 @@ neuronUpdateKernel(const NeuronLaunch L)
     }
     __syncthreads();
     if(isLast) {
+        __shared__ unsigned int stepSpikes;
+        if(threadIdx.x == 0) stepSpikes = 0u;
+        __syncthreads();
         for(unsigned int q = threadIdx.x; q < L.num_groups * L.batch; q += blockDim.x) {
             const b200_neuron_group &o = L.groups[q / L.batch];
             const unsigned int ob = q % L.batch;
             o.spk_cnt[ob * o.num_delay_slots + ringSlot(k + 2, o.num_delay_slots)] = 0;
+            atomicAdd(&stepSpikes, __ldcg(&o.spk_cnt[ob * o.num_delay_slots + ringSlot(k + 1, o.num_delay_slots)]));
         }
+        __syncthreads();
         if(threadIdx.x == 0) {
+            atomicMax(&L.state->peak_spikes, stepSpikes);
             L.state->ticket = 0;
             L.state->timestep = timestep + 1;
             L.state->steps_done = L.state->steps_done + 1;

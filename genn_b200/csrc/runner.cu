@@ -228,6 +228,16 @@ struct b200_runner
     bool useTiled = true;
     float tiledMinEvents = 1.0e6f;          // estimated events of a step from which the tiled kernel takes it
     bool tiledReady = false, tiledStale = true;
+    // The tiled kernels cost two launches per step even when they find nothing to do, so they are only
+    // launched ("armed") while the network's recent activity could reach the threshold: the neuron kernel
+    // keeps the largest spike count of a step in StepState::peak_spikes, the host fetches it (asynchronously,
+    // into page-locked memory) behind every block of steps and looks at it before the next block
+    bool tiledArmed = false;
+    unsigned int *peakHost = nullptr;
+    cudaEvent_t peakEvent = nullptr;
+    bool peakPending = false;
+    unsigned int quietBlocks = 0;
+    double eventsPerSpike = 0.0;
     std::string tiledWhyNot;
     TiledTile *tiledTiles = nullptr;
     TiledSource *tiledSources = nullptr;
@@ -1142,6 +1152,11 @@ int buildTiled(b200_runner *r)
     r->tiledSmemBytes = smem;
     r->tiledSynapses = total;
     r->tiledReady = true;
+    {
+        unsigned long long neurons = 0;
+        for(const auto &ng : r->neuronGroups) neurons += ng.num_neurons;
+        r->eventsPerSpike = neurons ? (double)r->tiledSynapses / (double)neurons : 0.0;
+    }
     return B200_OK;
 }
 
@@ -1167,12 +1182,18 @@ int ensureTiled(b200_runner *r)
     return B200_OK;
 }
 
-int enqueueSynapses(b200_runner *r, bool capturing)
+// (`force`: an update the caller asked for on its own, with spike lists of its choosing)
+bool tiledActive(const b200_runner *r, bool force = false)
+{
+    return r->tiledReady && (force || r->tiledArmed || r->tiledMinEvents == 0);
+}
+
+int enqueueSynapses(b200_runner *r, bool capturing, bool force = false)
 {
     if(r->sparseTable.num) {
         ScopedTimer tm(r, "presynaptic_update", capturing);
         SynapseLaunch S = synapseLaunch(r, r->sparseTable);
-        if(r->tiledReady) {
+        if(tiledActive(r, force)) {
             // the step's estimated events decide which of the two kernels delivers the served groups
             const TiledLaunch T = tiledLaunch(r);
             tiledDecideKernel<<<1, TILED_BLOCK, 0, r->stream>>>(T);
@@ -1238,6 +1259,40 @@ int enqueueNeurons(b200_runner *r, unsigned long long numRec, bool capturing)
     return B200_OK;
 }
 
+// Behind a block of steps of the per-kernel path: the block's largest spike count on its way to the host.
+int fetchPeak(b200_runner *r)
+{
+    if(!r->peakHost) {
+        CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&r->peakHost), sizeof(unsigned int), cudaHostAllocPortable));
+        CUDA_TRY(cudaEventCreateWithFlags(&r->peakEvent, cudaEventDisableTiming));
+        *r->peakHost = 0u;
+    }
+    if(r->peakPending) return B200_OK;          // the copy of an earlier block is still under way: keep it
+    CUDA_TRY(cudaMemcpyAsync(r->peakHost, &r->state->peak_spikes, sizeof(unsigned int), cudaMemcpyDeviceToHost, r->stream));
+    CUDA_TRY(cudaMemsetAsync(&r->state->peak_spikes, 0, sizeof(unsigned int), r->stream));
+    CUDA_TRY(cudaEventRecord(r->peakEvent, r->stream));
+    r->peakPending = true;
+    return B200_OK;
+}
+
+// Before a block of steps: arm or disarm the tiled kernels from the last spike count that has arrived.
+int pollPeak(b200_runner *r)
+{
+    if(!r->tiledReady || !r->peakPending || cudaEventQuery(r->peakEvent) != cudaSuccess) return B200_OK;
+    r->peakPending = false;
+    const double estimate = (double)*r->peakHost * r->eventsPerSpike;
+    const bool was = r->tiledArmed;
+    if(estimate * 4.0 >= (double)r->tiledMinEvents) {
+        r->tiledArmed = true;
+        r->quietBlocks = 0;
+    }
+    else if(r->tiledArmed && estimate * 16.0 < (double)r->tiledMinEvents && ++r->quietBlocks >= 3) {
+        r->tiledArmed = false;
+    }
+    if(was != r->tiledArmed) r->dropGraph();        // the captured steps launch other kernels now
+    return B200_OK;
+}
+
 int enqueueStep(b200_runner *r, unsigned long long numRec, bool capturing)
 {
     int e = enqueueSynapses(r, capturing);
@@ -1247,7 +1302,7 @@ int enqueueStep(b200_runner *r, unsigned long long numRec, bool capturing)
 
 unsigned int kernelsPerStep(const b200_runner *r)
 {
-    return 1u + (r->sparseTable.num ? (r->tiledReady ? 3u : 1u) : 0u) + (r->postSpanTable.num ? 1u : 0u) + (r->learnTable.num ? 1u : 0u) +
+    return 1u + (r->sparseTable.num ? (tiledActive(r) ? 3u : 1u) : 0u) + (r->postSpanTable.num ? 1u : 0u) + (r->learnTable.num ? 1u : 0u) +
            (r->proceduralTable.num ? 1u : 0u);
 }
 
@@ -1375,6 +1430,8 @@ int b200_runner_destroy(b200_runner *r)
     for(unsigned int p = 0; p < B200_MAX_RANKS; p++) {
         if(r->peerArena[p] && !r->peerLocal[p]) cudaIpcCloseMemHandle(r->peerArena[p]);
     }
+    if(r->peakHost) cudaFreeHost(r->peakHost);
+    if(r->peakEvent) cudaEventDestroy(r->peakEvent);
     if(r->ncclComm && ncclApi()) ncclApi()->commDestroy(r->ncclComm);
     if(r->reducePacked) cudaFree(r->reducePacked);
     if(r->arena) cudaFree(r->arena);
@@ -1898,7 +1955,7 @@ int b200_update_synapses(b200_runner *r)
     if(e) return e;
     e = ensureTiled(r);
     if(e) return e;
-    return enqueueSynapses(r, false);
+    return enqueueSynapses(r, false, true);
 }
 
 int b200_update_neurons(b200_runner *r, uint64_t num_recording_timesteps)
@@ -1930,7 +1987,7 @@ int b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_ti
             left -= n;
         }
     }
-    else if((e = ensureTiled(r)) != B200_OK) {
+    else if((e = ensureTiled(r)) != B200_OK || (e = pollPeak(r)) != B200_OK) {
         return e;
     }
     else if(r->useGraph && !r->timing && num_steps >= 2) {
@@ -1948,6 +2005,10 @@ int b200_step_time(b200_runner *r, uint64_t num_steps, uint64_t num_recording_ti
     }
     for(; left; left--) {
         e = enqueueStep(r, num_recording_timesteps, false);
+        if(e) return e;
+    }
+    if(r->tiledReady && !(r->useFused && r->fusedEligible && !r->timing)) {
+        e = fetchPeak(r);
         if(e) return e;
     }
     r->hostTimestep += num_steps;
@@ -2118,6 +2179,11 @@ int b200_get_counter(b200_runner *r, const char *name, uint64_t *value)
             if(e) return e;
         }
         *value = (uint64_t)r->schedule;
+        return B200_OK;
+    }
+    if(n == "tiled_armed") {
+        // whether the next block of steps on the one-launch-per-kernel path launches the tiled kernels
+        *value = tiledActive(r) ? 1u : 0u;
         return B200_OK;
     }
     if(n == "tiled_ready" || n == "tiled_synapses" || n == "heavy") {

@@ -353,7 +353,9 @@ int  b200_get_counter(b200_runner *r, const char *name, uint64_t *value);
  * "deliver at emission" schedule sends near synapses between processes through per-CTA queues of self-validating
  * words; 0: reduces them straight into the other process's rings and fences) / "near_queue_words" (capacity of
  * one queue, 2 .. 2048; what does not fit goes the direct way), "use_tiled" / "tiled_min_events" (target-tiled SPARSE delivery of steps
- * with at least that many estimated events on the one-launch-per-kernel path),
+ * with at least that many estimated events on the one-launch-per-kernel path; 0: every step.  The tiled kernels
+ * are launched only while the largest spike count of the steps before says such a step may come: counter
+ * "tiled_armed"; b200_update_synapses always launches them),
  * "barrier_spin_limit" / "exchange_spin_limit" (polls) and "stream_wait_cycles" (SM cycles): how long a wait
  * inside a persistent kernel lasts before the launch gives up and b200_synchronize reports
  * B200_ERR_DEVICE_CHECK (defaults: tens of milliseconds; about two seconds). */

@@ -92,6 +92,25 @@ def test_step_by_step_matches_reference_golden(name, path):
     rt.close()
 
 
+def test_tiled_kernels_are_armed_by_activity():
+    """A threshold the network's steps reach: after a block of steps whose spike counts have arrived on the
+    host the tiled kernels are launched, and the run still matches the reference fixture."""
+    model, steps, dump_every = CASES["potjans_mini"]()
+    net = resolve(model)
+    rt = _runtime(net, steps)
+    _select(rt, "per-kernel")
+    rt.set_option("tiled_min_events", 200)
+    assert rt.counter("tiled_ready") == 1 and rt.counter("tiled_armed") == 0
+    got = helpers.run_and_collect(_Adapter(rt), net, steps, dump_every)
+    helpers.compare(got, helpers.load_golden("potjans_mini"), exact_state=False, rtol=RTOL, atol=ATOL)
+    # (single steps arm and disarm as spikes come and go; a block of 100 steps holds spikes for certain)
+    rt.step_time(100)
+    rt.synchronize()
+    rt.step_time(1)
+    assert rt.counter("tiled_armed") == 1, "the block's peak spike count was meant to arm the tiled kernels"
+    rt.close()
+
+
 def test_tiled_copy_follows_pushed_weights():
     """The tile-major copy is private: pushing new weights into the caller's array must reach it."""
     model, steps, _ = CASES["ff_sparse"]()

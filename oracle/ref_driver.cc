@@ -188,6 +188,7 @@ int main(int argc, char *argv[])
                 else if(t[0] == "dump_every") dumpEvery = (unsigned int)std::stoul(t[1]);
                 else if(t[0] == "fuse_psm") fusePSM = (t[1] == "1");
                 else if(t[0] == "narrow_ind") narrowInd = (t[1] == "1");
+                else if(t[0] == "timing") timing = (t[1] == "1");       // per-kernel timers (they synchronise every step)
                 else if(t[0] == "pop") {
                     PopSpec p;
                     p.name = t[1]; p.n = (unsigned int)std::stoul(t[2]); p.kind = t[3];

@@ -117,3 +117,38 @@ def test_golden_networks_through_the_plugin(name, workdir):
     spec = write_netspec(resolve(model), os.path.join(workdir, "spec"), steps, dump_every)
     _run(B200_DRIVER, spec, workdir, os.path.join(workdir, "out"))
     helpers.compare(_collect(os.path.join(workdir, "out")), helpers.load_golden(name), exact_state=False, rtol=RTOL, atol=ATOL)
+
+
+@pytest.mark.gpu
+def test_potjans_through_the_plugin_fires_like_the_library(workdir, capsys):
+    """The Potjans architecture at a tenth of its neurons (published in-degrees: 30 M synapses, dendritic delays,
+    constant-current background) through GeNN's runtime on the B200 backend: per-population rates over 0.2 s must
+    agree with the descriptor library's run of the same arrays (a chaotic network: 10 %), and the time per step of
+    GeNN's stepTime loop is printed (one launch per kernel, as GeNN's runtime drives it)."""
+    from genn_b200 import workloads
+    from genn_b200.runtime import Runtime
+    _need(B200_DRIVER)
+    steps = 2000
+    model = workloads.potjans(neuron_scale=0.1, seed=99, host_connectivity=True, background="dc", record=True)
+    net = resolve(model)
+    spec = write_netspec(net, os.path.join(workdir, "spec"), steps, 0)
+    with open(spec, "a") as f:
+        f.write("timing 0\n")          # GeNN's per-kernel timers synchronise after every kernel group
+    _run(B200_DRIVER, spec, workdir, os.path.join(workdir, "out"))
+    timing = dict(l.split() for l in open(os.path.join(workdir, "out", "timing.txt")))
+    got = _collect(os.path.join(workdir, "out"))
+    rt = Runtime(None, steps, net=net)
+    rt.step_time(steps)
+    rt.synchronize()
+    rt.pull_recording_buffers()
+    total = 0
+    for p in net.pops:
+        lib = len(rt.recorded_spikes(p.name)[0][1]) / p.n
+        plug = len(got[f"spikes_{p.name}"]) / p.n
+        total += len(got[f"spikes_{p.name}"])
+        assert abs(plug - lib) <= 0.1 * max(lib, plug) + 0.02, f"{p.name}: {plug:.3f} spikes per neuron through the plug-in, {lib:.3f} in the library"
+    rt.close()
+    assert total > 1000
+    with capsys.disabled():
+        print(f"\nplug-in: Potjans x0.1, {steps} steps, {float(timing['loop_seconds']) / steps * 1e6:.1f} us per step "
+              f"in GeNN's stepTime loop, {total} spikes")

@@ -332,6 +332,67 @@ def reference_arm(args):
     print(json.dumps(line), flush=True)
 
 
+def run_c2(args):
+    """Recurrent conductance-based E/I network (80 000 + 20 000 LIF, fixed in-degree 1 000: 100 M synapses with constant
+    weights, 4 B per event; ExpCond, 1 ms axonal delay, dt = 0.1 ms), single GPU.  One bench step = --block time steps."""
+    import torch
+    from genn_b200 import workloads
+    torch.cuda.set_device(0)
+    block = args.block
+    model = workloads.cond_ei(neuron_scale=1.0, record=True)
+    model.build()
+    model.load(num_recording_timesteps=block, device=0)
+    rt = model._runtime
+    rt.set_option("count_events", 1)
+    for item in args.option:
+        opt_name, opt_value = item.split("=")
+        rt.set_option(opt_name, float(opt_value))
+    sampler = ClockSampler(0)
+    sampler.start()
+    for _ in range(args.warmup):
+        rt.step_time(block)
+    rt.synchronize()
+    ev0, sp0, l0 = rt.counter("synaptic_events"), rt.counter("spikes"), rt.kernel_launches
+    sampler.mark()
+    ms = rt.step_time_timed(args.steps * block)
+    clocks = sampler.stop()
+    ev1, sp1, l1 = rt.counter("synaptic_events"), rt.counter("spikes"), rt.kernel_launches
+    seconds, sim_seconds = ms * 1e-3, args.steps * block * DT_MS * 1e-3
+    d2h = sum(a.nbytes for n, a in rt.plan.arrays.items() if n.endswith(".record"))
+    model.step_time(block)
+    model.pull_recording_buffers_from_device()
+    e0 = rt.counter("synaptic_events")
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        model.step_time(block)
+        model.pull_recording_buffers_from_device()
+    e2e_s = time.perf_counter() - t0
+    e2e_ev = rt.counter("synaptic_events") - e0
+    n = sum(p.n for p in rt.net.pops)
+    bytes_algo = (ev1 - ev0) * bytes_per_event(rt.net) + (sp1 - sp0) * ALGO_BYTES_PER_SPIKE
+    hbm_peak, peak_kind = measured_peaks()
+    line = {"metric": "synaptic events/s (recurrent conductance-based E/I network)", "value": (ev1 - ev0) / seconds,
+            "unit": "synaptic events/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "realtime_factor": sim_seconds / seconds, "us_per_timestep": ms * 1e3 / (args.steps * block),
+            "config": {"workload": f"{n} LIF neurons (80 % excitatory), fixed in-degree 1000 drawn on the host, constant weights "
+                                   f"0.6 / 6.7 nS, ExpCond, 1 ms axonal delay, constant drive 0.35 nA, dt = 0.1 ms; one bench step = "
+                                   f"{block} time steps",
+                       "schedule": int(rt.schedule), "step_path": rt.step_path()[0],
+                       "mean_rate_hz": (sp1 - sp0) / n / sim_seconds, "bytes_per_event": bytes_per_event(rt.net),
+                       "l2": "400 MB of synapse indices, larger than L2"},
+            "clocks": clocks,
+            "e2e": {"value": e2e_ev / e2e_s, "unit": "synaptic events/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(l1 - l0),
+            "roofline": {"kernel": "persistent step kernel" if rt.step_path()[0] else "per-kernel path", "bound": "hbm",
+                         "achieved": bytes_algo / seconds / 1e9, "peak": hbm_peak, "unit": "GB/s",
+                         "frac": bytes_algo / seconds / 1e9 / hbm_peak, "traffic": None, "peak_source": peak_kind,
+                         "algorithmic_bytes_per_launch": bytes_algo,
+                         "note": "natural firing rates (3 Hz): a step is latency, not bandwidth"}}
+    print(json.dumps(line), flush=True)
+    model.unload()
+
+
 def run_c4(args):
     """PROCEDURAL connectivity stress test (single GPU): nothing of the ~1e9-synapse matrix is stored,
     every spike regenerates its row and weights.  One bench step = --block time steps of 1 ms (default
@@ -696,8 +757,9 @@ def main():
     ap.add_argument("--probe-dense-size", type=int, default=8192)
     ap.add_argument("--probe", choices=["presyn", "phases", "e2e", "dense"], default=None,
                     help="run a bounded single-kernel workload (for profiling) instead of the benchmark")
-    ap.add_argument("--workload", choices=["potjans", "c4", "c5"], default="potjans",
-                    help="potjans: the headline workload; c4: the PROCEDURAL connectivity stress test (1 M LIF neurons, "
+    ap.add_argument("--workload", choices=["potjans", "c2", "c4", "c5"], default="potjans",
+                    help="potjans: the headline workload; c2: recurrent conductance-based E/I network (80 k + 20 k LIF, "
+                         "in-degree 1000, 1 ms axonal delay; single GPU); c4: the PROCEDURAL connectivity stress test (1 M LIF neurons, "
                          "p = 0.001, dt = 1 ms; single GPU); c5: batched plasticity (10 k Poisson -> 10 k LIF, STDP, 32 batch "
                          "entries per GPU, batch-reduce + all-reduce every 100 steps)")
     ap.add_argument("--c5-batch", type=int, default=32, help="batch entries per GPU")
@@ -728,6 +790,9 @@ def main():
         return
     if args.probe:
         run_probe(args)
+        return
+    if args.workload == "c2":
+        run_c2(args)
         return
     if args.workload == "c4":
         run_c4(args)

@@ -172,3 +172,31 @@ def test_data_parallel_reduction_over_nccl_on_two_gpus():
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=600, env=env, cwd=REPO)
     assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
     assert "batch_allreduce_check ok" in res.stdout
+
+
+@pytest.mark.gpu
+def test_bench_workloads_build_and_step_at_small_size():
+    """The C4 and C5 workloads of bench.py at a size that runs in a second: PROCEDURAL stress network with 32 threads
+    per spike, batched STDP with its batch-reduce custom update."""
+    m = workloads.procedural_stress(num_neurons=4000, prob=0.01, threads_per_spike=32, record=True)
+    m.build()
+    m.load(num_recording_timesteps=50)
+    rt = m._runtime
+    rt.set_option("count_events", 1)
+    m.step_time(50)
+    rt.synchronize()
+    assert rt.counter("spikes") > 0 and rt.counter("synaptic_events") > 0
+    m.unload()
+
+    m, sg = workloads.batched_stdp(num_pre=300, num_post=200, batch=4)
+    m.build()
+    m.load()
+    rt = m._runtime
+    m.step_time(100)
+    g = rt.array("syn.g")
+    m.custom_update("gradient")
+    after = rt.array("syn.g")
+    want = g.sum(axis=0, dtype=np.float64) / 4
+    for b in range(4):
+        np.testing.assert_allclose(after[b], want, rtol=1e-5, atol=1e-6)
+    m.unload()

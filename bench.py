@@ -2,7 +2,9 @@
 Potjans-Diesmann microcircuit architecture on B200.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
-    python bench.py --probe presyn|phases|e2e [...]      # bounded single-kernel workloads for ncu
+    python bench.py --workload c2|c4|c5 [...]                  # the other configurations: E/I network, PROCEDURAL
+                                                               # stress test, batched STDP with batch-reduce + all-reduce
+    python bench.py --probe presyn|phases|e2e|dense [...]      # bounded single-kernel workloads (ncu, comparisons)
 
 A bench STEP is a block of ``--block`` (default 1000) simulation time steps of
 dt = 0.1 ms, i.e. 0.1 s of biological time, run by ONE launch of the persistent
@@ -16,9 +18,10 @@ public ``GeNNModel`` API with the spike recording copied to page-locked host
 memory every step; ``roofline`` is the persistent kernel of the timed region
 (algorithmic bytes of the launch over its CUDA-event time) and
 ``roofline_saturated`` the SPARSE delivery kernel driven with a quarter of all
-neurons spiking in one step (inputs far larger than L2); ``parity`` compares
-the population firing rates and CV-ISI of a 10 s run with those the reference's
-CPU backend produced for the same architecture; ``cpu_baseline`` times the
+neurons spiking in one step (inputs far larger than L2); ``parity`` runs the x1
+network the reference's CPU backend was run on (same arrays, drawn on the host),
+split over the N GPUs, for 10 s and compares population firing rates and CV-ISI
+with the reference's (tolerance 2 %); ``cpu_baseline`` times the
 reference's own single-threaded CPU backend (or, where its build is absent and
 labelled as such, the C port of its algorithm) on this box's host cores.
 """
@@ -599,7 +602,9 @@ def run_probe(args):
             2.6 GB x scale; one launch reads about scale x fraction x 2.1 GB (twice L2 at the defaults).
     phases: --probe-warm + --probe-steps time steps of the persistent kernel at natural rates with its
             clock64 phase counters on.
-    e2e:    where one GeNNModel.step_time + recording pull spends its time."""
+    e2e:    where one GeNNModel.step_time + recording pull spends its time.
+    dense:  batched DENSE presynaptic update, this library's row gather beside the same update as a contraction
+            through the vendor GEMM (8192 x 8192 weights, batch 1 / 32 / 256)."""
     from genn_b200 import workloads
     from genn_b200.runtime import Runtime
     if args.probe == "presyn":

@@ -1151,6 +1151,12 @@ int buildTiled(b200_runner *r)
     r->tiledGrid = grid;
     r->tiledSmemBytes = smem;
     r->tiledSynapses = total;
+    if(!r->peakHost) {
+        // where the neuron kernel's spike-count peaks land (allocated here, with the copy; never on the time-step path)
+        CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&r->peakHost), sizeof(unsigned int), cudaHostAllocPortable));
+        CUDA_TRY(cudaEventCreateWithFlags(&r->peakEvent, cudaEventDisableTiming));
+        *r->peakHost = 0u;
+    }
     r->tiledReady = true;
     {
         unsigned long long neurons = 0;
@@ -1262,12 +1268,7 @@ int enqueueNeurons(b200_runner *r, unsigned long long numRec, bool capturing)
 // Behind a block of steps of the per-kernel path: the block's largest spike count on its way to the host.
 int fetchPeak(b200_runner *r)
 {
-    if(!r->peakHost) {
-        CUDA_TRY(cudaHostAlloc(reinterpret_cast<void**>(&r->peakHost), sizeof(unsigned int), cudaHostAllocPortable));
-        CUDA_TRY(cudaEventCreateWithFlags(&r->peakEvent, cudaEventDisableTiming));
-        *r->peakHost = 0u;
-    }
-    if(r->peakPending) return B200_OK;          // the copy of an earlier block is still under way: keep it
+    if(!r->peakHost || r->peakPending) return B200_OK;      // (an earlier block's copy still under way: keep it)
     CUDA_TRY(cudaMemcpyAsync(r->peakHost, &r->state->peak_spikes, sizeof(unsigned int), cudaMemcpyDeviceToHost, r->stream));
     CUDA_TRY(cudaMemsetAsync(&r->state->peak_spikes, 0, sizeof(unsigned int), r->stream));
     CUDA_TRY(cudaEventRecord(r->peakEvent, r->stream));

@@ -297,6 +297,7 @@ presynapticPostSpanKernel(const SynapseLaunch L)
 // the number of spikes is only known on the device.  Every synapse costs one reduction into L2 and
 // no HBM traffic at all.
 constexpr unsigned int PROC_BLOCK = 256;
+constexpr unsigned int PROC_HOLD = 48;      // targets of a sub-row kept between its generation and its delivery
 
 __global__ void __launch_bounds__(PROC_BLOCK)
 presynapticProceduralKernel(const SynapseLaunch L)
@@ -330,31 +331,39 @@ presynapticProceduralKernel(const SynapseLaunch L)
         const bool work = live && pre != 0xFFFFFFFFu;
         const unsigned int fixedLength = !work ? 0u : (g.proc_connect == B200_CONNECT_FIXED_NUMBER_POST_WITH_REPLACEMENT)
             ? (unsigned int)g.proc_connect_params[0] : (g.row_length ? g.row_length[pre] : 0u);
-        // where this sub-row starts in the row: only drawn weights depend on it, and they cost a first
-        // pass that counts the sub-row's synapses
-        unsigned int base = 0, mine = 0;
+        auto deliver = [&](unsigned int at, unsigned int post) {
+            if(at >= g.row_stride) return;      // the row the initialisation kernel would have stored ends here
+            float w = g.wu_params[0];
+            if(!constant) {
+                b200_rng rng = b200_rng_init(L.seed, g.proc_weight_stream, (unsigned long long)pre * g.row_stride + at);
+                w = drawInitValue(g.proc_weight_init, g.proc_weight_params, &rng);
+            }
+            redAdd(target + post, w);
+        };
+        unsigned int n = 0;
         if(!constant && T > 1u) {
-            if(work) mine = generateRow(g.proc_connect, g.proc_connect_params, pre, 0u, numTrg, fixedLength, L.seed, g.rng_stream,
-                                        [](unsigned int, unsigned int) {}, t, t + 1u);
-            unsigned int incl = mine;
+            // Drawn weights are keyed on the position in the ROW, which a sub-row only knows once the sub-rows
+            // before it have been counted: generate the sub-row once into a small buffer, exchange the counts
+            // (shuffle scan over the T lanes of the spike), then draw the weights and deliver from the buffer.
+            // (A sub-row longer than the buffer is generated a second time for its tail.)
+            unsigned int held[PROC_HOLD];
+            if(work) n = generateRow(g.proc_connect, g.proc_connect_params, pre, 0u, numTrg, fixedLength, L.seed, g.rng_stream,
+                                     [&](unsigned int at, unsigned int post) { if(at < PROC_HOLD) held[at] = post; }, t, t + 1u);
+            unsigned int incl = n;
             for(unsigned int o = 1; o < T; o <<= 1) {
                 const unsigned int v = __shfl_up_sync(0xFFFFFFFFu, incl, o);
                 if((lane & (T - 1u)) >= o) incl += v;
             }
-            base = incl - mine;
+            const unsigned int base = incl - n;
+            const unsigned int fromBuffer = min(n, PROC_HOLD);
+            for(unsigned int at = 0; at < fromBuffer; at++) deliver(base + at, held[at]);
+            if(n > PROC_HOLD) {
+                generateRow(g.proc_connect, g.proc_connect_params, pre, 0u, numTrg, fixedLength, L.seed, g.rng_stream,
+                            [&](unsigned int at, unsigned int post) { if(at >= PROC_HOLD) deliver(base + at, post); }, t, t + 1u);
+            }
         }
-        unsigned int n = 0;
-        if(work) {
-            n = generateRow(g.proc_connect, g.proc_connect_params, pre, 0u, numTrg, fixedLength, L.seed, g.rng_stream,
-                [&](unsigned int at, unsigned int post) {
-                    if(base + at >= g.row_stride) return;      // the row the initialisation kernel would have stored ends here
-                    float w = g.wu_params[0];
-                    if(!constant) {
-                        b200_rng rng = b200_rng_init(L.seed, g.proc_weight_stream, (unsigned long long)pre * g.row_stride + base + at);
-                        w = drawInitValue(g.proc_weight_init, g.proc_weight_params, &rng);
-                    }
-                    redAdd(target + post, w);
-                }, t, t + 1u);
+        else if(work) {
+            n = generateRow(g.proc_connect, g.proc_connect_params, pre, 0u, numTrg, fixedLength, L.seed, g.rng_stream, deliver, t, t + 1u);
         }
         // the whole row's length: sum over the T lanes of the spike
         unsigned int rowLen = n;

@@ -1,0 +1,33 @@
+"""bench.py's tracked inputs: the ncu record of the persistent kernel's DRAM traffic must belong to the kernel
+sources in the tree (bench.py prints `"traffic": null` otherwise), the reference statistics it compares with must be
+complete, and its command line must parse."""
+import json
+import os
+import subprocess
+import sys
+
+REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, REPO)
+
+
+def test_dram_traffic_record_was_taken_on_the_sources_in_the_tree():
+    import bench
+    per_step, note = bench.captured_traffic("streamStepKernel")
+    assert per_step is not None, note + ": re-take the capture described in profiles/dram_traffic.txt"
+    # 0.68 MB of algorithmic bytes per step; the capture lies between 1x and 3x of that
+    assert 0.6e6 < per_step < 2.1e6
+
+
+def test_reference_statistics_cover_every_population():
+    for name, pops in (("stats_potjans_x1.json", ["23E", "23I", "4E", "4I", "5E", "5I", "6E", "6I"]), ("stats_cond_ei.json", ["E", "I"])):
+        doc = json.load(open(os.path.join(REPO, "tests", "golden", name)))
+        assert doc["steps"] == 100000 and "single_threaded_cpu" in doc["produced_by"]
+        for p in pops:
+            assert doc["populations"][p]["rate_hz"] > 0.5 and 0.5 < doc["populations"][p]["cv_isi"] < 1.5
+
+
+def test_bench_command_line():
+    out = subprocess.run([sys.executable, os.path.join(REPO, "bench.py"), "--help"], capture_output=True, text=True, timeout=120)
+    assert out.returncode == 0
+    for flag in ("--gpus", "--steps", "--warmup", "--impl", "--workload", "--probe", "--parity-seconds"):
+        assert flag in out.stdout

@@ -331,7 +331,10 @@ int  b200_step_time_timed(b200_runner *r, uint64_t num_steps, uint64_t num_recor
  * updates): begin waits for the stream and records, end records, waits and returns the elapsed time. */
 int  b200_timed_begin(b200_runner *r);
 int  b200_timed_end(b200_runner *r, float *milliseconds);
-/* Waits for the stream and reports failed device-side checks (out-of-range index, row overflow). */
+/* Waits for the stream and reports failed device-side checks (out-of-range index, row overflow, a wait inside a
+ * persistent kernel that ran out).  After a wait that ran out the launch has ended early: the model's state is that
+ * of an unknown step and, in a sharded model, words of the step may still be under way between the processes, so
+ * the runner is to be destroyed (on every process of a sharded model); the CUDA context stays usable. */
 int  b200_synchronize(b200_runner *r);
 int  b200_get_timestep(b200_runner *r, uint64_t *timestep);
 int  b200_set_timestep(b200_runner *r, uint64_t timestep);

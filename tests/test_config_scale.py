@@ -79,3 +79,21 @@ def test_statistics_helper_on_known_trains():
     merged = stats.merge([stats.partial(steps[:4], ids[:4], 1, first_id=0),
                           stats.partial(steps[4:], ids[4:], 2, first_id=1)], 1.0)
     assert merged["rate_hz"] == pytest.approx(3.0) and merged["cv_isi"] == pytest.approx(0.25)
+
+
+def test_host_drawn_potjans_is_the_same_network_every_time_and_shards_partition_it():
+    """The projections are drawn side by side by a thread pool, each from a stream of its own: the result must not
+    depend on the scheduling, and the shards of a sharded build must be exactly the unsharded network's synapses."""
+    from genn_b200 import workloads
+    from genn_b200.resolve import resolve
+    a = resolve(workloads.potjans(neuron_scale=0.01, seed=5, host_connectivity=True, background="dc"))
+    b = resolve(workloads.potjans(neuron_scale=0.01, seed=5, host_connectivity=True, background="dc"))
+    shards = [resolve(workloads.potjans(neuron_scale=0.01, seed=5, host_connectivity=True, background="dc", shard=(r, 2)))
+              for r in range(2)]
+    total = 0
+    for sa, sb in zip(a.syns, b.syns):
+        assert np.array_equal(sa.row_length, sb.row_length) and np.array_equal(sa.ind, sb.ind)
+        assert np.array_equal(sa.g, sb.g) and np.array_equal(sa.d, sb.d)
+        assert int(sa.row_length.sum()) == sum(int(s.syn(sa.name).row_length.sum()) for s in shards)
+        total += int(sa.row_length.sum())
+    assert total > 100000

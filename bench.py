@@ -880,12 +880,15 @@ def main():
     model.step_time(block)
     model.pull_recording_buffers_from_device()
     e2e_ev0 = rt.counter("synaptic_events")
+    d2h0 = rt.factory.d2h_bytes
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
         model.step_time(block)
         model.pull_recording_buffers_from_device()
     barrier()
+    # what the pulls really moved: the recording's non-zero words as (index, word) pairs
+    d2h_moved = (rt.factory.d2h_bytes - d2h0) / max(1, args.steps)
     e2e_seconds = allreduce(time.perf_counter() - t0, dist.ReduceOp.MAX if world > 1 else None)
     e2e_events = allreduce(float(rt.counter("synaptic_events") - e2e_ev0), dist.ReduceOp.SUM if world > 1 else None)
     # firing rates from the last pulled recording (sanity: the network is in its asynchronous state)
@@ -1043,8 +1046,11 @@ def main():
                        "mean_rates_hz": rates, "bytes_per_event": bpe},
             "clocks": clocks,
             "e2e": {"value": e2e_events / e2e_seconds, "unit": "synaptic events/s", "h2d_bytes_per_step": 0,
-                    "d2h_bytes_per_step": d2h, "realtime_factor": sim_seconds / e2e_seconds,
-                    "note": "GeNNModel.step_time + pull_recording_buffers_from_device into page-locked memory; "
+                    "d2h_bytes_per_step": d2h_moved, "recording_bytes_per_step": d2h,
+                    "realtime_factor": sim_seconds / e2e_seconds,
+                    "note": "GeNNModel.step_time + pull_recording_buffers_from_device into page-locked memory (the "
+                            "recording's non-zero bit words travel as (index, word) pairs listed on the device; "
+                            "recording_bytes_per_step is the size of the recording itself); "
                             "the model takes no per-step host input (background drive is drawn on the device, as in "
                             "the reference script)"},
             "gpu_launches": int(l1 - l0),

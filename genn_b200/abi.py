@@ -102,6 +102,7 @@ _PROTOTYPES = {
     "b200_array_pull": [C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t],
     "b200_array_memset": [C.c_void_p, C.c_void_p, C.c_int, C.c_size_t],
     "b200_exchange_alloc": [C.c_void_p, C.c_size_t, C.POINTER(C.c_void_p)],
+    "b200_compact_words": [C.c_void_p, C.c_void_p, C.c_uint64, C.c_uint32, C.c_void_p, C.c_uint32, C.c_void_p],
     "b200_timed_begin": [C.c_void_p],
     "b200_timed_end": [C.c_void_p, C.POINTER(C.c_float)],
     "b200_nccl_unique_id": [C.c_void_p],

@@ -69,6 +69,24 @@ postsynapticUpdateKernel(const SynapseLaunch L)
     }
 }
 
+// The non-zero words of a spike-recording array, as (word index + base, word) pairs appended to `pairs`
+// (`counter` counts them all, also those beyond `capacity`).  A recording is one bit per neuron and time step and
+// almost all zeros at cortical rates: the host fetches the pairs instead of the array (two per cent of its bytes
+// at 3 Hz and dt = 0.1 ms).
+__global__ void __launch_bounds__(256)
+compactWordsKernel(const unsigned int *__restrict__ words, unsigned long long numWords, unsigned int base,
+                   uint2 *__restrict__ pairs, unsigned int capacity, unsigned int *counter)
+{
+    const unsigned long long stride = (unsigned long long)gridDim.x * blockDim.x;
+    for(unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < numWords; i += stride) {
+        const unsigned int w = __ldg(&words[i]);
+        if(w) {
+            const unsigned int pos = atomicAdd(counter, 1u);
+            if(pos < capacity) pairs[pos] = make_uint2(base + (unsigned int)i, w);
+        }
+    }
+}
+
 constexpr int REDUCE_BLOCK = 256;
 
 // `phases`: bit 0 reduce, bit 1 write back.  Both in one pass on one GPU.  A data-parallel run reduces

@@ -2302,6 +2302,20 @@ int b200_step_time_timed(b200_runner *r, uint64_t num_steps, uint64_t num_record
     return B200_OK;
 }
 
+int b200_compact_words(b200_runner *r, const uint32_t *words, uint64_t num_words, uint32_t base_index,
+                       void *pairs, uint32_t capacity, uint32_t *counter)
+{
+    if(!r || !words || !pairs || !counter) return fail(B200_ERR_INVALID, "null argument to b200_compact_words");
+    if(base_index + num_words > 0xFFFFFFFFull) return fail(B200_ERR_INVALID, "word indices beyond 32 bits");
+    if(num_words == 0) return B200_OK;
+    CUDA_TRY(cudaSetDevice(r->device));
+    const unsigned int blocks = (unsigned int)std::min<uint64_t>((num_words + 255) / 256, 148u * 8u);
+    compactWordsKernel<<<blocks, 256, 0, r->stream>>>(words, num_words, base_index, static_cast<uint2*>(pairs), capacity, counter);
+    CUDA_TRY(cudaPeekAtLastError());
+    r->launches++;
+    return B200_OK;
+}
+
 int b200_timed_begin(b200_runner *r)
 {
     if(!r) return fail(B200_ERR_INVALID, "null runner");

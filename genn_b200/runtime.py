@@ -111,6 +111,9 @@ class Runtime:
         self.factory = DeviceFactory(self.lib, self.handle)
         self._pinned = []
         self._rec_host = {}
+        self.recording_pairs_capacity = None        # (index, word) pairs a recording pull has room for; None: 1/16 of the words
+        self._rec_compact = None        # device pair list, device counter, their page-locked copies, capacity
+        self._rec_pairs, self._rec_layout = None, {}
         self._rec_timestep = 0
         self.shard = shard
         # rank -> device pointer of a peer arena that is already addressable in this process
@@ -457,24 +460,61 @@ class Runtime:
         return np.frombuffer(buf, dtype=dtype, count=int(np.prod(shape, dtype=np.int64))).reshape(shape)
 
     def pull_recording_buffers(self):
-        """Copy the spike-recording bit words to page-locked host memory
-        (Runtime::pullRecordingBuffersFromDevice, runtime.cc:720-746).  Decoding
-        into (times, ids) happens lazily in :meth:`recorded_spikes`."""
+        """Bring the spike recording of the last ``num_recording_timesteps`` steps to page-locked host memory
+        (Runtime::pullRecordingBuffersFromDevice, runtime.cc:720-746, copies the bit words whole).  A recording is
+        almost all zeros at cortical rates, so the device first lists its non-zero words (b200_compact_words) and
+        only (index, word) pairs travel; a recording too dense for the pair buffer is copied whole instead.
+        Decoding into (times, ids) happens lazily in :meth:`recorded_spikes`."""
         T = self.num_recording_timesteps
         if not T:
             raise Exception("Recording buffer not allocated - cannot pull from device")
-        self.synchronize()
+        self.synchronize()          # (reports device-side checks of the steps behind the recording)
+        recs = [(p.name, self.plan.arrays[f"{p.name}.record"]) for p in self.net.pops if f"{p.name}.record" in self.plan.arrays]
+        self._rec_pairs, self._rec_layout = None, {}
+        total = sum(int(np.prod(a.shape, dtype=np.int64)) for _, a in recs)
+        if recs and total < (1 << 32):
+            if self._rec_compact is None:
+                # room for one non-zero word in sixteen unless the caller chose
+                cap = self.recording_pairs_capacity or max(1024, total // 16)
+                self._rec_compact = (self.factory.alloc(cap * 8), self.factory.alloc(4), self.pinned_empty((cap, 2), np.uint32),
+                                     self.pinned_empty((1,), np.uint32), cap)
+            pairs, counter, host_pairs, host_count, cap = self._rec_compact
+            check(self.lib.b200_array_memset(self.handle, counter.ptr, 0, 4))
+            base = 0
+            for name, arr in recs:
+                n = int(np.prod(arr.shape, dtype=np.int64))
+                check(self.lib.b200_compact_words(self.handle, arr.ptr, n, base, pairs.ptr, cap, counter.ptr))
+                self._rec_layout[name] = (base, arr.shape)
+                base += n
+            check(self.lib.b200_array_pull(self.handle, host_count.ctypes.data, counter.ptr, 4))     # waits for the stream
+            self.factory.d2h_bytes += 4
+            count = int(host_count[0])
+            if count <= cap:
+                if count:
+                    check(self.lib.b200_array_pull(self.handle, host_pairs.ctypes.data, pairs.ptr, count * 8))
+                    self.factory.d2h_bytes += count * 8
+                self._rec_pairs = host_pairs[:count].copy()
         self._rec_timestep = self.timestep
-        for p in self.net.pops:
-            arr = self.plan.arrays.get(f"{p.name}.record")
-            if arr is None:
-                continue
-            host = self._rec_host.get(p.name)
-            if host is None:
-                host = self._rec_host[p.name] = self.pinned_empty(arr.shape, arr.dtype)
-            self.factory.pull(arr.handle, host)
+        for name, arr in recs:
+            if self._rec_pairs is None:
+                host = self._rec_host.get(name)
+                if host is None:
+                    host = self._rec_host[name] = self.pinned_empty(arr.shape, arr.dtype)
+                self.factory.pull(arr.handle, host)
             if self.model is not None:
-                self.model.neuron_populations[p.name]._spike_recording_data = _LazyRecording(self, p.name)
+                self.model.neuron_populations[name]._spike_recording_data = _LazyRecording(self, name)
+
+    def _recording_words(self, pop: str) -> np.ndarray:
+        """The pulled recording of ``pop`` as its array of bit words [T][batch][words]."""
+        if self._rec_pairs is None:
+            return self._rec_host[pop]
+        base, shape = self._rec_layout[pop]
+        n = int(np.prod(shape, dtype=np.int64))
+        words = np.zeros(n, dtype=np.uint32)
+        idx = self._rec_pairs[:, 0].astype(np.int64) - base
+        mine = (idx >= 0) & (idx < n)
+        words[idx[mine]] = self._rec_pairs[mine, 1]
+        return words.reshape(shape)
 
     def recorded_spikes(self, pop: str):
         """Decode pulled recording words into [(times, ids)] per batch element,
@@ -488,7 +528,7 @@ class Runtime:
         lo, hi = (p.shard_bounds[self.shard[0]], p.shard_bounds[self.shard[0] + 1]) if self.shard else (0, p.n)
         start = (ts - T) * self.net.dt
         # the buffer is a ring over timestep % T: rotate so index 0 is the oldest step
-        words = np.roll(self._rec_host[pop], -(ts % T), axis=0)
+        words = np.roll(self._recording_words(pop), -(ts % T), axis=0)
         out = []
         for b in range(self.net.batch_size):
             bits = np.unpackbits(np.ascontiguousarray(words[:, b, :]).view(np.uint8), axis=1, bitorder="little")

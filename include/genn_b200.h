@@ -242,6 +242,13 @@ int  b200_host_free(b200_runner *r, void *host_ptr);
 int  b200_array_push(b200_runner *r, void *device_ptr, const void *host, size_t bytes);
 int  b200_array_pull(b200_runner *r, void *host, const void *device_ptr, size_t bytes);
 int  b200_array_memset(b200_runner *r, void *device_ptr, int value, size_t bytes);
+/* Spike recordings are one bit per neuron and time step and almost all zeros (Runtime::pullRecordingBuffersFromDevice,
+ * runtime.cc:720-746, copies them whole).  This appends the non-zero 32-bit words of `words` to `pairs` as
+ * (base_index + word index, word), 8 bytes each, on the runner's stream; `counter` (a device word the caller has
+ * zeroed) counts every non-zero word, also those that found no room below `capacity`: the caller then copies
+ * the array itself.  Order of the pairs is arbitrary. */
+int  b200_compact_words(b200_runner *r, const uint32_t *words, uint64_t num_words, uint32_t base_index,
+                        void *pairs, uint32_t capacity, uint32_t *counter);
 
 /* ---- spike exchange between processes (no counterpart in the reference, which has no model
  *      sharding: backendCUDAHIP.cc uses NCCL for the all-reduce of custom-update results only).

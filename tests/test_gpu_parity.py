@@ -156,6 +156,30 @@ def test_many_steps_in_one_call_and_recording_match_reference_golden(name, path)
     rt.close()
 
 
+@pytest.mark.parametrize("capacity", [None, 8])
+def test_recording_pull_as_pairs_equals_the_recording(capacity):
+    """The pull lists the recording's non-zero words on the device and fetches those; with no room
+    for them it copies the arrays whole.  Either way the host sees the device's words."""
+    model, steps, _ = CASES["potjans_mini"]()
+    net = resolve(model)
+    rt = _runtime(net, steps)
+    rt.recording_pairs_capacity = capacity
+    rt.step_time(steps)
+    before = rt.factory.d2h_bytes
+    rt.pull_recording_buffers()
+    moved = rt.factory.d2h_bytes - before
+    whole = 0
+    for p in net.pops:
+        if not p.record:
+            continue
+        device = rt.array(f"{p.name}.record")
+        whole += device.nbytes
+        assert np.array_equal(rt._recording_words(p.name), device), p.name
+    assert (rt._rec_pairs is None) == (capacity is not None)
+    assert moved < whole if capacity is None else moved >= whole
+    rt.close()
+
+
 @pytest.mark.parametrize("name,num", [("ff_sparse", 100), ("potjans_mini", 100), ("c1_full", 1000)])
 def test_matches_cpu_checker_every_step(name, num):
     """Same inputs through the CPU checker (itself bit-identical to the reference on these

@@ -635,10 +635,17 @@ def run_probe(args):
         rt.synchronize()
         sec = rt.timer("presynaptic_update") / args.probe_reps
         bpe = bytes_per_event(net)
-        print(json.dumps({"probe": "presyn", "scale": scale, "fraction": args.probe_fraction,
-                          "events_per_launch": events, "spikes_per_launch": spikes, "launch_ms": sec * 1e3,
-                          "events_per_s": events / sec, "bytes_per_event": bpe,
-                          "GBps": (events * bpe + spikes * ALGO_BYTES_PER_SPIKE) / sec / 1e9}))
+        out = {"probe": "presyn", "scale": scale, "fraction": args.probe_fraction,
+               "events_per_launch": events, "spikes_per_launch": spikes, "launch_ms": sec * 1e3,
+               "events_per_s": events / sec, "bytes_per_event": bpe,
+               "GBps": (events * bpe + spikes * ALGO_BYTES_PER_SPIKE) / sec / 1e9}
+        if any(item.startswith("fused_profile=") for item in args.option):
+            # the tiled kernel's own clock64 record of its last launch, per CTA: [min, median, max]
+            cyc = rt.cta_cycles()
+            rows = np.stack([cyc[:, 0], cyc[:, 1], cyc[:, 2] >> np.uint64(32), cyc[:, 2] & np.uint64(0xFFFFFFFF), cyc[:, 3]], axis=1).astype(np.int64)
+            out["tiled_cta_columns"] = ["cycles", "cycles_outside_ticket_loops", "segments", "tickets", "cycles_idle_at_loop_ends"]
+            out["tiled_cta_rows_by_cycles"] = rows[np.argsort(rows[:, 0])].tolist()
+        print(json.dumps(out))
         rt.close()
     elif args.probe == "dense":
         # Batched DENSE presynaptic update: this library's row gather (4 x numPost bytes per spike and batch
@@ -999,7 +1006,8 @@ def main():
         sat_s = rt.timer("presynaptic_update") / reps
         rt.enable_timing(False)
         sat_bytes = sat_events * bpe + sat_spikes * ALGO_BYTES_PER_SPIKE
-        roofline_sat = {"kernel": "presynapticSparseKernel", "bound": "hbm", "achieved": sat_bytes / sat_s / 1e9,
+        roofline_sat = {"kernel": "tiledDeliverKernel (with tiledDecideKernel before it and presynapticSparseKernel, left nothing, after)",
+                        "bound": "hbm", "achieved": sat_bytes / sat_s / 1e9,
                         "peak": hbm_peak, "unit": "GB/s", "frac": sat_bytes / sat_s / 1e9 / hbm_peak,
                         "traffic": None, "peak_source": peak_kind, "events_per_launch": sat_events,
                         "algorithmic_bytes_per_launch": sat_bytes, "launch_ms": sat_s * 1e3,

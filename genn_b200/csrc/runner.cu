@@ -226,6 +226,7 @@ struct b200_runner
     // target-tiled delivery of heavy steps on the one-launch-per-kernel path (tiled.cuh): private
     // re-packed copy of the non-learning SPARSE groups
     bool useTiled = true;
+    float tiledTicketEvents = 2048.0f, tiledTicketCost = 256.0f;     // (swept on Potjans x1 with a quarter of the neurons spiking)
     float tiledMinEvents = 1.0e6f;          // estimated events of a step from which the tiled kernel takes it
     bool tiledReady = false, tiledStale = true;
     // The tiled kernels cost two launches per step even when they find nothing to do, so they are only
@@ -962,6 +963,13 @@ struct ScopedTimer
     }
 };
 
+using TiledKernel = void (*)(const TiledLaunch);
+TiledKernel tiledKernelFor(bool key16, bool weights)
+{
+    if(key16) return weights ? tiledDeliverKernel<uint16_t, true> : tiledDeliverKernel<uint16_t, false>;
+    return weights ? tiledDeliverKernel<uint32_t, true> : tiledDeliverKernel<uint32_t, false>;
+}
+
 // (Re)build the private tile-major copy of the non-learning SPARSE groups (tiled.cuh).  Not on the
 // time-step path: runs when the per-kernel path is first used and after the arrays it copies changed.
 int buildTiled(b200_runner *r)
@@ -1134,14 +1142,7 @@ int buildTiled(b200_runner *r)
         if(ce == cudaSuccess) ce = cudaMalloc(&r->tiledCtaStart, sizeof(unsigned int) * 2 * (grid + 1));
         if(ce != cudaSuccess) { r->dropTiled(); CUDA_TRY(ce); }
     }
-    if(key16) {
-        if(anyWeights) CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint16_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        else CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint16_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    }
-    else {
-        if(anyWeights) CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint32_t, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        else CUDA_TRY(cudaFuncSetAttribute(tiledDeliverKernel<uint32_t, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    }
+    CUDA_TRY(cudaFuncSetAttribute(tiledKernelFor(key16, anyWeights), cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     r->tiledRunStart = static_cast<unsigned int*>(runStart.release());
     r->tiledKeys = keys.release();
     r->tiledWeights = static_cast<float*>(weights.release());
@@ -1175,6 +1176,8 @@ TiledLaunch tiledLaunch(const b200_runner *r)
     L.num_sources = r->tiledNumSources; L.grid = r->tiledGrid;
     L.batch = r->batch; L.post_bits = r->tiledPostBits; L.min_events = r->tiledMinEvents; L.state = r->state;
     L.count_events = r->countEvents ? 1u : 0u;
+    L.ticket_events = r->tiledTicketEvents; L.ticket_cost = r->tiledTicketCost;
+    L.profile = (r->fusedProfile && r->tiledGrid <= PROFILE_MAX_CTAS) ? r->fusedCtaCycles : nullptr;
     return L;
 }
 
@@ -1203,11 +1206,7 @@ int enqueueSynapses(b200_runner *r, bool capturing, bool force = false)
             // the step's estimated events decide which of the two kernels delivers the served groups
             const TiledLaunch T = tiledLaunch(r);
             tiledDecideKernel<<<1, TILED_BLOCK, 0, r->stream>>>(T);
-            const bool key16 = (r->tiledPostBits == 10u);
-            if(key16 && r->tiledWeights) tiledDeliverKernel<uint16_t, true><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
-            else if(key16) tiledDeliverKernel<uint16_t, false><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
-            else if(r->tiledWeights) tiledDeliverKernel<uint32_t, true><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
-            else tiledDeliverKernel<uint32_t, false><<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
+            tiledKernelFor(r->tiledPostBits == 10u, r->tiledWeights != nullptr)<<<r->tiledGrid, TILED_BLOCK, r->tiledSmemBytes, r->stream>>>(T);
             r->launches += 2;
             S.tiled_served = r->tiledServed;
         }
@@ -1843,6 +1842,8 @@ int b200_set_option(b200_runner *r, const char *name, double value)
     }
     else if(n == "use_tiled") { r->useTiled = (value != 0.0); r->tiledStale = true; }
     else if(n == "tiled_min_events") r->tiledMinEvents = (float)value;
+    else if(n == "tiled_ticket_events") { r->tiledTicketEvents = std::max(1.0f, (float)value); r->dropGraph(); }
+    else if(n == "tiled_ticket_cost") { r->tiledTicketCost = std::max(0.0f, (float)value); r->dropGraph(); }
     else return fail(B200_ERR_INVALID, "unknown option %s", name);
     r->dropGraph();
     return B200_OK;

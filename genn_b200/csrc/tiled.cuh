@@ -19,15 +19,18 @@
 // contiguous run of about out-degree / tiles synapses per tile: 6 bytes per event with
 // 16-bit keys against the 7 (uint16 indices) to 9 (uint32) of the reference layout.
 //
-// Work: 148 CTAs x 1024 threads, one per SM.  The unit of work is a batch of 32 spikes of one
-// source group into one tile.  tiledDecideKernel, one CTA launched before, lays all batches of
-// the step out on a line in (batch element, tile, source) order, each weighted with the mean
-// run length of its (tile, source) pair, and cuts the line into 148 equally heavy stretches
-// from the ACTUAL spike counts of the step; a CTA therefore touches one or two tiles (zeroed
-// and flushed once each) whatever the firing pattern.  Inside a stretch the warps draw batch
-// tickets from a shared-memory counter; a warp reads the 32 run bounds of its batch and walks
-// the concatenation of the runs with all lanes busy (run found by a shuffle search over the
-// prefix sums), four rounds of loads in flight.
+// Work: 148 CTAs x 1024 threads, one per SM.  The unit of work is a ticket: up to 32 spikes of one source
+// group into one tile, fewer where the runs of the (tile, source) pair are long, so that a ticket stays near two
+// thousand synaptic events (one warp walks a ticket: with coarser tickets the last ones of a tile ran with the
+// other warps idle, a third of the kernel's time).  tiledDecideKernel, one CTA launched before, lays all tickets
+// of the step out on a line in (batch element, tile, source) order, each weighted with the mean run length of its
+// (tile, source) pair plus a fixed cost, and cuts the line into 148 equally heavy stretches from the ACTUAL spike
+// counts of the step; a CTA therefore touches one to three tiles (zeroed and flushed once each) whatever the firing
+// pattern.  Inside a stretch the warps draw tickets from a shared-memory counter; a warp reads the run bounds of
+// its ticket's spikes and walks the concatenation of the runs with all lanes busy, two rounds of four loads per
+// lane in flight.  The run that holds an element is found without a search: the runs that begin inside a window of
+// 32 elements make a bit mask (one warp-wide OR), the run of an element is counted from it, its offset read from
+// shared memory.
 //
 // A step with few events is cheaper on the one-reduction-per-event kernel (no tile to zero
 // and flush); tiledDecideKernel estimates the step's events from the spike counts first and
@@ -74,6 +77,16 @@ struct TiledPair                // a (tile, source group) pair: the unit the ste
     float mean_run;             // synapses of the pair per source neuron
 };
 
+// Spikes of a (tile, source group) pair that make one ticket of the tiled kernel: 32, fewer where runs are long, so that
+// a ticket stays near a thousand synaptic events (one warp walks a ticket; the last tickets of a tile run with most
+// warps idle).
+__host__ __device__ __forceinline__ unsigned int tiledTicketSpikes(float meanRun, float ticketEvents)
+{
+    unsigned int s = 32u;
+    while(s > 1u && (float)s * meanRun > ticketEvents) s >>= 1;
+    return s;
+}
+
 struct TiledLaunch
 {
     const TiledTile *tiles;
@@ -92,8 +105,11 @@ struct TiledLaunch
     unsigned int batch;
     unsigned int post_bits;
     float min_events;
+    float ticket_events;                // synaptic events a ticket is sized for (tiledTicketSpikes)
+    float ticket_cost;                  // fixed cost of a ticket when the step's work is cut into stretches, in synaptic events
     StepState *state;
     unsigned int count_events;
+    unsigned long long *profile;        // NULL, or [grid][4]: cycles of the CTA, of them outside the ticket loops; segments << 32 | tickets; cycles the warps idled at the ends of the ticket loops (mean)
 };
 
 // ---- building the private copy -----------------------------------------------------------------
@@ -193,9 +209,10 @@ tiledDecideKernel(const TiledLaunch L)
     for(unsigned int p = lo; p < hi; p++) {
         const TiledPair &P = L.pairs[p % L.num_pairs];
         const TiledSource &S = L.sources[L.tiles[P.tile].first_source + P.source];
-        const unsigned int nb = (tiledSpikeCount(S, p / L.num_pairs, k) + 31u) / 32u;
+        const unsigned int spikes = tiledTicketSpikes(P.mean_run, L.ticket_events);
+        const unsigned int nb = (tiledSpikeCount(S, p / L.num_pairs, k) + spikes - 1u) / spikes;
         L.pair_batches[p] = nb;
-        run += (double)nb * (double)(32.0f * P.mean_run + 64.0f);       // + the fixed cost of a batch
+        run += (double)nb * (double)((float)spikes * P.mean_run + L.ticket_cost);
         L.pair_prefix[p] = run;
     }
     chunk[threadIdx.x] = run;
@@ -242,8 +259,13 @@ __global__ void __launch_bounds__(TILED_BLOCK, 1)
 tiledDeliverKernel(const TiledLaunch L)
 {
     extern __shared__ float acc[];
+    __shared__ unsigned int runOffset[TILED_BLOCK];     // per warp: (start of run - elements before it) of its non-empty runs
     __shared__ unsigned int pieceStart[TILED_MAX_SOURCES + 1];      // batch tickets before each piece of the segment
-    __shared__ unsigned int piecePair[TILED_MAX_SOURCES], pieceLow[TILED_MAX_SOURCES];
+    __shared__ unsigned int pieceLow[TILED_MAX_SOURCES];
+    // what a ticket of the piece needs: the spike list of its source, the run table of (tile, source), the ticket size
+    __shared__ const unsigned int *pieceSpk[TILED_MAX_SOURCES], *pieceRuns[TILED_MAX_SOURCES];
+    __shared__ unsigned int pieceCount[TILED_MAX_SOURCES], pieceRows[TILED_MAX_SOURCES], pieceSpikes[TILED_MAX_SOURCES];
+    __shared__ float pieceWeight[TILED_MAX_SOURCES];
     __shared__ unsigned int numPieces, nextTicket, segmentEnd;
     if(!L.state->heavy) return;
     const unsigned int k = L.state->phase;
@@ -253,6 +275,14 @@ tiledDeliverKernel(const TiledLaunch L)
     const unsigned int p0 = L.cta_start[2 * blockIdx.x], b0 = L.cta_start[2 * blockIdx.x + 1];
     const unsigned int p1 = L.cta_start[2 * blockIdx.x + 2], b1 = L.cta_start[2 * blockIdx.x + 3];
     unsigned long long events = 0;
+    // clock64 record of thread 0 (option fused_profile): start, last mark, cycles outside the ticket loops, segments << 32 | tickets
+    __shared__ long long prof[5], warpEnd[TILED_BLOCK / 32];
+    const bool profiling = (L.profile != nullptr) && (threadIdx.x == 0);
+    if(profiling) {
+        prof[0] = prof[1] = clock64();
+        prof[2] = prof[3] = prof[4] = 0;
+    }
+    const unsigned int laneLess = (1u << lane) - 1u, laneLessEq = laneLess | (1u << lane);
 
     // a segment: the pieces (pair, batch range) of this CTA's stretch that lie in ONE tile of one batch element
     unsigned int p = p0;
@@ -282,8 +312,17 @@ tiledDeliverKernel(const TiledLaunch L)
                 }
                 if(lane < cnt) {
                     pieceStart[n + lane] = before + incl - tk;
-                    piecePair[n + lane] = q;
                     pieceLow[n + lane] = low;
+                    const TiledPair &P = L.pairs[q % L.num_pairs];
+                    const TiledSource &S = L.sources[T.first_source + P.source];
+                    const unsigned int slots = S.src_delay_slots;
+                    const unsigned int rslot = ringSlot(k + slots - S.axonal_delay, slots);
+                    pieceCount[n + lane] = S.spk_cnt[b * slots + rslot];
+                    pieceSpk[n + lane] = S.spk + ((unsigned long long)b * slots + rslot) * S.num_src;
+                    pieceRuns[n + lane] = L.run_start + T.table + S.row_base;
+                    pieceRows[n + lane] = S.num_src;
+                    pieceWeight[n + lane] = S.const_weight;
+                    pieceSpikes[n + lane] = tiledTicketSpikes(P.mean_run, L.ticket_events);
                 }
                 before += __shfl_sync(0xFFFFFFFFu, incl, 31);
                 n += cnt;
@@ -299,6 +338,10 @@ tiledDeliverKernel(const TiledLaunch L)
         for(unsigned int c = threadIdx.x; c < T.depth * T.stride; c += TILED_BLOCK) acc[c] = 0.0f;
         __syncthreads();
         const unsigned int tickets = pieceStart[numPieces];
+        if(profiling) {
+            prof[2] += clock64() - prof[1];
+            prof[3] += (1ll << 32) + tickets;
+        }
         for(;;) {
             unsigned int ticket = 0;
             if(lane == 0) ticket = atomicAdd(&nextTicket, 1u);
@@ -307,18 +350,14 @@ tiledDeliverKernel(const TiledLaunch L)
             unsigned int j = 0;
             while(pieceStart[j + 1] <= ticket) j++;
             const unsigned int f = pieceLow[j] + (ticket - pieceStart[j]);
-            const TiledSource &S = L.sources[T.first_source + L.pairs[piecePair[j] % L.num_pairs].source];
-            const unsigned int slots = S.src_delay_slots;
-            const unsigned int rslot = ringSlot(k + slots - S.axonal_delay, slots);
-            const unsigned int count = S.spk_cnt[b * slots + rslot];
-            const unsigned int *__restrict__ spk = S.spk + ((unsigned long long)b * slots + rslot) * S.num_src;
-            const unsigned int *__restrict__ runs = L.run_start + T.table + S.row_base;
-            const float cw = S.const_weight;
-            const unsigned int i = f * 32u + lane;
+            const unsigned int perTicket = pieceSpikes[j];
+            const unsigned int *__restrict__ runs = pieceRuns[j];
+            const float cw = pieceWeight[j];
+            const unsigned int i = f * perTicket + lane;
             unsigned int a = 0, len = 0;
-            if(i < count) {
-                const unsigned int pre = spk[i];
-                if(pre < S.num_src) {
+            if(lane < perTicket && i < pieceCount[j]) {
+                const unsigned int pre = pieceSpk[j][i];
+                if(pre < pieceRows[j]) {
                     a = runs[pre];
                     len = runs[pre + 1] - a;
                 }
@@ -333,50 +372,69 @@ tiledDeliverKernel(const TiledLaunch L)
             const unsigned int excl = incl - len;
             const unsigned int total = __shfl_sync(0xFFFFFFFFu, incl, 31);
             events += (lane == 0) ? total : 0u;
-            // the concatenation of the 32 runs, TILED_UNROLL x 32 elements per round; the loads of round
-            // r + 1 are issued before the accumulations of round r (two rounds of loads in flight)
-            unsigned int key[TILED_UNROLL], nextKey[TILED_UNROLL];
-            float w[TILED_UNROLL], nextW[TILED_UNROLL];
-            unsigned int valid = 0, nextValid = 0;      // bit u: element u of the round exists
-            auto fetch = [&](unsigned int x0) {
-                nextValid = 0;
+            // The non-empty runs, in order, at the front of the warp's offset table: element x of the
+            // concatenation, in run c, lies at x + offset[c] of the tile's arrays.
+            unsigned int *offs = runOffset + (threadIdx.x & ~31u);
+            const unsigned int nonEmpty = __ballot_sync(0xFFFFFFFFu, len != 0u);
+            __syncwarp();                                   // (the previous ticket's reads of the table)
+            if(len) offs[__popc(nonEmpty & laneLess)] = a - excl;
+            __syncwarp();
+            // Non-empty runs begin at distinct elements.  For a window of 32 elements the lanes OR together one
+            // bit per run that begins inside it; the run of element j of the window is the number of runs
+            // begun before the window plus the bits up to j, minus one.
+            const unsigned int head = len ? excl : 0xFFFFFFFFu;
+            unsigned int begun = 0;
+            struct Round { unsigned int key[TILED_UNROLL]; float w[TILED_UNROLL]; unsigned int valid; };
+            auto fetch = [&](Round &R, unsigned int x0) {
+                R.valid = 0;
 #pragma unroll
                 for(unsigned int u = 0; u < TILED_UNROLL; u++) {
-                    const unsigned int x = x0 + u * 32u + lane;
-                    // the run that holds element x: the last one whose exclusive sum is <= x
-                    unsigned int lo = 0;
-#pragma unroll
-                    for(unsigned int st = 16; st > 0; st >>= 1) {
-                        const unsigned int v = __shfl_sync(0xFFFFFFFFu, excl, lo + st);
-                        if(v <= x) lo += st;
-                    }
-                    const unsigned int ra = __shfl_sync(0xFFFFFFFFu, a, lo);
-                    const unsigned int re = __shfl_sync(0xFFFFFFFFu, excl, lo);
+                    const unsigned int first = x0 + u * 32u;
+                    unsigned int bit;       // (shl gives 0 for a shift of 32 or more: a head before or beyond the window)
+                    asm("shl.b32 %0, %1, %2;" : "=r"(bit) : "r"(1u), "r"(head - first));
+                    const unsigned int heads = __reduce_or_sync(0xFFFFFFFFu, bit);
+                    const unsigned int c = begun + __popc(heads & laneLessEq) - 1u;
+                    begun += __popc(heads);
+                    const unsigned int x = first + lane;
                     if(x < total) {
-                        const unsigned int pos = ra + (x - re);
-                        nextKey[u] = keys[pos];
-                        nextW[u] = HAS_W ? L.weights[pos] : cw;
-                        nextValid |= 1u << u;
+                        const unsigned int pos = x + offs[c];
+                        R.key[u] = keys[pos];
+                        R.w[u] = HAS_W ? L.weights[pos] : cw;
+                        R.valid |= 1u << u;
                     }
                 }
             };
-            if(total) fetch(0);
-            for(unsigned int x0 = 0; x0 < total; x0 += 32u * TILED_UNROLL) {
-                valid = nextValid;
+            auto deliver = [&](const Round &R) {
 #pragma unroll
                 for(unsigned int u = 0; u < TILED_UNROLL; u++) {
-                    key[u] = nextKey[u];
-                    w[u] = nextW[u];
+                    if(R.valid & (1u << u)) sharedAdd(&acc[(R.key[u] >> L.post_bits) * T.stride + (R.key[u] & postMask)], R.w[u]);
                 }
-                if(x0 + 32u * TILED_UNROLL < total) fetch(x0 + 32u * TILED_UNROLL);
-#pragma unroll
-                for(unsigned int u = 0; u < TILED_UNROLL; u++) {
-                    if(valid & (1u << u)) sharedAdd(&acc[(key[u] >> L.post_bits) * T.stride + (key[u] & postMask)], w[u]);
-                }
+            };
+            // two rounds of loads in flight, in two sets of registers
+            constexpr unsigned int ROUND = 32u * TILED_UNROLL;
+            Round A, B;
+            if(total) fetch(A, 0);
+            for(unsigned int x0 = 0; x0 < total; x0 += 2u * ROUND) {
+                const bool second = x0 + ROUND < total;
+                if(second) fetch(B, x0 + ROUND);
+                deliver(A);
+                if(!second) break;
+                if(x0 + 2u * ROUND < total) fetch(A, x0 + 2u * ROUND);
+                deliver(B);
             }
         }
         // every touched cell goes to L2 once
+        if(L.profile && lane == 0) warpEnd[threadIdx.x >> 5] = clock64();
         __syncthreads();
+        if(profiling) {
+            prof[1] = clock64();
+            long long last = warpEnd[0], sum = 0;
+            for(unsigned int w = 0; w < TILED_BLOCK / 32; w++) {
+                last = max(last, warpEnd[w]);
+                sum += warpEnd[w];
+            }
+            prof[4] += last - sum / (TILED_BLOCK / 32);     // cycles the warps idled on average while the last ticket ran
+        }
         {
             const unsigned int front = (T.depth > 1u) ? ringSlot(k + 1u, T.depth) : 0u;
             float *base = T.target + (unsigned long long)b * T.depth * T.num_trg + T.first_trg;
@@ -416,5 +474,13 @@ tiledDeliverKernel(const TiledLaunch L)
         __syncthreads();
     }
     if(L.count_events && lane == 0 && events) atomicAdd(&L.state->synaptic_events, events);
+    if(profiling) {
+        const long long now = clock64();
+        unsigned long long *out = L.profile + 4ull * blockIdx.x;
+        out[0] = (unsigned long long)(now - prof[0]);
+        out[1] = (unsigned long long)(prof[2] + (now - prof[1]));
+        out[2] = (unsigned long long)prof[3];
+        out[3] = (unsigned long long)prof[4];
+    }
 }
 }   // namespace b200

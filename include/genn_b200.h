@@ -365,7 +365,9 @@ int  b200_get_counter(b200_runner *r, const char *name, uint64_t *value);
  * one queue, 2 .. 2048; what does not fit goes the direct way), "use_tiled" / "tiled_min_events" (target-tiled SPARSE delivery of steps
  * with at least that many estimated events on the one-launch-per-kernel path; 0: every step.  The tiled kernels
  * are launched only while the largest spike count of the steps before says such a step may come: counter
- * "tiled_armed"; b200_update_synapses always launches them),
+ * "tiled_armed"; b200_update_synapses always launches them), "tiled_ticket_events" / "tiled_ticket_cost" (the
+ * tiled kernel's unit of work, handed to one warp, is sized for about that many synaptic events, default 2048;
+ * its fixed cost in synaptic events when a step's work is cut into equal stretches per CTA, default 256),
  * "barrier_spin_limit" / "exchange_spin_limit" (polls) and "stream_wait_cycles" (SM cycles): how long a wait
  * inside a persistent kernel lasts before the launch gives up and b200_synchronize reports
  * B200_ERR_DEVICE_CHECK (defaults: tens of milliseconds; about two seconds). */

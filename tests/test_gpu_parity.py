@@ -27,7 +27,9 @@ PATHS = {"persistent": (1, 1, 1, 1, -1), "persistent-emit": (1, 0, 1, 1, -1),
          "persistent-plain": (1, 0, 0, 0, -1), "per-kernel": (0, 1, 1, 1, -1),
          # one launch per kernel with EVERY step delivered by the target-tiled kernel (shared-memory
          # accumulation over the private tile-major copy), which production takes only for heavy steps
-         "per-kernel-tiled": (0, 1, 1, 1, -1)}
+         "per-kernel-tiled": (0, 1, 1, 1, -1),
+         # the same with tickets of at most four synaptic events (one spike each, a ticket per run)
+         "per-kernel-tiled-small-tickets": (0, 1, 1, 1, -1)}
 # networks whose SPARSE groups the target-tiled kernel serves (non-learning)
 TILED_CASES = {"ff_sparse", "c1_full", "ff_sparse_narrow", "potjans_mini", "potjans_mini_d1", "cond_delay", "izhikevich"}
 # networks whose every synapse has a dendritic delay of at least one step
@@ -43,8 +45,10 @@ def _select(rt, path, name=None):
     rt.set_option("use_emit", emit)
     rt.set_option("use_split", split)
     rt.set_option("stream_warps", stream)
-    if path == "per-kernel-tiled":
+    if path.startswith("per-kernel-tiled"):
         rt.set_option("tiled_min_events", 0)
+        if path.endswith("small-tickets"):
+            rt.set_option("tiled_ticket_events", 4)
         if name in TILED_CASES:
             assert rt.counter("tiled_ready") == 1 and rt.counter("tiled_synapses") > 0
     if name is not None and rt.step_path()[0] >= 1:
@@ -87,7 +91,7 @@ def test_step_by_step_matches_reference_golden(name, path):
     _select(rt, path, name)
     got = helpers.run_and_collect(_Adapter(rt), net, steps, dump_every)
     helpers.compare(got, helpers.load_golden(name), exact_state=False, rtol=RTOL, atol=ATOL)
-    if path == "per-kernel-tiled" and name in TILED_CASES:
+    if path.startswith("per-kernel-tiled") and name in TILED_CASES:
         assert rt.counter("heavy") == 1, "the tiled kernel was meant to deliver every step"
     rt.close()
 

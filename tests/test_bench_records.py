@@ -6,6 +6,8 @@ import os
 import subprocess
 import sys
 
+import numpy as np
+
 REPO = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, REPO)
 
@@ -31,3 +33,26 @@ def test_bench_command_line():
     assert out.returncode == 0
     for flag in ("--gpus", "--steps", "--warmup", "--impl", "--workload", "--probe", "--parity-seconds"):
         assert flag in out.stdout
+
+
+def test_recording_words_are_rebuilt_from_the_pulled_pairs():
+    """Host side of the recording pull: the (index, word) pairs the device listed, in any order, give back
+    each population's array of bit words; the word index of a population starts at its base."""
+    import types
+    from genn_b200.runtime import Runtime
+    rng = np.random.default_rng(5)
+    shapes = {"a": (7, 1, 3), "b": (7, 2, 5)}
+    arrays, layout, pairs, base = {}, {}, [], 0
+    for name, shape in shapes.items():
+        words = np.where(rng.random(shape) < 0.2, rng.integers(1, 2 ** 32, size=shape, dtype=np.uint64), 0).astype(np.uint32)
+        arrays[name], layout[name] = words, (base, shape)
+        idx = np.flatnonzero(words.reshape(-1))
+        pairs += [(base + i, words.reshape(-1)[i]) for i in idx]
+        base += words.size
+    pairs = np.array(pairs, dtype=np.uint32)[rng.permutation(len(pairs))]
+    fake = types.SimpleNamespace(_rec_pairs=pairs, _rec_layout=layout, _rec_host={})
+    for name in shapes:
+        assert np.array_equal(Runtime._recording_words(fake, name), arrays[name])
+    # a recording that was copied whole is returned as it came
+    fake = types.SimpleNamespace(_rec_pairs=None, _rec_layout={}, _rec_host=arrays)
+    assert Runtime._recording_words(fake, "b") is arrays["b"]

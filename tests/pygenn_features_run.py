@@ -18,6 +18,10 @@ def main():
         return 5
     sys.path.insert(0, SITE)
     sys.path.insert(0, REPO)
+    try:
+        import bitarray  # noqa: F401  (test_custom_connectivity_update.py imports it)
+    except ImportError:
+        sys.path.insert(0, os.path.join(REPO, "tests", "standins"))
     os.environ.setdefault("CXX", "/usr/bin/g++")
     os.environ.setdefault("CC", "/usr/bin/gcc")
     os.chdir(os.path.join(SITE, "features"))       # the tests open their .npy fixtures by relative path

@@ -6,8 +6,10 @@ reference's test files beside them; genn_b200.pygenn_plugin.register() adds the 
 table.  The tests' `backend` fixture is parametrised over that table, so `-k b200` runs every test on the
 plug-in, at batch size 1 and 5.
 
-Every feature file of the reference runs except test_custom_connectivity_update.py (it imports `bitarray`,
-which this image does not have) and test_cuda_interface.py (CuPy interop of the CUDA backend's arrays)."""
+Every feature file of the reference runs except test_cuda_interface.py (CuPy interop of the CUDA backend's
+arrays).  test_custom_connectivity_update.py imports `bitarray`, which this image does not have:
+tests/standins/bitarray supplies the few operations it uses (checked against the reference's CPU backend, on
+which the file passes with it)."""
 import os
 import re
 import subprocess
@@ -20,7 +22,7 @@ SITE = os.path.join(REPO, "oracle", "_ref", "pygenn_site")
 FILES = ["test_event_propagation.py", "test_sparse.py", "test_wu_vars.py", "test_recording.py", "test_custom_update.py",
          "test_pre_post_neuron_vars.py", "test_post_psm_vars.py", "test_event_times.py", "test_continuous_propagation.py",
          "test_egp.py", "test_model_lifecycle.py", "test_model_timing.py", "test_connect_init.py", "test_num.py", "test_rng.py",
-         "test_dynamic_param.py"]
+         "test_dynamic_param.py", "test_custom_connectivity_update.py"]
 
 
 @pytest.mark.gpu
@@ -39,7 +41,7 @@ def test_reference_feature_suite_passes_on_the_b200_backend():
     tail = res.stdout[-3000:] + res.stderr[-2000:]
     assert res.returncode == 0, tail
     passed = re.search(r"(\d+) passed", res.stdout)
-    assert passed and int(passed.group(1)) >= 130, tail
+    assert passed and int(passed.group(1)) >= 138, tail
     print(res.stdout[-300:])
 
 

@@ -323,7 +323,7 @@ def reference_arm(args):
         "config": {"workload": f"Potjans-Diesmann microcircuit architecture x{args.ref_scale:g}: {r['neurons']} LIF neurons, "
                                f"published in-degrees ({r['synapses']} synapses, drawn on the host), SPARSE with dendritic "
                                f"delays, PoissonExp background, dt=0.1 ms; one bench step = {args.block} time steps "
-                               f"(0.1 s biological)",
+                               f"({args.block * 1e-4:g} s biological)",
                    "parallelism": "the reference's CPU backend is single-threaded; at N > 1 it runs the x1 network "
                                   "(a bounded sample of the xN workload: same in-degrees, same per-neuron work)",
                    "timing": "wall clock around the reference's stepTime loop (all warm-up and timed steps)"},
@@ -1038,7 +1038,7 @@ def main():
             "us_per_timestep": ms * 1e3 / (args.steps * block),
             "config": {"workload": f"Potjans-Diesmann microcircuit architecture x{scale:g}: {n_neurons} LIF neurons, "
                                    f"published in-degrees, SPARSE with dendritic delays, PoissonExp background, "
-                                   f"dt=0.1 ms; one bench step = {block} time steps (0.1 s biological)",
+                                   f"dt=0.1 ms; one bench step = {block} time steps ({block * 1e-4:g} s biological)",
                        "parallelism": f"postsynaptic sharding over {world} GPU(s)" if world > 1 else "single GPU",
                        "schedule": ["persistent kernel, every synapse delivered before the neuron update",
                                     "persistent kernel, split delivery: synapses that arrive in the same step before the "

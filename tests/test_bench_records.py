@@ -56,3 +56,27 @@ def test_recording_words_are_rebuilt_from_the_pulled_pairs():
     # a recording that was copied whole is returned as it came
     fake = types.SimpleNamespace(_rec_pairs=None, _rec_layout={}, _rec_host=arrays)
     assert Runtime._recording_words(fake, "b") is arrays["b"]
+
+
+def test_reference_arm_prints_the_contract_line_on_cpu():
+    """`bench.py --impl reference` runs the reference's CPU backend (no GPU involved): one JSON line with the
+    arm's keys, here on a hundredth of the network so that it ends in seconds."""
+    res = subprocess.run([sys.executable, os.path.join(REPO, "bench.py"), "--impl", "reference", "--ref-scale", "0.01",
+                          "--steps", "1", "--warmup", "3", "--block", "100"],
+                         capture_output=True, text=True, timeout=600, cwd=REPO)
+    assert res.returncode == 0, res.stderr[-2000:]
+    line = json.loads([l for l in res.stdout.splitlines() if l.startswith("{")][-1])
+    assert line["impl"] == "reference" and line["n_gpus"] == 1 and line["higher_is_better"] is True
+    assert line["metric"].startswith("synaptic events/s") and line["unit"] == "synaptic events/s" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] in ("reference", "port") and line["cpu_baseline"]["cores"] == 1
+    assert line["cpu_baseline"]["value"] == line["value"]
+    assert line["e2e"] == {"value": line["value"], "unit": line["unit"], "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}
+    assert "0.01 s biological" in line["config"]["workload"]
+
+
+def test_reference_arm_runs_on_rank_zero_only():
+    """Launched one process per GPU, the arm is rank 0's work: every other rank leaves at once, silently."""
+    env = dict(os.environ, RANK="1", LOCAL_RANK="1", WORLD_SIZE="2")
+    res = subprocess.run([sys.executable, os.path.join(REPO, "bench.py"), "--impl", "reference", "--gpus", "2", "--steps", "1"],
+                         capture_output=True, text=True, timeout=300, cwd=REPO, env=env)
+    assert res.returncode == 0 and res.stdout.strip() == ""

@@ -361,15 +361,15 @@ def run_c2(args):
     clocks = sampler.stop()
     ev1, sp1, l1 = rt.counter("synaptic_events"), rt.counter("spikes"), rt.kernel_launches
     seconds, sim_seconds = ms * 1e-3, args.steps * block * DT_MS * 1e-3
-    d2h = sum(a.nbytes for n, a in rt.plan.arrays.items() if n.endswith(".record"))
     model.step_time(block)
     model.pull_recording_buffers_from_device()
-    e0 = rt.counter("synaptic_events")
+    e0, moved0 = rt.counter("synaptic_events"), rt.factory.d2h_bytes
     t0 = time.perf_counter()
     for _ in range(args.steps):
         model.step_time(block)
         model.pull_recording_buffers_from_device()
     e2e_s = time.perf_counter() - t0
+    d2h = (rt.factory.d2h_bytes - moved0) / max(1, args.steps)      # what the pulls moved (non-zero recording words as pairs)
     e2e_ev = rt.counter("synaptic_events") - e0
     n = sum(p.n for p in rt.net.pops)
     bytes_algo = (ev1 - ev0) * bytes_per_event(rt.net) + (sp1 - sp0) * ALGO_BYTES_PER_SPIKE
@@ -435,15 +435,15 @@ def run_c4(args):
     pre_s, neu_s = rt.timer("presynaptic_update"), rt.timer("neuron_update")
     rt.enable_timing(False)
     # end to end: steps plus the spike recording pulled into page-locked memory
-    d2h = sum(a.nbytes for n, a in rt.plan.arrays.items() if n.endswith(".record"))
     model.step_time(block)
     model.pull_recording_buffers_from_device()
-    e0 = rt.counter("synaptic_events")
+    e0, moved0 = rt.counter("synaptic_events"), rt.factory.d2h_bytes
     t0 = time.perf_counter()
     for _ in range(args.steps):
         model.step_time(block)
         model.pull_recording_buffers_from_device()
     e2e_s = time.perf_counter() - t0
+    d2h = (rt.factory.d2h_bytes - moved0) / max(1, args.steps)      # what the pulls moved (non-zero recording words as pairs)
     e2e_ev = rt.counter("synaptic_events") - e0
     n = sum(p.n for p in rt.net.pops)
     line = {"metric": "synaptic events/s (PROCEDURAL connectivity stress test)", "value": (ev1 - ev0) / seconds,
@@ -895,7 +895,8 @@ def main():
         model.pull_recording_buffers_from_device()
     barrier()
     # what the pulls really moved: the recording's non-zero words as (index, word) pairs
-    d2h_moved = (rt.factory.d2h_bytes - d2h0) / max(1, args.steps)
+    d2h_moved = allreduce(float(rt.factory.d2h_bytes - d2h0) / max(1, args.steps), dist.ReduceOp.SUM if world > 1 else None)
+    d2h = allreduce(float(d2h), dist.ReduceOp.SUM if world > 1 else None)      # (whole job: every process pulls its slice)
     e2e_seconds = allreduce(time.perf_counter() - t0, dist.ReduceOp.MAX if world > 1 else None)
     e2e_events = allreduce(float(rt.counter("synaptic_events") - e2e_ev0), dist.ReduceOp.SUM if world > 1 else None)
     # firing rates from the last pulled recording (sanity: the network is in its asynchronous state)
